@@ -1,0 +1,27 @@
+"""B200-native YemongPolicy trunk: masked spatial attention over ship/field tokens fused
+with the per-ship Griffin RG-LRU recurrence, as hand-written sm_100a CUDA kernels behind the
+reference's own ``nn.Module`` signatures.
+
+    from boost_and_broadside_b200 import ModelConfig, TransformerBlock, YemongBlock, YemongTrunk
+
+The modules mirror ``boost_and_broadside.models.yemong.{attention,griffin}`` of the
+reference (same constructor arguments, parameter names and forward signatures) and call
+the C-ABI library ``libbnb_trunk.so`` (include/bnb_trunk.h).  There is no CPU path.
+"""
+
+from .config import ModelConfig
+from .yemong.attention import GatedMLP, TransformerBlock
+from .yemong.griffin import CONV_KERNEL, RGLRU, GriffinTemporalBlock, YemongBlock
+from .yemong.trunk import YemongTrunk, RaggedBatch
+
+__all__ = [
+    "CONV_KERNEL",
+    "GatedMLP",
+    "GriffinTemporalBlock",
+    "ModelConfig",
+    "RGLRU",
+    "RaggedBatch",
+    "TransformerBlock",
+    "YemongBlock",
+    "YemongTrunk",
+]

@@ -1,0 +1,175 @@
+"""ctypes binding of ``libbnb_trunk.so`` (declared in include/bnb_trunk.h).
+
+The library is the only compute path: if it is missing or does not export the declared
+symbols, importing this module raises.  Nothing here falls back to PyTorch arithmetic.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libbnb_trunk.so")
+
+BNB_FP32, BNB_BF16 = 0, 1
+ENGINE_AUTO, ENGINE_SIMT, ENGINE_TENSOR = 0, 1, 2
+ABI_VERSION = 1
+
+_fp = C.c_void_p
+
+
+class SpatialWeights(C.Structure):
+    _fields_ = [(n, _fp) for n in ("norm1_w", "qkv_w", "out_w", "norm2_w", "gate_w", "up_w", "down_w", "packed")]
+
+
+class TemporalWeights(C.Structure):
+    _fields_ = [
+        (n, _fp)
+        for n in (
+            "norm1_w", "linear1_w", "conv_w", "conv_b", "log_lambda", "a_w", "a_b", "x_w", "x_b",
+            "linear2_w", "out_w", "norm2_w", "gate_w", "up_w", "down_w", "field_sub_w", "packed",
+        )
+    ]
+
+
+class Batch(C.Structure):
+    _fields_ = [
+        ("n_envs", C.c_int32),
+        ("tokens_per_env", C.c_int32),
+        ("ships_per_env", C.c_int32),
+        ("max_tokens_per_env", C.c_int32),
+        ("total_tokens", C.c_int32),
+        ("total_ships", C.c_int32),
+        ("tok_off", _fp),
+        ("ship_off", _fp),
+    ]
+
+
+EXPORTS = {
+    "bnb_abi_version": (C.c_int, []),
+    "bnb_status_string": (C.c_char_p, [C.c_int]),
+    "bnb_supported": (C.c_int, [C.c_int] * 5),
+    "bnb_scratch_bytes": (C.c_size_t, [C.c_int, C.POINTER(Batch), C.c_int]),
+    "bnb_spatial_block_fwd": (
+        C.c_int,
+        [C.POINTER(SpatialWeights), C.c_int, C.c_int, _fp, _fp, _fp, C.POINTER(Batch), C.c_int, C.c_int, C.c_int,
+         _fp, C.c_size_t, _fp],
+    ),
+    "bnb_temporal_block_fwd": (
+        C.c_int,
+        [C.POINTER(TemporalWeights), C.c_int, _fp, _fp, _fp, _fp, _fp, C.POINTER(Batch), C.c_int, C.c_int, C.c_int,
+         _fp, C.c_size_t, _fp],
+    ),
+    "bnb_trunk_step": (
+        C.c_int,
+        [C.POINTER(SpatialWeights), C.POINTER(TemporalWeights), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+         _fp, _fp, _fp, _fp, _fp, _fp, C.POINTER(Batch), C.c_int, C.c_int, _fp, C.c_size_t, _fp],
+    ),
+    "bnb_trunk_sequence": (
+        C.c_int,
+        [C.POINTER(SpatialWeights), C.POINTER(TemporalWeights), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+         _fp, _fp, _fp, _fp, _fp, _fp, C.POINTER(Batch), C.c_int, C.c_int, C.c_int, _fp, C.c_size_t, _fp],
+    ),
+    "bnb_reset_hidden": (C.c_int, [_fp, _fp, _fp, C.c_int, C.c_int, C.POINTER(Batch), _fp]),
+    "bnb_packed_spatial_bytes": (C.c_size_t, [C.c_int]),
+    "bnb_packed_temporal_bytes": (C.c_size_t, [C.c_int]),
+    "bnb_pack_spatial": (C.c_int, [C.POINTER(SpatialWeights), C.c_int, C.c_int, _fp, _fp]),
+    "bnb_pack_temporal": (C.c_int, [C.POINTER(TemporalWeights), C.c_int, _fp, _fp]),
+}
+
+
+def load_library(path: str = LIB_PATH) -> C.CDLL:
+    if not os.path.exists(path):
+        raise RuntimeError(
+            f"{path} is missing: build it with `python boost-and-broadside_b200/build.py` "
+            "(nvcc, sm_100a). The trunk has no CPU or PyTorch fallback."
+        )
+    lib = C.CDLL(path)
+    for name, (res, args) in EXPORTS.items():
+        fn = getattr(lib, name)  # AttributeError if the symbol is not exported
+        fn.restype = res
+        fn.argtypes = args
+    if lib.bnb_abi_version() != ABI_VERSION:
+        raise RuntimeError(f"libbnb_trunk.so has ABI {lib.bnb_abi_version()}, binding expects {ABI_VERSION}")
+    return lib
+
+
+lib = load_library()
+
+
+class BnbError(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+    def __init__(self, fn: str, status: int):
+        self.status = status
+        super().__init__(f"{fn}: {lib.bnb_status_string(status).decode()} (status {status})")
+
+
+def check(fn: str, status: int) -> None:
+    if status != 0:
+        if status == 3:  # BNB_ERR_UNSUPPORTED_DIMS
+            raise ValueError(f"{fn}: {lib.bnb_status_string(status).decode()}")
+        raise BnbError(fn, status)
+
+
+def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def require_cuda(t: torch.Tensor, what: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(
+            f"{what} is on {t.device}; the trunk kernels run on CUDA only (sm_100a) and have no CPU path"
+        )
+
+
+def f32c(t: torch.Tensor) -> torch.Tensor:
+    """float32, contiguous view or copy of t."""
+    if t.dtype != torch.float32:
+        t = t.float()
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def u8(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    """One byte per element view of a bool tensor (or a converted copy)."""
+    if t is None:
+        return None
+    if t.dtype == torch.bool:
+        t = t if t.is_contiguous() else t.contiguous()
+        return t.view(torch.uint8)
+    return (t != 0).contiguous().view(torch.uint8)
+
+
+def current_precision(device: torch.device) -> int:
+    """BNB_BF16 inside torch.autocast(device, bfloat16), else BNB_FP32."""
+    if torch.is_autocast_enabled(device.type):
+        dt = torch.get_autocast_dtype(device.type)
+        if dt != torch.bfloat16:
+            raise RuntimeError(f"autocast dtype {dt} is not supported by the trunk kernels (bfloat16 only)")
+        return BNB_BF16
+    return BNB_FP32
+
+
+def stream_handle(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+_scratch: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def scratch_for(device: torch.device, nbytes: int) -> torch.Tensor:
+    """A scratch buffer owned by torch's allocator, grown on demand, one per device and stream."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream_handle(device))
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _scratch[key] = buf
+    return buf
+
+
+def uniform_batch(n_envs: int, tokens: int, ships: int) -> Batch:
+    return Batch(n_envs, tokens, ships, tokens, n_envs * tokens, n_envs * ships, None, None)

@@ -1,0 +1,283 @@
+// C ABI of the trunk kernels: argument validation and engine dispatch.
+// Every entry point is declared, with the reference interface it replaces, in
+// include/bnb_trunk.h.
+#include <cuda_runtime.h>
+
+#include "bnb_trunk.h"
+#include "exact_kernels.h"
+#include "tensor_kernels.h"
+
+namespace {
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_dims(int D, int H) {
+  if (D <= 0 || H <= 0 || D % H != 0) return BNB_ERR_BAD_ARGUMENT;
+  if (D % 32 != 0 || D > 128) return BNB_ERR_UNSUPPORTED_DIMS;
+  int dh = D / H;
+  if (dh != 8 && dh != 16 && dh != 32 && dh != 64) return BNB_ERR_UNSUPPORTED_DIMS;
+  return BNB_OK;
+}
+
+int check_batch(const BnbBatch* b) {
+  if (!b) return BNB_ERR_NULL_POINTER;
+  if (b->n_envs < 0 || b->total_tokens < 0 || b->total_ships < 0 || b->total_ships > b->total_tokens)
+    return BNB_ERR_BAD_ARGUMENT;
+  if ((b->tok_off == nullptr) != (b->ship_off == nullptr)) return BNB_ERR_BAD_ARGUMENT;
+  if (!b->tok_off) {
+    if (b->tokens_per_env < 0 || b->ships_per_env < 0 || b->ships_per_env > b->tokens_per_env)
+      return BNB_ERR_BAD_ARGUMENT;
+    if ((long long)b->n_envs * b->tokens_per_env != b->total_tokens) return BNB_ERR_BAD_ARGUMENT;
+    if ((long long)b->n_envs * b->ships_per_env != b->total_ships) return BNB_ERR_BAD_ARGUMENT;
+    if (b->max_tokens_per_env < b->tokens_per_env) return BNB_ERR_BAD_ARGUMENT;
+  } else if (b->max_tokens_per_env <= 0) {
+    return BNB_ERR_BAD_ARGUMENT;
+  }
+  return BNB_OK;
+}
+
+int check_spatial(const BnbSpatialWeights* w) {
+  if (!w) return BNB_ERR_NULL_POINTER;
+  const void* ps[] = {w->norm1_w, w->qkv_w, w->out_w, w->norm2_w, w->gate_w, w->up_w, w->down_w};
+  for (const void* p : ps) {
+    if (!p) return BNB_ERR_NULL_POINTER;
+    if (!aligned16(p)) return BNB_ERR_MISALIGNED;
+  }
+  return BNB_OK;
+}
+
+int check_temporal(const BnbTemporalWeights* w, bool need_field) {
+  if (!w) return BNB_ERR_NULL_POINTER;
+  const void* ps[] = {w->norm1_w, w->linear1_w, w->conv_w, w->conv_b, w->log_lambda, w->a_w, w->a_b, w->x_w,
+                      w->x_b, w->linear2_w, w->out_w, w->norm2_w, w->gate_w, w->up_w, w->down_w};
+  for (const void* p : ps) {
+    if (!p) return BNB_ERR_NULL_POINTER;
+    if (!aligned16(p)) return BNB_ERR_MISALIGNED;
+  }
+  if (need_field) {
+    if (!w->field_sub_w) return BNB_ERR_NULL_POINTER;
+    if (!aligned16(w->field_sub_w)) return BNB_ERR_MISALIGNED;
+  }
+  return BNB_OK;
+}
+
+size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct Scratch {
+  float* qkv;
+  float* o;
+};
+
+// SIMT spatial scratch: qkv (rows, 3D) then o (rows, D), float32.
+int carve(void* scratch, size_t bytes, size_t n_rows, int D, Scratch* out) {
+  size_t need = round_up(n_rows * 3 * D * sizeof(float), 256) + round_up(n_rows * D * sizeof(float), 256);
+  if (need == 0) { out->qkv = out->o = nullptr; return BNB_OK; }
+  if (!scratch) return BNB_ERR_NULL_POINTER;
+  if (!aligned16(scratch)) return BNB_ERR_MISALIGNED;
+  if (bytes < need) return BNB_ERR_SCRATCH_TOO_SMALL;
+  out->qkv = static_cast<float*>(scratch);
+  out->o = reinterpret_cast<float*>(static_cast<char*>(scratch) + round_up(n_rows * 3 * D * sizeof(float), 256));
+  return BNB_OK;
+}
+
+bool use_tensor(int precision, int engine, int D, int H, const BnbBatch* b) {
+  if (precision != BNB_BF16 || engine == BNB_ENGINE_SIMT) return false;
+  return bnb::tensor::supported(D, H, b->max_tokens_per_env);
+}
+
+}  // namespace
+
+extern "C" {
+
+int bnb_abi_version(void) { return BNB_ABI_VERSION; }
+
+const char* bnb_status_string(int status) {
+  switch (status) {
+    case BNB_OK: return "ok";
+    case BNB_ERR_NULL_POINTER: return "a required pointer is null";
+    case BNB_ERR_MISALIGNED: return "a pointer is not 16-byte aligned";
+    case BNB_ERR_UNSUPPORTED_DIMS: return "d_model / n_heads / engine combination is not built";
+    case BNB_ERR_TOO_MANY_TOKENS: return "an environment holds more tokens than the kernels take";
+    case BNB_ERR_BAD_ARGUMENT: return "inconsistent argument";
+    case BNB_ERR_SCRATCH_TOO_SMALL: return "scratch buffer smaller than bnb_scratch_bytes";
+    case BNB_ERR_LAUNCH: return "CUDA launch failed";
+    case BNB_ERR_NO_DEVICE: return "no CUDA device";
+    default: return "unknown status";
+  }
+}
+
+int bnb_supported(int d_model, int n_heads, int max_tokens_per_env, int precision, int engine) {
+  if (check_dims(d_model, n_heads) != BNB_OK) return 0;
+  if (max_tokens_per_env <= 0) return 0;
+  if (precision != BNB_FP32 && precision != BNB_BF16) return 0;
+  if (engine == BNB_ENGINE_TENSOR)
+    return precision == BNB_BF16 && bnb::tensor::supported(d_model, n_heads, max_tokens_per_env) ? 1 : 0;
+  return 1;
+}
+
+size_t bnb_scratch_bytes(int d_model, const BnbBatch* batch, int timesteps) {
+  if (!batch || d_model <= 0 || timesteps <= 0) return 0;
+  size_t n_rows = (size_t)timesteps * (size_t)batch->total_tokens;
+  size_t simt = round_up(n_rows * 3 * d_model * sizeof(float), 256) + round_up(n_rows * d_model * sizeof(float), 256);
+  size_t tc = bnb::tensor::scratch_bytes(d_model, *batch, timesteps);
+  return (simt > tc ? simt : tc) + 256;
+}
+
+int bnb_spatial_block_fwd(const BnbSpatialWeights* w, int d_model, int n_heads, const float* x,
+                          const uint8_t* alive, float* y, const BnbBatch* batch, int n_groups,
+                          int precision, int engine, void* scratch, size_t scratch_bytes, void* stream) {
+  int st = check_dims(d_model, n_heads);
+  if (st) return st;
+  if ((st = check_batch(batch))) return st;
+  if ((st = check_spatial(w))) return st;
+  if (n_groups < 0) return BNB_ERR_BAD_ARGUMENT;
+  if (precision != BNB_FP32 && precision != BNB_BF16) return BNB_ERR_BAD_ARGUMENT;
+  size_t n_rows = (size_t)n_groups * batch->total_tokens;
+  if (n_rows == 0) return BNB_OK;
+  if (!x || !y) return BNB_ERR_NULL_POINTER;
+  if (!aligned16(x) || !aligned16(y)) return BNB_ERR_MISALIGNED;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  if (use_tensor(precision, engine, d_model, n_heads, batch))
+    return bnb::tensor::spatial_block(*w, d_model, n_heads, x, alive, y, *batch, n_groups, scratch, scratch_bytes, cs);
+  if (engine == BNB_ENGINE_TENSOR) return BNB_ERR_UNSUPPORTED_DIMS;
+  Scratch s;
+  if ((st = carve(scratch, scratch_bytes, n_rows, d_model, &s))) return st;
+  return bnb::exact::spatial_block(*w, d_model, n_heads, x, alive, y, *batch, n_groups, precision == BNB_BF16,
+                                   s.qkv, s.o, cs);
+}
+
+int bnb_temporal_block_fwd(const BnbTemporalWeights* w, int d_model, const float* x, float* y,
+                           const float* hidden_in, float* hidden_out, const uint8_t* done,
+                           const BnbBatch* batch, int timesteps, int precision, int engine,
+                           void* scratch, size_t scratch_bytes, void* stream) {
+  int st = check_dims(d_model, d_model / 32);
+  if (st) return st;
+  if ((st = check_batch(batch))) return st;
+  if ((st = check_temporal(w, batch->total_tokens > batch->total_ships))) return st;
+  if (timesteps < 1) return BNB_ERR_BAD_ARGUMENT;
+  if (precision != BNB_FP32 && precision != BNB_BF16) return BNB_ERR_BAD_ARGUMENT;
+  if (batch->total_tokens == 0) return BNB_OK;
+  if (!x || !y) return BNB_ERR_NULL_POINTER;
+  if (batch->total_ships > 0 && (!hidden_in || !hidden_out)) return BNB_ERR_NULL_POINTER;
+  if (!aligned16(x) || !aligned16(y) || !aligned16(hidden_in) || !aligned16(hidden_out)) return BNB_ERR_MISALIGNED;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  if (precision == BNB_BF16 && engine != BNB_ENGINE_SIMT && bnb::tensor::supported(d_model, d_model / 32, 1))
+    return bnb::tensor::temporal_block(*w, d_model, x, y, hidden_in, hidden_out, done, nullptr, *batch, timesteps,
+                                       scratch, scratch_bytes, cs);
+  if (engine == BNB_ENGINE_TENSOR) return BNB_ERR_UNSUPPORTED_DIMS;
+  return bnb::exact::temporal_block(*w, d_model, x, y, hidden_in, hidden_out, done, nullptr, *batch, timesteps,
+                                    precision == BNB_BF16, cs);
+}
+
+static int trunk_common(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal, int n_blocks,
+                        int n_spatial, int n_temporal, int D, int H, const float* x, const uint8_t* alive,
+                        float* y, const float* hidden_in, float* hidden_out, const uint8_t* done,
+                        const uint8_t* reset_env, const BnbBatch* batch, int T, int precision, int engine,
+                        void* scratch, size_t scratch_bytes, void* stream, bool is_sequence) {
+  int st = check_dims(D, H);
+  if (st) return st;
+  if ((st = check_batch(batch))) return st;
+  if (n_blocks < 0 || n_spatial < 0 || n_temporal < 0 || T < 1) return BNB_ERR_BAD_ARGUMENT;
+  if (precision != BNB_FP32 && precision != BNB_BF16) return BNB_ERR_BAD_ARGUMENT;
+  if (n_blocks * n_spatial > 0 && !spatial) return BNB_ERR_NULL_POINTER;
+  if (n_blocks * n_temporal > 0 && !temporal) return BNB_ERR_NULL_POINTER;
+  for (int i = 0; i < n_blocks * n_spatial; ++i)
+    if ((st = check_spatial(&spatial[i]))) return st;
+  for (int i = 0; i < n_blocks * n_temporal; ++i)
+    if ((st = check_temporal(&temporal[i], batch->total_tokens > batch->total_ships))) return st;
+  size_t n_rows = (size_t)T * batch->total_tokens;
+  if (n_rows == 0) return BNB_OK;
+  if (!x || !y) return BNB_ERR_NULL_POINTER;
+  if (!aligned16(x) || !aligned16(y) || !aligned16(hidden_in) || !aligned16(hidden_out)) return BNB_ERR_MISALIGNED;
+  const bool has_state = n_blocks * n_temporal > 0 && batch->total_ships > 0;
+  if (has_state && !hidden_in) return BNB_ERR_NULL_POINTER;
+  if (has_state && !is_sequence && !hidden_out) return BNB_ERR_NULL_POINTER;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+
+  if (use_tensor(precision, engine, D, H, batch))
+    return bnb::tensor::trunk(spatial, temporal, n_blocks, n_spatial, n_temporal, D, H, x, alive, y, hidden_in,
+                              hidden_out, done, reset_env, *batch, T, scratch, scratch_bytes, cs);
+  if (engine == BNB_ENGINE_TENSOR) return BNB_ERR_UNSUPPORTED_DIMS;
+
+  Scratch s{nullptr, nullptr};
+  if (n_blocks * n_spatial > 0 && (st = carve(scratch, scratch_bytes, n_rows, D, &s))) return st;
+  const bool emu = precision == BNB_BF16;
+  const float* cur = x;
+  const size_t slot_stride = (size_t)batch->total_ships * 4 * D;
+  if (n_blocks * (n_spatial + n_temporal) == 0) {
+    if (y != x && cudaMemcpyAsync(y, x, n_rows * D * sizeof(float), cudaMemcpyDeviceToDevice, cs) != cudaSuccess)
+      return BNB_ERR_LAUNCH;
+    return BNB_OK;
+  }
+  for (int i = 0; i < n_blocks; ++i) {
+    for (int j = 0; j < n_spatial; ++j) {
+      st = bnb::exact::spatial_block(spatial[i * n_spatial + j], D, H, cur, alive, y, *batch, T, emu, s.qkv, s.o, cs);
+      if (st) return st;
+      cur = y;
+    }
+    for (int j = 0; j < n_temporal; ++j) {
+      int slot = i * n_temporal + j;
+      st = bnb::exact::temporal_block(temporal[slot], D, cur, y, hidden_in ? hidden_in + slot * slot_stride : nullptr,
+                                      hidden_out ? hidden_out + slot * slot_stride : nullptr, done, reset_env,
+                                      *batch, T, emu, cs);
+      if (st) return st;
+      cur = y;
+    }
+  }
+  return BNB_OK;
+}
+
+int bnb_trunk_step(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal, int n_blocks,
+                   int n_spatial, int n_temporal, int d_model, int n_heads, const float* x,
+                   const uint8_t* alive, float* y, const float* hidden_in, float* hidden_out,
+                   const uint8_t* reset_env, const BnbBatch* batch, int precision, int engine,
+                   void* scratch, size_t scratch_bytes, void* stream) {
+  return trunk_common(spatial, temporal, n_blocks, n_spatial, n_temporal, d_model, n_heads, x, alive, y, hidden_in,
+                      hidden_out, nullptr, reset_env, batch, 1, precision, engine, scratch, scratch_bytes, stream,
+                      false);
+}
+
+int bnb_trunk_sequence(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal, int n_blocks,
+                       int n_spatial, int n_temporal, int d_model, int n_heads, const float* x,
+                       const uint8_t* alive, float* y, const float* hidden_in, float* hidden_out,
+                       const uint8_t* done, const BnbBatch* batch, int timesteps, int precision, int engine,
+                       void* scratch, size_t scratch_bytes, void* stream) {
+  return trunk_common(spatial, temporal, n_blocks, n_spatial, n_temporal, d_model, n_heads, x, alive, y, hidden_in,
+                      hidden_out, done, nullptr, batch, timesteps, precision, engine, scratch, scratch_bytes, stream,
+                      true);
+}
+
+int bnb_reset_hidden(const float* hidden_in, float* hidden_out, const uint8_t* done, int n_slots, int d_model,
+                     const BnbBatch* batch, void* stream) {
+  int st = check_batch(batch);
+  if (st) return st;
+  if (d_model <= 0 || d_model % 4 != 0 || n_slots < 0) return BNB_ERR_BAD_ARGUMENT;
+  if ((size_t)n_slots * batch->total_ships == 0) return BNB_OK;
+  if (!hidden_in || !hidden_out || !done) return BNB_ERR_NULL_POINTER;
+  if (!aligned16(hidden_in) || !aligned16(hidden_out)) return BNB_ERR_MISALIGNED;
+  return bnb::exact::reset_hidden(hidden_in, hidden_out, done, n_slots, d_model, *batch,
+                                  static_cast<cudaStream_t>(stream));
+}
+
+size_t bnb_packed_spatial_bytes(int d_model) { return bnb::tensor::packed_spatial_bytes(d_model); }
+size_t bnb_packed_temporal_bytes(int d_model) { return bnb::tensor::packed_temporal_bytes(d_model); }
+
+int bnb_pack_spatial(const BnbSpatialWeights* w, int d_model, int n_heads, void* packed, void* stream) {
+  int st = check_dims(d_model, n_heads);
+  if (st) return st;
+  if ((st = check_spatial(w))) return st;
+  if (!packed) return BNB_ERR_NULL_POINTER;
+  if (!aligned16(packed)) return BNB_ERR_MISALIGNED;
+  return bnb::tensor::pack_spatial(*w, d_model, n_heads, packed, static_cast<cudaStream_t>(stream));
+}
+
+int bnb_pack_temporal(const BnbTemporalWeights* w, int d_model, void* packed, void* stream) {
+  int st = check_dims(d_model, d_model / 32);
+  if (st) return st;
+  if ((st = check_temporal(w, false))) return st;
+  if (!packed) return BNB_ERR_NULL_POINTER;
+  if (!aligned16(packed)) return BNB_ERR_MISALIGNED;
+  return bnb::tensor::pack_temporal(*w, d_model, packed, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

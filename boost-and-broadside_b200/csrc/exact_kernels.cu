@@ -1,0 +1,608 @@
+// CUDA-core (SIMT) kernels of the Yemong trunk: float32 arithmetic throughout, with the
+// bf16 roundings of the autocast contract applied in software when EMU is set.
+//
+// These kernels serve BNB_FP32 calls (1e-4 parity needs float32 products, which the
+// bf16 tensor-core path cannot give) and BNB_BF16 calls whose shapes the tensor-core
+// kernels are not built for.  They follow
+//   TransformerBlock.forward        models/yemong/attention.py:76-169
+//   GatedMLP.forward                models/yemong/attention.py:21-37
+//   GriffinTemporalBlock.*          models/yemong/griffin.py:249-317
+//   RGLRU gates / update            models/yemong/griffin.py:169-219
+//   causal conv + tap validity      models/yemong/griffin.py:67-140
+// of the reference.
+#include "common.cuh"
+#include "exact_kernels.h"
+
+namespace bnb {
+namespace exact {
+
+constexpr int ROWS = 32;        // token rows per CTA
+constexpr int NTHREADS = 256;   // 8 warps; warp w owns rows 4w..4w+3
+constexpr int KC = 32;          // K chunk staged per pass
+constexpr int WS_STRIDE = KC + 4;
+constexpr int NCHUNK = 128;     // output columns per tile_linear call
+
+// acc[i][j] += sum_k A[4*warp+i][k] * W[(lane + 32 j)][k]   for lane + 32 j < N
+// A: shared, row stride lda (floats), already rounded for EMU.  W: global, row stride ldw.
+// Ws: shared staging of NCHUNK x WS_STRIDE floats.  All threads of the CTA must call.
+template <bool EMU>
+__device__ __forceinline__ void tile_linear(const float* __restrict__ A, int lda,
+                                            const float* __restrict__ W, int ldw, int N, int K,
+                                            float* __restrict__ Ws, float (&acc)[4][4]) {
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  for (int k0 = 0; k0 < K; k0 += KC) {
+    __syncthreads();  // previous users of Ws are done
+    for (int idx = tid; idx < N * (KC / 4); idx += NTHREADS) {
+      int c = idx >> 3, q = idx & 7;
+      float4 v = *reinterpret_cast<const float4*>(W + (size_t)c * ldw + k0 + q * 4);
+      if constexpr (EMU) {
+        v.x = round_bf16(v.x); v.y = round_bf16(v.y); v.z = round_bf16(v.z); v.w = round_bf16(v.w);
+      }
+      *reinterpret_cast<float4*>(Ws + c * WS_STRIDE + q * 4) = v;
+    }
+    __syncthreads();
+#pragma unroll 2
+    for (int kk = 0; kk < KC; kk += 4) {
+      float4 a[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        a[i] = *reinterpret_cast<const float4*>(A + (4 * warp + i) * lda + k0 + kk);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        int c = lane + 32 * j;
+        if (c < N) {
+          float4 w = *reinterpret_cast<const float4*>(Ws + c * WS_STRIDE + kk);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            acc[i][j] = fmaf(a[i].x, w.x, acc[i][j]);
+            acc[i][j] = fmaf(a[i].y, w.y, acc[i][j]);
+            acc[i][j] = fmaf(a[i].z, w.z, acc[i][j]);
+            acc[i][j] = fmaf(a[i].w, w.w, acc[i][j]);
+          }
+        }
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void zero_acc(float (&acc)[4][4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+}
+
+// RMS norm of the rows of X (ROWS x D, stride ld) into Nrm (rounded for EMU).
+// Warp w handles rows 4w..4w+3.  Rows >= n_valid produce zeros.
+template <bool EMU>
+__device__ __forceinline__ void tile_rmsnorm(const float* X, float* Nrm, int ld, int D,
+                                             const float* __restrict__ g, int n_valid) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = 0; i < 4; ++i) {
+    int r = 4 * warp + i;
+    float ss = 0.f;
+    for (int c = lane; c < D; c += 32) { float v = X[r * ld + c]; ss = fmaf(v, v, ss); }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    float inv = rsqrtf(ss / (float)D + kRmsEps);
+    for (int c = lane; c < D; c += 32) {
+      float v = (r < n_valid) ? X[r * ld + c] * inv * g[c] : 0.f;
+      Nrm[r * ld + c] = rnd<EMU>(v);
+    }
+  }
+}
+
+// x2 = x1 + down(gelu(gate(m)) * up(m)) for the tile; m = rmsnorm(x1).  X holds x1 on entry
+// and is left untouched; the result is returned in out[i][j] for columns of chunk `oc`.
+// Shared buffers: Nrm (normed input), P (gated product chunk).  D <= 128.
+template <bool EMU>
+__device__ __forceinline__ void tile_gated_mlp(const float* Nrm, float* P, int ld, int D,
+                                               const float* __restrict__ Wg, const float* __restrict__ Wu,
+                                               const float* __restrict__ Wd, float* Ws,
+                                               float (&down)[4][4]) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int H = 4 * D;
+  zero_acc(down);
+  for (int h0 = 0; h0 < H; h0 += NCHUNK) {
+    int hn = min(NCHUNK, H - h0);
+    float g[4][4], u[4][4];
+    zero_acc(g);
+    zero_acc(u);
+    tile_linear<EMU>(Nrm, ld, Wg + (size_t)h0 * D, D, hn, D, Ws, g);
+    tile_linear<EMU>(Nrm, ld, Wu + (size_t)h0 * D, D, hn, D, Ws, u);
+    __syncthreads();  // previous readers of P are done
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        int c = lane + 32 * j;
+        if (c < hn) {
+          float ge = rnd<EMU>(gelu_erf(rnd<EMU>(g[i][j])));
+          P[(4 * warp + i) * ld + c] = rnd<EMU>(ge * rnd<EMU>(u[i][j]));
+        }
+      }
+    __syncthreads();
+    tile_linear<EMU>(P, ld, Wd + h0, H, D, hn, Ws, down);
+  }
+}
+
+// ------------------------------------------------------------------ spatial, stage 1
+// qkv = Linear(rmsnorm(x))  -> (rows, 3D) float32 scratch (values bf16-rounded for EMU)
+template <bool EMU>
+__global__ void __launch_bounds__(NTHREADS)
+k_spatial_qkv(const float* __restrict__ x, float* __restrict__ qkv, int n_rows, int D,
+              const float* __restrict__ g1, const float* __restrict__ Wqkv) {
+  extern __shared__ __align__(16) float smem[];
+  const int ld = D + 4;
+  float* X = smem;
+  float* Nrm = X + ROWS * ld;
+  float* Ws = Nrm + ROWS * ld;
+  const int row0 = blockIdx.x * ROWS;
+  const int n_valid = min(ROWS, n_rows - row0);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  for (int idx = tid; idx < ROWS * (D / 4); idx += NTHREADS) {
+    int r = idx / (D / 4), q = idx % (D / 4);
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < n_valid) v = *reinterpret_cast<const float4*>(x + (size_t)(row0 + r) * D + q * 4);
+    *reinterpret_cast<float4*>(X + r * ld + q * 4) = v;
+  }
+  __syncthreads();
+  tile_rmsnorm<EMU>(X, Nrm, ld, D, g1, n_valid);
+  for (int c0 = 0; c0 < 3 * D; c0 += NCHUNK) {
+    int cn = min(NCHUNK, 3 * D - c0);
+    float acc[4][4];
+    zero_acc(acc);
+    tile_linear<EMU>(Nrm, ld, Wqkv + (size_t)c0 * D, D, cn, D, Ws, acc);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      int r = 4 * warp + i;
+      if (r < n_valid)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          int c = lane + 32 * j;
+          if (c < cn) qkv[(size_t)(row0 + r) * 3 * D + c0 + c] = rnd<EMU>(acc[i][j]);
+        }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ spatial, stage 2
+// Masked softmax attention inside each environment, one thread per (query token, head),
+// single pass with a running maximum.  A dead key scores kMaskedScore, so its weight is
+// exactly 0 while any key of the environment is alive, and an environment with no live
+// key gives every key weight 1/n (attention.py:101-112 with finfo.min/2 as the bias).
+template <bool EMU, int DH>
+__global__ void __launch_bounds__(128)
+k_attention(const float* __restrict__ qkv, const uint8_t* __restrict__ alive, float* __restrict__ o,
+            EnvMap map, int n_groups, int D, int H) {
+  const int env_g = blockIdx.x;  // group-major environment index
+  const int grp = env_g / map.n_envs, e = env_g - grp * map.n_envs;
+  const int tok0 = grp * map.total_tokens + map.env_tok_begin(e);
+  const int n = map.env_tok_count(e);
+  const float scale = rsqrtf((float)DH);
+  for (int p = blockIdx.y * blockDim.x + threadIdx.x; p < n * H; p += gridDim.y * blockDim.x) {
+    const int qi = p / H, h = p - qi * H;
+    const float* qp = qkv + (size_t)(tok0 + qi) * 3 * D + h * DH;
+    float q[DH], acc[DH];
+#pragma unroll
+    for (int d = 0; d < DH; d += 4) {
+      float4 v = *reinterpret_cast<const float4*>(qp + d);
+      q[d] = v.x; q[d + 1] = v.y; q[d + 2] = v.z; q[d + 3] = v.w;
+      acc[d] = acc[d + 1] = acc[d + 2] = acc[d + 3] = 0.f;
+    }
+    float m = -INFINITY, l = 0.f;
+    for (int j = 0; j < n; ++j) {
+      const float* kp = qkv + (size_t)(tok0 + j) * 3 * D + D + h * DH;
+      float s = 0.f;
+#pragma unroll
+      for (int d = 0; d < DH; d += 4) {
+        float4 v = *reinterpret_cast<const float4*>(kp + d);
+        s = fmaf(q[d], v.x, s); s = fmaf(q[d + 1], v.y, s);
+        s = fmaf(q[d + 2], v.z, s); s = fmaf(q[d + 3], v.w, s);
+      }
+      s *= scale;
+      if (alive && !alive[tok0 + j]) s = kMaskedScore;
+      float mn = fmaxf(m, s);
+      float corr = expf(m - mn);   // m = -inf on the first key: exp(-inf) = 0
+      float pj = expf(s - mn);
+      l = l * corr + pj;
+      const float* vp = kp + D;
+#pragma unroll
+      for (int d = 0; d < DH; d += 4) {
+        float4 v = *reinterpret_cast<const float4*>(vp + d);
+        acc[d] = fmaf(pj, v.x, acc[d] * corr);
+        acc[d + 1] = fmaf(pj, v.y, acc[d + 1] * corr);
+        acc[d + 2] = fmaf(pj, v.z, acc[d + 2] * corr);
+        acc[d + 3] = fmaf(pj, v.w, acc[d + 3] * corr);
+      }
+      m = mn;
+    }
+    float inv = 1.0f / l;
+    float* op = o + (size_t)(tok0 + qi) * D + h * DH;
+#pragma unroll
+    for (int d = 0; d < DH; d += 4) {
+      float4 v = make_float4(rnd<EMU>(acc[d] * inv), rnd<EMU>(acc[d + 1] * inv),
+                             rnd<EMU>(acc[d + 2] * inv), rnd<EMU>(acc[d + 3] * inv));
+      *reinterpret_cast<float4*>(op + d) = v;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ spatial, stage 3
+// x1 = x + Linear_out(o);  y = x1 + GatedMLP(rmsnorm(x1))
+template <bool EMU>
+__global__ void __launch_bounds__(NTHREADS)
+k_spatial_post(const float* __restrict__ x, const float* __restrict__ o, float* __restrict__ y,
+               int n_rows, int D, const float* __restrict__ Wout, const float* __restrict__ g2,
+               const float* __restrict__ Wg, const float* __restrict__ Wu, const float* __restrict__ Wd) {
+  extern __shared__ __align__(16) float smem[];
+  const int ld = max(D, NCHUNK) + 4;
+  float* X = smem;
+  float* Nrm = X + ROWS * ld;
+  float* P = Nrm + ROWS * ld;
+  float* Ws = P + ROWS * ld;
+  const int row0 = blockIdx.x * ROWS;
+  const int n_valid = min(ROWS, n_rows - row0);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  for (int idx = tid; idx < ROWS * (D / 4); idx += NTHREADS) {
+    int r = idx / (D / 4), q = idx % (D / 4);
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f), w = v;
+    if (r < n_valid) {
+      v = *reinterpret_cast<const float4*>(x + (size_t)(row0 + r) * D + q * 4);
+      w = *reinterpret_cast<const float4*>(o + (size_t)(row0 + r) * D + q * 4);
+    }
+    *reinterpret_cast<float4*>(X + r * ld + q * 4) = v;
+    *reinterpret_cast<float4*>(P + r * ld + q * 4) = w;  // o is already rounded for EMU
+  }
+  float acc[4][4];
+  zero_acc(acc);
+  tile_linear<EMU>(P, ld, Wout, D, D, D, Ws, acc);
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      int c = lane + 32 * j;
+      if (c < D) X[(4 * warp + i) * ld + c] += rnd<EMU>(acc[i][j]);
+    }
+  __syncthreads();
+  tile_rmsnorm<EMU>(X, Nrm, ld, D, g2, n_valid);
+  float down[4][4];
+  tile_gated_mlp<EMU>(Nrm, P, ld, D, Wg, Wu, Wd, Ws, down);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int r = 4 * warp + i;
+    if (r < n_valid)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        int c = lane + 32 * j;
+        if (c < D) y[(size_t)(row0 + r) * D + c] = X[r * ld + c] + rnd<EMU>(down[i][j]);
+      }
+  }
+}
+
+// ------------------------------------------------------------------ temporal
+// One temporal sublayer.  FIELD = false: CTA owns ROWS ships and walks t = 0..T-1 with the
+// RG-LRU state and conv taps of its (row, column) elements in registers.  FIELD = true:
+// rows are (t, field token) pairs, no state, conv+RG-LRU replaced by the field_sub Linear.
+template <bool EMU, bool FIELD>
+__global__ void __launch_bounds__(NTHREADS, 1)
+k_temporal(const float* __restrict__ x, float* __restrict__ y,
+           const float* __restrict__ hidden_in, float* __restrict__ hidden_out,
+           const uint8_t* __restrict__ done, const uint8_t* __restrict__ reset_env,
+           EnvMap map, int T, int D, BnbTemporalWeights w) {
+  extern __shared__ __align__(16) float smem[];
+  const int ld = max(D, NCHUNK) + 4;
+  float* X = smem;                 // residual stream
+  float* Nrm = X + ROWS * ld;      // normed input of the current Linear group
+  float* P = Nrm + ROWS * ld;      // second operand tile (u, h*b2, gated product)
+  float* B2 = P + ROWS * ld;       // gelu(linear2(n))
+  float* Ws = B2 + ROWS * ld;
+  __shared__ int s_xrow[ROWS];     // token row (within a timestep) of each tile row
+  __shared__ int s_env[ROWS];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_items = FIELD ? map.total_fields() * T : map.total_ships;
+  const int item0 = blockIdx.x * ROWS;
+  const int n_valid = min(ROWS, n_items - item0);
+  if (tid < ROWS) {
+    int xr = 0, e = 0;
+    if (tid < n_valid) {
+      int it = item0 + tid;
+      if (FIELD) {
+        int nf = map.total_fields();
+        int t = it / nf, f = it - t * nf;
+        xr = t * map.total_tokens + map.field_token_row(f);
+      } else {
+        xr = map.ship_token_row(it, &e);
+      }
+    }
+    s_xrow[tid] = xr;
+    s_env[tid] = e;
+  }
+  __syncthreads();
+
+  // per-thread state for elements (row 4*warp+i, column lane+32j)
+  float hst[4][4], c0[4][4], c1[4][4], c2[4][4];
+  int lag_ok[4];  // valid stored lags of each owned row: 3 at t = 0
+  if constexpr (!FIELD) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      int r = 4 * warp + i;
+      lag_ok[i] = BNB_CONV_KERNEL - 1;
+      bool zero = (r >= n_valid) || (reset_env && reset_env[s_env[r]]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        int c = lane + 32 * j;
+        float vh = 0.f, v0 = 0.f, v1 = 0.f, v2 = 0.f;
+        if (!zero && c < D) {
+          const float* hp = hidden_in + (size_t)(item0 + r) * 4 * D + c;
+          vh = hp[0]; v0 = hp[D]; v1 = hp[2 * D]; v2 = hp[3 * D];
+        }
+        hst[i][j] = vh; c0[i][j] = v0; c1[i][j] = v1; c2[i][j] = v2;
+      }
+    }
+  }
+
+  const int steps = FIELD ? 1 : T;
+  for (int t = 0; t < steps; ++t) {
+    const size_t tbase = FIELD ? 0 : (size_t)t * map.total_tokens;
+    __syncthreads();
+    for (int idx = tid; idx < ROWS * (D / 4); idx += NTHREADS) {
+      int r = idx / (D / 4), q = idx % (D / 4);
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (r < n_valid) v = *reinterpret_cast<const float4*>(x + (tbase + s_xrow[r]) * D + q * 4);
+      *reinterpret_cast<float4*>(X + r * ld + q * 4) = v;
+    }
+    __syncthreads();
+    tile_rmsnorm<EMU>(X, Nrm, ld, D, w.norm1_w, n_valid);
+
+    float b1[4][4], acc[4][4];
+    zero_acc(b1);
+    tile_linear<EMU>(Nrm, ld, w.linear1_w, D, D, D, Ws, b1);
+    zero_acc(acc);
+    tile_linear<EMU>(Nrm, ld, w.linear2_w, D, D, D, Ws, acc);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        int c = lane + 32 * j;
+        b1[i][j] = rnd<EMU>(b1[i][j]);
+        if (c < D) B2[(4 * warp + i) * ld + c] = rnd<EMU>(gelu_erf(rnd<EMU>(acc[i][j])));
+      }
+
+    float br[4][4];  // recurrent-branch output per owned element
+    if constexpr (FIELD) {
+      // b1 <- field_sub(linear1(n))
+      __syncthreads();
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          int c = lane + 32 * j;
+          if (c < D) P[(4 * warp + i) * ld + c] = b1[i][j];
+        }
+      zero_acc(acc);
+      tile_linear<EMU>(P, ld, w.field_sub_w, D, D, D, Ws, acc);
+      __syncthreads();
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          int c = lane + 32 * j;
+          // bf16 * bf16 -> bf16 under autocast (griffin.py:316)
+          br[i][j] = (c < D) ? rnd<EMU>(rnd<EMU>(acc[i][j]) * B2[(4 * warp + i) * ld + c]) : 0.f;
+        }
+    } else {
+      // causal depthwise conv over (tap0, tap1, tap2, b1) with episode-boundary lag masks
+      float u[4][4];
+      bool reset_a[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        int r = 4 * warp + i;
+        bool boundary = false;
+        if (done && t >= 1 && r < n_valid) boundary = done[(size_t)(t - 1) * map.n_envs + s_env[r]] != 0;
+        if (t >= 1) lag_ok[i] = boundary ? 0 : min(lag_ok[i] + 1, BNB_CONV_KERNEL - 1);
+        reset_a[i] = boundary;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          int c = lane + 32 * j;
+          float uu = 0.f;
+          if (c < D) {
+            const float* cw = w.conv_w + c * BNB_CONV_KERNEL;
+            float t0 = lag_ok[i] >= 3 ? __fmul_rn(c0[i][j], cw[0]) : 0.f;
+            float t1 = lag_ok[i] >= 2 ? __fmul_rn(c1[i][j], cw[1]) : 0.f;
+            float t2 = lag_ok[i] >= 1 ? __fmul_rn(c2[i][j], cw[2]) : 0.f;
+            float t3 = __fmul_rn(b1[i][j], cw[3]);
+            uu = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(t0, t1), t2), t3), w.conv_b[c]);
+            P[(4 * warp + i) * ld + c] = rnd<EMU>(uu);
+          }
+          u[i][j] = uu;
+          c0[i][j] = c1[i][j]; c1[i][j] = c2[i][j]; c2[i][j] = b1[i][j];
+        }
+      float ga[4][4], gx[4][4];
+      zero_acc(ga);
+      tile_linear<EMU>(P, ld, w.a_w, D, D, D, Ws, ga);
+      zero_acc(gx);
+      tile_linear<EMU>(P, ld, w.x_w, D, D, D, Ws, gx);
+      __syncthreads();
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          int c = lane + 32 * j;
+          float out = 0.f;
+          if (c < D) {
+            float rg = rnd<EMU>(sigmoidf_(rnd<EMU>(ga[i][j] + rnd<EMU>(w.a_b[c]))));
+            float ig = rnd<EMU>(sigmoidf_(rnd<EMU>(gx[i][j] + rnd<EMU>(w.x_b[c]))));
+            float a = powf(sigmoidf_(w.log_lambda[c]), kRglruC * rg);
+            float gate = sqrtf(fmaxf((1.0f - a) * (1.0f + a), kGateFloor));
+            float bb = gate * (ig * u[i][j]);
+            if (reset_a[i]) a = 0.f;
+            hst[i][j] = a * hst[i][j] + bb;
+            out = hst[i][j] * B2[(4 * warp + i) * ld + c];  // fp32 * bf16 -> fp32
+          }
+          br[i][j] = out;
+        }
+    }
+    // x1 = x + linear_out(branch)
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        int c = lane + 32 * j;
+        if (c < D) P[(4 * warp + i) * ld + c] = rnd<EMU>(br[i][j]);
+      }
+    zero_acc(acc);
+    tile_linear<EMU>(P, ld, w.out_w, D, D, D, Ws, acc);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        int c = lane + 32 * j;
+        if (c < D) X[(4 * warp + i) * ld + c] += rnd<EMU>(acc[i][j]);
+      }
+    __syncthreads();
+    tile_rmsnorm<EMU>(X, Nrm, ld, D, w.norm2_w, n_valid);
+    float down[4][4];
+    tile_gated_mlp<EMU>(Nrm, P, ld, D, w.gate_w, w.up_w, w.down_w, Ws, down);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      int r = 4 * warp + i;
+      if (r < n_valid)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          int c = lane + 32 * j;
+          if (c < D) y[(tbase + s_xrow[r]) * D + c] = X[r * ld + c] + rnd<EMU>(down[i][j]);
+        }
+    }
+  }
+
+  if constexpr (!FIELD) {
+    if (hidden_out) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        int r = 4 * warp + i;
+        if (r < n_valid)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            int c = lane + 32 * j;
+            if (c < D) {
+              float* hp = hidden_out + (size_t)(item0 + r) * 4 * D + c;
+              hp[0] = hst[i][j]; hp[D] = c0[i][j]; hp[2 * D] = c1[i][j]; hp[3 * D] = c2[i][j];
+            }
+          }
+      }
+    }
+  }
+}
+
+__global__ void k_reset_hidden(const float* __restrict__ in, float* __restrict__ out,
+                               const uint8_t* __restrict__ done, EnvMap map, int n_slots, int D) {
+  const size_t row_f4 = (size_t)D;  // 4D floats = D float4
+  const size_t total = (size_t)n_slots * map.total_ships * row_f4;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    size_t row = i / row_f4;
+    int s = (int)(row % map.total_ships);
+    int e = map.env_of_ship(s);
+    float4 v = reinterpret_cast<const float4*>(in)[i];
+    if (done[e]) v = make_float4(0.f, 0.f, 0.f, 0.f);
+    reinterpret_cast<float4*>(out)[i] = v;
+  }
+}
+
+// ------------------------------------------------------------------ host launchers
+
+static size_t smem_rows(int D, int tiles) {
+  int ld = (D > NCHUNK ? D : NCHUNK) + 4;
+  return (size_t)(tiles * ROWS * ld + NCHUNK * WS_STRIDE) * sizeof(float);
+}
+
+template <class K>
+static bool opt_in(K kernel, size_t bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) == cudaSuccess;
+}
+
+template <bool EMU>
+static int spatial_impl(const BnbSpatialWeights& w, int D, int H, const float* x, const uint8_t* alive,
+                        float* y, const BnbBatch& b, int n_groups, float* qkv, float* o, cudaStream_t st) {
+  const int n_rows = n_groups * b.total_tokens;
+  const int n_tiles = (n_rows + ROWS - 1) / ROWS;
+  {
+    size_t sm = (size_t)(2 * ROWS * (D + 4) + NCHUNK * WS_STRIDE) * sizeof(float);
+    if (!opt_in(k_spatial_qkv<EMU>, sm)) return BNB_ERR_LAUNCH;
+    k_spatial_qkv<EMU><<<n_tiles, NTHREADS, sm, st>>>(x, qkv, n_rows, D, w.norm1_w, w.qkv_w);
+  }
+  {
+    EnvMap map = make_env_map(b);
+    int dh = D / H;
+    int per_env = b.max_tokens_per_env * H;
+    dim3 grid(n_groups * b.n_envs, (per_env + 127) / 128 > 4 ? 4 : (per_env + 127) / 128);
+    if (grid.y < 1) grid.y = 1;
+    switch (dh) {
+      case 8:  k_attention<EMU, 8><<<grid, 128, 0, st>>>(qkv, alive, o, map, n_groups, D, H); break;
+      case 16: k_attention<EMU, 16><<<grid, 128, 0, st>>>(qkv, alive, o, map, n_groups, D, H); break;
+      case 32: k_attention<EMU, 32><<<grid, 128, 0, st>>>(qkv, alive, o, map, n_groups, D, H); break;
+      case 64: k_attention<EMU, 64><<<grid, 128, 0, st>>>(qkv, alive, o, map, n_groups, D, H); break;
+      default: return BNB_ERR_UNSUPPORTED_DIMS;
+    }
+  }
+  {
+    size_t sm = smem_rows(D, 3);
+    if (!opt_in(k_spatial_post<EMU>, sm)) return BNB_ERR_LAUNCH;
+    k_spatial_post<EMU><<<n_tiles, NTHREADS, sm, st>>>(x, o, y, n_rows, D, w.out_w, w.norm2_w,
+                                                       w.gate_w, w.up_w, w.down_w);
+  }
+  return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
+}
+
+int spatial_block(const BnbSpatialWeights& w, int D, int H, const float* x, const uint8_t* alive,
+                  float* y, const BnbBatch& b, int n_groups, bool emulate_bf16,
+                  float* qkv_scratch, float* o_scratch, cudaStream_t st) {
+  return emulate_bf16 ? spatial_impl<true>(w, D, H, x, alive, y, b, n_groups, qkv_scratch, o_scratch, st)
+                      : spatial_impl<false>(w, D, H, x, alive, y, b, n_groups, qkv_scratch, o_scratch, st);
+}
+
+template <bool EMU>
+static int temporal_impl(const BnbTemporalWeights& w, int D, const float* x, float* y,
+                         const float* hin, float* hout, const uint8_t* done, const uint8_t* reset_env,
+                         const BnbBatch& b, int T, cudaStream_t st) {
+  EnvMap map = make_env_map(b);
+  size_t sm = smem_rows(D, 4);
+  if (b.total_ships > 0) {
+    if (!opt_in(k_temporal<EMU, false>, sm)) return BNB_ERR_LAUNCH;
+    int n_tiles = (b.total_ships + ROWS - 1) / ROWS;
+    k_temporal<EMU, false><<<n_tiles, NTHREADS, sm, st>>>(x, y, hin, hout, done, reset_env, map, T, D, w);
+  }
+  int n_fields = (b.total_tokens - b.total_ships) * T;
+  if (n_fields > 0) {
+    if (!w.field_sub_w) return BNB_ERR_NULL_POINTER;
+    if (!opt_in(k_temporal<EMU, true>, sm)) return BNB_ERR_LAUNCH;
+    int n_tiles = (n_fields + ROWS - 1) / ROWS;
+    k_temporal<EMU, true><<<n_tiles, NTHREADS, sm, st>>>(x, y, nullptr, nullptr, nullptr, nullptr, map, T, D, w);
+  }
+  return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
+}
+
+int temporal_block(const BnbTemporalWeights& w, int D, const float* x, float* y, const float* hidden_in,
+                   float* hidden_out, const uint8_t* done, const uint8_t* reset_env, const BnbBatch& b,
+                   int T, bool emulate_bf16, cudaStream_t st) {
+  return emulate_bf16 ? temporal_impl<true>(w, D, x, y, hidden_in, hidden_out, done, reset_env, b, T, st)
+                      : temporal_impl<false>(w, D, x, y, hidden_in, hidden_out, done, reset_env, b, T, st);
+}
+
+int reset_hidden(const float* in, float* out, const uint8_t* done, int n_slots, int D,
+                 const BnbBatch& b, cudaStream_t st) {
+  EnvMap map = make_env_map(b);
+  size_t total = (size_t)n_slots * b.total_ships * D;
+  if (total == 0) return BNB_OK;
+  int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+  k_reset_hidden<<<blocks, 256, 0, st>>>(in, out, done, map, n_slots, D);
+  return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
+}
+
+}  // namespace exact
+}  // namespace bnb

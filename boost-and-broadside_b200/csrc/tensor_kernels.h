@@ -1,0 +1,33 @@
+// Host interface of the tensor-core (tcgen05) trunk kernels (tensor_kernels.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+#include "bnb_trunk.h"
+
+namespace bnb {
+namespace tensor {
+
+// True when the tensor-core kernels are built for this width, head count and environment size.
+bool supported(int D, int H, int max_tokens_per_env);
+
+size_t scratch_bytes(int D, const BnbBatch& b, int T);
+size_t packed_spatial_bytes(int D);
+size_t packed_temporal_bytes(int D);
+int pack_spatial(const BnbSpatialWeights& w, int D, int H, void* packed, cudaStream_t st);
+int pack_temporal(const BnbTemporalWeights& w, int D, void* packed, cudaStream_t st);
+
+int spatial_block(const BnbSpatialWeights& w, int D, int H, const float* x, const uint8_t* alive, float* y,
+                  const BnbBatch& b, int n_groups, void* scratch, size_t scratch_bytes, cudaStream_t st);
+
+int temporal_block(const BnbTemporalWeights& w, int D, const float* x, float* y, const float* hidden_in,
+                   float* hidden_out, const uint8_t* done, const uint8_t* reset_env, const BnbBatch& b, int T,
+                   void* scratch, size_t scratch_bytes, cudaStream_t st);
+
+int trunk(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal, int n_blocks, int n_spatial,
+          int n_temporal, int D, int H, const float* x, const uint8_t* alive, float* y, const float* hidden_in,
+          float* hidden_out, const uint8_t* done, const uint8_t* reset_env, const BnbBatch& b, int T,
+          void* scratch, size_t scratch_bytes, cudaStream_t st);
+
+}  // namespace tensor
+}  // namespace bnb

@@ -1,0 +1,95 @@
+"""Spatial transformer sublayer, mirroring the reference's ``models/yemong/attention.py``.
+
+``GatedMLP`` and ``TransformerBlock`` keep the reference's constructor arguments,
+parameter names, shapes and float32 dtype (attention.py:21-74), so a reference
+``state_dict`` loads unchanged.  ``TransformerBlock.forward`` has the reference signature
+(attention.py:76-82) and runs ``bnb_spatial_block_fwd`` of the CUDA library.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from .. import _capi
+from ._weights import spatial_struct
+
+
+class GatedMLP(nn.Module):
+    """Parameter holder for down_proj(gelu(gate_proj(x)) * up_proj(x)) (attention.py:21-37).
+
+    The product is computed inside the fused sublayer kernels, not here.
+    """
+
+    def __init__(self, d_model: int, expand: int = 4) -> None:
+        super().__init__()
+        hidden = expand * d_model
+        self.gate_proj = nn.Linear(d_model, hidden, bias=False)
+        self.up_proj = nn.Linear(d_model, hidden, bias=False)
+        self.down_proj = nn.Linear(hidden, d_model, bias=False)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:  # pragma: no cover - not a product path
+        raise RuntimeError("GatedMLP runs only fused inside TransformerBlock / GriffinTemporalBlock kernels")
+
+
+class TransformerBlock(nn.Module):
+    """Pre-norm block: RMSNorm -> masked MHSA -> residual -> RMSNorm -> GatedMLP -> residual.
+
+    Args:
+        model_config: supplies ``d_model`` and ``n_heads``.
+        reads_bullets: allocate the bullet key/value parameters (attention.py:64-71).
+            The bullet cross-attention branch itself is not built: passing ``bullets``
+            raises ``NotImplementedError`` (never a silent PyTorch path).
+    """
+
+    def __init__(self, model_config, reads_bullets: bool = False) -> None:
+        super().__init__()
+        D = model_config.d_model
+        self.n_heads = model_config.n_heads
+        self.head_dim = D // model_config.n_heads
+        self.d_model = D
+        self.reads_bullets = reads_bullets
+
+        self.norm1 = nn.RMSNorm(D)
+        self.qkv = nn.Linear(D, 3 * D, bias=False)
+        self.out_proj = nn.Linear(D, D, bias=False)
+        if reads_bullets:
+            self.norm_bullet = nn.RMSNorm(D)
+            self.kv_bullet = nn.Linear(D, 2 * D, bias=False)
+        self.norm2 = nn.RMSNorm(D)
+        self.ffn = GatedMLP(D)
+
+    def forward(
+        self,
+        x: torch.Tensor,
+        alive_mask: torch.Tensor | None = None,
+        bullets: torch.Tensor | None = None,
+        bullet_mask: torch.Tensor | None = None,
+    ) -> torch.Tensor:
+        """(B, N, D) -> (B, N, D); ``alive_mask`` (B, N) bool masks dead entities as keys."""
+        if self.reads_bullets and bullets is not None:
+            raise NotImplementedError("bullet cross-attention is not built in the CUDA trunk")
+        if x.dim() != 3 or x.shape[-1] != self.d_model:
+            raise RuntimeError(f"expected x of shape (B, N, {self.d_model}), got {tuple(x.shape)}")
+        _capi.require_cuda(x, "x")
+        if torch.is_grad_enabled() and x.requires_grad:
+            raise NotImplementedError("the CUDA trunk is forward-only; call it under torch.no_grad()")
+        B, N, D = x.shape
+        if alive_mask is not None and tuple(alive_mask.shape) != (B, N):
+            raise RuntimeError(f"alive_mask must have shape {(B, N)}, got {tuple(alive_mask.shape)}")
+        dev = x.device
+        precision = _capi.current_precision(dev)
+        with torch.cuda.device(dev):
+            xin = _capi.f32c(x)
+            alive = _capi.u8(alive_mask)
+            y = torch.empty_like(xin)
+            batch = _capi.uniform_batch(B, N, N)
+            nbytes = _capi.lib.bnb_scratch_bytes(D, batch, 1)
+            scratch = _capi.scratch_for(dev, nbytes)
+            w = spatial_struct(self, dev)
+            st = _capi.lib.bnb_spatial_block_fwd(
+                w, D, self.n_heads, xin.data_ptr(), _capi.ptr(alive), y.data_ptr(), batch, 1, precision,
+                _capi.ENGINE_AUTO, scratch.data_ptr(), scratch.numel(), _capi.stream_handle(dev),
+            )
+        _capi.check("bnb_spatial_block_fwd", st)
+        return y

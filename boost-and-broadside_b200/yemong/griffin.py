@@ -1,0 +1,312 @@
+"""Griffin temporal sublayer and Yemong block, mirroring ``models/yemong/griffin.py``.
+
+Constructor arguments, sub-module names, parameter names/shapes/dtype and method
+signatures follow the reference (griffin.py:160-167, 236-247, 335-368, 376-385, 419-429).
+The arithmetic runs in the CUDA library: ``bnb_temporal_block_fwd`` for a temporal
+sublayer, ``bnb_trunk_step`` / ``bnb_trunk_sequence`` (with one block) for a Yemong block.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from .. import _capi
+from ._weights import spatial_struct, temporal_struct
+from .attention import GatedMLP, TransformerBlock
+
+CONV_KERNEL: int = 4  # causal depthwise conv kernel size (griffin.py:22)
+
+
+def _no_grad_inputs(*tensors) -> None:
+    if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors):
+        raise NotImplementedError("the CUDA trunk is forward-only; call it under torch.no_grad()")
+
+
+class RGLRU(nn.Module):
+    """Parameters of the Real-Gated Linear Recurrent Unit (griffin.py:160-167).
+
+    r = sigmoid(W_a x + b_a), i = sigmoid(W_x x + b_x), a = sigmoid(Lambda)^(c r),
+    h = a h + sqrt(1 - a^2) (i x).  The update runs fused inside the temporal kernels.
+    """
+
+    def __init__(self, d_model: int, c: float = 8.0) -> None:
+        super().__init__()
+        if c != 8.0:
+            raise ValueError("the CUDA RG-LRU is built for c = 8 (the reference's only value)")
+        self.c = c
+        self.log_lambda = nn.Parameter(torch.linspace(0.0, 4.0, d_model))
+        self.linear_a = nn.Linear(d_model, d_model, bias=True)
+        self.linear_x = nn.Linear(d_model, d_model, bias=True)
+
+    def forward_sequence(self, x_seq, h0, done_mask=None):  # pragma: no cover - not a product path
+        raise RuntimeError("RGLRU runs only fused inside GriffinTemporalBlock.forward_sequence")
+
+    _step = forward_sequence
+
+
+class GriffinTemporalBlock(nn.Module):
+    """norm -> (linear1 -> causal conv -> RG-LRU) * GeLU(linear2) -> linear_out -> residual
+    -> GatedMLP(norm) -> residual, applied per ship across time (griffin.py:222-286)."""
+
+    def __init__(self, d_model: int) -> None:
+        super().__init__()
+        self.d_model = d_model
+        self.norm1 = nn.RMSNorm(d_model)
+        self.linear1 = nn.Linear(d_model, d_model, bias=False)
+        self.conv = nn.Conv1d(d_model, d_model, kernel_size=CONV_KERNEL, groups=d_model, bias=True)
+        self.rg_lru = RGLRU(d_model)
+        self.linear2 = nn.Linear(d_model, d_model, bias=False)
+        self.linear_out = nn.Linear(d_model, d_model, bias=False)
+        self.norm2 = nn.RMSNorm(d_model)
+        self.gated_mlp = GatedMLP(d_model)
+
+    def forward_sequence(
+        self,
+        x_seq: torch.Tensor,  # (B_seq, T, D)
+        h0: torch.Tensor,  # (B_seq, D)
+        conv_buf: torch.Tensor,  # (B_seq, CONV_KERNEL-1, D)
+        done_mask: torch.Tensor | None = None,  # (B_seq, T) bool
+    ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        """Returns (out (B_seq, T, D), new_h (B_seq, D), new_conv_buf (B_seq, 3, D))."""
+        D = self.d_model
+        if x_seq.dim() != 3 or x_seq.shape[-1] != D:
+            raise RuntimeError(f"expected x_seq of shape (B_seq, T, {D}), got {tuple(x_seq.shape)}")
+        _capi.require_cuda(x_seq, "x_seq")
+        _no_grad_inputs(x_seq, h0, conv_buf)
+        R, T, _ = x_seq.shape
+        if tuple(h0.shape) != (R, D) or tuple(conv_buf.shape) != (R, CONV_KERNEL - 1, D):
+            raise RuntimeError("h0 / conv_buf shapes do not match x_seq")
+        dev = x_seq.device
+        precision = _capi.current_precision(dev)
+        with torch.cuda.device(dev):
+            x_t = _capi.f32c(x_seq.transpose(0, 1))  # (T, R, D), time-major for the kernel
+            hidden = torch.cat([h0.float(), conv_buf.float().reshape(R, (CONV_KERNEL - 1) * D)], dim=-1).contiguous()
+            done = None if done_mask is None else _capi.u8(done_mask.transpose(0, 1))
+            y = torch.empty_like(x_t)
+            new_hidden = torch.empty_like(hidden)
+            batch = _capi.uniform_batch(R, 1, 1)  # every row is its own one-ship environment
+            w = temporal_struct(self, None, dev)
+            st = _capi.lib.bnb_temporal_block_fwd(
+                w, D, x_t.data_ptr(), y.data_ptr(), hidden.data_ptr(), new_hidden.data_ptr(), _capi.ptr(done),
+                batch, T, precision, _capi.ENGINE_AUTO, None, 0, _capi.stream_handle(dev),
+            )
+        _capi.check("bnb_temporal_block_fwd", st)
+        return (
+            y.transpose(0, 1).contiguous(),
+            new_hidden[:, :D].contiguous(),
+            new_hidden[:, D:].reshape(R, CONV_KERNEL - 1, D),
+        )
+
+    def forward_nonrecurrent(self, x: torch.Tensor, sub: nn.Linear) -> torch.Tensor:
+        """The block with conv + RG-LRU replaced by the Linear ``sub`` (griffin.py:288-317)."""
+        D = self.d_model
+        if x.shape[-1] != D:
+            raise RuntimeError(f"expected x of shape (..., {D}), got {tuple(x.shape)}")
+        _capi.require_cuda(x, "x")
+        _no_grad_inputs(x)
+        dev = x.device
+        precision = _capi.current_precision(dev)
+        with torch.cuda.device(dev):
+            flat = _capi.f32c(x).reshape(-1, D)
+            R = flat.shape[0]
+            y = torch.empty_like(flat)
+            batch = _capi.uniform_batch(R, 1, 0)  # every row is a field token
+            w = temporal_struct(self, sub, dev)
+            st = _capi.lib.bnb_temporal_block_fwd(
+                w, D, flat.data_ptr(), y.data_ptr(), None, None, None, batch, 1, precision, _capi.ENGINE_AUTO,
+                None, 0, _capi.stream_handle(dev),
+            )
+        _capi.check("bnb_temporal_block_fwd", st)
+        return y.reshape(x.shape)
+
+
+def run_trunk(
+    blocks,
+    n_heads: int,
+    x: torch.Tensor,
+    alive: torch.Tensor | None,
+    hidden: torch.Tensor,
+    done: torch.Tensor | None,
+    reset_env: torch.Tensor | None,
+    batch: "_capi.Batch",
+    timesteps: int | None,
+    engine: int = _capi.ENGINE_AUTO,
+    keepalive: tuple = (),
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """Run ``blocks`` (YemongBlock modules of one structure) over x.
+
+    x is (total_tokens, D) for a step (timesteps None) or (T, total_tokens, D) for a
+    sequence; hidden is (L, total_ships, 4D) packed.  Returns (y, new_hidden).
+    """
+    dev = x.device
+    D = x.shape[-1]
+    n_blocks = len(blocks)
+    n_spatial = len(blocks[0].spatial) if n_blocks else 0
+    n_temporal = len(blocks[0].temporal) if n_blocks else 0
+    precision = _capi.current_precision(dev)
+    has_fields = batch.total_tokens > batch.total_ships
+    with torch.cuda.device(dev):
+        xin = _capi.f32c(x)
+        hin = _capi.f32c(hidden)
+        alive_u8 = _capi.u8(alive)
+        done_u8 = _capi.u8(done)
+        reset_u8 = _capi.u8(reset_env)
+        y = torch.empty_like(xin)
+        hout = torch.empty_like(hin)
+        sw = (_capi.SpatialWeights * max(1, n_blocks * n_spatial))()
+        tw = (_capi.TemporalWeights * max(1, n_blocks * n_temporal))()
+        for i, blk in enumerate(blocks):
+            for j, sp in enumerate(blk.spatial):
+                sw[i * n_spatial + j] = spatial_struct(sp, dev, blk._packed_ptr("spatial", j, dev, precision, engine))
+            for j, tp in enumerate(blk.temporal):
+                tw[i * n_temporal + j] = temporal_struct(
+                    tp, blk.field_sub[j] if has_fields else None, dev,
+                    blk._packed_ptr("temporal", j, dev, precision, engine),
+                )
+        T = 1 if timesteps is None else timesteps
+        nbytes = _capi.lib.bnb_scratch_bytes(D, batch, T)
+        scratch = _capi.scratch_for(dev, nbytes)
+        stream = _capi.stream_handle(dev)
+        if timesteps is None:
+            st = _capi.lib.bnb_trunk_step(
+                sw, tw, n_blocks, n_spatial, n_temporal, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8),
+                y.data_ptr(), _capi.ptr(hin), _capi.ptr(hout), _capi.ptr(reset_u8), batch, precision, engine,
+                scratch.data_ptr(), scratch.numel(), stream,
+            )
+            fn = "bnb_trunk_step"
+        else:
+            st = _capi.lib.bnb_trunk_sequence(
+                sw, tw, n_blocks, n_spatial, n_temporal, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8),
+                y.data_ptr(), _capi.ptr(hin), _capi.ptr(hout), _capi.ptr(done_u8), batch, T, precision, engine,
+                scratch.data_ptr(), scratch.numel(), stream,
+            )
+            fn = "bnb_trunk_sequence"
+    _capi.check(fn, st)
+    return y, hout
+
+
+class YemongBlock(nn.Module):
+    """Spatial sublayers followed by temporal sublayers (griffin.py:320-368)."""
+
+    def __init__(self, model_config) -> None:
+        super().__init__()
+        self.d_model = model_config.d_model
+        self.n_heads = model_config.n_heads
+        self.spatial = nn.ModuleList(
+            [
+                TransformerBlock(model_config, reads_bullets=i < model_config.n_bullet_cross_per_block)
+                for i in range(model_config.n_spatial_per_block)
+            ]
+        )
+        self.temporal = nn.ModuleList(
+            [GriffinTemporalBlock(model_config.d_model) for _ in range(model_config.n_temporal_per_block)]
+        )
+        self.field_sub = nn.ModuleList(
+            [
+                nn.Linear(model_config.d_model, model_config.d_model, bias=False)
+                for _ in range(model_config.n_temporal_per_block)
+            ]
+        )
+        for sub in self.field_sub:
+            nn.init.eye_(sub.weight)
+        self._packed: dict = {}
+
+    @property
+    def n_temporal(self) -> int:
+        """Hidden-state slots this block consumes."""
+        return len(self.temporal)
+
+    # -- tensor-core weight images: derived data, rebuilt when a parameter changes ----------
+    def _packed_ptr(self, kind: str, j: int, dev: torch.device, precision: int, engine: int):
+        if precision != _capi.BNB_BF16 or engine == _capi.ENGINE_SIMT:
+            return None
+        D = self.d_model
+        nbytes = (
+            _capi.lib.bnb_packed_spatial_bytes(D) if kind == "spatial" else _capi.lib.bnb_packed_temporal_bytes(D)
+        )
+        if nbytes == 0:
+            return None
+        mod = self.spatial[j] if kind == "spatial" else self.temporal[j]
+        params = list(mod.parameters()) + ([self.field_sub[j].weight] if kind == "temporal" else [])
+        stamp = tuple((p.data_ptr(), p._version) for p in params)
+        key = (kind, j, dev.index)
+        hit = self._packed.get(key)
+        if hit is not None and hit[0] == stamp:
+            return hit[1].data_ptr()
+        buf = hit[1] if hit is not None else torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        stream = _capi.stream_handle(dev)
+        if kind == "spatial":
+            st = _capi.lib.bnb_pack_spatial(spatial_struct(mod, dev), D, self.n_heads, buf.data_ptr(), stream)
+            _capi.check("bnb_pack_spatial", st)
+        else:
+            st = _capi.lib.bnb_pack_temporal(temporal_struct(mod, self.field_sub[j], dev), D, buf.data_ptr(), stream)
+            _capi.check("bnb_pack_temporal", st)
+        self._packed[key] = (stamp, buf)
+        return buf.data_ptr()
+
+    @staticmethod
+    def _pack_state(h: torch.Tensor, conv_buf: torch.Tensor) -> torch.Tensor:
+        L, R, D = h.shape
+        return torch.cat([h.float(), conv_buf.float().reshape(L, R, (CONV_KERNEL - 1) * D)], dim=-1).contiguous()
+
+    def _check_bullets(self, bullets) -> None:
+        if bullets is not None and any(sp.reads_bullets for sp in self.spatial):
+            raise NotImplementedError("bullet cross-attention is not built in the CUDA trunk")
+
+    def step(
+        self,
+        x: torch.Tensor,  # (B, N+M, D)
+        alive: torch.Tensor,  # (B, N+M) bool
+        h: torch.Tensor,  # (n_temporal, B*N, D)
+        conv_buf: torch.Tensor,  # (n_temporal, B*N, CONV_KERNEL-1, D)
+        num_recurrent: int | None = None,
+        bullets: torch.Tensor | None = None,
+        bullet_mask: torch.Tensor | None = None,
+    ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        """Single-step forward (griffin.py:376-417): returns (x, new_h, new_conv_buf)."""
+        self._check_bullets(bullets)
+        _capi.require_cuda(x, "x")
+        _no_grad_inputs(x, h, conv_buf)
+        B, NM, D = x.shape
+        n_rec = NM if num_recurrent is None else num_recurrent
+        batch = _capi.uniform_batch(B, NM, n_rec)
+        hidden = self._pack_state(h, conv_buf)
+        y, nh = run_trunk([self], self.n_heads, x.reshape(B * NM, D), None if alive is None else alive.reshape(-1),
+                          hidden, None, None, batch, None)
+        L, R = nh.shape[0], nh.shape[1]
+        if L == 0:
+            return y.reshape(B, NM, D), h[:0], conv_buf[:0]
+        return y.reshape(B, NM, D), nh[:, :, :D].contiguous(), nh[:, :, D:].reshape(L, R, CONV_KERNEL - 1, D)
+
+    def sequence(
+        self,
+        x: torch.Tensor,  # (T, B, N+M, D)
+        alive_mask: torch.Tensor,  # (T, B, N+M) bool
+        h0: torch.Tensor,  # (n_temporal, B*N, D)
+        conv_buf0: torch.Tensor,  # (n_temporal, B*N, CONV_KERNEL-1, D)
+        done_mask: torch.Tensor | None = None,  # (T, B) bool
+        num_recurrent: int | None = None,
+        bullets: torch.Tensor | None = None,
+        bullet_mask: torch.Tensor | None = None,
+    ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        """Full-sequence forward (griffin.py:419-472): returns (x, final h, final conv_buf)."""
+        self._check_bullets(bullets)
+        _capi.require_cuda(x, "x")
+        _no_grad_inputs(x, h0, conv_buf0)
+        T, B, NM, D = x.shape
+        n_rec = NM if num_recurrent is None else num_recurrent
+        batch = _capi.uniform_batch(B, NM, n_rec)
+        hidden = self._pack_state(h0, conv_buf0)
+        y, nh = run_trunk(
+            [self], self.n_heads, x.reshape(T, B * NM, D), None if alive_mask is None else alive_mask.reshape(T, -1),
+            hidden, done_mask, None, batch, T,
+        )
+        L, R = nh.shape[0], nh.shape[1]
+        if L == 0:
+            return y.reshape(T, B, NM, D), h0[:0], conv_buf0[:0]
+        return (
+            y.reshape(T, B, NM, D),
+            nh[:, :, :D].contiguous(),
+            nh[:, :, D:].reshape(L, R, CONV_KERNEL - 1, D),
+        )

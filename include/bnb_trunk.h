@@ -1,0 +1,206 @@
+/*
+ * C ABI of the B200 YemongPolicy trunk kernels.
+ *
+ * The reference (AvesNova/boost-and-broadside) is pure PyTorch and has no FFI layer;
+ * its trunk hot path sits behind nn.Module methods.  Each entry point below replaces
+ * the body of one of those methods and is what a binding on the reference side calls
+ * (a ctypes stub is enough: plain pointers, ints and one opaque stream handle).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless its name ends in _host;
+ *   - float tensors are float32, row-major, innermost stride 1, 16-byte aligned;
+ *   - bool tensors are one byte per element (torch.bool storage);
+ *   - Linear weights are (out_features, in_features) exactly as nn.Linear stores them;
+ *   - calls are asynchronous on `stream` (a cudaStream_t passed as void*), never
+ *     synchronise, never allocate, never free; scratch memory comes from the caller;
+ *   - the return value is a BnbStatus; nothing throws.
+ *
+ * Precision
+ *   BNB_FP32  every operation in float32 (the reference without autocast).
+ *   BNB_BF16  the reference under torch.autocast(bfloat16): Linear operands and outputs,
+ *             attention q/k/v/out, GeLU and gate*up rounded to bf16; norms, residual
+ *             stream, conv taps, pow, recurrence and hidden state float32.
+ */
+#ifndef BNB_TRUNK_H_
+#define BNB_TRUNK_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BNB_ABI_VERSION 1
+#define BNB_CONV_KERNEL 4 /* models/yemong/griffin.py:22 */
+
+typedef enum {
+  BNB_OK = 0,
+  BNB_ERR_NULL_POINTER = 1,
+  BNB_ERR_MISALIGNED = 2,
+  BNB_ERR_UNSUPPORTED_DIMS = 3,   /* d_model / n_heads / head width outside the built set */
+  BNB_ERR_TOO_MANY_TOKENS = 4,    /* an environment holds more tokens than the kernels take */
+  BNB_ERR_BAD_ARGUMENT = 5,
+  BNB_ERR_SCRATCH_TOO_SMALL = 6,
+  BNB_ERR_LAUNCH = 7,             /* the CUDA runtime refused a launch; see cudaGetLastError */
+  BNB_ERR_NO_DEVICE = 8
+} BnbStatus;
+
+typedef enum { BNB_FP32 = 0, BNB_BF16 = 1 } BnbPrecision;
+
+/* Which engine runs a BNB_BF16 call.
+ *   BNB_ENGINE_AUTO   tensor-core kernels where the shapes are built for them, else SIMT
+ *   BNB_ENGINE_SIMT   CUDA-core kernels with the bf16 roundings applied in software
+ *   BNB_ENGINE_TENSOR tensor-core kernels or BNB_ERR_UNSUPPORTED_DIMS
+ * BNB_FP32 always runs on the SIMT kernels. */
+typedef enum { BNB_ENGINE_AUTO = 0, BNB_ENGINE_SIMT = 1, BNB_ENGINE_TENSOR = 2 } BnbEngine;
+
+/* Parameters of one spatial sublayer.
+ * Replaces: TransformerBlock parameters, models/yemong/attention.py:51-74. */
+typedef struct {
+  const float* norm1_w;   /* (D)            norm1.weight          */
+  const float* qkv_w;     /* (3D, D)        qkv.weight            */
+  const float* out_w;     /* (D, D)         out_proj.weight       */
+  const float* norm2_w;   /* (D)            norm2.weight          */
+  const float* gate_w;    /* (4D, D)        ffn.gate_proj.weight  */
+  const float* up_w;      /* (4D, D)        ffn.up_proj.weight    */
+  const float* down_w;    /* (D, 4D)        ffn.down_proj.weight  */
+  const void*  packed;    /* optional: image written by bnb_pack_spatial, or NULL */
+} BnbSpatialWeights;
+
+/* Parameters of one temporal sublayer plus its field substitute.
+ * Replaces: GriffinTemporalBlock / RGLRU parameters, models/yemong/griffin.py:160-247,
+ * and YemongBlock.field_sub, griffin.py:359-368. */
+typedef struct {
+  const float* norm1_w;     /* (D)       norm1.weight            */
+  const float* linear1_w;   /* (D, D)    linear1.weight          */
+  const float* conv_w;      /* (D, 4)    conv.weight (D,1,4)     */
+  const float* conv_b;      /* (D)       conv.bias               */
+  const float* log_lambda;  /* (D)       rg_lru.log_lambda       */
+  const float* a_w;         /* (D, D)    rg_lru.linear_a.weight  */
+  const float* a_b;         /* (D)       rg_lru.linear_a.bias    */
+  const float* x_w;         /* (D, D)    rg_lru.linear_x.weight  */
+  const float* x_b;         /* (D)       rg_lru.linear_x.bias    */
+  const float* linear2_w;   /* (D, D)    linear2.weight          */
+  const float* out_w;       /* (D, D)    linear_out.weight       */
+  const float* norm2_w;     /* (D)       norm2.weight            */
+  const float* gate_w;      /* (4D, D)   gated_mlp.gate_proj     */
+  const float* up_w;        /* (4D, D)   gated_mlp.up_proj       */
+  const float* down_w;      /* (D, 4D)   gated_mlp.down_proj     */
+  const float* field_sub_w; /* (D, D)    field_sub[j].weight; may be NULL when no fields */
+  const void*  packed;      /* optional: image written by bnb_pack_temporal, or NULL */
+} BnbTemporalWeights;
+
+/* Geometry of one batch of environments.
+ *
+ * Uniform batch (tok_off == NULL): every environment holds tokens_per_env tokens, the
+ * first ships_per_env of which are ships (recurrent), the rest fields.  Token rows are
+ * env-major: row = env * tokens_per_env + token.  Hidden rows are env-major over ships:
+ * row = env * ships_per_env + ship (models/yemong/policy.py:284).
+ *
+ * Ragged batch (tok_off != NULL): environment e owns token rows
+ * [tok_off[e], tok_off[e+1]) and hidden rows [ship_off[e], ship_off[e+1]); its first
+ * ship_off[e+1]-ship_off[e] tokens are ships.  Both arrays hold n_envs+1 int32 on the
+ * device.  max_tokens_per_env must bound every environment.
+ */
+typedef struct {
+  int32_t n_envs;
+  int32_t tokens_per_env;
+  int32_t ships_per_env;
+  int32_t max_tokens_per_env;
+  int32_t total_tokens;        /* rows of x per timestep  */
+  int32_t total_ships;         /* rows of hidden          */
+  const int32_t* tok_off;
+  const int32_t* ship_off;
+} BnbBatch;
+
+int bnb_abi_version(void);
+const char* bnb_status_string(int status);
+
+/* Host-only query: 1 if (d_model, n_heads, max tokens per environment) can run with the
+ * given precision and engine, else 0.  No device is touched. */
+int bnb_supported(int d_model, int n_heads, int max_tokens_per_env, int precision, int engine);
+
+/* Bytes of scratch a call with this geometry may use (upper bound over all entry points).
+ * `timesteps` is 1 for a step. */
+size_t bnb_scratch_bytes(int d_model, const BnbBatch* batch, int timesteps);
+
+/* y = TransformerBlock.forward(x, alive_mask, bullets=None)
+ * Replaces: models/yemong/attention.py:76-99 (with _attn 114-147,168-169 and GatedMLP 21-37).
+ *   x, y    (n_rows, D) with n_rows = n_groups * batch->total_tokens; y may alias x
+ *   alive   (n_rows) bytes or NULL (no key masking, attention.py:142-145)
+ *   n_groups replicates the batch geometry (the T*B fold of griffin.py:443-449). */
+int bnb_spatial_block_fwd(const BnbSpatialWeights* w, int d_model, int n_heads,
+                          const float* x, const uint8_t* alive, float* y,
+                          const BnbBatch* batch, int n_groups, int precision, int engine,
+                          void* scratch, size_t scratch_bytes, void* stream);
+
+/* One temporal sublayer over T >= 1 timesteps for every token of the batch.
+ * Replaces: GriffinTemporalBlock.forward_sequence (griffin.py:249-286) on the ship tokens,
+ * GriffinTemporalBlock.forward_nonrecurrent (288-317) on the field tokens, and the
+ * split / permute / cat around them in YemongBlock.step (403-415) and .sequence (451-470).
+ *   x, y        (T, total_tokens, D); y may alias x
+ *   hidden_in   (total_ships, 4D) packed [h | tap0 | tap1 | tap2], taps oldest first
+ *               (models/yemong/policy.py:27-34); one slot of the policy's hidden tensor
+ *   hidden_out  same layout; may alias hidden_in
+ *   done        (T, n_envs) bytes or NULL; done[t] ends the episode at t, so step t+1
+ *               starts from a zero state and ignores conv taps from before it
+ *               (griffin.py:67-93, 213-218).  The taps written to hidden_out are the
+ *               last three linear1 outputs unmasked (griffin.py:277). */
+int bnb_temporal_block_fwd(const BnbTemporalWeights* w, int d_model,
+                           const float* x, float* y,
+                           const float* hidden_in, float* hidden_out,
+                           const uint8_t* done, const BnbBatch* batch, int timesteps,
+                           int precision, int engine,
+                           void* scratch, size_t scratch_bytes, void* stream);
+
+/* The whole trunk for one rollout step: n_blocks x (n_spatial spatial sublayers, then
+ * n_temporal temporal sublayers), hidden slot i*n_temporal+j for temporal sublayer j of
+ * block i.
+ * Replaces: the trunk loop and hidden unpack/repack of YemongPolicy.get_action_and_value,
+ * models/yemong/policy.py:315-354, with YemongBlock.step, griffin.py:376-417.
+ *   spatial   n_blocks*n_spatial entries, block-major
+ *   temporal  n_blocks*n_temporal entries, block-major
+ *   x, y      (total_tokens, D); y may alias x
+ *   hidden_in/out (n_blocks*n_temporal, total_ships, 4D); may alias
+ *   reset_env (n_envs) bytes or NULL: environments whose incoming state is taken as zero,
+ *             i.e. reset_hidden_for_envs (policy.py:268-285) folded into the load. */
+int bnb_trunk_step(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal,
+                   int n_blocks, int n_spatial, int n_temporal, int d_model, int n_heads,
+                   const float* x, const uint8_t* alive, float* y,
+                   const float* hidden_in, float* hidden_out, const uint8_t* reset_env,
+                   const BnbBatch* batch, int precision, int engine,
+                   void* scratch, size_t scratch_bytes, void* stream);
+
+/* The whole trunk over T timesteps from one initial state.
+ * Replaces: the trunk loop of YemongPolicy.evaluate_actions, models/yemong/policy.py:422-478,
+ * with YemongBlock.sequence, griffin.py:419-472.
+ *   x, y    (T, total_tokens, D); alive (T, total_tokens) or NULL; done (T, n_envs) or NULL
+ *   hidden_out receives the final state (the reference computes and drops it); may be NULL. */
+int bnb_trunk_sequence(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal,
+                       int n_blocks, int n_spatial, int n_temporal, int d_model, int n_heads,
+                       const float* x, const uint8_t* alive, float* y,
+                       const float* hidden_in, float* hidden_out, const uint8_t* done,
+                       const BnbBatch* batch, int timesteps, int precision, int engine,
+                       void* scratch, size_t scratch_bytes, void* stream);
+
+/* hidden_out = hidden_in * keep, keep = 0 for every ship row of a done environment.
+ * Replaces: YemongPolicy.reset_hidden_for_envs, models/yemong/policy.py:268-285.
+ *   hidden_in/out (n_slots, total_ships, 4D); may alias;  done (n_envs) bytes */
+int bnb_reset_hidden(const float* hidden_in, float* hidden_out, const uint8_t* done,
+                     int n_slots, int d_model, const BnbBatch* batch, void* stream);
+
+/* Bytes of the tensor-core weight image of one sublayer (bf16, pre-tiled). */
+size_t bnb_packed_spatial_bytes(int d_model);
+size_t bnb_packed_temporal_bytes(int d_model);
+
+/* Write the tensor-core image of a sublayer's float32 parameters into `packed`.
+ * Re-run after every parameter update; the image is derived data, never saved.
+ * No counterpart in the reference (it casts weights per call under autocast). */
+int bnb_pack_spatial(const BnbSpatialWeights* w, int d_model, int n_heads, void* packed, void* stream);
+int bnb_pack_temporal(const BnbTemporalWeights* w, int d_model, void* packed, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BNB_TRUNK_H_ */

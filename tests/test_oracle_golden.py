@@ -1,0 +1,130 @@
+"""The CPU oracle against outputs of the reference itself (tests/golden/*.npz)."""
+
+import pytest
+import torch
+
+from oracle import trunk_oracle as O
+from tests.helpers import assert_close, build_trunk, golden, stored_weights, trunk_params
+
+MODES = ("fp32", "bf16")
+
+
+def _spatial_params(g, D, H):
+    w = stored_weights(g)
+    if w:
+        return w
+    from boost_and_broadside_b200 import ModelConfig, TransformerBlock
+
+    torch.manual_seed(0)
+    return dict(TransformerBlock(ModelConfig(D, H, 2)).state_dict())
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("name", ["spatial_d128_n8", "spatial_d128_n152", "spatial_d64_n5", "spatial_d32_n3", "spatial_d32h2_n40"])
+def test_spatial_block(name, mode):
+    g = golden(name)
+    D, H = (int(v) for v in g["dims"])
+    p = _spatial_params(g, D, H)
+    y = O.spatial_block(g["x"], g["alive"], p, H, mode)
+    assert_close(y, g["y_" + mode], mode, name)
+    y = O.spatial_block(g["x"], None, p, H, mode)
+    assert_close(y, g["y_nomask_" + mode], mode, name + " (no mask)")
+
+
+def test_all_dead_environment_is_uniform_mean():
+    """An environment without a live key averages v over all its keys (attention.py:101-112)."""
+    g = golden("spatial_d128_n8")
+    assert not g["alive"][-1].any()
+    q = torch.randn(1, 2, 5, 8)
+    v = torch.randn(1, 2, 5, 8)
+    out = O.masked_attention(q, torch.randn(1, 2, 5, 8), v, torch.zeros(1, 5, dtype=torch.bool), "fp32")
+    assert torch.allclose(out, v.mean(dim=2, keepdim=True).expand_as(out), atol=1e-6)
+
+
+def _temporal_params(g, D):
+    w = stored_weights(g)
+    if w:
+        sub = w.pop("__sub.weight")
+        return w, sub
+    from boost_and_broadside_b200 import GriffinTemporalBlock
+
+    torch.manual_seed(0)
+    tb = GriffinTemporalBlock(D)
+    sub = torch.nn.Linear(D, D, bias=False)
+    p = dict(tb.state_dict())
+    p["conv.bias"] = g["conv_bias"]
+    return p, sub.weight.detach()
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("name", ["temporal_d128_t1", "temporal_d128_t9", "temporal_d64_t6"])
+def test_temporal_block(name, mode):
+    g = golden(name)
+    D = int(g["dims"][0])
+    p, sub = _temporal_params(g, D)
+    y, h, c = O.temporal_sequence(g["x"], g["h0"], g["conv"], None, p, mode)
+    assert_close(y, g["y_" + mode], mode, name + " y")
+    assert_close(h, g["h_" + mode], mode, name + " h")
+    assert_close(c, g["c_" + mode], mode, name + " conv")
+    if "yd_" + mode in g:
+        y, h, c = O.temporal_sequence(g["x"], g["h0"], g["conv"], g["done"], p, mode)
+        assert_close(y, g["yd_" + mode], mode, name + " y (done)")
+        assert_close(h, g["hd_" + mode], mode, name + " h (done)")
+        assert_close(c, g["cd_" + mode], mode, name + " conv (done)")
+    yf = O.temporal_nonrecurrent(g["x"], p, sub, mode)
+    assert_close(yf, g["yf_" + mode], mode, name + " field path")
+
+
+STEP_CASES = ["trunk_step_d128_8s4f", "trunk_step_d128_8s0f", "trunk_step_d128_30s2f", "trunk_step_d64_3s2f",
+              "trunk_step_d32_2s1f_b132"]
+SEQ_CASES = ["trunk_seq_d128_t6_8s0f", "trunk_seq_d128_t5_4s2f", "trunk_seq_d64_t7_3s2f"]
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("name", STEP_CASES)
+def test_trunk_step(name, mode):
+    g = golden(name)
+    trunk = build_trunk(g["dims"], g)
+    H = int(g["dims"][1])
+    y, nh = O.trunk_step(g["x"], g["alive"], g["hidden"], trunk_params(trunk), H, mode)
+    assert_close(y, g["y_" + mode], mode, name + " y")
+    assert_close(nh, g["hidden_" + mode], mode, name + " hidden")
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("name", SEQ_CASES)
+def test_trunk_sequence(name, mode):
+    g = golden(name)
+    trunk = build_trunk(g["dims"], g)
+    H = int(g["dims"][1])
+    P = trunk_params(trunk)
+    y, nh = O.trunk_sequence(g["x"], g["alive"], g["hidden"], g["done"], P, H, mode)
+    assert_close(y, g["y_" + mode], mode, name + " y")
+    assert_close(nh, g["hidden_" + mode], mode, name + " hidden")
+    y, nh = O.trunk_sequence(g["x"], g["alive"], g["hidden"], None, P, H, mode)
+    assert_close(y, g["y_nodone_" + mode], mode, name + " y (no done)")
+    assert_close(nh, g["hidden_nodone_" + mode], mode, name + " hidden (no done)")
+
+
+@pytest.mark.parametrize("name", SEQ_CASES)
+def test_sequence_equals_steps_with_resets(name):
+    """The load-bearing property of the trunk (tests/models/test_encoder.py:516-569 of the
+    reference): one sequence forward equals stepping with reset_hidden_for_envs."""
+    g = golden(name)
+    trunk = build_trunk(g["dims"], g)
+    H = int(g["dims"][1])
+    P = trunk_params(trunk)
+    y_seq, _ = O.trunk_sequence(g["x"], g["alive"], g["hidden"], g["done"], P, H, "fp32")
+    y_steps, _ = O.trunk_sequence_by_steps(g["x"], g["alive"], g["hidden"], g["done"], P, H, "fp32")
+    assert float((y_seq - y_steps).abs().max()) < 1e-4
+    assert_close(y_steps, g["y_steps_fp32"], "fp32", name + " reference step loop")
+
+
+def test_ragged_grouping_matches_uniform():
+    g = golden("trunk_step_d128_8s4f")
+    trunk = build_trunk(g["dims"], g)
+    P = trunk_params(trunk)
+    B, NM, D = g["x"].shape
+    y0, h0 = O.trunk_step(g["x"], g["alive"], g["hidden"], P, 4, "fp32")
+    y1, h1 = O.trunk_step_ragged(g["x"].reshape(-1, D), g["alive"].reshape(-1), g["hidden"], [NM] * B, [8] * B, P, 4, "fp32")
+    assert torch.equal(y0.reshape(-1, D), y1) and torch.equal(h0, h1)
