@@ -1,0 +1,364 @@
+"""Benchmark of the YemongPolicy trunk hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload C2|C3|C4|C5]
+
+A step is one pass of the trunk over one batch of synthetic environments.  The default
+workload is the full rollout policy step (all trunk attention layers + Griffin RG-LRU single
+step with carried hidden state) at 4v4 + 4 refractive-field tokens = 12 tokens/env, 8192
+envs, bf16 activations / fp32 state, random-init weights at the rl-fields profile's dims.
+With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank runs its own
+batch of that size: environments are independent, so there is no collective on the data
+path, and the aggregate is N batches over the slowest rank's device time (weak scaling).
+
+One JSON line is printed by rank 0: entity tokens/s with inputs resident in HBM (`value`),
+the same through the public module API with pinned host buffers and both copies inside the
+timed region (`e2e`), the HBM roofline fraction of the step from algorithmic bytes
+(`roofline`), and the CPU oracle timed on the host cores on a bounded sample
+(`cpu_baseline`).  `--impl reference` times that CPU restatement alone.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "policy-step entity tokens/sec per B200 (attn+RG-LRU), % of HBM roofline"
+UNIT = "entity_tokens/s"
+FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
+
+
+def measured_peaks() -> tuple[float, float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, FALLBACK_BF16_TFLOPS, "fallback"
+
+
+def make_workload(name: str, rank: int, scale: float = 1.0):
+    from boost_and_broadside_b200 import workloads as W
+
+    seed = 100 + rank
+    if name == "C2":
+        return W.c2(n_envs=max(1, int(8192 * scale)), seed=seed)
+    if name == "C3":
+        return W.c3(n_envs=max(1, int(1024 * scale)), seed=seed)
+    if name == "C4":
+        return W.c4(n_envs=max(1, int(4096 * scale)), seed=seed)
+    if name == "C5":
+        return W.c5(n_envs=max(1, int(16384 * scale)), seed=seed)
+    raise SystemExit(f"unknown workload {name}")
+
+
+WORKLOAD_TEXT = {
+    "C2": "rollout trunk step, 8192 envs x (8 ships + 4 fields), bf16 activations / fp32 state",
+    "C3": "trunk step, 1024 envs x 152 ships (64 v 88), bf16",
+    "C4": "recurrent-PPO sequence forward, T=32 x 4096 envs x 8 ships, bf16",
+    "C5": "ragged trunk step, 16384 envs, tokens U{2..128}, bf16",
+}
+
+
+# ----------------------------------------------------------------------------- clocks
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples of one GPU during the timed region."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.file = None
+
+    def start(self):
+        try:
+            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=self.file, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.file.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        try:
+            os.unlink(self.file.name)
+        except OSError:
+            pass
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ----------------------------------------------------------------------------- CPU arm
+
+
+def oracle_runner(workload, params, n_heads: int):
+    from oracle import trunk_oracle as O
+
+    w = workload
+    if w.kind == "step":
+        return lambda: O.trunk_step(w.x, w.alive, w.hidden, params, n_heads, w.mode)
+    if w.kind == "sequence":
+        return lambda: O.trunk_sequence(w.x, w.alive, w.hidden, w.done, params, n_heads, w.mode)
+    if w.kind == "ragged":
+        nt, ns = w.n_tokens.tolist(), w.n_ships.tolist()
+        return lambda: O.trunk_step_ragged(w.x, w.alive, w.hidden, nt, ns, params, n_heads, w.mode)
+    raise SystemExit("no CPU runner for this workload")
+
+
+def cpu_sample_scale(name: str) -> float:
+    # bounded samples of the workload: a few seconds of CPU work per pass
+    return {"C2": 1024 / 8192, "C3": 64 / 1024, "C4": 32 / 4096, "C5": 768 / 16384}[name]
+
+
+def time_cpu(name: str, passes: int, warmup: int) -> dict:
+    import boost_and_broadside_b200 as bnb
+    from boost_and_broadside_b200 import workloads as W
+    from oracle import trunk_oracle as O
+
+    cores = len(os.sched_getaffinity(0))
+    torch.set_num_threads(cores)
+    torch.manual_seed(0)
+    trunk = bnb.YemongTrunk(W.rl_config()).eval()
+    params = O.split_trunk_state_dict(trunk.state_dict())
+    w = make_workload(name, 0, cpu_sample_scale(name))
+    run = oracle_runner(w, params, 4)
+    with torch.no_grad():
+        for _ in range(warmup):
+            run()
+        times = []
+        for _ in range(passes):
+            t0 = time.perf_counter()
+            run()
+            times.append(time.perf_counter() - t0)
+    t = statistics.median(times)
+    return {
+        "value": w.entity_tokens / t, "unit": UNIT, "cores": cores, "kind": "port",
+        "sample": f"{w.meta.get('n_envs')} envs of {name} per pass ({w.entity_tokens} tokens), median of {passes} passes, "
+                  f"torch CPU oracle with {cores} threads",
+        "ms_per_pass": t * 1e3, "tokens_per_pass": w.entity_tokens,
+    }
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    passes = max(1, min(args.steps, 20))
+    base = time_cpu(args.workload, passes, max(1, min(args.warmup, 3)))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": passes, "warmup": max(1, min(args.warmup, 3)), "ms_per_step": base["ms_per_pass"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD_TEXT[args.workload], "id": args.workload,
+                   "note": "CPU restatement of the reference's PyTorch forward on a bounded sample of the workload"},
+        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- GPU arm
+
+
+def run_ours(args) -> None:
+    import boost_and_broadside_b200 as bnb
+    from boost_and_broadside_b200 import _capi
+    from boost_and_broadside_b200 import workloads as W
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the trunk has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+
+    cfg = W.rl_config()
+    torch.manual_seed(0)
+    trunk = bnb.YemongTrunk(cfg).eval()
+    n_params = sum(p.numel() for n, p in trunk.named_parameters() if "bullet" not in n)
+    trunk = trunk.to(dev)
+    w = make_workload(args.workload, rank)
+    engine = {"auto": _capi.ENGINE_AUTO, "simt": _capi.ENGINE_SIMT, "tensor": _capi.ENGINE_TENSOR}[args.engine]
+
+    x_h = w.x.pin_memory()
+    alive_h = w.alive.pin_memory()
+    x_d = x_h.to(dev, non_blocking=True)
+    alive_d = alive_h.to(dev, non_blocking=True)
+    hidden = [w.hidden.to(dev), None]
+    done_d = None if w.done is None else w.done.to(dev)
+    ragged = bnb.RaggedBatch(w.n_tokens, w.n_ships) if w.kind == "ragged" else None
+
+    def step(xin, alive, h):
+        if w.kind == "step":
+            return trunk.step(xin, alive, h, engine=engine)
+        if w.kind == "sequence":
+            return trunk.sequence(xin, alive, h, done_d, engine=engine)
+        return trunk.step_ragged(xin, alive, h, ragged, engine=engine)
+
+    carry = w.kind != "sequence"  # a sequence forward restarts from the same initial state
+    ctx = torch.autocast("cuda", dtype=torch.bfloat16)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing
+    with torch.no_grad(), ctx:
+        h = hidden[0]
+        for _ in range(args.warmup):
+            y, h2 = step(x_d, alive_d, h)
+            h = h2 if carry else h
+        barrier()
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        launches0 = _capi.lib.bnb_launch_count()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+        ev[0].record()
+        for i in range(args.steps):
+            y, h2 = step(x_d, alive_d, h)
+            h = h2 if carry else h
+            ev[i + 1].record()
+        barrier()
+        launches = _capi.lib.bnb_launch_count() - launches0
+        clocks = sampler.stop() if rank == 0 else None
+    total_ms = ev[0].elapsed_time(ev[-1])
+    per_step = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+
+    # ---- end to end through the public API with pinned host buffers
+    y_h = torch.empty(w.x.shape, dtype=torch.float32).pin_memory()
+    with torch.no_grad(), ctx:
+        h = hidden[0]
+        for _ in range(max(1, min(args.warmup, 3))):
+            y, h2 = step(x_h.to(dev, non_blocking=True), alive_h.to(dev, non_blocking=True), h)
+            y_h.copy_(y, non_blocking=True)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            y, h2 = step(x_h.to(dev, non_blocking=True), alive_h.to(dev, non_blocking=True), h)
+            h = h2 if carry else h
+            y_h.copy_(y, non_blocking=True)
+        e1.record()
+        barrier()
+    e2e_ms = e0.elapsed_time(e1)
+
+    t = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms = float(t[0]), float(t[1])
+    tokens = w.entity_tokens
+    if dist is not None:
+        tk = torch.tensor([tokens], dtype=torch.float64, device=dev)
+        dist.all_reduce(tk)
+        tokens_all = float(tk[0])
+    else:
+        tokens_all = float(tokens)
+
+    if rank == 0:
+        hbm, tflops, src = measured_peaks()
+        ms_step = total_ms / args.steps
+        alg_bytes = W.algorithmic_bytes(w, n_params)
+        alg_flops = W.algorithmic_flops(w, cfg)
+        kernel_ms = statistics.mean(per_step)
+        achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": tokens_all * args.steps / (total_ms * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD_TEXT[args.workload], "id": args.workload, "engine": args.engine,
+                       "tokens_per_step_per_gpu": tokens, "l2": "inputs larger than L2 (no flush)",
+                       "weights": "random init, seed 0, rl-fields dims (D=128, 4 heads, S S T | S S T)"},
+            "e2e": {"value": tokens_all * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": x_h.numel() * 4 + alive_h.numel(), "d2h_bytes_per_step": y_h.numel() * 4,
+                    "note": "x and alive from pinned host memory, y back to pinned host memory, hidden state carried on the device"},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
+                         "traffic": None, "of": src, "algorithmic_bytes_per_step": alg_bytes,
+                         "kernel": "whole trunk step (all launches of one step)", "kernel_ms": kernel_ms},
+            "tensor": {"achieved": alg_flops / (kernel_ms * 1e-3) / 1e12, "peak": tflops, "unit": "TFLOP/s",
+                       "frac": alg_flops / (kernel_ms * 1e-3) / 1e12 / tflops, "of": src,
+                       "algorithmic_flops_per_step": alg_flops},
+            "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")} if clocks else None,
+        }
+        if world == 1 and not args.no_cpu:
+            base = time_cpu(args.workload, 3, 1)
+            line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="C2", choices=sorted(WORKLOAD_TEXT))
+    ap.add_argument("--engine", default="auto", choices=["auto", "simt", "tensor"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -52,6 +52,7 @@ class Batch(C.Structure):
 EXPORTS = {
     "bnb_abi_version": (C.c_int, []),
     "bnb_status_string": (C.c_char_p, [C.c_int]),
+    "bnb_launch_count": (C.c_ulonglong, []),
     "bnb_supported": (C.c_int, [C.c_int] * 5),
     "bnb_scratch_bytes": (C.c_size_t, [C.c_int, C.POINTER(Batch), C.c_int]),
     "bnb_spatial_block_fwd": (

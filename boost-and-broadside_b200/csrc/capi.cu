@@ -5,7 +5,12 @@
 
 #include "bnb_trunk.h"
 #include "exact_kernels.h"
+#include "launch_count.h"
 #include "tensor_kernels.h"
+
+namespace bnb {
+std::atomic<unsigned long long> g_launches{0};
+}
 
 namespace {
 
@@ -90,6 +95,8 @@ bool use_tensor(int precision, int engine, int D, int H, const BnbBatch* b) {
 extern "C" {
 
 int bnb_abi_version(void) { return BNB_ABI_VERSION; }
+
+unsigned long long bnb_launch_count(void) { return bnb::g_launches.load(std::memory_order_relaxed); }
 
 const char* bnb_status_string(int status) {
   switch (status) {

@@ -12,6 +12,7 @@
 // of the reference.
 #include "common.cuh"
 #include "exact_kernels.h"
+#include "launch_count.h"
 
 namespace bnb {
 namespace exact {
@@ -534,6 +535,7 @@ static int spatial_impl(const BnbSpatialWeights& w, int D, int H, const float* x
   {
     size_t sm = (size_t)(2 * ROWS * (D + 4) + NCHUNK * WS_STRIDE) * sizeof(float);
     if (!opt_in(k_spatial_qkv<EMU>, sm)) return BNB_ERR_LAUNCH;
+    count_launch();
     k_spatial_qkv<EMU><<<n_tiles, NTHREADS, sm, st>>>(x, qkv, n_rows, D, w.norm1_w, w.qkv_w);
   }
   {
@@ -542,6 +544,7 @@ static int spatial_impl(const BnbSpatialWeights& w, int D, int H, const float* x
     int per_env = b.max_tokens_per_env * H;
     dim3 grid(n_groups * b.n_envs, (per_env + 127) / 128 > 4 ? 4 : (per_env + 127) / 128);
     if (grid.y < 1) grid.y = 1;
+    count_launch();
     switch (dh) {
       case 8:  k_attention<EMU, 8><<<grid, 128, 0, st>>>(qkv, alive, o, map, n_groups, D, H); break;
       case 16: k_attention<EMU, 16><<<grid, 128, 0, st>>>(qkv, alive, o, map, n_groups, D, H); break;
@@ -553,6 +556,7 @@ static int spatial_impl(const BnbSpatialWeights& w, int D, int H, const float* x
   {
     size_t sm = smem_rows(D, 3);
     if (!opt_in(k_spatial_post<EMU>, sm)) return BNB_ERR_LAUNCH;
+    count_launch();
     k_spatial_post<EMU><<<n_tiles, NTHREADS, sm, st>>>(x, o, y, n_rows, D, w.out_w, w.norm2_w,
                                                        w.gate_w, w.up_w, w.down_w);
   }
@@ -575,6 +579,7 @@ static int temporal_impl(const BnbTemporalWeights& w, int D, const float* x, flo
   if (b.total_ships > 0) {
     if (!opt_in(k_temporal<EMU, false>, sm)) return BNB_ERR_LAUNCH;
     int n_tiles = (b.total_ships + ROWS - 1) / ROWS;
+    count_launch();
     k_temporal<EMU, false><<<n_tiles, NTHREADS, sm, st>>>(x, y, hin, hout, done, reset_env, map, T, D, w);
   }
   int n_fields = (b.total_tokens - b.total_ships) * T;
@@ -582,6 +587,7 @@ static int temporal_impl(const BnbTemporalWeights& w, int D, const float* x, flo
     if (!w.field_sub_w) return BNB_ERR_NULL_POINTER;
     if (!opt_in(k_temporal<EMU, true>, sm)) return BNB_ERR_LAUNCH;
     int n_tiles = (n_fields + ROWS - 1) / ROWS;
+    count_launch();
     k_temporal<EMU, true><<<n_tiles, NTHREADS, sm, st>>>(x, y, nullptr, nullptr, nullptr, nullptr, map, T, D, w);
   }
   return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
@@ -600,6 +606,7 @@ int reset_hidden(const float* in, float* out, const uint8_t* done, int n_slots, 
   size_t total = (size_t)n_slots * b.total_ships * D;
   if (total == 0) return BNB_OK;
   int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+  count_launch();
   k_reset_hidden<<<blocks, 256, 0, st>>>(in, out, done, map, n_slots, D);
   return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
 }

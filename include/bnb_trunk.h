@@ -117,6 +117,10 @@ typedef struct {
 int bnb_abi_version(void);
 const char* bnb_status_string(int status);
 
+/* Kernels launched by this library in this process so far (instrumentation for the
+ * benchmark's launch accounting; no counterpart in the reference). */
+unsigned long long bnb_launch_count(void);
+
 /* Host-only query: 1 if (d_model, n_heads, max tokens per environment) can run with the
  * given precision and engine, else 0.  No device is touched. */
 int bnb_supported(int d_model, int n_heads, int max_tokens_per_env, int precision, int engine);

@@ -1,0 +1,84 @@
+"""The C-ABI library loads and exports every symbol include/bnb_trunk.h declares; host-side
+argument validation returns status codes without touching a device."""
+
+import ctypes as C
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "bnb_trunk.h")
+
+
+def declared_functions() -> list[str]:
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(bnb_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_header_and_binding_agree():
+    from boost_and_broadside_b200 import _capi
+
+    assert declared_functions() == sorted(_capi.EXPORTS)
+
+
+def test_library_exports_every_declared_symbol():
+    from boost_and_broadside_b200 import _capi
+
+    lib = C.CDLL(_capi.LIB_PATH)
+    for name in declared_functions():
+        assert hasattr(lib, name), f"{name} is declared in bnb_trunk.h but not exported"
+    assert _capi.lib.bnb_abi_version() == 1
+    assert _capi.lib.bnb_status_string(0) == b"ok"
+    assert b"null" in _capi.lib.bnb_status_string(1)
+
+
+def test_supported_query_is_host_only():
+    from boost_and_broadside_b200 import _capi
+
+    q = _capi.lib.bnb_supported
+    assert q(128, 4, 12, _capi.BNB_FP32, _capi.ENGINE_AUTO) == 1
+    assert q(128, 4, 152, _capi.BNB_BF16, _capi.ENGINE_AUTO) == 1
+    assert q(64, 4, 8, _capi.BNB_BF16, _capi.ENGINE_SIMT) == 1
+    assert q(32, 4, 8, _capi.BNB_FP32, _capi.ENGINE_SIMT) == 1
+    assert q(100, 4, 8, _capi.BNB_FP32, _capi.ENGINE_AUTO) == 0      # not a multiple of 32
+    assert q(256, 4, 8, _capi.BNB_FP32, _capi.ENGINE_AUTO) == 0      # above the built width
+    assert q(128, 3, 8, _capi.BNB_FP32, _capi.ENGINE_AUTO) == 0      # heads do not divide
+    assert q(128, 4, 0, _capi.BNB_FP32, _capi.ENGINE_AUTO) == 0
+    assert q(128, 4, 8, 7, _capi.ENGINE_AUTO) == 0
+
+
+def test_argument_validation_returns_status_codes():
+    """Bad arguments are rejected on the host before any launch."""
+    from boost_and_broadside_b200 import _capi
+
+    lib = _capi.lib
+    batch = _capi.uniform_batch(4, 8, 8)
+    w = _capi.SpatialWeights()  # all null
+    st = lib.bnb_spatial_block_fwd(w, 128, 4, None, None, None, batch, 1, 0, 0, None, 0, None)
+    assert st == 1  # BNB_ERR_NULL_POINTER
+    st = lib.bnb_spatial_block_fwd(w, 100, 4, None, None, None, batch, 1, 0, 0, None, 0, None)
+    assert st == 3  # BNB_ERR_UNSUPPORTED_DIMS
+    bad = _capi.Batch(4, 8, 9, 8, 32, 36, None, None)  # more ships than tokens
+    st = lib.bnb_spatial_block_fwd(w, 128, 4, None, None, None, bad, 1, 0, 0, None, 0, None)
+    assert st == 5  # BNB_ERR_BAD_ARGUMENT
+    fake = 0x1000
+    w = _capi.SpatialWeights(*([fake] * 7), None)
+    st = lib.bnb_spatial_block_fwd(w, 128, 4, fake + 4, None, fake, batch, 1, 0, 0, fake, 1 << 30, None)
+    assert st == 2  # BNB_ERR_MISALIGNED
+    st = lib.bnb_spatial_block_fwd(w, 128, 4, fake, None, fake, batch, 1, 0, 1, fake, 16, None)
+    assert st == 6  # BNB_ERR_SCRATCH_TOO_SMALL
+    st = lib.bnb_spatial_block_fwd(w, 128, 4, fake, None, fake, batch, 1, 9, 0, fake, 1 << 30, None)
+    assert st == 5
+    # an empty batch is a successful no-op
+    empty = _capi.uniform_batch(0, 8, 8)
+    assert lib.bnb_spatial_block_fwd(w, 128, 4, None, None, None, empty, 1, 0, 0, None, 0, None) == 0
+    assert lib.bnb_scratch_bytes(128, batch, 1) >= 4 * 8 * 4 * 128 * 4
+
+
+def test_missing_library_fails_loudly(tmp_path):
+    from boost_and_broadside_b200 import _capi
+
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        _capi.load_library(str(tmp_path / "libbnb_trunk.so"))

@@ -1,0 +1,105 @@
+"""Host-side mirror of the reference interface: parameter names, shapes, init, errors."""
+
+import numpy as np
+import pytest
+import torch
+
+from tests.helpers import build_trunk, checksum, golden
+
+
+def test_state_dict_keys_match_reference_layout():
+    trunk = build_trunk([128, 4, 2, 2, 1, 1])
+    keys = set(trunk.state_dict())
+    for i in range(2):
+        for j in range(2):
+            base = f"yemong_layers.{i}.spatial.{j}."
+            for n in ("norm1.weight", "qkv.weight", "out_proj.weight", "norm2.weight", "ffn.gate_proj.weight",
+                      "ffn.up_proj.weight", "ffn.down_proj.weight"):
+                assert base + n in keys
+        assert f"yemong_layers.{i}.spatial.0.kv_bullet.weight" in keys
+        assert f"yemong_layers.{i}.spatial.1.kv_bullet.weight" not in keys
+        base = f"yemong_layers.{i}.temporal.0."
+        for n in ("norm1.weight", "linear1.weight", "conv.weight", "conv.bias", "rg_lru.log_lambda",
+                  "rg_lru.linear_a.weight", "rg_lru.linear_a.bias", "rg_lru.linear_x.weight", "rg_lru.linear_x.bias",
+                  "linear2.weight", "linear_out.weight", "norm2.weight", "gated_mlp.gate_proj.weight",
+                  "gated_mlp.up_proj.weight", "gated_mlp.down_proj.weight"):
+            assert base + n in keys
+        assert f"yemong_layers.{i}.field_sub.0.weight" in keys
+    sd = trunk.state_dict()
+    assert sd["yemong_layers.0.spatial.0.qkv.weight"].shape == (384, 128)
+    assert sd["yemong_layers.0.spatial.0.kv_bullet.weight"].shape == (256, 128)
+    assert sd["yemong_layers.0.temporal.0.conv.weight"].shape == (128, 1, 4)
+    assert all(v.dtype == torch.float32 for v in sd.values())
+    assert sum(v.numel() for v in trunk.parameters()) == 1_707_776
+    assert torch.equal(sd["yemong_layers.1.field_sub.0.weight"], torch.eye(128))
+    assert torch.equal(sd["yemong_layers.0.temporal.0.rg_lru.log_lambda"], torch.linspace(0.0, 4.0, 128))
+
+
+@pytest.mark.parametrize("name", ["trunk_step_d128_8s4f", "trunk_step_d64_3s2f", "trunk_seq_d128_t6_8s0f"])
+def test_seeded_init_reproduces_reference_weights(name):
+    """The mirror modules draw parameters in the reference's order, so seed 0 gives the
+    reference's weights (checksums stored when the golden vectors were made)."""
+    g = golden(name)
+    trunk = build_trunk(g["dims"])
+    got = checksum(trunk.state_dict())
+    assert np.allclose(got, g["wsum"].numpy(), rtol=0, atol=1e-9), (got, g["wsum"])
+
+
+def test_hidden_layout_helpers():
+    trunk = build_trunk([64, 4, 3, 1, 2, 0])
+    h = trunk.initial_hidden(5, 3, torch.device("cpu"))
+    assert h.shape == (6, 15, 256) and h.dtype == torch.float32 and not h.any()
+    assert trunk.n_hidden_layers == 6
+    assert trunk.yemong_layers[0].n_temporal == 2
+
+
+def test_no_cpu_path():
+    from boost_and_broadside_b200 import ModelConfig, TransformerBlock
+
+    block = TransformerBlock(ModelConfig(128, 4, 1))
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        block(torch.zeros(1, 2, 128))
+    trunk = build_trunk([128, 4, 1, 1, 1, 0])
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        trunk.step(torch.zeros(1, 2, 128), None, torch.zeros(1, 2, 512))
+
+
+def test_config_validation_mirrors_reference():
+    from boost_and_broadside_b200 import ModelConfig
+
+    with pytest.raises(ValueError):
+        ModelConfig(130, 4, 1)
+    with pytest.raises(ValueError):
+        ModelConfig(128, 4, 1, n_spatial_per_block=1, n_bullet_cross_per_block=2)
+    assert ModelConfig(128, 4, 2, 2, 1).n_hidden_layers == 2
+
+
+def test_ragged_batch_offsets():
+    from boost_and_broadside_b200 import RaggedBatch
+
+    rb = RaggedBatch(torch.tensor([4, 2, 7]), torch.tensor([2, 2, 6]))
+    batch, keep = rb.build(torch.device("cpu"))
+    assert batch.n_envs == 3 and batch.total_tokens == 13 and batch.total_ships == 10
+    assert batch.max_tokens_per_env == 7
+    assert keep[0].tolist() == [0, 4, 6, 13] and keep[1].tolist() == [0, 2, 4, 10]
+    with pytest.raises(RuntimeError):
+        RaggedBatch(torch.tensor([2]), torch.tensor([3])).build(torch.device("cpu"))
+
+
+def test_workload_generators_follow_the_configurations():
+    from boost_and_broadside_b200 import workloads as W
+
+    w = W.c1()
+    assert w.x.shape == (256, 8, 128) and w.alive[:, :4].any(1).all() and w.alive[:, 4:].any(1).all()
+    w = W.c2(n_envs=64)
+    assert w.x.shape == (64, 12, 128) and w.hidden.shape == (2, 512, 512) and w.alive[:, 8:].all()
+    assert abs(float(w.hidden.std()) - 0.5) < 0.01
+    w = W.c3(n_envs=16)
+    assert w.x.shape == (16, 152, 128) and w.alive[:, :64].any(1).all() and w.alive[:, 64:].any(1).all()
+    w = W.c4(n_envs=8, timesteps=32)
+    assert w.x.shape == (32, 8, 8, 128) and w.done.shape == (32, 8)
+    w = W.c5(n_envs=500)
+    n, s = w.n_tokens, w.n_ships
+    assert int(n.min()) >= 2 and int(n.max()) <= 128 and bool((s >= 2).all()) and bool((s % 2 == 0).all())
+    assert bool(((n - s) >= 0).all()) and bool(((n - s) <= 4).all())
+    assert w.x.shape[0] == int(n.sum()) and w.hidden.shape[1] == int(s.sum())
