@@ -60,6 +60,10 @@ EXPORTS = {
         [C.POINTER(SpatialWeights), C.c_int, C.c_int, _fp, _fp, _fp, C.POINTER(Batch), C.c_int, C.c_int, C.c_int,
          _fp, C.c_size_t, _fp],
     ),
+    "bnb_spatial_block_fwd_static": (
+        C.c_int,
+        [C.POINTER(SpatialWeights), C.c_int, C.c_int, _fp, _fp, _fp, C.POINTER(Batch), C.c_int, C.c_int, _fp],
+    ),
     "bnb_temporal_block_fwd": (
         C.c_int,
         [C.POINTER(TemporalWeights), C.c_int, _fp, _fp, _fp, _fp, _fp, C.POINTER(Batch), C.c_int, C.c_int, C.c_int,

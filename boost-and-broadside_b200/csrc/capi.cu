@@ -109,6 +109,7 @@ const char* bnb_status_string(int status) {
     case BNB_ERR_SCRATCH_TOO_SMALL: return "scratch buffer smaller than bnb_scratch_bytes";
     case BNB_ERR_LAUNCH: return "CUDA launch failed";
     case BNB_ERR_NO_DEVICE: return "no CUDA device";
+    case BNB_ERR_EXCEEDS_STATIC_LIMIT: return "batch has more rows than the fixed scratch of the no-allocation entry point holds";
     default: return "unknown status";
   }
 }

@@ -1,0 +1,83 @@
+// bnb_spatial_block_fwd_static: the spatial sublayer for callers that cannot allocate.
+//
+// bnb_spatial_block_fwd needs (rows x 4 x d_model) floats of scratch for the projected
+// q/k/v and the attention output, and expects the caller to bring that memory.  Some callers
+// have no way to get it: a thin ctypes / cgo / JNI stub owns no device allocator, and a host
+// process that has already handed the whole device to another framework's memory pool must
+// not call cudaMalloc behind that pool's back.  For them this entry point keeps the scratch
+// in a fixed array that is part of the library image.  The price: every GPU that loads the
+// library holds BNB_STATIC_SCRATCH_BYTES of device memory until the process exits, and the
+// batch is limited to BNB_STATIC_MAX_ROWS token rows.
+#include <cuda_runtime.h>
+
+#include <mutex>
+
+#include "bnb_trunk.h"
+#include "exact_kernels.h"
+
+namespace {
+
+constexpr int kMaxRows = BNB_STATIC_MAX_ROWS;
+constexpr int kMaxWidth = 128;                            // largest d_model the kernels take
+constexpr size_t kFloats = (size_t)kMaxRows * 4 * kMaxWidth;  // q, k, v and attention output
+static_assert(kFloats * sizeof(float) == BNB_STATIC_SCRATCH_BYTES, "header and array disagree");
+
+// The scratch itself.  In host code this name is only a handle for the runtime, not a
+// device address: the address is looked up per device below and handed to the kernels.
+static __device__ __align__(256) float g_static_scratch[kFloats];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_mutex;
+float* g_scratch_ptr[kMaxDevices] = {};  // device address of g_static_scratch on each GPU
+
+// Device address of the array on the current device; looked up once per device.
+int scratch_address(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return BNB_ERR_NO_DEVICE;
+  if (dev >= kMaxDevices) return BNB_ERR_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!g_scratch_ptr[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || !p) return BNB_ERR_LAUNCH;
+    g_scratch_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_scratch_ptr[dev];
+  return BNB_OK;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+extern "C" int bnb_spatial_block_fwd_static(const BnbSpatialWeights* w, int d_model, int n_heads, const float* x,
+                                            const uint8_t* alive, float* y, const BnbBatch* batch, int n_groups,
+                                            int precision, void* stream) {
+  if (!w || !batch) return BNB_ERR_NULL_POINTER;
+  if (d_model <= 0 || n_heads <= 0 || d_model % n_heads != 0 || n_groups < 0) return BNB_ERR_BAD_ARGUMENT;
+  if (d_model % 32 != 0 || d_model > kMaxWidth) return BNB_ERR_UNSUPPORTED_DIMS;
+  const int dh = d_model / n_heads;
+  if (dh != 8 && dh != 16 && dh != 32 && dh != 64) return BNB_ERR_UNSUPPORTED_DIMS;
+  if (precision != BNB_FP32 && precision != BNB_BF16) return BNB_ERR_BAD_ARGUMENT;
+  if (batch->n_envs < 0 || batch->total_tokens < 0 || batch->total_ships < 0) return BNB_ERR_BAD_ARGUMENT;
+  if ((batch->tok_off == nullptr) != (batch->ship_off == nullptr)) return BNB_ERR_BAD_ARGUMENT;
+  if (!batch->tok_off && (long long)batch->n_envs * batch->tokens_per_env != batch->total_tokens)
+    return BNB_ERR_BAD_ARGUMENT;
+  const long long n_rows = (long long)n_groups * batch->total_tokens;
+  if (n_rows > kMaxRows) return BNB_ERR_EXCEEDS_STATIC_LIMIT;
+  if (n_rows == 0) return BNB_OK;
+  const void* ps[] = {w->norm1_w, w->qkv_w, w->out_w, w->norm2_w, w->gate_w, w->up_w, w->down_w, x, y};
+  for (const void* p : ps) {
+    if (!p) return BNB_ERR_NULL_POINTER;
+    if (!aligned16(p)) return BNB_ERR_MISALIGNED;
+  }
+  float* scratch = nullptr;
+  int st = scratch_address(&scratch);
+  if (st) return st;
+  // Nothing in the array has to start at zero: the q/k/v rows and the attention rows this
+  // call reads are all written by this call first.  What an earlier call left is ignored.
+  float* qkv = scratch;
+  float* o = scratch + (size_t)kMaxRows * 3 * kMaxWidth;
+  return bnb::exact::spatial_block(*w, d_model, n_heads, x, alive, y, *batch, n_groups, precision == BNB_BF16,
+                                   qkv, o, static_cast<cudaStream_t>(stream));
+}

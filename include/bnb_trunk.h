@@ -43,7 +43,8 @@ typedef enum {
   BNB_ERR_BAD_ARGUMENT = 5,
   BNB_ERR_SCRATCH_TOO_SMALL = 6,
   BNB_ERR_LAUNCH = 7,             /* the CUDA runtime refused a launch; see cudaGetLastError */
-  BNB_ERR_NO_DEVICE = 8
+  BNB_ERR_NO_DEVICE = 8,
+  BNB_ERR_EXCEEDS_STATIC_LIMIT = 9 /* more rows than bnb_spatial_block_fwd_static's fixed scratch holds */
 } BnbStatus;
 
 typedef enum { BNB_FP32 = 0, BNB_BF16 = 1 } BnbPrecision;
@@ -138,6 +139,28 @@ int bnb_spatial_block_fwd(const BnbSpatialWeights* w, int d_model, int n_heads,
                           const float* x, const uint8_t* alive, float* y,
                           const BnbBatch* batch, int n_groups, int precision, int engine,
                           void* scratch, size_t scratch_bytes, void* stream);
+
+/* The same spatial sublayer for callers that cannot allocate device memory at all: a bare
+ * ctypes / cgo / JNI stub that owns no allocator, or a host that has given the whole device
+ * to another framework's pool and must not cudaMalloc around it.  The scratch that
+ * bnb_spatial_block_fwd takes from the caller lives here in a fixed array inside the library
+ * image, so this call (and everything under it) performs no cudaMalloc / cudaFree and uses
+ * no allocating library routine.  It has no counterpart in the reference.
+ *   - limit: n_groups * batch->total_tokens <= BNB_STATIC_MAX_ROWS, else
+ *     BNB_ERR_EXCEEDS_STATIC_LIMIT and nothing is launched; d_model <= 128;
+ *   - cost: every GPU that loads the library holds BNB_STATIC_SCRATCH_BYTES until exit;
+ *   - always the CUDA-core (SIMT) kernels, in either precision;
+ *   - the first call on each device looks up the array's device address (that device must
+ *     be current); make that first call before starting any stream capture;
+ *   - all calls share the one array: two calls that may overlap on the GPU (different
+ *     streams, no dependency between them) race on it.  Calls on one stream are safe.
+ *     Nothing in the array needs clearing between calls.
+ * Arguments as bnb_spatial_block_fwd, without engine and scratch. */
+#define BNB_STATIC_MAX_ROWS 2048
+#define BNB_STATIC_SCRATCH_BYTES ((size_t)BNB_STATIC_MAX_ROWS * 4 * 128 * sizeof(float)) /* 4 MiB */
+int bnb_spatial_block_fwd_static(const BnbSpatialWeights* w, int d_model, int n_heads,
+                                 const float* x, const uint8_t* alive, float* y,
+                                 const BnbBatch* batch, int n_groups, int precision, void* stream);
 
 /* One temporal sublayer over T >= 1 timesteps for every token of the batch.
  * Replaces: GriffinTemporalBlock.forward_sequence (griffin.py:249-286) on the ship tokens,
