@@ -46,6 +46,8 @@ class Batch(C.Structure):
         ("total_ships", C.c_int32),
         ("tok_off", _fp),
         ("ship_off", _fp),
+        ("tile_env_begin", _fp),
+        ("n_tiles", C.c_int32),
     ]
 
 
@@ -54,6 +56,7 @@ EXPORTS = {
     "bnb_status_string": (C.c_char_p, [C.c_int]),
     "bnb_launch_count": (C.c_ulonglong, []),
     "bnb_supported": (C.c_int, [C.c_int] * 5),
+    "bnb_plan_tiles": (C.c_int, [_fp, C.c_int, _fp, C.c_int, C.POINTER(C.c_int)]),
     "bnb_scratch_bytes": (C.c_size_t, [C.c_int, C.POINTER(Batch), C.c_int]),
     "bnb_spatial_block_fwd": (
         C.c_int,
@@ -177,4 +180,15 @@ def scratch_for(device: torch.device, nbytes: int) -> torch.Tensor:
 
 
 def uniform_batch(n_envs: int, tokens: int, ships: int) -> Batch:
-    return Batch(n_envs, tokens, ships, tokens, n_envs * tokens, n_envs * ships, None, None)
+    return Batch(n_envs, tokens, ships, tokens, n_envs * tokens, n_envs * ships, None, None, None, 0)
+
+
+def tensor_engine_status(device: torch.device) -> int:
+    """Status word the tensor-core kernels left in the scratch buffer of the current stream
+    (0 = every bounded wait completed).  Synchronises; meant for tests and debugging."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream_handle(device))
+    buf = _scratch.get(key)
+    if buf is None:
+        return 0
+    torch.cuda.synchronize(device)
+    return int(buf[:4].view(torch.int32).item())

@@ -87,7 +87,14 @@ int carve(void* scratch, size_t bytes, size_t n_rows, int D, Scratch* out) {
 
 bool use_tensor(int precision, int engine, int D, int H, const BnbBatch* b) {
   if (precision != BNB_BF16 || engine == BNB_ENGINE_SIMT) return false;
-  return bnb::tensor::supported(D, H, b->max_tokens_per_env);
+  return bnb::tensor::supported_batch(D, H, *b);
+}
+
+// The tensor engine needs the packed weight image of every sublayer it runs.
+bool all_packed(const BnbSpatialWeights* s, int ns, const BnbTemporalWeights* t, int nt) {
+  for (int i = 0; i < ns; ++i) if (!s[i].packed) return false;
+  for (int i = 0; i < nt; ++i) if (!t[i].packed) return false;
+  return true;
 }
 
 }  // namespace
@@ -123,6 +130,13 @@ int bnb_supported(int d_model, int n_heads, int max_tokens_per_env, int precisio
   return 1;
 }
 
+int bnb_plan_tiles(const int32_t* tok_off_host, int n_envs, int32_t* tile_env_begin_host, int capacity,
+                   int* n_tiles) {
+  if (!tok_off_host || !tile_env_begin_host || !n_tiles) return BNB_ERR_NULL_POINTER;
+  if (n_envs < 0 || capacity < 1) return BNB_ERR_BAD_ARGUMENT;
+  return bnb::tensor::plan_tiles(tok_off_host, n_envs, tile_env_begin_host, capacity, n_tiles);
+}
+
 size_t bnb_scratch_bytes(int d_model, const BnbBatch* batch, int timesteps) {
   if (!batch || d_model <= 0 || timesteps <= 0) return 0;
   size_t n_rows = (size_t)timesteps * (size_t)batch->total_tokens;
@@ -145,7 +159,7 @@ int bnb_spatial_block_fwd(const BnbSpatialWeights* w, int d_model, int n_heads, 
   if (!x || !y) return BNB_ERR_NULL_POINTER;
   if (!aligned16(x) || !aligned16(y)) return BNB_ERR_MISALIGNED;
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
-  if (use_tensor(precision, engine, d_model, n_heads, batch))
+  if (use_tensor(precision, engine, d_model, n_heads, batch) && (w->packed || engine == BNB_ENGINE_TENSOR))
     return bnb::tensor::spatial_block(*w, d_model, n_heads, x, alive, y, *batch, n_groups, scratch, scratch_bytes, cs);
   if (engine == BNB_ENGINE_TENSOR) return BNB_ERR_UNSUPPORTED_DIMS;
   Scratch s;
@@ -169,7 +183,7 @@ int bnb_temporal_block_fwd(const BnbTemporalWeights* w, int d_model, const float
   if (batch->total_ships > 0 && (!hidden_in || !hidden_out)) return BNB_ERR_NULL_POINTER;
   if (!aligned16(x) || !aligned16(y) || !aligned16(hidden_in) || !aligned16(hidden_out)) return BNB_ERR_MISALIGNED;
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
-  if (precision == BNB_BF16 && engine != BNB_ENGINE_SIMT && bnb::tensor::supported(d_model, d_model / 32, 1))
+  if (use_tensor(precision, engine, d_model, 4, batch) && (w->packed || engine == BNB_ENGINE_TENSOR))
     return bnb::tensor::temporal_block(*w, d_model, x, y, hidden_in, hidden_out, done, nullptr, *batch, timesteps,
                                        scratch, scratch_bytes, cs);
   if (engine == BNB_ENGINE_TENSOR) return BNB_ERR_UNSUPPORTED_DIMS;
@@ -202,7 +216,8 @@ static int trunk_common(const BnbSpatialWeights* spatial, const BnbTemporalWeigh
   if (has_state && !is_sequence && !hidden_out) return BNB_ERR_NULL_POINTER;
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
 
-  if (use_tensor(precision, engine, D, H, batch))
+  if (use_tensor(precision, engine, D, H, batch) &&
+      (engine == BNB_ENGINE_TENSOR || all_packed(spatial, n_blocks * n_spatial, temporal, n_blocks * n_temporal)))
     return bnb::tensor::trunk(spatial, temporal, n_blocks, n_spatial, n_temporal, D, H, x, alive, y, hidden_in,
                               hidden_out, done, reset_env, *batch, T, scratch, scratch_bytes, cs);
   if (engine == BNB_ENGINE_TENSOR) return BNB_ERR_UNSUPPORTED_DIMS;

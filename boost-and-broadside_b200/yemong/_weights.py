@@ -48,3 +48,35 @@ def temporal_struct(tb, sub, dev: torch.device, packed: int | None = None) -> _c
         None if sub is None else _p(sub.weight, dev, "field_sub.weight"),
         packed,
     )
+
+
+def packed_image(owner, kind: str, key, params, make_struct, n_heads: int, dev: torch.device, precision: int, engine: int):
+    """Device address of the tensor-core weight image of one sublayer, or None.
+
+    The image is derived data: it is rebuilt whenever a parameter's storage or version
+    changes, lives in a cache on `owner` and is never part of a state_dict.
+    """
+    if precision != _capi.BNB_BF16 or engine == _capi.ENGINE_SIMT:
+        return None
+    D = params[0].shape[-1]
+    if not _capi.lib.bnb_supported(D, n_heads, 1, _capi.BNB_BF16, _capi.ENGINE_TENSOR):
+        return None
+    nbytes = _capi.lib.bnb_packed_spatial_bytes(D) if kind == "spatial" else _capi.lib.bnb_packed_temporal_bytes(D)
+    if nbytes == 0:
+        return None
+    cache = owner.__dict__.setdefault("_bnb_packed", {})
+    stamp = tuple((p.data_ptr(), p._version) for p in params)
+    ckey = (kind, key, dev.index)
+    hit = cache.get(ckey)
+    if hit is not None and hit[0] == stamp:
+        return hit[1].data_ptr()
+    buf = hit[1] if hit is not None else torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    stream = _capi.stream_handle(dev)
+    if kind == "spatial":
+        st = _capi.lib.bnb_pack_spatial(make_struct(), D, n_heads, buf.data_ptr(), stream)
+        _capi.check("bnb_pack_spatial", st)
+    else:
+        st = _capi.lib.bnb_pack_temporal(make_struct(), D, buf.data_ptr(), stream)
+        _capi.check("bnb_pack_temporal", st)
+    cache[ckey] = (stamp, buf)
+    return buf.data_ptr()

@@ -12,7 +12,7 @@ import torch
 import torch.nn as nn
 
 from .. import _capi
-from ._weights import spatial_struct
+from ._weights import packed_image, spatial_struct
 
 
 class GatedMLP(nn.Module):
@@ -86,7 +86,11 @@ class TransformerBlock(nn.Module):
             batch = _capi.uniform_batch(B, N, N)
             nbytes = _capi.lib.bnb_scratch_bytes(D, batch, 1)
             scratch = _capi.scratch_for(dev, nbytes)
-            w = spatial_struct(self, dev)
+            params = [self.qkv.weight, self.out_proj.weight, self.ffn.gate_proj.weight, self.ffn.up_proj.weight,
+                      self.ffn.down_proj.weight]
+            packed = packed_image(self, "spatial", 0, params, lambda: spatial_struct(self, dev), self.n_heads, dev,
+                                  precision, _capi.ENGINE_AUTO)
+            w = spatial_struct(self, dev, packed)
             st = _capi.lib.bnb_spatial_block_fwd(
                 w, D, self.n_heads, xin.data_ptr(), _capi.ptr(alive), y.data_ptr(), batch, 1, precision,
                 _capi.ENGINE_AUTO, scratch.data_ptr(), scratch.numel(), _capi.stream_handle(dev),

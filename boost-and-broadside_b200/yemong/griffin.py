@@ -12,7 +12,7 @@ import torch
 import torch.nn as nn
 
 from .. import _capi
-from ._weights import spatial_struct, temporal_struct
+from ._weights import packed_image, spatial_struct, temporal_struct
 from .attention import GatedMLP, TransformerBlock
 
 CONV_KERNEL: int = 4  # causal depthwise conv kernel size (griffin.py:22)
@@ -61,6 +61,13 @@ class GriffinTemporalBlock(nn.Module):
         self.norm2 = nn.RMSNorm(d_model)
         self.gated_mlp = GatedMLP(d_model)
 
+    def _packed_ptr(self, sub, dev: torch.device, precision: int):
+        params = [self.linear1.weight, self.linear2.weight, self.rg_lru.linear_a.weight, self.rg_lru.linear_x.weight,
+                  self.linear_out.weight, self.gated_mlp.gate_proj.weight, self.gated_mlp.up_proj.weight,
+                  self.gated_mlp.down_proj.weight] + ([] if sub is None else [sub.weight])
+        return packed_image(self, "temporal", "fields" if sub is not None else "ships", params,
+                            lambda: temporal_struct(self, sub, dev), 4, dev, precision, _capi.ENGINE_AUTO)
+
     def forward_sequence(
         self,
         x_seq: torch.Tensor,  # (B_seq, T, D)
@@ -86,10 +93,11 @@ class GriffinTemporalBlock(nn.Module):
             y = torch.empty_like(x_t)
             new_hidden = torch.empty_like(hidden)
             batch = _capi.uniform_batch(R, 1, 1)  # every row is its own one-ship environment
-            w = temporal_struct(self, None, dev)
+            w = temporal_struct(self, None, dev, self._packed_ptr(None, dev, precision))
+            scratch = _capi.scratch_for(dev, _capi.lib.bnb_scratch_bytes(D, batch, T))
             st = _capi.lib.bnb_temporal_block_fwd(
                 w, D, x_t.data_ptr(), y.data_ptr(), hidden.data_ptr(), new_hidden.data_ptr(), _capi.ptr(done),
-                batch, T, precision, _capi.ENGINE_AUTO, None, 0, _capi.stream_handle(dev),
+                batch, T, precision, _capi.ENGINE_AUTO, scratch.data_ptr(), scratch.numel(), _capi.stream_handle(dev),
             )
         _capi.check("bnb_temporal_block_fwd", st)
         return (
@@ -112,10 +120,11 @@ class GriffinTemporalBlock(nn.Module):
             R = flat.shape[0]
             y = torch.empty_like(flat)
             batch = _capi.uniform_batch(R, 1, 0)  # every row is a field token
-            w = temporal_struct(self, sub, dev)
+            w = temporal_struct(self, sub, dev, self._packed_ptr(sub, dev, precision))
+            scratch = _capi.scratch_for(dev, _capi.lib.bnb_scratch_bytes(D, batch, 1))
             st = _capi.lib.bnb_temporal_block_fwd(
                 w, D, flat.data_ptr(), y.data_ptr(), None, None, None, batch, 1, precision, _capi.ENGINE_AUTO,
-                None, 0, _capi.stream_handle(dev),
+                scratch.data_ptr(), scratch.numel(), _capi.stream_handle(dev),
             )
         _capi.check("bnb_temporal_block_fwd", st)
         return y.reshape(x.shape)
@@ -210,7 +219,6 @@ class YemongBlock(nn.Module):
         )
         for sub in self.field_sub:
             nn.init.eye_(sub.weight)
-        self._packed: dict = {}
 
     @property
     def n_temporal(self) -> int:
@@ -219,31 +227,18 @@ class YemongBlock(nn.Module):
 
     # -- tensor-core weight images: derived data, rebuilt when a parameter changes ----------
     def _packed_ptr(self, kind: str, j: int, dev: torch.device, precision: int, engine: int):
-        if precision != _capi.BNB_BF16 or engine == _capi.ENGINE_SIMT:
-            return None
-        D = self.d_model
-        nbytes = (
-            _capi.lib.bnb_packed_spatial_bytes(D) if kind == "spatial" else _capi.lib.bnb_packed_temporal_bytes(D)
-        )
-        if nbytes == 0:
-            return None
-        mod = self.spatial[j] if kind == "spatial" else self.temporal[j]
-        params = list(mod.parameters()) + ([self.field_sub[j].weight] if kind == "temporal" else [])
-        stamp = tuple((p.data_ptr(), p._version) for p in params)
-        key = (kind, j, dev.index)
-        hit = self._packed.get(key)
-        if hit is not None and hit[0] == stamp:
-            return hit[1].data_ptr()
-        buf = hit[1] if hit is not None else torch.empty(nbytes, dtype=torch.uint8, device=dev)
-        stream = _capi.stream_handle(dev)
         if kind == "spatial":
-            st = _capi.lib.bnb_pack_spatial(spatial_struct(mod, dev), D, self.n_heads, buf.data_ptr(), stream)
-            _capi.check("bnb_pack_spatial", st)
-        else:
-            st = _capi.lib.bnb_pack_temporal(temporal_struct(mod, self.field_sub[j], dev), D, buf.data_ptr(), stream)
-            _capi.check("bnb_pack_temporal", st)
-        self._packed[key] = (stamp, buf)
-        return buf.data_ptr()
+            mod = self.spatial[j]
+            params = [mod.qkv.weight, mod.out_proj.weight, mod.ffn.gate_proj.weight, mod.ffn.up_proj.weight,
+                      mod.ffn.down_proj.weight]
+            return packed_image(self, kind, j, params, lambda: spatial_struct(mod, dev), self.n_heads, dev,
+                                precision, engine)
+        mod = self.temporal[j]
+        sub = self.field_sub[j]
+        params = [mod.linear1.weight, mod.linear2.weight, mod.rg_lru.linear_a.weight, mod.rg_lru.linear_x.weight,
+                  mod.linear_out.weight, mod.gated_mlp.gate_proj.weight, mod.gated_mlp.up_proj.weight,
+                  mod.gated_mlp.down_proj.weight, sub.weight]
+        return packed_image(self, kind, j, params, lambda: temporal_struct(mod, sub, dev), 4, dev, precision, engine)
 
     @staticmethod
     def _pack_state(h: torch.Tensor, conv_buf: torch.Tensor) -> torch.Tensor:

@@ -69,11 +69,17 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None, mode: str) -> torch.Tensor:
-    """y = x W^T (+ b).  bf16 mode: bf16 operands, fp32 accumulate, bf16 result."""
-    y = _r(x, mode) @ _r(w, mode).t()
+    """y = x W^T (+ b).  bf16 mode: what autocast does to nn.Linear: input, weight and bias
+    cast to bf16, product accumulated in fp32, result rounded to bf16 (returned in float32)."""
+    if mode == "bf16":
+        y = torch.nn.functional.linear(
+            x.to(torch.bfloat16), w.to(torch.bfloat16), None if b is None else b.to(torch.bfloat16)
+        )
+        return y.to(torch.float32)
+    y = x @ w.t()
     if b is not None:
-        y = y + _r(b, mode)
-    return _r(y, mode)
+        y = y + b
+    return y
 
 
 def gelu_erf(x: torch.Tensor) -> torch.Tensor:

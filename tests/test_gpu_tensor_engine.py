@@ -1,0 +1,130 @@
+"""The tensor-core (tcgen05) engine against the CPU oracle and against the SIMT engine on
+the same inputs, called through the C ABI with the engine chosen explicitly."""
+
+import pytest
+import torch
+
+from oracle import trunk_oracle as O
+from tests.helpers import assert_close, build_trunk, golden, norm_err, trunk_params
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _engines():
+    from boost_and_broadside_b200 import _capi
+
+    return _capi, _capi.ENGINE_SIMT, _capi.ENGINE_TENSOR
+
+
+def _status_ok():
+    from boost_and_broadside_b200 import _capi
+
+    st = _capi.tensor_engine_status(torch.device("cuda", torch.cuda.current_device()))
+    assert st == 0, f"tensor engine status word {st}: a bounded wait ran out"
+
+
+@pytest.mark.parametrize("n_envs,ships,fields", [(10, 8, 4), (23, 8, 4), (16, 8, 0), (7, 30, 2), (3, 1, 0), (5, 2, 3), (2, 64, 0), (1, 128, 0)])
+def test_step_tensor_vs_oracle_and_simt(n_envs, ships, fields):
+    from boost_and_broadside_b200 import workloads as W
+
+    _capi, SIMT, TENSOR = _engines()
+    w = W.c2(n_envs=n_envs, seed=21, ships=ships, fields=fields)
+    trunk = build_trunk([128, 4, 2, 2, 1, 1])
+    ref_y, ref_h = O.trunk_step(w.x, w.alive, w.hidden, trunk_params(trunk), 4, "bf16")
+    trunk = trunk.to(DEV)
+    x, alive, hidden = w.x.to(DEV), w.alive.to(DEV), w.hidden.to(DEV)
+    with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
+        ys, hs = trunk.step(x, alive, hidden, engine=SIMT)
+        yt, ht = trunk.step(x, alive, hidden, engine=TENSOR)
+    _status_ok()
+    assert_close(yt, ref_y, "bf16", "tensor y vs oracle")
+    assert_close(ht, ref_h, "bf16", "tensor hidden vs oracle")
+    assert norm_err(yt.cpu(), ys.cpu()) < 1e-2
+    assert norm_err(ht.cpu(), hs.cpu()) < 1e-2
+
+
+def test_single_spatial_and_temporal_sublayers():
+    """One sublayer at a time through bnb_spatial_block_fwd / bnb_temporal_block_fwd."""
+    from boost_and_broadside_b200 import GriffinTemporalBlock, ModelConfig, TransformerBlock
+
+    gen = torch.Generator().manual_seed(3)
+    torch.manual_seed(0)
+    block = TransformerBlock(ModelConfig(128, 4, 2)).eval()
+    P = dict(block.state_dict())
+    x = torch.randn(21, 12, 128, generator=gen)
+    alive = torch.rand(21, 12, generator=gen) < 0.8
+    alive[3] = False
+    ref = O.spatial_block(x, alive, P, 4, "bf16")
+    block = block.to(DEV)
+    with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
+        y = block(x.to(DEV), alive.to(DEV))
+    _status_ok()
+    assert_close(y, ref, "bf16", "spatial sublayer")
+
+    torch.manual_seed(0)
+    tb = GriffinTemporalBlock(128).eval()
+    sub = torch.nn.Linear(128, 128, bias=False)
+    P = dict(tb.state_dict())
+    xs = torch.randn(150, 5, 128, generator=gen)
+    h0 = torch.randn(150, 128, generator=gen) * 0.5
+    cb = torch.randn(150, 3, 128, generator=gen) * 0.5
+    done = torch.rand(150, 5, generator=gen) < 0.3
+    ref_y, ref_h, ref_c = O.temporal_sequence(xs, h0, cb, done, P, "bf16")
+    ref_f = O.temporal_nonrecurrent(xs, P, sub.weight.detach(), "bf16")
+    tb, sub = tb.to(DEV), sub.to(DEV)
+    with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
+        y, h, c = tb.forward_sequence(xs.to(DEV), h0.to(DEV), cb.to(DEV), done.to(DEV))
+        _status_ok()
+        yf = tb.forward_nonrecurrent(xs.to(DEV), sub)
+        _status_ok()
+    assert_close(y, ref_y, "bf16", "temporal y")
+    assert_close(h, ref_h, "bf16", "temporal h")
+    assert_close(c, ref_c, "bf16", "temporal conv")
+    assert_close(yf, ref_f, "bf16", "field path")
+
+
+def test_sequence_tensor_vs_oracle():
+    from boost_and_broadside_b200 import workloads as W
+
+    _capi, SIMT, TENSOR = _engines()
+    w = W.c4(n_envs=37, timesteps=9, seed=31)
+    trunk = build_trunk([128, 4, 2, 2, 1, 1])
+    ref_y, ref_h = O.trunk_sequence(w.x, w.alive, w.hidden, w.done, trunk_params(trunk), 4, "bf16")
+    trunk = trunk.to(DEV)
+    with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
+        y, nh = trunk.sequence(w.x.to(DEV), w.alive.to(DEV), w.hidden.to(DEV), w.done.to(DEV), engine=TENSOR)
+    _status_ok()
+    assert_close(y, ref_y, "bf16", "sequence y")
+    assert_close(nh, ref_h, "bf16", "sequence hidden")
+
+
+def test_weights_are_repacked_after_an_update():
+    """The packed image is derived data: an in-place parameter update must be picked up."""
+    from boost_and_broadside_b200 import workloads as W
+
+    _capi, SIMT, TENSOR = _engines()
+    w = W.c2(n_envs=20, seed=41)
+    trunk = build_trunk([128, 4, 2, 2, 1, 1]).to(DEV)
+    x, alive, hidden = w.x.to(DEV), w.alive.to(DEV), w.hidden.to(DEV)
+    with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
+        y0, _ = trunk.step(x, alive, hidden, engine=TENSOR)
+        for p in trunk.parameters():
+            p.mul_(1.05)
+        y1, _ = trunk.step(x, alive, hidden, engine=TENSOR)
+        ys, _ = trunk.step(x, alive, hidden, engine=SIMT)
+    assert norm_err(y1.cpu(), y0.cpu()) > 1e-3
+    assert norm_err(y1.cpu(), ys.cpu()) < 1e-2
+
+
+def test_tensor_engine_refuses_what_it_is_not_built_for():
+    from boost_and_broadside_b200 import workloads as W
+
+    _capi, SIMT, TENSOR = _engines()
+    w = W.c3(n_envs=2)  # 152 tokens per environment: more than one tile
+    trunk = build_trunk([128, 4, 2, 2, 1, 1]).to(DEV)
+    with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
+        with pytest.raises(ValueError):
+            trunk.step(w.x.to(DEV), w.alive.to(DEV), w.hidden.to(DEV), engine=TENSOR)
+        y, _ = trunk.step(w.x.to(DEV), w.alive.to(DEV), w.hidden.to(DEV))  # AUTO falls back to SIMT
+    assert torch.isfinite(y).all()
