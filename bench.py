@@ -228,7 +228,7 @@ def run_ours(args) -> None:
     trunk = bnb.YemongTrunk(cfg).eval()
     n_params = sum(p.numel() for n, p in trunk.named_parameters() if "bullet" not in n)
     trunk = trunk.to(dev)
-    w = make_workload(args.workload, rank)
+    w = make_workload(args.workload, rank, args.envs_scale)
     engine = {"auto": _capi.ENGINE_AUTO, "simt": _capi.ENGINE_SIMT, "tensor": _capi.ENGINE_TENSOR}[args.engine]
 
     x_h = w.x.pin_memory()
@@ -320,7 +320,7 @@ def run_ours(args) -> None:
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD_TEXT[args.workload], "id": args.workload, "engine": args.engine,
-                       "tokens_per_step_per_gpu": tokens, "l2": "inputs larger than L2 (no flush)",
+                       "tokens_per_step_per_gpu": tokens, "envs_scale": args.envs_scale, "l2": "inputs larger than L2 (no flush)",
                        "weights": "random init, seed 0, rl-fields dims (D=128, 4 heads, S S T | S S T)"},
             "e2e": {"value": tokens_all * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": x_h.numel() * 4 + alive_h.numel(), "d2h_bytes_per_step": y_h.numel() * 4,
@@ -352,6 +352,8 @@ def main() -> None:
     ap.add_argument("--workload", default="C2", choices=sorted(WORKLOAD_TEXT))
     ap.add_argument("--engine", default="auto", choices=["auto", "simt", "tensor"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--envs-scale", type=float, default=1.0,
+                    help="fraction of the workload's environments (small cases for profiler captures only)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
