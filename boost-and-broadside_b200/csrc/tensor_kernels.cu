@@ -16,8 +16,8 @@
 //                           operand 128x64 bf16, 2-slot ring of 16 KB weight chunks, q|k|v
 //                           staging for the attention warps.
 //
-// 160 threads: warps 0-3 own one tile row per thread (TMEM lane = row) and do every epilogue,
-// thread 0 also issues the MMAs; warp 4 streams weight chunks.  Two CTAs fit one SM (256 TMEM
+// 256 threads, two per tile row (TMEM lane = row, half of the columns each), do every epilogue;
+// thread 0 also issues the MMAs and the bulk copies of the weight stream.  Two CTAs fit one SM (256 TMEM
 // columns, about 108 KB of shared memory each) so one CTA's epilogue overlaps the other's MMAs.
 //
 // Every wait on an mbarrier is bounded; a wait that runs out records a code in the status
@@ -41,8 +41,8 @@ constexpr int TILE = 128;
 constexpr int CHUNK_BYTES = 16384;       // one weight chunk: up to 128 rows x 64 bf16
 constexpr int N_SPATIAL_CHUNKS = 34;
 constexpr int N_TEMPORAL_CHUNKS = 36;
-constexpr int EPI_THREADS = 128;
-constexpr int NTHREADS = 160;
+constexpr int EPI_THREADS = 256;
+constexpr int NTHREADS = 256;
 constexpr int STAGE_STRIDE = 208;        // bytes per staged q|k|v row (96 bf16 + pad)
 constexpr int MAX_SUBLAYERS = 8;
 
@@ -53,7 +53,8 @@ constexpr int OFF_RING = 49152;          // 2 x 16 KB
 constexpr int OFF_STAGE = 81920;         // 128 x 208 = 26624
 constexpr int OFF_META = 108544;         // env_first[128], env_n[128], alive[128], items[128]
 constexpr int OFF_BAR = 109056;          // full[2], empty[2], acc, tmem base
-constexpr int SMEM_BYTES = 109056 + 64 + 1024;
+constexpr int OFF_SS = 109120;           // partial sums of squares, 2 x 128 floats
+constexpr int SMEM_BYTES = 109120 + 1024 + 1024;
 
 constexpr uint32_t TMEM_COLS = 256;
 constexpr uint32_t COL_RESID = 0;
@@ -129,7 +130,7 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
@@ -167,6 +168,13 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&v)[3
         "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
         "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
         "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
       : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
@@ -223,11 +231,10 @@ __device__ __forceinline__ float sqrt_fast(float v) {
 // erf GeLU as 0.5 x (1 + tanh(x (c1 + c3 x^2 + c5 x^4))): the inner polynomial is a minimax
 // fit to x * Phi(x) (max abs error 2.5e-5, max relative error 1.2e-3 where |gelu| > 1e-2).
 __device__ __forceinline__ float gelu_fast(float v) {
-  const float xc = fminf(fmaxf(v, -10.0f), 10.0f);
-  const float x2 = xc * xc;
+  const float x2 = fminf(v * v, 100.0f);  // beyond |x| = 10 the polynomial stays positive and tanh saturates
   float p = fmaf(x2, -3.51516841e-4f, 3.70056464e-2f);
   p = fmaf(x2, p, 7.97507884e-1f);
-  const float t = tanh_fast(xc * p);
+  const float t = tanh_fast(v * p);
   const float h = 0.5f * v;
   return fmaf(h, t, h);
 }
@@ -302,11 +309,15 @@ __global__ void k_pack_temporal(BnbTemporalWeights w, uint8_t* out) {
 }
 
 // ------------------------------------------------------------------ the tile kernel
+//
+// Thread layout: 256 epilogue threads, two per tile row.  Thread (row, half) owns TMEM lane
+// `row` (warps w and w+4 both reach lanes 32*(w%4)..) and half of the columns of whatever is
+// being read: K atom `half` of a 128-wide operand, 32 of the 64 columns of a gate|up chunk, ...
 
 struct Ctx {
   uint8_t* smem;
   uint32_t sA, sP, sRing, sStage;   // shared addresses
-  uint32_t bar_full[2], bar_empty[2], bar_acc;
+  uint32_t bar_full[2], bar_acc;
   uint32_t tmem;                    // base tensor-memory address
   uint32_t lane_addr;               // tmem + (row's lane << 16)
   int* status;
@@ -314,18 +325,47 @@ struct Ctx {
   uint32_t acc_phase;
   uint32_t cons_count;              // chunks consumed so far (thread 0)
   int row;                          // tile row owned by this thread
+  int half;                         // which half of the columns
+  float* ss_part;                   // [2][128] partial sums of squares
+  // weight stream cursor (thread 0 only): next chunk to fetch
+  const TrunkArgs* args;
+  uint32_t prod_count;
+  int p_tile, p_t, p_si, p_ch;
 };
 
-// Epilogue threads have written an operand to shared memory / finished reading tensor
-// memory; after this thread 0 may issue MMAs.
+// Thread 0: fetch weight chunks of the stream into every free ring slot.  Called when all
+// earlier MMAs are known to be complete (start of the kernel, end of a round), so a slot
+// whose chunk has been consumed is free to overwrite.
+__device__ __forceinline__ void refill(Ctx& c) {
+  const TrunkArgs& a = *c.args;
+  while (c.prod_count - c.cons_count < 2u && c.p_tile < a.n_tiles) {
+    const SubLayer& s = a.sub[c.p_si];
+    const int n_chunks = s.type == SUB_SPATIAL ? N_SPATIAL_CHUNKS : N_TEMPORAL_CHUNKS;
+    if (s.type == SUB_TEMPORAL && !a.has_fields && c.p_ch == 8) c.p_ch = 10;  // no field_sub round
+    const uint32_t slot = c.prod_count & 1u;
+    mbar_expect_tx(c.bar_full[slot], CHUNK_BYTES);
+    bulk_g2s(c.sRing + slot * CHUNK_BYTES, s.packed + (size_t)c.p_ch * CHUNK_BYTES, CHUNK_BYTES, c.bar_full[slot]);
+    ++c.prod_count;
+    if (++c.p_ch == n_chunks) {
+      c.p_ch = 0;
+      if (++c.p_si == a.n_sub) {
+        c.p_si = 0;
+        if (++c.p_t == a.t_loop) {
+          c.p_t = 0;
+          c.p_tile += gridDim.x;
+        }
+      }
+    }
+  }
+}
+
 __device__ __forceinline__ void round_begin(Ctx& c) {
   fence_proxy_async();
   tc_fence_before();
   epi_barrier();
   if (threadIdx.x == 0) tc_fence_after();
 }
-// Thread 0: take the next weight chunk of the stream and multiply it by the operand at
-// a_addr (one 64-wide K atom): D[128 x n] (+)= A[128 x 64] * W[n x 64]^T.
+// Thread 0: D[128 x n] (+)= A[128 x 64] * W[n x 64]^T with the next weight chunk of the stream.
 __device__ __forceinline__ void issue_chunk(Ctx& c, uint32_t a_addr, uint32_t n, uint32_t d_col, uint32_t accumulate) {
   const uint32_t slot = c.cons_count & 1u;
   mbar_wait(c.bar_full[slot], (c.cons_count >> 1) & 1u, c.status, c.aborted, ST_TIMEOUT_FULL);
@@ -335,44 +375,47 @@ __device__ __forceinline__ void issue_chunk(Ctx& c, uint32_t a_addr, uint32_t n,
 #pragma unroll
   for (int k = 0; k < 4; ++k)
     tc_mma(c.tmem + d_col, smem_desc(a_addr + k * 32), smem_desc(b_addr + k * 32), idesc, (accumulate | (uint32_t)k) ? 1u : 0u);
-  tc_commit(c.bar_empty[slot]);
   ++c.cons_count;
 }
-// Thread 0 signals the end of the round; everybody waits for the accumulator.
 __device__ __forceinline__ void round_end(Ctx& c) {
   if (threadIdx.x == 0) tc_commit(c.bar_acc);
   mbar_wait(c.bar_acc, c.acc_phase, c.status, c.aborted, ST_TIMEOUT_ACC);
   c.acc_phase ^= 1u;
+  if (threadIdx.x == 0) refill(c);
   __syncwarp();  // the spin above may leave the warp diverged; tcgen05.ld/st need it converged
   tc_fence_after();
 }
 
-// residual (TMEM) -> RMSNorm -> bf16 A operand (both K atoms)
+// residual (TMEM) -> RMSNorm -> bf16 A operand; each thread norms its 64 columns = K atom `half`
 __device__ __forceinline__ void norm_to_A(Ctx& c, const float* __restrict__ g) {
-  uint32_t v[32];
+  uint32_t v[32], w[32];
+  tmem_ld32_nowait(c.lane_addr + COL_RESID + c.half * 64, v);
+  tmem_ld32_nowait(c.lane_addr + COL_RESID + c.half * 64 + 32, w);
+  tmem_wait_ld();
   float ss = 0.f;
 #pragma unroll
-  for (int ch = 0; ch < 4; ++ch) {
-    tmem_ld32(c.lane_addr + COL_RESID + ch * 32, v);
-#pragma unroll
-    for (int i = 0; i < 32; ++i) { float f = __uint_as_float(v[i]); ss = fmaf(f, f, ss); }
+  for (int i = 0; i < 32; ++i) {
+    float a = __uint_as_float(v[i]), b = __uint_as_float(w[i]);
+    ss = fmaf(a, a, ss);
+    ss = fmaf(b, b, ss);
   }
+  c.ss_part[c.half * TILE + c.row] = ss;
+  epi_barrier();
+  ss += c.ss_part[(c.half ^ 1) * TILE + c.row];
   const float inv = rsqrtf(ss * (1.0f / D) + kRmsEps);
+  uint8_t* dst = c.smem + OFF_A + c.half * CHUNK_BYTES;
+  const float* gg = g + c.half * 64;
 #pragma unroll
-  for (int ch = 0; ch < 4; ++ch) {
-    tmem_ld32(c.lane_addr + COL_RESID + ch * 32, v);
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const int col = ch * 32 + q * 8;
-      float4 g0 = __ldg(reinterpret_cast<const float4*>(g + col));
-      float4 g1 = __ldg(reinterpret_cast<const float4*>(g + col + 4));
-      uint4 o;
-      o.x = pack_bf16(__uint_as_float(v[q * 8 + 0]) * inv * g0.x, __uint_as_float(v[q * 8 + 1]) * inv * g0.y);
-      o.y = pack_bf16(__uint_as_float(v[q * 8 + 2]) * inv * g0.z, __uint_as_float(v[q * 8 + 3]) * inv * g0.w);
-      o.z = pack_bf16(__uint_as_float(v[q * 8 + 4]) * inv * g1.x, __uint_as_float(v[q * 8 + 5]) * inv * g1.y);
-      o.w = pack_bf16(__uint_as_float(v[q * 8 + 6]) * inv * g1.z, __uint_as_float(v[q * 8 + 7]) * inv * g1.w);
-      *reinterpret_cast<uint4*>(c.smem + OFF_A + (col >> 6) * CHUNK_BYTES + swz(c.row, (col & 63) >> 3)) = o;
-    }
+  for (int q = 0; q < 8; ++q) {
+    const uint32_t* src = q < 4 ? &v[q * 8] : &w[(q - 4) * 8];
+    float4 g0 = __ldg(reinterpret_cast<const float4*>(gg + q * 8));
+    float4 g1 = __ldg(reinterpret_cast<const float4*>(gg + q * 8 + 4));
+    uint4 o;
+    o.x = pack_bf16(__uint_as_float(src[0]) * inv * g0.x, __uint_as_float(src[1]) * inv * g0.y);
+    o.y = pack_bf16(__uint_as_float(src[2]) * inv * g0.z, __uint_as_float(src[3]) * inv * g0.w);
+    o.z = pack_bf16(__uint_as_float(src[4]) * inv * g1.x, __uint_as_float(src[5]) * inv * g1.y);
+    o.w = pack_bf16(__uint_as_float(src[6]) * inv * g1.z, __uint_as_float(src[7]) * inv * g1.w);
+    *reinterpret_cast<uint4*>(dst + swz(c.row, q)) = o;
   }
 }
 
@@ -385,24 +428,19 @@ __device__ __forceinline__ void ffn(Ctx& c) {
       issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1);
     }
     round_end(c);
-    // gate = acc[0,64), up = acc[64,128) -> bf16(bf16(gelu(bf16 gate)) * bf16 up) -> second operand
+    // gate = acc[0,64), up = acc[64,128); this thread: hidden columns [32 half, 32 half + 32)
+    uint32_t gv[32], uv[32];
+    tmem_ld32_nowait(c.lane_addr + COL_ACC + c.half * 32, gv);
+    tmem_ld32_nowait(c.lane_addr + COL_ACC + 64 + c.half * 32, uv);
+    tmem_wait_ld();
 #pragma unroll
-    for (int ch = 0; ch < 2; ++ch) {
-      uint32_t gv[32], uv[32];
-      tmem_ld32_nowait(c.lane_addr + COL_ACC + ch * 32, gv);
-      tmem_ld32_nowait(c.lane_addr + COL_ACC + 64 + ch * 32, uv);
-      tmem_wait_ld();
+    for (int q = 0; q < 4; ++q) {
+      uint32_t o[4];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint32_t o[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float g0 = round_bf16(__uint_as_float(gv[q * 8 + 2 * j])), g1 = round_bf16(__uint_as_float(gv[q * 8 + 2 * j + 1]));
-          float u0 = round_bf16(__uint_as_float(uv[q * 8 + 2 * j])), u1 = round_bf16(__uint_as_float(uv[q * 8 + 2 * j + 1]));
-          o[j] = pack_bf16(round_bf16(gelu_fast(g0)) * u0, round_bf16(gelu_fast(g1)) * u1);
-        }
-        *reinterpret_cast<uint4*>(c.smem + OFF_P + swz(c.row, ch * 4 + q)) = make_uint4(o[0], o[1], o[2], o[3]);
-      }
+      for (int j = 0; j < 4; ++j)
+        o[j] = pack_bf16(gelu_fast(__uint_as_float(gv[q * 8 + 2 * j])) * __uint_as_float(uv[q * 8 + 2 * j]),
+                         gelu_fast(__uint_as_float(gv[q * 8 + 2 * j + 1])) * __uint_as_float(uv[q * 8 + 2 * j + 1]));
+      *reinterpret_cast<uint4*>(c.smem + OFF_P + swz(c.row, c.half * 4 + q)) = make_uint4(o[0], o[1], o[2], o[3]);
     }
     round_begin(c);
     if (threadIdx.x == 0) issue_chunk(c, c.sP, 128, COL_RESID, 1);
@@ -412,17 +450,18 @@ __device__ __forceinline__ void ffn(Ctx& c) {
 
 // Attention of one head for every environment of the tile, from the staged q|k|v rows
 // (row-major, q at bf16 column 0, k at 32, v at 64) into columns [32*hh, 32*hh+32) of the
-// second operand.  One warp per block of 16 query rows of one environment.
+// second operand.  One warp per block of 16 query rows of one environment; MAXKB blocks of
+// 16 keys at most.
+template <int MAXKB>
 __device__ __forceinline__ void attention_head(Ctx& c, int hh, int n_items) {
   const uint8_t* meta = c.smem + OFF_META;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const float scale = 0.17677669529663687f;  // 1/sqrt(32)
-  for (int it = warp; it < n_items; it += 4) {
+  for (int it = warp; it < n_items; it += 8) {
     const int r0 = meta[384 + it];
     const int e0 = meta[r0], n = meta[128 + r0] + 1;   // first tile row and size of the environment
     const int last = e0 + n - 1;
-    // query fragments (two k-steps over the 32 head dims)
     uint32_t qa[2][4];
     {
       int row = min(r0 + (lane & 7) + ((lane >> 3) & 1) * 8, last);
@@ -431,9 +470,9 @@ __device__ __forceinline__ void attention_head(Ctx& c, int hh, int n_items) {
         ldsm_x4(c.sStage + row * STAGE_STRIDE + (ks * 16 + (lane >> 4) * 8) * 2, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3]);
     }
     const int nkb = (n + 15) >> 4;
-    float s[8][2][4];
+    float s[MAXKB][2][4];
 #pragma unroll
-    for (int kb = 0; kb < 8; ++kb) {
+    for (int kb = 0; kb < MAXKB; ++kb) {
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
@@ -449,10 +488,9 @@ __device__ __forceinline__ void attention_head(Ctx& c, int hh, int n_items) {
         }
       }
     }
-    // masked softmax over the n keys; rows g and g+8 of the block
     float m0 = -INFINITY, m1 = -INFINITY;
 #pragma unroll
-    for (int kb = 0; kb < 8; ++kb)
+    for (int kb = 0; kb < MAXKB; ++kb)
       if (kb < nkb) {
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
@@ -475,7 +513,7 @@ __device__ __forceinline__ void attention_head(Ctx& c, int hh, int n_items) {
     m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 2));
     float l0 = 0.f, l1 = 0.f;
 #pragma unroll
-    for (int kb = 0; kb < 8; ++kb)
+    for (int kb = 0; kb < MAXKB; ++kb)
       if (kb < nkb) {
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
@@ -492,14 +530,13 @@ __device__ __forceinline__ void attention_head(Ctx& c, int hh, int n_items) {
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    // o = p v
     float o[4][4];
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
       for (int i = 0; i < 4; ++i) o[nt][i] = 0.f;
 #pragma unroll
-    for (int kb = 0; kb < 8; ++kb)
+    for (int kb = 0; kb < MAXKB; ++kb)
       if (kb < nkb) {
         uint32_t a0 = pack_bf16(s[kb][0][0], s[kb][0][1]), a1 = pack_bf16(s[kb][0][2], s[kb][0][3]);
         uint32_t a2 = pack_bf16(s[kb][1][0], s[kb][1][1]), a3 = pack_bf16(s[kb][1][2], s[kb][1][3]);
@@ -525,6 +562,7 @@ __device__ __forceinline__ void attention_head(Ctx& c, int hh, int n_items) {
   }
 }
 
+template <int MAXKB>
 __device__ __forceinline__ void run_spatial(Ctx& c, const SubLayer& s, int n_items, bool row_valid) {
   norm_to_A(c, s.g1);
   for (int p = 0; p < 2; ++p) {
@@ -535,30 +573,29 @@ __device__ __forceinline__ void run_spatial(Ctx& c, const SubLayer& s, int n_ite
         issue_chunk(c, c.sA + CHUNK_BYTES, 96, COL_ACC, 1);
       }
       round_end(c);
-      // q|k|v of this head -> bf16 staging rows
+      // q|k|v of this head -> bf16 staging rows; this thread: accumulator columns [48 half, 48 half + 48)
+      {
+        uint32_t v[32], w[16];
+        tmem_ld32_nowait(c.lane_addr + COL_ACC + c.half * 48, v);
+        tmem_ld16_nowait(c.lane_addr + COL_ACC + c.half * 48 + 32, w);
+        tmem_wait_ld();
+        uint8_t* dst = c.smem + OFF_STAGE + c.row * STAGE_STRIDE + c.half * 96;
 #pragma unroll
-      for (int ch = 0; ch < 3; ++ch) {
-        uint32_t v[32];
-        tmem_ld32(c.lane_addr + COL_ACC + ch * 32, v);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint4 o = make_uint4(pack_bf16(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1])),
-                               pack_bf16(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3])),
-                               pack_bf16(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5])),
-                               pack_bf16(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7])));
-          *reinterpret_cast<uint4*>(c.smem + OFF_STAGE + c.row * STAGE_STRIDE + ch * 64 + q * 16) = o;
+        for (int q = 0; q < 6; ++q) {
+          const uint32_t* src = q < 4 ? &v[q * 8] : &w[(q - 4) * 8];
+          *reinterpret_cast<uint4*>(dst + q * 16) =
+              make_uint4(pack_bf16(__uint_as_float(src[0]), __uint_as_float(src[1])), pack_bf16(__uint_as_float(src[2]), __uint_as_float(src[3])),
+                         pack_bf16(__uint_as_float(src[4]), __uint_as_float(src[5])), pack_bf16(__uint_as_float(src[6]), __uint_as_float(src[7])));
         }
       }
-      if (!row_valid) {
+      if (!row_valid && hh == 0) {
         // rows outside every environment contribute a zero operand row
-        if (hh == 0) {
 #pragma unroll
-          for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(c.smem + OFF_P + swz(c.row, q)) = make_uint4(0u, 0u, 0u, 0u);
-        }
+        for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(c.smem + OFF_P + swz(c.row, c.half * 4 + q)) = make_uint4(0u, 0u, 0u, 0u);
       }
       tc_fence_before();
       epi_barrier();
-      attention_head(c, hh, n_items);
+      attention_head<MAXKB>(c, hh, n_items);
       epi_barrier();  // staging rows are free again
     }
     round_begin(c);
@@ -575,13 +612,15 @@ struct RowState {
   bool zero_in;    // incoming state taken as zero (reset_env)
 };
 
-// One temporal sublayer on the tile at one timestep.
+// One temporal sublayer on the tile at one timestep.  Thread (row, half) works on hidden
+// columns [32 half, 32 half + 32) and [64 + 32 half, 64 + 32 half + 32): the columns whose
+// gates it sees in the two gate rounds.
 __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const RowState& rs, bool is_field, bool boundary,
                                              bool has_fields, const float* hid_in) {
   const bool is_ship = rs.hrow >= 0;
   norm_to_A(c, s.g1);
-  // b2 = bf16(gelu(bf16(linear2 n))), parked in registers as packed bf16 pairs
-  uint32_t b2p[64];
+  // b2 = bf16(gelu(linear2 n)) for this thread's columns, parked as packed bf16 pairs
+  uint32_t b2p[2][16];
   round_begin(c);
   if (threadIdx.x == 0) {
     issue_chunk(c, c.sA, 128, COL_ACC, 0);
@@ -589,14 +628,15 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
   }
   round_end(c);
 #pragma unroll
-  for (int ch = 0; ch < 4; ++ch) {
+  for (int rnd = 0; rnd < 2; ++rnd) {
     uint32_t v[32];
-    tmem_ld32(c.lane_addr + COL_ACC + ch * 32, v);
+    tmem_ld32(c.lane_addr + COL_ACC + rnd * 64 + c.half * 32, v);
 #pragma unroll
     for (int j = 0; j < 16; ++j)
-      b2p[ch * 16 + j] = pack_bf16(gelu_fast(round_bf16(__uint_as_float(v[2 * j]))), gelu_fast(round_bf16(__uint_as_float(v[2 * j + 1]))));
+      b2p[rnd][j] = pack_bf16(gelu_fast(__uint_as_float(v[2 * j])), gelu_fast(__uint_as_float(v[2 * j + 1])));
   }
-  // b1 = bf16(linear1 n); ships: causal conv with the stored taps -> u; fields: keep b1
+  // b1 = bf16(linear1 n); ships: causal conv with the stored taps -> u; fields: keep b1.
+  // This thread: columns [64 half, 64 half + 64) = K atom `half` of the operand.
   round_begin(c);
   if (threadIdx.x == 0) {
     issue_chunk(c, c.sA, 128, COL_ACC, 0);
@@ -606,12 +646,12 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
   const float* hin = is_ship ? hid_in + (size_t)rs.hrow * 4 * D : nullptr;
   float* hout = is_ship ? s.hid_out + (size_t)rs.hrow * 4 * D : nullptr;
 #pragma unroll
-  for (int ch = 0; ch < 4; ++ch) {
+  for (int ch = 0; ch < 2; ++ch) {
     uint32_t v[32];
-    tmem_ld32(c.lane_addr + COL_ACC + ch * 32, v);
+    tmem_ld32(c.lane_addr + COL_ACC + c.half * 64 + ch * 32, v);
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      const int col = ch * 32 + q * 8;
+      const int col = c.half * 64 + ch * 32 + q * 8;
       float u[8];
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
@@ -626,11 +666,9 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
             t1 = *reinterpret_cast<const float4*>(hin + 2 * D + cc);
             t2 = *reinterpret_cast<const float4*>(hin + 3 * D + cc);
           }
-          if (hout) {
-            *reinterpret_cast<float4*>(hout + D + cc) = t1;
-            *reinterpret_cast<float4*>(hout + 2 * D + cc) = t2;
-            *reinterpret_cast<float4*>(hout + 3 * D + cc) = make_float4(b1[0], b1[1], b1[2], b1[3]);
-          }
+          *reinterpret_cast<float4*>(hout + D + cc) = t1;
+          *reinterpret_cast<float4*>(hout + 2 * D + cc) = t2;
+          *reinterpret_cast<float4*>(hout + 3 * D + cc) = make_float4(b1[0], b1[1], b1[2], b1[3]);
           const float a0[4] = {t0.x, t0.y, t0.z, t0.w}, a1[4] = {t1.x, t1.y, t1.z, t1.w}, a2[4] = {t2.x, t2.y, t2.z, t2.w};
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -647,63 +685,63 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
         }
       }
       uint4 o = make_uint4(pack_bf16(u[0], u[1]), pack_bf16(u[2], u[3]), pack_bf16(u[4], u[5]), pack_bf16(u[6], u[7]));
-      *reinterpret_cast<uint4*>(c.smem + OFF_A + (col >> 6) * CHUNK_BYTES + swz(c.row, (col & 63) >> 3)) = o;
+      *reinterpret_cast<uint4*>(c.smem + OFF_A + c.half * CHUNK_BYTES + swz(c.row, ch * 4 + q)) = o;
     }
   }
-  // gates and state update, 64 columns per round: acc[0,64) = W_a u, acc[64,128) = W_x u
+  // gates and state update, 64 hidden columns per round: acc[0,64) = W_a u, acc[64,128) = W_x u
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
+  for (int rnd = 0; rnd < 2; ++rnd) {
     round_begin(c);
     if (threadIdx.x == 0) {
       issue_chunk(c, c.sA, 128, COL_ACC, 0);
       issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1);
     }
     round_end(c);
-    {
+    uint32_t rv[32], iv[32];
+    tmem_ld32_nowait(c.lane_addr + COL_ACC + c.half * 32, rv);       // executed by every lane of the warp
+    tmem_ld32_nowait(c.lane_addr + COL_ACC + 64 + c.half * 32, iv);
+    tmem_wait_ld();
+    if (is_ship) {
 #pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
-        uint32_t rv[32], iv[32];
-        tmem_ld32_nowait(c.lane_addr + COL_ACC + ch * 32, rv);       // executed by every lane of the warp
-        tmem_ld32_nowait(c.lane_addr + COL_ACC + 64 + ch * 32, iv);
-        tmem_wait_ld();
-        if (is_ship) {
+      for (int q = 0; q < 4; ++q) {
+        const int col = rnd * 64 + c.half * 32 + q * 8;
+        // u (bf16) back from the A operand (K atom rnd)
+        uint8_t* ua = c.smem + OFF_A + rnd * CHUNK_BYTES + swz(c.row, c.half * 4 + q);
+        const uint4 ub = *reinterpret_cast<const uint4*>(ua);
+        const uint32_t uw[4] = {ub.x, ub.y, ub.z, ub.w};
+        uint32_t ob[4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int col = half * 64 + ch * 32 + q * 8;
-          // u (bf16) back from the A operand this thread wrote
-          uint8_t* ua = c.smem + OFF_A + half * CHUNK_BYTES + swz(c.row, (col & 63) >> 3);
-          const uint4 ub = *reinterpret_cast<const uint4*>(ua);
-          const uint32_t uw[4] = {ub.x, ub.y, ub.z, ub.w};
-          uint32_t ob[4];
+        for (int hf = 0; hf < 2; ++hf) {
+          const int cc = col + hf * 4;
+          float4 hv = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (!rs.zero_in) hv = *reinterpret_cast<const float4*>(hin + cc);
+          const float4 ab = __ldg(reinterpret_cast<const float4*>(s.a_b + cc));
+          const float4 xb = __ldg(reinterpret_cast<const float4*>(s.x_b + cc));
+          const float4 dl = __ldg(reinterpret_cast<const float4*>(s.decay_log2 + cc));
+          const float abv[4] = {ab.x, ab.y, ab.z, ab.w}, xbv[4] = {xb.x, xb.y, xb.z, xb.w}, dlv[4] = {dl.x, dl.y, dl.z, dl.w};
+          float hn[4] = {hv.x, hv.y, hv.z, hv.w};
 #pragma unroll
-          for (int hf = 0; hf < 2; ++hf) {
-            const int cc = col + hf * 4;
-            float4 hv = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (!rs.zero_in) hv = *reinterpret_cast<const float4*>(hin + cc);
-            float hn[4] = {hv.x, hv.y, hv.z, hv.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int k = q * 8 + hf * 4 + i;
-              float rg = round_bf16(sigmoid_fast(round_bf16(__uint_as_float(rv[k]) + round_bf16(__ldg(s.a_b + cc + i)))));
-              float ig = round_bf16(sigmoid_fast(round_bf16(__uint_as_float(iv[k]) + round_bf16(__ldg(s.x_b + cc + i)))));
-              // sigmoid(Lambda)^(8 r) = 2^(r * 8 log2 sigmoid(Lambda)); the table is part of the weight image
-              float a = ex2_fast(rg * __ldg(s.decay_log2 + cc + i));
-              float gate = sqrt_fast(fmaxf((1.0f - a) * (1.0f + a), kGateFloor));
-              uint32_t uword = uw[hf * 2 + (i >> 1)];
-              float uu = (i & 1) ? bf16_hi(uword) : bf16_lo(uword);
-              float bb = gate * (ig * uu);
-              if (boundary) a = 0.f;
-              hn[i] = a * hn[i] + bb;
-            }
-            if (hout) *reinterpret_cast<float4*>(hout + cc) = make_float4(hn[0], hn[1], hn[2], hn[3]);
-            const int bi = (cc >> 1);
-            ob[hf * 2] = pack_bf16(hn[0] * bf16_lo(b2p[bi]), hn[1] * bf16_hi(b2p[bi]));
-            ob[hf * 2 + 1] = pack_bf16(hn[2] * bf16_lo(b2p[bi + 1]), hn[3] * bf16_hi(b2p[bi + 1]));
+          for (int i = 0; i < 4; ++i) {
+            const int k = q * 8 + hf * 4 + i;
+            float rg = round_bf16(sigmoid_fast(__uint_as_float(rv[k]) + abv[i]));
+            float ig = round_bf16(sigmoid_fast(__uint_as_float(iv[k]) + xbv[i]));
+            // sigmoid(Lambda)^(8 r) = 2^(r * 8 log2 sigmoid(Lambda)); the table is part of the weight image
+            float a = ex2_fast(rg * dlv[i]);
+            float gate = sqrt_fast(fmaxf((1.0f - a) * (1.0f + a), kGateFloor));
+            uint32_t uword = uw[hf * 2 + (i >> 1)];
+            float uu = (i & 1) ? bf16_hi(uword) : bf16_lo(uword);
+            float bb = gate * (ig * uu);
+            if (boundary) a = 0.f;
+            hn[i] = fmaf(a, hn[i], bb);
           }
-          uint8_t* dst = half == 0 ? c.smem + OFF_P + swz(c.row, (col & 63) >> 3) : ua;
-          *reinterpret_cast<uint4*>(dst) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+          *reinterpret_cast<float4*>(hout + cc) = make_float4(hn[0], hn[1], hn[2], hn[3]);
+          const int bi = q * 4 + hf * 2;
+          ob[hf * 2] = pack_bf16(hn[0] * bf16_lo(b2p[rnd][bi]), hn[1] * bf16_hi(b2p[rnd][bi]));
+          ob[hf * 2 + 1] = pack_bf16(hn[2] * bf16_lo(b2p[rnd][bi + 1]), hn[3] * bf16_hi(b2p[rnd][bi + 1]));
         }
-        }
+        // branch operand for linear_out: K atom 0 lives in the second operand, K atom 1 in place
+        uint8_t* dst = rnd == 0 ? c.smem + OFF_P + swz(c.row, c.half * 4 + q) : ua;
+        *reinterpret_cast<uint4*>(dst) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
       }
     }
   }
@@ -715,35 +753,33 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
       issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1);
     }
     round_end(c);
-    {
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t v[32];
-        tmem_ld32(c.lane_addr + COL_ACC + ch * 32, v);        // executed by every lane of the warp
-        if (!is_ship) {
+    for (int rnd = 0; rnd < 2; ++rnd) {
+      uint32_t v[32];
+      tmem_ld32(c.lane_addr + COL_ACC + rnd * 64 + c.half * 32, v);        // executed by every lane of the warp
+      if (!is_ship) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const int col = ch * 32 + q * 8;
           uint32_t ob[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const int bi = (col >> 1) + j;
-            float f0 = is_field ? round_bf16(__uint_as_float(v[q * 8 + 2 * j])) * bf16_lo(b2p[bi]) : 0.f;
-            float f1 = is_field ? round_bf16(__uint_as_float(v[q * 8 + 2 * j + 1])) * bf16_hi(b2p[bi]) : 0.f;
+            const int bi = q * 4 + j;
+            float f0 = is_field ? round_bf16(__uint_as_float(v[q * 8 + 2 * j])) * bf16_lo(b2p[rnd][bi]) : 0.f;
+            float f1 = is_field ? round_bf16(__uint_as_float(v[q * 8 + 2 * j + 1])) * bf16_hi(b2p[rnd][bi]) : 0.f;
             ob[j] = pack_bf16(f0, f1);
           }
-          uint8_t* dst = col < 64 ? c.smem + OFF_P + swz(c.row, col >> 3) : c.smem + OFF_A + CHUNK_BYTES + swz(c.row, (col & 63) >> 3);
+          uint8_t* dst = rnd == 0 ? c.smem + OFF_P + swz(c.row, c.half * 4 + q)
+                                  : c.smem + OFF_A + CHUNK_BYTES + swz(c.row, c.half * 4 + q);
           *reinterpret_cast<uint4*>(dst) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
-        }
         }
       }
     }
   } else if (!is_ship) {
     // rows outside every environment: zero operand rows
 #pragma unroll
-    for (int q = 0; q < 8; ++q) {
-      *reinterpret_cast<uint4*>(c.smem + OFF_P + swz(c.row, q)) = make_uint4(0u, 0u, 0u, 0u);
-      *reinterpret_cast<uint4*>(c.smem + OFF_A + CHUNK_BYTES + swz(c.row, q)) = make_uint4(0u, 0u, 0u, 0u);
+    for (int q = 0; q < 4; ++q) {
+      *reinterpret_cast<uint4*>(c.smem + OFF_P + swz(c.row, c.half * 4 + q)) = make_uint4(0u, 0u, 0u, 0u);
+      *reinterpret_cast<uint4*>(c.smem + OFF_A + CHUNK_BYTES + swz(c.row, c.half * 4 + q)) = make_uint4(0u, 0u, 0u, 0u);
     }
   }
   // residual += linear_out(branch): K atom 0 from the second operand, K atom 1 from A
@@ -757,6 +793,7 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
   ffn(c);
 }
 
+template <int MAXKB>
 __global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_constant__ TrunkArgs args) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -784,27 +821,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4) {
-    // ---------------------------------------------------------------- weight producer
-    if ((tid & 31) == 0) {
-      uint32_t count = 0;
-      const uint32_t ring = smem_u32(smem + OFF_RING);
-      for (int tile = blockIdx.x; tile < args.n_tiles; tile += gridDim.x)
-        for (int t = 0; t < args.t_loop; ++t)
-          for (int si = 0; si < args.n_sub; ++si) {
-            const SubLayer& s = args.sub[si];
-            const int n_chunks = s.type == SUB_SPATIAL ? N_SPATIAL_CHUNKS : N_TEMPORAL_CHUNKS;
-            for (int ch = 0; ch < n_chunks; ++ch) {
-              if (s.type == SUB_TEMPORAL && !args.has_fields && (ch == 8 || ch == 9)) continue;
-              const uint32_t slot = count & 1u;
-              mbar_wait(smem_u32(&bars[2 + slot]), ((count >> 1) & 1u) ^ 1u, args.status, &s_aborted, ST_TIMEOUT_EMPTY);
-              mbar_expect_tx(smem_u32(&bars[slot]), CHUNK_BYTES);
-              bulk_g2s(ring + slot * CHUNK_BYTES, s.packed + (size_t)ch * CHUNK_BYTES, CHUNK_BYTES, smem_u32(&bars[slot]));
-              ++count;
-            }
-          }
-    }
-  } else {
+  {
     // ---------------------------------------------------------------- tile owners
     Ctx c;
     c.smem = smem;
@@ -814,19 +831,27 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_consta
     c.sStage = smem_u32(smem + OFF_STAGE);
     c.bar_full[0] = smem_u32(&bars[0]);
     c.bar_full[1] = smem_u32(&bars[1]);
-    c.bar_empty[0] = smem_u32(&bars[2]);
-    c.bar_empty[1] = smem_u32(&bars[3]);
     c.bar_acc = smem_u32(&bars[4]);
     c.tmem = tmem_base;
-    c.lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    c.row = tid & (TILE - 1);
+    c.half = tid >> 7;
+    c.lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     c.status = args.status;
     c.aborted = &s_aborted;
     c.acc_phase = 0;
     c.cons_count = 0;
-    c.row = tid;
+    c.ss_part = reinterpret_cast<float*>(smem + OFF_SS);
+    c.args = &args;
+    c.prod_count = 0;
+    c.p_tile = blockIdx.x;
+    c.p_t = 0;
+    c.p_si = 0;
+    c.p_ch = 0;
+    if (tid == 0) refill(c);
     uint8_t* meta = smem + OFF_META;
     const EnvMap& map = args.map;
     const int NM = map.tokens_per_env;
+    const int row = c.row;
 
     for (int tile = blockIdx.x; tile < args.n_tiles; tile += gridDim.x) {
       // ---- rows of this tile: whole environments, ships first then fields in each
@@ -840,22 +865,22 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_consta
         const int e_lo = args.tile_env_begin[eb], e_hi = args.tile_env_begin[eb + 1];
         const int base = map.tok_off[e_lo];
         const int rows = map.tok_off[e_hi] - base;
-        valid = tid < rows;
+        valid = row < rows;
         env = e_lo;
         if (valid) {
-          while (map.tok_off[env + 1] - base <= tid) ++env;
+          while (map.tok_off[env + 1] - base <= row) ++env;
         }
         env_first = map.tok_off[env] - base;
         env_n = map.tok_off[env + 1] - map.tok_off[env];
         env_ships = map.ship_off[env + 1] - map.ship_off[env];
-        tok = tid - env_first;
-        grow = (size_t)grp * map.total_tokens + (size_t)(base + tid);
+        tok = row - env_first;
+        grow = (size_t)grp * map.total_tokens + (size_t)(base + row);
         hrow_if_ship = map.ship_off[env] + tok;
       } else {
         const int env0 = eb * args.envs_per_tile;
         const int env_cnt = min(args.envs_per_tile, map.n_envs - env0);
-        const int el = tid / NM;
-        tok = tid - el * NM;
+        const int el = row / NM;
+        tok = row - el * NM;
         valid = el < env_cnt;
         env = env0 + el;
         env_first = el * NM;
@@ -872,27 +897,29 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_consta
       rs.lag_ok = BNB_CONV_KERNEL - 1;
       rs.zero_in = is_ship && args.reset_env && args.reset_env[env];
       epi_barrier();  // previous tile's readers of the meta arrays are done
-      meta[tid] = (uint8_t)(valid ? env_first : tid);
-      meta[128 + tid] = (uint8_t)(valid ? env_n - 1 : 0);
+      if (c.half == 0) {
+        meta[row] = (uint8_t)(valid ? env_first : row);
+        meta[128 + row] = (uint8_t)(valid ? env_n - 1 : 0);
+      }
       if (tid == 0) s_items = 0;
       epi_barrier();
-      if (valid && (tok & 15) == 0) meta[384 + atomicAdd(&s_items, 1)] = (uint8_t)tid;
+      if (c.half == 0 && valid && (tok & 15) == 0) meta[384 + atomicAdd(&s_items, 1)] = (uint8_t)row;
 
       for (int t = 0; t < args.t_loop; ++t) {
         const size_t trow = grow + (size_t)t * map.total_tokens;
-        meta[256 + tid] = valid ? (args.alive ? args.alive[trow] : (uint8_t)1) : (uint8_t)0;
-        // residual <- x
+        if (c.half == 0) meta[256 + row] = valid ? (args.alive ? args.alive[trow] : (uint8_t)1) : (uint8_t)0;
+        // residual <- x (this thread: columns [64 half, 64 half + 64))
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
+        for (int ch = 0; ch < 2; ++ch) {
           uint32_t v[32];
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
             float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (valid) f = *reinterpret_cast<const float4*>(args.x + trow * D + ch * 32 + q * 4);
+            if (valid) f = *reinterpret_cast<const float4*>(args.x + trow * D + c.half * 64 + ch * 32 + q * 4);
             v[q * 4 + 0] = __float_as_uint(f.x); v[q * 4 + 1] = __float_as_uint(f.y);
             v[q * 4 + 2] = __float_as_uint(f.z); v[q * 4 + 3] = __float_as_uint(f.w);
           }
-          tmem_st32(c.lane_addr + COL_RESID + ch * 32, v);
+          tmem_st32(c.lane_addr + COL_RESID + c.half * 64 + ch * 32, v);
         }
         bool boundary = false;
         if (t >= 1) {
@@ -900,22 +927,24 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_consta
           rs.lag_ok = boundary ? 0 : min(rs.lag_ok + 1, BNB_CONV_KERNEL - 1);
           rs.zero_in = false;
         }
+        tc_fence_before();
         epi_barrier();
+        tc_fence_after();
         const int n_items = s_items;
         for (int si = 0; si < args.n_sub; ++si) {
           const SubLayer& s = args.sub[si];
-          if (s.type == SUB_SPATIAL) run_spatial(c, s, n_items, valid);
+          if (s.type == SUB_SPATIAL) run_spatial<MAXKB>(c, s, n_items, valid);
           else run_temporal(c, s, rs, is_field, boundary, args.has_fields != 0, t == 0 ? s.hid_in : s.hid_out);
         }
         // y <- residual
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
+        for (int ch = 0; ch < 2; ++ch) {
           uint32_t v[32];
-          tmem_ld32(c.lane_addr + COL_RESID + ch * 32, v);
+          tmem_ld32(c.lane_addr + COL_RESID + c.half * 64 + ch * 32, v);
           if (valid) {
 #pragma unroll
             for (int q = 0; q < 8; ++q)
-              *reinterpret_cast<float4*>(args.y + trow * D + ch * 32 + q * 4) =
+              *reinterpret_cast<float4*>(args.y + trow * D + c.half * 64 + ch * 32 + q * 4) =
                   make_float4(__uint_as_float(v[q * 4]), __uint_as_float(v[q * 4 + 1]), __uint_as_float(v[q * 4 + 2]), __uint_as_float(v[q * 4 + 3]));
           }
         }
@@ -995,13 +1024,15 @@ static int launch(TrunkArgs& a, const BnbBatch& b, cudaStream_t st) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BNB_ERR_NO_DEVICE;
   if (!configured[dev]) {
-    if (cudaFuncSetAttribute(k_trunk_tiles, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(k_trunk_tiles<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
+        cudaFuncSetAttribute(k_trunk_tiles<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
       return BNB_ERR_LAUNCH;
     configured[dev] = true;
   }
   int grid = a.n_tiles < 2 * 148 ? a.n_tiles : 2 * 148;
   count_launch();
-  k_trunk_tiles<<<grid, NTHREADS, SMEM_BYTES, st>>>(a);
+  if (b.max_tokens_per_env <= 64) k_trunk_tiles<4><<<grid, NTHREADS, SMEM_BYTES, st>>>(a);
+  else k_trunk_tiles<8><<<grid, NTHREADS, SMEM_BYTES, st>>>(a);
   return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
 }
 
