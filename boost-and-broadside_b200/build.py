@@ -47,7 +47,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     for src in SOURCES:
         obj = os.path.join(HERE, "build", src.replace(".cu", ".o"))
         os.makedirs(os.path.dirname(obj), exist_ok=True)
-        cmd = [_nvcc(), *NVCC_FLAGS, "-I", os.path.join(ROOT, "include"), "-I", CSRC, "-c",
+        cmd = [_nvcc(), *NVCC_FLAGS, *os.environ.get("BNB_NVCC_FLAGS", "").split(), "-I", os.path.join(ROOT, "include"), "-I", CSRC, "-c",
                os.path.join(CSRC, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")

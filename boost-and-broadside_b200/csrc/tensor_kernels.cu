@@ -54,7 +54,8 @@ constexpr int OFF_STAGE = 81920;         // 128 x 208 = 26624
 constexpr int OFF_META = 108544;         // env_first[128], env_n[128], alive[128], items[128]
 constexpr int OFF_BAR = 109056;          // full[2], empty[2], acc, tmem base
 constexpr int OFF_SS = 109120;           // partial sums of squares, 2 x 128 floats
-constexpr int SMEM_BYTES = 109120 + 1024 + 1024;
+constexpr int OFF_ROWINFO = 110144;      // hidden row of each tile row (int, -1 = no state), then flags
+constexpr int SMEM_BYTES = 110144 + 512 + 128 + 1024;
 
 constexpr uint32_t TMEM_COLS = 256;
 constexpr uint32_t COL_RESID = 0;
@@ -314,38 +315,69 @@ __global__ void k_pack_temporal(BnbTemporalWeights w, uint8_t* out) {
 // `row` (warps w and w+4 both reach lanes 32*(w%4)..) and half of the columns of whatever is
 // being read: K atom `half` of a 128-wide operand, 32 of the 64 columns of a gate|up chunk, ...
 
+// Optional cycle accounting (compile with -DBNB_TIMING): thread 64 of every CTA adds up the
+// cycles it spends in each phase and stores them behind the status word.
+#ifdef BNB_TIMING
+#define T_BEGIN(c) long long _t0 = clock64()
+#define T_END(c, slot) (c).tacc[slot] += clock64() - _t0
+#else
+#define T_BEGIN(c)
+#define T_END(c, slot)
+#endif
+enum : int { TM_WAIT = 0, TM_BARRIER, TM_NORM, TM_FFN_EPI, TM_QKV_EPI, TM_ATTN, TM_TEMPORAL_EPI, TM_IO, TM_TOTAL, TM_COUNT };
+
 struct Ctx {
+#ifdef BNB_TIMING
+  long long tacc[TM_COUNT];
+#endif
   uint8_t* smem;
   uint32_t sA, sP, sRing, sStage;   // shared addresses
-  uint32_t bar_full[2], bar_acc;
+  uint32_t bar_full[3], bar_acc;
   uint32_t tmem;                    // base tensor-memory address
   uint32_t lane_addr;               // tmem + (row's lane << 16)
   int* status;
   volatile int* aborted;
   uint32_t acc_phase;
-  uint32_t cons_count;              // chunks consumed so far (thread 0)
   int row;                          // tile row owned by this thread
   int half;                         // which half of the columns
   float* ss_part;                   // [2][128] partial sums of squares
-  // weight stream cursor (thread 0 only): next chunk to fetch
+  // weight stream (thread 0 only).  Three ring slots: two dedicated, the third is the q|k|v
+  // staging area, which only the GatedMLP chunks use (attention is over by then).
   const TrunkArgs* args;
-  uint32_t prod_count;
-  int p_tile, p_t, p_si, p_ch;
+  int p_tile, p_t, p_si, p_ch;      // next chunk to fetch
+  uint32_t pending;                 // slots holding a chunk that is loaded or in flight and not yet retired
+  uint32_t issued;                  // slots whose chunk was consumed by MMAs of the current round
+  uint32_t parity;                  // per-slot phase bit of the full barrier
+  uint32_t qbits, qlen;             // FIFO of slot ids in fetch order (2 bits each)
 };
+
+__device__ __forceinline__ uint32_t slot_addr(const Ctx& c, uint32_t slot) {
+  return slot < 2 ? c.sRing + slot * CHUNK_BYTES : c.sStage;
+}
+__device__ __forceinline__ uint32_t chunk_slot(int type, int ch) {
+  const int first_ffn = type == SUB_SPATIAL ? 10 : 12;
+  return ch < first_ffn ? (uint32_t)(ch & 1) : (uint32_t)((ch - first_ffn) % 3);
+}
 
 // Thread 0: fetch weight chunks of the stream into every free ring slot.  Called when all
 // earlier MMAs are known to be complete (start of the kernel, end of a round), so a slot
 // whose chunk has been consumed is free to overwrite.
 __device__ __forceinline__ void refill(Ctx& c) {
   const TrunkArgs& a = *c.args;
-  while (c.prod_count - c.cons_count < 2u && c.p_tile < a.n_tiles) {
+  // every MMA issued so far is complete: the slots they read are free again
+  c.pending &= ~c.issued;
+  c.issued = 0;
+  while (c.qlen < 3u && c.p_tile < a.n_tiles) {
     const SubLayer& s = a.sub[c.p_si];
     const int n_chunks = s.type == SUB_SPATIAL ? N_SPATIAL_CHUNKS : N_TEMPORAL_CHUNKS;
     if (s.type == SUB_TEMPORAL && !a.has_fields && c.p_ch == 8) c.p_ch = 10;  // no field_sub round
-    const uint32_t slot = c.prod_count & 1u;
+    const uint32_t slot = chunk_slot(s.type, c.p_ch);
+    if (c.pending & (1u << slot)) break;
     mbar_expect_tx(c.bar_full[slot], CHUNK_BYTES);
-    bulk_g2s(c.sRing + slot * CHUNK_BYTES, s.packed + (size_t)c.p_ch * CHUNK_BYTES, CHUNK_BYTES, c.bar_full[slot]);
-    ++c.prod_count;
+    bulk_g2s(slot_addr(c, slot), s.packed + (size_t)c.p_ch * CHUNK_BYTES, CHUNK_BYTES, c.bar_full[slot]);
+    c.pending |= 1u << slot;
+    c.qbits |= slot << (2u * c.qlen);
+    ++c.qlen;
     if (++c.p_ch == n_chunks) {
       c.p_ch = 0;
       if (++c.p_si == a.n_sub) {
@@ -360,34 +392,42 @@ __device__ __forceinline__ void refill(Ctx& c) {
 }
 
 __device__ __forceinline__ void round_begin(Ctx& c) {
+  T_BEGIN(c);
   fence_proxy_async();
   tc_fence_before();
   epi_barrier();
   if (threadIdx.x == 0) tc_fence_after();
+  T_END(c, TM_BARRIER);
 }
 // Thread 0: D[128 x n] (+)= A[128 x 64] * W[n x 64]^T with the next weight chunk of the stream.
 __device__ __forceinline__ void issue_chunk(Ctx& c, uint32_t a_addr, uint32_t n, uint32_t d_col, uint32_t accumulate) {
-  const uint32_t slot = c.cons_count & 1u;
-  mbar_wait(c.bar_full[slot], (c.cons_count >> 1) & 1u, c.status, c.aborted, ST_TIMEOUT_FULL);
+  const uint32_t slot = c.qbits & 3u;
+  c.qbits >>= 2;
+  --c.qlen;
+  mbar_wait(c.bar_full[slot], (c.parity >> slot) & 1u, c.status, c.aborted, ST_TIMEOUT_FULL);
+  c.parity ^= 1u << slot;
   tc_fence_after();
-  const uint32_t b_addr = c.sRing + slot * CHUNK_BYTES;
+  const uint32_t b_addr = slot_addr(c, slot);
   const uint32_t idesc = instr_desc(n);
 #pragma unroll
   for (int k = 0; k < 4; ++k)
     tc_mma(c.tmem + d_col, smem_desc(a_addr + k * 32), smem_desc(b_addr + k * 32), idesc, (accumulate | (uint32_t)k) ? 1u : 0u);
-  ++c.cons_count;
+  c.issued |= 1u << slot;
 }
 __device__ __forceinline__ void round_end(Ctx& c) {
+  T_BEGIN(c);
   if (threadIdx.x == 0) tc_commit(c.bar_acc);
   mbar_wait(c.bar_acc, c.acc_phase, c.status, c.aborted, ST_TIMEOUT_ACC);
   c.acc_phase ^= 1u;
   if (threadIdx.x == 0) refill(c);
   __syncwarp();  // the spin above may leave the warp diverged; tcgen05.ld/st need it converged
   tc_fence_after();
+  T_END(c, TM_WAIT);
 }
 
 // residual (TMEM) -> RMSNorm -> bf16 A operand; each thread norms its 64 columns = K atom `half`
 __device__ __forceinline__ void norm_to_A(Ctx& c, const float* __restrict__ g) {
+  T_BEGIN(c);
   uint32_t v[32], w[32];
   tmem_ld32_nowait(c.lane_addr + COL_RESID + c.half * 64, v);
   tmem_ld32_nowait(c.lane_addr + COL_RESID + c.half * 64 + 32, w);
@@ -417,18 +457,20 @@ __device__ __forceinline__ void norm_to_A(Ctx& c, const float* __restrict__ g) {
     o.w = pack_bf16(__uint_as_float(src[6]) * inv * g1.z, __uint_as_float(src[7]) * inv * g1.w);
     *reinterpret_cast<uint4*>(dst + swz(c.row, q)) = o;
   }
+  T_END(c, TM_NORM);
 }
 
 // GatedMLP on the A operand (already normed): residual += down(gelu(gate) * up).
 __device__ __forceinline__ void ffn(Ctx& c) {
+  round_begin(c);
+  if (threadIdx.x == 0) {
+    issue_chunk(c, c.sA, 128, COL_ACC, 0);
+    issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1);
+  }
+  round_end(c);
   for (int cc = 0; cc < 8; ++cc) {
-    round_begin(c);
-    if (threadIdx.x == 0) {
-      issue_chunk(c, c.sA, 128, COL_ACC, 0);
-      issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1);
-    }
-    round_end(c);
     // gate = acc[0,64), up = acc[64,128); this thread: hidden columns [32 half, 32 half + 32)
+    T_BEGIN(c);
     uint32_t gv[32], uv[32];
     tmem_ld32_nowait(c.lane_addr + COL_ACC + c.half * 32, gv);
     tmem_ld32_nowait(c.lane_addr + COL_ACC + 64 + c.half * 32, uv);
@@ -442,8 +484,17 @@ __device__ __forceinline__ void ffn(Ctx& c) {
                          gelu_fast(__uint_as_float(gv[q * 8 + 2 * j + 1])) * __uint_as_float(uv[q * 8 + 2 * j + 1]));
       *reinterpret_cast<uint4*>(c.smem + OFF_P + swz(c.row, c.half * 4 + q)) = make_uint4(o[0], o[1], o[2], o[3]);
     }
+    T_END(c, TM_FFN_EPI);
+    // one round: this chunk's down projection into the residual, then the next chunk's
+    // gate|up (the accumulator has been read, the product operand is only read by `down`)
     round_begin(c);
-    if (threadIdx.x == 0) issue_chunk(c, c.sP, 128, COL_RESID, 1);
+    if (threadIdx.x == 0) {
+      issue_chunk(c, c.sP, 128, COL_RESID, 1);
+      if (cc < 7) {
+        issue_chunk(c, c.sA, 128, COL_ACC, 0);
+        issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1);
+      }
+    }
     round_end(c);
   }
 }
@@ -575,6 +626,7 @@ __device__ __forceinline__ void run_spatial(Ctx& c, const SubLayer& s, int n_ite
       round_end(c);
       // q|k|v of this head -> bf16 staging rows; this thread: accumulator columns [48 half, 48 half + 48)
       {
+        T_BEGIN(c);
         uint32_t v[32], w[16];
         tmem_ld32_nowait(c.lane_addr + COL_ACC + c.half * 48, v);
         tmem_ld16_nowait(c.lane_addr + COL_ACC + c.half * 48 + 32, w);
@@ -587,6 +639,7 @@ __device__ __forceinline__ void run_spatial(Ctx& c, const SubLayer& s, int n_ite
               make_uint4(pack_bf16(__uint_as_float(src[0]), __uint_as_float(src[1])), pack_bf16(__uint_as_float(src[2]), __uint_as_float(src[3])),
                          pack_bf16(__uint_as_float(src[4]), __uint_as_float(src[5])), pack_bf16(__uint_as_float(src[6]), __uint_as_float(src[7])));
         }
+        T_END(c, TM_QKV_EPI);
       }
       if (!row_valid && hh == 0) {
         // rows outside every environment contribute a zero operand row
@@ -594,9 +647,13 @@ __device__ __forceinline__ void run_spatial(Ctx& c, const SubLayer& s, int n_ite
         for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(c.smem + OFF_P + swz(c.row, c.half * 4 + q)) = make_uint4(0u, 0u, 0u, 0u);
       }
       tc_fence_before();
-      epi_barrier();
-      attention_head<MAXKB>(c, hh, n_items);
-      epi_barrier();  // staging rows are free again
+      {
+        T_BEGIN(c);
+        epi_barrier();
+        attention_head<MAXKB>(c, hh, n_items);
+        epi_barrier();  // staging rows are free again
+        T_END(c, TM_ATTN);
+      }
     }
     round_begin(c);
     if (threadIdx.x == 0) issue_chunk(c, c.sP, 128, COL_RESID, 1);
@@ -627,6 +684,8 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
     issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1);
   }
   round_end(c);
+  {
+  T_BEGIN(c);
 #pragma unroll
   for (int rnd = 0; rnd < 2; ++rnd) {
     uint32_t v[32];
@@ -634,6 +693,8 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
 #pragma unroll
     for (int j = 0; j < 16; ++j)
       b2p[rnd][j] = pack_bf16(gelu_fast(__uint_as_float(v[2 * j])), gelu_fast(__uint_as_float(v[2 * j + 1])));
+  }
+  T_END(c, TM_TEMPORAL_EPI);
   }
   // b1 = bf16(linear1 n); ships: causal conv with the stored taps -> u; fields: keep b1.
   // This thread: columns [64 half, 64 half + 64) = K atom `half` of the operand.
@@ -645,49 +706,73 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
   round_end(c);
   const float* hin = is_ship ? hid_in + (size_t)rs.hrow * 4 * D : nullptr;
   float* hout = is_ship ? s.hid_out + (size_t)rs.hrow * 4 * D : nullptr;
+  T_BEGIN(c);
+  // (1) every thread parks bf16(b1) of its 64 columns in the A operand (K atom `half`)
 #pragma unroll
   for (int ch = 0; ch < 2; ++ch) {
     uint32_t v[32];
     tmem_ld32(c.lane_addr + COL_ACC + c.half * 64 + ch * 32, v);
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      const int col = c.half * 64 + ch * 32 + q * 8;
-      float u[8];
-#pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        const int cc = col + hf * 4;
-        float b1[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) b1[i] = round_bf16(__uint_as_float(v[q * 8 + hf * 4 + i]));
-        if (is_ship) {
-          float4 t0 = make_float4(0.f, 0.f, 0.f, 0.f), t1 = t0, t2 = t0;
-          if (!rs.zero_in) {
-            t0 = *reinterpret_cast<const float4*>(hin + D + cc);
-            t1 = *reinterpret_cast<const float4*>(hin + 2 * D + cc);
-            t2 = *reinterpret_cast<const float4*>(hin + 3 * D + cc);
-          }
-          *reinterpret_cast<float4*>(hout + D + cc) = t1;
-          *reinterpret_cast<float4*>(hout + 2 * D + cc) = t2;
-          *reinterpret_cast<float4*>(hout + 3 * D + cc) = make_float4(b1[0], b1[1], b1[2], b1[3]);
-          const float a0[4] = {t0.x, t0.y, t0.z, t0.w}, a1[4] = {t1.x, t1.y, t1.z, t1.w}, a2[4] = {t2.x, t2.y, t2.z, t2.w};
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            float4 cw = __ldg(reinterpret_cast<const float4*>(s.conv_w + (cc + i) * 4));
-            float p0 = rs.lag_ok >= 3 ? __fmul_rn(a0[i], cw.x) : 0.f;
-            float p1 = rs.lag_ok >= 2 ? __fmul_rn(a1[i], cw.y) : 0.f;
-            float p2 = rs.lag_ok >= 1 ? __fmul_rn(a2[i], cw.z) : 0.f;
-            float p3 = __fmul_rn(b1[i], cw.w);
-            u[hf * 4 + i] = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(p0, p1), p2), p3), __ldg(s.conv_b + cc + i));
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) u[hf * 4 + i] = b1[i];
-        }
-      }
-      uint4 o = make_uint4(pack_bf16(u[0], u[1]), pack_bf16(u[2], u[3]), pack_bf16(u[4], u[5]), pack_bf16(u[6], u[7]));
+      uint4 o = make_uint4(pack_bf16(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1])),
+                           pack_bf16(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3])),
+                           pack_bf16(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5])),
+                           pack_bf16(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7])));
       *reinterpret_cast<uint4*>(c.smem + OFF_A + c.half * CHUNK_BYTES + swz(c.row, ch * 4 + q)) = o;
     }
   }
+  tc_fence_before();
+  epi_barrier();
+  // (2) causal conv, one warp per ship row and four columns per lane, so that the stored taps
+  // are read and written as whole 512-byte rows.  u = bias + w0 tap0 + w1 tap1 + w2 tap2 + w3 b1,
+  // summed in the reference's order; new taps = (tap1, tap2, b1); bf16(u) replaces b1 in A.
+  {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int col = lane * 4;
+    float cw[4][4], cb[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float4 w4 = __ldg(reinterpret_cast<const float4*>(s.conv_w + (col + i) * 4));
+      cw[i][0] = w4.x; cw[i][1] = w4.y; cw[i][2] = w4.z; cw[i][3] = w4.w;
+      cb[i] = __ldg(s.conv_b + col + i);
+    }
+    const int* row_hrow = reinterpret_cast<const int*>(c.smem + OFF_ROWINFO);
+    const uint8_t* row_flags = c.smem + OFF_ROWINFO + 512;
+#pragma unroll 4
+    for (int r = warp; r < TILE; r += 8) {
+      const int hr = row_hrow[r];
+      if (hr < 0) continue;
+      const int flags = row_flags[r];
+      const int lag_ok = flags & 3;
+      const bool zero_in = (flags & 4) != 0;
+      const float* hi = hid_in + (size_t)hr * 4 * D + col;
+      float* ho = s.hid_out + (size_t)hr * 4 * D + col;
+      float4 t0 = make_float4(0.f, 0.f, 0.f, 0.f), t1 = t0, t2 = t0;
+      if (!zero_in) {
+        t0 = *reinterpret_cast<const float4*>(hi + D);
+        t1 = *reinterpret_cast<const float4*>(hi + 2 * D);
+        t2 = *reinterpret_cast<const float4*>(hi + 3 * D);
+      }
+      uint8_t* bp = c.smem + OFF_A + (lane >> 4) * CHUNK_BYTES + swz(r, (lane & 15) >> 1) + (lane & 1) * 8;
+      const uint2 bw = *reinterpret_cast<const uint2*>(bp);
+      const float b1[4] = {bf16_lo(bw.x), bf16_hi(bw.x), bf16_lo(bw.y), bf16_hi(bw.y)};
+      *reinterpret_cast<float4*>(ho + D) = t1;
+      *reinterpret_cast<float4*>(ho + 2 * D) = t2;
+      *reinterpret_cast<float4*>(ho + 3 * D) = make_float4(b1[0], b1[1], b1[2], b1[3]);
+      const float a0[4] = {t0.x, t0.y, t0.z, t0.w}, a1[4] = {t1.x, t1.y, t1.z, t1.w}, a2[4] = {t2.x, t2.y, t2.z, t2.w};
+      float u[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float p0 = lag_ok >= 3 ? __fmul_rn(a0[i], cw[i][0]) : 0.f;
+        float p1 = lag_ok >= 2 ? __fmul_rn(a1[i], cw[i][1]) : 0.f;
+        float p2 = lag_ok >= 1 ? __fmul_rn(a2[i], cw[i][2]) : 0.f;
+        float p3 = __fmul_rn(b1[i], cw[i][3]);
+        u[i] = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(p0, p1), p2), p3), cb[i]);
+      }
+      *reinterpret_cast<uint2*>(bp) = make_uint2(pack_bf16(u[0], u[1]), pack_bf16(u[2], u[3]));
+    }
+  }
+  T_END(c, TM_TEMPORAL_EPI);
   // gates and state update, 64 hidden columns per round: acc[0,64) = W_a u, acc[64,128) = W_x u
 #pragma unroll
   for (int rnd = 0; rnd < 2; ++rnd) {
@@ -696,7 +781,15 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
       issue_chunk(c, c.sA, 128, COL_ACC, 0);
       issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1);
     }
+    // previous state of this thread's 32 columns, requested before waiting for the gates
+    float4 hprev[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      hprev[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (is_ship && !rs.zero_in) hprev[q] = *reinterpret_cast<const float4*>(hin + rnd * 64 + c.half * 32 + q * 4);
+    }
     round_end(c);
+    T_BEGIN(c);
     uint32_t rv[32], iv[32];
     tmem_ld32_nowait(c.lane_addr + COL_ACC + c.half * 32, rv);       // executed by every lane of the warp
     tmem_ld32_nowait(c.lane_addr + COL_ACC + 64 + c.half * 32, iv);
@@ -713,8 +806,7 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
           const int cc = col + hf * 4;
-          float4 hv = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (!rs.zero_in) hv = *reinterpret_cast<const float4*>(hin + cc);
+          const float4 hv = hprev[q * 2 + hf];
           const float4 ab = __ldg(reinterpret_cast<const float4*>(s.a_b + cc));
           const float4 xb = __ldg(reinterpret_cast<const float4*>(s.x_b + cc));
           const float4 dl = __ldg(reinterpret_cast<const float4*>(s.decay_log2 + cc));
@@ -744,6 +836,7 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
         *reinterpret_cast<uint4*>(dst) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
       }
     }
+    T_END(c, TM_IO);
   }
   if (has_fields) {
     // field rows: branch = bf16(bf16(field_sub b1) * b2)
@@ -831,6 +924,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_consta
     c.sStage = smem_u32(smem + OFF_STAGE);
     c.bar_full[0] = smem_u32(&bars[0]);
     c.bar_full[1] = smem_u32(&bars[1]);
+    c.bar_full[2] = smem_u32(&bars[2]);
     c.bar_acc = smem_u32(&bars[4]);
     c.tmem = tmem_base;
     c.row = tid & (TILE - 1);
@@ -839,10 +933,13 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_consta
     c.status = args.status;
     c.aborted = &s_aborted;
     c.acc_phase = 0;
-    c.cons_count = 0;
     c.ss_part = reinterpret_cast<float*>(smem + OFF_SS);
+#ifdef BNB_TIMING
+    for (int i = 0; i < TM_COUNT; ++i) c.tacc[i] = 0;
+    const long long t_kernel0 = clock64();
+#endif
     c.args = &args;
-    c.prod_count = 0;
+    c.pending = c.issued = c.parity = c.qbits = c.qlen = 0;
     c.p_tile = blockIdx.x;
     c.p_t = 0;
     c.p_si = 0;
@@ -901,6 +998,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_consta
         meta[row] = (uint8_t)(valid ? env_first : row);
         meta[128 + row] = (uint8_t)(valid ? env_n - 1 : 0);
       }
+      if (c.half == 0) reinterpret_cast<int*>(smem + OFF_ROWINFO)[row] = rs.hrow;
       if (tid == 0) s_items = 0;
       epi_barrier();
       if (c.half == 0 && valid && (tok & 15) == 0) meta[384 + atomicAdd(&s_items, 1)] = (uint8_t)row;
@@ -927,6 +1025,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_consta
           rs.lag_ok = boundary ? 0 : min(rs.lag_ok + 1, BNB_CONV_KERNEL - 1);
           rs.zero_in = false;
         }
+        if (c.half == 0) smem[OFF_ROWINFO + 512 + row] = (uint8_t)(rs.lag_ok | (rs.zero_in ? 4 : 0));
         tc_fence_before();
         epi_barrier();
         tc_fence_after();
@@ -950,6 +1049,12 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_consta
         }
       }
     }
+#ifdef BNB_TIMING
+  if (tid == 64) {
+    c.tacc[TM_TOTAL] = clock64() - t_kernel0;
+    for (int i = 0; i < TM_COUNT; ++i) reinterpret_cast<long long*>(args.status)[32 + blockIdx.x * TM_COUNT + i] = c.tacc[i];
+  }
+#endif
   }
   tc_fence_before();
   __syncthreads();
@@ -989,7 +1094,7 @@ int plan_tiles(const int32_t* tok_off, int n_envs, int32_t* tile_env_begin, int 
   return BNB_OK;
 }
 
-size_t scratch_bytes(int, const BnbBatch&, int) { return 256; }
+size_t scratch_bytes(int, const BnbBatch&, int) { return 65536; }
 size_t packed_spatial_bytes(int d_model) { return d_model == D ? (size_t)N_SPATIAL_CHUNKS * CHUNK_BYTES : 0; }
 size_t packed_temporal_bytes(int d_model) { return d_model == D ? (size_t)N_TEMPORAL_CHUNKS * CHUNK_BYTES + 1024 : 0; }
 
@@ -1038,7 +1143,7 @@ static int launch(TrunkArgs& a, const BnbBatch& b, cudaStream_t st) {
 
 static int prepare_status(void* scratch, size_t scratch_bytes, cudaStream_t st, int** status) {
   if (!scratch) return BNB_ERR_NULL_POINTER;
-  if (scratch_bytes < 256) return BNB_ERR_SCRATCH_TOO_SMALL;
+  if (scratch_bytes < 65536) return BNB_ERR_SCRATCH_TOO_SMALL;
   *status = static_cast<int*>(scratch);
   if (cudaMemsetAsync(scratch, 0, 256, st) != cudaSuccess) return BNB_ERR_LAUNCH;
   return BNB_OK;
