@@ -324,7 +324,7 @@ __global__ void k_pack_temporal(BnbTemporalWeights w, uint8_t* out) {
 #define T_BEGIN(c)
 #define T_END(c, slot)
 #endif
-enum : int { TM_WAIT = 0, TM_BARRIER, TM_NORM, TM_FFN_EPI, TM_QKV_EPI, TM_ATTN, TM_TEMPORAL_EPI, TM_IO, TM_TOTAL, TM_COUNT };
+enum : int { TM_WAIT = 0, TM_BARRIER, TM_NORM, TM_FFN_EPI, TM_QKV_EPI, TM_ATTN, TM_TEMPORAL_EPI, TM_IO, TM_TOTAL, TM_FULL_WAIT, TM_REFILL, TM_EXPECT, TM_BULK, TM_ISSUE, TM_COUNT };
 
 struct Ctx {
 #ifdef BNB_TIMING
@@ -341,15 +341,19 @@ struct Ctx {
   int row;                          // tile row owned by this thread
   int half;                         // which half of the columns
   float* ss_part;                   // [2][128] partial sums of squares
-  // weight stream (thread 0 only).  Three ring slots: two dedicated, the third is the q|k|v
-  // staging area, which only the GatedMLP chunks use (attention is over by then).
-  const TrunkArgs* args;
-  int p_tile, p_t, p_si, p_ch;      // next chunk to fetch
-  uint32_t pending;                 // slots holding a chunk that is loaded or in flight and not yet retired
-  uint32_t issued;                  // slots whose chunk was consumed by MMAs of the current round
-  uint32_t parity;                  // per-slot phase bit of the full barrier
-  uint32_t qbits, qlen;             // FIFO of slot ids in fetch order (2 bits each)
+  // Weight stream.  Three ring slots: two dedicated, the third is the q|k|v staging area,
+  // which only the GatedMLP chunks use (attention is over by then).  Every call site knows
+  // the slot of the chunk it consumes; the fetching thread walks a schedule table.
+  uint32_t parity;                  // consumer (thread 0): per-slot phase bit of the full barrier
+  int cons_count;                   // consumer: chunks consumed so far
+  volatile int* s_cons;             // shared copy of cons_count, published before each commit
+  const uint16_t* sched;            // fetcher: schedule of one pass over the sublayers
+  int sched_len, p_idx, p_seq, p_left;
+  int occ[3];                       // fetcher: sequence number of the chunk in each slot (-1 = none)
+  const SubLayer* subs;             // sublayer table in shared memory
 };
+
+constexpr int FETCH_THREAD = 224;   // lane 0 of warp 7 fetches weights; thread 0 issues the MMAs
 
 __device__ __forceinline__ uint32_t slot_addr(const Ctx& c, uint32_t slot) {
   return slot < 2 ? c.sRing + slot * CHUNK_BYTES : c.sStage;
@@ -359,35 +363,23 @@ __device__ __forceinline__ uint32_t chunk_slot(int type, int ch) {
   return ch < first_ffn ? (uint32_t)(ch & 1) : (uint32_t)((ch - first_ffn) % 3);
 }
 
-// Thread 0: fetch weight chunks of the stream into every free ring slot.  Called when all
-// earlier MMAs are known to be complete (start of the kernel, end of a round), so a slot
-// whose chunk has been consumed is free to overwrite.
+// Fetching thread: bring the next chunks of the stream into every slot whose previous
+// chunk has been retired.  Called right after a wait on the accumulator barrier, when all
+// MMAs issued so far are complete, so a chunk with sequence number < *s_cons is retired.
 __device__ __forceinline__ void refill(Ctx& c) {
-  const TrunkArgs& a = *c.args;
-  // every MMA issued so far is complete: the slots they read are free again
-  c.pending &= ~c.issued;
-  c.issued = 0;
-  while (c.qlen < 3u && c.p_tile < a.n_tiles) {
-    const SubLayer& s = a.sub[c.p_si];
-    const int n_chunks = s.type == SUB_SPATIAL ? N_SPATIAL_CHUNKS : N_TEMPORAL_CHUNKS;
-    if (s.type == SUB_TEMPORAL && !a.has_fields && c.p_ch == 8) c.p_ch = 10;  // no field_sub round
-    const uint32_t slot = chunk_slot(s.type, c.p_ch);
-    if (c.pending & (1u << slot)) break;
+  const int retired = *c.s_cons;
+  while (c.p_left > 0) {
+    const uint32_t e = c.sched[c.p_idx];
+    const uint32_t slot = e & 3u;
+    const int occ = slot == 0 ? c.occ[0] : (slot == 1 ? c.occ[1] : c.occ[2]);
+    if (occ >= retired) break;
+    const SubLayer& s = c.subs[(e >> 2) & 15u];
     mbar_expect_tx(c.bar_full[slot], CHUNK_BYTES);
-    bulk_g2s(slot_addr(c, slot), s.packed + (size_t)c.p_ch * CHUNK_BYTES, CHUNK_BYTES, c.bar_full[slot]);
-    c.pending |= 1u << slot;
-    c.qbits |= slot << (2u * c.qlen);
-    ++c.qlen;
-    if (++c.p_ch == n_chunks) {
-      c.p_ch = 0;
-      if (++c.p_si == a.n_sub) {
-        c.p_si = 0;
-        if (++c.p_t == a.t_loop) {
-          c.p_t = 0;
-          c.p_tile += gridDim.x;
-        }
-      }
-    }
+    bulk_g2s(slot_addr(c, slot), s.packed + (size_t)(e >> 6) * CHUNK_BYTES, CHUNK_BYTES, c.bar_full[slot]);
+    if (slot == 0) c.occ[0] = c.p_seq; else if (slot == 1) c.occ[1] = c.p_seq; else c.occ[2] = c.p_seq;
+    ++c.p_seq;
+    --c.p_left;
+    if (++c.p_idx == c.sched_len) c.p_idx = 0;
   }
 }
 
@@ -399,27 +391,41 @@ __device__ __forceinline__ void round_begin(Ctx& c) {
   if (threadIdx.x == 0) tc_fence_after();
   T_END(c, TM_BARRIER);
 }
-// Thread 0: D[128 x n] (+)= A[128 x 64] * W[n x 64]^T with the next weight chunk of the stream.
-__device__ __forceinline__ void issue_chunk(Ctx& c, uint32_t a_addr, uint32_t n, uint32_t d_col, uint32_t accumulate) {
-  const uint32_t slot = c.qbits & 3u;
-  c.qbits >>= 2;
-  --c.qlen;
-  mbar_wait(c.bar_full[slot], (c.parity >> slot) & 1u, c.status, c.aborted, ST_TIMEOUT_FULL);
+// Thread 0: D[128 x n] (+)= A[128 x 64] * W[n x 64]^T with the next weight chunk of the stream,
+// which the schedule placed in ring slot `slot`.
+__device__ __forceinline__ void issue_chunk(Ctx& c, uint32_t a_addr, uint32_t n, uint32_t d_col, uint32_t accumulate, uint32_t slot) {
+  {
+    T_BEGIN(c);
+    mbar_wait(c.bar_full[slot], (c.parity >> slot) & 1u, c.status, c.aborted, ST_TIMEOUT_FULL);
+    T_END(c, TM_FULL_WAIT);
+  }
   c.parity ^= 1u << slot;
   tc_fence_after();
   const uint32_t b_addr = slot_addr(c, slot);
   const uint32_t idesc = instr_desc(n);
+  {
+    T_BEGIN(c);
 #pragma unroll
-  for (int k = 0; k < 4; ++k)
-    tc_mma(c.tmem + d_col, smem_desc(a_addr + k * 32), smem_desc(b_addr + k * 32), idesc, (accumulate | (uint32_t)k) ? 1u : 0u);
-  c.issued |= 1u << slot;
+    for (int k = 0; k < 4; ++k)
+      tc_mma(c.tmem + d_col, smem_desc(a_addr + k * 32), smem_desc(b_addr + k * 32), idesc, (accumulate | (uint32_t)k) ? 1u : 0u);
+    T_END(c, TM_ISSUE);
+  }
+  ++c.cons_count;
 }
 __device__ __forceinline__ void round_end(Ctx& c) {
   T_BEGIN(c);
-  if (threadIdx.x == 0) tc_commit(c.bar_acc);
+  if (threadIdx.x == 0) {
+    *c.s_cons = c.cons_count;
+    __threadfence_block();
+    tc_commit(c.bar_acc);
+  }
   mbar_wait(c.bar_acc, c.acc_phase, c.status, c.aborted, ST_TIMEOUT_ACC);
   c.acc_phase ^= 1u;
-  if (threadIdx.x == 0) refill(c);
+  if (threadIdx.x == FETCH_THREAD) {
+    T_BEGIN(c);
+    refill(c);
+    T_END(c, TM_REFILL);
+  }
   __syncwarp();  // the spin above may leave the warp diverged; tcgen05.ld/st need it converged
   tc_fence_after();
   T_END(c, TM_WAIT);
@@ -464,8 +470,8 @@ __device__ __forceinline__ void norm_to_A(Ctx& c, const float* __restrict__ g) {
 __device__ __forceinline__ void ffn(Ctx& c) {
   round_begin(c);
   if (threadIdx.x == 0) {
-    issue_chunk(c, c.sA, 128, COL_ACC, 0);
-    issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1);
+    issue_chunk(c, c.sA, 128, COL_ACC, 0, 0);
+    issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1, 1);
   }
   round_end(c);
   for (int cc = 0; cc < 8; ++cc) {
@@ -489,10 +495,10 @@ __device__ __forceinline__ void ffn(Ctx& c) {
     // gate|up (the accumulator has been read, the product operand is only read by `down`)
     round_begin(c);
     if (threadIdx.x == 0) {
-      issue_chunk(c, c.sP, 128, COL_RESID, 1);
+      issue_chunk(c, c.sP, 128, COL_RESID, 1, 2);
       if (cc < 7) {
-        issue_chunk(c, c.sA, 128, COL_ACC, 0);
-        issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1);
+        issue_chunk(c, c.sA, 128, COL_ACC, 0, 0);
+        issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1, 1);
       }
     }
     round_end(c);
@@ -620,8 +626,8 @@ __device__ __forceinline__ void run_spatial(Ctx& c, const SubLayer& s, int n_ite
     for (int hh = 0; hh < 2; ++hh) {
       round_begin(c);
       if (threadIdx.x == 0) {
-        issue_chunk(c, c.sA, 96, COL_ACC, 0);
-        issue_chunk(c, c.sA + CHUNK_BYTES, 96, COL_ACC, 1);
+        issue_chunk(c, c.sA, 96, COL_ACC, 0, (uint32_t)(p & 1));          // chunks 5p+2hh, 5p+2hh+1
+        issue_chunk(c, c.sA + CHUNK_BYTES, 96, COL_ACC, 1, (uint32_t)((p & 1) ^ 1));
       }
       round_end(c);
       // q|k|v of this head -> bf16 staging rows; this thread: accumulator columns [48 half, 48 half + 48)
@@ -656,7 +662,7 @@ __device__ __forceinline__ void run_spatial(Ctx& c, const SubLayer& s, int n_ite
       }
     }
     round_begin(c);
-    if (threadIdx.x == 0) issue_chunk(c, c.sP, 128, COL_RESID, 1);
+    if (threadIdx.x == 0) issue_chunk(c, c.sP, 128, COL_RESID, 1, (uint32_t)(p & 1));  // chunk 5p+4
     round_end(c);
   }
   norm_to_A(c, s.g2);
@@ -680,8 +686,8 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
   uint32_t b2p[2][16];
   round_begin(c);
   if (threadIdx.x == 0) {
-    issue_chunk(c, c.sA, 128, COL_ACC, 0);
-    issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1);
+    issue_chunk(c, c.sA, 128, COL_ACC, 0, 0);
+    issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1, 1);
   }
   round_end(c);
   {
@@ -700,8 +706,8 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
   // This thread: columns [64 half, 64 half + 64) = K atom `half` of the operand.
   round_begin(c);
   if (threadIdx.x == 0) {
-    issue_chunk(c, c.sA, 128, COL_ACC, 0);
-    issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1);
+    issue_chunk(c, c.sA, 128, COL_ACC, 0, 0);
+    issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1, 1);
   }
   round_end(c);
   const float* hin = is_ship ? hid_in + (size_t)rs.hrow * 4 * D : nullptr;
@@ -778,8 +784,8 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
   for (int rnd = 0; rnd < 2; ++rnd) {
     round_begin(c);
     if (threadIdx.x == 0) {
-      issue_chunk(c, c.sA, 128, COL_ACC, 0);
-      issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1);
+      issue_chunk(c, c.sA, 128, COL_ACC, 0, 0);
+      issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1, 1);
     }
     // previous state of this thread's 32 columns, requested before waiting for the gates
     float4 hprev[8];
@@ -842,8 +848,8 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
     // field rows: branch = bf16(bf16(field_sub b1) * b2)
     round_begin(c);
     if (threadIdx.x == 0) {
-      issue_chunk(c, c.sA, 128, COL_ACC, 0);
-      issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1);
+      issue_chunk(c, c.sA, 128, COL_ACC, 0, 0);
+      issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1, 1);
     }
     round_end(c);
 #pragma unroll
@@ -878,8 +884,8 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
   // residual += linear_out(branch): K atom 0 from the second operand, K atom 1 from A
   round_begin(c);
   if (threadIdx.x == 0) {
-    issue_chunk(c, c.sP, 128, COL_RESID, 1);
-    issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_RESID, 1);
+    issue_chunk(c, c.sP, 128, COL_RESID, 1, 0);
+    issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_RESID, 1, 1);
   }
   round_end(c);
   norm_to_A(c, s.g2);
@@ -892,7 +898,25 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_consta
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ int s_aborted;
   __shared__ int s_items;
+  __shared__ SubLayer s_sub[MAX_SUBLAYERS];  // kernel parameters are slow to index dynamically
+  __shared__ uint16_t s_sched[MAX_SUBLAYERS * N_TEMPORAL_CHUNKS];  // (chunk << 6) | (sublayer << 2) | slot
+  __shared__ int s_sched_len;
+  __shared__ int s_cons;
   const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid < args.n_sub) s_sub[tid] = args.sub[tid];
+  if (tid == 32) {
+    int n = 0;
+    for (int si = 0; si < args.n_sub; ++si) {
+      const int type = args.sub[si].type;
+      const int n_chunks = type == SUB_SPATIAL ? N_SPATIAL_CHUNKS : N_TEMPORAL_CHUNKS;
+      for (int ch = 0; ch < n_chunks; ++ch) {
+        if (type == SUB_TEMPORAL && !args.has_fields && (ch == 8 || ch == 9)) continue;  // no field_sub round
+        s_sched[n++] = (uint16_t)((ch << 6) | (si << 2) | chunk_slot(type, ch));
+      }
+    }
+    s_sched_len = n;
+    s_cons = 0;
+  }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_BAR + 48);
 
@@ -938,13 +962,20 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_consta
     for (int i = 0; i < TM_COUNT; ++i) c.tacc[i] = 0;
     const long long t_kernel0 = clock64();
 #endif
-    c.args = &args;
-    c.pending = c.issued = c.parity = c.qbits = c.qlen = 0;
-    c.p_tile = blockIdx.x;
-    c.p_t = 0;
-    c.p_si = 0;
-    c.p_ch = 0;
-    if (tid == 0) refill(c);
+    c.subs = s_sub;
+    c.parity = 0;
+    c.cons_count = 0;
+    c.s_cons = &s_cons;
+    c.sched = s_sched;
+    c.sched_len = s_sched_len;
+    c.p_idx = 0;
+    c.p_seq = 0;
+    {
+      const int my_tiles = blockIdx.x < args.n_tiles ? (args.n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+      c.p_left = my_tiles * args.t_loop * s_sched_len;
+    }
+    c.occ[0] = c.occ[1] = c.occ[2] = -1;
+    if (tid == FETCH_THREAD) refill(c);
     uint8_t* meta = smem + OFF_META;
     const EnvMap& map = args.map;
     const int NM = map.tokens_per_env;
@@ -1031,7 +1062,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_consta
         tc_fence_after();
         const int n_items = s_items;
         for (int si = 0; si < args.n_sub; ++si) {
-          const SubLayer& s = args.sub[si];
+          const SubLayer& s = s_sub[si];
           if (s.type == SUB_SPATIAL) run_spatial<MAXKB>(c, s, n_items, valid);
           else run_temporal(c, s, rs, is_field, boundary, args.has_fields != 0, t == 0 ? s.hid_in : s.hid_out);
         }
@@ -1050,9 +1081,11 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_consta
       }
     }
 #ifdef BNB_TIMING
-  if (tid == 64) {
+  if (tid == 64 || tid == 0) {
     c.tacc[TM_TOTAL] = clock64() - t_kernel0;
-    for (int i = 0; i < TM_COUNT; ++i) reinterpret_cast<long long*>(args.status)[32 + blockIdx.x * TM_COUNT + i] = c.tacc[i];
+    for (int i = 0; i < TM_COUNT; ++i)
+      if (tid == 64 ? i < TM_FULL_WAIT : i >= TM_FULL_WAIT)
+        reinterpret_cast<long long*>(args.status)[32 + blockIdx.x * TM_COUNT + i] = c.tacc[i];
   }
 #endif
   }
