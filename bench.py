@@ -38,6 +38,10 @@ METRIC = "policy-step entity tokens/sec per B200 (attn+RG-LRU), % of HBM rooflin
 UNIT = "entity_tokens/s"
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
+# DRAM bytes per entity token of the fused C2 step, from one ncu capture of k_trunk_tiles on the
+# half-size case (dram__bytes_read.sum + dram__bytes_write.sum = 375 034 112 B for 49 152 tokens);
+# traffic grows in proportion to the tokens, so a full launch is this times its tokens.
+NCU_C2_DRAM_BYTES_PER_TOKEN = 375034112 / 49152
 
 
 def measured_peaks() -> tuple[float, float, str]:
@@ -327,8 +331,9 @@ def run_ours(args) -> None:
                     "note": "x and alive from pinned host memory, y back to pinned host memory, hidden state carried on the device"},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
-                         "traffic": None, "of": src, "algorithmic_bytes_per_step": alg_bytes,
-                         "kernel": "whole trunk step (all launches of one step)", "kernel_ms": kernel_ms},
+                         "traffic": (NCU_C2_DRAM_BYTES_PER_TOKEN * tokens if args.workload == "C2" and launches == args.steps else None),
+                         "of": src, "algorithmic_bytes_per_step": alg_bytes,
+                         "kernel": "k_trunk_tiles (one launch = one trunk step)" if launches == args.steps else "whole trunk step (all launches of one step)", "kernel_ms": kernel_ms},
             "tensor": {"achieved": alg_flops / (kernel_ms * 1e-3) / 1e12, "peak": tflops, "unit": "TFLOP/s",
                        "frac": alg_flops / (kernel_ms * 1e-3) / 1e12 / tflops, "of": src,
                        "algorithmic_flops_per_step": alg_flops},
