@@ -61,7 +61,10 @@ constexpr uint32_t TMEM_COLS = 256;
 constexpr uint32_t COL_RESID = 0;
 constexpr uint32_t COL_ACC = 128;
 
-enum : int { SUB_SPATIAL = 0, SUB_TEMPORAL = 1 };
+// SUB_SPATIAL_PRE / _POST split a spatial sublayer around a separate attention kernel
+// (environments larger than one tile): PRE = norm1 + QKV to global scratch, POST = attention
+// output from scratch + out_proj + norm2 + GatedMLP.
+enum : int { SUB_SPATIAL = 0, SUB_TEMPORAL = 1, SUB_SPATIAL_PRE = 2, SUB_SPATIAL_POST = 3 };
 enum : int { ST_TIMEOUT_FULL = 101, ST_TIMEOUT_EMPTY = 102, ST_TIMEOUT_ACC = 103 };
 
 struct SubLayer {
@@ -76,6 +79,8 @@ struct SubLayer {
   const float* decay_log2;   // 8 * log2(sigmoid(log_lambda)), written by the pack kernel
   const float* hid_in;
   float* hid_out;
+  __nv_bfloat16* qkv_out;        // PRE: (rows, 384) q|k|v, head-major inside each third
+  const __nv_bfloat16* o_in;     // POST: (rows, 128) attention output
 };
 
 struct TrunkArgs {
@@ -92,6 +97,7 @@ struct TrunkArgs {
   int envs_per_tile;
   int env_tiles;      // tiles per group
   int has_fields;
+  int flat_rows;      // 1: tiles are plain 128-row slices of the token rows (no attention inside)
   const int* tile_env_begin;  // ragged batches: first environment of each tile (+ end), else null
   int* status;
   SubLayer sub[MAX_SUBLAYERS];
@@ -359,8 +365,18 @@ __device__ __forceinline__ uint32_t slot_addr(const Ctx& c, uint32_t slot) {
   return slot < 2 ? c.sRing + slot * CHUNK_BYTES : c.sStage;
 }
 __device__ __forceinline__ uint32_t chunk_slot(int type, int ch) {
-  const int first_ffn = type == SUB_SPATIAL ? 10 : 12;
-  return ch < first_ffn ? (uint32_t)(ch & 1) : (uint32_t)((ch - first_ffn) % 3);
+  if (type == SUB_TEMPORAL) return ch < 12 ? (uint32_t)(ch & 1) : (uint32_t)((ch - 12) % 3);
+  if (ch >= 10) return (uint32_t)((ch - 10) % 3);
+  if (type == SUB_SPATIAL) return (uint32_t)(ch & 1);
+  if (type == SUB_SPATIAL_PRE) return (uint32_t)((ch < 5 ? ch : ch - 1) & 1);  // q|k|v chunks only: K atom 0 -> slot 0
+  return ch == 4 ? 0u : 1u;                                                    // POST: the two out_proj chunks
+}
+// Does a sublayer of `type` consume chunk `ch` of its weight image?
+__device__ __forceinline__ bool chunk_used(int type, int ch, bool has_fields) {
+  if (type == SUB_TEMPORAL) return has_fields || (ch != 8 && ch != 9);
+  if (type == SUB_SPATIAL_PRE) return ch < 10 && ch != 4 && ch != 9;
+  if (type == SUB_SPATIAL_POST) return ch == 4 || ch >= 9;
+  return true;
 }
 
 // Fetching thread: bring the next chunks of the stream into every slot whose previous
@@ -669,6 +685,59 @@ __device__ __forceinline__ void run_spatial(Ctx& c, const SubLayer& s, int n_ite
   ffn(c);
 }
 
+// Spatial sublayer, first part, for environments that span several tiles: norm1 and the
+// q|k|v projection of every head, written as bf16 to global scratch for the attention kernel.
+__device__ __forceinline__ void run_spatial_pre(Ctx& c, const SubLayer& s, size_t grow, bool row_valid) {
+  norm_to_A(c, s.g1);
+  for (int hd = 0; hd < HEADS; ++hd) {
+    round_begin(c);
+    if (threadIdx.x == 0) {
+      issue_chunk(c, c.sA, 96, COL_ACC, 0, 0);
+      issue_chunk(c, c.sA + CHUNK_BYTES, 96, COL_ACC, 1, 1);
+    }
+    round_end(c);
+    uint32_t v[32], w[16];
+    tmem_ld32_nowait(c.lane_addr + COL_ACC + c.half * 48, v);
+    tmem_ld16_nowait(c.lane_addr + COL_ACC + c.half * 48 + 32, w);
+    tmem_wait_ld();
+    if (row_valid) {
+      __nv_bfloat16* dst = s.qkv_out + grow * (3 * D);
+#pragma unroll
+      for (int q = 0; q < 6; ++q) {
+        const uint32_t* src = q < 4 ? &v[q * 8] : &w[(q - 4) * 8];
+        const int j = c.half * 48 + q * 8;                 // accumulator column: q (0-31), k (32-63), v (64-95)
+        const int col = (j >> 5) * D + hd * DH + (j & 31);
+        *reinterpret_cast<uint4*>(dst + col) =
+            make_uint4(pack_bf16(__uint_as_float(src[0]), __uint_as_float(src[1])), pack_bf16(__uint_as_float(src[2]), __uint_as_float(src[3])),
+                       pack_bf16(__uint_as_float(src[4]), __uint_as_float(src[5])), pack_bf16(__uint_as_float(src[6]), __uint_as_float(src[7])));
+      }
+    }
+  }
+}
+
+// Spatial sublayer, second part: attention output from global scratch -> out_proj into the
+// residual -> norm2 -> GatedMLP.
+__device__ __forceinline__ void run_spatial_post(Ctx& c, const SubLayer& s, size_t grow, bool row_valid) {
+  {
+    const uint4* src = reinterpret_cast<const uint4*>(s.o_in + grow * D + c.half * 64);
+    uint8_t* dst = c.smem + OFF_A + c.half * CHUNK_BYTES;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      uint4 o = make_uint4(0u, 0u, 0u, 0u);
+      if (row_valid) o = src[q];
+      *reinterpret_cast<uint4*>(dst + swz(c.row, q)) = o;
+    }
+  }
+  round_begin(c);
+  if (threadIdx.x == 0) {
+    issue_chunk(c, c.sA, 128, COL_RESID, 1, 0);
+    issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_RESID, 1, 1);
+  }
+  round_end(c);
+  norm_to_A(c, s.g2);
+  ffn(c);
+}
+
 struct RowState {
   int hrow;        // row of the packed hidden state, -1 for field / invalid rows
   int lag_ok;      // stored conv lags still inside the current episode (0..3)
@@ -908,9 +977,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_consta
     int n = 0;
     for (int si = 0; si < args.n_sub; ++si) {
       const int type = args.sub[si].type;
-      const int n_chunks = type == SUB_SPATIAL ? N_SPATIAL_CHUNKS : N_TEMPORAL_CHUNKS;
+      const int n_chunks = type == SUB_TEMPORAL ? N_TEMPORAL_CHUNKS : N_SPATIAL_CHUNKS;
       for (int ch = 0; ch < n_chunks; ++ch) {
-        if (type == SUB_TEMPORAL && !args.has_fields && (ch == 8 || ch == 9)) continue;  // no field_sub round
+        if (!chunk_used(type, ch, args.has_fields != 0)) continue;
         s_sched[n++] = (uint16_t)((ch << 6) | (si << 2) | chunk_slot(type, ch));
       }
     }
@@ -988,7 +1057,18 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_consta
       int env, tok, env_first, env_n, env_ships;
       size_t grow = 0;
       int hrow_if_ship;
-      if (args.tile_env_begin) {
+      if (args.flat_rows) {
+        // plain slices of the token rows; the environment of a row is looked up
+        const int r = eb * TILE + row;
+        valid = r < map.total_tokens;
+        env = valid ? map.env_of_token(r) : 0;
+        env_first = 0;
+        env_n = 1;
+        tok = valid ? r - map.env_tok_begin(env) : 0;
+        env_ships = valid ? map.env_ship_count(env) : 0;
+        grow = (size_t)grp * map.total_tokens + (size_t)r;
+        hrow_if_ship = map.env_ship_begin(env) + tok;
+      } else if (args.tile_env_begin) {
         // ragged: the tile holds environments [e_lo, e_hi), rows in token order
         const int e_lo = args.tile_env_begin[eb], e_hi = args.tile_env_begin[eb + 1];
         const int base = map.tok_off[e_lo];
@@ -1064,6 +1144,8 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_consta
         for (int si = 0; si < args.n_sub; ++si) {
           const SubLayer& s = s_sub[si];
           if (s.type == SUB_SPATIAL) run_spatial<MAXKB>(c, s, n_items, valid);
+          else if (s.type == SUB_SPATIAL_PRE) run_spatial_pre(c, s, trow, valid);
+          else if (s.type == SUB_SPATIAL_POST) run_spatial_post(c, s, trow, valid);
           else run_temporal(c, s, rs, is_field, boundary, args.has_fields != 0, t == 0 ? s.hid_in : s.hid_out);
         }
         // y <- residual
@@ -1097,14 +1179,145 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_consta
   }
 }
 
+// ------------------------------------------------------------------ attention for large environments
+//
+// One CTA per (environment, head): q, k, v of that head are staged from the bf16 scratch the
+// PRE phase wrote, then each warp takes blocks of 16 query rows and walks the keys in blocks of
+// 16 with a running maximum (mma.sync, fp32 softmax).  Dead keys score kMaskedScore, so their
+// weight is exactly 0 unless no key of the environment is alive, in which case every key gets
+// the same weight (models/yemong/attention.py:101-112 of the reference).
+constexpr int FLASH_STRIDE = 80;  // bytes per staged row of one head (32 bf16 + pad)
+
+__global__ void __launch_bounds__(128) k_attention_flash(const __nv_bfloat16* __restrict__ qkv, const uint8_t* __restrict__ alive,
+                                                         __nv_bfloat16* __restrict__ o, EnvMap map, int n_groups) {
+  extern __shared__ __align__(16) uint8_t fs[];
+  const int env_g = blockIdx.x, hd = blockIdx.y;
+  const int grp = env_g / map.n_envs, e = env_g - grp * map.n_envs;
+  const size_t tok0 = (size_t)grp * map.total_tokens + map.env_tok_begin(e);
+  const int n = map.env_tok_count(e);
+  uint8_t* Qs = fs;
+  uint8_t* Ks = Qs + (size_t)n * FLASH_STRIDE;
+  uint8_t* Vs = Ks + (size_t)n * FLASH_STRIDE;
+  uint8_t* live = Vs + (size_t)n * FLASH_STRIDE;
+  for (int i = threadIdx.x; i < n * 12; i += blockDim.x) {
+    const int r = i / 12, part = (i % 12) >> 2, q = i & 3;
+    const uint4 v = *reinterpret_cast<const uint4*>(qkv + (tok0 + r) * (3 * D) + part * D + hd * DH + q * 8);
+    *reinterpret_cast<uint4*>(fs + ((size_t)part * n + r) * FLASH_STRIDE + q * 16) = v;
+  }
+  for (int i = threadIdx.x; i < n; i += blockDim.x) live[i] = alive ? alive[tok0 + i] : (uint8_t)1;
+  __syncthreads();
+  const uint32_t sQ = smem_u32(Qs), sK = smem_u32(Ks), sV = smem_u32(Vs);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const float scale = 0.17677669529663687f;
+  const int last = n - 1;
+  const int nkb = (n + 15) >> 4;
+  for (int qb = warp; qb * 16 < n; qb += 4) {
+    uint32_t qa[2][4];
+    {
+      const int row = min(qb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, last);
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks)
+        ldsm_x4(sQ + row * FLASH_STRIDE + (ks * 16 + (lane >> 4) * 8) * 2, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3]);
+    }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    float acc[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
+    for (int kb = 0; kb < nkb; ++kb) {
+      float sc[2][4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sc[nt][i] = 0.f;
+      const int krow = min(kb * 16 + (lane >> 4) * 8 + (lane & 7), last);
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(sK + krow * FLASH_STRIDE + (ks * 16 + ((lane >> 3) & 1) * 8) * 2, b0, b1, b2, b3);
+        mma_bf16(sc[0], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+        mma_bf16(sc[1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b2, b3);
+      }
+      float bm0 = -INFINITY, bm1 = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int j = kb * 16 + nt * 8 + 2 * t + i;
+          const bool valid = j < n;
+          const bool lv = valid && live[j];
+          const float a = valid ? (lv ? sc[nt][i] * scale : kMaskedScore) : -INFINITY;
+          const float b = valid ? (lv ? sc[nt][2 + i] * scale : kMaskedScore) : -INFINITY;
+          sc[nt][i] = a;
+          sc[nt][2 + i] = b;
+          bm0 = fmaxf(bm0, a);
+          bm1 = fmaxf(bm1, b);
+        }
+      bm0 = fmaxf(bm0, __shfl_xor_sync(0xffffffffu, bm0, 1));
+      bm0 = fmaxf(bm0, __shfl_xor_sync(0xffffffffu, bm0, 2));
+      bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, 1));
+      bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, 2));
+      const float n0 = fmaxf(m0, bm0), n1 = fmaxf(m1, bm1);   // finite: every block holds a valid key
+      const float c0 = __expf(m0 - n0), c1 = __expf(m1 - n1); // exp(-inf) = 0 on the first block
+      m0 = n0;
+      m1 = n1;
+      l0 *= c0;
+      l1 *= c1;
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        acc[nt][0] *= c0; acc[nt][1] *= c0;
+        acc[nt][2] *= c1; acc[nt][3] *= c1;
+      }
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const float a = __expf(sc[nt][i] - m0), b = __expf(sc[nt][2 + i] - m1);
+          sc[nt][i] = a;
+          sc[nt][2 + i] = b;
+          l0 += a;
+          l1 += b;
+        }
+      const uint32_t a0 = pack_bf16(sc[0][0], sc[0][1]), a1 = pack_bf16(sc[0][2], sc[0][3]);
+      const uint32_t a2 = pack_bf16(sc[1][0], sc[1][1]), a3 = pack_bf16(sc[1][2], sc[1][3]);
+      const int vrow = min(kb * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), last);
+#pragma unroll
+      for (int np = 0; np < 2; ++np) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(sV + vrow * FLASH_STRIDE + ((np * 2 + (lane >> 4)) * 8) * 2, b0, b1, b2, b3);
+        mma_bf16(acc[np * 2], a0, a1, a2, a3, b0, b1);
+        mma_bf16(acc[np * 2 + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float i0 = 1.0f / l0, i1 = 1.0f / l1;
+    const int q0 = qb * 16 + g, q1 = q0 + 8;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const int col = hd * DH + nt * 8 + 2 * t;
+      if (q0 <= last) *reinterpret_cast<uint32_t*>(o + (tok0 + q0) * D + col) = pack_bf16(acc[nt][0] * i0, acc[nt][1] * i0);
+      if (q1 <= last) *reinterpret_cast<uint32_t*>(o + (tok0 + q1) * D + col) = pack_bf16(acc[nt][2] * i1, acc[nt][3] * i1);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ host side
 
+constexpr int MAX_ENV_TOKENS = 512;  // split-attention path: q, k, v of one head of one environment in shared memory
+
 bool supported(int d_model, int n_heads, int max_tokens_per_env) {
-  return d_model == D && n_heads == HEADS && max_tokens_per_env >= 1 && max_tokens_per_env <= TILE;
+  return d_model == D && n_heads == HEADS && max_tokens_per_env >= 1 && max_tokens_per_env <= MAX_ENV_TOKENS;
 }
+// Environments that fit one 128-row tile run fully fused; larger ones take the split path.
+static bool fits_tile(const BnbBatch& b) { return b.max_tokens_per_env <= TILE; }
 bool supported_batch(int d_model, int n_heads, const BnbBatch& b) {
   if (!supported(d_model, n_heads, b.max_tokens_per_env)) return false;
-  if (b.tok_off) return b.tile_env_begin != nullptr && b.n_tiles > 0;
+  if (b.tok_off) return fits_tile(b) && b.tile_env_begin != nullptr && b.n_tiles > 0;
   return b.tokens_per_env >= 1;
 }
 
@@ -1127,7 +1340,11 @@ int plan_tiles(const int32_t* tok_off, int n_envs, int32_t* tile_env_begin, int 
   return BNB_OK;
 }
 
-size_t scratch_bytes(int, const BnbBatch&, int) { return 65536; }
+size_t scratch_bytes(int, const BnbBatch& b, int T) {
+  size_t bytes = 65536;  // status word (and cycle accounting)
+  if (!fits_tile(b)) bytes += (size_t)T * b.total_tokens * 4 * D * sizeof(__nv_bfloat16);  // q|k|v + attention output
+  return bytes;
+}
 size_t packed_spatial_bytes(int d_model) { return d_model == D ? (size_t)N_SPATIAL_CHUNKS * CHUNK_BYTES : 0; }
 size_t packed_temporal_bytes(int d_model) { return d_model == D ? (size_t)N_TEMPORAL_CHUNKS * CHUNK_BYTES + 1024 : 0; }
 
@@ -1146,7 +1363,11 @@ int pack_temporal(const BnbTemporalWeights& w, int d_model, void* packed, cudaSt
 
 static int launch(TrunkArgs& a, const BnbBatch& b, cudaStream_t st) {
   a.map = make_env_map(b);
-  if (b.tok_off) {
+  if (a.flat_rows) {
+    a.tile_env_begin = nullptr;
+    a.envs_per_tile = 0;
+    a.env_tiles = (b.total_tokens + TILE - 1) / TILE;
+  } else if (b.tok_off) {
     a.tile_env_begin = b.tile_env_begin;
     a.envs_per_tile = 0;
     a.env_tiles = b.n_tiles;
@@ -1169,7 +1390,7 @@ static int launch(TrunkArgs& a, const BnbBatch& b, cudaStream_t st) {
   }
   int grid = a.n_tiles < 2 * 148 ? a.n_tiles : 2 * 148;
   count_launch();
-  if (b.max_tokens_per_env <= 64) k_trunk_tiles<4><<<grid, NTHREADS, SMEM_BYTES, st>>>(a);
+  if (b.max_tokens_per_env <= 64 || a.flat_rows) k_trunk_tiles<4><<<grid, NTHREADS, SMEM_BYTES, st>>>(a);
   else k_trunk_tiles<8><<<grid, NTHREADS, SMEM_BYTES, st>>>(a);
   return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
 }
@@ -1204,29 +1425,139 @@ static void fill_temporal(SubLayer& s, const BnbTemporalWeights& w, const float*
   s.hid_out = hout;
 }
 
+static int launch_attention(const __nv_bfloat16* qkv, const uint8_t* alive, __nv_bfloat16* o, const BnbBatch& b,
+                            int n_groups, cudaStream_t st) {
+  static bool configured[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BNB_ERR_NO_DEVICE;
+  const int max_smem = MAX_ENV_TOKENS * (3 * FLASH_STRIDE + 1) + 16;
+  if (!configured[dev]) {
+    if (cudaFuncSetAttribute(k_attention_flash, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess)
+      return BNB_ERR_LAUNCH;
+    configured[dev] = true;
+  }
+  const size_t smem = (size_t)b.max_tokens_per_env * (3 * FLASH_STRIDE + 1) + 16;
+  dim3 grid(b.n_envs * n_groups, HEADS);
+  count_launch();
+  k_attention_flash<<<grid, 128, smem, st>>>(qkv, alive, o, make_env_map(b), n_groups);
+  return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
+}
+
+// Accumulates sublayers into tile-kernel launches.  In split mode (environments larger than
+// one tile) a spatial sublayer becomes PRE | attention kernel | POST, and the tile kernel
+// walks plain 128-row slices.
+struct Plan {
+  const BnbBatch& b;
+  cudaStream_t st;
+  int* status;
+  bool split;
+  const uint8_t* alive;
+  const uint8_t* done;
+  const uint8_t* reset_env;
+  const float* cur;      // where the residual stream currently lives
+  float* y;
+  __nv_bfloat16* qkv;
+  __nv_bfloat16* o;
+  int n_groups, t_loop;  // geometry of the pending program
+  TrunkArgs a;
+  int n;
+
+  void begin(int groups, int tl) {
+    a = TrunkArgs{};
+    n = 0;
+    n_groups = groups;
+    t_loop = tl;
+  }
+  int flush() {
+    if (n == 0) return BNB_OK;
+    a.status = status;
+    a.alive = split ? nullptr : alive;
+    a.done = done;
+    a.reset_env = reset_env;
+    a.n_groups = n_groups;
+    a.t_loop = t_loop;
+    a.n_sub = n;
+    a.flat_rows = split ? 1 : 0;
+    a.x = cur;
+    a.y = y;
+    int rc = launch(a, b, st);
+    cur = y;
+    const int g = n_groups, tl = t_loop;
+    begin(g, tl);
+    return rc;
+  }
+  int ensure(int groups, int tl) {
+    if (n > 0 && (groups != n_groups || tl != t_loop)) {
+      int rc = flush();
+      if (rc) return rc;
+    }
+    n_groups = groups;
+    t_loop = tl;
+    return BNB_OK;
+  }
+  int add_spatial(const BnbSpatialWeights& w, int groups) {
+    int rc = ensure(groups, 1);
+    if (rc) return rc;
+    if (n == MAX_SUBLAYERS && (rc = flush())) return rc;
+    fill_spatial(a.sub[n], w);
+    if (!split) { ++n; return BNB_OK; }
+    a.sub[n].type = SUB_SPATIAL_PRE;
+    a.sub[n].qkv_out = qkv;
+    ++n;
+    if ((rc = flush())) return rc;
+    if ((rc = launch_attention(qkv, alive, o, b, groups, st))) return rc;
+    fill_spatial(a.sub[n], w);
+    a.sub[n].type = SUB_SPATIAL_POST;
+    a.sub[n].o_in = o;
+    ++n;
+    return BNB_OK;
+  }
+  int add_temporal(const BnbTemporalWeights& w, const float* hin, float* hout, int tl) {
+    int rc = ensure(tl > 1 ? 1 : n_groups, tl);
+    if (rc) return rc;
+    if (tl > 1 && n > 0 && (rc = flush())) return rc;   // a time walk runs alone
+    if (n == MAX_SUBLAYERS && (rc = flush())) return rc;
+    fill_temporal(a.sub[n++], w, hin, hout);
+    if (tl > 1) return flush();
+    return BNB_OK;
+  }
+};
+
+static int make_plan(Plan& p, void* scratch, size_t scratch_bytes, int T) {
+  int rc = prepare_status(scratch, scratch_bytes, p.st, &p.status);
+  if (rc) return rc;
+  p.split = !fits_tile(p.b);
+  p.qkv = nullptr;
+  p.o = nullptr;
+  if (p.split) {
+    const size_t rows = (size_t)T * p.b.total_tokens;
+    if (scratch_bytes < 65536 + rows * 4 * D * sizeof(__nv_bfloat16)) return BNB_ERR_SCRATCH_TOO_SMALL;
+    p.qkv = reinterpret_cast<__nv_bfloat16*>(static_cast<uint8_t*>(scratch) + 65536);
+    p.o = p.qkv + rows * 3 * D;
+  }
+  p.begin(1, 1);
+  return BNB_OK;
+}
+
 int spatial_block(const BnbSpatialWeights& w, int d_model, int n_heads, const float* x, const uint8_t* alive, float* y,
                   const BnbBatch& b, int n_groups, void* scratch, size_t scratch_bytes, cudaStream_t st) {
   if (!supported_batch(d_model, n_heads, b) || !w.packed) return BNB_ERR_UNSUPPORTED_DIMS;
-  TrunkArgs a{};
-  int rc = prepare_status(scratch, scratch_bytes, st, &a.status);
+  Plan p{b, st, nullptr, false, alive, nullptr, nullptr, x, y};
+  int rc = make_plan(p, scratch, scratch_bytes, n_groups);
   if (rc) return rc;
-  a.x = x; a.y = y; a.alive = alive;
-  a.n_groups = n_groups; a.t_loop = 1; a.n_sub = 1;
-  fill_spatial(a.sub[0], w);
-  return launch(a, b, st);
+  if ((rc = p.add_spatial(w, n_groups))) return rc;
+  return p.flush();
 }
 
 int temporal_block(const BnbTemporalWeights& w, int d_model, const float* x, float* y, const float* hidden_in,
                    float* hidden_out, const uint8_t* done, const uint8_t* reset_env, const BnbBatch& b, int T,
                    void* scratch, size_t scratch_bytes, cudaStream_t st) {
   if (!supported_batch(d_model, HEADS, b) || !w.packed) return BNB_ERR_UNSUPPORTED_DIMS;
-  TrunkArgs a{};
-  int rc = prepare_status(scratch, scratch_bytes, st, &a.status);
+  Plan p{b, st, nullptr, false, nullptr, done, reset_env, x, y};
+  int rc = make_plan(p, scratch, scratch_bytes, T);
   if (rc) return rc;
-  a.x = x; a.y = y; a.done = done; a.reset_env = reset_env;
-  a.n_groups = 1; a.t_loop = T; a.n_sub = 1;
-  fill_temporal(a.sub[0], w, hidden_in, hidden_out);
-  return launch(a, b, st);
+  if ((rc = p.add_temporal(w, hidden_in, hidden_out, T))) return rc;
+  return p.flush();
 }
 
 int trunk(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal, int n_blocks, int n_spatial,
@@ -1236,69 +1567,23 @@ int trunk(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal, 
   if (!supported_batch(d_model, n_heads, b)) return BNB_ERR_UNSUPPORTED_DIMS;
   for (int i = 0; i < n_blocks * n_spatial; ++i) if (!spatial[i].packed) return BNB_ERR_UNSUPPORTED_DIMS;
   for (int i = 0; i < n_blocks * n_temporal; ++i) if (!temporal[i].packed) return BNB_ERR_UNSUPPORTED_DIMS;
-  int* status = nullptr;
-  int rc = prepare_status(scratch, scratch_bytes, st, &status);
+  // a time walk carries its state through hidden_out between timesteps
+  if (T > 1 && n_blocks * n_temporal > 0 && b.total_ships > 0 && !hidden_out) return BNB_ERR_NULL_POINTER;
+  Plan p{b, st, nullptr, false, alive, done, reset_env, x, y};
+  int rc = make_plan(p, scratch, scratch_bytes, T);
   if (rc) return rc;
   const size_t slot_stride = (size_t)b.total_ships * 4 * D;
-  const float* cur = x;
-  if (T == 1) {
-    // one launch per group of at most MAX_SUBLAYERS sublayers, the tile resident throughout
-    TrunkArgs a{};
-    a.status = status; a.alive = alive; a.reset_env = reset_env; a.n_groups = 1; a.t_loop = 1;
-    int n = 0;
-    auto flush = [&]() -> int {
-      if (n == 0) return BNB_OK;
-      a.x = cur; a.y = y; a.n_sub = n;
-      int r = launch(a, b, st);
-      cur = y; n = 0;
-      return r;
-    };
-    for (int i = 0; i < n_blocks; ++i) {
-      for (int j = 0; j < n_spatial; ++j) {
-        fill_spatial(a.sub[n++], spatial[i * n_spatial + j]);
-        if (n == MAX_SUBLAYERS && (rc = flush())) return rc;
-      }
-      for (int j = 0; j < n_temporal; ++j) {
-        int slot = i * n_temporal + j;
-        fill_temporal(a.sub[n++], temporal[slot], hidden_in + slot * slot_stride, hidden_out + slot * slot_stride);
-        if (n == MAX_SUBLAYERS && (rc = flush())) return rc;
-      }
-    }
-    if ((rc = flush())) return rc;
-    if (cur == x && y != x) {
-      if (cudaMemcpyAsync(y, x, (size_t)b.total_tokens * D * sizeof(float), cudaMemcpyDeviceToDevice, st) != cudaSuccess)
-        return BNB_ERR_LAUNCH;
-    }
-    return BNB_OK;
-  }
-  // sequence: spatial sublayers over T*B environments at once, temporal sublayers walking t
   for (int i = 0; i < n_blocks; ++i) {
-    if (n_spatial > 0) {
-      int done_s = 0;
-      while (done_s < n_spatial) {
-        TrunkArgs a{};
-        a.status = status; a.alive = alive; a.n_groups = T; a.t_loop = 1;
-        int n = 0;
-        while (done_s < n_spatial && n < MAX_SUBLAYERS) fill_spatial(a.sub[n++], spatial[i * n_spatial + done_s++]);
-        a.x = cur; a.y = y; a.n_sub = n;
-        if ((rc = launch(a, b, st))) return rc;
-        cur = y;
-      }
-    }
+    for (int j = 0; j < n_spatial; ++j)
+      if ((rc = p.add_spatial(spatial[i * n_spatial + j], T))) return rc;
     for (int j = 0; j < n_temporal; ++j) {
-      int slot = i * n_temporal + j;
-      TrunkArgs a{};
-      a.status = status; a.done = done; a.n_groups = 1; a.t_loop = T; a.n_sub = 1;
-      // the final state is optional for a sequence; without it the walk still needs a place
-      // to carry the state between timesteps, so the caller's output buffer is required
-      if (!hidden_out) return BNB_ERR_NULL_POINTER;
-      fill_temporal(a.sub[0], temporal[slot], hidden_in + slot * slot_stride, hidden_out + slot * slot_stride);
-      a.x = cur; a.y = y;
-      if ((rc = launch(a, b, st))) return rc;
-      cur = y;
+      const int slot = i * n_temporal + j;
+      if ((rc = p.add_temporal(temporal[slot], hidden_in ? hidden_in + slot * slot_stride : nullptr,
+                               hidden_out ? hidden_out + slot * slot_stride : nullptr, T))) return rc;
     }
   }
-  if (cur == x && y != x) {
+  if ((rc = p.flush())) return rc;
+  if (p.cur == x && y != x) {
     if (cudaMemcpyAsync(y, x, (size_t)T * b.total_tokens * D * sizeof(float), cudaMemcpyDeviceToDevice, st) != cudaSuccess)
       return BNB_ERR_LAUNCH;
   }

@@ -117,14 +117,53 @@ def test_weights_are_repacked_after_an_update():
     assert norm_err(y1.cpu(), ys.cpu()) < 1e-2
 
 
-def test_tensor_engine_refuses_what_it_is_not_built_for():
+@pytest.mark.parametrize("n_envs,teams", [(3, (64, 88)), (2, (100, 100)), (1, (65, 64)), (2, (250, 262))])
+def test_large_environments_split_attention_path(n_envs, teams):
+    """Environments larger than one 128-row tile: q|k|v through scratch and a separate
+    attention kernel with a running-maximum softmax over key blocks."""
     from boost_and_broadside_b200 import workloads as W
 
     _capi, SIMT, TENSOR = _engines()
-    w = W.c3(n_envs=2)  # 152 tokens per environment: more than one tile
+    w = W.c3(n_envs=n_envs, seed=51, teams=teams)
+    trunk = build_trunk([128, 4, 2, 2, 1, 1])
+    ref_y, ref_h = O.trunk_step(w.x, w.alive, w.hidden, trunk_params(trunk), 4, "bf16")
+    trunk = trunk.to(DEV)
+    with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
+        y, nh = trunk.step(w.x.to(DEV), w.alive.to(DEV), w.hidden.to(DEV), engine=TENSOR)
+    _status_ok()
+    assert_close(y, ref_y, "bf16", "large env y")
+    assert_close(nh, ref_h, "bf16", "large env hidden")
+
+
+def test_large_environment_sequence_and_all_dead():
+    from boost_and_broadside_b200 import workloads as W
+
+    _capi, SIMT, TENSOR = _engines()
+    gen = torch.Generator().manual_seed(61)
+    T, B, N = 3, 2, 152
+    x = torch.randn(T, B, N, 128, generator=gen)
+    alive = torch.rand(T, B, N, generator=gen) < 0.6
+    alive[1, 0] = False  # an environment without a live key at one timestep
+    hidden = torch.randn(2, B * N, 512, generator=gen) * 0.5
+    done = torch.rand(T, B, generator=gen) < 0.4
+    trunk = build_trunk([128, 4, 2, 2, 1, 1])
+    ref_y, ref_h = O.trunk_sequence(x, alive, hidden, done, trunk_params(trunk), 4, "bf16")
+    trunk = trunk.to(DEV)
+    with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
+        y, nh = trunk.sequence(x.to(DEV), alive.to(DEV), hidden.to(DEV), done.to(DEV), engine=TENSOR)
+    _status_ok()
+    assert_close(y, ref_y, "bf16", "large env sequence y")
+    assert_close(nh, ref_h, "bf16", "large env sequence hidden")
+
+
+def test_tensor_engine_refuses_what_it_is_not_built_for():
+    _capi, SIMT, TENSOR = _engines()
+    gen = torch.Generator().manual_seed(71)
+    x = torch.randn(1, 600, 128, generator=gen).to(DEV)   # more tokens per environment than the split path stages
+    hidden = torch.zeros(2, 600, 512, device=DEV)
     trunk = build_trunk([128, 4, 2, 2, 1, 1]).to(DEV)
     with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
         with pytest.raises(ValueError):
-            trunk.step(w.x.to(DEV), w.alive.to(DEV), w.hidden.to(DEV), engine=TENSOR)
-        y, _ = trunk.step(w.x.to(DEV), w.alive.to(DEV), w.hidden.to(DEV))  # AUTO falls back to SIMT
+            trunk.step(x, None, hidden, engine=TENSOR)
+        y, _ = trunk.step(x, None, hidden)  # AUTO falls back to SIMT
     assert torch.isfinite(y).all()
