@@ -379,24 +379,44 @@ __device__ __forceinline__ bool chunk_used(int type, int ch, bool has_fields) {
   return true;
 }
 
-// Fetching thread: bring the next chunks of the stream into every slot whose previous
-// chunk has been retired.  Called right after a wait on the accumulator barrier, when all
-// MMAs issued so far are complete, so a chunk with sequence number < *s_cons is retired.
+// Fetching warp: bring the next chunks of the stream into every slot whose previous chunk has
+// been retired.  Called right after the accumulator barrier, when all MMAs issued so far are
+// complete, so a chunk with sequence number < *s_cons is retired.  The whole warp runs the
+// bookkeeping (warp-uniform); lanes 0..2 each issue one of up to three copies.
 __device__ __forceinline__ void refill(Ctx& c) {
+  const int lane = threadIdx.x & 31;
   const int retired = *c.s_cons;
-  while (c.p_left > 0) {
-    const uint32_t e = c.sched[c.p_idx];
-    const uint32_t slot = e & 3u;
-    const int occ = slot == 0 ? c.occ[0] : (slot == 1 ? c.occ[1] : c.occ[2]);
-    if (occ >= retired) break;
+  // candidate of this lane: the lane-th next chunk of the schedule
+  int idx = c.p_idx + lane;
+  if (idx >= c.sched_len) idx -= c.sched_len;
+  if (idx >= c.sched_len) idx -= c.sched_len;
+  const bool in_range = lane < 3 && lane < c.p_left;
+  const uint32_t e = c.sched[in_range ? idx : 0];
+  const uint32_t slot = e & 3u;
+  const int occ = slot == 0 ? c.occ[0] : (slot == 1 ? c.occ[1] : c.occ[2]);
+  // a chunk may go out if its slot is free and no earlier chunk of this batch takes the same slot
+  const uint32_t s0 = __shfl_sync(0xffffffffu, slot, 0), s1 = __shfl_sync(0xffffffffu, slot, 1);
+  bool ok = in_range && occ < retired;
+  if (lane == 1 && slot == s0) ok = false;
+  if (lane == 2 && (slot == s0 || slot == s1)) ok = false;
+  const uint32_t okmask = __ballot_sync(0xffffffffu, ok);
+  const int n = (okmask & 1u) ? ((okmask & 2u) ? ((okmask & 4u) ? 3 : 2) : 1) : 0;  // leading run
+  if (lane < n) {
     const SubLayer& s = c.subs[(e >> 2) & 15u];
     mbar_expect_tx(c.bar_full[slot], CHUNK_BYTES);
     bulk_g2s(slot_addr(c, slot), s.packed + (size_t)(e >> 6) * CHUNK_BYTES, CHUNK_BYTES, c.bar_full[slot]);
-    if (slot == 0) c.occ[0] = c.p_seq; else if (slot == 1) c.occ[1] = c.p_seq; else c.occ[2] = c.p_seq;
-    ++c.p_seq;
-    --c.p_left;
-    if (++c.p_idx == c.sched_len) c.p_idx = 0;
   }
+#pragma unroll
+  for (int l = 0; l < 3; ++l) {
+    const uint32_t sl = __shfl_sync(0xffffffffu, slot, l);
+    if (l < n) {
+      if (sl == 0) c.occ[0] = c.p_seq + l; else if (sl == 1) c.occ[1] = c.p_seq + l; else c.occ[2] = c.p_seq + l;
+    }
+  }
+  c.p_seq += n;
+  c.p_left -= n;
+  c.p_idx += n;
+  if (c.p_idx >= c.sched_len) c.p_idx -= c.sched_len;
 }
 
 __device__ __forceinline__ void round_begin(Ctx& c) {
@@ -435,14 +455,20 @@ __device__ __forceinline__ void round_end(Ctx& c) {
     __threadfence_block();
     tc_commit(c.bar_acc);
   }
-  mbar_wait(c.bar_acc, c.acc_phase, c.status, c.aborted, ST_TIMEOUT_ACC);
+  // Warp 0 polls the mbarrier; everybody else sleeps on a hardware barrier instead of spending
+  // issue slots of the co-resident CTA on a spin loop.
+  if (threadIdx.x < 32) {
+    __syncwarp();
+    mbar_wait(c.bar_acc, c.acc_phase, c.status, c.aborted, ST_TIMEOUT_ACC);
+  }
   c.acc_phase ^= 1u;
-  if (threadIdx.x == FETCH_THREAD) {
+  asm volatile("bar.sync 2, 256;" ::: "memory");
+  if ((threadIdx.x >> 5) == FETCH_THREAD / 32) {
     T_BEGIN(c);
     refill(c);
     T_END(c, TM_REFILL);
   }
-  __syncwarp();  // the spin above may leave the warp diverged; tcgen05.ld/st need it converged
+  __syncwarp();
   tc_fence_after();
   T_END(c, TM_WAIT);
 }
@@ -813,38 +839,53 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
     }
     const int* row_hrow = reinterpret_cast<const int*>(c.smem + OFF_ROWINFO);
     const uint8_t* row_flags = c.smem + OFF_ROWINFO + 512;
-#pragma unroll 4
-    for (int r = warp; r < TILE; r += 8) {
-      const int hr = row_hrow[r];
-      if (hr < 0) continue;
-      const int flags = row_flags[r];
-      const int lag_ok = flags & 3;
-      const bool zero_in = (flags & 4) != 0;
-      const float* hi = hid_in + (size_t)hr * 4 * D + col;
-      float* ho = s.hid_out + (size_t)hr * 4 * D + col;
-      float4 t0 = make_float4(0.f, 0.f, 0.f, 0.f), t1 = t0, t2 = t0;
-      if (!zero_in) {
-        t0 = *reinterpret_cast<const float4*>(hi + D);
-        t1 = *reinterpret_cast<const float4*>(hi + 2 * D);
-        t2 = *reinterpret_cast<const float4*>(hi + 3 * D);
-      }
-      uint8_t* bp = c.smem + OFF_A + (lane >> 4) * CHUNK_BYTES + swz(r, (lane & 15) >> 1) + (lane & 1) * 8;
-      const uint2 bw = *reinterpret_cast<const uint2*>(bp);
-      const float b1[4] = {bf16_lo(bw.x), bf16_hi(bw.x), bf16_lo(bw.y), bf16_hi(bw.y)};
-      *reinterpret_cast<float4*>(ho + D) = t1;
-      *reinterpret_cast<float4*>(ho + 2 * D) = t2;
-      *reinterpret_cast<float4*>(ho + 3 * D) = make_float4(b1[0], b1[1], b1[2], b1[3]);
-      const float a0[4] = {t0.x, t0.y, t0.z, t0.w}, a1[4] = {t1.x, t1.y, t1.z, t1.w}, a2[4] = {t2.x, t2.y, t2.z, t2.w};
-      float u[4];
+    // Four rows at a time: all loads of the group are issued before any store, because the
+    // state may be updated in place and the compiler must otherwise keep loads behind stores.
+    for (int r0 = warp; r0 < TILE; r0 += 32) {
+      float4 t0[4], t1[4], t2[4];
+      uint2 bw[4];
+      int hr[4], lag[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float p0 = lag_ok >= 3 ? __fmul_rn(a0[i], cw[i][0]) : 0.f;
-        float p1 = lag_ok >= 2 ? __fmul_rn(a1[i], cw[i][1]) : 0.f;
-        float p2 = lag_ok >= 1 ? __fmul_rn(a2[i], cw[i][2]) : 0.f;
-        float p3 = __fmul_rn(b1[i], cw[i][3]);
-        u[i] = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(p0, p1), p2), p3), cb[i]);
+      for (int k = 0; k < 4; ++k) {
+        const int r = r0 + 8 * k;
+        hr[k] = row_hrow[r];
+        const int flags = row_flags[r];
+        lag[k] = flags & 3;
+        t0[k] = t1[k] = t2[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        bw[k] = make_uint2(0u, 0u);
+        if (hr[k] >= 0) {
+          if (!(flags & 4)) {
+            const float* hi = hid_in + (size_t)hr[k] * 4 * D + col;
+            t0[k] = *reinterpret_cast<const float4*>(hi + D);
+            t1[k] = *reinterpret_cast<const float4*>(hi + 2 * D);
+            t2[k] = *reinterpret_cast<const float4*>(hi + 3 * D);
+          }
+          bw[k] = *reinterpret_cast<const uint2*>(c.smem + OFF_A + (lane >> 4) * CHUNK_BYTES + swz(r, (lane & 15) >> 1) + (lane & 1) * 8);
+        }
       }
-      *reinterpret_cast<uint2*>(bp) = make_uint2(pack_bf16(u[0], u[1]), pack_bf16(u[2], u[3]));
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (hr[k] < 0) continue;
+        const int r = r0 + 8 * k;
+        float* ho = s.hid_out + (size_t)hr[k] * 4 * D + col;
+        const float b1[4] = {bf16_lo(bw[k].x), bf16_hi(bw[k].x), bf16_lo(bw[k].y), bf16_hi(bw[k].y)};
+        *reinterpret_cast<float4*>(ho + D) = t1[k];
+        *reinterpret_cast<float4*>(ho + 2 * D) = t2[k];
+        *reinterpret_cast<float4*>(ho + 3 * D) = make_float4(b1[0], b1[1], b1[2], b1[3]);
+        const float a0[4] = {t0[k].x, t0[k].y, t0[k].z, t0[k].w}, a1[4] = {t1[k].x, t1[k].y, t1[k].z, t1[k].w},
+                    a2[4] = {t2[k].x, t2[k].y, t2[k].z, t2[k].w};
+        float u[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float p0 = lag[k] >= 3 ? __fmul_rn(a0[i], cw[i][0]) : 0.f;
+          float p1 = lag[k] >= 2 ? __fmul_rn(a1[i], cw[i][1]) : 0.f;
+          float p2 = lag[k] >= 1 ? __fmul_rn(a2[i], cw[i][2]) : 0.f;
+          float p3 = __fmul_rn(b1[i], cw[i][3]);
+          u[i] = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(p0, p1), p2), p3), cb[i]);
+        }
+        *reinterpret_cast<uint2*>(c.smem + OFF_A + (lane >> 4) * CHUNK_BYTES + swz(r, (lane & 15) >> 1) + (lane & 1) * 8) =
+            make_uint2(pack_bf16(u[0], u[1]), pack_bf16(u[2], u[3]));
+      }
     }
   }
   T_END(c, TM_TEMPORAL_EPI);
@@ -1044,7 +1085,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_consta
       c.p_left = my_tiles * args.t_loop * s_sched_len;
     }
     c.occ[0] = c.occ[1] = c.occ[2] = -1;
-    if (tid == FETCH_THREAD) refill(c);
+    if ((tid >> 5) == FETCH_THREAD / 32) refill(c);
     uint8_t* meta = smem + OFF_META;
     const EnvMap& map = args.map;
     const int NM = map.tokens_per_env;
