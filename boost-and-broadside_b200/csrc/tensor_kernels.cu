@@ -1369,13 +1369,13 @@ int plan_tiles(const int32_t* tok_off, int n_envs, int32_t* tile_env_begin, int 
     const int n = tok_off[e + 1] - tok_off[e];
     if (n <= 0 || n > TILE) return BNB_ERR_TOO_MANY_TOKENS;
     if (tiles == 0 || used + n > TILE) {
-      if (tiles >= capacity) return BNB_ERR_SCRATCH_TOO_SMALL;
+      if (tiles + 1 >= capacity) return BNB_ERR_SCRATCH_TOO_SMALL;
       tile_env_begin[tiles++] = e;
       used = 0;
     }
     used += n;
   }
-  if (tiles >= capacity + 0 && n_envs > 0 && tiles > capacity - 1) return BNB_ERR_SCRATCH_TOO_SMALL;
+  if (tiles >= capacity) return BNB_ERR_SCRATCH_TOO_SMALL;  // the end marker needs one more entry
   tile_env_begin[tiles] = n_envs;
   *n_tiles = tiles;
   return BNB_OK;
