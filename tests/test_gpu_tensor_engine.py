@@ -167,3 +167,30 @@ def test_tensor_engine_refuses_what_it_is_not_built_for():
             trunk.step(x, None, hidden, engine=TENSOR)
         y, _ = trunk.step(x, None, hidden)  # AUTO falls back to SIMT
     assert torch.isfinite(y).all()
+
+
+def test_step_can_be_replayed_from_a_cuda_graph():
+    """The reference's default launch mode wraps the policy in CUDA graphs
+    (torch.compile(mode="reduce-overhead"), cli.py:204-211): a trunk step must be capturable
+    after one warm-up call (no synchronisation, no allocation outside torch's allocator)."""
+    from boost_and_broadside_b200 import workloads as W
+
+    w = W.c2(n_envs=64, seed=81)
+    trunk = build_trunk([128, 4, 2, 2, 1, 1]).to(DEV)
+    x, alive, hidden = w.x.to(DEV), w.alive.to(DEV), w.hidden.to(DEV)
+    side = torch.cuda.Stream()
+    with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
+        y_ref, h_ref = trunk.step(x, alive, hidden)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            trunk.step(x, alive, hidden)  # warm-up on the capture stream: scratch, kernel attributes
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            y_g, h_g = trunk.step(x, alive, hidden)
+        x.add_(0.25)                      # new input in the captured buffer
+        y_new, h_new = trunk.step(x, alive, hidden)
+        g.replay()
+        torch.cuda.synchronize()
+    assert not torch.equal(y_new, y_ref)
+    assert torch.equal(y_g, y_new) and torch.equal(h_g, h_new)
