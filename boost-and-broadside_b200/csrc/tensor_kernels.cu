@@ -41,8 +41,6 @@ constexpr int TILE = 128;
 constexpr int CHUNK_BYTES = 16384;       // one weight chunk: up to 128 rows x 64 bf16
 constexpr int N_SPATIAL_CHUNKS = 34;
 constexpr int N_TEMPORAL_CHUNKS = 36;
-constexpr int EPI_THREADS = 256;
-constexpr int NTHREADS = 256;
 constexpr int STAGE_STRIDE = 208;        // bytes per staged q|k|v row (96 bf16 + pad)
 constexpr int MAX_SUBLAYERS = 8;
 
@@ -53,9 +51,9 @@ constexpr int OFF_RING = 49152;          // 2 x 16 KB
 constexpr int OFF_STAGE = 81920;         // 128 x 208 = 26624
 constexpr int OFF_META = 108544;         // env_first[128], env_n[128], alive[128], items[128]
 constexpr int OFF_BAR = 109056;          // full[2], empty[2], acc, tmem base
-constexpr int OFF_SS = 109120;           // partial sums of squares, 2 x 128 floats
-constexpr int OFF_ROWINFO = 110144;      // hidden row of each tile row (int, -1 = no state), then flags
-constexpr int SMEM_BYTES = 110144 + 512 + 128 + 1024;
+constexpr int OFF_SS = 109120;           // partial sums of squares, up to 4 x 128 floats
+constexpr int OFF_ROWINFO = 111168;      // hidden row of each tile row (int, -1 = no state), then flags
+constexpr int SMEM_BYTES = 111168 + 512 + 128 + 1024;
 
 constexpr uint32_t TMEM_COLS = 256;
 constexpr uint32_t COL_RESID = 0;
@@ -137,7 +135,11 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+// Named barriers of the epilogue threads (ids 1 and 2; id 0 is __syncthreads).
+template <int NQ>
+__device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(128 * NQ) : "memory"); }
+template <int NQ>
+__device__ __forceinline__ void wake_barrier() { asm volatile("bar.sync 2, %0;" ::"n"(128 * NQ) : "memory"); }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
@@ -183,6 +185,30 @@ __device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t (&v)[1
       : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
         "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
       : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld8_nowait(uint32_t taddr, uint32_t* v) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+               : "r"(taddr) : "memory");
+}
+// N consecutive columns of this thread's lane (N a multiple of 8, at most 64); no wait.
+template <int N>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&v)[N]) {
+  static_assert(N % 8 == 0 && N <= 64, "column count");
+  int done = 0;
+  if constexpr (N >= 32) {
+    tmem_ld32_nowait(taddr, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+    done = 32;
+    if constexpr (N >= 64) {
+      tmem_ld32_nowait(taddr + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+      done = 64;
+    }
+  }
+  if constexpr ((N % 32) >= 16) {
+    tmem_ld16_nowait(taddr + done, *reinterpret_cast<uint32_t(*)[16]>(&v[N - (N % 32)]));
+    done += 16;
+  }
+  if constexpr ((N % 16) == 8) tmem_ld8_nowait(taddr + done, &v[N - 8]);
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
   tmem_ld32_nowait(taddr, v);
@@ -345,8 +371,8 @@ struct Ctx {
   volatile int* aborted;
   uint32_t acc_phase;
   int row;                          // tile row owned by this thread
-  int half;                         // which half of the columns
-  float* ss_part;                   // [2][128] partial sums of squares
+  int part;                         // which slice of the columns (0 .. NQ-1)
+  float* ss_part;                   // [NQ][128] partial sums of squares
   // Weight stream.  Three ring slots: two dedicated, the third is the q|k|v staging area,
   // which only the GatedMLP chunks use (attention is over by then).  Every call site knows
   // the slot of the chunk it consumes; the fetching thread walks a schedule table.
@@ -359,7 +385,7 @@ struct Ctx {
   const SubLayer* subs;             // sublayer table in shared memory
 };
 
-constexpr int FETCH_THREAD = 224;   // lane 0 of warp 7 fetches weights; thread 0 issues the MMAs
+// The last warp fetches weights; thread 0 issues the MMAs.
 
 __device__ __forceinline__ uint32_t slot_addr(const Ctx& c, uint32_t slot) {
   return slot < 2 ? c.sRing + slot * CHUNK_BYTES : c.sStage;
@@ -419,11 +445,12 @@ __device__ __forceinline__ void refill(Ctx& c) {
   if (c.p_idx >= c.sched_len) c.p_idx -= c.sched_len;
 }
 
+template <int NQ>
 __device__ __forceinline__ void round_begin(Ctx& c) {
   T_BEGIN(c);
   fence_proxy_async();
   tc_fence_before();
-  epi_barrier();
+  epi_barrier<NQ>();
   if (threadIdx.x == 0) tc_fence_after();
   T_END(c, TM_BARRIER);
 }
@@ -448,6 +475,7 @@ __device__ __forceinline__ void issue_chunk(Ctx& c, uint32_t a_addr, uint32_t n,
   }
   ++c.cons_count;
 }
+template <int NQ>
 __device__ __forceinline__ void round_end(Ctx& c) {
   T_BEGIN(c);
   if (threadIdx.x == 0) {
@@ -462,8 +490,8 @@ __device__ __forceinline__ void round_end(Ctx& c) {
     mbar_wait(c.bar_acc, c.acc_phase, c.status, c.aborted, ST_TIMEOUT_ACC);
   }
   c.acc_phase ^= 1u;
-  asm volatile("bar.sync 2, 256;" ::: "memory");
-  if ((threadIdx.x >> 5) == FETCH_THREAD / 32) {
+  wake_barrier<NQ>();
+  if ((threadIdx.x >> 5) == 4 * NQ - 1) {
     T_BEGIN(c);
     refill(c);
     T_END(c, TM_REFILL);
@@ -473,69 +501,76 @@ __device__ __forceinline__ void round_end(Ctx& c) {
   T_END(c, TM_WAIT);
 }
 
-// residual (TMEM) -> RMSNorm -> bf16 A operand; each thread norms its 64 columns = K atom `half`
+// Thread layout of the epilogues: NQ threads per tile row (2 or 4), thread (row, part) owns
+// TMEM lane `row` and columns [part * 128/NQ, ...) of a 128-wide row, [part * 64/NQ, ...) of a
+// 64-wide block and [part * 96/NQ, ...) of a q|k|v accumulator.
+
+// residual (TMEM) -> RMSNorm -> bf16 A operand
+template <int NQ>
 __device__ __forceinline__ void norm_to_A(Ctx& c, const float* __restrict__ g) {
+  constexpr int CPT = 128 / NQ;
   T_BEGIN(c);
-  uint32_t v[32], w[32];
-  tmem_ld32_nowait(c.lane_addr + COL_RESID + c.half * 64, v);
-  tmem_ld32_nowait(c.lane_addr + COL_RESID + c.half * 64 + 32, w);
+  uint32_t v[CPT];
+  tmem_ld_cols<CPT>(c.lane_addr + COL_RESID + c.part * CPT, v);
   tmem_wait_ld();
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    float a = __uint_as_float(v[i]), b = __uint_as_float(w[i]);
+  for (int i = 0; i < CPT; ++i) {
+    float a = __uint_as_float(v[i]);
     ss = fmaf(a, a, ss);
-    ss = fmaf(b, b, ss);
   }
-  c.ss_part[c.half * TILE + c.row] = ss;
-  epi_barrier();
-  ss += c.ss_part[(c.half ^ 1) * TILE + c.row];
-  const float inv = rsqrtf(ss * (1.0f / D) + kRmsEps);
-  uint8_t* dst = c.smem + OFF_A + c.half * CHUNK_BYTES;
-  const float* gg = g + c.half * 64;
+  c.ss_part[c.part * TILE + c.row] = ss;
+  epi_barrier<NQ>();
+  ss = 0.f;
 #pragma unroll
-  for (int q = 0; q < 8; ++q) {
-    const uint32_t* src = q < 4 ? &v[q * 8] : &w[(q - 4) * 8];
-    float4 g0 = __ldg(reinterpret_cast<const float4*>(gg + q * 8));
-    float4 g1 = __ldg(reinterpret_cast<const float4*>(gg + q * 8 + 4));
+  for (int q = 0; q < NQ; ++q) ss += c.ss_part[q * TILE + c.row];
+  const float inv = rsqrtf(ss * (1.0f / D) + kRmsEps);
+#pragma unroll
+  for (int q = 0; q < CPT / 8; ++q) {
+    const int col = c.part * CPT + q * 8;
+    const uint32_t* src = &v[q * 8];
+    float4 g0 = __ldg(reinterpret_cast<const float4*>(g + col));
+    float4 g1 = __ldg(reinterpret_cast<const float4*>(g + col + 4));
     uint4 o;
     o.x = pack_bf16(__uint_as_float(src[0]) * inv * g0.x, __uint_as_float(src[1]) * inv * g0.y);
     o.y = pack_bf16(__uint_as_float(src[2]) * inv * g0.z, __uint_as_float(src[3]) * inv * g0.w);
     o.z = pack_bf16(__uint_as_float(src[4]) * inv * g1.x, __uint_as_float(src[5]) * inv * g1.y);
     o.w = pack_bf16(__uint_as_float(src[6]) * inv * g1.z, __uint_as_float(src[7]) * inv * g1.w);
-    *reinterpret_cast<uint4*>(dst + swz(c.row, q)) = o;
+    *reinterpret_cast<uint4*>(c.smem + OFF_A + (col >> 6) * CHUNK_BYTES + swz(c.row, (col & 63) >> 3)) = o;
   }
   T_END(c, TM_NORM);
 }
 
 // GatedMLP on the A operand (already normed): residual += down(gelu(gate) * up).
+template <int NQ>
 __device__ __forceinline__ void ffn(Ctx& c) {
-  round_begin(c);
+  constexpr int GC = 64 / NQ;
+  round_begin<NQ>(c);
   if (threadIdx.x == 0) {
     issue_chunk(c, c.sA, 128, COL_ACC, 0, 0);
     issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1, 1);
   }
-  round_end(c);
+  round_end<NQ>(c);
   for (int cc = 0; cc < 8; ++cc) {
-    // gate = acc[0,64), up = acc[64,128); this thread: hidden columns [32 half, 32 half + 32)
+    // gate = acc[0,64), up = acc[64,128); this thread: hidden columns [GC part, GC part + GC)
     T_BEGIN(c);
-    uint32_t gv[32], uv[32];
-    tmem_ld32_nowait(c.lane_addr + COL_ACC + c.half * 32, gv);
-    tmem_ld32_nowait(c.lane_addr + COL_ACC + 64 + c.half * 32, uv);
+    uint32_t gv[GC], uv[GC];
+    tmem_ld_cols<GC>(c.lane_addr + COL_ACC + c.part * GC, gv);
+    tmem_ld_cols<GC>(c.lane_addr + COL_ACC + 64 + c.part * GC, uv);
     tmem_wait_ld();
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
+    for (int q = 0; q < GC / 8; ++q) {
       uint32_t o[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j)
         o[j] = pack_bf16(gelu_fast(__uint_as_float(gv[q * 8 + 2 * j])) * __uint_as_float(uv[q * 8 + 2 * j]),
                          gelu_fast(__uint_as_float(gv[q * 8 + 2 * j + 1])) * __uint_as_float(uv[q * 8 + 2 * j + 1]));
-      *reinterpret_cast<uint4*>(c.smem + OFF_P + swz(c.row, c.half * 4 + q)) = make_uint4(o[0], o[1], o[2], o[3]);
+      *reinterpret_cast<uint4*>(c.smem + OFF_P + swz(c.row, c.part * (GC / 8) + q)) = make_uint4(o[0], o[1], o[2], o[3]);
     }
     T_END(c, TM_FFN_EPI);
     // one round: this chunk's down projection into the residual, then the next chunk's
     // gate|up (the accumulator has been read, the product operand is only read by `down`)
-    round_begin(c);
+    round_begin<NQ>(c);
     if (threadIdx.x == 0) {
       issue_chunk(c, c.sP, 128, COL_RESID, 1, 2);
       if (cc < 7) {
@@ -543,7 +578,7 @@ __device__ __forceinline__ void ffn(Ctx& c) {
         issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1, 1);
       }
     }
-    round_end(c);
+    round_end<NQ>(c);
   }
 }
 
@@ -551,13 +586,13 @@ __device__ __forceinline__ void ffn(Ctx& c) {
 // (row-major, q at bf16 column 0, k at 32, v at 64) into columns [32*hh, 32*hh+32) of the
 // second operand.  One warp per block of 16 query rows of one environment; MAXKB blocks of
 // 16 keys at most.
-template <int MAXKB>
+template <int NQ, int MAXKB>
 __device__ __forceinline__ void attention_head(Ctx& c, int hh, int n_items) {
   const uint8_t* meta = c.smem + OFF_META;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const float scale = 0.17677669529663687f;  // 1/sqrt(32)
-  for (int it = warp; it < n_items; it += 8) {
+  for (int it = warp; it < n_items; it += 4 * NQ) {
     const int r0 = meta[384 + it];
     const int e0 = meta[r0], n = meta[128 + r0] + 1;   // first tile row and size of the environment
     const int last = e0 + n - 1;
@@ -661,81 +696,81 @@ __device__ __forceinline__ void attention_head(Ctx& c, int hh, int n_items) {
   }
 }
 
-template <int MAXKB>
+// bf16 pack of N accumulator columns into 16-byte groups
+__device__ __forceinline__ uint4 pack8(const uint32_t* src) {
+  return make_uint4(pack_bf16(__uint_as_float(src[0]), __uint_as_float(src[1])), pack_bf16(__uint_as_float(src[2]), __uint_as_float(src[3])),
+                    pack_bf16(__uint_as_float(src[4]), __uint_as_float(src[5])), pack_bf16(__uint_as_float(src[6]), __uint_as_float(src[7])));
+}
+
+template <int NQ, int MAXKB>
 __device__ __forceinline__ void run_spatial(Ctx& c, const SubLayer& s, int n_items, bool row_valid) {
-  norm_to_A(c, s.g1);
+  constexpr int QC = 96 / NQ, GC = 64 / NQ;
+  norm_to_A<NQ>(c, s.g1);
   for (int p = 0; p < 2; ++p) {
     for (int hh = 0; hh < 2; ++hh) {
-      round_begin(c);
+      round_begin<NQ>(c);
       if (threadIdx.x == 0) {
         issue_chunk(c, c.sA, 96, COL_ACC, 0, (uint32_t)(p & 1));          // chunks 5p+2hh, 5p+2hh+1
         issue_chunk(c, c.sA + CHUNK_BYTES, 96, COL_ACC, 1, (uint32_t)((p & 1) ^ 1));
       }
-      round_end(c);
-      // q|k|v of this head -> bf16 staging rows; this thread: accumulator columns [48 half, 48 half + 48)
+      round_end<NQ>(c);
+      // q|k|v of this head -> bf16 staging rows; this thread: accumulator columns [QC part, QC part + QC)
       {
         T_BEGIN(c);
-        uint32_t v[32], w[16];
-        tmem_ld32_nowait(c.lane_addr + COL_ACC + c.half * 48, v);
-        tmem_ld16_nowait(c.lane_addr + COL_ACC + c.half * 48 + 32, w);
+        uint32_t v[QC];
+        tmem_ld_cols<QC>(c.lane_addr + COL_ACC + c.part * QC, v);
         tmem_wait_ld();
-        uint8_t* dst = c.smem + OFF_STAGE + c.row * STAGE_STRIDE + c.half * 96;
+        uint8_t* dst = c.smem + OFF_STAGE + c.row * STAGE_STRIDE + c.part * QC * 2;
 #pragma unroll
-        for (int q = 0; q < 6; ++q) {
-          const uint32_t* src = q < 4 ? &v[q * 8] : &w[(q - 4) * 8];
-          *reinterpret_cast<uint4*>(dst + q * 16) =
-              make_uint4(pack_bf16(__uint_as_float(src[0]), __uint_as_float(src[1])), pack_bf16(__uint_as_float(src[2]), __uint_as_float(src[3])),
-                         pack_bf16(__uint_as_float(src[4]), __uint_as_float(src[5])), pack_bf16(__uint_as_float(src[6]), __uint_as_float(src[7])));
-        }
+        for (int q = 0; q < QC / 8; ++q) *reinterpret_cast<uint4*>(dst + q * 16) = pack8(&v[q * 8]);
         T_END(c, TM_QKV_EPI);
       }
       if (!row_valid && hh == 0) {
         // rows outside every environment contribute a zero operand row
 #pragma unroll
-        for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(c.smem + OFF_P + swz(c.row, c.half * 4 + q)) = make_uint4(0u, 0u, 0u, 0u);
+        for (int q = 0; q < GC / 8; ++q)
+          *reinterpret_cast<uint4*>(c.smem + OFF_P + swz(c.row, c.part * (GC / 8) + q)) = make_uint4(0u, 0u, 0u, 0u);
       }
       tc_fence_before();
       {
         T_BEGIN(c);
-        epi_barrier();
-        attention_head<MAXKB>(c, hh, n_items);
-        epi_barrier();  // staging rows are free again
+        epi_barrier<NQ>();
+        attention_head<NQ, MAXKB>(c, hh, n_items);
+        epi_barrier<NQ>();  // staging rows are free again
         T_END(c, TM_ATTN);
       }
     }
-    round_begin(c);
+    round_begin<NQ>(c);
     if (threadIdx.x == 0) issue_chunk(c, c.sP, 128, COL_RESID, 1, (uint32_t)(p & 1));  // chunk 5p+4
-    round_end(c);
+    round_end<NQ>(c);
   }
-  norm_to_A(c, s.g2);
-  ffn(c);
+  norm_to_A<NQ>(c, s.g2);
+  ffn<NQ>(c);
 }
 
 // Spatial sublayer, first part, for environments that span several tiles: norm1 and the
 // q|k|v projection of every head, written as bf16 to global scratch for the attention kernel.
+template <int NQ>
 __device__ __forceinline__ void run_spatial_pre(Ctx& c, const SubLayer& s, size_t grow, bool row_valid) {
-  norm_to_A(c, s.g1);
+  constexpr int QC = 96 / NQ;
+  norm_to_A<NQ>(c, s.g1);
   for (int hd = 0; hd < HEADS; ++hd) {
-    round_begin(c);
+    round_begin<NQ>(c);
     if (threadIdx.x == 0) {
       issue_chunk(c, c.sA, 96, COL_ACC, 0, 0);
       issue_chunk(c, c.sA + CHUNK_BYTES, 96, COL_ACC, 1, 1);
     }
-    round_end(c);
-    uint32_t v[32], w[16];
-    tmem_ld32_nowait(c.lane_addr + COL_ACC + c.half * 48, v);
-    tmem_ld16_nowait(c.lane_addr + COL_ACC + c.half * 48 + 32, w);
+    round_end<NQ>(c);
+    uint32_t v[QC];
+    tmem_ld_cols<QC>(c.lane_addr + COL_ACC + c.part * QC, v);
     tmem_wait_ld();
     if (row_valid) {
       __nv_bfloat16* dst = s.qkv_out + grow * (3 * D);
 #pragma unroll
-      for (int q = 0; q < 6; ++q) {
-        const uint32_t* src = q < 4 ? &v[q * 8] : &w[(q - 4) * 8];
-        const int j = c.half * 48 + q * 8;                 // accumulator column: q (0-31), k (32-63), v (64-95)
+      for (int q = 0; q < QC / 8; ++q) {
+        const int j = c.part * QC + q * 8;                 // accumulator column: q (0-31), k (32-63), v (64-95)
         const int col = (j >> 5) * D + hd * DH + (j & 31);
-        *reinterpret_cast<uint4*>(dst + col) =
-            make_uint4(pack_bf16(__uint_as_float(src[0]), __uint_as_float(src[1])), pack_bf16(__uint_as_float(src[2]), __uint_as_float(src[3])),
-                       pack_bf16(__uint_as_float(src[4]), __uint_as_float(src[5])), pack_bf16(__uint_as_float(src[6]), __uint_as_float(src[7])));
+        *reinterpret_cast<uint4*>(dst + col) = pack8(&v[q * 8]);
       }
     }
   }
@@ -743,25 +778,27 @@ __device__ __forceinline__ void run_spatial_pre(Ctx& c, const SubLayer& s, size_
 
 // Spatial sublayer, second part: attention output from global scratch -> out_proj into the
 // residual -> norm2 -> GatedMLP.
+template <int NQ>
 __device__ __forceinline__ void run_spatial_post(Ctx& c, const SubLayer& s, size_t grow, bool row_valid) {
+  constexpr int CPT = 128 / NQ;
   {
-    const uint4* src = reinterpret_cast<const uint4*>(s.o_in + grow * D + c.half * 64);
-    uint8_t* dst = c.smem + OFF_A + c.half * CHUNK_BYTES;
+    const uint4* src = reinterpret_cast<const uint4*>(s.o_in + grow * D + c.part * CPT);
 #pragma unroll
-    for (int q = 0; q < 8; ++q) {
+    for (int q = 0; q < CPT / 8; ++q) {
+      const int col = c.part * CPT + q * 8;
       uint4 o = make_uint4(0u, 0u, 0u, 0u);
       if (row_valid) o = src[q];
-      *reinterpret_cast<uint4*>(dst + swz(c.row, q)) = o;
+      *reinterpret_cast<uint4*>(c.smem + OFF_A + (col >> 6) * CHUNK_BYTES + swz(c.row, (col & 63) >> 3)) = o;
     }
   }
-  round_begin(c);
+  round_begin<NQ>(c);
   if (threadIdx.x == 0) {
     issue_chunk(c, c.sA, 128, COL_RESID, 1, 0);
     issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_RESID, 1, 1);
   }
-  round_end(c);
-  norm_to_A(c, s.g2);
-  ffn(c);
+  round_end<NQ>(c);
+  norm_to_A<NQ>(c, s.g2);
+  ffn<NQ>(c);
 }
 
 struct RowState {
@@ -770,60 +807,58 @@ struct RowState {
   bool zero_in;    // incoming state taken as zero (reset_env)
 };
 
-// One temporal sublayer on the tile at one timestep.  Thread (row, half) works on hidden
-// columns [32 half, 32 half + 32) and [64 + 32 half, 64 + 32 half + 32): the columns whose
-// gates it sees in the two gate rounds.
+// One temporal sublayer on the tile at one timestep.  In the gate rounds thread (row, part)
+// works on hidden columns [64 rnd + GC part, +GC), GC = 64 / NQ, and parks b2 for exactly those.
+template <int NQ>
 __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const RowState& rs, bool is_field, bool boundary,
                                              bool has_fields, const float* hid_in) {
+  constexpr int CPT = 128 / NQ, GC = 64 / NQ, WARPS = 4 * NQ;
   const bool is_ship = rs.hrow >= 0;
-  norm_to_A(c, s.g1);
+  norm_to_A<NQ>(c, s.g1);
   // b2 = bf16(gelu(linear2 n)) for this thread's columns, parked as packed bf16 pairs
-  uint32_t b2p[2][16];
-  round_begin(c);
+  uint32_t b2p[2][GC / 2];
+  round_begin<NQ>(c);
   if (threadIdx.x == 0) {
     issue_chunk(c, c.sA, 128, COL_ACC, 0, 0);
     issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1, 1);
   }
-  round_end(c);
+  round_end<NQ>(c);
   {
-  T_BEGIN(c);
+    T_BEGIN(c);
 #pragma unroll
-  for (int rnd = 0; rnd < 2; ++rnd) {
-    uint32_t v[32];
-    tmem_ld32(c.lane_addr + COL_ACC + rnd * 64 + c.half * 32, v);
+    for (int rnd = 0; rnd < 2; ++rnd) {
+      uint32_t v[GC];
+      tmem_ld_cols<GC>(c.lane_addr + COL_ACC + rnd * 64 + c.part * GC, v);
+      tmem_wait_ld();
 #pragma unroll
-    for (int j = 0; j < 16; ++j)
-      b2p[rnd][j] = pack_bf16(gelu_fast(__uint_as_float(v[2 * j])), gelu_fast(__uint_as_float(v[2 * j + 1])));
-  }
-  T_END(c, TM_TEMPORAL_EPI);
+      for (int j = 0; j < GC / 2; ++j)
+        b2p[rnd][j] = pack_bf16(gelu_fast(__uint_as_float(v[2 * j])), gelu_fast(__uint_as_float(v[2 * j + 1])));
+    }
+    T_END(c, TM_TEMPORAL_EPI);
   }
   // b1 = bf16(linear1 n); ships: causal conv with the stored taps -> u; fields: keep b1.
-  // This thread: columns [64 half, 64 half + 64) = K atom `half` of the operand.
-  round_begin(c);
+  round_begin<NQ>(c);
   if (threadIdx.x == 0) {
     issue_chunk(c, c.sA, 128, COL_ACC, 0, 0);
     issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1, 1);
   }
-  round_end(c);
+  round_end<NQ>(c);
   const float* hin = is_ship ? hid_in + (size_t)rs.hrow * 4 * D : nullptr;
   float* hout = is_ship ? s.hid_out + (size_t)rs.hrow * 4 * D : nullptr;
   T_BEGIN(c);
-  // (1) every thread parks bf16(b1) of its 64 columns in the A operand (K atom `half`)
+  // (1) every thread parks bf16(b1) of its CPT columns in the A operand
+  {
+    uint32_t v[CPT];
+    tmem_ld_cols<CPT>(c.lane_addr + COL_ACC + c.part * CPT, v);
+    tmem_wait_ld();
 #pragma unroll
-  for (int ch = 0; ch < 2; ++ch) {
-    uint32_t v[32];
-    tmem_ld32(c.lane_addr + COL_ACC + c.half * 64 + ch * 32, v);
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      uint4 o = make_uint4(pack_bf16(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1])),
-                           pack_bf16(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3])),
-                           pack_bf16(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5])),
-                           pack_bf16(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7])));
-      *reinterpret_cast<uint4*>(c.smem + OFF_A + c.half * CHUNK_BYTES + swz(c.row, ch * 4 + q)) = o;
+    for (int q = 0; q < CPT / 8; ++q) {
+      const int col = c.part * CPT + q * 8;
+      *reinterpret_cast<uint4*>(c.smem + OFF_A + (col >> 6) * CHUNK_BYTES + swz(c.row, (col & 63) >> 3)) = pack8(&v[q * 8]);
     }
   }
   tc_fence_before();
-  epi_barrier();
+  epi_barrier<NQ>();
   // (2) causal conv, one warp per ship row and four columns per lane, so that the stored taps
   // are read and written as whole 512-byte rows.  u = bias + w0 tap0 + w1 tap1 + w2 tap2 + w3 b1,
   // summed in the reference's order; new taps = (tap1, tap2, b1); bf16(u) replaces b1 in A.
@@ -841,13 +876,13 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
     const uint8_t* row_flags = c.smem + OFF_ROWINFO + 512;
     // Four rows at a time: all loads of the group are issued before any store, because the
     // state may be updated in place and the compiler must otherwise keep loads behind stores.
-    for (int r0 = warp; r0 < TILE; r0 += 32) {
+    for (int r0 = warp; r0 < TILE; r0 += 4 * WARPS) {
       float4 t0[4], t1[4], t2[4];
       uint2 bw[4];
       int hr[4], lag[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const int r = r0 + 8 * k;
+        const int r = r0 + WARPS * k;
         hr[k] = row_hrow[r];
         const int flags = row_flags[r];
         lag[k] = flags & 3;
@@ -866,7 +901,7 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         if (hr[k] < 0) continue;
-        const int r = r0 + 8 * k;
+        const int r = r0 + WARPS * k;
         float* ho = s.hid_out + (size_t)hr[k] * 4 * D + col;
         const float b1[4] = {bf16_lo(bw[k].x), bf16_hi(bw[k].x), bf16_lo(bw[k].y), bf16_hi(bw[k].y)};
         *reinterpret_cast<float4*>(ho + D) = t1[k];
@@ -892,30 +927,30 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
   // gates and state update, 64 hidden columns per round: acc[0,64) = W_a u, acc[64,128) = W_x u
 #pragma unroll
   for (int rnd = 0; rnd < 2; ++rnd) {
-    round_begin(c);
+    round_begin<NQ>(c);
     if (threadIdx.x == 0) {
       issue_chunk(c, c.sA, 128, COL_ACC, 0, 0);
       issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1, 1);
     }
-    // previous state of this thread's 32 columns, requested before waiting for the gates
-    float4 hprev[8];
+    // previous state of this thread's columns, requested before waiting for the gates
+    float4 hprev[GC / 4];
 #pragma unroll
-    for (int q = 0; q < 8; ++q) {
+    for (int q = 0; q < GC / 4; ++q) {
       hprev[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (is_ship && !rs.zero_in) hprev[q] = *reinterpret_cast<const float4*>(hin + rnd * 64 + c.half * 32 + q * 4);
+      if (is_ship && !rs.zero_in) hprev[q] = *reinterpret_cast<const float4*>(hin + rnd * 64 + c.part * GC + q * 4);
     }
-    round_end(c);
+    round_end<NQ>(c);
     T_BEGIN(c);
-    uint32_t rv[32], iv[32];
-    tmem_ld32_nowait(c.lane_addr + COL_ACC + c.half * 32, rv);       // executed by every lane of the warp
-    tmem_ld32_nowait(c.lane_addr + COL_ACC + 64 + c.half * 32, iv);
+    uint32_t rv[GC], iv[GC];
+    tmem_ld_cols<GC>(c.lane_addr + COL_ACC + c.part * GC, rv);       // executed by every lane of the warp
+    tmem_ld_cols<GC>(c.lane_addr + COL_ACC + 64 + c.part * GC, iv);
     tmem_wait_ld();
     if (is_ship) {
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const int col = rnd * 64 + c.half * 32 + q * 8;
+      for (int q = 0; q < GC / 8; ++q) {
+        const int col = rnd * 64 + c.part * GC + q * 8;
         // u (bf16) back from the A operand (K atom rnd)
-        uint8_t* ua = c.smem + OFF_A + rnd * CHUNK_BYTES + swz(c.row, c.half * 4 + q);
+        uint8_t* ua = c.smem + OFF_A + rnd * CHUNK_BYTES + swz(c.row, c.part * (GC / 8) + q);
         const uint4 ub = *reinterpret_cast<const uint4*>(ua);
         const uint32_t uw[4] = {ub.x, ub.y, ub.z, ub.w};
         uint32_t ob[4];
@@ -948,7 +983,7 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
           ob[hf * 2 + 1] = pack_bf16(hn[2] * bf16_lo(b2p[rnd][bi + 1]), hn[3] * bf16_hi(b2p[rnd][bi + 1]));
         }
         // branch operand for linear_out: K atom 0 lives in the second operand, K atom 1 in place
-        uint8_t* dst = rnd == 0 ? c.smem + OFF_P + swz(c.row, c.half * 4 + q) : ua;
+        uint8_t* dst = rnd == 0 ? c.smem + OFF_P + swz(c.row, c.part * (GC / 8) + q) : ua;
         *reinterpret_cast<uint4*>(dst) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
       }
     }
@@ -956,19 +991,20 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
   }
   if (has_fields) {
     // field rows: branch = bf16(bf16(field_sub b1) * b2)
-    round_begin(c);
+    round_begin<NQ>(c);
     if (threadIdx.x == 0) {
       issue_chunk(c, c.sA, 128, COL_ACC, 0, 0);
       issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1, 1);
     }
-    round_end(c);
+    round_end<NQ>(c);
 #pragma unroll
     for (int rnd = 0; rnd < 2; ++rnd) {
-      uint32_t v[32];
-      tmem_ld32(c.lane_addr + COL_ACC + rnd * 64 + c.half * 32, v);        // executed by every lane of the warp
+      uint32_t v[GC];
+      tmem_ld_cols<GC>(c.lane_addr + COL_ACC + rnd * 64 + c.part * GC, v);        // executed by every lane of the warp
+      tmem_wait_ld();
       if (!is_ship) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
+        for (int q = 0; q < GC / 8; ++q) {
           uint32_t ob[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -977,8 +1013,8 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
             float f1 = is_field ? round_bf16(__uint_as_float(v[q * 8 + 2 * j + 1])) * bf16_hi(b2p[rnd][bi]) : 0.f;
             ob[j] = pack_bf16(f0, f1);
           }
-          uint8_t* dst = rnd == 0 ? c.smem + OFF_P + swz(c.row, c.half * 4 + q)
-                                  : c.smem + OFF_A + CHUNK_BYTES + swz(c.row, c.half * 4 + q);
+          uint8_t* dst = rnd == 0 ? c.smem + OFF_P + swz(c.row, c.part * (GC / 8) + q)
+                                  : c.smem + OFF_A + CHUNK_BYTES + swz(c.row, c.part * (GC / 8) + q);
           *reinterpret_cast<uint4*>(dst) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
         }
       }
@@ -986,24 +1022,24 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
   } else if (!is_ship) {
     // rows outside every environment: zero operand rows
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      *reinterpret_cast<uint4*>(c.smem + OFF_P + swz(c.row, c.half * 4 + q)) = make_uint4(0u, 0u, 0u, 0u);
-      *reinterpret_cast<uint4*>(c.smem + OFF_A + CHUNK_BYTES + swz(c.row, c.half * 4 + q)) = make_uint4(0u, 0u, 0u, 0u);
+    for (int q = 0; q < GC / 8; ++q) {
+      *reinterpret_cast<uint4*>(c.smem + OFF_P + swz(c.row, c.part * (GC / 8) + q)) = make_uint4(0u, 0u, 0u, 0u);
+      *reinterpret_cast<uint4*>(c.smem + OFF_A + CHUNK_BYTES + swz(c.row, c.part * (GC / 8) + q)) = make_uint4(0u, 0u, 0u, 0u);
     }
   }
   // residual += linear_out(branch): K atom 0 from the second operand, K atom 1 from A
-  round_begin(c);
+  round_begin<NQ>(c);
   if (threadIdx.x == 0) {
     issue_chunk(c, c.sP, 128, COL_RESID, 1, 0);
     issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_RESID, 1, 1);
   }
-  round_end(c);
-  norm_to_A(c, s.g2);
-  ffn(c);
+  round_end<NQ>(c);
+  norm_to_A<NQ>(c, s.g2);
+  ffn<NQ>(c);
 }
 
-template <int MAXKB>
-__global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_constant__ TrunkArgs args) {
+template <int NQ, int MAXKB>
+__global__ void __launch_bounds__(128 * NQ, 2) k_trunk_tiles(const __grid_constant__ TrunkArgs args) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ int s_aborted;
@@ -1062,7 +1098,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_consta
     c.bar_acc = smem_u32(&bars[4]);
     c.tmem = tmem_base;
     c.row = tid & (TILE - 1);
-    c.half = tid >> 7;
+    c.part = tid >> 7;
     c.lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     c.status = args.status;
     c.aborted = &s_aborted;
@@ -1085,7 +1121,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_consta
       c.p_left = my_tiles * args.t_loop * s_sched_len;
     }
     c.occ[0] = c.occ[1] = c.occ[2] = -1;
-    if ((tid >> 5) == FETCH_THREAD / 32) refill(c);
+    if (warp == 4 * NQ - 1) refill(c);
     uint8_t* meta = smem + OFF_META;
     const EnvMap& map = args.map;
     const int NM = map.tokens_per_env;
@@ -1145,31 +1181,32 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_consta
       rs.hrow = is_ship ? hrow_if_ship : -1;
       rs.lag_ok = BNB_CONV_KERNEL - 1;
       rs.zero_in = is_ship && args.reset_env && args.reset_env[env];
-      epi_barrier();  // previous tile's readers of the meta arrays are done
-      if (c.half == 0) {
+      epi_barrier<NQ>();  // previous tile's readers of the meta arrays are done
+      if (c.part == 0) {
         meta[row] = (uint8_t)(valid ? env_first : row);
         meta[128 + row] = (uint8_t)(valid ? env_n - 1 : 0);
       }
-      if (c.half == 0) reinterpret_cast<int*>(smem + OFF_ROWINFO)[row] = rs.hrow;
+      if (c.part == 0) reinterpret_cast<int*>(smem + OFF_ROWINFO)[row] = rs.hrow;
       if (tid == 0) s_items = 0;
-      epi_barrier();
-      if (c.half == 0 && valid && (tok & 15) == 0) meta[384 + atomicAdd(&s_items, 1)] = (uint8_t)row;
+      epi_barrier<NQ>();
+      if (c.part == 0 && valid && (tok & 15) == 0) meta[384 + atomicAdd(&s_items, 1)] = (uint8_t)row;
 
       for (int t = 0; t < args.t_loop; ++t) {
         const size_t trow = grow + (size_t)t * map.total_tokens;
-        if (c.half == 0) meta[256 + row] = valid ? (args.alive ? args.alive[trow] : (uint8_t)1) : (uint8_t)0;
-        // residual <- x (this thread: columns [64 half, 64 half + 64))
+        if (c.part == 0) meta[256 + row] = valid ? (args.alive ? args.alive[trow] : (uint8_t)1) : (uint8_t)0;
+        // residual <- x (this thread: columns [CPT part, CPT part + CPT))
+        constexpr int CPT = 128 / NQ;
 #pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {
+        for (int ch = 0; ch < CPT / 32; ++ch) {
           uint32_t v[32];
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
             float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (valid) f = *reinterpret_cast<const float4*>(args.x + trow * D + c.half * 64 + ch * 32 + q * 4);
+            if (valid) f = *reinterpret_cast<const float4*>(args.x + trow * D + c.part * CPT + ch * 32 + q * 4);
             v[q * 4 + 0] = __float_as_uint(f.x); v[q * 4 + 1] = __float_as_uint(f.y);
             v[q * 4 + 2] = __float_as_uint(f.z); v[q * 4 + 3] = __float_as_uint(f.w);
           }
-          tmem_st32(c.lane_addr + COL_RESID + c.half * 64 + ch * 32, v);
+          tmem_st32(c.lane_addr + COL_RESID + c.part * CPT + ch * 32, v);
         }
         bool boundary = false;
         if (t >= 1) {
@@ -1177,27 +1214,27 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_trunk_tiles(const __grid_consta
           rs.lag_ok = boundary ? 0 : min(rs.lag_ok + 1, BNB_CONV_KERNEL - 1);
           rs.zero_in = false;
         }
-        if (c.half == 0) smem[OFF_ROWINFO + 512 + row] = (uint8_t)(rs.lag_ok | (rs.zero_in ? 4 : 0));
+        if (c.part == 0) smem[OFF_ROWINFO + 512 + row] = (uint8_t)(rs.lag_ok | (rs.zero_in ? 4 : 0));
         tc_fence_before();
-        epi_barrier();
+        epi_barrier<NQ>();
         tc_fence_after();
         const int n_items = s_items;
         for (int si = 0; si < args.n_sub; ++si) {
           const SubLayer& s = s_sub[si];
-          if (s.type == SUB_SPATIAL) run_spatial<MAXKB>(c, s, n_items, valid);
-          else if (s.type == SUB_SPATIAL_PRE) run_spatial_pre(c, s, trow, valid);
-          else if (s.type == SUB_SPATIAL_POST) run_spatial_post(c, s, trow, valid);
-          else run_temporal(c, s, rs, is_field, boundary, args.has_fields != 0, t == 0 ? s.hid_in : s.hid_out);
+          if (s.type == SUB_SPATIAL) run_spatial<NQ, MAXKB>(c, s, n_items, valid);
+          else if (s.type == SUB_SPATIAL_PRE) run_spatial_pre<NQ>(c, s, trow, valid);
+          else if (s.type == SUB_SPATIAL_POST) run_spatial_post<NQ>(c, s, trow, valid);
+          else run_temporal<NQ>(c, s, rs, is_field, boundary, args.has_fields != 0, t == 0 ? s.hid_in : s.hid_out);
         }
         // y <- residual
 #pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {
+        for (int ch = 0; ch < CPT / 32; ++ch) {
           uint32_t v[32];
-          tmem_ld32(c.lane_addr + COL_RESID + c.half * 64 + ch * 32, v);
+          tmem_ld32(c.lane_addr + COL_RESID + c.part * CPT + ch * 32, v);
           if (valid) {
 #pragma unroll
             for (int q = 0; q < 8; ++q)
-              *reinterpret_cast<float4*>(args.y + trow * D + c.half * 64 + ch * 32 + q * 4) =
+              *reinterpret_cast<float4*>(args.y + trow * D + c.part * CPT + ch * 32 + q * 4) =
                   make_float4(__uint_as_float(v[q * 4]), __uint_as_float(v[q * 4 + 1]), __uint_as_float(v[q * 4 + 2]), __uint_as_float(v[q * 4 + 3]));
           }
         }
@@ -1424,15 +1461,17 @@ static int launch(TrunkArgs& a, const BnbBatch& b, cudaStream_t st) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BNB_ERR_NO_DEVICE;
   if (!configured[dev]) {
-    if (cudaFuncSetAttribute(k_trunk_tiles<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
-        cudaFuncSetAttribute(k_trunk_tiles<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(k_trunk_tiles<2, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
+        cudaFuncSetAttribute(k_trunk_tiles<2, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
       return BNB_ERR_LAUNCH;
     configured[dev] = true;
   }
   int grid = a.n_tiles < 2 * 148 ? a.n_tiles : 2 * 148;
   count_launch();
-  if (b.max_tokens_per_env <= 64 || a.flat_rows) k_trunk_tiles<4><<<grid, NTHREADS, SMEM_BYTES, st>>>(a);
-  else k_trunk_tiles<8><<<grid, NTHREADS, SMEM_BYTES, st>>>(a);
+  // Two threads per tile row: four (64 registers per thread at two CTAs per SM) spill and were
+  // measured slower.
+  if (b.max_tokens_per_env <= 64 || a.flat_rows) k_trunk_tiles<2, 4><<<grid, 256, SMEM_BYTES, st>>>(a);
+  else k_trunk_tiles<2, 8><<<grid, 256, SMEM_BYTES, st>>>(a);
   return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
 }
 
