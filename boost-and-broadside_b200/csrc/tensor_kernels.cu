@@ -847,13 +847,14 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
   float* hout = is_ship ? s.hid_out + (size_t)rs.hrow * 4 * D : nullptr;
   T_BEGIN(c);
   // (1) every thread parks bf16(b1) of its CPT columns in the A operand
-  {
-    uint32_t v[CPT];
-    tmem_ld_cols<CPT>(c.lane_addr + COL_ACC + c.part * CPT, v);
+#pragma unroll
+  for (int ch = 0; ch < CPT / 32; ++ch) {
+    uint32_t v[32];
+    tmem_ld_cols<32>(c.lane_addr + COL_ACC + c.part * CPT + ch * 32, v);
     tmem_wait_ld();
 #pragma unroll
-    for (int q = 0; q < CPT / 8; ++q) {
-      const int col = c.part * CPT + q * 8;
+    for (int q = 0; q < 4; ++q) {
+      const int col = c.part * CPT + ch * 32 + q * 8;
       *reinterpret_cast<uint4*>(c.smem + OFF_A + (col >> 6) * CHUNK_BYTES + swz(c.row, (col & 63) >> 3)) = pack8(&v[q * 8]);
     }
   }
@@ -941,50 +942,56 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
     }
     round_end<NQ>(c);
     T_BEGIN(c);
-    uint32_t rv[GC], iv[GC];
-    tmem_ld_cols<GC>(c.lane_addr + COL_ACC + c.part * GC, rv);       // executed by every lane of the warp
-    tmem_ld_cols<GC>(c.lane_addr + COL_ACC + 64 + c.part * GC, iv);
-    tmem_wait_ld();
-    if (is_ship) {
+    // sixteen columns at a time keeps the gate accumulators, the parked b2 and the prefetched
+    // state inside the register budget
 #pragma unroll
-      for (int q = 0; q < GC / 8; ++q) {
-        const int col = rnd * 64 + c.part * GC + q * 8;
-        // u (bf16) back from the A operand (K atom rnd)
-        uint8_t* ua = c.smem + OFF_A + rnd * CHUNK_BYTES + swz(c.row, c.part * (GC / 8) + q);
-        const uint4 ub = *reinterpret_cast<const uint4*>(ua);
-        const uint32_t uw[4] = {ub.x, ub.y, ub.z, ub.w};
-        uint32_t ob[4];
+    for (int sc = 0; sc < GC / 16; ++sc) {
+      uint32_t rv[16], iv[16];
+      tmem_ld_cols<16>(c.lane_addr + COL_ACC + c.part * GC + sc * 16, rv);       // executed by every lane of the warp
+      tmem_ld_cols<16>(c.lane_addr + COL_ACC + 64 + c.part * GC + sc * 16, iv);
+      tmem_wait_ld();
+      if (is_ship) {
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          const int cc = col + hf * 4;
-          const float4 hv = hprev[q * 2 + hf];
-          const float4 ab = __ldg(reinterpret_cast<const float4*>(s.a_b + cc));
-          const float4 xb = __ldg(reinterpret_cast<const float4*>(s.x_b + cc));
-          const float4 dl = __ldg(reinterpret_cast<const float4*>(s.decay_log2 + cc));
-          const float abv[4] = {ab.x, ab.y, ab.z, ab.w}, xbv[4] = {xb.x, xb.y, xb.z, xb.w}, dlv[4] = {dl.x, dl.y, dl.z, dl.w};
-          float hn[4] = {hv.x, hv.y, hv.z, hv.w};
+        for (int q2 = 0; q2 < 2; ++q2) {
+          const int q = sc * 2 + q2;
+          const int col = rnd * 64 + c.part * GC + q * 8;
+          // u (bf16) back from the A operand (K atom rnd)
+          uint8_t* ua = c.smem + OFF_A + rnd * CHUNK_BYTES + swz(c.row, c.part * (GC / 8) + q);
+          const uint4 ub = *reinterpret_cast<const uint4*>(ua);
+          const uint32_t uw[4] = {ub.x, ub.y, ub.z, ub.w};
+          uint32_t ob[4];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int k = q * 8 + hf * 4 + i;
-            float rg = round_bf16(sigmoid_fast(__uint_as_float(rv[k]) + abv[i]));
-            float ig = round_bf16(sigmoid_fast(__uint_as_float(iv[k]) + xbv[i]));
-            // sigmoid(Lambda)^(8 r) = 2^(r * 8 log2 sigmoid(Lambda)); the table is part of the weight image
-            float a = ex2_fast(rg * dlv[i]);
-            float gate = sqrt_fast(fmaxf((1.0f - a) * (1.0f + a), kGateFloor));
-            uint32_t uword = uw[hf * 2 + (i >> 1)];
-            float uu = (i & 1) ? bf16_hi(uword) : bf16_lo(uword);
-            float bb = gate * (ig * uu);
-            if (boundary) a = 0.f;
-            hn[i] = fmaf(a, hn[i], bb);
+          for (int hf = 0; hf < 2; ++hf) {
+            const int cc = col + hf * 4;
+            const float4 hv = hprev[q * 2 + hf];
+            const float4 ab = __ldg(reinterpret_cast<const float4*>(s.a_b + cc));
+            const float4 xb = __ldg(reinterpret_cast<const float4*>(s.x_b + cc));
+            const float4 dl = __ldg(reinterpret_cast<const float4*>(s.decay_log2 + cc));
+            const float abv[4] = {ab.x, ab.y, ab.z, ab.w}, xbv[4] = {xb.x, xb.y, xb.z, xb.w}, dlv[4] = {dl.x, dl.y, dl.z, dl.w};
+            float hn[4] = {hv.x, hv.y, hv.z, hv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int k = q2 * 8 + hf * 4 + i;
+              float rg = round_bf16(sigmoid_fast(__uint_as_float(rv[k]) + abv[i]));
+              float ig = round_bf16(sigmoid_fast(__uint_as_float(iv[k]) + xbv[i]));
+              // sigmoid(Lambda)^(8 r) = 2^(r * 8 log2 sigmoid(Lambda)); the table is part of the weight image
+              float a = ex2_fast(rg * dlv[i]);
+              float gate = sqrt_fast(fmaxf((1.0f - a) * (1.0f + a), kGateFloor));
+              uint32_t uword = uw[hf * 2 + (i >> 1)];
+              float uu = (i & 1) ? bf16_hi(uword) : bf16_lo(uword);
+              float bb = gate * (ig * uu);
+              if (boundary) a = 0.f;
+              hn[i] = fmaf(a, hn[i], bb);
+            }
+            *reinterpret_cast<float4*>(hout + cc) = make_float4(hn[0], hn[1], hn[2], hn[3]);
+            const int bi = q * 4 + hf * 2;
+            ob[hf * 2] = pack_bf16(hn[0] * bf16_lo(b2p[rnd][bi]), hn[1] * bf16_hi(b2p[rnd][bi]));
+            ob[hf * 2 + 1] = pack_bf16(hn[2] * bf16_lo(b2p[rnd][bi + 1]), hn[3] * bf16_hi(b2p[rnd][bi + 1]));
           }
-          *reinterpret_cast<float4*>(hout + cc) = make_float4(hn[0], hn[1], hn[2], hn[3]);
-          const int bi = q * 4 + hf * 2;
-          ob[hf * 2] = pack_bf16(hn[0] * bf16_lo(b2p[rnd][bi]), hn[1] * bf16_hi(b2p[rnd][bi]));
-          ob[hf * 2 + 1] = pack_bf16(hn[2] * bf16_lo(b2p[rnd][bi + 1]), hn[3] * bf16_hi(b2p[rnd][bi + 1]));
+          // branch operand for linear_out: K atom 0 lives in the second operand, K atom 1 in place
+          uint8_t* dst = rnd == 0 ? c.smem + OFF_P + swz(c.row, c.part * (GC / 8) + q) : ua;
+          *reinterpret_cast<uint4*>(dst) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
         }
-        // branch operand for linear_out: K atom 0 lives in the second operand, K atom 1 in place
-        uint8_t* dst = rnd == 0 ? c.smem + OFF_P + swz(c.row, c.part * (GC / 8) + q) : ua;
-        *reinterpret_cast<uint4*>(dst) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
       }
     }
     T_END(c, TM_IO);
