@@ -1228,6 +1228,13 @@ __global__ void __launch_bounds__(128 * NQ, 2) k_trunk_tiles(const __grid_consta
         const int n_items = s_items;
         for (int si = 0; si < args.n_sub; ++si) {
           const SubLayer& s = s_sub[si];
+          // Ask L2 for the recurrent state of the temporal sublayer that follows this one: every
+          // CTA reaches it at about the same time, and the rows are needed one sublayer from now.
+          if (is_ship && t == 0 && si + 1 < args.n_sub && s_sub[si + 1].type == SUB_TEMPORAL && s.type != SUB_TEMPORAL) {
+            const char* base = reinterpret_cast<const char*>(s_sub[si + 1].hid_in + (size_t)rs.hrow * 4 * D) + c.part * (2048 / NQ);
+#pragma unroll
+            for (int l = 0; l < 16 / NQ; ++l) asm volatile("prefetch.global.L2 [%0];" ::"l"(base + l * 128));
+          }
           if (s.type == SUB_SPATIAL) run_spatial<NQ, MAXKB>(c, s, n_items, valid);
           else if (s.type == SUB_SPATIAL_PRE) run_spatial_pre<NQ>(c, s, trow, valid);
           else if (s.type == SUB_SPATIAL_POST) run_spatial_post<NQ>(c, s, trow, valid);
