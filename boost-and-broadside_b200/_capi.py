@@ -47,6 +47,7 @@ class Batch(C.Structure):
         ("tok_off", _fp),
         ("ship_off", _fp),
         ("tile_env_begin", _fp),
+        ("tile_env_ids", _fp),
         ("n_tiles", C.c_int32),
     ]
 
@@ -56,7 +57,7 @@ EXPORTS = {
     "bnb_status_string": (C.c_char_p, [C.c_int]),
     "bnb_launch_count": (C.c_ulonglong, []),
     "bnb_supported": (C.c_int, [C.c_int] * 5),
-    "bnb_plan_tiles": (C.c_int, [_fp, C.c_int, _fp, C.c_int, C.POINTER(C.c_int)]),
+    "bnb_plan_tiles": (C.c_int, [_fp, C.c_int, _fp, _fp, C.c_int, C.POINTER(C.c_int)]),
     "bnb_scratch_bytes": (C.c_size_t, [C.c_int, C.POINTER(Batch), C.c_int]),
     "bnb_spatial_block_fwd": (
         C.c_int,
@@ -180,7 +181,7 @@ def scratch_for(device: torch.device, nbytes: int) -> torch.Tensor:
 
 
 def uniform_batch(n_envs: int, tokens: int, ships: int) -> Batch:
-    return Batch(n_envs, tokens, ships, tokens, n_envs * tokens, n_envs * ships, None, None, None, 0)
+    return Batch(n_envs, tokens, ships, tokens, n_envs * tokens, n_envs * ships, None, None, None, None, 0)
 
 
 def tensor_engine_status(device: torch.device) -> int:

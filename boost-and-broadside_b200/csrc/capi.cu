@@ -130,11 +130,11 @@ int bnb_supported(int d_model, int n_heads, int max_tokens_per_env, int precisio
   return 1;
 }
 
-int bnb_plan_tiles(const int32_t* tok_off_host, int n_envs, int32_t* tile_env_begin_host, int capacity,
-                   int* n_tiles) {
-  if (!tok_off_host || !tile_env_begin_host || !n_tiles) return BNB_ERR_NULL_POINTER;
+int bnb_plan_tiles(const int32_t* tok_off_host, int n_envs, int32_t* tile_env_begin_host,
+                   int32_t* tile_env_ids_host, int capacity, int* n_tiles) {
+  if (!tok_off_host || !tile_env_begin_host || !tile_env_ids_host || !n_tiles) return BNB_ERR_NULL_POINTER;
   if (n_envs < 0 || capacity < 1) return BNB_ERR_BAD_ARGUMENT;
-  return bnb::tensor::plan_tiles(tok_off_host, n_envs, tile_env_begin_host, capacity, n_tiles);
+  return bnb::tensor::plan_tiles(tok_off_host, n_envs, tile_env_begin_host, tile_env_ids_host, capacity, n_tiles);
 }
 
 size_t bnb_scratch_bytes(int d_model, const BnbBatch* batch, int timesteps) {

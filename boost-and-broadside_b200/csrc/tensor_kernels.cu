@@ -28,6 +28,8 @@
 
 #include <cuda_bf16.h>
 
+#include <vector>
+
 #include "common.cuh"
 #include "launch_count.h"
 
@@ -96,7 +98,8 @@ struct TrunkArgs {
   int env_tiles;      // tiles per group
   int has_fields;
   int flat_rows;      // 1: tiles are plain 128-row slices of the token rows (no attention inside)
-  const int* tile_env_begin;  // ragged batches: first environment of each tile (+ end), else null
+  const int* tile_env_begin;  // ragged batches: range of each tile in tile_env_ids (+ end), else null
+  const int* tile_env_ids;    // ragged batches: environments in tile order
   int* status;
   SubLayer sub[MAX_SUBLAYERS];
 };
@@ -1153,20 +1156,23 @@ __global__ void __launch_bounds__(128 * NQ, 2) k_trunk_tiles(const __grid_consta
         grow = (size_t)grp * map.total_tokens + (size_t)r;
         hrow_if_ship = map.env_ship_begin(env) + tok;
       } else if (args.tile_env_begin) {
-        // ragged: the tile holds environments [e_lo, e_hi), rows in token order
-        const int e_lo = args.tile_env_begin[eb], e_hi = args.tile_env_begin[eb + 1];
-        const int base = map.tok_off[e_lo];
-        const int rows = map.tok_off[e_hi] - base;
-        valid = row < rows;
-        env = e_lo;
-        if (valid) {
-          while (map.tok_off[env + 1] - base <= row) ++env;
+        // ragged: the tile holds the environments tile_env_ids[k_lo .. k_hi), rows in that order
+        const int k_lo = args.tile_env_begin[eb], k_hi = args.tile_env_begin[eb + 1];
+        int k = k_lo, first = 0;
+        env = args.tile_env_ids[k];
+        int cnt = map.tok_off[env + 1] - map.tok_off[env];
+        while (row >= first + cnt && k + 1 < k_hi) {
+          first += cnt;
+          ++k;
+          env = args.tile_env_ids[k];
+          cnt = map.tok_off[env + 1] - map.tok_off[env];
         }
-        env_first = map.tok_off[env] - base;
-        env_n = map.tok_off[env + 1] - map.tok_off[env];
+        valid = row < first + cnt;
+        env_first = first;
+        env_n = cnt;
         env_ships = map.ship_off[env + 1] - map.ship_off[env];
-        tok = row - env_first;
-        grow = (size_t)grp * map.total_tokens + (size_t)(base + row);
+        tok = row - first;
+        grow = (size_t)grp * map.total_tokens + (size_t)(map.tok_off[env] + tok);
         hrow_if_ship = map.ship_off[env] + tok;
       } else {
         const int env0 = eb * args.envs_per_tile;
@@ -1409,26 +1415,53 @@ bool supported(int d_model, int n_heads, int max_tokens_per_env) {
 static bool fits_tile(const BnbBatch& b) { return b.max_tokens_per_env <= TILE; }
 bool supported_batch(int d_model, int n_heads, const BnbBatch& b) {
   if (!supported(d_model, n_heads, b.max_tokens_per_env)) return false;
-  if (b.tok_off) return fits_tile(b) && b.tile_env_begin != nullptr && b.n_tiles > 0;
+  if (b.tok_off) return fits_tile(b) && b.tile_env_begin != nullptr && b.tile_env_ids != nullptr && b.n_tiles > 0;
   return b.tokens_per_env >= 1;
 }
 
-int plan_tiles(const int32_t* tok_off, int n_envs, int32_t* tile_env_begin, int capacity, int* n_tiles) {
-  // contiguous first-fit: an environment joins the open tile while the tile stays <= 128 rows
-  int tiles = 0, used = 0;
-  for (int e = 0; e < n_envs; ++e) {
-    const int n = tok_off[e + 1] - tok_off[e];
-    if (n <= 0 || n > TILE) return BNB_ERR_TOO_MANY_TOKENS;
-    if (tiles == 0 || used + n > TILE) {
-      if (tiles + 1 >= capacity) return BNB_ERR_SCRATCH_TOO_SMALL;
-      tile_env_begin[tiles++] = e;
-      used = 0;
+int plan_tiles(const int32_t* tok_off, int n_envs, int32_t* tile_env_begin, int32_t* tile_env_ids, int capacity,
+               int* n_tiles) {
+  // Best-fit decreasing: environments sorted by size (counting sort, sizes 1..128), each put into
+  // the open tile with the least room that still takes it.  Tiles are then listed as ranges of
+  // tile_env_ids.  Near-full tiles matter: a tile costs about the same whatever its fill.
+  if (capacity < n_envs + 1) return BNB_ERR_SCRATCH_TOO_SMALL;
+  std::vector<int> order;
+  order.reserve(n_envs);
+  {
+    std::vector<std::vector<int>> by_size(TILE + 1);
+    for (int e = 0; e < n_envs; ++e) {
+      const int n = tok_off[e + 1] - tok_off[e];
+      if (n <= 0 || n > TILE) return BNB_ERR_TOO_MANY_TOKENS;
+      by_size[n].push_back(e);
     }
-    used += n;
+    for (int n = TILE; n >= 1; --n) order.insert(order.end(), by_size[n].begin(), by_size[n].end());
   }
-  if (tiles >= capacity) return BNB_ERR_SCRATCH_TOO_SMALL;  // the end marker needs one more entry
-  tile_env_begin[tiles] = n_envs;
-  *n_tiles = tiles;
+  std::vector<std::vector<int>> tiles;                   // environments of each tile
+  std::vector<std::vector<int>> open_by_room(TILE + 1);  // tiles with exactly r free rows
+  for (int e : order) {
+    const int n = tok_off[e + 1] - tok_off[e];
+    int room = -1;
+    for (int r = n; r <= TILE; ++r)
+      if (!open_by_room[r].empty()) { room = r; break; }
+    int t;
+    if (room < 0) {
+      t = (int)tiles.size();
+      tiles.emplace_back();
+      room = TILE;
+    } else {
+      t = open_by_room[room].back();
+      open_by_room[room].pop_back();
+    }
+    tiles[t].push_back(e);
+    open_by_room[room - n].push_back(t);
+  }
+  int k = 0;
+  for (size_t t = 0; t < tiles.size(); ++t) {
+    tile_env_begin[t] = k;
+    for (int e : tiles[t]) tile_env_ids[k++] = e;
+  }
+  tile_env_begin[tiles.size()] = k;
+  *n_tiles = (int)tiles.size();
   return BNB_OK;
 }
 
@@ -1461,6 +1494,7 @@ static int launch(TrunkArgs& a, const BnbBatch& b, cudaStream_t st) {
     a.env_tiles = (b.total_tokens + TILE - 1) / TILE;
   } else if (b.tok_off) {
     a.tile_env_begin = b.tile_env_begin;
+    a.tile_env_ids = b.tile_env_ids;
     a.envs_per_tile = 0;
     a.env_tiles = b.n_tiles;
   } else {

@@ -14,7 +14,8 @@ bool supported(int D, int H, int max_tokens_per_env);
 bool supported_batch(int D, int H, const BnbBatch& b);
 
 // Host-only: pack the environments of a ragged batch into tiles of whole environments.
-int plan_tiles(const int32_t* tok_off_host, int n_envs, int32_t* tile_env_begin_host, int capacity, int* n_tiles);
+int plan_tiles(const int32_t* tok_off_host, int n_envs, int32_t* tile_env_begin_host, int32_t* tile_env_ids_host,
+               int capacity, int* n_tiles);
 
 size_t scratch_bytes(int D, const BnbBatch& b, int T);
 size_t packed_spatial_bytes(int D);

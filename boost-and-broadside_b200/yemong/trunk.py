@@ -49,20 +49,22 @@ class RaggedBatch:
         tok_d = tok_off.to(device)
         ship_d = ship_off.to(device)
         # tile plan for the tensor-core engine (environments of at most 128 tokens only)
-        tiles_d, n_tiles = None, 0
+        tiles_d, ids_d, n_tiles = None, None, 0
         if B and int(nt.max()) <= 128 and int(nt.min()) >= 1:
             plan = torch.zeros(B + 1, dtype=torch.int32)
+            ids = torch.zeros(B, dtype=torch.int32)
             n = _capi.C.c_int(0)
-            st = _capi.lib.bnb_plan_tiles(tok_off.data_ptr(), B, plan.data_ptr(), B + 1, _capi.C.byref(n))
+            st = _capi.lib.bnb_plan_tiles(tok_off.data_ptr(), B, plan.data_ptr(), ids.data_ptr(), B + 1, _capi.C.byref(n))
             _capi.check("bnb_plan_tiles", st)
             n_tiles = n.value
             tiles_d = plan[: n_tiles + 1].to(device)
+            ids_d = ids.to(device)
         batch = _capi.Batch(
             B, 0, 0, int(nt.max()) if B else 0, int(tok_off[-1]), int(ship_off[-1]), tok_d.data_ptr(), ship_d.data_ptr(),
-            None if tiles_d is None else tiles_d.data_ptr(), n_tiles,
+            None if tiles_d is None else tiles_d.data_ptr(), None if ids_d is None else ids_d.data_ptr(), n_tiles,
         )
         self.tile_fill = float(tok_off[-1]) / (128.0 * n_tiles) if n_tiles else 0.0
-        return batch, (tok_d, ship_d, tiles_d)
+        return batch, (tok_d, ship_d, tiles_d, ids_d)
 
 
 class YemongTrunk(nn.Module):

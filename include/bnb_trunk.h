@@ -114,9 +114,11 @@ typedef struct {
   const int32_t* tok_off;
   const int32_t* ship_off;
   /* Ragged batches on the tensor-core engine only: tile plan written by bnb_plan_tiles and
-   * copied to the device (n_tiles + 1 int32).  NULL / 0 keeps a ragged batch on the SIMT
-   * engine. */
+   * copied to the device: tile t holds the environments tile_env_ids[tile_env_begin[t] ..
+   * tile_env_begin[t+1]) (n_tiles + 1 and n_envs int32).  NULL / 0 keeps a ragged batch on
+   * the SIMT engine. */
   const int32_t* tile_env_begin;
+  const int32_t* tile_env_ids;
   int32_t n_tiles;
 } BnbBatch;
 
@@ -131,17 +133,17 @@ unsigned long long bnb_launch_count(void);
  * given precision and engine, else 0.  No device is touched. */
 int bnb_supported(int d_model, int n_heads, int max_tokens_per_env, int precision, int engine);
 
-/* Host-only: group the environments of a ragged batch, in order, into tiles of whole
- * environments (at most 128 token rows each) for the tensor-core engine.
+/* Host-only: group the environments of a ragged batch into tiles of whole environments (at
+ * most 128 token rows each, best-fit decreasing) for the tensor-core engine.
  *   tok_off_host        n_envs + 1 prefix sums on the HOST
- *   tile_env_begin_host receives n_tiles + 1 entries (first environment of each tile, then
- *                       n_envs); capacity is the number of int32 it can hold (n_envs + 1 is
- *                       always enough)
+ *   tile_env_begin_host receives n_tiles + 1 offsets into tile_env_ids_host; capacity is the
+ *                       number of int32 it can hold and must be at least n_envs + 1
+ *   tile_env_ids_host   receives the n_envs environment indices in tile order
  * Returns BNB_ERR_TOO_MANY_TOKENS when an environment has more than 128 tokens.
  * No counterpart in the reference (it cannot express per-environment fleet sizes in one call,
  * models/yemong/griffin.py:398-399). */
-int bnb_plan_tiles(const int32_t* tok_off_host, int n_envs, int32_t* tile_env_begin_host, int capacity,
-                   int* n_tiles);
+int bnb_plan_tiles(const int32_t* tok_off_host, int n_envs, int32_t* tile_env_begin_host,
+                   int32_t* tile_env_ids_host, int capacity, int* n_tiles);
 
 /* Bytes of scratch a call with this geometry may use (upper bound over all entry points).
  * `timesteps` is 1 for a step. */

@@ -85,7 +85,7 @@ def test_missing_library_fails_loudly(tmp_path):
 
 
 def test_plan_tiles_is_a_host_function():
-    """First-fit packing of whole environments into 128-row tiles, on the host."""
+    """Best-fit-decreasing packing of whole environments into 128-row tiles, on the host."""
     import torch
 
     from boost_and_broadside_b200 import _capi
@@ -94,15 +94,19 @@ def test_plan_tiles_is_a_host_function():
     off = torch.zeros(len(sizes) + 1, dtype=torch.int32)
     off[1:] = sizes.cumsum(0)
     plan = torch.zeros(len(sizes) + 1, dtype=torch.int32)
+    ids = torch.zeros(len(sizes), dtype=torch.int32)
     n = C.c_int(0)
-    st = _capi.lib.bnb_plan_tiles(off.data_ptr(), len(sizes), plan.data_ptr(), len(sizes) + 1, C.byref(n))
+    st = _capi.lib.bnb_plan_tiles(off.data_ptr(), len(sizes), plan.data_ptr(), ids.data_ptr(), len(sizes) + 1, C.byref(n))
     assert st == 0
-    # [100, 28] | [1] would overflow with 128 -> [1] alone? no: 1 joins nothing before 128 -> tiles:
-    # {100, 28}, {1}, {128}, {64, 64}, {2}, {127}  (2 + 127 = 129 does not fit)
-    assert n.value == 6
-    assert plan[: n.value + 1].tolist() == [0, 2, 3, 4, 6, 7, 8]
+    # best-fit decreasing: 128 | 127+1 | 100+28 | 64+64 | 2  -> five tiles, every environment once
+    assert n.value == 5
+    begins = plan[: n.value + 1].tolist()
+    assert begins[0] == 0 and begins[-1] == len(sizes)
+    assert sorted(ids.tolist()) == list(range(len(sizes)))
+    for t in range(n.value):
+        assert sum(int(sizes[e]) for e in ids[begins[t] : begins[t + 1]].tolist()) <= 128
     # an environment larger than a tile is refused
     off2 = torch.tensor([0, 129], dtype=torch.int32)
-    st = _capi.lib.bnb_plan_tiles(off2.data_ptr(), 1, plan.data_ptr(), 2, C.byref(n))
+    st = _capi.lib.bnb_plan_tiles(off2.data_ptr(), 1, plan.data_ptr(), ids.data_ptr(), 2, C.byref(n))
     assert st == 4  # BNB_ERR_TOO_MANY_TOKENS
-    assert _capi.lib.bnb_plan_tiles(None, 1, plan.data_ptr(), 2, C.byref(n)) == 1
+    assert _capi.lib.bnb_plan_tiles(None, 1, plan.data_ptr(), ids.data_ptr(), 2, C.byref(n)) == 1
