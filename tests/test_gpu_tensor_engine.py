@@ -194,3 +194,33 @@ def test_step_can_be_replayed_from_a_cuda_graph():
         torch.cuda.synchronize()
     assert not torch.equal(y_new, y_ref)
     assert torch.equal(y_g, y_new) and torch.equal(h_g, h_new)
+
+
+@pytest.mark.parametrize("name", ["C3", "C4", "C5"])
+def test_full_size_configurations_tensor_vs_simt(name):
+    """At the full sizes of the large-fleet, sequence and ragged configurations the CPU oracle
+    is too slow, so the tensor-core engine is checked against the CUDA-core engine (itself
+    checked against the oracle at reduced sizes) on every output element, plus finiteness."""
+    from boost_and_broadside_b200 import RaggedBatch
+    from boost_and_broadside_b200 import workloads as W
+
+    _capi, SIMT, TENSOR = _engines()
+    trunk = build_trunk([128, 4, 2, 2, 1, 1]).to(DEV)
+    if name == "C3":
+        w = W.c3()
+        run = lambda eng: trunk.step(w.x.to(DEV), w.alive.to(DEV), w.hidden.to(DEV), engine=eng)
+    elif name == "C4":
+        w = W.c4(n_envs=2048)  # half the environments: 2 x 268 MB of activations per engine
+        run = lambda eng: trunk.sequence(w.x.to(DEV), w.alive.to(DEV), w.hidden.to(DEV), w.done.to(DEV), engine=eng)
+    else:
+        w = W.c5()
+        rb = RaggedBatch(w.n_tokens, w.n_ships)
+        run = lambda eng: trunk.step_ragged(w.x.to(DEV), w.alive.to(DEV), w.hidden.to(DEV), rb, engine=eng)
+    with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
+        yt, ht = run(TENSOR)
+        _status_ok()
+        ys, hs = run(SIMT)
+    assert torch.isfinite(yt).all() and torch.isfinite(ht).all()
+    ey = float((yt - ys).abs().max()) / float(ys.abs().max())
+    eh = float((ht - hs).abs().max()) / float(hs.abs().max())
+    assert ey < 2e-2 and eh < 2e-2, (ey, eh)
