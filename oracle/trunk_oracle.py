@@ -121,9 +121,22 @@ def masked_attention(
 
 
 def spatial_block(
-    x: torch.Tensor, alive: torch.Tensor | None, p: Params, n_heads: int, mode: str
+    x: torch.Tensor,
+    alive: torch.Tensor | None,
+    p: Params,
+    n_heads: int,
+    mode: str,
+    bullets: torch.Tensor | None = None,
+    bullet_mask: torch.Tensor | None = None,
 ) -> torch.Tensor:
-    """TransformerBlock.forward without bullets; attention.py:76-99,114-147,168-169."""
+    """TransformerBlock.forward; attention.py:76-99,114-169.
+
+    A sublayer reads bullets when its parameters hold ``kv_bullet.weight`` (the
+    reference's ``reads_bullets``) and ``bullets`` (B, NB, D) is given: a second
+    softmax over the environment's bullet keys, gated to zero for an environment with
+    no active bullet when a mask is given, summed with the self-attention output
+    before the shared output projection (attention.py:149-166).
+    """
     B, N, D = x.shape
     dh = D // n_heads
     n = rms_norm(x, p["norm1.weight"])
@@ -133,6 +146,16 @@ def spatial_block(
     k = k.view(B, N, n_heads, dh).permute(0, 2, 1, 3)
     v = v.view(B, N, n_heads, dh).permute(0, 2, 1, 3)
     o = masked_attention(q, k, v, alive, mode)
+    if bullets is not None and "kv_bullet.weight" in p:
+        NB = bullets.shape[1]
+        kvb = linear(rms_norm(bullets, p["norm_bullet.weight"]), p["kv_bullet.weight"], None, mode)
+        kb, vb = kvb.split(D, dim=-1)
+        kb = kb.view(B, NB, n_heads, dh).permute(0, 2, 1, 3)
+        vb = vb.view(B, NB, n_heads, dh).permute(0, 2, 1, 3)
+        ob = masked_attention(q, kb, vb, bullet_mask, mode)
+        if bullet_mask is not None:
+            ob = ob * bullet_mask.any(dim=-1)[:, None, None, None].to(ob.dtype)
+        o = _r(o + ob, mode)
     o = o.permute(0, 2, 1, 3).reshape(B, N, D)
     x1 = x + linear(o, p["out_proj.weight"], None, mode)
     m = rms_norm(x1, p["norm2.weight"])
@@ -247,18 +270,22 @@ def yemong_block_sequence(
     p: Params,
     n_heads: int,
     mode: str,
+    bullets: torch.Tensor | None = None,
+    bullet_mask: torch.Tensor | None = None,
 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """YemongBlock.sequence; griffin.py:419-472.
 
     x (T, B, NM, D), alive (T, B, NM) | None, h0 (nt, B*n_rec, D), conv0 (nt, B*n_rec, 3, D),
-    done (T, B) | None.
+    done (T, B) | None, bullets (T*B, NB, D) | None, bullet_mask (T*B, NB) | None.
     """
     T, B, NM, D = x.shape
     n_rec = NM if n_rec is None else n_rec
     ns, nt = block_counts(p)
     for j in range(ns):
         a = None if alive is None else alive.reshape(T * B, NM)
-        x = spatial_block(x.reshape(T * B, NM, D), a, _sub(p, f"spatial.{j}."), n_heads, mode).reshape(T, B, NM, D)
+        x = spatial_block(
+            x.reshape(T * B, NM, D), a, _sub(p, f"spatial.{j}."), n_heads, mode, bullets, bullet_mask
+        ).reshape(T, B, NM, D)
     done_rt = None if done is None else done.permute(1, 0).repeat_interleave(n_rec, dim=0)
     new_h, new_c = [], []
     for j in range(nt):
@@ -277,10 +304,11 @@ def yemong_block_sequence(
     return x, torch.stack(new_h), torch.stack(new_c)
 
 
-def yemong_block_step(x, alive, h, conv, n_rec, p, n_heads, mode):
+def yemong_block_step(x, alive, h, conv, n_rec, p, n_heads, mode, bullets=None, bullet_mask=None):
     """YemongBlock.step; griffin.py:376-417 (the T = 1 case of the sequence, no done)."""
     y, nh, nc = yemong_block_sequence(
-        x.unsqueeze(0), None if alive is None else alive.unsqueeze(0), h, conv, None, n_rec, p, n_heads, mode
+        x.unsqueeze(0), None if alive is None else alive.unsqueeze(0), h, conv, None, n_rec, p, n_heads, mode,
+        bullets, bullet_mask,
     )
     return y.squeeze(0), nh, nc
 
@@ -306,10 +334,13 @@ def trunk_step(
     blocks: Sequence[Params],
     n_heads: int,
     mode: str,
+    bullets: torch.Tensor | None = None,
+    bullet_mask: torch.Tensor | None = None,
 ) -> tuple[torch.Tensor, torch.Tensor]:
     """Trunk loop of get_action_and_value; policy.py:315-354.
 
-    x (B, NM, D) fp32, alive (B, NM) bool, hidden (L, B*n_rec, 4D) fp32.
+    x (B, NM, D) fp32, alive (B, NM) bool, hidden (L, B*n_rec, 4D) fp32,
+    bullets (B, NB, D) | None and bullet_mask (B, NB) | None.
     Returns the trunk output (B, NM, D) and the repacked new hidden.
     """
     B, NM, D = x.shape
@@ -319,7 +350,9 @@ def trunk_step(
     new_h, new_c = [], []
     for p in blocks:
         _, nt = block_counts(p)
-        x, nh, nc = yemong_block_step(x, alive, hs[slot : slot + nt], cs[slot : slot + nt], n_rec, p, n_heads, mode)
+        x, nh, nc = yemong_block_step(
+            x, alive, hs[slot : slot + nt], cs[slot : slot + nt], n_rec, p, n_heads, mode, bullets, bullet_mask
+        )
         slot += nt
         new_h.append(nh)
         new_c.append(nc)
@@ -336,10 +369,13 @@ def trunk_sequence(
     blocks: Sequence[Params],
     n_heads: int,
     mode: str,
+    bullets: torch.Tensor | None = None,
+    bullet_mask: torch.Tensor | None = None,
 ) -> tuple[torch.Tensor, torch.Tensor]:
     """Trunk loop of evaluate_actions; policy.py:422-478.
 
-    x (T, B, NM, D), alive (T, B, NM), hidden0 (L, B*n_rec, 4D), done (T, B) | None.
+    x (T, B, NM, D), alive (T, B, NM), hidden0 (L, B*n_rec, 4D), done (T, B) | None,
+    bullets (T*B, NB, D) | None, bullet_mask (T*B, NB) | None.
     Returns the trunk output and the final hidden (the reference drops the latter).
     """
     T, B, NM, D = x.shape
@@ -349,7 +385,9 @@ def trunk_sequence(
     new_h, new_c = [], []
     for p in blocks:
         _, nt = block_counts(p)
-        x, nh, nc = yemong_block_sequence(x, alive, hs[slot : slot + nt], cs[slot : slot + nt], done, n_rec, p, n_heads, mode)
+        x, nh, nc = yemong_block_sequence(
+            x, alive, hs[slot : slot + nt], cs[slot : slot + nt], done, n_rec, p, n_heads, mode, bullets, bullet_mask
+        )
         slot += nt
         new_h.append(nh)
         new_c.append(nc)

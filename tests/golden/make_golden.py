@@ -64,7 +64,12 @@ def team_alive(gen, B, n_ships, n_fields, p=0.9):
     return alive
 
 
+ONLY = ""
+
+
 def save(name, **arrays):
+    if not name.startswith(ONLY):
+        return
     out = {}
     for k, v in arrays.items():
         if isinstance(v, torch.Tensor):
@@ -82,7 +87,10 @@ def weights_as_arrays(sd, prefix="w::"):
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference/src")
+    ap.add_argument("--only", default="", help="write only the files whose name starts with this prefix")
     args = ap.parse_args()
+    global ONLY
+    ONLY = args.only
     sys.path.insert(0, args.reference)
 
     from boost_and_broadside.config import ModelConfig
@@ -165,7 +173,7 @@ def main() -> None:
         torch.manual_seed(0)
         return torch.nn.ModuleList([YemongBlock(c) for _ in range(c.n_yemong_blocks)]).eval()
 
-    def ref_step(layers, c, x, alive, hidden):
+    def ref_step(layers, c, x, alive, hidden, bullets=None, bullet_mask=None):
         """policy.py:315-354 restated with the reference's own blocks."""
         B, NM, D = x.shape
         L = hidden.shape[0]
@@ -177,14 +185,14 @@ def main() -> None:
         nh, nc = [], []
         for i, layer in enumerate(layers):
             sl = slice(i * nt, (i + 1) * nt)
-            x, h, cb = layer.step(x, alive, hs[sl], cs[sl], n_rec, None, None)
+            x, h, cb = layer.step(x, alive, hs[sl], cs[sl], n_rec, bullets, bullet_mask)
             nh.append(h)
             nc.append(cb)
         new_h = torch.cat(nh, dim=0)
         new_c = torch.cat(nc, dim=0).reshape(L, B_rec, (CONV_KERNEL - 1) * D)
         return x, torch.cat([new_h, new_c], dim=-1)
 
-    def ref_seq(layers, c, x, alive, hidden, done):
+    def ref_seq(layers, c, x, alive, hidden, done, bullets=None, bullet_mask=None):
         """policy.py:422-478 restated with the reference's own blocks."""
         T, B, NM, D = x.shape
         L = hidden.shape[0]
@@ -196,7 +204,7 @@ def main() -> None:
         nh, nc = [], []
         for i, layer in enumerate(layers):
             sl = slice(i * nt, (i + 1) * nt)
-            x, h, cb = layer.sequence(x, alive, hs[sl], cs[sl], done, n_rec, None, None)
+            x, h, cb = layer.sequence(x, alive, hs[sl], cs[sl], done, n_rec, bullets, bullet_mask)
             nh.append(h)
             nc.append(cb)
         new_h = torch.cat(nh, dim=0)
@@ -267,6 +275,77 @@ def main() -> None:
                            c.n_temporal_per_block, c.n_bullet_cross_per_block, N, M]),
             wsum=checksum(sd), **out, **(weights_as_arrays(sd) if store else {}),
         )
+
+    # ------------------------------------------------------------------ bullet cross-attention
+    def bullet_inputs(gen, B, NB, D):
+        """Encoded bullet tokens (the bullet encoder ends in an RMSNorm, so O(1) values) and
+        the active mask: env 1 has nothing in flight, env 2 a full ring buffer."""
+        bullets = torch.randn(B, NB, D, generator=gen)
+        mask = torch.rand(B, NB, generator=gen) < 0.5
+        if B > 1:
+            mask[1] = False
+        if B > 2:
+            mask[2] = True
+        return bullets, mask
+
+    for D, H, B, N, NB, tag in ((128, 4, 6, 12, 80, "d128_n12_nb80"), (32, 4, 4, 3, 7, "d32_n3_nb7")):
+        torch.manual_seed(0)
+        block = TransformerBlock(cfg(D, H), reads_bullets=True).eval()
+        gen = torch.Generator().manual_seed(5)
+        with torch.no_grad():
+            block.norm_bullet.weight.copy_(1.0 + 0.1 * torch.randn(D, generator=gen))
+        x = torch.randn(B, N, D, generator=gen)
+        alive = team_alive(gen, B, N, 0)
+        bullets, mask = bullet_inputs(gen, B, NB, D)
+        out = {}
+        for mode in ("fp32", "bf16"):
+            with torch.no_grad(), autocast(mode):
+                out["y_" + mode] = block(x, alive, bullets, mask).float()
+                out["y_nobmask_" + mode] = block(x, alive, bullets, None).float()
+                out["y_nobullets_" + mode] = block(x, alive).float()
+        save(
+            f"bullets_spatial_{tag}", x=x, alive=alive, bullets=bullets, bullet_mask=mask, dims=np.array([D, H]),
+            wsum=checksum(block.state_dict()), norm_bullet=block.norm_bullet.weight,
+            **out, **(weights_as_arrays(block.state_dict()) if D < 64 else {}),
+        )
+
+    c = cfg(128, 4, 2, 2, 1, 1)
+    layers = build_trunk(c)
+    sd = {f"yemong_layers.{k}": v for k, v in layers.state_dict().items()}
+    D = c.d_model
+    dims = np.array([D, c.n_heads, c.n_yemong_blocks, c.n_spatial_per_block, c.n_temporal_per_block,
+                     c.n_bullet_cross_per_block, 0, 0])
+
+    B, N, M, NB = 5, 8, 4, 80
+    gen = torch.Generator().manual_seed(6)
+    x = torch.randn(B, N + M, D, generator=gen)
+    alive = team_alive(gen, B, N, M)
+    hidden = torch.randn(c.n_hidden_layers, B * N, CONV_KERNEL * D, generator=gen) * 0.5
+    bullets, mask = bullet_inputs(gen, B, NB, D)
+    out = {}
+    for mode in ("fp32", "bf16"):
+        with torch.no_grad(), autocast(mode):
+            y, nh = ref_step(layers, c, x, alive, hidden, bullets, mask)
+            out["y_" + mode], out["hidden_" + mode] = y.float(), nh.float()
+    dims[6:] = (N, M)
+    save("bullets_trunk_step_d128_8s4f", x=x, alive=alive, hidden=hidden, bullets=bullets, bullet_mask=mask,
+         dims=dims.copy(), wsum=checksum(sd), **out)
+
+    T, B, N, M, NB = 4, 3, 4, 2, 12
+    gen = torch.Generator().manual_seed(7)
+    x = torch.randn(T, B, N + M, D, generator=gen)
+    alive = team_alive(gen, T * B, N, M).reshape(T, B, N + M)
+    hidden = torch.randn(c.n_hidden_layers, B * N, CONV_KERNEL * D, generator=gen) * 0.5
+    done = torch.rand(T, B, generator=gen) < 0.3
+    bullets, mask = bullet_inputs(gen, T * B, NB, D)
+    out = {}
+    for mode in ("fp32", "bf16"):
+        with torch.no_grad(), autocast(mode):
+            y, nh = ref_seq(layers, c, x, alive, hidden, done, bullets, mask)
+            out["y_" + mode], out["hidden_" + mode] = y.float(), nh.float()
+    dims[6:] = (N, M)
+    save("bullets_trunk_seq_d128_t4_4s2f", x=x, alive=alive, hidden=hidden, done=done, bullets=bullets,
+         bullet_mask=mask, dims=dims.copy(), wsum=checksum(sd), **out)
 
 
 if __name__ == "__main__":

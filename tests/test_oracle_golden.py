@@ -128,3 +128,56 @@ def test_ragged_grouping_matches_uniform():
     y0, h0 = O.trunk_step(g["x"], g["alive"], g["hidden"], P, 4, "fp32")
     y1, h1 = O.trunk_step_ragged(g["x"].reshape(-1, D), g["alive"].reshape(-1), g["hidden"], [NM] * B, [8] * B, P, 4, "fp32")
     assert torch.equal(y0.reshape(-1, D), y1) and torch.equal(h0, h1)
+
+
+# ----------------------------------------------------------------------------- bullet cross-attention
+
+
+def _bullet_spatial_params(g, D, H):
+    w = stored_weights(g)
+    if w:
+        return w
+    from boost_and_broadside_b200 import ModelConfig, TransformerBlock
+
+    torch.manual_seed(0)
+    p = dict(TransformerBlock(ModelConfig(D, H, 2), reads_bullets=True).state_dict())
+    p["norm_bullet.weight"] = g["norm_bullet"]
+    return p
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("name", ["bullets_spatial_d128_n12_nb80", "bullets_spatial_d32_n3_nb7"])
+def test_spatial_block_with_bullets(name, mode):
+    """attention.py:149-166: second softmax over bullet keys, gated per environment."""
+    g = golden(name)
+    D, H = (int(v) for v in g["dims"])
+    p = _bullet_spatial_params(g, D, H)
+    assert not g["bullet_mask"][1].any() and g["bullet_mask"][2].all()
+    y = O.spatial_block(g["x"], g["alive"], p, H, mode, g["bullets"], g["bullet_mask"])
+    assert_close(y, g["y_" + mode], mode, name)
+    y = O.spatial_block(g["x"], g["alive"], p, H, mode, g["bullets"], None)
+    assert_close(y, g["y_nobmask_" + mode], mode, name + " (no bullet mask)")
+    y0 = O.spatial_block(g["x"], g["alive"], p, H, mode)
+    assert_close(y0, g["y_nobullets_" + mode], mode, name + " (no bullets)")
+    # an environment with nothing in flight gets exactly the bullet-free result
+    y = O.spatial_block(g["x"], g["alive"], p, H, mode, g["bullets"], g["bullet_mask"])
+    assert torch.equal(y[1], y0[1])
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_trunk_step_with_bullets(mode):
+    g = golden("bullets_trunk_step_d128_8s4f")
+    trunk = build_trunk(g["dims"], g)
+    y, nh = O.trunk_step(g["x"], g["alive"], g["hidden"], trunk_params(trunk), 4, mode, g["bullets"], g["bullet_mask"])
+    assert_close(y, g["y_" + mode], mode, "bullets step y")
+    assert_close(nh, g["hidden_" + mode], mode, "bullets step hidden")
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_trunk_sequence_with_bullets(mode):
+    g = golden("bullets_trunk_seq_d128_t4_4s2f")
+    trunk = build_trunk(g["dims"], g)
+    y, nh = O.trunk_sequence(g["x"], g["alive"], g["hidden"], g["done"], trunk_params(trunk), 4, mode,
+                             g["bullets"], g["bullet_mask"])
+    assert_close(y, g["y_" + mode], mode, "bullets sequence y")
+    assert_close(nh, g["hidden_" + mode], mode, "bullets sequence hidden")
