@@ -17,13 +17,18 @@ LIB_PATH = os.path.join(_HERE, "libbnb_trunk.so")
 
 BNB_FP32, BNB_BF16 = 0, 1
 ENGINE_AUTO, ENGINE_SIMT, ENGINE_TENSOR = 0, 1, 2
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 _fp = C.c_void_p
 
 
 class SpatialWeights(C.Structure):
-    _fields_ = [(n, _fp) for n in ("norm1_w", "qkv_w", "out_w", "norm2_w", "gate_w", "up_w", "down_w", "packed")]
+    _fields_ = [(n, _fp) for n in ("norm1_w", "qkv_w", "out_w", "norm2_w", "gate_w", "up_w", "down_w",
+                                   "norm_bullet_w", "kv_bullet_w", "packed")]
+
+
+class Bullets(C.Structure):
+    _fields_ = [("tokens", _fp), ("active", _fp), ("per_env", C.c_int32)]
 
 
 class TemporalWeights(C.Structure):
@@ -58,11 +63,11 @@ EXPORTS = {
     "bnb_launch_count": (C.c_ulonglong, []),
     "bnb_supported": (C.c_int, [C.c_int] * 5),
     "bnb_plan_tiles": (C.c_int, [_fp, C.c_int, _fp, _fp, C.c_int, C.POINTER(C.c_int)]),
-    "bnb_scratch_bytes": (C.c_size_t, [C.c_int, C.POINTER(Batch), C.c_int]),
+    "bnb_scratch_bytes": (C.c_size_t, [C.c_int, C.POINTER(Batch), C.c_int, C.c_int]),
     "bnb_spatial_block_fwd": (
         C.c_int,
-        [C.POINTER(SpatialWeights), C.c_int, C.c_int, _fp, _fp, _fp, C.POINTER(Batch), C.c_int, C.c_int, C.c_int,
-         _fp, C.c_size_t, _fp],
+        [C.POINTER(SpatialWeights), C.c_int, C.c_int, _fp, _fp, C.POINTER(Bullets), _fp, C.POINTER(Batch), C.c_int,
+         C.c_int, C.c_int, _fp, C.c_size_t, _fp],
     ),
     "bnb_spatial_block_fwd_static": (
         C.c_int,
@@ -76,12 +81,13 @@ EXPORTS = {
     "bnb_trunk_step": (
         C.c_int,
         [C.POINTER(SpatialWeights), C.POINTER(TemporalWeights), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
-         _fp, _fp, _fp, _fp, _fp, _fp, C.POINTER(Batch), C.c_int, C.c_int, _fp, C.c_size_t, _fp],
+         _fp, _fp, C.POINTER(Bullets), _fp, _fp, _fp, _fp, C.POINTER(Batch), C.c_int, C.c_int, _fp, C.c_size_t, _fp],
     ),
     "bnb_trunk_sequence": (
         C.c_int,
         [C.POINTER(SpatialWeights), C.POINTER(TemporalWeights), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
-         _fp, _fp, _fp, _fp, _fp, _fp, C.POINTER(Batch), C.c_int, C.c_int, C.c_int, _fp, C.c_size_t, _fp],
+         _fp, _fp, C.POINTER(Bullets), _fp, _fp, _fp, _fp, C.POINTER(Batch), C.c_int, C.c_int, C.c_int, _fp, C.c_size_t,
+         _fp],
     ),
     "bnb_reset_hidden": (C.c_int, [_fp, _fp, _fp, C.c_int, C.c_int, C.POINTER(Batch), _fp]),
     "bnb_packed_spatial_bytes": (C.c_size_t, [C.c_int]),
@@ -178,6 +184,34 @@ def scratch_for(device: torch.device, nbytes: int) -> torch.Tensor:
         buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _scratch[key] = buf
     return buf
+
+
+class BulletArgs:
+    """The bullet tokens of a call in the form the C ABI takes, or ``None`` for a call without.
+
+    ``bullets`` (E, NB, D) float and ``bullet_mask`` (E, NB) bool | None, E = the number of
+    environments of the call (T*B for a sequence); models/yemong/attention.py:85-87.
+    Holds the converted tensors so they outlive the asynchronous launch.
+    """
+
+    def __init__(self, bullets: Optional[torch.Tensor], bullet_mask: Optional[torch.Tensor], n_envs: int, d_model: int):
+        self.struct = None
+        self.per_env = 0
+        if bullets is None:
+            return
+        if bullets.dim() != 3 or bullets.shape[0] != n_envs or bullets.shape[2] != d_model or bullets.shape[1] < 1:
+            raise RuntimeError(f"bullets must have shape ({n_envs}, NB >= 1, {d_model}), got {tuple(bullets.shape)}")
+        require_cuda(bullets, "bullets")
+        if bullet_mask is not None and tuple(bullet_mask.shape) != tuple(bullets.shape[:2]):
+            raise RuntimeError(f"bullet_mask must have shape {tuple(bullets.shape[:2])}, got {tuple(bullet_mask.shape)}")
+        self.tokens = f32c(bullets)
+        self.active = u8(bullet_mask)
+        self.per_env = int(bullets.shape[1])
+        self.struct = Bullets(self.tokens.data_ptr(), ptr(self.active), self.per_env)
+
+    @property
+    def arg(self):
+        return None if self.struct is None else C.byref(self.struct)
 
 
 def uniform_batch(n_envs: int, tokens: int, ships: int) -> Batch:

@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 
 #include "bnb_trunk.h"
+#include "bullet_slices.h"
 #include "exact_kernels.h"
 #include "launch_count.h"
 #include "tensor_kernels.h"
@@ -48,7 +49,24 @@ int check_spatial(const BnbSpatialWeights* w) {
     if (!p) return BNB_ERR_NULL_POINTER;
     if (!aligned16(p)) return BNB_ERR_MISALIGNED;
   }
+  if ((w->norm_bullet_w == nullptr) != (w->kv_bullet_w == nullptr)) return BNB_ERR_NULL_POINTER;
+  if (!aligned16(w->norm_bullet_w) || !aligned16(w->kv_bullet_w)) return BNB_ERR_MISALIGNED;
   return BNB_OK;
+}
+
+// bullets may be null (no cross-attention in this call); otherwise it must be complete.
+int check_bullets(const BnbBullets* b) {
+  if (!b) return BNB_OK;
+  if (!b->tokens) return BNB_ERR_NULL_POINTER;
+  if (!aligned16(b->tokens)) return BNB_ERR_MISALIGNED;
+  if (b->per_env < 1) return BNB_ERR_BAD_ARGUMENT;
+  return BNB_OK;
+}
+
+bool any_reads_bullets(const BnbSpatialWeights* s, int ns, const BnbBullets* b) {
+  if (!b) return false;
+  for (int i = 0; i < ns; ++i) if (s[i].kv_bullet_w) return true;
+  return false;
 }
 
 int check_temporal(const BnbTemporalWeights* w, bool need_field) {
@@ -71,17 +89,32 @@ size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 struct Scratch {
   float* qkv;
   float* o;
+  float* kvb;     // bullet keys and values of one slice of environments, or null
+  int kvb_envs;   // environments per slice
 };
 
-// SIMT spatial scratch: qkv (rows, 3D) then o (rows, D), float32.
-int carve(void* scratch, size_t bytes, size_t n_rows, int D, Scratch* out) {
-  size_t need = round_up(n_rows * 3 * D * sizeof(float), 256) + round_up(n_rows * D * sizeof(float), 256);
-  if (need == 0) { out->qkv = out->o = nullptr; return BNB_OK; }
+size_t simt_scratch_bytes(size_t n_rows, int D, long long total_envs, int nb) {
+  return round_up(n_rows * 3 * D * sizeof(float), 256) + round_up(n_rows * D * sizeof(float), 256) +
+         round_up(bnb::bullet_slice_bytes(total_envs, nb, D, sizeof(float)), 256);
+}
+
+// SIMT spatial scratch: qkv (rows, 3D), o (rows, D), then the bullet slice, float32.
+int carve(void* scratch, size_t bytes, size_t n_rows, int D, long long total_envs, int nb, Scratch* out) {
+  size_t need = simt_scratch_bytes(n_rows, D, total_envs, nb);
+  *out = Scratch{nullptr, nullptr, nullptr, 0};
+  if (need == 0) return BNB_OK;
   if (!scratch) return BNB_ERR_NULL_POINTER;
   if (!aligned16(scratch)) return BNB_ERR_MISALIGNED;
   if (bytes < need) return BNB_ERR_SCRATCH_TOO_SMALL;
-  out->qkv = static_cast<float*>(scratch);
-  out->o = reinterpret_cast<float*>(static_cast<char*>(scratch) + round_up(n_rows * 3 * D * sizeof(float), 256));
+  char* p = static_cast<char*>(scratch);
+  out->qkv = reinterpret_cast<float*>(p);
+  p += round_up(n_rows * 3 * D * sizeof(float), 256);
+  out->o = reinterpret_cast<float*>(p);
+  p += round_up(n_rows * D * sizeof(float), 256);
+  if (nb > 0 && total_envs > 0) {
+    out->kvb = reinterpret_cast<float*>(p);
+    out->kvb_envs = bnb::bullet_slice_envs(total_envs, nb, D, sizeof(float));
+  }
   return BNB_OK;
 }
 
@@ -137,21 +170,25 @@ int bnb_plan_tiles(const int32_t* tok_off_host, int n_envs, int32_t* tile_env_be
   return bnb::tensor::plan_tiles(tok_off_host, n_envs, tile_env_begin_host, tile_env_ids_host, capacity, n_tiles);
 }
 
-size_t bnb_scratch_bytes(int d_model, const BnbBatch* batch, int timesteps) {
+size_t bnb_scratch_bytes(int d_model, const BnbBatch* batch, int timesteps, int bullets_per_env) {
   if (!batch || d_model <= 0 || timesteps <= 0) return 0;
+  if (bullets_per_env < 0) bullets_per_env = 0;
   size_t n_rows = (size_t)timesteps * (size_t)batch->total_tokens;
-  size_t simt = round_up(n_rows * 3 * d_model * sizeof(float), 256) + round_up(n_rows * d_model * sizeof(float), 256);
+  size_t simt = simt_scratch_bytes(n_rows, d_model, (long long)timesteps * batch->n_envs, bullets_per_env);
   size_t tc = bnb::tensor::scratch_bytes(d_model, *batch, timesteps);
   return (simt > tc ? simt : tc) + 256;
 }
 
 int bnb_spatial_block_fwd(const BnbSpatialWeights* w, int d_model, int n_heads, const float* x,
-                          const uint8_t* alive, float* y, const BnbBatch* batch, int n_groups,
-                          int precision, int engine, void* scratch, size_t scratch_bytes, void* stream) {
+                          const uint8_t* alive, const BnbBullets* bullets, float* y, const BnbBatch* batch,
+                          int n_groups, int precision, int engine, void* scratch, size_t scratch_bytes,
+                          void* stream) {
   int st = check_dims(d_model, n_heads);
   if (st) return st;
   if ((st = check_batch(batch))) return st;
   if ((st = check_spatial(w))) return st;
+  if ((st = check_bullets(bullets))) return st;
+  if (!any_reads_bullets(w, 1, bullets)) bullets = nullptr;
   if (n_groups < 0) return BNB_ERR_BAD_ARGUMENT;
   if (precision != BNB_FP32 && precision != BNB_BF16) return BNB_ERR_BAD_ARGUMENT;
   size_t n_rows = (size_t)n_groups * batch->total_tokens;
@@ -159,13 +196,16 @@ int bnb_spatial_block_fwd(const BnbSpatialWeights* w, int d_model, int n_heads, 
   if (!x || !y) return BNB_ERR_NULL_POINTER;
   if (!aligned16(x) || !aligned16(y)) return BNB_ERR_MISALIGNED;
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
-  if (use_tensor(precision, engine, d_model, n_heads, batch) && (w->packed || engine == BNB_ENGINE_TENSOR))
-    return bnb::tensor::spatial_block(*w, d_model, n_heads, x, alive, y, *batch, n_groups, scratch, scratch_bytes, cs);
+  if (!bullets && use_tensor(precision, engine, d_model, n_heads, batch) && (w->packed || engine == BNB_ENGINE_TENSOR))
+    return bnb::tensor::spatial_block(*w, d_model, n_heads, x, alive, y, *batch, n_groups, scratch,
+                                      scratch_bytes, cs);
   if (engine == BNB_ENGINE_TENSOR) return BNB_ERR_UNSUPPORTED_DIMS;
   Scratch s;
-  if ((st = carve(scratch, scratch_bytes, n_rows, d_model, &s))) return st;
-  return bnb::exact::spatial_block(*w, d_model, n_heads, x, alive, y, *batch, n_groups, precision == BNB_BF16,
-                                   s.qkv, s.o, cs);
+  if ((st = carve(scratch, scratch_bytes, n_rows, d_model, (long long)n_groups * batch->n_envs,
+                  bullets ? bullets->per_env : 0, &s)))
+    return st;
+  return bnb::exact::spatial_block(*w, d_model, n_heads, x, alive, bullets, y, *batch, n_groups,
+                                   precision == BNB_BF16, s.qkv, s.o, s.kvb, s.kvb_envs, cs);
 }
 
 int bnb_temporal_block_fwd(const BnbTemporalWeights* w, int d_model, const float* x, float* y,
@@ -193,7 +233,7 @@ int bnb_temporal_block_fwd(const BnbTemporalWeights* w, int d_model, const float
 
 static int trunk_common(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal, int n_blocks,
                         int n_spatial, int n_temporal, int D, int H, const float* x, const uint8_t* alive,
-                        float* y, const float* hidden_in, float* hidden_out, const uint8_t* done,
+                        const BnbBullets* bullets, float* y, const float* hidden_in, float* hidden_out, const uint8_t* done,
                         const uint8_t* reset_env, const BnbBatch* batch, int T, int precision, int engine,
                         void* scratch, size_t scratch_bytes, void* stream, bool is_sequence) {
   int st = check_dims(D, H);
@@ -207,6 +247,8 @@ static int trunk_common(const BnbSpatialWeights* spatial, const BnbTemporalWeigh
     if ((st = check_spatial(&spatial[i]))) return st;
   for (int i = 0; i < n_blocks * n_temporal; ++i)
     if ((st = check_temporal(&temporal[i], batch->total_tokens > batch->total_ships))) return st;
+  if ((st = check_bullets(bullets))) return st;
+  if (!any_reads_bullets(spatial, n_blocks * n_spatial, bullets)) bullets = nullptr;
   size_t n_rows = (size_t)T * batch->total_tokens;
   if (n_rows == 0) return BNB_OK;
   if (!x || !y) return BNB_ERR_NULL_POINTER;
@@ -216,14 +258,16 @@ static int trunk_common(const BnbSpatialWeights* spatial, const BnbTemporalWeigh
   if (has_state && !is_sequence && !hidden_out) return BNB_ERR_NULL_POINTER;
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
 
-  if (use_tensor(precision, engine, D, H, batch) &&
+  if (!bullets && use_tensor(precision, engine, D, H, batch) &&
       (engine == BNB_ENGINE_TENSOR || all_packed(spatial, n_blocks * n_spatial, temporal, n_blocks * n_temporal)))
     return bnb::tensor::trunk(spatial, temporal, n_blocks, n_spatial, n_temporal, D, H, x, alive, y, hidden_in,
                               hidden_out, done, reset_env, *batch, T, scratch, scratch_bytes, cs);
   if (engine == BNB_ENGINE_TENSOR) return BNB_ERR_UNSUPPORTED_DIMS;
 
-  Scratch s{nullptr, nullptr};
-  if (n_blocks * n_spatial > 0 && (st = carve(scratch, scratch_bytes, n_rows, D, &s))) return st;
+  Scratch s{nullptr, nullptr, nullptr, 0};
+  if (n_blocks * n_spatial > 0 &&
+      (st = carve(scratch, scratch_bytes, n_rows, D, (long long)T * batch->n_envs, bullets ? bullets->per_env : 0, &s)))
+    return st;
   const bool emu = precision == BNB_BF16;
   const float* cur = x;
   const size_t slot_stride = (size_t)batch->total_ships * 4 * D;
@@ -234,7 +278,8 @@ static int trunk_common(const BnbSpatialWeights* spatial, const BnbTemporalWeigh
   }
   for (int i = 0; i < n_blocks; ++i) {
     for (int j = 0; j < n_spatial; ++j) {
-      st = bnb::exact::spatial_block(spatial[i * n_spatial + j], D, H, cur, alive, y, *batch, T, emu, s.qkv, s.o, cs);
+      st = bnb::exact::spatial_block(spatial[i * n_spatial + j], D, H, cur, alive, bullets, y, *batch, T, emu, s.qkv,
+                                     s.o, s.kvb, s.kvb_envs, cs);
       if (st) return st;
       cur = y;
     }
@@ -252,21 +297,21 @@ static int trunk_common(const BnbSpatialWeights* spatial, const BnbTemporalWeigh
 
 int bnb_trunk_step(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal, int n_blocks,
                    int n_spatial, int n_temporal, int d_model, int n_heads, const float* x,
-                   const uint8_t* alive, float* y, const float* hidden_in, float* hidden_out,
-                   const uint8_t* reset_env, const BnbBatch* batch, int precision, int engine,
+                   const uint8_t* alive, const BnbBullets* bullets, float* y, const float* hidden_in,
+                   float* hidden_out, const uint8_t* reset_env, const BnbBatch* batch, int precision, int engine,
                    void* scratch, size_t scratch_bytes, void* stream) {
-  return trunk_common(spatial, temporal, n_blocks, n_spatial, n_temporal, d_model, n_heads, x, alive, y, hidden_in,
-                      hidden_out, nullptr, reset_env, batch, 1, precision, engine, scratch, scratch_bytes, stream,
+  return trunk_common(spatial, temporal, n_blocks, n_spatial, n_temporal, d_model, n_heads, x, alive, bullets, y,
+                      hidden_in, hidden_out, nullptr, reset_env, batch, 1, precision, engine, scratch, scratch_bytes, stream,
                       false);
 }
 
 int bnb_trunk_sequence(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal, int n_blocks,
                        int n_spatial, int n_temporal, int d_model, int n_heads, const float* x,
-                       const uint8_t* alive, float* y, const float* hidden_in, float* hidden_out,
-                       const uint8_t* done, const BnbBatch* batch, int timesteps, int precision, int engine,
+                       const uint8_t* alive, const BnbBullets* bullets, float* y, const float* hidden_in,
+                       float* hidden_out, const uint8_t* done, const BnbBatch* batch, int timesteps, int precision, int engine,
                        void* scratch, size_t scratch_bytes, void* stream) {
-  return trunk_common(spatial, temporal, n_blocks, n_spatial, n_temporal, d_model, n_heads, x, alive, y, hidden_in,
-                      hidden_out, done, nullptr, batch, timesteps, precision, engine, scratch, scratch_bytes, stream,
+  return trunk_common(spatial, temporal, n_blocks, n_spatial, n_temporal, d_model, n_heads, x, alive, bullets, y,
+                      hidden_in, hidden_out, done, nullptr, batch, timesteps, precision, engine, scratch, scratch_bytes, stream,
                       true);
 }
 

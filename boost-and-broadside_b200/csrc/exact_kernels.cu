@@ -129,10 +129,11 @@ __device__ __forceinline__ void tile_gated_mlp(const float* Nrm, float* P, int l
 }
 
 // ------------------------------------------------------------------ spatial, stage 1
-// qkv = Linear(rmsnorm(x))  -> (rows, 3D) float32 scratch (values bf16-rounded for EMU)
+// qkv = Linear(rmsnorm(x))  -> (rows, n_out) float32 scratch (values bf16-rounded for EMU).
+// n_out = 3D for the entity tokens (qkv), 2D for the bullet tokens (kv_bullet of norm_bullet).
 template <bool EMU>
 __global__ void __launch_bounds__(NTHREADS)
-k_spatial_qkv(const float* __restrict__ x, float* __restrict__ qkv, int n_rows, int D,
+k_spatial_qkv(const float* __restrict__ x, float* __restrict__ qkv, int n_rows, int D, int n_out,
               const float* __restrict__ g1, const float* __restrict__ Wqkv) {
   extern __shared__ __align__(16) float smem[];
   const int ld = D + 4;
@@ -150,8 +151,8 @@ k_spatial_qkv(const float* __restrict__ x, float* __restrict__ qkv, int n_rows, 
   }
   __syncthreads();
   tile_rmsnorm<EMU>(X, Nrm, ld, D, g1, n_valid);
-  for (int c0 = 0; c0 < 3 * D; c0 += NCHUNK) {
-    int cn = min(NCHUNK, 3 * D - c0);
+  for (int c0 = 0; c0 < n_out; c0 += NCHUNK) {
+    int cn = min(NCHUNK, n_out - c0);
     float acc[4][4];
     zero_acc(acc);
     tile_linear<EMU>(Nrm, ld, Wqkv + (size_t)c0 * D, D, cn, D, Ws, acc);
@@ -162,26 +163,78 @@ k_spatial_qkv(const float* __restrict__ x, float* __restrict__ qkv, int n_rows, 
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           int c = lane + 32 * j;
-          if (c < cn) qkv[(size_t)(row0 + r) * 3 * D + c0 + c] = rnd<EMU>(acc[i][j]);
+          if (c < cn) qkv[(size_t)(row0 + r) * n_out + c0 + c] = rnd<EMU>(acc[i][j]);
         }
     }
   }
 }
 
 // ------------------------------------------------------------------ spatial, stage 2
-// Masked softmax attention inside each environment, one thread per (query token, head),
-// single pass with a running maximum.  A dead key scores kMaskedScore, so its weight is
-// exactly 0 while any key of the environment is alive, and an environment with no live
-// key gives every key weight 1/n (attention.py:101-112 with finfo.min/2 as the bias).
+// One softmax(q k^T / sqrt(dh) + bias) v over n keys, single pass with a running maximum.
+// Key j sits at kbase + j * stride, its value `voff` floats after it.  A masked key scores
+// kMaskedScore, so its weight is exactly 0 while any key is live, and when none is live
+// every key gets weight 1/n (attention.py:101-112 with finfo.min/2 as the bias).
+template <int DH>
+__device__ __forceinline__ void attend(const float (&q)[DH], const float* __restrict__ kbase, size_t stride,
+                                       int voff, int n, const uint8_t* __restrict__ mask, float scale,
+                                       float (&acc)[DH]) {
+#pragma unroll
+  for (int d = 0; d < DH; ++d) acc[d] = 0.f;
+  float m = -INFINITY, l = 0.f;
+  for (int j = 0; j < n; ++j) {
+    const float* kp = kbase + (size_t)j * stride;
+    float s = 0.f;
+#pragma unroll
+    for (int d = 0; d < DH; d += 4) {
+      float4 v = *reinterpret_cast<const float4*>(kp + d);
+      s = fmaf(q[d], v.x, s); s = fmaf(q[d + 1], v.y, s);
+      s = fmaf(q[d + 2], v.z, s); s = fmaf(q[d + 3], v.w, s);
+    }
+    s *= scale;
+    if (mask && !mask[j]) s = kMaskedScore;
+    float mn = fmaxf(m, s);
+    float corr = expf(m - mn);   // m = -inf on the first key: exp(-inf) = 0
+    float pj = expf(s - mn);
+    l = l * corr + pj;
+    const float* vp = kp + voff;
+#pragma unroll
+    for (int d = 0; d < DH; d += 4) {
+      float4 v = *reinterpret_cast<const float4*>(vp + d);
+      acc[d] = fmaf(pj, v.x, acc[d] * corr);
+      acc[d + 1] = fmaf(pj, v.y, acc[d + 1] * corr);
+      acc[d + 2] = fmaf(pj, v.z, acc[d + 2] * corr);
+      acc[d + 3] = fmaf(pj, v.w, acc[d + 3] * corr);
+    }
+    m = mn;
+  }
+  float inv = 1.0f / l;
+#pragma unroll
+  for (int d = 0; d < DH; ++d) acc[d] *= inv;
+}
+
+// Masked attention inside each environment, one thread per (query token, head): self-attention
+// over the environment's tokens and, when kvb is given, a second softmax over its bullet keys
+// (kvb holds nb rows of [k (D) | v (D)] per environment of this launch's slice), gated to zero
+// for an environment with no active bullet, and summed before the output projection
+// (attention.py:149-166).  env_base is the first environment (group-major) of the slice.
 template <bool EMU, int DH>
 __global__ void __launch_bounds__(128)
 k_attention(const float* __restrict__ qkv, const uint8_t* __restrict__ alive, float* __restrict__ o,
-            EnvMap map, int n_groups, int D, int H) {
-  const int env_g = blockIdx.x;  // group-major environment index
+            EnvMap map, int env_base, int D, int H, const float* __restrict__ kvb,
+            const uint8_t* __restrict__ bullet_active, int nb) {
+  const int env_g = env_base + blockIdx.x;  // group-major environment index
   const int grp = env_g / map.n_envs, e = env_g - grp * map.n_envs;
   const int tok0 = grp * map.total_tokens + map.env_tok_begin(e);
   const int n = map.env_tok_count(e);
   const float scale = rsqrtf((float)DH);
+  float gate = 1.f;
+  const uint8_t* bmask = nullptr;
+  if (kvb && bullet_active) {
+    bmask = bullet_active + (size_t)env_g * nb;
+    int any = 0;
+    for (int j = 0; j < nb; ++j) any |= bmask[j];
+    gate = any ? 1.f : 0.f;
+  }
   for (int p = blockIdx.y * blockDim.x + threadIdx.x; p < n * H; p += gridDim.y * blockDim.x) {
     const int qi = p / H, h = p - qi * H;
     const float* qp = qkv + (size_t)(tok0 + qi) * 3 * D + h * DH;
@@ -190,42 +243,25 @@ k_attention(const float* __restrict__ qkv, const uint8_t* __restrict__ alive, fl
     for (int d = 0; d < DH; d += 4) {
       float4 v = *reinterpret_cast<const float4*>(qp + d);
       q[d] = v.x; q[d + 1] = v.y; q[d + 2] = v.z; q[d + 3] = v.w;
-      acc[d] = acc[d + 1] = acc[d + 2] = acc[d + 3] = 0.f;
     }
-    float m = -INFINITY, l = 0.f;
-    for (int j = 0; j < n; ++j) {
-      const float* kp = qkv + (size_t)(tok0 + j) * 3 * D + D + h * DH;
-      float s = 0.f;
-#pragma unroll
-      for (int d = 0; d < DH; d += 4) {
-        float4 v = *reinterpret_cast<const float4*>(kp + d);
-        s = fmaf(q[d], v.x, s); s = fmaf(q[d + 1], v.y, s);
-        s = fmaf(q[d + 2], v.z, s); s = fmaf(q[d + 3], v.w, s);
-      }
-      s *= scale;
-      if (alive && !alive[tok0 + j]) s = kMaskedScore;
-      float mn = fmaxf(m, s);
-      float corr = expf(m - mn);   // m = -inf on the first key: exp(-inf) = 0
-      float pj = expf(s - mn);
-      l = l * corr + pj;
-      const float* vp = kp + D;
-#pragma unroll
-      for (int d = 0; d < DH; d += 4) {
-        float4 v = *reinterpret_cast<const float4*>(vp + d);
-        acc[d] = fmaf(pj, v.x, acc[d] * corr);
-        acc[d + 1] = fmaf(pj, v.y, acc[d + 1] * corr);
-        acc[d + 2] = fmaf(pj, v.z, acc[d + 2] * corr);
-        acc[d + 3] = fmaf(pj, v.w, acc[d + 3] * corr);
-      }
-      m = mn;
-    }
-    float inv = 1.0f / l;
+    attend<DH>(q, qkv + (size_t)tok0 * 3 * D + D + h * DH, (size_t)3 * D, D, n,
+               alive ? alive + tok0 : nullptr, scale, acc);
     float* op = o + (size_t)(tok0 + qi) * D + h * DH;
 #pragma unroll
-    for (int d = 0; d < DH; d += 4) {
-      float4 v = make_float4(rnd<EMU>(acc[d] * inv), rnd<EMU>(acc[d + 1] * inv),
-                             rnd<EMU>(acc[d + 2] * inv), rnd<EMU>(acc[d + 3] * inv));
-      *reinterpret_cast<float4*>(op + d) = v;
+    for (int d = 0; d < DH; d += 4)
+      *reinterpret_cast<float4*>(op + d) = make_float4(rnd<EMU>(acc[d]), rnd<EMU>(acc[d + 1]),
+                                                       rnd<EMU>(acc[d + 2]), rnd<EMU>(acc[d + 3]));
+    if (kvb) {
+      attend<DH>(q, kvb + (size_t)blockIdx.x * nb * 2 * D + h * DH, (size_t)2 * D, D, nb, bmask, scale, acc);
+#pragma unroll
+      for (int d = 0; d < DH; d += 4) {
+        float4 s = *reinterpret_cast<const float4*>(op + d);   // this thread's own write above
+        s.x = rnd<EMU>(s.x + rnd<EMU>(acc[d]) * gate);
+        s.y = rnd<EMU>(s.y + rnd<EMU>(acc[d + 1]) * gate);
+        s.z = rnd<EMU>(s.z + rnd<EMU>(acc[d + 2]) * gate);
+        s.w = rnd<EMU>(s.w + rnd<EMU>(acc[d + 3]) * gate);
+        *reinterpret_cast<float4*>(op + d) = s;
+      }
     }
   }
 }
@@ -528,30 +564,50 @@ static bool opt_in(K kernel, size_t bytes) {
 }
 
 template <bool EMU>
+static int launch_attention(const float* qkv, const uint8_t* alive, float* o, const EnvMap& map, int env_base,
+                            int n_env, int max_tokens, int D, int H, const float* kvb, const uint8_t* active,
+                            int nb, cudaStream_t st) {
+  int per_env = max_tokens * H;
+  int gy = (per_env + 127) / 128;
+  dim3 grid(n_env, gy > 4 ? 4 : (gy < 1 ? 1 : gy));
+  count_launch();
+  switch (D / H) {
+    case 8:  k_attention<EMU, 8><<<grid, 128, 0, st>>>(qkv, alive, o, map, env_base, D, H, kvb, active, nb); break;
+    case 16: k_attention<EMU, 16><<<grid, 128, 0, st>>>(qkv, alive, o, map, env_base, D, H, kvb, active, nb); break;
+    case 32: k_attention<EMU, 32><<<grid, 128, 0, st>>>(qkv, alive, o, map, env_base, D, H, kvb, active, nb); break;
+    case 64: k_attention<EMU, 64><<<grid, 128, 0, st>>>(qkv, alive, o, map, env_base, D, H, kvb, active, nb); break;
+    default: return BNB_ERR_UNSUPPORTED_DIMS;
+  }
+  return BNB_OK;
+}
+
+template <bool EMU>
 static int spatial_impl(const BnbSpatialWeights& w, int D, int H, const float* x, const uint8_t* alive,
-                        float* y, const BnbBatch& b, int n_groups, float* qkv, float* o, cudaStream_t st) {
+                        const BnbBullets* bul, float* y, const BnbBatch& b, int n_groups, float* qkv, float* o,
+                        float* kvb, int kvb_envs, cudaStream_t st) {
   const int n_rows = n_groups * b.total_tokens;
   const int n_tiles = (n_rows + ROWS - 1) / ROWS;
-  {
-    size_t sm = (size_t)(2 * ROWS * (D + 4) + NCHUNK * WS_STRIDE) * sizeof(float);
-    if (!opt_in(k_spatial_qkv<EMU>, sm)) return BNB_ERR_LAUNCH;
-    count_launch();
-    k_spatial_qkv<EMU><<<n_tiles, NTHREADS, sm, st>>>(x, qkv, n_rows, D, w.norm1_w, w.qkv_w);
-  }
-  {
-    EnvMap map = make_env_map(b);
-    int dh = D / H;
-    int per_env = b.max_tokens_per_env * H;
-    dim3 grid(n_groups * b.n_envs, (per_env + 127) / 128 > 4 ? 4 : (per_env + 127) / 128);
-    if (grid.y < 1) grid.y = 1;
-    count_launch();
-    switch (dh) {
-      case 8:  k_attention<EMU, 8><<<grid, 128, 0, st>>>(qkv, alive, o, map, n_groups, D, H); break;
-      case 16: k_attention<EMU, 16><<<grid, 128, 0, st>>>(qkv, alive, o, map, n_groups, D, H); break;
-      case 32: k_attention<EMU, 32><<<grid, 128, 0, st>>>(qkv, alive, o, map, n_groups, D, H); break;
-      case 64: k_attention<EMU, 64><<<grid, 128, 0, st>>>(qkv, alive, o, map, n_groups, D, H); break;
-      default: return BNB_ERR_UNSUPPORTED_DIMS;
+  const size_t sm_qkv = (size_t)(2 * ROWS * (D + 4) + NCHUNK * WS_STRIDE) * sizeof(float);
+  if (!opt_in(k_spatial_qkv<EMU>, sm_qkv)) return BNB_ERR_LAUNCH;
+  count_launch();
+  k_spatial_qkv<EMU><<<n_tiles, NTHREADS, sm_qkv, st>>>(x, qkv, n_rows, D, 3 * D, w.norm1_w, w.qkv_w);
+  EnvMap map = make_env_map(b);
+  const int total_envs = n_groups * b.n_envs;
+  if (bul && w.kv_bullet_w) {
+    // keys and values of the bullets, one slice of environments at a time
+    const int nb = bul->per_env;
+    for (int e0 = 0; e0 < total_envs; e0 += kvb_envs) {
+      int ne = total_envs - e0 < kvb_envs ? total_envs - e0 : kvb_envs;
+      int rows = ne * nb;
+      count_launch();
+      k_spatial_qkv<EMU><<<(rows + ROWS - 1) / ROWS, NTHREADS, sm_qkv, st>>>(
+          bul->tokens + (size_t)e0 * nb * D, kvb, rows, D, 2 * D, w.norm_bullet_w, w.kv_bullet_w);
+      int rc = launch_attention<EMU>(qkv, alive, o, map, e0, ne, b.max_tokens_per_env, D, H, kvb, bul->active, nb, st);
+      if (rc) return rc;
     }
+  } else if (total_envs > 0) {
+    int rc = launch_attention<EMU>(qkv, alive, o, map, 0, total_envs, b.max_tokens_per_env, D, H, nullptr, nullptr, 0, st);
+    if (rc) return rc;
   }
   {
     size_t sm = smem_rows(D, 3);
@@ -564,10 +620,12 @@ static int spatial_impl(const BnbSpatialWeights& w, int D, int H, const float* x
 }
 
 int spatial_block(const BnbSpatialWeights& w, int D, int H, const float* x, const uint8_t* alive,
-                  float* y, const BnbBatch& b, int n_groups, bool emulate_bf16,
-                  float* qkv_scratch, float* o_scratch, cudaStream_t st) {
-  return emulate_bf16 ? spatial_impl<true>(w, D, H, x, alive, y, b, n_groups, qkv_scratch, o_scratch, st)
-                      : spatial_impl<false>(w, D, H, x, alive, y, b, n_groups, qkv_scratch, o_scratch, st);
+                  const BnbBullets* bullets, float* y, const BnbBatch& b, int n_groups, bool emulate_bf16,
+                  float* qkv_scratch, float* o_scratch, float* kvb_scratch, int kvb_envs, cudaStream_t st) {
+  return emulate_bf16 ? spatial_impl<true>(w, D, H, x, alive, bullets, y, b, n_groups, qkv_scratch, o_scratch,
+                                           kvb_scratch, kvb_envs, st)
+                      : spatial_impl<false>(w, D, H, x, alive, bullets, y, b, n_groups, qkv_scratch, o_scratch,
+                                            kvb_scratch, kvb_envs, st);
 }
 
 template <bool EMU>

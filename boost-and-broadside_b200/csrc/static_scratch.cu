@@ -78,6 +78,6 @@ extern "C" int bnb_spatial_block_fwd_static(const BnbSpatialWeights* w, int d_mo
   // call reads are all written by this call first.  What an earlier call left is ignored.
   float* qkv = scratch;
   float* o = scratch + (size_t)kMaxRows * 3 * kMaxWidth;
-  return bnb::exact::spatial_block(*w, d_model, n_heads, x, alive, y, *batch, n_groups, precision == BNB_BF16,
-                                   qkv, o, static_cast<cudaStream_t>(stream));
+  return bnb::exact::spatial_block(*w, d_model, n_heads, x, alive, nullptr, y, *batch, n_groups,
+                                   precision == BNB_BF16, qkv, o, nullptr, 0, static_cast<cudaStream_t>(stream));
 }

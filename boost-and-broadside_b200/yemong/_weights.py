@@ -24,6 +24,8 @@ def spatial_struct(block, dev: torch.device, packed: int | None = None) -> _capi
         _p(block.ffn.gate_proj.weight, dev, "ffn.gate_proj.weight"),
         _p(block.ffn.up_proj.weight, dev, "ffn.up_proj.weight"),
         _p(block.ffn.down_proj.weight, dev, "ffn.down_proj.weight"),
+        _p(block.norm_bullet.weight, dev, "norm_bullet.weight") if block.reads_bullets else None,
+        _p(block.kv_bullet.weight, dev, "kv_bullet.weight") if block.reads_bullets else None,
         packed,
     )
 

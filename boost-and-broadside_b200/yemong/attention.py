@@ -37,9 +37,8 @@ class TransformerBlock(nn.Module):
 
     Args:
         model_config: supplies ``d_model`` and ``n_heads``.
-        reads_bullets: allocate the bullet key/value parameters (attention.py:64-71).
-            The bullet cross-attention branch itself is not built: passing ``bullets``
-            raises ``NotImplementedError`` (never a silent PyTorch path).
+        reads_bullets: allocate the bullet key/value parameters (attention.py:64-71);
+            such a block cross-attends to ``bullets`` when they are passed.
     """
 
     def __init__(self, model_config, reads_bullets: bool = False) -> None:
@@ -66,9 +65,11 @@ class TransformerBlock(nn.Module):
         bullets: torch.Tensor | None = None,
         bullet_mask: torch.Tensor | None = None,
     ) -> torch.Tensor:
-        """(B, N, D) -> (B, N, D); ``alive_mask`` (B, N) bool masks dead entities as keys."""
-        if self.reads_bullets and bullets is not None:
-            raise NotImplementedError("bullet cross-attention is not built in the CUDA trunk")
+        """(B, N, D) -> (B, N, D); ``alive_mask`` (B, N) bool masks dead entities as keys.
+
+        ``bullets`` (B, NB, D) are extra keys/values of a block built with ``reads_bullets``,
+        ``bullet_mask`` (B, NB) bool marks the active ring-buffer slots (attention.py:149-166).
+        """
         if x.dim() != 3 or x.shape[-1] != self.d_model:
             raise RuntimeError(f"expected x of shape (B, N, {self.d_model}), got {tuple(x.shape)}")
         _capi.require_cuda(x, "x")
@@ -84,15 +85,16 @@ class TransformerBlock(nn.Module):
             alive = _capi.u8(alive_mask)
             y = torch.empty_like(xin)
             batch = _capi.uniform_batch(B, N, N)
-            nbytes = _capi.lib.bnb_scratch_bytes(D, batch, 1)
+            bul = _capi.BulletArgs(bullets if self.reads_bullets else None, bullet_mask, B, D)
+            nbytes = _capi.lib.bnb_scratch_bytes(D, batch, 1, bul.per_env)
             scratch = _capi.scratch_for(dev, nbytes)
             params = [self.qkv.weight, self.out_proj.weight, self.ffn.gate_proj.weight, self.ffn.up_proj.weight,
-                      self.ffn.down_proj.weight]
+                      self.ffn.down_proj.weight] + ([self.kv_bullet.weight] if self.reads_bullets else [])
             packed = packed_image(self, "spatial", 0, params, lambda: spatial_struct(self, dev), self.n_heads, dev,
                                   precision, _capi.ENGINE_AUTO)
             w = spatial_struct(self, dev, packed)
             st = _capi.lib.bnb_spatial_block_fwd(
-                w, D, self.n_heads, xin.data_ptr(), _capi.ptr(alive), y.data_ptr(), batch, 1, precision,
+                w, D, self.n_heads, xin.data_ptr(), _capi.ptr(alive), bul.arg, y.data_ptr(), batch, 1, precision,
                 _capi.ENGINE_AUTO, scratch.data_ptr(), scratch.numel(), _capi.stream_handle(dev),
             )
         _capi.check("bnb_spatial_block_fwd", st)

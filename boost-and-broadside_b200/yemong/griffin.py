@@ -121,7 +121,7 @@ class GriffinTemporalBlock(nn.Module):
             y = torch.empty_like(flat)
             batch = _capi.uniform_batch(R, 1, 0)  # every row is a field token
             w = temporal_struct(self, sub, dev, self._packed_ptr(sub, dev, precision))
-            scratch = _capi.scratch_for(dev, _capi.lib.bnb_scratch_bytes(D, batch, 1))
+            scratch = _capi.scratch_for(dev, _capi.lib.bnb_scratch_bytes(D, batch, 1, 0))
             st = _capi.lib.bnb_temporal_block_fwd(
                 w, D, flat.data_ptr(), y.data_ptr(), None, None, None, batch, 1, precision, _capi.ENGINE_AUTO,
                 scratch.data_ptr(), scratch.numel(), _capi.stream_handle(dev),
@@ -142,11 +142,15 @@ def run_trunk(
     timesteps: int | None,
     engine: int = _capi.ENGINE_AUTO,
     keepalive: tuple = (),
+    bullets: torch.Tensor | None = None,
+    bullet_mask: torch.Tensor | None = None,
 ) -> tuple[torch.Tensor, torch.Tensor]:
     """Run ``blocks`` (YemongBlock modules of one structure) over x.
 
     x is (total_tokens, D) for a step (timesteps None) or (T, total_tokens, D) for a
-    sequence; hidden is (L, total_ships, 4D) packed.  Returns (y, new_hidden).
+    sequence; hidden is (L, total_ships, 4D) packed; bullets (T * n_envs, NB, D) and
+    bullet_mask (T * n_envs, NB) feed the spatial sublayers that read them.
+    Returns (y, new_hidden).
     """
     dev = x.device
     D = x.shape[-1]
@@ -174,19 +178,21 @@ def run_trunk(
                     blk._packed_ptr("temporal", j, dev, precision, engine),
                 )
         T = 1 if timesteps is None else timesteps
-        nbytes = _capi.lib.bnb_scratch_bytes(D, batch, T)
+        reads = any(sp.reads_bullets for blk in blocks for sp in blk.spatial)
+        bul = _capi.BulletArgs(bullets if reads else None, bullet_mask, T * batch.n_envs, D)
+        nbytes = _capi.lib.bnb_scratch_bytes(D, batch, T, bul.per_env)
         scratch = _capi.scratch_for(dev, nbytes)
         stream = _capi.stream_handle(dev)
         if timesteps is None:
             st = _capi.lib.bnb_trunk_step(
-                sw, tw, n_blocks, n_spatial, n_temporal, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8),
+                sw, tw, n_blocks, n_spatial, n_temporal, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8), bul.arg,
                 y.data_ptr(), _capi.ptr(hin), _capi.ptr(hout), _capi.ptr(reset_u8), batch, precision, engine,
                 scratch.data_ptr(), scratch.numel(), stream,
             )
             fn = "bnb_trunk_step"
         else:
             st = _capi.lib.bnb_trunk_sequence(
-                sw, tw, n_blocks, n_spatial, n_temporal, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8),
+                sw, tw, n_blocks, n_spatial, n_temporal, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8), bul.arg,
                 y.data_ptr(), _capi.ptr(hin), _capi.ptr(hout), _capi.ptr(done_u8), batch, T, precision, engine,
                 scratch.data_ptr(), scratch.numel(), stream,
             )
@@ -230,7 +236,7 @@ class YemongBlock(nn.Module):
         if kind == "spatial":
             mod = self.spatial[j]
             params = [mod.qkv.weight, mod.out_proj.weight, mod.ffn.gate_proj.weight, mod.ffn.up_proj.weight,
-                      mod.ffn.down_proj.weight]
+                      mod.ffn.down_proj.weight] + ([mod.kv_bullet.weight] if mod.reads_bullets else [])
             return packed_image(self, kind, j, params, lambda: spatial_struct(mod, dev), self.n_heads, dev,
                                 precision, engine)
         mod = self.temporal[j]
@@ -245,10 +251,6 @@ class YemongBlock(nn.Module):
         L, R, D = h.shape
         return torch.cat([h.float(), conv_buf.float().reshape(L, R, (CONV_KERNEL - 1) * D)], dim=-1).contiguous()
 
-    def _check_bullets(self, bullets) -> None:
-        if bullets is not None and any(sp.reads_bullets for sp in self.spatial):
-            raise NotImplementedError("bullet cross-attention is not built in the CUDA trunk")
-
     def step(
         self,
         x: torch.Tensor,  # (B, N+M, D)
@@ -260,7 +262,6 @@ class YemongBlock(nn.Module):
         bullet_mask: torch.Tensor | None = None,
     ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         """Single-step forward (griffin.py:376-417): returns (x, new_h, new_conv_buf)."""
-        self._check_bullets(bullets)
         _capi.require_cuda(x, "x")
         _no_grad_inputs(x, h, conv_buf)
         B, NM, D = x.shape
@@ -268,7 +269,7 @@ class YemongBlock(nn.Module):
         batch = _capi.uniform_batch(B, NM, n_rec)
         hidden = self._pack_state(h, conv_buf)
         y, nh = run_trunk([self], self.n_heads, x.reshape(B * NM, D), None if alive is None else alive.reshape(-1),
-                          hidden, None, None, batch, None)
+                          hidden, None, None, batch, None, bullets=bullets, bullet_mask=bullet_mask)
         L, R = nh.shape[0], nh.shape[1]
         if L == 0:
             return y.reshape(B, NM, D), h[:0], conv_buf[:0]
@@ -286,7 +287,6 @@ class YemongBlock(nn.Module):
         bullet_mask: torch.Tensor | None = None,
     ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         """Full-sequence forward (griffin.py:419-472): returns (x, final h, final conv_buf)."""
-        self._check_bullets(bullets)
         _capi.require_cuda(x, "x")
         _no_grad_inputs(x, h0, conv_buf0)
         T, B, NM, D = x.shape
@@ -295,7 +295,7 @@ class YemongBlock(nn.Module):
         hidden = self._pack_state(h0, conv_buf0)
         y, nh = run_trunk(
             [self], self.n_heads, x.reshape(T, B * NM, D), None if alive_mask is None else alive_mask.reshape(T, -1),
-            hidden, done_mask, None, batch, T,
+            hidden, done_mask, None, batch, T, bullets=bullets, bullet_mask=bullet_mask,
         )
         L, R = nh.shape[0], nh.shape[1]
         if L == 0:

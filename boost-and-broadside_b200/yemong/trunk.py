@@ -120,6 +120,8 @@ class YemongTrunk(nn.Module):
         hidden: torch.Tensor,  # (n_layers, B*N, 4D)
         reset_env: torch.Tensor | None = None,  # (B,) bool: treat incoming state as zero
         engine: int = _capi.ENGINE_AUTO,
+        bullets: torch.Tensor | None = None,  # (B, NB, D) encoded bullet tokens
+        bullet_mask: torch.Tensor | None = None,  # (B, NB) bool active slots
     ) -> tuple[torch.Tensor, torch.Tensor]:
         """One rollout step of the trunk: returns (x_out (B, N+M, D), new_hidden)."""
         self._check(x, hidden)
@@ -129,7 +131,8 @@ class YemongTrunk(nn.Module):
             raise RuntimeError("hidden rows are not a multiple of the environment count")
         batch = _capi.uniform_batch(B, NM, n_rec)
         y, nh = run_trunk(list(self.yemong_layers), self.n_heads, x.reshape(B * NM, D),
-                          None if alive is None else alive.reshape(-1), hidden, None, reset_env, batch, None, engine)
+                          None if alive is None else alive.reshape(-1), hidden, None, reset_env, batch, None, engine,
+                          bullets=bullets, bullet_mask=bullet_mask)
         return y.reshape(B, NM, D), nh
 
     def sequence(
@@ -139,6 +142,8 @@ class YemongTrunk(nn.Module):
         initial_hidden: torch.Tensor,  # (n_layers, B*N, 4D)
         done_mask: torch.Tensor | None = None,  # (T, B) bool
         engine: int = _capi.ENGINE_AUTO,
+        bullets: torch.Tensor | None = None,  # (T*B, NB, D) encoded bullet tokens
+        bullet_mask: torch.Tensor | None = None,  # (T*B, NB) bool active slots
     ) -> tuple[torch.Tensor, torch.Tensor]:
         """The trunk over T timesteps from one initial state: returns (x_out, final_hidden)."""
         self._check(x, initial_hidden)
@@ -147,7 +152,7 @@ class YemongTrunk(nn.Module):
         batch = _capi.uniform_batch(B, NM, n_rec)
         y, nh = run_trunk(list(self.yemong_layers), self.n_heads, x.reshape(T, B * NM, D),
                           None if alive_mask is None else alive_mask.reshape(T, -1), initial_hidden, done_mask, None,
-                          batch, T, engine)
+                          batch, T, engine, bullets=bullets, bullet_mask=bullet_mask)
         return y.reshape(T, B, NM, D), nh
 
     def step_ragged(

@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define BNB_ABI_VERSION 1
+#define BNB_ABI_VERSION 2
 #define BNB_CONV_KERNEL 4 /* models/yemong/griffin.py:22 */
 
 typedef enum {
@@ -66,8 +66,21 @@ typedef struct {
   const float* gate_w;    /* (4D, D)        ffn.gate_proj.weight  */
   const float* up_w;      /* (4D, D)        ffn.up_proj.weight    */
   const float* down_w;    /* (D, 4D)        ffn.down_proj.weight  */
+  /* Only for a sublayer built with reads_bullets (attention.py:64-71); both NULL otherwise. */
+  const float* norm_bullet_w; /* (D)        norm_bullet.weight    */
+  const float* kv_bullet_w;   /* (2D, D)    kv_bullet.weight      */
   const void*  packed;    /* optional: image written by bnb_pack_spatial, or NULL */
 } BnbSpatialWeights;
+
+/* Encoded bullet tokens of a call: keys and values of the cross-attention branch of the
+ * sublayers that read bullets, never queries (models/yemong/attention.py:149-166).
+ * Every environment of every group holds the same number of ring-buffer slots. */
+typedef struct {
+  const float* tokens;    /* (n_groups * n_envs, per_env, D) float32, group-major like x */
+  const uint8_t* active;  /* (n_groups * n_envs, per_env) bytes, or NULL: every slot is a key and
+                             the branch is never gated off (bullet_mask=None in the reference) */
+  int32_t per_env;        /* NB >= 1 */
+} BnbBullets;
 
 /* Parameters of one temporal sublayer plus its field substitute.
  * Replaces: GriffinTemporalBlock / RGLRU parameters, models/yemong/griffin.py:160-247,
@@ -146,16 +159,20 @@ int bnb_plan_tiles(const int32_t* tok_off_host, int n_envs, int32_t* tile_env_be
                    int32_t* tile_env_ids_host, int capacity, int* n_tiles);
 
 /* Bytes of scratch a call with this geometry may use (upper bound over all entry points).
- * `timesteps` is 1 for a step. */
-size_t bnb_scratch_bytes(int d_model, const BnbBatch* batch, int timesteps);
+ * `timesteps` is 1 for a step; `bullets_per_env` is 0 for calls without bullets.  The bullet
+ * keys and values are projected in slices of environments, so their share of the scratch is
+ * capped (256 MiB) whatever the batch. */
+size_t bnb_scratch_bytes(int d_model, const BnbBatch* batch, int timesteps, int bullets_per_env);
 
-/* y = TransformerBlock.forward(x, alive_mask, bullets=None)
- * Replaces: models/yemong/attention.py:76-99 (with _attn 114-147,168-169 and GatedMLP 21-37).
+/* y = TransformerBlock.forward(x, alive_mask, bullets, bullet_mask)
+ * Replaces: models/yemong/attention.py:76-99 (with _attn 114-169 and GatedMLP 21-37).
  *   x, y    (n_rows, D) with n_rows = n_groups * batch->total_tokens; y may alias x
  *   alive   (n_rows) bytes or NULL (no key masking, attention.py:142-145)
+ *   bullets NULL, or the bullet tokens; read only when w->kv_bullet_w is set
+ *           (attention.py:149: reads_bullets and bullets is not None)
  *   n_groups replicates the batch geometry (the T*B fold of griffin.py:443-449). */
 int bnb_spatial_block_fwd(const BnbSpatialWeights* w, int d_model, int n_heads,
-                          const float* x, const uint8_t* alive, float* y,
+                          const float* x, const uint8_t* alive, const BnbBullets* bullets, float* y,
                           const BnbBatch* batch, int n_groups, int precision, int engine,
                           void* scratch, size_t scratch_bytes, void* stream);
 
@@ -174,7 +191,7 @@ int bnb_spatial_block_fwd(const BnbSpatialWeights* w, int d_model, int n_heads,
  *   - all calls share the one array: two calls that may overlap on the GPU (different
  *     streams, no dependency between them) race on it.  Calls on one stream are safe.
  *     Nothing in the array needs clearing between calls.
- * Arguments as bnb_spatial_block_fwd, without engine and scratch. */
+ * Arguments as bnb_spatial_block_fwd, without bullets, engine and scratch. */
 #define BNB_STATIC_MAX_ROWS 2048
 #define BNB_STATIC_SCRATCH_BYTES ((size_t)BNB_STATIC_MAX_ROWS * 4 * 128 * sizeof(float)) /* 4 MiB */
 int bnb_spatial_block_fwd_static(const BnbSpatialWeights* w, int d_model, int n_heads,
@@ -209,11 +226,13 @@ int bnb_temporal_block_fwd(const BnbTemporalWeights* w, int d_model,
  *   temporal  n_blocks*n_temporal entries, block-major
  *   x, y      (total_tokens, D); y may alias x
  *   hidden_in/out (n_blocks*n_temporal, total_ships, 4D); may alias
+ *   bullets   NULL or the step's bullet tokens (n_groups = 1), passed to every spatial
+ *             sublayer as griffin.py:400-401 does
  *   reset_env (n_envs) bytes or NULL: environments whose incoming state is taken as zero,
  *             i.e. reset_hidden_for_envs (policy.py:268-285) folded into the load. */
 int bnb_trunk_step(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal,
                    int n_blocks, int n_spatial, int n_temporal, int d_model, int n_heads,
-                   const float* x, const uint8_t* alive, float* y,
+                   const float* x, const uint8_t* alive, const BnbBullets* bullets, float* y,
                    const float* hidden_in, float* hidden_out, const uint8_t* reset_env,
                    const BnbBatch* batch, int precision, int engine,
                    void* scratch, size_t scratch_bytes, void* stream);
@@ -222,10 +241,11 @@ int bnb_trunk_step(const BnbSpatialWeights* spatial, const BnbTemporalWeights* t
  * Replaces: the trunk loop of YemongPolicy.evaluate_actions, models/yemong/policy.py:422-478,
  * with YemongBlock.sequence, griffin.py:419-472.
  *   x, y    (T, total_tokens, D); alive (T, total_tokens) or NULL; done (T, n_envs) or NULL
+ *   bullets NULL or the bullet tokens of all T * n_envs environments (n_groups = T)
  *   hidden_out receives the final state (the reference computes and drops it); may be NULL. */
 int bnb_trunk_sequence(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal,
                        int n_blocks, int n_spatial, int n_temporal, int d_model, int n_heads,
-                       const float* x, const uint8_t* alive, float* y,
+                       const float* x, const uint8_t* alive, const BnbBullets* bullets, float* y,
                        const float* hidden_in, float* hidden_out, const uint8_t* done,
                        const BnbBatch* batch, int timesteps, int precision, int engine,
                        void* scratch, size_t scratch_bytes, void* stream);

@@ -29,7 +29,7 @@ def test_library_exports_every_declared_symbol():
     lib = C.CDLL(_capi.LIB_PATH)
     for name in declared_functions():
         assert hasattr(lib, name), f"{name} is declared in bnb_trunk.h but not exported"
-    assert _capi.lib.bnb_abi_version() == 1
+    assert _capi.lib.bnb_abi_version() == 2
     assert _capi.lib.bnb_status_string(0) == b"ok"
     assert b"null" in _capi.lib.bnb_status_string(1)
 
@@ -56,25 +56,37 @@ def test_argument_validation_returns_status_codes():
     lib = _capi.lib
     batch = _capi.uniform_batch(4, 8, 8)
     w = _capi.SpatialWeights()  # all null
-    st = lib.bnb_spatial_block_fwd(w, 128, 4, None, None, None, batch, 1, 0, 0, None, 0, None)
+    st = lib.bnb_spatial_block_fwd(w, 128, 4, None, None, None, None, batch, 1, 0, 0, None, 0, None)
     assert st == 1  # BNB_ERR_NULL_POINTER
-    st = lib.bnb_spatial_block_fwd(w, 100, 4, None, None, None, batch, 1, 0, 0, None, 0, None)
+    st = lib.bnb_spatial_block_fwd(w, 100, 4, None, None, None, None, batch, 1, 0, 0, None, 0, None)
     assert st == 3  # BNB_ERR_UNSUPPORTED_DIMS
     bad = _capi.Batch(4, 8, 9, 8, 32, 36, None, None)  # more ships than tokens
-    st = lib.bnb_spatial_block_fwd(w, 128, 4, None, None, None, bad, 1, 0, 0, None, 0, None)
+    st = lib.bnb_spatial_block_fwd(w, 128, 4, None, None, None, None, bad, 1, 0, 0, None, 0, None)
     assert st == 5  # BNB_ERR_BAD_ARGUMENT
     fake = 0x1000
-    w = _capi.SpatialWeights(*([fake] * 7), None)
-    st = lib.bnb_spatial_block_fwd(w, 128, 4, fake + 4, None, fake, batch, 1, 0, 0, fake, 1 << 30, None)
+    w = _capi.SpatialWeights(*([fake] * 7), None, None, None)
+    st = lib.bnb_spatial_block_fwd(w, 128, 4, fake + 4, None, None, fake, batch, 1, 0, 0, fake, 1 << 30, None)
     assert st == 2  # BNB_ERR_MISALIGNED
-    st = lib.bnb_spatial_block_fwd(w, 128, 4, fake, None, fake, batch, 1, 0, 1, fake, 16, None)
+    st = lib.bnb_spatial_block_fwd(w, 128, 4, fake, None, None, fake, batch, 1, 0, 1, fake, 16, None)
     assert st == 6  # BNB_ERR_SCRATCH_TOO_SMALL
-    st = lib.bnb_spatial_block_fwd(w, 128, 4, fake, None, fake, batch, 1, 9, 0, fake, 1 << 30, None)
+    st = lib.bnb_spatial_block_fwd(w, 128, 4, fake, None, None, fake, batch, 1, 9, 0, fake, 1 << 30, None)
     assert st == 5
+    # bullet arguments: a half-given parameter pair, and a bullet set without tokens
+    half = _capi.SpatialWeights(*([fake] * 8), None, None)
+    assert lib.bnb_spatial_block_fwd(half, 128, 4, fake, None, None, fake, batch, 1, 0, 0, fake, 1 << 30, None) == 1
+    reads = _capi.SpatialWeights(*([fake] * 9), None)
+    no_tokens = _capi.Bullets(None, None, 10)
+    assert lib.bnb_spatial_block_fwd(reads, 128, 4, fake, None, no_tokens, fake, batch, 1, 0, 0, fake, 1 << 30, None) == 1
+    no_slots = _capi.Bullets(fake, None, 0)
+    assert lib.bnb_spatial_block_fwd(reads, 128, 4, fake, None, no_slots, fake, batch, 1, 0, 0, fake, 1 << 30, None) == 5
+    # the bullet share of the scratch is bounded whatever the batch
+    big = _capi.uniform_batch(1 << 20, 12, 8)
+    assert lib.bnb_scratch_bytes(128, big, 1, 80) - lib.bnb_scratch_bytes(128, big, 1, 0) <= (256 << 20) + 512
+    assert lib.bnb_scratch_bytes(128, batch, 1, 80) > lib.bnb_scratch_bytes(128, batch, 1, 0)
     # an empty batch is a successful no-op
     empty = _capi.uniform_batch(0, 8, 8)
-    assert lib.bnb_spatial_block_fwd(w, 128, 4, None, None, None, empty, 1, 0, 0, None, 0, None) == 0
-    assert lib.bnb_scratch_bytes(128, batch, 1) >= 4 * 8 * 4 * 128 * 4
+    assert lib.bnb_spatial_block_fwd(w, 128, 4, None, None, None, None, empty, 1, 0, 0, None, 0, None) == 0
+    assert lib.bnb_scratch_bytes(128, batch, 1, 0) >= 4 * 8 * 4 * 128 * 4
 
 
 def test_missing_library_fails_loudly(tmp_path):

@@ -332,8 +332,10 @@ def test_errors_are_python_exceptions():
 
     block = TransformerBlock(ModelConfig(128, 4, 2), reads_bullets=True).to(DEV)
     x = torch.zeros(2, 3, 128, device=DEV)
-    with pytest.raises(NotImplementedError):
-        block(x, None, torch.zeros(2, 5, 128, device=DEV), None)
+    with pytest.raises(RuntimeError):
+        block(x, None, torch.zeros(3, 5, 128, device=DEV), None)  # bullets of another batch size
+    with pytest.raises(RuntimeError):
+        block(x, None, torch.zeros(2, 5, 128, device=DEV), torch.ones(2, 4, dtype=torch.bool, device=DEV))
     with pytest.raises(RuntimeError):
         block(torch.zeros(2, 3, 64, device=DEV))
     with pytest.raises(RuntimeError):
@@ -344,3 +346,97 @@ def test_errors_are_python_exceptions():
     trunk = YemongTrunk(ModelConfig(128, 4, 2, 2, 1)).to(DEV)
     with pytest.raises(RuntimeError):
         trunk.step(x, None, torch.zeros(3, 6, 512, device=DEV))
+
+
+# ------------------------------------------------------------------ bullet cross-attention
+
+
+def _bullet_block(g, D, H):
+    from boost_and_broadside_b200 import ModelConfig, TransformerBlock
+
+    torch.manual_seed(0)
+    block = TransformerBlock(ModelConfig(D, H, 2), reads_bullets=True).eval()
+    w = stored_weights(g)
+    if w:
+        block.load_state_dict(w)
+    else:
+        block.norm_bullet.weight.data.copy_(g["norm_bullet"])
+    return block.to(DEV)
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("name", ["bullets_spatial_d128_n12_nb80", "bullets_spatial_d32_n3_nb7"])
+def test_spatial_block_with_bullets_golden(name, mode):
+    """attention.py:149-166 against the reference's own outputs: with the active mask (one
+    environment with nothing in flight, one with a full ring), without a mask, without bullets."""
+    g = golden(name)
+    D, H = (int(v) for v in g["dims"])
+    block = _bullet_block(g, D, H)
+    x, alive, bul, bm = _to(g["x"]), _to(g["alive"]), _to(g["bullets"]), _to(g["bullet_mask"])
+    with torch.no_grad(), autocast_for(mode, DEV):
+        y = block(x, alive, bul, bm)
+        y_nomask = block(x, alive, bul, None)
+        y_none = block(x, alive)
+    assert_close(y, g["y_" + mode], mode, name)
+    assert_close(y_nomask, g["y_nobmask_" + mode], mode, name + " (no bullet mask)")
+    assert_close(y_none, g["y_nobullets_" + mode], mode, name + " (no bullets)")
+    assert torch.equal(y[1], y_none[1])  # nothing in flight: the branch is gated off exactly
+
+
+def test_inactive_bullets_do_not_influence_output():
+    """tests/models/test_encoder.py:700-751 of the reference, at the sublayer: garbling the
+    inactive slots changes nothing, garbling an active one does."""
+    g = golden("bullets_spatial_d128_n12_nb80")
+    block = _bullet_block(g, 128, 4)
+    x, alive, bul, bm = _to(g["x"]), _to(g["alive"]), _to(g["bullets"]), _to(g["bullet_mask"])
+    garbled = torch.where(bm[..., None], bul, torch.full_like(bul, 1.0e3))
+    for mode in MODES:
+        with torch.no_grad(), autocast_for(mode, DEV):
+            assert torch.equal(block(x, alive, bul, bm), block(x, alive, garbled, bm))
+            moved = bul.clone()
+            moved[bm] += 1.0
+            assert not torch.equal(block(x, alive, bul, bm), block(x, alive, moved, bm))
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_trunk_with_bullets_golden(mode):
+    g = golden("bullets_trunk_step_d128_8s4f")
+    trunk = build_trunk(g["dims"], g).to(DEV)
+    with torch.no_grad(), autocast_for(mode, DEV):
+        y, nh = trunk.step(_to(g["x"]), _to(g["alive"]), _to(g["hidden"]), bullets=_to(g["bullets"]),
+                           bullet_mask=_to(g["bullet_mask"]))
+    assert_close(y, g["y_" + mode], mode, "bullets step y")
+    assert_close(nh, g["hidden_" + mode], mode, "bullets step hidden")
+    g = golden("bullets_trunk_seq_d128_t4_4s2f")
+    with torch.no_grad(), autocast_for(mode, DEV):
+        y, nh = trunk.sequence(_to(g["x"]), _to(g["alive"]), _to(g["hidden"]), _to(g["done"]),
+                               bullets=_to(g["bullets"]), bullet_mask=_to(g["bullet_mask"]))
+    assert_close(y, g["y_" + mode], mode, "bullets sequence y")
+    assert_close(nh, g["hidden_" + mode], mode, "bullets sequence hidden")
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_block_step_with_bullets_vs_oracle(mode):
+    """YemongBlock.step with the reference's argument list (griffin.py:376-385), seeded inputs."""
+    from boost_and_broadside_b200 import ModelConfig, YemongBlock
+
+    torch.manual_seed(3)
+    cfg = ModelConfig(128, 4, 1, 2, 1, n_bullet_cross_per_block=2)
+    blk = YemongBlock(cfg).eval()
+    P = {k: v.detach().float() for k, v in blk.state_dict().items()}
+    B, N, M, NB = 37, 6, 3, 60
+    gen = torch.Generator().manual_seed(11)
+    x = torch.randn(B, N + M, 128, generator=gen)
+    alive = torch.rand(B, N + M, generator=gen) < 0.8
+    h = torch.randn(1, B * N, 128, generator=gen) * 0.5
+    cb = torch.randn(1, B * N, 3, 128, generator=gen) * 0.5
+    bul = torch.randn(B, NB, 128, generator=gen)
+    bm = torch.rand(B, NB, generator=gen) < 0.3
+    bm[0] = False
+    ry, rh, rc = O.yemong_block_step(x, alive, h, cb, N, P, 4, mode, bul, bm)
+    blk = blk.to(DEV)
+    with torch.no_grad(), autocast_for(mode, DEV):
+        y, nh, nc = blk.step(_to(x), _to(alive), _to(h), _to(cb), N, _to(bul), _to(bm))
+    assert_close(y, ry, mode, "block step y")
+    assert_close(nh, rh, mode, "block step h")
+    assert_close(nc, rc, mode, "block step conv")

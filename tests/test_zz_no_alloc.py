@@ -42,15 +42,15 @@ def test_static_entry_point_matches_the_ordinary_one_twice(mode_bf16):
 
     # ordinary entry point, caller-provided scratch
     y_ref = torch.empty_like(x)
-    scratch = torch.empty(lib.bnb_scratch_bytes(128, batch, 1), dtype=torch.uint8, device=dev)
-    st = lib.bnb_spatial_block_fwd(weights, 128, 4, x.data_ptr(), alive.data_ptr(), y_ref.data_ptr(), batch, 1,
+    scratch = torch.empty(lib.bnb_scratch_bytes(128, batch, 1, 0), dtype=torch.uint8, device=dev)
+    st = lib.bnb_spatial_block_fwd(weights, 128, 4, x.data_ptr(), alive.data_ptr(), None, y_ref.data_ptr(), batch, 1,
                                    precision, _capi.ENGINE_SIMT, scratch.data_ptr(), scratch.numel(), stream)
     assert st == 0, lib.bnb_status_string(st)
 
     # a second, different input so that the second static call cannot pass on stale scratch
     _, _, _, x2, alive2, _, _, _ = _setup(mode_bf16, 256, 7)
     y_ref2 = torch.empty_like(x2)
-    st = lib.bnb_spatial_block_fwd(weights, 128, 4, x2.data_ptr(), alive2.data_ptr(), y_ref2.data_ptr(), batch, 1,
+    st = lib.bnb_spatial_block_fwd(weights, 128, 4, x2.data_ptr(), alive2.data_ptr(), None, y_ref2.data_ptr(), batch, 1,
                                    precision, _capi.ENGINE_SIMT, scratch.data_ptr(), scratch.numel(), stream)
     assert st == 0, lib.bnb_status_string(st)
 
