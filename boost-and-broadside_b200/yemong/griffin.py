@@ -94,7 +94,7 @@ class GriffinTemporalBlock(nn.Module):
             new_hidden = torch.empty_like(hidden)
             batch = _capi.uniform_batch(R, 1, 1)  # every row is its own one-ship environment
             w = temporal_struct(self, None, dev, self._packed_ptr(None, dev, precision))
-            scratch = _capi.scratch_for(dev, _capi.lib.bnb_scratch_bytes(D, batch, T))
+            scratch = _capi.scratch_for(dev, _capi.lib.bnb_scratch_bytes(D, batch, T, 0))
             st = _capi.lib.bnb_temporal_block_fwd(
                 w, D, x_t.data_ptr(), y.data_ptr(), hidden.data_ptr(), new_hidden.data_ptr(), _capi.ptr(done),
                 batch, T, precision, _capi.ENGINE_AUTO, scratch.data_ptr(), scratch.numel(), _capi.stream_handle(dev),

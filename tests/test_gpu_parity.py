@@ -380,7 +380,10 @@ def test_spatial_block_with_bullets_golden(name, mode):
     assert_close(y, g["y_" + mode], mode, name)
     assert_close(y_nomask, g["y_nobmask_" + mode], mode, name + " (no bullet mask)")
     assert_close(y_none, g["y_nobullets_" + mode], mode, name + " (no bullets)")
-    assert torch.equal(y[1], y_none[1])  # nothing in flight: the branch is gated off exactly
+    if mode == "fp32":  # one engine for both calls: the gated-off branch changes nothing, exactly
+        assert torch.equal(y[1], y_none[1])
+    else:               # bf16 may take different kernels with and without bullets
+        assert_close(y[1], y_none[1], mode, name + " (nothing in flight)")
 
 
 def test_inactive_bullets_do_not_influence_output():
