@@ -118,8 +118,9 @@ int carve(void* scratch, size_t bytes, size_t n_rows, int D, long long total_env
   return BNB_OK;
 }
 
-bool use_tensor(int precision, int engine, int D, int H, const BnbBatch* b) {
+bool use_tensor(int precision, int engine, int D, int H, const BnbBatch* b, const BnbBullets* bullets) {
   if (precision != BNB_BF16 || engine == BNB_ENGINE_SIMT) return false;
+  if (bullets && !bnb::tensor::supported_bullets(*b, bullets->per_env)) return false;
   return bnb::tensor::supported_batch(D, H, *b);
 }
 
@@ -175,7 +176,7 @@ size_t bnb_scratch_bytes(int d_model, const BnbBatch* batch, int timesteps, int 
   if (bullets_per_env < 0) bullets_per_env = 0;
   size_t n_rows = (size_t)timesteps * (size_t)batch->total_tokens;
   size_t simt = simt_scratch_bytes(n_rows, d_model, (long long)timesteps * batch->n_envs, bullets_per_env);
-  size_t tc = bnb::tensor::scratch_bytes(d_model, *batch, timesteps);
+  size_t tc = bnb::tensor::scratch_bytes(d_model, *batch, timesteps, bullets_per_env);
   return (simt > tc ? simt : tc) + 256;
 }
 
@@ -196,8 +197,8 @@ int bnb_spatial_block_fwd(const BnbSpatialWeights* w, int d_model, int n_heads, 
   if (!x || !y) return BNB_ERR_NULL_POINTER;
   if (!aligned16(x) || !aligned16(y)) return BNB_ERR_MISALIGNED;
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
-  if (!bullets && use_tensor(precision, engine, d_model, n_heads, batch) && (w->packed || engine == BNB_ENGINE_TENSOR))
-    return bnb::tensor::spatial_block(*w, d_model, n_heads, x, alive, y, *batch, n_groups, scratch,
+  if (use_tensor(precision, engine, d_model, n_heads, batch, bullets) && (w->packed || engine == BNB_ENGINE_TENSOR))
+    return bnb::tensor::spatial_block(*w, d_model, n_heads, x, alive, bullets, y, *batch, n_groups, scratch,
                                       scratch_bytes, cs);
   if (engine == BNB_ENGINE_TENSOR) return BNB_ERR_UNSUPPORTED_DIMS;
   Scratch s;
@@ -223,7 +224,7 @@ int bnb_temporal_block_fwd(const BnbTemporalWeights* w, int d_model, const float
   if (batch->total_ships > 0 && (!hidden_in || !hidden_out)) return BNB_ERR_NULL_POINTER;
   if (!aligned16(x) || !aligned16(y) || !aligned16(hidden_in) || !aligned16(hidden_out)) return BNB_ERR_MISALIGNED;
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
-  if (use_tensor(precision, engine, d_model, 4, batch) && (w->packed || engine == BNB_ENGINE_TENSOR))
+  if (use_tensor(precision, engine, d_model, 4, batch, nullptr) && (w->packed || engine == BNB_ENGINE_TENSOR))
     return bnb::tensor::temporal_block(*w, d_model, x, y, hidden_in, hidden_out, done, nullptr, *batch, timesteps,
                                        scratch, scratch_bytes, cs);
   if (engine == BNB_ENGINE_TENSOR) return BNB_ERR_UNSUPPORTED_DIMS;
@@ -258,9 +259,9 @@ static int trunk_common(const BnbSpatialWeights* spatial, const BnbTemporalWeigh
   if (has_state && !is_sequence && !hidden_out) return BNB_ERR_NULL_POINTER;
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
 
-  if (!bullets && use_tensor(precision, engine, D, H, batch) &&
+  if (use_tensor(precision, engine, D, H, batch, bullets) &&
       (engine == BNB_ENGINE_TENSOR || all_packed(spatial, n_blocks * n_spatial, temporal, n_blocks * n_temporal)))
-    return bnb::tensor::trunk(spatial, temporal, n_blocks, n_spatial, n_temporal, D, H, x, alive, y, hidden_in,
+    return bnb::tensor::trunk(spatial, temporal, n_blocks, n_spatial, n_temporal, D, H, x, alive, bullets, y, hidden_in,
                               hidden_out, done, reset_env, *batch, T, scratch, scratch_bytes, cs);
   if (engine == BNB_ENGINE_TENSOR) return BNB_ERR_UNSUPPORTED_DIMS;
 

@@ -24,6 +24,7 @@
 // word and the kernel drains without hanging.
 //
 // Reference arithmetic: models/yemong/attention.py:76-169, models/yemong/griffin.py:67-317.
+#include "bullet_slices.h"
 #include "tensor_kernels.h"
 
 #include <cuda_bf16.h>
@@ -41,7 +42,9 @@ constexpr int HEADS = 4;
 constexpr int DH = 32;
 constexpr int TILE = 128;
 constexpr int CHUNK_BYTES = 16384;       // one weight chunk: up to 128 rows x 64 bf16
-constexpr int N_SPATIAL_CHUNKS = 34;
+constexpr int N_SPATIAL_CHUNKS = 34;       // chunks of a spatial sublayer proper
+constexpr int N_BULLET_CHUNKS = 4;         // kv_bullet: keys (2 K atoms), values (2 K atoms); zero when absent
+constexpr int N_SPATIAL_IMAGE = N_SPATIAL_CHUNKS + N_BULLET_CHUNKS;
 constexpr int N_TEMPORAL_CHUNKS = 36;
 constexpr int STAGE_STRIDE = 208;        // bytes per staged q|k|v row (96 bf16 + pad)
 constexpr int MAX_SUBLAYERS = 8;
@@ -64,7 +67,9 @@ constexpr uint32_t COL_ACC = 128;
 // SUB_SPATIAL_PRE / _POST split a spatial sublayer around a separate attention kernel
 // (environments larger than one tile): PRE = norm1 + QKV to global scratch, POST = attention
 // output from scratch + out_proj + norm2 + GatedMLP.
-enum : int { SUB_SPATIAL = 0, SUB_TEMPORAL = 1, SUB_SPATIAL_PRE = 2, SUB_SPATIAL_POST = 3 };
+// SUB_BULLET_KV runs over bullet rows instead of token rows: norm_bullet + kv_bullet, keys and
+// values written as bf16 to global scratch for the attention kernel; it leaves no residual.
+enum : int { SUB_SPATIAL = 0, SUB_TEMPORAL = 1, SUB_SPATIAL_PRE = 2, SUB_SPATIAL_POST = 3, SUB_BULLET_KV = 4 };
 enum : int { ST_TIMEOUT_FULL = 101, ST_TIMEOUT_EMPTY = 102, ST_TIMEOUT_ACC = 103 };
 
 struct SubLayer {
@@ -81,6 +86,7 @@ struct SubLayer {
   float* hid_out;
   __nv_bfloat16* qkv_out;        // PRE: (rows, 384) q|k|v, head-major inside each third
   const __nv_bfloat16* o_in;     // POST: (rows, 128) attention output
+  __nv_bfloat16* kvb_out;        // BULLET_KV: (rows, 256) k | v of the bullet rows
 };
 
 struct TrunkArgs {
@@ -302,6 +308,12 @@ __device__ __forceinline__ const float* spatial_chunk_row(const BnbSpatialWeight
     }
     return w.out_w + (size_t)r * D + 64 * p;
   }
+  if (c >= N_SPATIAL_CHUNKS) {
+    // kv_bullet (2D, D): rows 0..127 are the keys of all heads, 128..255 the values
+    if (!w.kv_bullet_w) return nullptr;
+    const int i = c - N_SPATIAL_CHUNKS;
+    return w.kv_bullet_w + (size_t)((i >> 1) * D + r) * D + (i & 1) * 64;
+  }
   return ffn_chunk_row(c - 10, r, w.gate_w, w.up_w, w.down_w);
 }
 __device__ __forceinline__ const float* temporal_chunk_row(const BnbTemporalWeights& w, int c, int r) {
@@ -334,7 +346,7 @@ __device__ __forceinline__ void pack_image(const W& w, int n_chunks, uint8_t* ou
   }
 }
 __global__ void k_pack_spatial(BnbSpatialWeights w, uint8_t* out) {
-  pack_image(w, N_SPATIAL_CHUNKS, out, [](const BnbSpatialWeights& ww, int c, int r) { return spatial_chunk_row(ww, c, r); });
+  pack_image(w, N_SPATIAL_IMAGE, out, [](const BnbSpatialWeights& ww, int c, int r) { return spatial_chunk_row(ww, c, r); });
 }
 __global__ void k_pack_temporal(BnbTemporalWeights w, uint8_t* out) {
   if (blockIdx.x == 0 && threadIdx.x < D) {
@@ -395,6 +407,7 @@ __device__ __forceinline__ uint32_t slot_addr(const Ctx& c, uint32_t slot) {
 }
 __device__ __forceinline__ uint32_t chunk_slot(int type, int ch) {
   if (type == SUB_TEMPORAL) return ch < 12 ? (uint32_t)(ch & 1) : (uint32_t)((ch - 12) % 3);
+  if (type == SUB_BULLET_KV) return (uint32_t)(ch & 1);
   if (ch >= 10) return (uint32_t)((ch - 10) % 3);
   if (type == SUB_SPATIAL) return (uint32_t)(ch & 1);
   if (type == SUB_SPATIAL_PRE) return (uint32_t)((ch < 5 ? ch : ch - 1) & 1);  // q|k|v chunks only: K atom 0 -> slot 0
@@ -403,6 +416,8 @@ __device__ __forceinline__ uint32_t chunk_slot(int type, int ch) {
 // Does a sublayer of `type` consume chunk `ch` of its weight image?
 __device__ __forceinline__ bool chunk_used(int type, int ch, bool has_fields) {
   if (type == SUB_TEMPORAL) return has_fields || (ch != 8 && ch != 9);
+  if (type == SUB_BULLET_KV) return ch >= N_SPATIAL_CHUNKS;
+  if (ch >= N_SPATIAL_CHUNKS) return false;
   if (type == SUB_SPATIAL_PRE) return ch < 10 && ch != 4 && ch != 9;
   if (type == SUB_SPATIAL_POST) return ch == 4 || ch >= 9;
   return true;
@@ -804,6 +819,32 @@ __device__ __forceinline__ void run_spatial_post(Ctx& c, const SubLayer& s, size
   ffn<NQ>(c);
 }
 
+// Bullet rows: norm_bullet and the kv_bullet projection, keys then values of all heads, written
+// as bf16 to global scratch (models/yemong/attention.py:151 of the reference).
+template <int NQ>
+__device__ __forceinline__ void run_bullet_kv(Ctx& c, const SubLayer& s, size_t grow, bool row_valid) {
+  constexpr int CPT = 128 / NQ;
+  norm_to_A<NQ>(c, s.g1);
+  for (int half = 0; half < 2; ++half) {
+    round_begin<NQ>(c);
+    if (threadIdx.x == 0) {
+      issue_chunk(c, c.sA, 128, COL_ACC, 0, 0);
+      issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1, 1);
+    }
+    round_end<NQ>(c);
+#pragma unroll
+    for (int ch = 0; ch < CPT / 32; ++ch) {
+      uint32_t v[32];
+      tmem_ld32(c.lane_addr + COL_ACC + c.part * CPT + ch * 32, v);
+      if (row_valid) {
+        __nv_bfloat16* dst = s.kvb_out + grow * (2 * D) + half * D + c.part * CPT + ch * 32;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(dst + q * 8) = pack8(&v[q * 8]);
+      }
+    }
+  }
+}
+
 struct RowState {
   int hrow;        // row of the packed hidden state, -1 for field / invalid rows
   int lag_ok;      // stored conv lags still inside the current episode (0..3)
@@ -1064,7 +1105,7 @@ __global__ void __launch_bounds__(128 * NQ, 2) k_trunk_tiles(const __grid_consta
     int n = 0;
     for (int si = 0; si < args.n_sub; ++si) {
       const int type = args.sub[si].type;
-      const int n_chunks = type == SUB_TEMPORAL ? N_TEMPORAL_CHUNKS : N_SPATIAL_CHUNKS;
+      const int n_chunks = type == SUB_TEMPORAL ? N_TEMPORAL_CHUNKS : N_SPATIAL_IMAGE;
       for (int ch = 0; ch < n_chunks; ++ch) {
         if (!chunk_used(type, ch, args.has_fields != 0)) continue;
         s_sched[n++] = (uint16_t)((ch << 6) | (si << 2) | chunk_slot(type, ch));
@@ -1244,6 +1285,7 @@ __global__ void __launch_bounds__(128 * NQ, 2) k_trunk_tiles(const __grid_consta
           if (s.type == SUB_SPATIAL) run_spatial<NQ, MAXKB>(c, s, n_items, valid);
           else if (s.type == SUB_SPATIAL_PRE) run_spatial_pre<NQ>(c, s, trow, valid);
           else if (s.type == SUB_SPATIAL_POST) run_spatial_post<NQ>(c, s, trow, valid);
+          else if (s.type == SUB_BULLET_KV) run_bullet_kv<NQ>(c, s, trow, valid);
           else run_temporal<NQ>(c, s, rs, is_field, boundary, args.has_fields != 0, t == 0 ? s.hid_in : s.hid_out);
         }
         // y <- residual
@@ -1251,7 +1293,7 @@ __global__ void __launch_bounds__(128 * NQ, 2) k_trunk_tiles(const __grid_consta
         for (int ch = 0; ch < CPT / 32; ++ch) {
           uint32_t v[32];
           tmem_ld32(c.lane_addr + COL_RESID + c.part * CPT + ch * 32, v);
-          if (valid) {
+          if (valid && args.y) {
 #pragma unroll
             for (int q = 0; q < 8; ++q)
               *reinterpret_cast<float4*>(args.y + trow * D + c.part * CPT + ch * 32 + q * 4) =
@@ -1277,39 +1319,149 @@ __global__ void __launch_bounds__(128 * NQ, 2) k_trunk_tiles(const __grid_consta
   }
 }
 
-// ------------------------------------------------------------------ attention for large environments
+// ------------------------------------------------------------------ attention kernel of the split path
 //
 // One CTA per (environment, head): q, k, v of that head are staged from the bf16 scratch the
 // PRE phase wrote, then each warp takes blocks of 16 query rows and walks the keys in blocks of
 // 16 with a running maximum (mma.sync, fp32 softmax).  Dead keys score kMaskedScore, so their
 // weight is exactly 0 unless no key of the environment is alive, in which case every key gets
-// the same weight (models/yemong/attention.py:101-112 of the reference).
+// the same weight (models/yemong/attention.py:101-112 of the reference).  When the sublayer
+// reads bullets, the environment's bullet keys and values (written by the BULLET_KV phase) are
+// staged too and get a softmax of their own; its output, gated to zero when the environment has
+// no active bullet, is added to the self-attention output (attention.py:149-166).
 constexpr int FLASH_STRIDE = 80;  // bytes per staged row of one head (32 bf16 + pad)
 
+// One softmax pass of a block of 16 queries (fragments qa) over n keys staged at sK / sV with
+// liveness bytes `live`; returns the normalised output fragments in acc.
+__device__ __forceinline__ void flash_pass(const uint32_t (&qa)[2][4], uint32_t sK, uint32_t sV,
+                                           const uint8_t* __restrict__ live, int n, int lane, float (&acc)[4][4]) {
+  const int t = lane & 3;
+  const float scale = 0.17677669529663687f;
+  const int last = n - 1;
+  const int nkb = (n + 15) >> 4;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
+  for (int kb = 0; kb < nkb; ++kb) {
+    float sc[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sc[nt][i] = 0.f;
+    const int krow = min(kb * 16 + (lane >> 4) * 8 + (lane & 7), last);
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4(sK + krow * FLASH_STRIDE + (ks * 16 + ((lane >> 3) & 1) * 8) * 2, b0, b1, b2, b3);
+      mma_bf16(sc[0], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+      mma_bf16(sc[1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b2, b3);
+    }
+    float bm0 = -INFINITY, bm1 = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int j = kb * 16 + nt * 8 + 2 * t + i;
+        const bool valid = j < n;
+        const bool lv = valid && live[j];
+        const float a = valid ? (lv ? sc[nt][i] * scale : kMaskedScore) : -INFINITY;
+        const float b = valid ? (lv ? sc[nt][2 + i] * scale : kMaskedScore) : -INFINITY;
+        sc[nt][i] = a;
+        sc[nt][2 + i] = b;
+        bm0 = fmaxf(bm0, a);
+        bm1 = fmaxf(bm1, b);
+      }
+    bm0 = fmaxf(bm0, __shfl_xor_sync(0xffffffffu, bm0, 1));
+    bm0 = fmaxf(bm0, __shfl_xor_sync(0xffffffffu, bm0, 2));
+    bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, 1));
+    bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, 2));
+    const float n0 = fmaxf(m0, bm0), n1 = fmaxf(m1, bm1);   // finite: every block holds a valid key
+    const float c0 = __expf(m0 - n0), c1 = __expf(m1 - n1); // exp(-inf) = 0 on the first block
+    m0 = n0;
+    m1 = n1;
+    l0 *= c0;
+    l1 *= c1;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      acc[nt][0] *= c0; acc[nt][1] *= c0;
+      acc[nt][2] *= c1; acc[nt][3] *= c1;
+    }
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const float a = __expf(sc[nt][i] - m0), b = __expf(sc[nt][2 + i] - m1);
+        sc[nt][i] = a;
+        sc[nt][2 + i] = b;
+        l0 += a;
+        l1 += b;
+      }
+    const uint32_t a0 = pack_bf16(sc[0][0], sc[0][1]), a1 = pack_bf16(sc[0][2], sc[0][3]);
+    const uint32_t a2 = pack_bf16(sc[1][0], sc[1][1]), a3 = pack_bf16(sc[1][2], sc[1][3]);
+    const int vrow = min(kb * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), last);
+#pragma unroll
+    for (int np = 0; np < 2; ++np) {
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4_t(sV + vrow * FLASH_STRIDE + ((np * 2 + (lane >> 4)) * 8) * 2, b0, b1, b2, b3);
+      mma_bf16(acc[np * 2], a0, a1, a2, a3, b0, b1);
+      mma_bf16(acc[np * 2 + 1], a0, a1, a2, a3, b2, b3);
+    }
+  }
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  const float i0 = 1.0f / l0, i1 = 1.0f / l1;
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt) {
+    acc[nt][0] *= i0; acc[nt][1] *= i0;
+    acc[nt][2] *= i1; acc[nt][3] *= i1;
+  }
+}
+
+// env_base: first environment (group-major) of this launch.  kvb / bullet_active / nb describe
+// the bullet keys of the launch's environments (kvb indexed from env_base), or null / 0.
 __global__ void __launch_bounds__(128) k_attention_flash(const __nv_bfloat16* __restrict__ qkv, const uint8_t* __restrict__ alive,
-                                                         __nv_bfloat16* __restrict__ o, EnvMap map, int n_groups) {
+                                                         __nv_bfloat16* __restrict__ o, EnvMap map, int env_base,
+                                                         const __nv_bfloat16* __restrict__ kvb,
+                                                         const uint8_t* __restrict__ bullet_active, int nb) {
   extern __shared__ __align__(16) uint8_t fs[];
-  const int env_g = blockIdx.x, hd = blockIdx.y;
+  const int env_g = env_base + blockIdx.x, hd = blockIdx.y;
   const int grp = env_g / map.n_envs, e = env_g - grp * map.n_envs;
   const size_t tok0 = (size_t)grp * map.total_tokens + map.env_tok_begin(e);
   const int n = map.env_tok_count(e);
+  if (!kvb) nb = 0;
   uint8_t* Qs = fs;
   uint8_t* Ks = Qs + (size_t)n * FLASH_STRIDE;
   uint8_t* Vs = Ks + (size_t)n * FLASH_STRIDE;
-  uint8_t* live = Vs + (size_t)n * FLASH_STRIDE;
+  uint8_t* Kb = Vs + (size_t)n * FLASH_STRIDE;
+  uint8_t* Vb = Kb + (size_t)nb * FLASH_STRIDE;
+  uint8_t* live = Vb + (size_t)nb * FLASH_STRIDE;
+  uint8_t* liveb = live + n;
   for (int i = threadIdx.x; i < n * 12; i += blockDim.x) {
     const int r = i / 12, part = (i % 12) >> 2, q = i & 3;
     const uint4 v = *reinterpret_cast<const uint4*>(qkv + (tok0 + r) * (3 * D) + part * D + hd * DH + q * 8);
     *reinterpret_cast<uint4*>(fs + ((size_t)part * n + r) * FLASH_STRIDE + q * 16) = v;
   }
+  for (int i = threadIdx.x; i < nb * 8; i += blockDim.x) {
+    const int r = i >> 3, part = (i >> 2) & 1, q = i & 3;
+    const uint4 v = *reinterpret_cast<const uint4*>(kvb + ((size_t)blockIdx.x * nb + r) * (2 * D) + part * D + hd * DH + q * 8);
+    *reinterpret_cast<uint4*>(Kb + ((size_t)part * nb + r) * FLASH_STRIDE + q * 16) = v;
+  }
   for (int i = threadIdx.x; i < n; i += blockDim.x) live[i] = alive ? alive[tok0 + i] : (uint8_t)1;
-  __syncthreads();
+  int any_here = 0;
+  for (int i = threadIdx.x; i < nb; i += blockDim.x) {
+    const uint8_t a = bullet_active ? bullet_active[(size_t)env_g * nb + i] : (uint8_t)1;
+    liveb[i] = a;
+    any_here |= a;
+  }
+  const float gate = __syncthreads_or(any_here) ? 1.f : 0.f;   // also orders the staging writes
   const uint32_t sQ = smem_u32(Qs), sK = smem_u32(Ks), sV = smem_u32(Vs);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const float scale = 0.17677669529663687f;
   const int last = n - 1;
-  const int nkb = (n + 15) >> 4;
   for (int qb = warp; qb * 16 < n; qb += 4) {
     uint32_t qa[2][4];
     {
@@ -1318,88 +1470,23 @@ __global__ void __launch_bounds__(128) k_attention_flash(const __nv_bfloat16* __
       for (int ks = 0; ks < 2; ++ks)
         ldsm_x4(sQ + row * FLASH_STRIDE + (ks * 16 + (lane >> 4) * 8) * 2, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3]);
     }
-    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
     float acc[4][4];
+    flash_pass(qa, sK, sV, live, n, lane, acc);
+    if (nb > 0) {
+      float accb[4][4];
+      flash_pass(qa, smem_u32(Kb), smem_u32(Vb), liveb, nb, lane, accb);
+      // both outputs are bf16 tensors in the reference; so is their sum
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt)
+      for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
-    for (int kb = 0; kb < nkb; ++kb) {
-      float sc[2][4];
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) sc[nt][i] = 0.f;
-      const int krow = min(kb * 16 + (lane >> 4) * 8 + (lane & 7), last);
-#pragma unroll
-      for (int ks = 0; ks < 2; ++ks) {
-        uint32_t b0, b1, b2, b3;
-        ldsm_x4(sK + krow * FLASH_STRIDE + (ks * 16 + ((lane >> 3) & 1) * 8) * 2, b0, b1, b2, b3);
-        mma_bf16(sc[0], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
-        mma_bf16(sc[1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b2, b3);
-      }
-      float bm0 = -INFINITY, bm1 = -INFINITY;
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int j = kb * 16 + nt * 8 + 2 * t + i;
-          const bool valid = j < n;
-          const bool lv = valid && live[j];
-          const float a = valid ? (lv ? sc[nt][i] * scale : kMaskedScore) : -INFINITY;
-          const float b = valid ? (lv ? sc[nt][2 + i] * scale : kMaskedScore) : -INFINITY;
-          sc[nt][i] = a;
-          sc[nt][2 + i] = b;
-          bm0 = fmaxf(bm0, a);
-          bm1 = fmaxf(bm1, b);
-        }
-      bm0 = fmaxf(bm0, __shfl_xor_sync(0xffffffffu, bm0, 1));
-      bm0 = fmaxf(bm0, __shfl_xor_sync(0xffffffffu, bm0, 2));
-      bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, 1));
-      bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, 2));
-      const float n0 = fmaxf(m0, bm0), n1 = fmaxf(m1, bm1);   // finite: every block holds a valid key
-      const float c0 = __expf(m0 - n0), c1 = __expf(m1 - n1); // exp(-inf) = 0 on the first block
-      m0 = n0;
-      m1 = n1;
-      l0 *= c0;
-      l1 *= c1;
-#pragma unroll
-      for (int nt = 0; nt < 4; ++nt) {
-        acc[nt][0] *= c0; acc[nt][1] *= c0;
-        acc[nt][2] *= c1; acc[nt][3] *= c1;
-      }
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const float a = __expf(sc[nt][i] - m0), b = __expf(sc[nt][2 + i] - m1);
-          sc[nt][i] = a;
-          sc[nt][2 + i] = b;
-          l0 += a;
-          l1 += b;
-        }
-      const uint32_t a0 = pack_bf16(sc[0][0], sc[0][1]), a1 = pack_bf16(sc[0][2], sc[0][3]);
-      const uint32_t a2 = pack_bf16(sc[1][0], sc[1][1]), a3 = pack_bf16(sc[1][2], sc[1][3]);
-      const int vrow = min(kb * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), last);
-#pragma unroll
-      for (int np = 0; np < 2; ++np) {
-        uint32_t b0, b1, b2, b3;
-        ldsm_x4_t(sV + vrow * FLASH_STRIDE + ((np * 2 + (lane >> 4)) * 8) * 2, b0, b1, b2, b3);
-        mma_bf16(acc[np * 2], a0, a1, a2, a3, b0, b1);
-        mma_bf16(acc[np * 2 + 1], a0, a1, a2, a3, b2, b3);
-      }
+        for (int i = 0; i < 4; ++i) acc[nt][i] = round_bf16(acc[nt][i]) + round_bf16(accb[nt][i]) * gate;
     }
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    const float i0 = 1.0f / l0, i1 = 1.0f / l1;
     const int q0 = qb * 16 + g, q1 = q0 + 8;
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
       const int col = hd * DH + nt * 8 + 2 * t;
-      if (q0 <= last) *reinterpret_cast<uint32_t*>(o + (tok0 + q0) * D + col) = pack_bf16(acc[nt][0] * i0, acc[nt][1] * i0);
-      if (q1 <= last) *reinterpret_cast<uint32_t*>(o + (tok0 + q1) * D + col) = pack_bf16(acc[nt][2] * i1, acc[nt][3] * i1);
+      if (q0 <= last) *reinterpret_cast<uint32_t*>(o + (tok0 + q0) * D + col) = pack_bf16(acc[nt][0], acc[nt][1]);
+      if (q1 <= last) *reinterpret_cast<uint32_t*>(o + (tok0 + q1) * D + col) = pack_bf16(acc[nt][2], acc[nt][3]);
     }
   }
 }
@@ -1465,12 +1552,26 @@ int plan_tiles(const int32_t* tok_off, int n_envs, int32_t* tile_env_begin, int3
   return BNB_OK;
 }
 
-size_t scratch_bytes(int, const BnbBatch& b, int T) {
+static size_t round256(size_t v) { return (v + 255) / 256 * 256; }
+// Shared memory of the attention kernel for environments of up to max_tokens tokens and nb bullets.
+static size_t flash_smem(int max_tokens, int nb) {
+  return (size_t)(3 * max_tokens + 2 * nb) * FLASH_STRIDE + (size_t)max_tokens + (size_t)nb + 16;
+}
+constexpr size_t FLASH_SMEM_MAX = 227 * 1024;
+bool supported_bullets(const BnbBatch& b, int bullets_per_env) {
+  return bullets_per_env >= 1 && flash_smem(b.max_tokens_per_env, bullets_per_env) <= FLASH_SMEM_MAX;
+}
+
+// Layout: status area | q|k|v and attention output of every row (split path: environments larger
+// than a tile, or any sublayer reading bullets) | bullet keys and values of one slice of environments.
+size_t scratch_bytes(int, const BnbBatch& b, int T, int bullets_per_env) {
   size_t bytes = 65536;  // status word (and cycle accounting)
-  if (!fits_tile(b)) bytes += (size_t)T * b.total_tokens * 4 * D * sizeof(__nv_bfloat16);  // q|k|v + attention output
+  if (!fits_tile(b) || bullets_per_env > 0)
+    bytes += round256((size_t)T * b.total_tokens * 4 * D * sizeof(__nv_bfloat16));
+  bytes += round256(bullet_slice_bytes((long long)T * b.n_envs, bullets_per_env, D, sizeof(__nv_bfloat16)));
   return bytes;
 }
-size_t packed_spatial_bytes(int d_model) { return d_model == D ? (size_t)N_SPATIAL_CHUNKS * CHUNK_BYTES : 0; }
+size_t packed_spatial_bytes(int d_model) { return d_model == D ? (size_t)N_SPATIAL_IMAGE * CHUNK_BYTES : 0; }
 size_t packed_temporal_bytes(int d_model) { return d_model == D ? (size_t)N_TEMPORAL_CHUNKS * CHUNK_BYTES + 1024 : 0; }
 
 int pack_spatial(const BnbSpatialWeights& w, int d_model, int n_heads, void* packed, cudaStream_t st) {
@@ -1553,27 +1654,57 @@ static void fill_temporal(SubLayer& s, const BnbTemporalWeights& w, const float*
   s.hid_out = hout;
 }
 
+// Attention of the environments [env_base, env_base + n_env) (group-major), with the bullet keys
+// of the same environments in kvb when nb > 0.
 static int launch_attention(const __nv_bfloat16* qkv, const uint8_t* alive, __nv_bfloat16* o, const BnbBatch& b,
-                            int n_groups, cudaStream_t st) {
+                            int env_base, int n_env, const __nv_bfloat16* kvb, const uint8_t* bullet_active, int nb,
+                            cudaStream_t st) {
   static bool configured[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BNB_ERR_NO_DEVICE;
-  const int max_smem = MAX_ENV_TOKENS * (3 * FLASH_STRIDE + 1) + 16;
   if (!configured[dev]) {
-    if (cudaFuncSetAttribute(k_attention_flash, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(k_attention_flash, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FLASH_SMEM_MAX) != cudaSuccess)
       return BNB_ERR_LAUNCH;
     configured[dev] = true;
   }
-  const size_t smem = (size_t)b.max_tokens_per_env * (3 * FLASH_STRIDE + 1) + 16;
-  dim3 grid(b.n_envs * n_groups, HEADS);
+  if (n_env <= 0) return BNB_OK;
+  const size_t smem = flash_smem(b.max_tokens_per_env, kvb ? nb : 0);
+  if (smem > FLASH_SMEM_MAX) return BNB_ERR_TOO_MANY_TOKENS;
+  dim3 grid(n_env, HEADS);
   count_launch();
-  k_attention_flash<<<grid, 128, smem, st>>>(qkv, alive, o, make_env_map(b), n_groups);
+  k_attention_flash<<<grid, 128, smem, st>>>(qkv, alive, o, make_env_map(b), env_base, kvb, bullet_active, nb);
   return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
+}
+
+// norm_bullet + kv_bullet of `rows` bullet rows (a slice of whole environments) into kvb.
+static int launch_bullet_kv(const BnbSpatialWeights& w, const float* bullet_rows, int rows, __nv_bfloat16* kvb,
+                            int* status, cudaStream_t st) {
+  if (rows <= 0) return BNB_OK;
+  TrunkArgs a{};
+  a.x = bullet_rows;
+  a.y = nullptr;              // nothing but the keys and values leaves this program
+  a.status = status;
+  a.n_groups = 1;
+  a.t_loop = 1;
+  a.n_sub = 1;
+  a.flat_rows = 1;
+  a.sub[0].type = SUB_BULLET_KV;
+  a.sub[0].packed = static_cast<const uint8_t*>(w.packed);
+  a.sub[0].g1 = w.norm_bullet_w;
+  a.sub[0].kvb_out = kvb;
+  BnbBatch rb{};              // every bullet row is a one-token environment without state
+  rb.n_envs = rows;
+  rb.tokens_per_env = 1;
+  rb.max_tokens_per_env = 1;
+  rb.total_tokens = rows;
+  return launch(a, rb, st);
 }
 
 // Accumulates sublayers into tile-kernel launches.  In split mode (environments larger than
 // one tile) a spatial sublayer becomes PRE | attention kernel | POST, and the tile kernel
-// walks plain 128-row slices.
+// walks plain 128-row slices.  A sublayer that reads bullets takes the same three-part form
+// whatever the environment size, with the bullet key/value projection and the attention kernel
+// run once per slice of environments.
 struct Plan {
   const BnbBatch& b;
   cudaStream_t st;
@@ -1584,8 +1715,11 @@ struct Plan {
   const uint8_t* reset_env;
   const float* cur;      // where the residual stream currently lives
   float* y;
+  const BnbBullets* bullets;
   __nv_bfloat16* qkv;
   __nv_bfloat16* o;
+  __nv_bfloat16* kvb;    // bullet keys and values of one slice
+  int kvb_envs;          // environments per slice
   int n_groups, t_loop;  // geometry of the pending program
   TrunkArgs a;
   int n;
@@ -1627,13 +1761,24 @@ struct Plan {
     int rc = ensure(groups, 1);
     if (rc) return rc;
     if (n == MAX_SUBLAYERS && (rc = flush())) return rc;
+    const bool reads = bullets && w.kv_bullet_w;
     fill_spatial(a.sub[n], w);
-    if (!split) { ++n; return BNB_OK; }
+    if (!split && !reads) { ++n; return BNB_OK; }
     a.sub[n].type = SUB_SPATIAL_PRE;
     a.sub[n].qkv_out = qkv;
     ++n;
     if ((rc = flush())) return rc;
-    if ((rc = launch_attention(qkv, alive, o, b, groups, st))) return rc;
+    const int total_envs = groups * b.n_envs;
+    if (reads) {
+      const int nb = bullets->per_env;
+      for (int e0 = 0; e0 < total_envs; e0 += kvb_envs) {
+        const int ne = total_envs - e0 < kvb_envs ? total_envs - e0 : kvb_envs;
+        if ((rc = launch_bullet_kv(w, bullets->tokens + (size_t)e0 * nb * D, ne * nb, kvb, status, st))) return rc;
+        if ((rc = launch_attention(qkv, alive, o, b, e0, ne, kvb, bullets->active, nb, st))) return rc;
+      }
+    } else if ((rc = launch_attention(qkv, alive, o, b, 0, total_envs, nullptr, nullptr, 0, st))) {
+      return rc;
+    }
     fill_spatial(a.sub[n], w);
     a.sub[n].type = SUB_SPATIAL_POST;
     a.sub[n].o_in = o;
@@ -1657,20 +1802,31 @@ static int make_plan(Plan& p, void* scratch, size_t scratch_bytes, int T) {
   p.split = !fits_tile(p.b);
   p.qkv = nullptr;
   p.o = nullptr;
-  if (p.split) {
+  p.kvb = nullptr;
+  p.kvb_envs = 0;
+  const int nb = p.bullets ? p.bullets->per_env : 0;
+  if (nb > 0 && !supported_bullets(p.b, nb)) return BNB_ERR_UNSUPPORTED_DIMS;
+  if (scratch_bytes < tensor::scratch_bytes(D, p.b, T, nb)) return BNB_ERR_SCRATCH_TOO_SMALL;
+  uint8_t* base = static_cast<uint8_t*>(scratch) + 65536;
+  if (p.split || nb > 0) {
     const size_t rows = (size_t)T * p.b.total_tokens;
-    if (scratch_bytes < 65536 + rows * 4 * D * sizeof(__nv_bfloat16)) return BNB_ERR_SCRATCH_TOO_SMALL;
-    p.qkv = reinterpret_cast<__nv_bfloat16*>(static_cast<uint8_t*>(scratch) + 65536);
+    p.qkv = reinterpret_cast<__nv_bfloat16*>(base);
     p.o = p.qkv + rows * 3 * D;
+    base += round256(rows * 4 * D * sizeof(__nv_bfloat16));
+  }
+  if (nb > 0) {
+    p.kvb = reinterpret_cast<__nv_bfloat16*>(base);
+    p.kvb_envs = bullet_slice_envs((long long)T * p.b.n_envs, nb, D, sizeof(__nv_bfloat16));
   }
   p.begin(1, 1);
   return BNB_OK;
 }
 
-int spatial_block(const BnbSpatialWeights& w, int d_model, int n_heads, const float* x, const uint8_t* alive, float* y,
-                  const BnbBatch& b, int n_groups, void* scratch, size_t scratch_bytes, cudaStream_t st) {
+int spatial_block(const BnbSpatialWeights& w, int d_model, int n_heads, const float* x, const uint8_t* alive,
+                  const BnbBullets* bullets, float* y, const BnbBatch& b, int n_groups, void* scratch,
+                  size_t scratch_bytes, cudaStream_t st) {
   if (!supported_batch(d_model, n_heads, b) || !w.packed) return BNB_ERR_UNSUPPORTED_DIMS;
-  Plan p{b, st, nullptr, false, alive, nullptr, nullptr, x, y};
+  Plan p{b, st, nullptr, false, alive, nullptr, nullptr, x, y, bullets};
   int rc = make_plan(p, scratch, scratch_bytes, n_groups);
   if (rc) return rc;
   if ((rc = p.add_spatial(w, n_groups))) return rc;
@@ -1681,7 +1837,7 @@ int temporal_block(const BnbTemporalWeights& w, int d_model, const float* x, flo
                    float* hidden_out, const uint8_t* done, const uint8_t* reset_env, const BnbBatch& b, int T,
                    void* scratch, size_t scratch_bytes, cudaStream_t st) {
   if (!supported_batch(d_model, HEADS, b) || !w.packed) return BNB_ERR_UNSUPPORTED_DIMS;
-  Plan p{b, st, nullptr, false, nullptr, done, reset_env, x, y};
+  Plan p{b, st, nullptr, false, nullptr, done, reset_env, x, y, nullptr};
   int rc = make_plan(p, scratch, scratch_bytes, T);
   if (rc) return rc;
   if ((rc = p.add_temporal(w, hidden_in, hidden_out, T))) return rc;
@@ -1689,15 +1845,15 @@ int temporal_block(const BnbTemporalWeights& w, int d_model, const float* x, flo
 }
 
 int trunk(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal, int n_blocks, int n_spatial,
-          int n_temporal, int d_model, int n_heads, const float* x, const uint8_t* alive, float* y,
-          const float* hidden_in, float* hidden_out, const uint8_t* done, const uint8_t* reset_env,
+          int n_temporal, int d_model, int n_heads, const float* x, const uint8_t* alive, const BnbBullets* bullets,
+          float* y, const float* hidden_in, float* hidden_out, const uint8_t* done, const uint8_t* reset_env,
           const BnbBatch& b, int T, void* scratch, size_t scratch_bytes, cudaStream_t st) {
   if (!supported_batch(d_model, n_heads, b)) return BNB_ERR_UNSUPPORTED_DIMS;
   for (int i = 0; i < n_blocks * n_spatial; ++i) if (!spatial[i].packed) return BNB_ERR_UNSUPPORTED_DIMS;
   for (int i = 0; i < n_blocks * n_temporal; ++i) if (!temporal[i].packed) return BNB_ERR_UNSUPPORTED_DIMS;
   // a time walk carries its state through hidden_out between timesteps
   if (T > 1 && n_blocks * n_temporal > 0 && b.total_ships > 0 && !hidden_out) return BNB_ERR_NULL_POINTER;
-  Plan p{b, st, nullptr, false, alive, done, reset_env, x, y};
+  Plan p{b, st, nullptr, false, alive, done, reset_env, x, y, bullets};
   int rc = make_plan(p, scratch, scratch_bytes, T);
   if (rc) return rc;
   const size_t slot_stride = (size_t)b.total_ships * 4 * D;

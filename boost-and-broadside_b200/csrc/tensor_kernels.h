@@ -17,22 +17,26 @@ bool supported_batch(int D, int H, const BnbBatch& b);
 int plan_tiles(const int32_t* tok_off_host, int n_envs, int32_t* tile_env_begin_host, int32_t* tile_env_ids_host,
                int capacity, int* n_tiles);
 
-size_t scratch_bytes(int D, const BnbBatch& b, int T);
+// True when the attention kernel can stage this many bullet keys beside an environment's tokens.
+bool supported_bullets(const BnbBatch& b, int bullets_per_env);
+
+size_t scratch_bytes(int D, const BnbBatch& b, int T, int bullets_per_env);
 size_t packed_spatial_bytes(int D);
 size_t packed_temporal_bytes(int D);
 int pack_spatial(const BnbSpatialWeights& w, int D, int H, void* packed, cudaStream_t st);
 int pack_temporal(const BnbTemporalWeights& w, int D, void* packed, cudaStream_t st);
 
-int spatial_block(const BnbSpatialWeights& w, int D, int H, const float* x, const uint8_t* alive, float* y,
-                  const BnbBatch& b, int n_groups, void* scratch, size_t scratch_bytes, cudaStream_t st);
+int spatial_block(const BnbSpatialWeights& w, int D, int H, const float* x, const uint8_t* alive,
+                  const BnbBullets* bullets, float* y, const BnbBatch& b, int n_groups, void* scratch,
+                  size_t scratch_bytes, cudaStream_t st);
 
 int temporal_block(const BnbTemporalWeights& w, int D, const float* x, float* y, const float* hidden_in,
                    float* hidden_out, const uint8_t* done, const uint8_t* reset_env, const BnbBatch& b, int T,
                    void* scratch, size_t scratch_bytes, cudaStream_t st);
 
 int trunk(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal, int n_blocks, int n_spatial,
-          int n_temporal, int D, int H, const float* x, const uint8_t* alive, float* y, const float* hidden_in,
-          float* hidden_out, const uint8_t* done, const uint8_t* reset_env, const BnbBatch& b, int T,
+          int n_temporal, int D, int H, const float* x, const uint8_t* alive, const BnbBullets* bullets, float* y,
+          const float* hidden_in, float* hidden_out, const uint8_t* done, const uint8_t* reset_env, const BnbBatch& b, int T,
           void* scratch, size_t scratch_bytes, cudaStream_t st);
 
 }  // namespace tensor

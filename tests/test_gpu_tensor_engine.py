@@ -224,3 +224,95 @@ def test_full_size_configurations_tensor_vs_simt(name):
     ey = float((yt - ys).abs().max()) / float(ys.abs().max())
     eh = float((ht - hs).abs().max()) / float(hs.abs().max())
     assert ey < 2e-2 and eh < 2e-2, (ey, eh)
+
+
+# ------------------------------------------------------------------ bullet cross-attention
+
+
+def _bullets(n_envs, nb, seed, p_active=0.4):
+    gen = torch.Generator().manual_seed(seed)
+    bul = torch.randn(n_envs, nb, 128, generator=gen)
+    mask = torch.rand(n_envs, nb, generator=gen) < p_active
+    mask[0] = False                    # nothing in flight
+    if n_envs > 1:
+        mask[1] = True                 # full ring buffer
+    return bul, mask
+
+
+@pytest.mark.parametrize("n_envs,ships,fields,nb", [(10, 8, 4, 80), (37, 8, 0, 33), (5, 30, 2, 300), (3, 1, 0, 1), (2, 100, 52, 80)])
+def test_step_with_bullets_tensor_vs_oracle_and_simt(n_envs, ships, fields, nb):
+    """Bullet-reading sublayers on the tensor engine: the bullet key/value projection as a tile
+    program over bullet rows, then one attention kernel for both softmaxes; environments of up
+    to one tile and larger ones (152 tokens)."""
+    from boost_and_broadside_b200 import workloads as W
+
+    _capi, SIMT, TENSOR = _engines()
+    w = W.c2(n_envs=n_envs, seed=23, ships=ships, fields=fields)
+    bul, mask = _bullets(n_envs, nb, 5)
+    trunk = build_trunk([128, 4, 2, 2, 1, 1])
+    ref_y, ref_h = O.trunk_step(w.x, w.alive, w.hidden, trunk_params(trunk), 4, "bf16", bul, mask)
+    ref_y0, _ = O.trunk_step(w.x, w.alive, w.hidden, trunk_params(trunk), 4, "bf16")
+    assert norm_err(ref_y, ref_y0) > 1e-2          # the bullets matter in this case
+    trunk = trunk.to(DEV)
+    x, alive, hidden, bul_d, mask_d = (t.to(DEV) for t in (w.x, w.alive, w.hidden, bul, mask))
+    with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
+        ys, hs = trunk.step(x, alive, hidden, engine=SIMT, bullets=bul_d, bullet_mask=mask_d)
+        yt, ht = trunk.step(x, alive, hidden, engine=TENSOR, bullets=bul_d, bullet_mask=mask_d)
+        yn, _ = trunk.step(x, alive, hidden, engine=TENSOR, bullets=bul_d, bullet_mask=None)
+    _status_ok()
+    assert_close(yt, ref_y, "bf16", "tensor y vs oracle")
+    assert_close(ht, ref_h, "bf16", "tensor hidden vs oracle")
+    assert norm_err(yt.cpu(), ys.cpu()) < 1e-2
+    assert norm_err(ht.cpu(), hs.cpu()) < 1e-2
+    ref_n, _ = O.trunk_step(w.x, w.alive, w.hidden, trunk_params(trunk.cpu()), 4, "bf16", bul, None)
+    assert_close(yn, ref_n, "bf16", "tensor y vs oracle, no bullet mask")
+
+
+def test_sequence_with_bullets_tensor_vs_oracle():
+    from boost_and_broadside_b200 import workloads as W
+
+    _capi, SIMT, TENSOR = _engines()
+    w = W.c4(n_envs=9, timesteps=5, seed=29)
+    T, B = w.x.shape[0], w.x.shape[1]
+    bul, mask = _bullets(T * B, 40, 6)
+    trunk = build_trunk([128, 4, 2, 2, 1, 1])
+    ref_y, ref_h = O.trunk_sequence(w.x, w.alive, w.hidden, w.done, trunk_params(trunk), 4, "bf16", bul, mask)
+    trunk = trunk.to(DEV)
+    with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
+        yt, ht = trunk.sequence(w.x.to(DEV), w.alive.to(DEV), w.hidden.to(DEV), w.done.to(DEV), engine=TENSOR,
+                                bullets=bul.to(DEV), bullet_mask=mask.to(DEV))
+    _status_ok()
+    assert_close(yt, ref_y, "bf16", "sequence y vs oracle")
+    assert_close(ht, ref_h, "bf16", "sequence hidden vs oracle")
+
+
+def test_bullets_full_size_step_is_sliced_and_engines_agree():
+    """The rollout-step configuration with its 80 bullet slots per environment: 8192 x 80 bullet
+    rows exceed one slice of the key/value scratch on both engines, so the projection and the
+    attention run slice by slice; tensor and SIMT engines must agree and every environment
+    without an active bullet must equal the bullet-free result."""
+    from boost_and_broadside_b200 import workloads as W
+
+    _capi, SIMT, TENSOR = _engines()
+    w = W.c2(seed=31)
+    n_envs = w.x.shape[0]
+    batch = _capi.uniform_batch(n_envs, w.x.shape[1], 8)
+    assert _capi.lib.bnb_scratch_bytes(128, batch, 1, 80) < n_envs * 80 * 256 * 4  # smaller than all keys/values in fp32
+    gen = torch.Generator().manual_seed(7)
+    bul = torch.randn(n_envs, 80, 128, generator=gen)
+    mask = torch.rand(n_envs, 80, generator=gen) < 0.3
+    idle = torch.rand(n_envs, generator=gen) < 0.25
+    mask[idle] = False
+    trunk = build_trunk([128, 4, 2, 2, 1, 1]).to(DEV)
+    x, alive, hidden, bul_d, mask_d = (t.to(DEV) for t in (w.x, w.alive, w.hidden, bul, mask))
+    with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
+        ys, hs = trunk.step(x, alive, hidden, engine=SIMT, bullets=bul_d, bullet_mask=mask_d)
+        yt, ht = trunk.step(x, alive, hidden, engine=TENSOR, bullets=bul_d, bullet_mask=mask_d)
+        y0, _ = trunk.step(x, alive, hidden, engine=TENSOR)
+    _status_ok()
+    assert torch.isfinite(yt).all() and torch.isfinite(ht).all()
+    assert norm_err(yt.cpu(), ys.cpu()) < 2e-2
+    assert norm_err(ht.cpu(), hs.cpu()) < 2e-2
+    idle_d = idle.to(DEV)
+    assert norm_err(yt[idle_d].cpu(), y0[idle_d].cpu()) < 1e-2      # gated off; kernels differ, values agree
+    assert norm_err(yt[~idle_d].cpu(), y0[~idle_d].cpu()) > 1e-2    # and the bullets matter elsewhere
