@@ -1,6 +1,6 @@
 """Benchmark of the YemongPolicy trunk hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload C2|C3|C4|C5]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload C2|C2B|C3|C4|C5]
 
 A step is one pass of the trunk over one batch of synthetic environments.  The default
 workload is the full rollout policy step (all trunk attention layers + Griffin RG-LRU single
@@ -60,6 +60,8 @@ def make_workload(name: str, rank: int, scale: float = 1.0):
     seed = 100 + rank
     if name == "C2":
         return W.c2(n_envs=max(1, int(8192 * scale)), seed=seed)
+    if name == "C2B":
+        return W.c2b(n_envs=max(1, int(8192 * scale)), seed=seed)
     if name == "C3":
         return W.c3(n_envs=max(1, int(1024 * scale)), seed=seed)
     if name == "C4":
@@ -71,6 +73,7 @@ def make_workload(name: str, rank: int, scale: float = 1.0):
 
 WORKLOAD_TEXT = {
     "C2": "rollout trunk step, 8192 envs x (8 ships + 4 fields), bf16 activations / fp32 state",
+    "C2B": "rollout trunk step with bullet cross-attention, 8192 envs x (8 ships + 4 fields + 80 bullet slots), bf16",
     "C3": "trunk step, 1024 envs x 152 ships (64 v 88), bf16",
     "C4": "recurrent-PPO sequence forward, T=32 x 4096 envs x 8 ships, bf16",
     "C5": "ragged trunk step, 16384 envs, tokens U{2..128}, bf16",
@@ -143,7 +146,7 @@ def oracle_runner(workload, params, n_heads: int):
 
     w = workload
     if w.kind == "step":
-        return lambda: O.trunk_step(w.x, w.alive, w.hidden, params, n_heads, w.mode)
+        return lambda: O.trunk_step(w.x, w.alive, w.hidden, params, n_heads, w.mode, w.bullets, w.bullet_mask)
     if w.kind == "sequence":
         return lambda: O.trunk_sequence(w.x, w.alive, w.hidden, w.done, params, n_heads, w.mode)
     if w.kind == "ragged":
@@ -154,7 +157,7 @@ def oracle_runner(workload, params, n_heads: int):
 
 def cpu_sample_scale(name: str) -> float:
     # bounded samples of the workload: a few seconds of CPU work per pass
-    return {"C2": 1024 / 8192, "C3": 64 / 1024, "C4": 32 / 4096, "C5": 768 / 16384}[name]
+    return {"C2": 1024 / 8192, "C2B": 512 / 8192, "C3": 64 / 1024, "C4": 32 / 4096, "C5": 768 / 16384}[name]
 
 
 def time_cpu(name: str, passes: int, warmup: int) -> dict:
@@ -230,9 +233,9 @@ def run_ours(args) -> None:
     cfg = W.rl_config()
     torch.manual_seed(0)
     trunk = bnb.YemongTrunk(cfg).eval()
-    n_params = sum(p.numel() for n, p in trunk.named_parameters() if "bullet" not in n)
-    trunk = trunk.to(dev)
     w = make_workload(args.workload, rank, args.envs_scale)
+    n_params = sum(p.numel() for n, p in trunk.named_parameters() if w.bullets is not None or "bullet" not in n)
+    trunk = trunk.to(dev)
     engine = {"auto": _capi.ENGINE_AUTO, "simt": _capi.ENGINE_SIMT, "tensor": _capi.ENGINE_TENSOR}[args.engine]
 
     x_h = w.x.pin_memory()
@@ -242,9 +245,17 @@ def run_ours(args) -> None:
     hidden = [w.hidden.to(dev), None]
     done_d = None if w.done is None else w.done.to(dev)
     ragged = bnb.RaggedBatch(w.n_tokens, w.n_ships) if w.kind == "ragged" else None
+    has_bullets = w.bullets is not None
+    bul_h = w.bullets.pin_memory() if has_bullets else None
+    bmask_h = w.bullet_mask.pin_memory() if has_bullets else None
+    bul_d = bul_h.to(dev, non_blocking=True) if has_bullets else None
+    bmask_d = bmask_h.to(dev, non_blocking=True) if has_bullets else None
 
-    def step(xin, alive, h):
+    def step(xin, alive, h, bul=None, bmask=None):
         if w.kind == "step":
+            if has_bullets:
+                return trunk.step(xin, alive, h, engine=engine, bullets=bul_d if bul is None else bul,
+                                  bullet_mask=bmask_d if bmask is None else bmask)
             return trunk.step(xin, alive, h, engine=engine)
         if w.kind == "sequence":
             return trunk.sequence(xin, alive, h, done_d, engine=engine)
@@ -289,6 +300,8 @@ def run_ours(args) -> None:
     y_h = [torch.empty(w.x.shape, dtype=torch.float32).pin_memory() for _ in range(2)]
     x_in = [torch.empty_like(x_d) for _ in range(2)]
     a_in = [torch.empty_like(alive_d) for _ in range(2)]
+    b_in = [torch.empty_like(bul_d) for _ in range(2)] if has_bullets else None
+    m_in = [torch.empty_like(bmask_d) for _ in range(2)] if has_bullets else None
     s_in, s_cmp, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
 
     def e2e_loop(n, h):
@@ -302,10 +315,13 @@ def run_ours(args) -> None:
                     s_in.wait_event(ev_cmp[i - 2])  # the kernels that read this input buffer are done
                 x_in[b].copy_(x_h, non_blocking=True)
                 a_in[b].copy_(alive_h, non_blocking=True)
+                if has_bullets:
+                    b_in[b].copy_(bul_h, non_blocking=True)
+                    m_in[b].copy_(bmask_h, non_blocking=True)
                 ev_in[i].record(s_in)
             with torch.cuda.stream(s_cmp):
                 s_cmp.wait_event(ev_in[i])
-                y, h2 = step(x_in[b], a_in[b], h)
+                y, h2 = step(x_in[b], a_in[b], h, b_in[b] if has_bullets else None, m_in[b] if has_bullets else None)
                 h = h2 if carry else h
                 ev_cmp[i].record(s_cmp)
             with torch.cuda.stream(s_out):
@@ -360,7 +376,8 @@ def run_ours(args) -> None:
                        "tokens_per_step_per_gpu": tokens, "envs_scale": args.envs_scale, "l2": "inputs larger than L2 (no flush)",
                        "weights": "random init, seed 0, rl-fields dims (D=128, 4 heads, S S T | S S T)"},
             "e2e": {"value": tokens_all * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
-                    "h2d_bytes_per_step": x_h.numel() * 4 + alive_h.numel(), "d2h_bytes_per_step": y_h[0].numel() * 4,
+                    "h2d_bytes_per_step": x_h.numel() * 4 + alive_h.numel()
+                    + (bul_h.numel() * 4 + bmask_h.numel() if has_bullets else 0), "d2h_bytes_per_step": y_h[0].numel() * 4,
                     "note": "every step: x and alive from pinned host memory, trunk step, y back to pinned host memory; upload, kernels and download pipelined on three streams; hidden state carried on the device"},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,

@@ -6,7 +6,7 @@
 
 namespace bnb {
 
-constexpr size_t kBulletScratchCap = (size_t)256 << 20;
+constexpr size_t kBulletScratchCap = (size_t)512 << 20;
 
 // Environments per slice: as many as keep nb rows of [k | v] (2D elements of `elt` bytes) per
 // environment under the cap, at least one, at most all.

@@ -106,6 +106,10 @@ struct TrunkArgs {
   int flat_rows;      // 1: tiles are plain 128-row slices of the token rows (no attention inside)
   const int* tile_env_begin;  // ragged batches: range of each tile in tile_env_ids (+ end), else null
   const int* tile_env_ids;    // ragged batches: environments in tile order
+  // Bullet key/value program only: tile row r reads input row row_index[r], and only the first
+  // *n_rows_dev rows exist (the active bullets, compacted on the device); null = all rows, in order.
+  const int* row_index;
+  const int* n_rows_dev;
   int* status;
   SubLayer sub[MAX_SUBLAYERS];
 };
@@ -140,6 +144,9 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* st
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -819,30 +826,46 @@ __device__ __forceinline__ void run_spatial_post(Ctx& c, const SubLayer& s, size
   ffn<NQ>(c);
 }
 
-// Bullet rows: norm_bullet and the kv_bullet projection, keys then values of all heads, written
-// as bf16 to global scratch (models/yemong/attention.py:151 of the reference).
+// Bullet rows: norm_bullet and the kv_bullet projection, keys and values of all heads, written
+// as bf16 to global scratch (models/yemong/attention.py:151 of the reference).  This program
+// runs alone in its launch and its four weight chunks are the same for every tile, so they are
+// loaded once per CTA (ring slots 0 and 1: keys; staging area and P: values) and stay put.
+// The residual is dead after the norm, so one round projects the keys into the accumulator
+// columns and the values into the residual columns.
 template <int NQ>
 __device__ __forceinline__ void run_bullet_kv(Ctx& c, const SubLayer& s, size_t grow, bool row_valid) {
   constexpr int CPT = 128 / NQ;
   norm_to_A<NQ>(c, s.g1);
-  for (int half = 0; half < 2; ++half) {
-    round_begin<NQ>(c);
-    if (threadIdx.x == 0) {
-      issue_chunk(c, c.sA, 128, COL_ACC, 0, 0);
-      issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_ACC, 1, 1);
+  round_begin<NQ>(c);
+  if (threadIdx.x == 0) {
+    if (!(c.parity & 1u)) {   // first tile of this CTA: the resident chunks are still arriving
+      mbar_wait(c.bar_full[0], 0, c.status, c.aborted, ST_TIMEOUT_FULL);
+      c.parity |= 1u;
     }
-    round_end<NQ>(c);
+    tc_fence_after();
+    const uint32_t idesc = instr_desc(128);
+    const uint32_t wk[2] = {c.sRing, c.sRing + CHUNK_BYTES}, wv[2] = {c.sStage, c.sP};
+#pragma unroll
+    for (int atom = 0; atom < 2; ++atom)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        tc_mma(c.tmem + COL_ACC, smem_desc(c.sA + atom * CHUNK_BYTES + k * 32), smem_desc(wk[atom] + k * 32), idesc, (atom | k) ? 1u : 0u);
+        tc_mma(c.tmem + COL_RESID, smem_desc(c.sA + atom * CHUNK_BYTES + k * 32), smem_desc(wv[atom] + k * 32), idesc, (atom | k) ? 1u : 0u);
+      }
+  }
+  round_end<NQ>(c);
+#pragma unroll
+  for (int half = 0; half < 2; ++half)
 #pragma unroll
     for (int ch = 0; ch < CPT / 32; ++ch) {
       uint32_t v[32];
-      tmem_ld32(c.lane_addr + COL_ACC + c.part * CPT + ch * 32, v);
+      tmem_ld32(c.lane_addr + (half ? COL_RESID : COL_ACC) + c.part * CPT + ch * 32, v);
       if (row_valid) {
         __nv_bfloat16* dst = s.kvb_out + grow * (2 * D) + half * D + c.part * CPT + ch * 32;
 #pragma unroll
         for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(dst + q * 8) = pack8(&v[q * 8]);
       }
     }
-  }
 }
 
 struct RowState {
@@ -1172,15 +1195,31 @@ __global__ void __launch_bounds__(128 * NQ, 2) k_trunk_tiles(const __grid_consta
       c.p_left = my_tiles * args.t_loop * s_sched_len;
     }
     c.occ[0] = c.occ[1] = c.occ[2] = -1;
+    // A bullet key/value program keeps its four weight chunks resident instead of streaming them.
+    const bool kv_resident = args.n_sub == 1 && s_sub[0].type == SUB_BULLET_KV;
+    if (kv_resident) {
+      c.p_left = 0;
+      if (warp == 4 * NQ - 1 && blockIdx.x < args.n_tiles) {
+        const int lane = tid & 31;
+        if (lane == 0) mbar_expect_tx(c.bar_full[0], N_BULLET_CHUNKS * CHUNK_BYTES);
+        __syncwarp();
+        if (lane < N_BULLET_CHUNKS) {
+          const uint32_t dst = lane == 0 ? c.sRing : (lane == 1 ? c.sRing + CHUNK_BYTES : (lane == 2 ? c.sStage : c.sP));
+          bulk_g2s(dst, s_sub[0].packed + (size_t)(N_SPATIAL_CHUNKS + lane) * CHUNK_BYTES, CHUNK_BYTES, c.bar_full[0]);
+        }
+      }
+    }
     if (warp == 4 * NQ - 1) refill(c);
     uint8_t* meta = smem + OFF_META;
     const EnvMap& map = args.map;
     const int NM = map.tokens_per_env;
     const int row = c.row;
 
+    const int flat_limit = args.n_rows_dev ? *args.n_rows_dev : map.total_tokens;
     for (int tile = blockIdx.x; tile < args.n_tiles; tile += gridDim.x) {
       // ---- rows of this tile: whole environments, ships first then fields in each
       const int grp = tile / args.env_tiles, eb = tile - grp * args.env_tiles;
+      if (args.flat_rows && eb * TILE >= flat_limit) continue;   // same decision in every thread of the CTA
       bool valid;
       int env, tok, env_first, env_n, env_ships;
       size_t grow = 0;
@@ -1188,7 +1227,17 @@ __global__ void __launch_bounds__(128 * NQ, 2) k_trunk_tiles(const __grid_consta
       if (args.flat_rows) {
         // plain slices of the token rows; the environment of a row is looked up
         const int r = eb * TILE + row;
-        valid = r < map.total_tokens;
+        if (kv_resident) {
+          // ask L2 for this thread's share of the next tile's input rows
+          const long long rn = (long long)r + (long long)gridDim.x * TILE;
+          if (rn < flat_limit) {
+            const size_t src = args.row_index ? (size_t)args.row_index[rn] : (size_t)rn;
+            const char* nx = reinterpret_cast<const char*>(args.x + src * D) + c.part * (512 / NQ);
+#pragma unroll
+            for (int l = 0; l < 4 / NQ; ++l) asm volatile("prefetch.global.L2 [%0];" ::"l"(nx + l * 128));
+          }
+        }
+        valid = r < flat_limit;
         env = valid ? map.env_of_token(r) : 0;
         env_first = 0;
         env_n = 1;
@@ -1229,6 +1278,8 @@ __global__ void __launch_bounds__(128 * NQ, 2) k_trunk_tiles(const __grid_consta
         hrow_if_ship = env * map.ships_per_env + tok;
       }
       if (!valid) { grow = 0; env = 0; }
+      // input row of this tile row (differs from the output row only for compacted bullet rows)
+      const size_t xrow0 = (args.row_index && valid) ? (size_t)args.row_index[grow] : grow;
       const bool is_ship = valid && tok < env_ships;
       const bool is_field = valid && !is_ship;
       RowState rs;
@@ -1256,7 +1307,7 @@ __global__ void __launch_bounds__(128 * NQ, 2) k_trunk_tiles(const __grid_consta
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
             float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (valid) f = *reinterpret_cast<const float4*>(args.x + trow * D + c.part * CPT + ch * 32 + q * 4);
+            if (valid) f = *reinterpret_cast<const float4*>(args.x + (xrow0 + (size_t)t * map.total_tokens) * D + c.part * CPT + ch * 32 + q * 4);
             v[q * 4 + 0] = __float_as_uint(f.x); v[q * 4 + 1] = __float_as_uint(f.y);
             v[q * 4 + 2] = __float_as_uint(f.z); v[q * 4 + 3] = __float_as_uint(f.w);
           }
@@ -1302,6 +1353,10 @@ __global__ void __launch_bounds__(128 * NQ, 2) k_trunk_tiles(const __grid_consta
         }
       }
     }
+    // a CTA whose tiles were all beyond the compacted row count has not yet waited for its
+    // resident weight chunks; they must have landed before the CTA gives up its shared memory
+    if (kv_resident && tid == 0 && blockIdx.x < args.n_tiles && !(c.parity & 1u))
+      mbar_wait(c.bar_full[0], 0, c.status, c.aborted, ST_TIMEOUT_FULL);
 #ifdef BNB_TIMING
   if (tid == 64 || tid == 0) {
     c.tacc[TM_TOTAL] = clock64() - t_kernel0;
@@ -1329,11 +1384,13 @@ __global__ void __launch_bounds__(128 * NQ, 2) k_trunk_tiles(const __grid_consta
 // reads bullets, the environment's bullet keys and values (written by the BULLET_KV phase) are
 // staged too and get a softmax of their own; its output, gated to zero when the environment has
 // no active bullet, is added to the self-attention output (attention.py:149-166).
-constexpr int FLASH_STRIDE = 80;  // bytes per staged row of one head (32 bf16 + pad)
+// A CTA stages HPC heads of one environment (all four when they fit in shared memory, else one):
+// a staged row holds HPC x 32 bf16 plus 16 bytes of padding, which keeps ldmatrix conflict-free.
+__host__ __device__ constexpr int flash_stride(int hpc) { return hpc * 64 + 16; }
 
 // One softmax pass of a block of 16 queries (fragments qa) over n keys staged at sK / sV with
 // liveness bytes `live`; returns the normalised output fragments in acc.
-__device__ __forceinline__ void flash_pass(const uint32_t (&qa)[2][4], uint32_t sK, uint32_t sV,
+__device__ __forceinline__ void flash_pass(const uint32_t (&qa)[2][4], uint32_t sK, uint32_t sV, int stride,
                                            const uint8_t* __restrict__ live, int n, int lane, float (&acc)[4][4]) {
   const int t = lane & 3;
   const float scale = 0.17677669529663687f;
@@ -1354,7 +1411,7 @@ __device__ __forceinline__ void flash_pass(const uint32_t (&qa)[2][4], uint32_t 
 #pragma unroll
     for (int ks = 0; ks < 2; ++ks) {
       uint32_t b0, b1, b2, b3;
-      ldsm_x4(sK + krow * FLASH_STRIDE + (ks * 16 + ((lane >> 3) & 1) * 8) * 2, b0, b1, b2, b3);
+      ldsm_x4(sK + krow * stride + (ks * 16 + ((lane >> 3) & 1) * 8) * 2, b0, b1, b2, b3);
       mma_bf16(sc[0], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
       mma_bf16(sc[1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b2, b3);
     }
@@ -1365,7 +1422,7 @@ __device__ __forceinline__ void flash_pass(const uint32_t (&qa)[2][4], uint32_t 
       for (int i = 0; i < 2; ++i) {
         const int j = kb * 16 + nt * 8 + 2 * t + i;
         const bool valid = j < n;
-        const bool lv = valid && live[j];
+        const bool lv = valid && (!live || live[j]);
         const float a = valid ? (lv ? sc[nt][i] * scale : kMaskedScore) : -INFINITY;
         const float b = valid ? (lv ? sc[nt][2 + i] * scale : kMaskedScore) : -INFINITY;
         sc[nt][i] = a;
@@ -1404,7 +1461,7 @@ __device__ __forceinline__ void flash_pass(const uint32_t (&qa)[2][4], uint32_t 
 #pragma unroll
     for (int np = 0; np < 2; ++np) {
       uint32_t b0, b1, b2, b3;
-      ldsm_x4_t(sV + vrow * FLASH_STRIDE + ((np * 2 + (lane >> 4)) * 8) * 2, b0, b1, b2, b3);
+      ldsm_x4_t(sV + vrow * stride + ((np * 2 + (lane >> 4)) * 8) * 2, b0, b1, b2, b3);
       mma_bf16(acc[np * 2], a0, a1, a2, a3, b0, b1);
       mma_bf16(acc[np * 2 + 1], a0, a1, a2, a3, b2, b3);
     }
@@ -1421,72 +1478,157 @@ __device__ __forceinline__ void flash_pass(const uint32_t (&qa)[2][4], uint32_t 
   }
 }
 
-// env_base: first environment (group-major) of this launch.  kvb / bullet_active / nb describe
-// the bullet keys of the launch's environments (kvb indexed from env_base), or null / 0.
+// env_base: first environment (group-major) of this launch.  kvb holds the bullet keys and values
+// of the launch's environments (null: none): with env_off, the rows of the active bullets only,
+// environment i of the launch owning rows [env_off[i], env_off[i+1]) (an inactive bullet has
+// weight exactly 0 and an environment without active bullets is gated off, so neither needs a
+// row); without env_off, nb rows per environment, all of them keys (no mask was given).
+// blockIdx.y selects a group of hpc heads; the warps share out (head, query block) pairs.
 __global__ void __launch_bounds__(128) k_attention_flash(const __nv_bfloat16* __restrict__ qkv, const uint8_t* __restrict__ alive,
-                                                         __nv_bfloat16* __restrict__ o, EnvMap map, int env_base,
+                                                         __nv_bfloat16* __restrict__ o, EnvMap map, int env_base, int hpc,
                                                          const __nv_bfloat16* __restrict__ kvb,
-                                                         const uint8_t* __restrict__ bullet_active, int nb) {
+                                                         const int* __restrict__ env_off, int nb) {
   extern __shared__ __align__(16) uint8_t fs[];
-  const int env_g = env_base + blockIdx.x, hd = blockIdx.y;
+  const int env_g = env_base + blockIdx.x, hd0 = blockIdx.y * hpc;
   const int grp = env_g / map.n_envs, e = env_g - grp * map.n_envs;
   const size_t tok0 = (size_t)grp * map.total_tokens + map.env_tok_begin(e);
   const int n = map.env_tok_count(e);
-  if (!kvb) nb = 0;
+  size_t brow0 = 0;
+  if (!kvb) {
+    nb = 0;
+  } else if (env_off) {
+    brow0 = (size_t)env_off[blockIdx.x];
+    nb = env_off[blockIdx.x + 1] - (int)brow0;
+  } else {
+    brow0 = (size_t)blockIdx.x * nb;
+  }
+  const int stride = flash_stride(hpc);
   uint8_t* Qs = fs;
-  uint8_t* Ks = Qs + (size_t)n * FLASH_STRIDE;
-  uint8_t* Vs = Ks + (size_t)n * FLASH_STRIDE;
-  uint8_t* Kb = Vs + (size_t)n * FLASH_STRIDE;
-  uint8_t* Vb = Kb + (size_t)nb * FLASH_STRIDE;
-  uint8_t* live = Vb + (size_t)nb * FLASH_STRIDE;
-  uint8_t* liveb = live + n;
-  for (int i = threadIdx.x; i < n * 12; i += blockDim.x) {
-    const int r = i / 12, part = (i % 12) >> 2, q = i & 3;
-    const uint4 v = *reinterpret_cast<const uint4*>(qkv + (tok0 + r) * (3 * D) + part * D + hd * DH + q * 8);
-    *reinterpret_cast<uint4*>(fs + ((size_t)part * n + r) * FLASH_STRIDE + q * 16) = v;
+  uint8_t* Ks = Qs + (size_t)n * stride;
+  uint8_t* Vs = Ks + (size_t)n * stride;
+  uint8_t* Kb = Vs + (size_t)n * stride;
+  uint8_t* Vb = Kb + (size_t)nb * stride;
+  uint8_t* live = Vb + (size_t)nb * stride;
+  const int gpr = hpc * 4;   // 16-byte groups per staged row
+  // asynchronous 16-byte copies: all of them are in flight before the first one is waited for
+  for (int i = threadIdx.x; i < n * 3 * gpr; i += blockDim.x) {
+    const int r = i / (3 * gpr), rem = i - r * 3 * gpr, part = rem / gpr, q = rem - part * gpr;
+    cp_async16(smem_u32(fs + ((size_t)part * n + r) * stride + q * 16),
+               qkv + (tok0 + r) * (3 * D) + part * D + hd0 * DH + q * 8);
   }
-  for (int i = threadIdx.x; i < nb * 8; i += blockDim.x) {
-    const int r = i >> 3, part = (i >> 2) & 1, q = i & 3;
-    const uint4 v = *reinterpret_cast<const uint4*>(kvb + ((size_t)blockIdx.x * nb + r) * (2 * D) + part * D + hd * DH + q * 8);
-    *reinterpret_cast<uint4*>(Kb + ((size_t)part * nb + r) * FLASH_STRIDE + q * 16) = v;
+  for (int i = threadIdx.x; i < nb * 2 * gpr; i += blockDim.x) {
+    const int r = i / (2 * gpr), rem = i - r * 2 * gpr, part = rem / gpr, q = rem - part * gpr;
+    cp_async16(smem_u32(Kb + ((size_t)part * nb + r) * stride + q * 16),
+               kvb + (brow0 + r) * (2 * D) + part * D + hd0 * DH + q * 8);
   }
+  asm volatile("cp.async.commit_group;" ::: "memory");
   for (int i = threadIdx.x; i < n; i += blockDim.x) live[i] = alive ? alive[tok0 + i] : (uint8_t)1;
-  int any_here = 0;
-  for (int i = threadIdx.x; i < nb; i += blockDim.x) {
-    const uint8_t a = bullet_active ? bullet_active[(size_t)env_g * nb + i] : (uint8_t)1;
-    liveb[i] = a;
-    any_here |= a;
-  }
-  const float gate = __syncthreads_or(any_here) ? 1.f : 0.f;   // also orders the staging writes
-  const uint32_t sQ = smem_u32(Qs), sK = smem_u32(Ks), sV = smem_u32(Vs);
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int last = n - 1;
-  for (int qb = warp; qb * 16 < n; qb += 4) {
+  const int nqb = (n + 15) >> 4;
+  for (int item = warp; item < hpc * nqb; item += 4) {
+    const int hl = item % hpc, qb = item / hpc;
+    const uint32_t hoff = (uint32_t)hl * 64;
+    const uint32_t sQ = smem_u32(Qs) + hoff, sK = smem_u32(Ks) + hoff, sV = smem_u32(Vs) + hoff;
     uint32_t qa[2][4];
     {
       const int row = min(qb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, last);
 #pragma unroll
       for (int ks = 0; ks < 2; ++ks)
-        ldsm_x4(sQ + row * FLASH_STRIDE + (ks * 16 + (lane >> 4) * 8) * 2, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3]);
+        ldsm_x4(sQ + row * stride + (ks * 16 + (lane >> 4) * 8) * 2, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3]);
     }
     float acc[4][4];
-    flash_pass(qa, sK, sV, live, n, lane, acc);
+    flash_pass(qa, sK, sV, stride, live, n, lane, acc);
     if (nb > 0) {
       float accb[4][4];
-      flash_pass(qa, smem_u32(Kb), smem_u32(Vb), liveb, nb, lane, accb);
+      flash_pass(qa, smem_u32(Kb) + hoff, smem_u32(Vb) + hoff, stride, nullptr, nb, lane, accb);
       // both outputs are bf16 tensors in the reference; so is their sum
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[nt][i] = round_bf16(acc[nt][i]) + round_bf16(accb[nt][i]) * gate;
+        for (int i = 0; i < 4; ++i) acc[nt][i] = round_bf16(acc[nt][i]) + round_bf16(accb[nt][i]);
     }
     const int q0 = qb * 16 + g, q1 = q0 + 8;
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
-      const int col = hd * DH + nt * 8 + 2 * t;
+      const int col = (hd0 + hl) * DH + nt * 8 + 2 * t;
       if (q0 <= last) *reinterpret_cast<uint32_t*>(o + (tok0 + q0) * D + col) = pack_bf16(acc[nt][0], acc[nt][1]);
       if (q1 <= last) *reinterpret_cast<uint32_t*>(o + (tok0 + q1) * D + col) = pack_bf16(acc[nt][2], acc[nt][3]);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ compaction of the active bullets
+//
+// Three small kernels turn the active mask of a slice of environments into (a) env_off, the
+// exclusive prefix sum of the per-environment active counts (n_env + 1 entries), and (b) idx,
+// the bullet rows of the slice that are active, in order.  The key/value projection then runs
+// over idx only and the attention kernel stages rows [env_off[e], env_off[e+1]).
+
+// one warp per environment: cnt[e] = number of active slots
+__global__ void __launch_bounds__(256) k_bullet_count(const uint8_t* __restrict__ active, int n_env, int nb, int* __restrict__ cnt) {
+  const int lane = threadIdx.x & 31;
+  for (int e = blockIdx.x * 8 + (threadIdx.x >> 5); e < n_env; e += gridDim.x * 8) {
+    int c = 0;
+    for (int j0 = 0; j0 < nb; j0 += 32) {
+      const int j = j0 + lane;
+      const bool a = j < nb && active[(size_t)e * nb + j];
+      c += __popc(__ballot_sync(0xffffffffu, a));
+    }
+    if (lane == 0) cnt[e] = c;
+  }
+}
+// one CTA: env_off = exclusive scan of cnt, in place (env_off[n_env] = total)
+__global__ void __launch_bounds__(1024) k_bullet_scan(int* __restrict__ env_off, int n_env) {
+  __shared__ int warp_sum[32];
+  __shared__ int carry;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  for (int base = 0; base < n_env; base += 1024) {
+    const int i = base + threadIdx.x;
+    const int v = i < n_env ? env_off[i] : 0;
+    int inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int u = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += u;
+    }
+    if (lane == 31) warp_sum[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+      int w = warp_sum[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += u;
+      }
+      warp_sum[lane] = w;
+    }
+    __syncthreads();
+    const int before = carry + (warp ? warp_sum[warp - 1] : 0) + inc - v;
+    if (i < n_env) env_off[i] = before;
+    __syncthreads();
+    if (threadIdx.x == 1023) carry = before + v;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) env_off[n_env] = carry;
+}
+// one warp per environment: the active slots of environment e, in order, at idx[env_off[e]...]
+__global__ void __launch_bounds__(256) k_bullet_fill(const uint8_t* __restrict__ active, int n_env, int nb,
+                                                     const int* __restrict__ env_off, int* __restrict__ idx) {
+  const int lane = threadIdx.x & 31;
+  for (int e = blockIdx.x * 8 + (threadIdx.x >> 5); e < n_env; e += gridDim.x * 8) {
+    int off = env_off[e];
+    for (int j0 = 0; j0 < nb; j0 += 32) {
+      const int j = j0 + lane;
+      const bool a = j < nb && active[(size_t)e * nb + j];
+      const uint32_t m = __ballot_sync(0xffffffffu, a);
+      if (a) idx[off + __popc(m & ((1u << lane) - 1u))] = e * nb + j;
+      off += __popc(m);
     }
   }
 }
@@ -1554,12 +1696,16 @@ int plan_tiles(const int32_t* tok_off, int n_envs, int32_t* tile_env_begin, int3
 
 static size_t round256(size_t v) { return (v + 255) / 256 * 256; }
 // Shared memory of the attention kernel for environments of up to max_tokens tokens and nb bullets.
-static size_t flash_smem(int max_tokens, int nb) {
-  return (size_t)(3 * max_tokens + 2 * nb) * FLASH_STRIDE + (size_t)max_tokens + (size_t)nb + 16;
+static size_t flash_smem(int max_tokens, int nb, int hpc) {
+  return (size_t)(3 * max_tokens + 2 * nb) * flash_stride(hpc) + (size_t)max_tokens + (size_t)nb + 16;
 }
 constexpr size_t FLASH_SMEM_MAX = 227 * 1024;
+// All four heads in one CTA while that leaves room for three CTAs per SM, else one head per CTA.
+static int flash_heads_per_cta(int max_tokens, int nb) {
+  return flash_smem(max_tokens, nb, HEADS) <= 72 * 1024 ? HEADS : 1;
+}
 bool supported_bullets(const BnbBatch& b, int bullets_per_env) {
-  return bullets_per_env >= 1 && flash_smem(b.max_tokens_per_env, bullets_per_env) <= FLASH_SMEM_MAX;
+  return bullets_per_env >= 1 && flash_smem(b.max_tokens_per_env, bullets_per_env, 1) <= FLASH_SMEM_MAX;
 }
 
 // Layout: status area | q|k|v and attention output of every row (split path: environments larger
@@ -1569,6 +1715,11 @@ size_t scratch_bytes(int, const BnbBatch& b, int T, int bullets_per_env) {
   if (!fits_tile(b) || bullets_per_env > 0)
     bytes += round256((size_t)T * b.total_tokens * 4 * D * sizeof(__nv_bfloat16));
   bytes += round256(bullet_slice_bytes((long long)T * b.n_envs, bullets_per_env, D, sizeof(__nv_bfloat16)));
+  if (bullets_per_env > 0) {
+    // env_off (slice environments + 1) and idx (one int per bullet row of a slice)
+    const size_t envs = (size_t)bullet_slice_envs((long long)T * b.n_envs, bullets_per_env, D, sizeof(__nv_bfloat16));
+    bytes += round256((envs + 1) * sizeof(int)) + round256(envs * bullets_per_env * sizeof(int));
+  }
   return bytes;
 }
 size_t packed_spatial_bytes(int d_model) { return d_model == D ? (size_t)N_SPATIAL_IMAGE * CHUNK_BYTES : 0; }
@@ -1657,7 +1808,7 @@ static void fill_temporal(SubLayer& s, const BnbTemporalWeights& w, const float*
 // Attention of the environments [env_base, env_base + n_env) (group-major), with the bullet keys
 // of the same environments in kvb when nb > 0.
 static int launch_attention(const __nv_bfloat16* qkv, const uint8_t* alive, __nv_bfloat16* o, const BnbBatch& b,
-                            int env_base, int n_env, const __nv_bfloat16* kvb, const uint8_t* bullet_active, int nb,
+                            int env_base, int n_env, const __nv_bfloat16* kvb, const int* env_off, int nb,
                             cudaStream_t st) {
   static bool configured[64] = {};
   int dev = 0;
@@ -1668,20 +1819,37 @@ static int launch_attention(const __nv_bfloat16* qkv, const uint8_t* alive, __nv
     configured[dev] = true;
   }
   if (n_env <= 0) return BNB_OK;
-  const size_t smem = flash_smem(b.max_tokens_per_env, kvb ? nb : 0);
+  const int hpc = flash_heads_per_cta(b.max_tokens_per_env, kvb ? nb : 0);
+  const size_t smem = flash_smem(b.max_tokens_per_env, kvb ? nb : 0, hpc);
   if (smem > FLASH_SMEM_MAX) return BNB_ERR_TOO_MANY_TOKENS;
-  dim3 grid(n_env, HEADS);
+  dim3 grid(n_env, HEADS / hpc);
   count_launch();
-  k_attention_flash<<<grid, 128, smem, st>>>(qkv, alive, o, make_env_map(b), env_base, kvb, bullet_active, nb);
+  k_attention_flash<<<grid, 128, smem, st>>>(qkv, alive, o, make_env_map(b), env_base, hpc, kvb, env_off, nb);
   return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
 }
 
-// norm_bullet + kv_bullet of `rows` bullet rows (a slice of whole environments) into kvb.
-static int launch_bullet_kv(const BnbSpatialWeights& w, const float* bullet_rows, int rows, __nv_bfloat16* kvb,
-                            int* status, cudaStream_t st) {
+// env_off / idx of the active bullets of n_env environments (see the compaction kernels).
+static int launch_compact(const uint8_t* active, int n_env, int nb, int* env_off, int* idx, cudaStream_t st) {
+  if (n_env <= 0) return BNB_OK;
+  const int blocks = (n_env + 7) / 8 < 148 * 8 ? (n_env + 7) / 8 : 148 * 8;
+  count_launch();
+  k_bullet_count<<<blocks, 256, 0, st>>>(active, n_env, nb, env_off);
+  count_launch();
+  k_bullet_scan<<<1, 1024, 0, st>>>(env_off, n_env);
+  count_launch();
+  k_bullet_fill<<<blocks, 256, 0, st>>>(active, n_env, nb, env_off, idx);
+  return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
+}
+
+// norm_bullet + kv_bullet of bullet rows (a slice of whole environments) into kvb: all `rows`
+// rows in order, or, with idx / n_rows_dev, the first *n_rows_dev rows of idx.
+static int launch_bullet_kv(const BnbSpatialWeights& w, const float* bullet_rows, int rows, const int* idx,
+                            const int* n_rows_dev, __nv_bfloat16* kvb, int* status, cudaStream_t st) {
   if (rows <= 0) return BNB_OK;
   TrunkArgs a{};
   a.x = bullet_rows;
+  a.row_index = idx;
+  a.n_rows_dev = n_rows_dev;
   a.y = nullptr;              // nothing but the keys and values leaves this program
   a.status = status;
   a.n_groups = 1;
@@ -1720,6 +1888,9 @@ struct Plan {
   __nv_bfloat16* o;
   __nv_bfloat16* kvb;    // bullet keys and values of one slice
   int kvb_envs;          // environments per slice
+  int* env_off;          // compaction of the slice's active bullets (see launch_compact)
+  int* idx;
+  int compacted_e0;      // first environment of the slice env_off / idx currently describe, -1 = none
   int n_groups, t_loop;  // geometry of the pending program
   TrunkArgs a;
   int n;
@@ -1773,8 +1944,16 @@ struct Plan {
       const int nb = bullets->per_env;
       for (int e0 = 0; e0 < total_envs; e0 += kvb_envs) {
         const int ne = total_envs - e0 < kvb_envs ? total_envs - e0 : kvb_envs;
-        if ((rc = launch_bullet_kv(w, bullets->tokens + (size_t)e0 * nb * D, ne * nb, kvb, status, st))) return rc;
-        if ((rc = launch_attention(qkv, alive, o, b, e0, ne, kvb, bullets->active, nb, st))) return rc;
+        const bool masked = bullets->active != nullptr;
+        if (masked && compacted_e0 != e0) {
+          // the mask is the same for every reading sublayer of the call: one slice -> compact once
+          if ((rc = launch_compact(bullets->active + (size_t)e0 * nb, ne, nb, env_off, idx, st))) return rc;
+          compacted_e0 = e0;
+        }
+        if ((rc = launch_bullet_kv(w, bullets->tokens + (size_t)e0 * nb * D, ne * nb, masked ? idx : nullptr,
+                                   masked ? env_off + ne : nullptr, kvb, status, st)))
+          return rc;
+        if ((rc = launch_attention(qkv, alive, o, b, e0, ne, kvb, masked ? env_off : nullptr, nb, st))) return rc;
       }
     } else if ((rc = launch_attention(qkv, alive, o, b, 0, total_envs, nullptr, nullptr, 0, st))) {
       return rc;
@@ -1814,9 +1993,16 @@ static int make_plan(Plan& p, void* scratch, size_t scratch_bytes, int T) {
     p.o = p.qkv + rows * 3 * D;
     base += round256(rows * 4 * D * sizeof(__nv_bfloat16));
   }
+  p.env_off = nullptr;
+  p.idx = nullptr;
+  p.compacted_e0 = -1;
   if (nb > 0) {
     p.kvb = reinterpret_cast<__nv_bfloat16*>(base);
     p.kvb_envs = bullet_slice_envs((long long)T * p.b.n_envs, nb, D, sizeof(__nv_bfloat16));
+    base += round256(bullet_slice_bytes((long long)T * p.b.n_envs, nb, D, sizeof(__nv_bfloat16)));
+    p.env_off = reinterpret_cast<int*>(base);
+    base += round256(((size_t)p.kvb_envs + 1) * sizeof(int));
+    p.idx = reinterpret_cast<int*>(base);
   }
   p.begin(1, 1);
   return BNB_OK;

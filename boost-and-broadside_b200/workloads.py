@@ -8,6 +8,9 @@ the GPU kernels see identical bits; callers move the tensors where they need the
     C3  trunk step, 1024 envs x 152 ships (64 v 88), casualty fraction U(0, 0.7) per env
     C4  trunk sequence, T=32 x 4096 envs x 8 ships, done ~ Bernoulli(0.02)
     C5  trunk step, 16384 ragged envs, tokens U{2..128}, 0-4 fields, sharded by rank
+    C2B C2 with the 80 bullet slots per environment (8 ships x 10) that the first spatial
+        sublayer of each block cross-attends to; slots active ~ Bernoulli(0.3), a quarter of
+        the environments with nothing in flight
 """
 
 from __future__ import annotations
@@ -71,6 +74,8 @@ class Workload:
     done: torch.Tensor | None = None
     n_tokens: torch.Tensor | None = None  # ragged only
     n_ships: torch.Tensor | None = None
+    bullets: torch.Tensor | None = None      # (envs, NB, D) encoded bullet tokens
+    bullet_mask: torch.Tensor | None = None  # (envs, NB) bool active slots
     meta: dict = field(default_factory=dict)
 
     @property
@@ -94,6 +99,18 @@ def c2(n_envs: int = 8192, seed: int = 2, ships: int = 8, fields: int = 4) -> Wo
     alive = team_alive(gen, n_envs, ships, fields)
     hidden = torch.randn(2, n_envs * ships, 512, generator=gen) * 0.5
     return Workload("C2", "step", "bf16", x, alive, hidden, meta=dict(n_envs=n_envs, ships=ships, fields=fields))
+
+
+def c2b(n_envs: int = 8192, seed: int = 6, bullets_per_env: int = 80) -> Workload:
+    """C2 plus encoded bullet tokens (the bullet encoder ends in an RMSNorm, so N(0, 1) values)."""
+    w = c2(n_envs=n_envs, seed=seed)
+    gen = torch.Generator().manual_seed(seed + 1000)
+    w.name = "C2B"
+    w.bullets = torch.randn(n_envs, bullets_per_env, 128, generator=gen)
+    w.bullet_mask = torch.rand(n_envs, bullets_per_env, generator=gen) < 0.3
+    w.bullet_mask[torch.rand(n_envs, generator=gen) < 0.25] = False
+    w.meta["bullets"] = bullets_per_env
+    return w
 
 
 def c3(n_envs: int = 1024, seed: int = 3, teams: tuple[int, int] = (64, 88)) -> Workload:
@@ -152,9 +169,11 @@ def c5(n_envs: int = 16384, seed: int = 5, max_tokens: int = 128) -> Workload:
 def algorithmic_bytes(w: Workload, n_params: int, n_hidden_layers: int = 2, d_model: int = 128) -> int:
     """Compulsory HBM bytes of one pass: x in + x out in float32, hidden in + out once per
     call, one byte per token of mask (+ one per (t, env) done flag), weights once at
-    2 B/param (bf16) or 4 B/param (fp32)."""
+    2 B/param (bf16) or 4 B/param (fp32); bullet tokens and their mask once."""
     tokens = w.entity_tokens
     b = 2 * 4 * d_model * tokens + tokens
+    if w.bullets is not None:
+        b += w.bullets.numel() * 4 + w.bullet_mask.numel()
     if w.hidden is not None:
         b += 2 * w.hidden.numel() * 4
     if w.done is not None:
@@ -181,4 +200,10 @@ def algorithmic_flops(w: Workload, cfg: ModelConfig) -> int:
     envs, ships, fields = w.meta["n_envs"], w.meta["ships"], w.meta["fields"]
     keys = ships + fields
     tok = T * envs * keys
-    return int(ns * tok * (2 * 16 * D * D + 4 * D * keys) + nt * T * envs * 2 * D * D * (17 * ships + 16 * fields))
+    total = ns * tok * (2 * 16 * D * D + 4 * D * keys) + nt * T * envs * 2 * D * D * (17 * ships + 16 * fields)
+    if w.bullets is not None:
+        # per reading sublayer: kv_bullet (2 D^2 MACs per bullet) and one more softmax over NB keys
+        nb = w.bullets.shape[1]
+        n_read = cfg.n_yemong_blocks * cfg.n_bullet_cross_per_block
+        total += n_read * (T * envs * nb * 2 * 2 * D * D + tok * 4 * D * nb)
+    return int(total)

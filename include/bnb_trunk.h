@@ -161,7 +161,7 @@ int bnb_plan_tiles(const int32_t* tok_off_host, int n_envs, int32_t* tile_env_be
 /* Bytes of scratch a call with this geometry may use (upper bound over all entry points).
  * `timesteps` is 1 for a step; `bullets_per_env` is 0 for calls without bullets.  The bullet
  * keys and values are projected in slices of environments, so their share of the scratch is
- * capped (256 MiB) whatever the batch. */
+ * capped (512 MiB) whatever the batch. */
 size_t bnb_scratch_bytes(int d_model, const BnbBatch* batch, int timesteps, int bullets_per_env);
 
 /* y = TransformerBlock.forward(x, alive_mask, bullets, bullet_mask)

@@ -287,7 +287,7 @@ def test_sequence_with_bullets_tensor_vs_oracle():
 
 
 def test_bullets_full_size_step_is_sliced_and_engines_agree():
-    """The rollout-step configuration with its 80 bullet slots per environment: 8192 x 80 bullet
+    """The rollout-step configuration with 160 bullet slots per environment: 8192 x 160 bullet
     rows exceed one slice of the key/value scratch on both engines, so the projection and the
     attention run slice by slice; tensor and SIMT engines must agree and every environment
     without an active bullet must equal the bullet-free result."""
@@ -297,10 +297,12 @@ def test_bullets_full_size_step_is_sliced_and_engines_agree():
     w = W.c2(seed=31)
     n_envs = w.x.shape[0]
     batch = _capi.uniform_batch(n_envs, w.x.shape[1], 8)
-    assert _capi.lib.bnb_scratch_bytes(128, batch, 1, 80) < n_envs * 80 * 256 * 4  # smaller than all keys/values in fp32
+    nb = 160
+    share = _capi.lib.bnb_scratch_bytes(128, batch, 1, nb) - _capi.lib.bnb_scratch_bytes(128, batch, 1, 0)
+    assert share < n_envs * nb * 256 * 2  # less than all keys and values, even in bf16: more than one slice
     gen = torch.Generator().manual_seed(7)
-    bul = torch.randn(n_envs, 80, 128, generator=gen)
-    mask = torch.rand(n_envs, 80, generator=gen) < 0.3
+    bul = torch.randn(n_envs, nb, 128, generator=gen)
+    mask = torch.rand(n_envs, nb, generator=gen) < 0.3
     idle = torch.rand(n_envs, generator=gen) < 0.25
     mask[idle] = False
     trunk = build_trunk([128, 4, 2, 2, 1, 1]).to(DEV)
