@@ -443,3 +443,49 @@ def test_block_step_with_bullets_vs_oracle(mode):
     assert_close(y, ry, mode, "block step y")
     assert_close(nh, rh, mode, "block step h")
     assert_close(nc, rc, mode, "block step conv")
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_step_matches_sequence_with_bullets(mode):
+    """tests/models/test_encoder.py:782-814 of the reference, at the trunk: one sequence forward
+    with per-step bullets equals stepping with reset_hidden_for_envs after finished steps; the
+    bullets add no recurrent state (770-780)."""
+    g = golden("bullets_trunk_seq_d128_t4_4s2f")
+    trunk = build_trunk(g["dims"], g).to(DEV)
+    x, alive, hidden, done = _to(g["x"]), _to(g["alive"]), _to(g["hidden"]), _to(g["done"])
+    T, B = x.shape[0], x.shape[1]
+    NB = g["bullets"].shape[1]
+    bul = _to(g["bullets"]).reshape(T, B, NB, -1)
+    bm = _to(g["bullet_mask"]).reshape(T, B, NB)
+    with torch.no_grad(), autocast_for(mode, DEV):
+        y_seq, h_seq = trunk.sequence(x, alive, hidden, done, bullets=bul.reshape(T * B, NB, -1),
+                                      bullet_mask=bm.reshape(T * B, NB))
+        h = hidden
+        ys = []
+        for t in range(T):
+            y, h = trunk.step(x[t], alive[t], h, bullets=bul[t], bullet_mask=bm[t])
+            assert h.shape == hidden.shape
+            ys.append(y)
+            h = trunk.reset_hidden_for_envs(h, done[t], x.shape[2] - 2)
+    assert_close(torch.stack(ys), y_seq, mode, "steps vs sequence with bullets", scale=1.0 if mode == "fp32" else 1.0)
+    assert_close(y_seq, g["y_" + mode], mode, "sequence vs reference")
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("ships,fields,nb", [(2, 0, 4), (16, 3, 160), (8, 4, 1)])
+def test_bullets_at_unseen_fleet_sizes(mode, ships, fields, nb):
+    """tests/models/test_encoder.py:886-906: the same weights at other fleet and ring sizes."""
+    from boost_and_broadside_b200 import workloads as W
+
+    trunk = build_trunk([128, 4, 2, 2, 1, 1])
+    P = trunk_params(trunk)
+    w = W.c2(n_envs=9, seed=41, ships=ships, fields=fields)
+    gen = torch.Generator().manual_seed(43)
+    bul = torch.randn(9, nb, 128, generator=gen)
+    bm = torch.rand(9, nb, generator=gen) < 0.5
+    ref_y, ref_h = O.trunk_step(w.x, w.alive, w.hidden, P, 4, mode, bul, bm)
+    trunk = trunk.to(DEV)
+    with torch.no_grad(), autocast_for(mode, DEV):
+        y, nh = trunk.step(_to(w.x), _to(w.alive), _to(w.hidden), bullets=_to(bul), bullet_mask=_to(bm))
+    assert_close(y, ref_y, mode, "y")
+    assert_close(nh, ref_h, mode, "hidden")
