@@ -174,6 +174,29 @@ def stream_handle(device: torch.device) -> int:
 
 
 _scratch: dict[tuple[int, int], torch.Tensor] = {}
+_alloc_worker = None
+
+
+def persistent_bytes(device: torch.device, nbytes: int) -> torch.Tensor:
+    """A byte buffer that outlives the call that creates it (scratch, weight images).
+
+    It is allocated on a helper thread: torch.compile's CUDA-graph trees route every allocation
+    made by the *calling* thread, during warm-up as well as capture, into the graph's private
+    pool and insist that nothing in that pool survives the call; allocations of other threads
+    stay in the ordinary pool.  The buffers are only ever used by work enqueued after their
+    creation, and they are created before the first capture (the warm-up call needs them).
+    """
+    global _alloc_worker
+    if _alloc_worker is None:
+        import concurrent.futures
+
+        _alloc_worker = concurrent.futures.ThreadPoolExecutor(max_workers=1, thread_name_prefix="bnb-alloc")
+
+    def make() -> torch.Tensor:
+        with torch.cuda.device(device):
+            return torch.empty(nbytes, dtype=torch.uint8, device=device)
+
+    return _alloc_worker.submit(make).result()
 
 
 def scratch_for(device: torch.device, nbytes: int) -> torch.Tensor:
@@ -181,7 +204,7 @@ def scratch_for(device: torch.device, nbytes: int) -> torch.Tensor:
     key = (device.index if device.index is not None else torch.cuda.current_device(), stream_handle(device))
     buf = _scratch.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        buf = persistent_bytes(device, max(nbytes, 1 << 20))
         _scratch[key] = buf
     return buf
 

@@ -1,0 +1,162 @@
+"""Opaque ``torch.library`` operators around the C ABI.
+
+``torch.compile(policy)`` (the reference trains and evaluates through it,
+train/rl/ppo.py:396-400) must neither trace into ctypes nor break CUDA-graph capture, so the
+calls into the library are registered as custom operators: Dynamo sees one opaque node with a
+shape-only fake implementation; the real implementation below builds the ctypes argument
+structs, looks up (or rebuilds) the tensor-core weight images, takes scratch from torch's
+allocator and launches on the current stream.  Nothing here synchronises.
+
+The operators are forward-only: no autograd formula is registered, and the module methods
+refuse inputs that require grad.
+"""
+
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+from torch import Tensor
+
+from .. import _capi
+from ._weights import N_SPATIAL, N_TEMPORAL, packed_image, spatial_struct_from, temporal_struct_from
+
+# geom: the integers of a call, in this order
+(G_BLOCKS, G_SPATIAL, G_TEMPORAL, G_HEADS, G_BULLET_CROSS, G_FIELD_SUB, G_ENVS, G_TOKENS_PER_ENV, G_SHIPS_PER_ENV,
+ G_MAX_TOKENS, G_TOTAL_TOKENS, G_TOTAL_SHIPS, G_TILES, G_TIMESTEPS, G_ENGINE, G_PRECISION) = range(16)
+
+
+def uniform_geom(n_envs: int, tokens: int, ships: int) -> List[int]:
+    """Batch part of ``geom`` for environments of one size (entries G_ENVS .. G_TILES)."""
+    return [n_envs, tokens, ships, tokens, n_envs * tokens, n_envs * ships, 0]
+
+
+def _batch(geom: List[int], offsets: List[Tensor]) -> "_capi.Batch":
+    if offsets:
+        tok, ship = offsets[0], offsets[1]
+        tiles = offsets[2] if len(offsets) > 2 else None
+        ids = offsets[3] if len(offsets) > 3 else None
+        return _capi.Batch(geom[G_ENVS], 0, 0, geom[G_MAX_TOKENS], geom[G_TOTAL_TOKENS], geom[G_TOTAL_SHIPS],
+                           tok.data_ptr(), ship.data_ptr(), _capi.ptr(tiles), _capi.ptr(ids), geom[G_TILES])
+    return _capi.Batch(geom[G_ENVS], geom[G_TOKENS_PER_ENV], geom[G_SHIPS_PER_ENV], geom[G_MAX_TOKENS],
+                       geom[G_TOTAL_TOKENS], geom[G_TOTAL_SHIPS], None, None, None, None, 0)
+
+
+@torch.library.custom_op("bnb_b200::trunk_forward", mutates_args=(), device_types="cuda")
+def trunk_forward(
+    x: Tensor,
+    alive: Optional[Tensor],
+    hidden: Tensor,
+    done: Optional[Tensor],
+    reset_env: Optional[Tensor],
+    bullets: Optional[Tensor],
+    bullet_mask: Optional[Tensor],
+    weights: List[Tensor],
+    offsets: List[Tensor],
+    geom: List[int],
+) -> Tuple[Tensor, Tensor]:
+    """Blocks of (spatial sublayers, temporal sublayers) over x: ``bnb_trunk_step`` when
+    geom[G_TIMESTEPS] is 0, else ``bnb_trunk_sequence`` over that many timesteps.
+
+    x (total_tokens, D) or (T, total_tokens, D); hidden (L, total_ships, 4D) packed;
+    ``weights`` the parameters of every sublayer, block-major, spatial before temporal inside a
+    block, each sublayer in the order of ``_weights.spatial_tensors`` / ``temporal_tensors``;
+    ``offsets`` empty for environments of one size, else [tok_off, ship_off(, tile_env_begin,
+    tile_env_ids)].  Returns (y like x, new hidden like hidden), both float32.
+    """
+    dev = x.device
+    D = x.shape[-1]
+    n_blocks, n_spatial, n_temporal = geom[G_BLOCKS], geom[G_SPATIAL], geom[G_TEMPORAL]
+    n_heads, n_cross, field_sub = geom[G_HEADS], geom[G_BULLET_CROSS], geom[G_FIELD_SUB]
+    engine, precision = geom[G_ENGINE], geom[G_PRECISION]
+    T = max(1, geom[G_TIMESTEPS])
+    with torch.cuda.device(dev):
+        batch = _batch(geom, offsets)
+        xin = _capi.f32c(x)
+        hin = _capi.f32c(hidden)
+        alive_u8 = _capi.u8(alive)
+        done_u8 = _capi.u8(done)
+        reset_u8 = _capi.u8(reset_env)
+        y = torch.empty_like(xin)
+        hout = torch.empty_like(hin)
+        sw = (_capi.SpatialWeights * max(1, n_blocks * n_spatial))()
+        tw = (_capi.TemporalWeights * max(1, n_blocks * n_temporal))()
+        pos = 0
+        for i in range(n_blocks):
+            for j in range(n_spatial):
+                n = N_SPATIAL + (2 if j < n_cross else 0)
+                ts = list(weights[pos : pos + n])
+                pos += n
+                sw[i * n_spatial + j] = spatial_struct_from(
+                    ts, dev, packed_image("spatial", ts, n_heads, dev, precision, engine))
+            for j in range(n_temporal):
+                n = N_TEMPORAL + (1 if field_sub else 0)
+                ts = list(weights[pos : pos + n])
+                pos += n
+                tw[i * n_temporal + j] = temporal_struct_from(
+                    ts, dev, packed_image("temporal", ts, 4, dev, precision, engine))
+        if pos != len(weights):
+            raise RuntimeError(f"expected {pos} parameter tensors for this trunk structure, got {len(weights)}")
+        bul = _capi.BulletArgs(bullets if n_cross > 0 else None, bullet_mask, T * batch.n_envs, D)
+        nbytes = _capi.lib.bnb_scratch_bytes(D, batch, T, bul.per_env)
+        scratch = _capi.scratch_for(dev, nbytes)
+        stream = _capi.stream_handle(dev)
+        if geom[G_TIMESTEPS] == 0:
+            fn = "bnb_trunk_step"
+            st = _capi.lib.bnb_trunk_step(
+                sw, tw, n_blocks, n_spatial, n_temporal, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8), bul.arg,
+                y.data_ptr(), _capi.ptr(hin), _capi.ptr(hout), _capi.ptr(reset_u8), batch, precision, engine,
+                scratch.data_ptr(), scratch.numel(), stream,
+            )
+        else:
+            fn = "bnb_trunk_sequence"
+            st = _capi.lib.bnb_trunk_sequence(
+                sw, tw, n_blocks, n_spatial, n_temporal, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8), bul.arg,
+                y.data_ptr(), _capi.ptr(hin), _capi.ptr(hout), _capi.ptr(done_u8), batch, T, precision, engine,
+                scratch.data_ptr(), scratch.numel(), stream,
+            )
+    _capi.check(fn, st)
+    return y, hout
+
+
+@trunk_forward.register_fake
+def _trunk_forward_fake(x, alive, hidden, done, reset_env, bullets, bullet_mask, weights, offsets, geom):
+    return (x.new_empty(x.shape, dtype=torch.float32), hidden.new_empty(hidden.shape, dtype=torch.float32))
+
+
+@torch.library.custom_op("bnb_b200::spatial_forward", mutates_args=(), device_types="cuda")
+def spatial_forward(
+    x: Tensor,
+    alive: Optional[Tensor],
+    bullets: Optional[Tensor],
+    bullet_mask: Optional[Tensor],
+    weights: List[Tensor],
+    n_heads: int,
+    precision: int,
+    engine: int,
+) -> Tensor:
+    """One spatial sublayer, ``bnb_spatial_block_fwd``: x (B, N, D), alive (B, N) or None,
+    bullets (B, NB, D) / bullet_mask (B, NB) or None; returns float32 (B, N, D)."""
+    dev = x.device
+    B, N, D = x.shape
+    ts = list(weights)
+    with torch.cuda.device(dev):
+        xin = _capi.f32c(x)
+        alive_u8 = _capi.u8(alive)
+        y = torch.empty_like(xin)
+        batch = _capi.uniform_batch(B, N, N)
+        bul = _capi.BulletArgs(bullets if len(ts) > N_SPATIAL else None, bullet_mask, B, D)
+        nbytes = _capi.lib.bnb_scratch_bytes(D, batch, 1, bul.per_env)
+        scratch = _capi.scratch_for(dev, nbytes)
+        w = spatial_struct_from(ts, dev, packed_image("spatial", ts, n_heads, dev, precision, engine))
+        st = _capi.lib.bnb_spatial_block_fwd(
+            w, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8), bul.arg, y.data_ptr(), batch, 1, precision, engine,
+            scratch.data_ptr(), scratch.numel(), _capi.stream_handle(dev),
+        )
+    _capi.check("bnb_spatial_block_fwd", st)
+    return y
+
+
+@spatial_forward.register_fake
+def _spatial_forward_fake(x, alive, bullets, bullet_mask, weights, n_heads, precision, engine):
+    return x.new_empty(x.shape, dtype=torch.float32)

@@ -3,7 +3,8 @@
 ``GatedMLP`` and ``TransformerBlock`` keep the reference's constructor arguments,
 parameter names, shapes and float32 dtype (attention.py:21-74), so a reference
 ``state_dict`` loads unchanged.  ``TransformerBlock.forward`` has the reference signature
-(attention.py:76-82) and runs ``bnb_spatial_block_fwd`` of the CUDA library.
+(attention.py:76-82) and runs ``bnb_spatial_block_fwd`` of the CUDA library through the opaque
+``bnb_b200::spatial_forward`` operator.
 """
 
 from __future__ import annotations
@@ -12,7 +13,8 @@ import torch
 import torch.nn as nn
 
 from .. import _capi
-from ._weights import packed_image, spatial_struct
+from . import _ops
+from ._weights import spatial_tensors
 
 
 class GatedMLP(nn.Module):
@@ -78,24 +80,7 @@ class TransformerBlock(nn.Module):
         B, N, D = x.shape
         if alive_mask is not None and tuple(alive_mask.shape) != (B, N):
             raise RuntimeError(f"alive_mask must have shape {(B, N)}, got {tuple(alive_mask.shape)}")
-        dev = x.device
-        precision = _capi.current_precision(dev)
-        with torch.cuda.device(dev):
-            xin = _capi.f32c(x)
-            alive = _capi.u8(alive_mask)
-            y = torch.empty_like(xin)
-            batch = _capi.uniform_batch(B, N, N)
-            bul = _capi.BulletArgs(bullets if self.reads_bullets else None, bullet_mask, B, D)
-            nbytes = _capi.lib.bnb_scratch_bytes(D, batch, 1, bul.per_env)
-            scratch = _capi.scratch_for(dev, nbytes)
-            params = [self.qkv.weight, self.out_proj.weight, self.ffn.gate_proj.weight, self.ffn.up_proj.weight,
-                      self.ffn.down_proj.weight] + ([self.kv_bullet.weight] if self.reads_bullets else [])
-            packed = packed_image(self, "spatial", 0, params, lambda: spatial_struct(self, dev), self.n_heads, dev,
-                                  precision, _capi.ENGINE_AUTO)
-            w = spatial_struct(self, dev, packed)
-            st = _capi.lib.bnb_spatial_block_fwd(
-                w, D, self.n_heads, xin.data_ptr(), _capi.ptr(alive), bul.arg, y.data_ptr(), batch, 1, precision,
-                _capi.ENGINE_AUTO, scratch.data_ptr(), scratch.numel(), _capi.stream_handle(dev),
-            )
-        _capi.check("bnb_spatial_block_fwd", st)
-        return y
+        return _ops.spatial_forward(
+            x, alive_mask, bullets if self.reads_bullets else None, bullet_mask if self.reads_bullets else None,
+            spatial_tensors(self), self.n_heads, _capi.current_precision(x.device), _capi.ENGINE_AUTO,
+        )

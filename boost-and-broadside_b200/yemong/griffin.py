@@ -12,7 +12,8 @@ import torch
 import torch.nn as nn
 
 from .. import _capi
-from ._weights import packed_image, spatial_struct, temporal_struct
+from . import _ops
+from ._weights import packed_image, spatial_tensors, temporal_struct, temporal_tensors
 from .attention import GatedMLP, TransformerBlock
 
 CONV_KERNEL: int = 4  # causal depthwise conv kernel size (griffin.py:22)
@@ -62,11 +63,7 @@ class GriffinTemporalBlock(nn.Module):
         self.gated_mlp = GatedMLP(d_model)
 
     def _packed_ptr(self, sub, dev: torch.device, precision: int):
-        params = [self.linear1.weight, self.linear2.weight, self.rg_lru.linear_a.weight, self.rg_lru.linear_x.weight,
-                  self.linear_out.weight, self.gated_mlp.gate_proj.weight, self.gated_mlp.up_proj.weight,
-                  self.gated_mlp.down_proj.weight] + ([] if sub is None else [sub.weight])
-        return packed_image(self, "temporal", "fields" if sub is not None else "ships", params,
-                            lambda: temporal_struct(self, sub, dev), 4, dev, precision, _capi.ENGINE_AUTO)
+        return packed_image("temporal", temporal_tensors(self, sub), 4, dev, precision, _capi.ENGINE_AUTO)
 
     def forward_sequence(
         self,
@@ -138,67 +135,39 @@ def run_trunk(
     hidden: torch.Tensor,
     done: torch.Tensor | None,
     reset_env: torch.Tensor | None,
-    batch: "_capi.Batch",
+    batch_geom: list[int],
     timesteps: int | None,
     engine: int = _capi.ENGINE_AUTO,
-    keepalive: tuple = (),
+    offsets: list[torch.Tensor] | None = None,
     bullets: torch.Tensor | None = None,
     bullet_mask: torch.Tensor | None = None,
 ) -> tuple[torch.Tensor, torch.Tensor]:
     """Run ``blocks`` (YemongBlock modules of one structure) over x.
 
     x is (total_tokens, D) for a step (timesteps None) or (T, total_tokens, D) for a
-    sequence; hidden is (L, total_ships, 4D) packed; bullets (T * n_envs, NB, D) and
-    bullet_mask (T * n_envs, NB) feed the spatial sublayers that read them.
-    Returns (y, new_hidden).
+    sequence; hidden is (L, total_ships, 4D) packed; ``batch_geom`` is the batch part of the
+    operator's integer list (``_ops.uniform_geom`` for environments of one size), ``offsets``
+    the device prefix sums of a ragged batch; bullets (T * n_envs, NB, D) and bullet_mask
+    (T * n_envs, NB) feed the spatial sublayers that read them.  Returns (y, new_hidden).
+
+    Everything below the parameter gathering happens inside the opaque operator
+    ``bnb_b200::trunk_forward``, so ``torch.compile`` records one node for the whole trunk.
     """
-    dev = x.device
-    D = x.shape[-1]
     n_blocks = len(blocks)
     n_spatial = len(blocks[0].spatial) if n_blocks else 0
     n_temporal = len(blocks[0].temporal) if n_blocks else 0
-    precision = _capi.current_precision(dev)
-    has_fields = batch.total_tokens > batch.total_ships
-    with torch.cuda.device(dev):
-        xin = _capi.f32c(x)
-        hin = _capi.f32c(hidden)
-        alive_u8 = _capi.u8(alive)
-        done_u8 = _capi.u8(done)
-        reset_u8 = _capi.u8(reset_env)
-        y = torch.empty_like(xin)
-        hout = torch.empty_like(hin)
-        sw = (_capi.SpatialWeights * max(1, n_blocks * n_spatial))()
-        tw = (_capi.TemporalWeights * max(1, n_blocks * n_temporal))()
-        for i, blk in enumerate(blocks):
-            for j, sp in enumerate(blk.spatial):
-                sw[i * n_spatial + j] = spatial_struct(sp, dev, blk._packed_ptr("spatial", j, dev, precision, engine))
-            for j, tp in enumerate(blk.temporal):
-                tw[i * n_temporal + j] = temporal_struct(
-                    tp, blk.field_sub[j] if has_fields else None, dev,
-                    blk._packed_ptr("temporal", j, dev, precision, engine),
-                )
-        T = 1 if timesteps is None else timesteps
-        reads = any(sp.reads_bullets for blk in blocks for sp in blk.spatial)
-        bul = _capi.BulletArgs(bullets if reads else None, bullet_mask, T * batch.n_envs, D)
-        nbytes = _capi.lib.bnb_scratch_bytes(D, batch, T, bul.per_env)
-        scratch = _capi.scratch_for(dev, nbytes)
-        stream = _capi.stream_handle(dev)
-        if timesteps is None:
-            st = _capi.lib.bnb_trunk_step(
-                sw, tw, n_blocks, n_spatial, n_temporal, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8), bul.arg,
-                y.data_ptr(), _capi.ptr(hin), _capi.ptr(hout), _capi.ptr(reset_u8), batch, precision, engine,
-                scratch.data_ptr(), scratch.numel(), stream,
-            )
-            fn = "bnb_trunk_step"
-        else:
-            st = _capi.lib.bnb_trunk_sequence(
-                sw, tw, n_blocks, n_spatial, n_temporal, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8), bul.arg,
-                y.data_ptr(), _capi.ptr(hin), _capi.ptr(hout), _capi.ptr(done_u8), batch, T, precision, engine,
-                scratch.data_ptr(), scratch.numel(), stream,
-            )
-            fn = "bnb_trunk_sequence"
-    _capi.check(fn, st)
-    return y, hout
+    n_cross = sum(1 for sp in blocks[0].spatial if sp.reads_bullets) if n_blocks else 0
+    has_fields = batch_geom[4] > batch_geom[5]          # total_tokens > total_ships
+    weights: list[torch.Tensor] = []
+    for blk in blocks:
+        for sp in blk.spatial:
+            weights += spatial_tensors(sp)
+        for j, tp in enumerate(blk.temporal):
+            weights += temporal_tensors(tp, blk.field_sub[j] if has_fields else None)
+    geom = [n_blocks, n_spatial, n_temporal, n_heads, n_cross, 1 if has_fields else 0, *batch_geom,
+            0 if timesteps is None else timesteps, engine, _capi.current_precision(x.device)]
+    return _ops.trunk_forward(x, alive, hidden, done, reset_env, bullets if n_cross else None,
+                              bullet_mask if n_cross else None, weights, offsets or [], geom)
 
 
 class YemongBlock(nn.Module):
@@ -231,21 +200,6 @@ class YemongBlock(nn.Module):
         """Hidden-state slots this block consumes."""
         return len(self.temporal)
 
-    # -- tensor-core weight images: derived data, rebuilt when a parameter changes ----------
-    def _packed_ptr(self, kind: str, j: int, dev: torch.device, precision: int, engine: int):
-        if kind == "spatial":
-            mod = self.spatial[j]
-            params = [mod.qkv.weight, mod.out_proj.weight, mod.ffn.gate_proj.weight, mod.ffn.up_proj.weight,
-                      mod.ffn.down_proj.weight] + ([mod.kv_bullet.weight] if mod.reads_bullets else [])
-            return packed_image(self, kind, j, params, lambda: spatial_struct(mod, dev), self.n_heads, dev,
-                                precision, engine)
-        mod = self.temporal[j]
-        sub = self.field_sub[j]
-        params = [mod.linear1.weight, mod.linear2.weight, mod.rg_lru.linear_a.weight, mod.rg_lru.linear_x.weight,
-                  mod.linear_out.weight, mod.gated_mlp.gate_proj.weight, mod.gated_mlp.up_proj.weight,
-                  mod.gated_mlp.down_proj.weight, sub.weight]
-        return packed_image(self, kind, j, params, lambda: temporal_struct(mod, sub, dev), 4, dev, precision, engine)
-
     @staticmethod
     def _pack_state(h: torch.Tensor, conv_buf: torch.Tensor) -> torch.Tensor:
         L, R, D = h.shape
@@ -266,7 +220,7 @@ class YemongBlock(nn.Module):
         _no_grad_inputs(x, h, conv_buf)
         B, NM, D = x.shape
         n_rec = NM if num_recurrent is None else num_recurrent
-        batch = _capi.uniform_batch(B, NM, n_rec)
+        batch = _ops.uniform_geom(B, NM, n_rec)
         hidden = self._pack_state(h, conv_buf)
         y, nh = run_trunk([self], self.n_heads, x.reshape(B * NM, D), None if alive is None else alive.reshape(-1),
                           hidden, None, None, batch, None, bullets=bullets, bullet_mask=bullet_mask)
@@ -291,7 +245,7 @@ class YemongBlock(nn.Module):
         _no_grad_inputs(x, h0, conv_buf0)
         T, B, NM, D = x.shape
         n_rec = NM if num_recurrent is None else num_recurrent
-        batch = _capi.uniform_batch(B, NM, n_rec)
+        batch = _ops.uniform_geom(B, NM, n_rec)
         hidden = self._pack_state(h0, conv_buf0)
         y, nh = run_trunk(
             [self], self.n_heads, x.reshape(T, B * NM, D), None if alive_mask is None else alive_mask.reshape(T, -1),

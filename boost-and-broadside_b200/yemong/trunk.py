@@ -20,6 +20,7 @@ import torch
 import torch.nn as nn
 
 from .. import _capi
+from . import _ops
 from .griffin import CONV_KERNEL, YemongBlock, run_trunk
 
 
@@ -34,7 +35,8 @@ class RaggedBatch:
     n_tokens: torch.Tensor  # (B,) int, host or device
     n_ships: torch.Tensor  # (B,) int
 
-    def build(self, device: torch.device) -> tuple["_capi.Batch", tuple]:
+    def build(self, device: torch.device) -> tuple[list[int], list[torch.Tensor]]:
+        """Batch integers (the ``_ops`` geometry entries) and the device prefix sums / tile plan."""
         nt = self.n_tokens.to("cpu", torch.int64)
         ns = self.n_ships.to("cpu", torch.int64)
         if nt.shape != ns.shape or nt.dim() != 1:
@@ -59,12 +61,10 @@ class RaggedBatch:
             n_tiles = n.value
             tiles_d = plan[: n_tiles + 1].to(device)
             ids_d = ids.to(device)
-        batch = _capi.Batch(
-            B, 0, 0, int(nt.max()) if B else 0, int(tok_off[-1]), int(ship_off[-1]), tok_d.data_ptr(), ship_d.data_ptr(),
-            None if tiles_d is None else tiles_d.data_ptr(), None if ids_d is None else ids_d.data_ptr(), n_tiles,
-        )
+        geom = [B, 0, 0, int(nt.max()) if B else 0, int(tok_off[-1]), int(ship_off[-1]), n_tiles]
         self.tile_fill = float(tok_off[-1]) / (128.0 * n_tiles) if n_tiles else 0.0
-        return batch, (tok_d, ship_d, tiles_d, ids_d)
+        offsets = [tok_d, ship_d] + ([tiles_d, ids_d] if tiles_d is not None else [])
+        return geom, offsets
 
 
 class YemongTrunk(nn.Module):
@@ -129,7 +129,7 @@ class YemongTrunk(nn.Module):
         n_rec = hidden.shape[1] // B if self.n_hidden_layers else NM
         if self.n_hidden_layers and hidden.shape[1] != B * n_rec:
             raise RuntimeError("hidden rows are not a multiple of the environment count")
-        batch = _capi.uniform_batch(B, NM, n_rec)
+        batch = _ops.uniform_geom(B, NM, n_rec)
         y, nh = run_trunk(list(self.yemong_layers), self.n_heads, x.reshape(B * NM, D),
                           None if alive is None else alive.reshape(-1), hidden, None, reset_env, batch, None, engine,
                           bullets=bullets, bullet_mask=bullet_mask)
@@ -149,7 +149,7 @@ class YemongTrunk(nn.Module):
         self._check(x, initial_hidden)
         T, B, NM, D = x.shape
         n_rec = initial_hidden.shape[1] // B if self.n_hidden_layers else NM
-        batch = _capi.uniform_batch(B, NM, n_rec)
+        batch = _ops.uniform_geom(B, NM, n_rec)
         y, nh = run_trunk(list(self.yemong_layers), self.n_heads, x.reshape(T, B * NM, D),
                           None if alive_mask is None else alive_mask.reshape(T, -1), initial_hidden, done_mask, None,
                           batch, T, engine, bullets=bullets, bullet_mask=bullet_mask)
@@ -165,9 +165,9 @@ class YemongTrunk(nn.Module):
     ) -> tuple[torch.Tensor, torch.Tensor]:
         """One step over environments of different sizes (ships first, then fields, per env)."""
         self._check(x, hidden)
-        batch, keep = ragged.build(x.device)
-        if x.shape[0] != batch.total_tokens or hidden.shape[1] != batch.total_ships:
+        batch, offsets = ragged.build(x.device)
+        if x.shape[0] != batch[4] or hidden.shape[1] != batch[5]:
             raise RuntimeError("x / hidden rows do not match the ragged batch")
         y, nh = run_trunk(list(self.yemong_layers), self.n_heads, x, alive, hidden, None, None, batch, None, engine,
-                          keepalive=keep)
+                          offsets=offsets)
         return y, nh

@@ -318,3 +318,41 @@ def test_bullets_full_size_step_is_sliced_and_engines_agree():
     idle_d = idle.to(DEV)
     assert norm_err(yt[idle_d].cpu(), y0[idle_d].cpu()) < 1e-2      # gated off; kernels differ, values agree
     assert norm_err(yt[~idle_d].cpu(), y0[~idle_d].cpu()) > 1e-2    # and the bullets matter elsewhere
+
+
+# ------------------------------------------------------------------ torch.compile
+
+
+@pytest.mark.parametrize("mode", ["default", "reduce-overhead"])
+def test_trunk_step_under_torch_compile(mode):
+    """The reference wraps its policy in torch.compile (train/rl/ppo.py:396-400, CUDA graphs with
+    reduce-overhead).  The trunk is one opaque operator there: no graph break (fullgraph), the
+    same bits as the eager call, and replayable from the compiled CUDA graph."""
+    import torch._dynamo
+
+    from boost_and_broadside_b200 import workloads as W
+
+    torch._dynamo.reset()
+    trunk = build_trunk([128, 4, 2, 2, 1, 1]).to(DEV)
+    w = W.c2b(n_envs=64, seed=51)
+    x, alive, hidden, bul, bm = (t.to(DEV) for t in (w.x, w.alive, w.hidden, w.bullets, w.bullet_mask))
+
+    def step(x, alive, hidden, bul, bm):
+        with torch.autocast(DEV, dtype=torch.bfloat16):
+            y, h = trunk.step(x, alive, hidden, bullets=bul, bullet_mask=bm)
+        return y * 1.0, h          # something for the compiler to fuse around the operator
+
+    compiled = torch.compile(step, fullgraph=True, mode=mode)
+    with torch.no_grad():
+        y0, h0 = step(x, alive, hidden, bul, bm)
+        for _ in range(3):         # warm-up, capture, replay
+            y1, h1 = compiled(x, alive, hidden, bul, bm)
+            y1, h1 = y1.clone(), h1.clone()
+    _status_ok()
+    assert torch.equal(y0, y1) and torch.equal(h0, h1)
+    # a changed input flows through the replay
+    with torch.no_grad():
+        y2, _ = compiled(x + 1.0, alive, hidden, bul, bm)
+        y3, _ = step(x + 1.0, alive, hidden, bul, bm)
+    assert torch.equal(y2.clone(), y3)
+    torch._dynamo.reset()

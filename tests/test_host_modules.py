@@ -78,10 +78,11 @@ def test_ragged_batch_offsets():
     from boost_and_broadside_b200 import RaggedBatch
 
     rb = RaggedBatch(torch.tensor([4, 2, 7]), torch.tensor([2, 2, 6]))
-    batch, keep = rb.build(torch.device("cpu"))
-    assert batch.n_envs == 3 and batch.total_tokens == 13 and batch.total_ships == 10
-    assert batch.max_tokens_per_env == 7
-    assert keep[0].tolist() == [0, 4, 6, 13] and keep[1].tolist() == [0, 2, 4, 10]
+    geom, offsets = rb.build(torch.device("cpu"))
+    n_envs, _, _, max_tokens, total_tokens, total_ships, n_tiles = geom
+    assert n_envs == 3 and total_tokens == 13 and total_ships == 10 and max_tokens == 7
+    assert offsets[0].tolist() == [0, 4, 6, 13] and offsets[1].tolist() == [0, 2, 4, 10]
+    assert n_tiles == 1 and offsets[2].tolist() == [0, 3] and sorted(offsets[3].tolist()) == [0, 1, 2]
     with pytest.raises(RuntimeError):
         RaggedBatch(torch.tensor([2]), torch.tensor([3])).build(torch.device("cpu"))
 
@@ -103,3 +104,21 @@ def test_workload_generators_follow_the_configurations():
     assert int(n.min()) >= 2 and int(n.max()) <= 128 and bool((s >= 2).all()) and bool((s % 2 == 0).all())
     assert bool(((n - s) >= 0).all()) and bool(((n - s) <= 4).all())
     assert w.x.shape[0] == int(n.sum()) and w.hidden.shape[1] == int(s.sum())
+
+
+def test_operators_are_registered_with_shape_only_fakes():
+    """The opaque operators trace without touching a device: torch.compile records one node per
+    trunk call and infers the output shapes from the fake implementations."""
+    import boost_and_broadside_b200  # noqa: F401  (registers the operators)
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    assert hasattr(torch.ops.bnb_b200, "trunk_forward") and hasattr(torch.ops.bnb_b200, "spatial_forward")
+    with FakeTensorMode():
+        x = torch.empty(5, 12, 128, device="cuda")
+        hidden = torch.empty(2, 40, 512, device="cuda")
+        w = [torch.empty(4, device="cuda")]
+        y, h = torch.ops.bnb_b200.trunk_forward(x.reshape(60, 128), None, hidden, None, None, None, None, w, [],
+                                                [0] * 16)
+        assert y.shape == (60, 128) and h.shape == (2, 40, 512) and y.dtype == torch.float32
+        y = torch.ops.bnb_b200.spatial_forward(x, None, None, None, w, 4, 1, 0)
+        assert y.shape == (5, 12, 128)
