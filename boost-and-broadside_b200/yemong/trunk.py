@@ -162,6 +162,8 @@ class YemongTrunk(nn.Module):
         hidden: torch.Tensor,  # (n_layers, sum ships, 4D)
         ragged: RaggedBatch,
         engine: int = _capi.ENGINE_AUTO,
+        bullets: torch.Tensor | None = None,  # (B, NB, D): the same ring size in every environment
+        bullet_mask: torch.Tensor | None = None,  # (B, NB) bool
     ) -> tuple[torch.Tensor, torch.Tensor]:
         """One step over environments of different sizes (ships first, then fields, per env)."""
         self._check(x, hidden)
@@ -169,5 +171,5 @@ class YemongTrunk(nn.Module):
         if x.shape[0] != batch[4] or hidden.shape[1] != batch[5]:
             raise RuntimeError("x / hidden rows do not match the ragged batch")
         y, nh = run_trunk(list(self.yemong_layers), self.n_heads, x, alive, hidden, None, None, batch, None, engine,
-                          offsets=offsets)
+                          offsets=offsets, bullets=bullets, bullet_mask=bullet_mask)
         return y, nh

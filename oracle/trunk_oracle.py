@@ -429,13 +429,15 @@ def trunk_step_ragged(
     blocks: Sequence[Params],
     n_heads: int,
     mode: str,
+    bullets: torch.Tensor | None = None,
+    bullet_mask: torch.Tensor | None = None,
 ) -> tuple[torch.Tensor, torch.Tensor]:
     """Trunk step over environments of different sizes.
 
     The reference expresses one (ships, fields) split per call (griffin.py:398-399),
     so a mixed batch is evaluated by grouping environments of equal shape and calling
     the uniform path once per group.  x_flat (sum tokens, D) env-major, hidden
-    (L, sum ships, 4D) env-major.
+    (L, sum ships, 4D) env-major, bullets (n_envs, NB, D) / bullet_mask (n_envs, NB) optional.
     """
     D = x_flat.shape[-1]
     tok_off = [0]
@@ -454,7 +456,9 @@ def trunk_step_ragged(
         xg = x_flat[tok_idx].reshape(len(envs), nt, D)
         ag = alive_flat[tok_idx].reshape(len(envs), nt)
         hg = hidden[:, ship_idx, :]
-        yg, nhg = trunk_step(xg, ag, hg, blocks, n_heads, mode)
+        bg = None if bullets is None else bullets[envs]
+        mg = None if bullet_mask is None else bullet_mask[envs]
+        yg, nhg = trunk_step(xg, ag, hg, blocks, n_heads, mode, bg, mg)
         y[tok_idx] = yg.reshape(-1, D)
         new_hidden[:, ship_idx, :] = nhg
     return y, new_hidden

@@ -356,3 +356,27 @@ def test_trunk_step_under_torch_compile(mode):
         y3, _ = step(x + 1.0, alive, hidden, bul, bm)
     assert torch.equal(y2.clone(), y3)
     torch._dynamo.reset()
+
+
+@pytest.mark.parametrize("mode", ["fp32", "bf16"])
+def test_ragged_step_with_bullets(mode):
+    """Mixed fleet sizes in one call, every environment with its ring of bullet slots; bf16 runs
+    the tensor engine (tile plan + PRE | attention | POST for the reading sublayers), fp32 the
+    SIMT engine."""
+    from boost_and_broadside_b200 import RaggedBatch
+    from boost_and_broadside_b200 import workloads as W
+
+    w = W.c5(n_envs=57, seed=61)
+    bul, mask = _bullets(57, 24, 8)
+    trunk = build_trunk([128, 4, 2, 2, 1, 1])
+    ref_y, ref_h = O.trunk_step_ragged(w.x, w.alive, w.hidden, w.n_tokens.tolist(), w.n_ships.tolist(),
+                                       trunk_params(trunk), 4, mode, bul, mask)
+    trunk = trunk.to(DEV)
+    ctx = torch.autocast(DEV, dtype=torch.bfloat16) if mode == "bf16" else torch.autocast(DEV, enabled=False)
+    with torch.no_grad(), ctx:
+        y, h = trunk.step_ragged(w.x.to(DEV), w.alive.to(DEV), w.hidden.to(DEV), RaggedBatch(w.n_tokens, w.n_ships),
+                                 bullets=bul.to(DEV), bullet_mask=mask.to(DEV))
+    if mode == "bf16":
+        _status_ok()   # the status word only exists in the tensor engine's scratch layout
+    assert_close(y, ref_y, mode, "ragged y")
+    assert_close(h, ref_h, mode, "ragged hidden")
