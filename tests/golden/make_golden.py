@@ -86,7 +86,7 @@ def weights_as_arrays(sd, prefix="w::"):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference/src")
+    ap.add_argument("--reference", required=True, help="path to the src/ folder of the reference tree")
     ap.add_argument("--only", default="", help="write only the files whose name starts with this prefix")
     args = ap.parse_args()
     global ONLY
