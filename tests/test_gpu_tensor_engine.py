@@ -380,3 +380,24 @@ def test_ragged_step_with_bullets(mode):
         _status_ok()   # the status word only exists in the tensor engine's scratch layout
     assert_close(y, ref_y, mode, "ragged y")
     assert_close(h, ref_h, mode, "ragged hidden")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_second_device_while_the_first_is_current():
+    """Replicas: the trunk follows its tensors' device, whatever the current device is (weight
+    images, scratch and kernel attributes are kept per device)."""
+    from boost_and_broadside_b200 import workloads as W
+
+    w = W.c2b(n_envs=40, seed=71)
+    trunk0 = build_trunk([128, 4, 2, 2, 1, 1]).to("cuda:0")
+    trunk1 = build_trunk([128, 4, 2, 2, 1, 1]).to("cuda:1")
+    outs = []
+    with torch.cuda.device(0), torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        for dev, trunk in (("cuda:0", trunk0), ("cuda:1", trunk1)):
+            y, h = trunk.step(w.x.to(dev), w.alive.to(dev), w.hidden.to(dev), bullets=w.bullets.to(dev),
+                              bullet_mask=w.bullet_mask.to(dev))
+            assert y.device == torch.device(dev)
+            outs.append((y.cpu(), h.cpu()))
+    torch.cuda.synchronize(0)
+    torch.cuda.synchronize(1)
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
