@@ -1,5 +1,6 @@
-// CUDA-core (SIMT) kernels of the Yemong trunk: float32 arithmetic throughout, with the
-// bf16 roundings of the autocast contract applied in software when EMU is set.
+// Exact-arithmetic kernels of the Yemong trunk: float32 results throughout (elementwise math on
+// the CUDA cores, Linear products as 3 x tf32 tensor-core MMAs with float32 accumulation), with
+// the bf16 roundings of the autocast contract applied in software when EMU is set.
 //
 // These kernels serve BNB_FP32 calls (1e-4 parity needs float32 products, which the
 // bf16 tensor-core path cannot give) and BNB_BF16 calls whose shapes the tensor-core
@@ -23,48 +24,106 @@ constexpr int KC = 32;          // K chunk staged per pass
 constexpr int WS_STRIDE = KC + 4;
 constexpr int NCHUNK = 128;     // output columns per tile_linear call
 
+// Split of a float into two tf32 numbers, hi + lo = v to about 2^-21: the products
+// lo*hi + hi*lo + hi*hi of two such pairs, accumulated in float32 by the tensor cores, keep
+// float32-level accuracy (the dropped lo*lo term is below 2^-22 relative).
+__device__ __forceinline__ uint32_t to_tf32(float v) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+  return r;
+}
+__device__ __forceinline__ void split_tf32(float v, uint32_t& hi, uint32_t& lo) {
+  hi = to_tf32(v);
+  lo = to_tf32(v - __uint_as_float(hi));
+}
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
 // acc[i][j] += sum_k A[4*warp+i][k] * W[(lane + 32 j)][k]   for lane + 32 j < N
-// A: shared, row stride lda (floats), already rounded for EMU.  W: global, row stride ldw.
-// Ws: shared staging of NCHUNK x WS_STRIDE floats.  All threads of the CTA must call.
+// A: shared, row stride lda (floats, lda = 4 mod 32), already rounded for EMU.  W: global, row
+// stride ldw.  Ws: shared staging of NCHUNK x WS_STRIDE floats.  All threads of the CTA must call.
+//
+// The products run on the tensor cores as m16n8k8 tf32 MMAs with float32 accumulation: warp w
+// owns rows 16 (w & 1) .. +15 and the 8-column blocks (w >> 1) + 4 q.  With EMU the operands are
+// bf16 values, exact in tf32, so one MMA per block; otherwise each operand is split in two tf32
+// numbers and three MMAs give the float32 product.  The result goes through shared memory into
+// the (4 rows x 4 strided columns) per-thread layout the callers' epilogues use.
 template <bool EMU>
 __device__ __forceinline__ void tile_linear(const float* __restrict__ A, int lda,
                                             const float* __restrict__ W, int ldw, int N, int K,
                                             float* __restrict__ Ws, float (&acc)[4][4]) {
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int mrow = 16 * (warp & 1) + g;
+  float c[4][4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) c[q][i] = 0.f;
   for (int k0 = 0; k0 < K; k0 += KC) {
     __syncthreads();  // previous users of Ws are done
     for (int idx = tid; idx < N * (KC / 4); idx += NTHREADS) {
-      int c = idx >> 3, q = idx & 7;
-      float4 v = *reinterpret_cast<const float4*>(W + (size_t)c * ldw + k0 + q * 4);
+      int cc = idx >> 3, q = idx & 7;
+      float4 v = *reinterpret_cast<const float4*>(W + (size_t)cc * ldw + k0 + q * 4);
       if constexpr (EMU) {
         v.x = round_bf16(v.x); v.y = round_bf16(v.y); v.z = round_bf16(v.z); v.w = round_bf16(v.w);
       }
-      *reinterpret_cast<float4*>(Ws + c * WS_STRIDE + q * 4) = v;
+      *reinterpret_cast<float4*>(Ws + cc * WS_STRIDE + q * 4) = v;
     }
     __syncthreads();
-#pragma unroll 2
-    for (int kk = 0; kk < KC; kk += 4) {
-      float4 a[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        a[i] = *reinterpret_cast<const float4*>(A + (4 * warp + i) * lda + k0 + kk);
+    for (int kk = 0; kk < KC; kk += 8) {
+      const float* ap = A + mrow * lda + k0 + kk + t;
+      const float af[4] = {ap[0], ap[8 * lda], ap[4], ap[8 * lda + 4]};
+      uint32_t ah[4], al[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        int c = lane + 32 * j;
-        if (c < N) {
-          float4 w = *reinterpret_cast<const float4*>(Ws + c * WS_STRIDE + kk);
+      for (int i = 0; i < 4; ++i) {
+        if constexpr (EMU) ah[i] = __float_as_uint(af[i]);
+        else split_tf32(af[i], ah[i], al[i]);
+      }
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            acc[i][j] = fmaf(a[i].x, w.x, acc[i][j]);
-            acc[i][j] = fmaf(a[i].y, w.y, acc[i][j]);
-            acc[i][j] = fmaf(a[i].z, w.z, acc[i][j]);
-            acc[i][j] = fmaf(a[i].w, w.w, acc[i][j]);
+      for (int q = 0; q < 4; ++q) {
+        const int n0 = 8 * ((warp >> 1) + 4 * q);
+        if (n0 < N) {
+          const float* bp = Ws + (n0 + g) * WS_STRIDE + kk + t;
+          if constexpr (EMU) {
+            mma_tf32(c[q], ah, __float_as_uint(bp[0]), __float_as_uint(bp[4]));
+          } else {
+            uint32_t bh0, bl0, bh1, bl1;
+            split_tf32(bp[0], bh0, bl0);
+            split_tf32(bp[4], bh1, bl1);
+            mma_tf32(c[q], al, bh0, bh1);
+            mma_tf32(c[q], ah, bl0, bl1);
+            mma_tf32(c[q], ah, bh0, bh1);
           }
         }
       }
     }
   }
+  // fragments -> shared (the staging area is free now) -> the callers' per-thread layout
+  constexpr int LDC = NCHUNK + 4;
+  static_assert(ROWS * LDC <= NCHUNK * WS_STRIDE, "the staging area must hold one output tile");
+  __syncthreads();
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int n0 = 8 * ((warp >> 1) + 4 * q);
+    if (n0 < N) {
+      *reinterpret_cast<float2*>(Ws + mrow * LDC + n0 + 2 * t) = make_float2(c[q][0], c[q][1]);
+      *reinterpret_cast<float2*>(Ws + (mrow + 8) * LDC + n0 + 2 * t) = make_float2(c[q][2], c[q][3]);
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int col = lane + 32 * j;
+      if (col < N) acc[i][j] += Ws[(4 * warp + i) * LDC + col];
+    }
 }
 
 __device__ __forceinline__ void zero_acc(float (&acc)[4][4]) {
