@@ -50,10 +50,11 @@ typedef enum {
 typedef enum { BNB_FP32 = 0, BNB_BF16 = 1 } BnbPrecision;
 
 /* Which engine runs a BNB_BF16 call.
- *   BNB_ENGINE_AUTO   tensor-core kernels where the shapes are built for them, else SIMT
- *   BNB_ENGINE_SIMT   CUDA-core kernels with the bf16 roundings applied in software
- *   BNB_ENGINE_TENSOR tensor-core kernels or BNB_ERR_UNSUPPORTED_DIMS
- * BNB_FP32 always runs on the SIMT kernels. */
+ *   BNB_ENGINE_AUTO   the fused tcgen05 kernels where the shapes are built for them, else SIMT
+ *   BNB_ENGINE_SIMT   the exact kernels: float32 elementwise math on the CUDA cores, Linear
+ *                     products float32-accurate (3 x tf32 MMAs), bf16 roundings applied in software
+ *   BNB_ENGINE_TENSOR the fused tcgen05 kernels or BNB_ERR_UNSUPPORTED_DIMS
+ * BNB_FP32 always runs on the exact kernels. */
 typedef enum { BNB_ENGINE_AUTO = 0, BNB_ENGINE_SIMT = 1, BNB_ENGINE_TENSOR = 2 } BnbEngine;
 
 /* Parameters of one spatial sublayer.
@@ -185,7 +186,7 @@ int bnb_spatial_block_fwd(const BnbSpatialWeights* w, int d_model, int n_heads,
  *   - limit: n_groups * batch->total_tokens <= BNB_STATIC_MAX_ROWS, else
  *     BNB_ERR_EXCEEDS_STATIC_LIMIT and nothing is launched; d_model <= 128;
  *   - cost: every GPU that loads the library holds BNB_STATIC_SCRATCH_BYTES until exit;
- *   - always the CUDA-core (SIMT) kernels, in either precision;
+ *   - always the exact (BNB_ENGINE_SIMT) kernels, in either precision;
  *   - the first call on each device looks up the array's device address (that device must
  *     be current); make that first call before starting any stream capture;
  *   - all calls share the one array: two calls that may overlap on the GPU (different
