@@ -382,7 +382,7 @@ k_spatial_post(const float* __restrict__ x, const float* __restrict__ o, float* 
 // RG-LRU state and conv taps of its (row, column) elements in registers.  FIELD = true:
 // rows are (t, field token) pairs, no state, conv+RG-LRU replaced by the field_sub Linear.
 template <bool EMU, bool FIELD>
-__global__ void __launch_bounds__(NTHREADS, 1)
+__global__ void __launch_bounds__(NTHREADS, 2)
 k_temporal(const float* __restrict__ x, float* __restrict__ y,
            const float* __restrict__ hidden_in, float* __restrict__ hidden_out,
            const uint8_t* __restrict__ done, const uint8_t* __restrict__ reset_env,
