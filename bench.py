@@ -84,8 +84,15 @@ WORKLOAD_TEXT = {
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples of one GPU during the timed region."""
+    """SM clock and throttle-reason samples of one GPU during the timed region.
 
+    The timed region of a default run lasts tens of milliseconds, shorter than the start-up of an
+    `nvidia-smi -lms` process, so the samples are read through NVML (the library nvidia-smi itself
+    uses) from a background thread every 2 ms; `nvidia-smi` is the fallback when the NVML binding is
+    missing.  Only reads: no clock, power or mode setting is touched.
+    """
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
@@ -94,47 +101,92 @@ class ClockSampler:
         self.index = index
         self.proc = None
         self.file = None
+        self.thread = None
+        self.stop_flag = None
+        self.sm, self.mx, self.reasons = [], [], set()
+        self.source = None
+
+    def _nvml_handle(self):
+        import pynvml
+
+        pynvml.nvmlInit()
+        try:
+            uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            return pynvml, pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+        except Exception:
+            return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.index)
 
     def start(self):
+        try:
+            import threading
+
+            nv, handle = self._nvml_handle()
+            max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
+            self.stop_flag = threading.Event()
+
+            def loop():
+                while not self.stop_flag.is_set():
+                    try:
+                        self.sm.append(float(nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)))
+                        self.mx.append(max_mhz)
+                        mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(handle))
+                        for bit, name in self.REASONS.items():
+                            if mask & bit:
+                                self.reasons.add(name)
+                    except Exception:
+                        pass
+                    time.sleep(0.002)
+
+            self.thread = threading.Thread(target=loop, daemon=True)
+            self.thread.start()
+            self.source = "nvml"
+            return
+        except Exception:
+            self.thread = None
         try:
             self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
                  "-lms", "100"], stdout=self.file, stderr=subprocess.DEVNULL)
+            self.source = "nvidia-smi"
         except Exception:
             self.proc = None
 
     def stop(self) -> dict:
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self.proc is None:
-            return out
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        self.file.flush()
-        self.file.seek(0)
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.file.read().splitlines():
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 7:
-                continue
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "source": self.source}
+        if self.thread is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+        elif self.proc is not None:
+            self.proc.terminate()
             try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
-            except ValueError:
-                continue
-            for n, v in zip(names, parts[3:7]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        try:
-            os.unlink(self.file.name)
-        except OSError:
-            pass
-        if sm:
-            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+            self.file.flush()
+            self.file.seek(0)
+            names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+            for line in self.file.read().splitlines():
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 7:
+                    continue
+                try:
+                    self.sm.append(float(parts[0]))
+                    self.mx.append(float(parts[1]))
+                except ValueError:
+                    continue
+                for n, v in zip(names, parts[3:7]):
+                    if v.lower().startswith("active"):
+                        self.reasons.add(n)
+            try:
+                os.unlink(self.file.name)
+            except OSError:
+                pass
+        if self.sm:
+            out.update(sm_mhz=statistics.median(self.sm), sm_max_mhz=max(self.mx), reasons=sorted(self.reasons),
+                       samples=len(self.sm))
         return out
 
 
@@ -387,7 +439,7 @@ def run_ours(args) -> None:
             "tensor": {"achieved": alg_flops / (kernel_ms * 1e-3) / 1e12, "peak": tflops, "unit": "TFLOP/s",
                        "frac": alg_flops / (kernel_ms * 1e-3) / 1e12 / tflops, "of": src,
                        "algorithmic_flops_per_step": alg_flops},
-            "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")} if clocks else None,
+            "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons", "samples", "source")} if clocks else None,
         }
         if world == 1 and not args.no_cpu:
             base = time_cpu(args.workload, 3, 1)
