@@ -282,6 +282,20 @@ def run_ours(args) -> None:
         dist = dist_mod
         dist.init_process_group("nccl", device_id=dev)
 
+    if world > 1:
+        # One process per GPU: run this rank on the CPUs next to its GPU, so that the pinned host
+        # buffers of the end-to-end leg are placed (first touch) in that GPU's NUMA node instead of
+        # all ranks sharing one socket's memory and the inter-socket link.
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(local).uuid)
+            handle = pynvml.nvmlDeviceGetHandleByUUID((uuid if uuid.startswith("GPU-") else "GPU-" + uuid).encode())
+            pynvml.nvmlDeviceSetCpuAffinity(handle)
+        except Exception:
+            pass
+
     cfg = W.rl_config()
     torch.manual_seed(0)
     trunk = bnb.YemongTrunk(cfg).eval()

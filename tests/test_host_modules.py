@@ -1,5 +1,8 @@
 """Host-side mirror of the reference interface: parameter names, shapes, init, errors."""
 
+import os
+import sys
+
 import numpy as np
 import pytest
 import torch
@@ -122,3 +125,39 @@ def test_operators_are_registered_with_shape_only_fakes():
         assert y.shape == (60, 128) and h.shape == (2, 40, 512) and y.dtype == torch.float32
         y = torch.ops.bnb_b200.spatial_forward(x, None, None, None, w, 4, 1, 0)
         assert y.shape == (5, 12, 128)
+
+
+@pytest.mark.skipif(not os.environ.get("BNB_REFERENCE_SRC"), reason="set BNB_REFERENCE_SRC to the reference's src/ folder")
+def test_class_swap_inside_the_reference_policy():
+    """The drop-in itself: the reference's YemongPolicy built with this package's YemongBlock in
+    place of its own has the same state_dict keys and, from the same seed, the same values, and
+    loads the reference's state_dict strictly.  Construction only; nothing is computed."""
+    sys.path.insert(0, os.environ["BNB_REFERENCE_SRC"])
+    import boost_and_broadside.models.yemong.policy as ref_policy
+    from boost_and_broadside.config import ModelConfig as RefConfig
+    from boost_and_broadside.config import ShipConfig
+    from boost_and_broadside.train.rl.features import build_bullet_coordinator, build_standard_coordinator
+
+    import boost_and_broadside_b200 as bnb
+
+    cfg = RefConfig(d_model=128, n_heads=4, n_yemong_blocks=2, n_spatial_per_block=2, n_temporal_per_block=1,
+                    n_bullet_cross_per_block=1)
+    ships = ShipConfig()
+
+    def make():
+        torch.manual_seed(0)
+        return ref_policy.YemongPolicy(cfg, build_standard_coordinator(ships), num_value_components=12, num_ships=8,
+                                       team_pma_k=(), bullet_coordinator=build_bullet_coordinator(ships))
+
+    reference = make()
+    original = ref_policy.YemongBlock
+    ref_policy.YemongBlock = bnb.YemongBlock
+    try:
+        swapped = make()
+    finally:
+        ref_policy.YemongBlock = original
+    assert isinstance(swapped.yemong_layers[0], bnb.YemongBlock)
+    a, b = reference.state_dict(), swapped.state_dict()
+    assert list(a.keys()) == list(b.keys())
+    assert all(torch.equal(a[k], b[k]) for k in a)
+    swapped.load_state_dict(a, strict=True)
