@@ -36,6 +36,8 @@ def shard_workload(w: Workload, rank: int, world: int) -> Workload:
         return dataclasses.replace(
             w, x=w.x[tok[lo] : tok[hi]], alive=w.alive[tok[lo] : tok[hi]],
             hidden=w.hidden[:, ship[lo] : ship[hi]], n_tokens=w.n_tokens[lo:hi], n_ships=w.n_ships[lo:hi],
+            bullets=None if w.bullets is None else w.bullets[lo:hi],
+            bullet_mask=None if w.bullet_mask is None else w.bullet_mask[lo:hi],
             meta=dict(w.meta, n_envs=hi - lo),
         )
     env_dim = 1 if w.kind == "sequence" else 0
@@ -46,7 +48,11 @@ def shard_workload(w: Workload, rank: int, world: int) -> Workload:
     return dataclasses.replace(
         w, x=w.x[sl], alive=None if w.alive is None else w.alive[sl],
         hidden=None if w.hidden is None else w.hidden[:, lo * ships : hi * ships],
-        done=None if w.done is None else w.done[:, lo:hi], meta=dict(w.meta, n_envs=hi - lo),
+        done=None if w.done is None else w.done[:, lo:hi],
+        # bullets of a step are env-major like x (a sequence's are (T * n_envs, ...): not sharded here)
+        bullets=None if w.bullets is None or env_dim else w.bullets[lo:hi],
+        bullet_mask=None if w.bullet_mask is None or env_dim else w.bullet_mask[lo:hi],
+        meta=dict(w.meta, n_envs=hi - lo),
     )
 
 

@@ -29,6 +29,11 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
         w = W.c2(n_envs=37, seed=11)
         s = sharding.shard_workload(w, rank, world)
         results["c2"] = O.trunk_step(s.x, s.alive, s.hidden, P, 4, "fp32")
+        # uniform step with bullet tokens: the bullets follow their environments
+        w = W.c2b(n_envs=11, seed=14, bullets_per_env=9)
+        s = sharding.shard_workload(w, rank, world)
+        assert s.bullets.shape[0] == s.x.shape[0] == s.bullet_mask.shape[0]
+        results["c2b"] = O.trunk_step(s.x, s.alive, s.hidden, P, 4, "fp32", s.bullets, s.bullet_mask)
         # sequence with done flags
         w = W.c4(n_envs=5, timesteps=4, seed=12)
         s = sharding.shard_workload(w, rank, world)
@@ -78,6 +83,11 @@ def test_two_ranks_reproduce_the_single_rank_result(tmp_path):
     y, h = O.trunk_step(w.x, w.alive, w.hidden, P, 4, "fp32")
     assert torch.allclose(torch.cat([p["c2"][0] for p in parts]), y, atol=1e-5)
     assert torch.allclose(torch.cat([p["c2"][1] for p in parts], dim=1), h, atol=1e-5)
+
+    w = W.c2b(n_envs=11, seed=14, bullets_per_env=9)
+    y, h = O.trunk_step(w.x, w.alive, w.hidden, P, 4, "fp32", w.bullets, w.bullet_mask)
+    assert torch.allclose(torch.cat([p["c2b"][0] for p in parts]), y, atol=1e-5)
+    assert torch.allclose(torch.cat([p["c2b"][1] for p in parts], dim=1), h, atol=1e-5)
 
     w = W.c4(n_envs=5, timesteps=4, seed=12)
     y, h = O.trunk_sequence(w.x, w.alive, w.hidden, w.done, P, 4, "fp32")
