@@ -489,3 +489,22 @@ def test_bullets_at_unseen_fleet_sizes(mode, ships, fields, nb):
         y, nh = trunk.step(_to(w.x), _to(w.alive), _to(w.hidden), bullets=_to(bul), bullet_mask=_to(bm))
     assert_close(y, ref_y, mode, "y")
     assert_close(nh, ref_h, mode, "hidden")
+
+
+def test_backward_through_the_operators_is_refused_loudly():
+    """Forward-only: with grad mode on and parameters that require grad, the operators carry no
+    autograd formula, so a backward through their outputs raises instead of silently skipping
+    the trunk's parameters; inputs that require grad are refused at the call."""
+    from boost_and_broadside_b200 import ModelConfig, YemongTrunk
+
+    trunk = YemongTrunk(ModelConfig(128, 4, 1, 1, 1)).to(DEV)
+    x = torch.randn(2, 3, 128, device=DEV)
+    hidden = torch.zeros(1, 6, 512, device=DEV)
+    with pytest.raises(NotImplementedError):
+        trunk.step(x.clone().requires_grad_(True), None, hidden)
+    y, _ = trunk.step(x, None, hidden)          # grad mode on, parameters require grad
+    if y.requires_grad:
+        with pytest.raises(RuntimeError):
+            y.sum().backward()
+    else:
+        assert all(p.grad is None for p in trunk.parameters())
