@@ -18,12 +18,24 @@ from typing import List, Optional, Tuple
 import torch
 from torch import Tensor
 
+import os
+
 from .. import _capi
 from ._weights import N_SPATIAL, N_TEMPORAL, packed_image, spatial_struct_from, temporal_struct_from
 
 # geom: the integers of a call, in this order
 (G_BLOCKS, G_SPATIAL, G_TEMPORAL, G_HEADS, G_BULLET_CROSS, G_FIELD_SUB, G_ENVS, G_TOKENS_PER_ENV, G_SHIPS_PER_ENV,
  G_MAX_TOKENS, G_TOTAL_TOKENS, G_TOTAL_SHIPS, G_TILES, G_TIMESTEPS, G_ENGINE, G_PRECISION) = range(16)
+
+
+def _debug_check(fn: str, dev: torch.device, precision: int) -> None:
+    """With BNB_DEBUG_SYNC=1 in the environment every call waits for its kernels and raises if
+    one of the tensor-core kernels' bounded waits ran out (status word at the head of the scratch
+    buffer).  Off by default: the check synchronises, so it cannot run under graph capture."""
+    if precision == _capi.BNB_BF16 and os.environ.get("BNB_DEBUG_SYNC") == "1":
+        st = _capi.tensor_engine_status(dev)
+        if 100 < st < 200:   # the ST_TIMEOUT_* codes; other values are scratch data of the exact engine
+            raise RuntimeError(f"{fn}: a bounded wait of the tensor-core kernels ran out (code {st})")
 
 
 def uniform_geom(n_envs: int, tokens: int, ships: int) -> List[int]:
@@ -116,6 +128,7 @@ def trunk_forward(
                 scratch.data_ptr(), scratch.numel(), stream,
             )
     _capi.check(fn, st)
+    _debug_check(fn, dev, precision)
     return y, hout
 
 
@@ -154,6 +167,7 @@ def spatial_forward(
             scratch.data_ptr(), scratch.numel(), _capi.stream_handle(dev),
         )
     _capi.check("bnb_spatial_block_fwd", st)
+    _debug_check("bnb_spatial_block_fwd", dev, precision)
     return y
 
 
