@@ -538,17 +538,23 @@ __device__ __forceinline__ void norm_to_A(Ctx& c, const float* __restrict__ g) {
   uint32_t v[CPT];
   tmem_ld_cols<CPT>(c.lane_addr + COL_RESID + c.part * CPT, v);
   tmem_wait_ld();
+  // Sum of squares in chains of 32 columns, combined pairwise, so that the result has the same
+  // bits whether a row is shared by two threads or by four.
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < CPT; ++i) {
-    float a = __uint_as_float(v[i]);
-    ss = fmaf(a, a, ss);
+  for (int h = 0; h < CPT / 32; ++h) {
+    float sh = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      float a = __uint_as_float(v[h * 32 + i]);
+      sh = fmaf(a, a, sh);
+    }
+    ss = h == 0 ? sh : ss + sh;
   }
   c.ss_part[c.part * TILE + c.row] = ss;
   epi_barrier<NQ>();
-  ss = 0.f;
-#pragma unroll
-  for (int q = 0; q < NQ; ++q) ss += c.ss_part[q * TILE + c.row];
+  if constexpr (NQ == 2) ss = c.ss_part[c.row] + c.ss_part[TILE + c.row];
+  else ss = (c.ss_part[c.row] + c.ss_part[TILE + c.row]) + (c.ss_part[2 * TILE + c.row] + c.ss_part[3 * TILE + c.row]);
   const float inv = rsqrtf(ss * (1.0f / D) + kRmsEps);
 #pragma unroll
   for (int q = 0; q < CPT / 8; ++q) {
@@ -1113,7 +1119,7 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
 }
 
 template <int NQ, int MAXKB>
-__global__ void __launch_bounds__(128 * NQ, 2) k_trunk_tiles(const __grid_constant__ TrunkArgs args) {
+__global__ void __launch_bounds__(128 * NQ, NQ == 4 ? 1 : 2) k_trunk_tiles(const __grid_constant__ TrunkArgs args) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ int s_aborted;
@@ -1762,7 +1768,9 @@ static int launch(TrunkArgs& a, const BnbBatch& b, cudaStream_t st) {
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BNB_ERR_NO_DEVICE;
   if (!configured[dev]) {
     if (cudaFuncSetAttribute(k_trunk_tiles<2, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
-        cudaFuncSetAttribute(k_trunk_tiles<2, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+        cudaFuncSetAttribute(k_trunk_tiles<2, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
+        cudaFuncSetAttribute(k_trunk_tiles<4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
+        cudaFuncSetAttribute(k_trunk_tiles<4, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
       return BNB_ERR_LAUNCH;
     configured[dev] = true;
   }
@@ -1770,8 +1778,17 @@ static int launch(TrunkArgs& a, const BnbBatch& b, cudaStream_t st) {
   count_launch();
   // Two threads per tile row: four (64 registers per thread at two CTAs per SM) spill and were
   // measured slower.
-  if (b.max_tokens_per_env <= 64 || a.flat_rows) k_trunk_tiles<2, 4><<<grid, 256, SMEM_BYTES, st>>>(a);
-  else k_trunk_tiles<2, 8><<<grid, 256, SMEM_BYTES, st>>>(a);
+  const bool small_keys = b.max_tokens_per_env <= 64 || a.flat_rows;
+  if (a.n_tiles <= 148) {
+    // At most one tile per SM: the launch is one tile chain long, so each tile gets a whole SM:
+    // four threads per row with the full register budget (one CTA per SM).
+    if (small_keys) k_trunk_tiles<4, 4><<<grid, 512, SMEM_BYTES, st>>>(a);
+    else k_trunk_tiles<4, 8><<<grid, 512, SMEM_BYTES, st>>>(a);
+  } else if (small_keys) {
+    k_trunk_tiles<2, 4><<<grid, 256, SMEM_BYTES, st>>>(a);
+  } else {
+    k_trunk_tiles<2, 8><<<grid, 256, SMEM_BYTES, st>>>(a);
+  }
   return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
 }
 

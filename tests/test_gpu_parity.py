@@ -258,8 +258,9 @@ def test_full_size_step_properties():
         assert torch.isfinite(y1).all() and torch.isfinite(h1).all()
         lo, hi = 1000, 1640
         ys, hs = trunk.step(x[lo:hi], alive[lo:hi], hidden[:, lo * 8 : hi * 8])
-        assert_close(ys, y1[lo:hi], "bf16", "env slice y", scale=0.05)
-        assert_close(hs, h1[:, lo * 8 : hi * 8], "bf16", "env slice hidden", scale=0.05)
+        # 640 environments are 64 tiles: the one-CTA-per-SM variant of the kernel (four threads per
+        # row) runs them, the full batch runs on the two-CTA variant, and the bits still agree
+        assert torch.equal(ys, y1[lo:hi]) and torch.equal(hs, h1[:, lo * 8 : hi * 8])
         # perturb dead ships only
         dead = ~alive
         x2 = x.clone()
