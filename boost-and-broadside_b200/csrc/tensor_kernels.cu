@@ -1774,14 +1774,16 @@ static int launch(TrunkArgs& a, const BnbBatch& b, cudaStream_t st) {
       return BNB_ERR_LAUNCH;
     configured[dev] = true;
   }
-  int grid = a.n_tiles < 2 * 148 ? a.n_tiles : 2 * 148;
+  // Two variants: two CTAs per SM with two threads per row (four threads per row would have 64
+  // registers each and spill), or one CTA per SM with four threads per row and the full register
+  // budget, in which a tile takes about 0.6 of the time but only one runs per SM: it wins when
+  // the tiles fit one per SM (measured no better at 297..444 tiles, three of its rounds against
+  // two of the other's).
+  const bool one_per_sm = a.n_tiles <= 148;
+  int grid = one_per_sm ? (a.n_tiles < 148 ? a.n_tiles : 148) : (a.n_tiles < 2 * 148 ? a.n_tiles : 2 * 148);
   count_launch();
-  // Two threads per tile row: four (64 registers per thread at two CTAs per SM) spill and were
-  // measured slower.
   const bool small_keys = b.max_tokens_per_env <= 64 || a.flat_rows;
-  if (a.n_tiles <= 148) {
-    // At most one tile per SM: the launch is one tile chain long, so each tile gets a whole SM:
-    // four threads per row with the full register budget (one CTA per SM).
+  if (one_per_sm) {
     if (small_keys) k_trunk_tiles<4, 4><<<grid, 512, SMEM_BYTES, st>>>(a);
     else k_trunk_tiles<4, 8><<<grid, 512, SMEM_BYTES, st>>>(a);
   } else if (small_keys) {
