@@ -28,6 +28,7 @@
 #include "tensor_kernels.h"
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include <vector>
 
@@ -286,6 +287,25 @@ __device__ __forceinline__ float gelu_fast(float v) {
   const float t = tanh_fast(v * p);
   const float h = 0.5f * v;
   return fmaf(h, t, h);
+}
+// gelu(g) * u for two elements at once in half precision (11 mantissa bits against the 8 of the
+// bf16 result), packed as two bf16: one tanh.approx.f16x2 and about half the instructions of two
+// float evaluations.  g * g saturates at 100 as in gelu_fast (an overflow to inf lands there too).
+__device__ __forceinline__ uint32_t gelu_mul_bf16x2(float g0, float g1, float u0, float u1) {
+  const __half2 g = __floats2half2_rn(g0, g1);
+  const __half2 u = __floats2half2_rn(u0, u1);
+  const __half2 x2 = __hmin2(__hmul2(g, g), __float2half2_rn(100.0f));
+  __half2 p = __hfma2(x2, __float2half2_rn(-3.51516841e-4f), __float2half2_rn(3.70056464e-2f));
+  p = __hfma2(x2, p, __float2half2_rn(7.97507884e-1f));
+  const __half2 a = __hmul2(g, p);
+  uint32_t ti, to;
+  ti = *reinterpret_cast<const uint32_t*>(&a);
+  asm("tanh.approx.f16x2 %0, %1;" : "=r"(to) : "r"(ti));
+  const __half2 t = *reinterpret_cast<const __half2*>(&to);
+  const __half2 h = __hmul2(g, __float2half2_rn(0.5f));
+  const __half2 r = __hmul2(__hfma2(h, t, h), u);
+  const float2 f = __half22float2(r);
+  return pack_bf16(f.x, f.y);
 }
 __device__ __forceinline__ float sigmoid_fast(float v) { return fmaf(0.5f, tanh_fast(0.5f * v), 0.5f); }
 
@@ -594,8 +614,8 @@ __device__ __forceinline__ void ffn(Ctx& c) {
       uint32_t o[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j)
-        o[j] = pack_bf16(gelu_fast(__uint_as_float(gv[q * 8 + 2 * j])) * __uint_as_float(uv[q * 8 + 2 * j]),
-                         gelu_fast(__uint_as_float(gv[q * 8 + 2 * j + 1])) * __uint_as_float(uv[q * 8 + 2 * j + 1]));
+        o[j] = gelu_mul_bf16x2(__uint_as_float(gv[q * 8 + 2 * j]), __uint_as_float(gv[q * 8 + 2 * j + 1]),
+                               __uint_as_float(uv[q * 8 + 2 * j]), __uint_as_float(uv[q * 8 + 2 * j + 1]));
       *reinterpret_cast<uint4*>(c.smem + OFF_P + swz(c.row, c.part * (GC / 8) + q)) = make_uint4(o[0], o[1], o[2], o[3]);
     }
     T_END(c, TM_FFN_EPI);
