@@ -76,8 +76,6 @@ enum : int { ST_TIMEOUT_FULL = 101, ST_TIMEOUT_EMPTY = 102, ST_TIMEOUT_ACC = 103
 struct SubLayer {
   int type;
   const uint8_t* packed;
-  const float* g1;
-  const float* g2;
   const float* conv_w;
   const float* conv_b;
   const float* a_b;
@@ -356,8 +354,24 @@ __device__ __forceinline__ const float* temporal_chunk_row(const BnbTemporalWeig
   }
 }
 
-template <class W, class F>
-__device__ __forceinline__ void pack_image(const W& w, int n_chunks, uint8_t* out, F row_of) {
+// RMSNorm gain folded into chunk `c`: the 64 gains of the chunk's K columns when the chunk's
+// input is a normed activation, else nullptr.  The kernels then feed x * rsqrt(mean x^2 + eps)
+// without the gain, and the products see W[n][k] * g[k] rounded to bf16 once.
+__device__ __forceinline__ const float* spatial_chunk_gain(const BnbSpatialWeights& w, int c) {
+  if (c < 10) { const int i = c % 5; return i < 4 ? w.norm1_w + (i % 2) * 64 : nullptr; }
+  if (c >= N_SPATIAL_CHUNKS) return w.norm_bullet_w ? w.norm_bullet_w + ((c - N_SPATIAL_CHUNKS) & 1) * 64 : nullptr;
+  const int i = (c - 10) % 3;
+  return i < 2 ? w.norm2_w + i * 64 : nullptr;
+}
+__device__ __forceinline__ const float* temporal_chunk_gain(const BnbTemporalWeights& w, int c) {
+  if (c < 4) return w.norm1_w + (c & 1) * 64;        // linear2, linear1
+  if (c < 12) return nullptr;                         // gates, field_sub, linear_out: not fed by a norm
+  const int i = (c - 12) % 3;
+  return i < 2 ? w.norm2_w + i * 64 : nullptr;
+}
+
+template <class W, class F, class G>
+__device__ __forceinline__ void pack_image(const W& w, int n_chunks, uint8_t* out, F row_of, G gain_of) {
   // one thread per 16-byte group: (chunk, row, group of 8 columns)
   const int total = n_chunks * TILE * 8;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
@@ -367,20 +381,27 @@ __device__ __forceinline__ void pack_image(const W& w, int n_chunks, uint8_t* ou
     if (src) {
       float4 a = *reinterpret_cast<const float4*>(src + g * 8);
       float4 b = *reinterpret_cast<const float4*>(src + g * 8 + 4);
+      if (const float* gain = gain_of(w, c)) {
+        const float4 ga = *reinterpret_cast<const float4*>(gain + g * 8), gb = *reinterpret_cast<const float4*>(gain + g * 8 + 4);
+        a.x *= ga.x; a.y *= ga.y; a.z *= ga.z; a.w *= ga.w;
+        b.x *= gb.x; b.y *= gb.y; b.z *= gb.z; b.w *= gb.w;
+      }
       v = make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(b.x, b.y), pack_bf16(b.z, b.w));
     }
     *reinterpret_cast<uint4*>(out + (size_t)c * CHUNK_BYTES + swz(r, g)) = v;
   }
 }
 __global__ void k_pack_spatial(BnbSpatialWeights w, uint8_t* out) {
-  pack_image(w, N_SPATIAL_IMAGE, out, [](const BnbSpatialWeights& ww, int c, int r) { return spatial_chunk_row(ww, c, r); });
+  pack_image(w, N_SPATIAL_IMAGE, out, [](const BnbSpatialWeights& ww, int c, int r) { return spatial_chunk_row(ww, c, r); },
+             [](const BnbSpatialWeights& ww, int c) { return spatial_chunk_gain(ww, c); });
 }
 __global__ void k_pack_temporal(BnbTemporalWeights w, uint8_t* out) {
   if (blockIdx.x == 0 && threadIdx.x < D) {
     float sg = 1.0f / (1.0f + expf(-w.log_lambda[threadIdx.x]));
     reinterpret_cast<float*>(out + (size_t)N_TEMPORAL_CHUNKS * CHUNK_BYTES)[threadIdx.x] = kRglruC * log2f(sg);
   }
-  pack_image(w, N_TEMPORAL_CHUNKS, out, [](const BnbTemporalWeights& ww, int c, int r) { return temporal_chunk_row(ww, c, r); });
+  pack_image(w, N_TEMPORAL_CHUNKS, out, [](const BnbTemporalWeights& ww, int c, int r) { return temporal_chunk_row(ww, c, r); },
+             [](const BnbTemporalWeights& ww, int c) { return temporal_chunk_gain(ww, c); });
 }
 
 // ------------------------------------------------------------------ the tile kernel
@@ -550,9 +571,9 @@ __device__ __forceinline__ void round_end(Ctx& c) {
 // TMEM lane `row` and columns [part * 128/NQ, ...) of a 128-wide row, [part * 64/NQ, ...) of a
 // 64-wide block and [part * 96/NQ, ...) of a q|k|v accumulator.
 
-// residual (TMEM) -> RMSNorm -> bf16 A operand
+// residual (TMEM) -> x * rsqrt(mean x^2 + eps) -> bf16 A operand (the RMSNorm gain is in the weights)
 template <int NQ>
-__device__ __forceinline__ void norm_to_A(Ctx& c, const float* __restrict__ g) {
+__device__ __forceinline__ void norm_to_A(Ctx& c) {
   constexpr int CPT = 128 / NQ;
   T_BEGIN(c);
   uint32_t v[CPT];
@@ -580,13 +601,12 @@ __device__ __forceinline__ void norm_to_A(Ctx& c, const float* __restrict__ g) {
   for (int q = 0; q < CPT / 8; ++q) {
     const int col = c.part * CPT + q * 8;
     const uint32_t* src = &v[q * 8];
-    float4 g0 = __ldg(reinterpret_cast<const float4*>(g + col));
-    float4 g1 = __ldg(reinterpret_cast<const float4*>(g + col + 4));
     uint4 o;
-    o.x = pack_bf16(__uint_as_float(src[0]) * inv * g0.x, __uint_as_float(src[1]) * inv * g0.y);
-    o.y = pack_bf16(__uint_as_float(src[2]) * inv * g0.z, __uint_as_float(src[3]) * inv * g0.w);
-    o.z = pack_bf16(__uint_as_float(src[4]) * inv * g1.x, __uint_as_float(src[5]) * inv * g1.y);
-    o.w = pack_bf16(__uint_as_float(src[6]) * inv * g1.z, __uint_as_float(src[7]) * inv * g1.w);
+    // the gain lives in the weights that consume this operand (see *_chunk_gain)
+    o.x = pack_bf16(__uint_as_float(src[0]) * inv, __uint_as_float(src[1]) * inv);
+    o.y = pack_bf16(__uint_as_float(src[2]) * inv, __uint_as_float(src[3]) * inv);
+    o.z = pack_bf16(__uint_as_float(src[4]) * inv, __uint_as_float(src[5]) * inv);
+    o.w = pack_bf16(__uint_as_float(src[6]) * inv, __uint_as_float(src[7]) * inv);
     *reinterpret_cast<uint4*>(c.smem + OFF_A + (col >> 6) * CHUNK_BYTES + swz(c.row, (col & 63) >> 3)) = o;
   }
   T_END(c, TM_NORM);
@@ -756,7 +776,7 @@ __device__ __forceinline__ uint4 pack8(const uint32_t* src) {
 template <int NQ, int MAXKB>
 __device__ __forceinline__ void run_spatial(Ctx& c, const SubLayer& s, int n_items, bool row_valid) {
   constexpr int QC = 96 / NQ, GC = 64 / NQ;
-  norm_to_A<NQ>(c, s.g1);
+  norm_to_A<NQ>(c);
   for (int p = 0; p < 2; ++p) {
     for (int hh = 0; hh < 2; ++hh) {
       round_begin<NQ>(c);
@@ -795,7 +815,7 @@ __device__ __forceinline__ void run_spatial(Ctx& c, const SubLayer& s, int n_ite
     if (threadIdx.x == 0) issue_chunk(c, c.sP, 128, COL_RESID, 1, (uint32_t)(p & 1));  // chunk 5p+4
     round_end<NQ>(c);
   }
-  norm_to_A<NQ>(c, s.g2);
+  norm_to_A<NQ>(c);
   ffn<NQ>(c);
 }
 
@@ -804,7 +824,7 @@ __device__ __forceinline__ void run_spatial(Ctx& c, const SubLayer& s, int n_ite
 template <int NQ>
 __device__ __forceinline__ void run_spatial_pre(Ctx& c, const SubLayer& s, size_t grow, bool row_valid) {
   constexpr int QC = 96 / NQ;
-  norm_to_A<NQ>(c, s.g1);
+  norm_to_A<NQ>(c);
   for (int hd = 0; hd < HEADS; ++hd) {
     round_begin<NQ>(c);
     if (threadIdx.x == 0) {
@@ -848,7 +868,7 @@ __device__ __forceinline__ void run_spatial_post(Ctx& c, const SubLayer& s, size
     issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_RESID, 1, 1);
   }
   round_end<NQ>(c);
-  norm_to_A<NQ>(c, s.g2);
+  norm_to_A<NQ>(c);
   ffn<NQ>(c);
 }
 
@@ -861,7 +881,7 @@ __device__ __forceinline__ void run_spatial_post(Ctx& c, const SubLayer& s, size
 template <int NQ>
 __device__ __forceinline__ void run_bullet_kv(Ctx& c, const SubLayer& s, size_t grow, bool row_valid) {
   constexpr int CPT = 128 / NQ;
-  norm_to_A<NQ>(c, s.g1);
+  norm_to_A<NQ>(c);
   round_begin<NQ>(c);
   if (threadIdx.x == 0) {
     if (!(c.parity & 1u)) {   // first tile of this CTA: the resident chunks are still arriving
@@ -907,7 +927,7 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
                                              bool has_fields, const float* hid_in) {
   constexpr int CPT = 128 / NQ, GC = 64 / NQ, WARPS = 4 * NQ;
   const bool is_ship = rs.hrow >= 0;
-  norm_to_A<NQ>(c, s.g1);
+  norm_to_A<NQ>(c);
   // b2 = bf16(gelu(linear2 n)) for this thread's columns, parked as packed bf16 pairs
   uint32_t b2p[2][GC / 2];
   round_begin<NQ>(c);
@@ -1134,7 +1154,7 @@ __device__ __forceinline__ void run_temporal(Ctx& c, const SubLayer& s, const Ro
     issue_chunk(c, c.sA + CHUNK_BYTES, 128, COL_RESID, 1, 1);
   }
   round_end<NQ>(c);
-  norm_to_A<NQ>(c, s.g2);
+  norm_to_A<NQ>(c);
   ffn<NQ>(c);
 }
 
@@ -1826,15 +1846,11 @@ static void fill_spatial(SubLayer& s, const BnbSpatialWeights& w) {
   s = SubLayer{};
   s.type = SUB_SPATIAL;
   s.packed = static_cast<const uint8_t*>(w.packed);
-  s.g1 = w.norm1_w;
-  s.g2 = w.norm2_w;
 }
 static void fill_temporal(SubLayer& s, const BnbTemporalWeights& w, const float* hin, float* hout) {
   s = SubLayer{};
   s.type = SUB_TEMPORAL;
   s.packed = static_cast<const uint8_t*>(w.packed);
-  s.g1 = w.norm1_w;
-  s.g2 = w.norm2_w;
   s.conv_w = w.conv_w;
   s.conv_b = w.conv_b;
   s.a_b = w.a_b;
@@ -1897,7 +1913,6 @@ static int launch_bullet_kv(const BnbSpatialWeights& w, const float* bullet_rows
   a.flat_rows = 1;
   a.sub[0].type = SUB_BULLET_KV;
   a.sub[0].packed = static_cast<const uint8_t*>(w.packed);
-  a.sub[0].g1 = w.norm_bullet_w;
   a.sub[0].kvb_out = kvb;
   BnbBatch rb{};              // every bullet row is a one-token environment without state
   rb.n_envs = rows;

@@ -401,3 +401,43 @@ def test_second_device_while_the_first_is_current():
     torch.cuda.synchronize(0)
     torch.cuda.synchronize(1)
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+
+
+def test_norm_gains_folded_into_the_weight_image():
+    """The tensor engine multiplies the RMSNorm gains into the packed weights of the Linear layers
+    that consume the normed activations.  Fresh modules have unit gains, so give every norm a
+    random gain (and the conv / gate biases random values) and compare with the oracle and with
+    the exact engine; then change one gain in place and check that the image follows."""
+    from boost_and_broadside_b200 import workloads as W
+
+    _capi, SIMT, TENSOR = _engines()
+    trunk = build_trunk([128, 4, 2, 2, 1, 1])
+    gen = torch.Generator().manual_seed(81)
+    with torch.no_grad():
+        for name, p in trunk.named_parameters():
+            if "norm" in name:
+                p.copy_(1.0 + 0.3 * torch.randn(p.shape, generator=gen))
+            elif name.endswith("bias"):
+                p.copy_(0.2 * torch.randn(p.shape, generator=gen))
+    w = W.c2b(n_envs=33, seed=83)
+    ref_y, ref_h = O.trunk_step(w.x, w.alive, w.hidden, trunk_params(trunk), 4, "bf16", w.bullets, w.bullet_mask)
+    trunk = trunk.to(DEV)
+    args = [t.to(DEV) for t in (w.x, w.alive, w.hidden)]
+    kw = dict(bullets=w.bullets.to(DEV), bullet_mask=w.bullet_mask.to(DEV))
+    with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
+        ys, hs = trunk.step(*args, engine=SIMT, **kw)   # first: it uses the head of the scratch as data
+        yt, ht = trunk.step(*args, engine=TENSOR, **kw)
+    _status_ok()
+    assert_close(yt, ref_y, "bf16", "y vs oracle")
+    assert_close(ht, ref_h, "bf16", "hidden vs oracle")
+    assert norm_err(yt.cpu(), ys.cpu()) < 1e-2 and norm_err(ht.cpu(), hs.cpu()) < 1e-2
+    with torch.no_grad():
+        trunk.yemong_layers[1].temporal[0].norm2.weight.mul_(1.5)
+        trunk.yemong_layers[0].spatial[0].norm_bullet.weight.mul_(0.5)
+    ref_y2, ref_h2 = O.trunk_step(w.x, w.alive, w.hidden, trunk_params(trunk.cpu()), 4, "bf16", w.bullets, w.bullet_mask)
+    trunk = trunk.to(DEV)
+    with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
+        yt2, ht2 = trunk.step(*args, engine=TENSOR, **kw)
+    assert norm_err(ref_y2, ref_y) > 1e-2          # the change matters
+    assert_close(yt2, ref_y2, "bf16", "y after a gain update")
+    assert_close(ht2, ref_h2, "bf16", "hidden after a gain update")
