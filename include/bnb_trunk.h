@@ -262,7 +262,10 @@ size_t bnb_packed_spatial_bytes(int d_model);
 size_t bnb_packed_temporal_bytes(int d_model);
 
 /* Write the tensor-core image of a sublayer's float32 parameters into `packed`.
- * Re-run after every parameter update; the image is derived data, never saved.
+ * Re-run after every parameter update; the image is derived data, never saved.  It holds the
+ * Linear weights pre-tiled in bf16 with the RMSNorm gains of their inputs multiplied in (and the
+ * decay table of log_lambda), so an update of any parameter of the sublayer, gains included,
+ * needs a new image.
  * No counterpart in the reference (it casts weights per call under autocast). */
 int bnb_pack_spatial(const BnbSpatialWeights* w, int d_model, int n_heads, void* packed, void* stream);
 int bnb_pack_temporal(const BnbTemporalWeights* w, int d_model, void* packed, void* stream);
