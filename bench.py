@@ -41,7 +41,7 @@ FALLBACK_BF16_TFLOPS = 1590.0
 # DRAM bytes per entity token of the fused C2 step, from one ncu capture of k_trunk_tiles on the
 # half-size case (dram__bytes_read.sum + dram__bytes_write.sum = 344 109 824 B for 49 152 tokens);
 # traffic grows in proportion to the tokens, so a full launch is this times its tokens.
-NCU_C2_DRAM_BYTES_PER_TOKEN = 344109824 / 49152
+NCU_C2_DRAM_BYTES_PER_TOKEN = (200308992 + 150321408) / 49152
 
 
 def measured_peaks() -> tuple[float, float, str]:
