@@ -593,7 +593,9 @@ __device__ __forceinline__ void norm_to_A(Ctx& c) {
     ss = h == 0 ? sh : ss + sh;
   }
   c.ss_part[c.part * TILE + c.row] = ss;
-  epi_barrier<NQ>();
+  // only the NQ warps that share these 32 rows exchange partial sums: a barrier of their own
+  // (named barriers 3..6, one per group of 32 rows)
+  asm volatile("bar.sync %0, %1;" ::"r"(3 + ((threadIdx.x >> 5) & 3)), "n"(32 * NQ) : "memory");
   if constexpr (NQ == 2) ss = c.ss_part[c.row] + c.ss_part[TILE + c.row];
   else ss = (c.ss_part[c.row] + c.ss_part[TILE + c.row]) + (c.ss_part[2 * TILE + c.row] + c.ss_part[3 * TILE + c.row]);
   const float inv = rsqrtf(ss * (1.0f / D) + kRmsEps);
