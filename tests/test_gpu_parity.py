@@ -509,3 +509,19 @@ def test_backward_through_the_operators_is_refused_loudly():
             y.sum().backward()
     else:
         assert all(p.grad is None for p in trunk.parameters())
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_long_sequence_does_not_drift(mode):
+    """T = 100 timesteps with resets (three times the length of the recurrent-PPO minibatch): the
+    in-kernel time walk stays within the parity tolerance against the oracle's sequential loop."""
+    from boost_and_broadside_b200 import workloads as W
+
+    trunk = build_trunk([128, 4, 2, 2, 1, 1])
+    w = W.c4(n_envs=5, timesteps=100, seed=91)
+    ref_y, ref_h = O.trunk_sequence(w.x, w.alive, w.hidden, w.done, trunk_params(trunk), 4, mode)
+    trunk = trunk.to(DEV)
+    with torch.no_grad(), autocast_for(mode, DEV):
+        y, h = trunk.sequence(_to(w.x), _to(w.alive), _to(w.hidden), _to(w.done))
+    assert_close(y, ref_y, mode, "T=100 y")
+    assert_close(h, ref_h, mode, "T=100 hidden")
