@@ -399,21 +399,28 @@ def run_ours(args) -> None:
                 ev_out[i].record(s_out)
         return h
 
+    # Three passes of K steps, the median pass reported: the host side of this leg (pinned memory,
+    # PCIe root complex) is shared with the other tenants of the machine, and a single stall of theirs
+    # inside a 20 ms pass would otherwise decide the figure.
+    E2E_PASSES = 3
+    e2e_times = []
     with torch.no_grad(), ctx:
         h = hidden[0]
         h = e2e_loop(max(3, min(args.warmup, 5)), h)
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for st_ in (s_in, s_cmp, s_out):
-            st_.wait_event(e0)
-        h = e2e_loop(args.steps, h)
         cur = torch.cuda.current_stream(dev)
-        for st_ in (s_in, s_cmp, s_out):
-            cur.wait_stream(st_)
-        e1.record()
-        barrier()
-    e2e_ms = e0.elapsed_time(e1)
+        for _ in range(E2E_PASSES):
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for st_ in (s_in, s_cmp, s_out):
+                st_.wait_event(e0)
+            h = e2e_loop(args.steps, h)
+            for st_ in (s_in, s_cmp, s_out):
+                cur.wait_stream(st_)
+            e1.record()
+            barrier()
+            e2e_times.append(e0.elapsed_time(e1))
+    e2e_ms = statistics.median(e2e_times)
 
     t = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
     if dist is not None:
@@ -444,7 +451,7 @@ def run_ours(args) -> None:
             "e2e": {"value": tokens_all * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": x_h.numel() * 4 + alive_h.numel()
                     + (bul_h.numel() * 4 + bmask_h.numel() if has_bullets else 0), "d2h_bytes_per_step": y_h[0].numel() * 4,
-                    "note": "every step: x and alive from pinned host memory, trunk step, y back to pinned host memory; upload, kernels and download pipelined on three streams; hidden state carried on the device"},
+                    "note": "every step: x and alive from pinned host memory, trunk step, y back to pinned host memory; upload, kernels and download pipelined on three streams; hidden state carried on the device; median of 3 passes of K steps", "passes_ms": [round(v, 3) for v in e2e_times]},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
                          "traffic": (NCU_C2_DRAM_BYTES_PER_TOKEN * tokens if args.workload == "C2" and launches == args.steps else None),
