@@ -299,7 +299,12 @@ def run_ours(args) -> None:
     cfg = W.rl_config()
     torch.manual_seed(0)
     trunk = bnb.YemongTrunk(cfg).eval()
-    w = make_workload(args.workload, rank, args.envs_scale)
+    if args.shard and world > 1:
+        from boost_and_broadside_b200 import sharding
+
+        w = sharding.shard_workload(make_workload(args.workload, 0, args.envs_scale), rank, world)
+    else:
+        w = make_workload(args.workload, rank, args.envs_scale)
     n_params = sum(p.numel() for n, p in trunk.named_parameters() if w.bullets is not None or "bullet" not in n)
     trunk = trunk.to(dev)
     engine = {"auto": _capi.ENGINE_AUTO, "simt": _capi.ENGINE_SIMT, "tensor": _capi.ENGINE_TENSOR}[args.engine]
@@ -444,7 +449,8 @@ def run_ours(args) -> None:
         line = {
             "metric": METRIC, "value": tokens_all * args.steps / (total_ms * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "scaling": "strong" if args.shard and world > 1 else "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
             "config": {"workload": WORKLOAD_TEXT[args.workload], "id": args.workload, "engine": args.engine,
                        "tokens_per_step_per_gpu": tokens, "envs_scale": args.envs_scale, "l2": "inputs larger than L2 (no flush)",
                        "weights": "random init, seed 0, rl-fields dims (D=128, 4 heads, S S T | S S T)"},
@@ -480,6 +486,9 @@ def main() -> None:
     ap.add_argument("--workload", default="C2", choices=sorted(WORKLOAD_TEXT))
     ap.add_argument("--engine", default="auto", choices=["auto", "simt", "tensor"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--shard", action="store_true",
+                    help="one global batch, environments sharded contiguously over the ranks (strong scaling) "
+                         "instead of one full batch per rank")
     ap.add_argument("--envs-scale", type=float, default=1.0,
                     help="fraction of the workload's environments (small cases for profiler captures only)")
     args = ap.parse_args()
