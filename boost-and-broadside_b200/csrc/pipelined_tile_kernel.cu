@@ -1,0 +1,903 @@
+// The fused trunk kernel for sm_100a: one CTA per SM walks a tile of 128 token rows (whole
+// environments) through a program of spatial and temporal sublayers, with the residual stream
+// resident in tensor memory and three warp roles that only meet at mbarriers:
+//
+//   16 epilogue warps   four threads per tile row (thread (row, part): TMEM lane = row, a quarter
+//                       of whatever columns are being read).  RMSNorm, q|k|v staging, attention
+//                       (mma.sync), gelu(gate) * up, causal conv, RG-LRU gates and state update.
+//   1 issuing warp      one lane issues every tcgen05.mma.  It waits for "operand ready" (the
+//                       epilogue warps arrive on an mbarrier after fence.proxy.async) and for
+//                       "chunk landed" (the bulk copy's complete_tx), and signals "accumulator
+//                       ready" / "slot free" with tcgen05.commit.
+//   1 fetching warp     one lane streams the pre-tiled weight image through a ring of nine
+//                       16 KB slots with cp.async.bulk, following a static schedule.
+//
+//   TMEM  [0,128)    residual stream, fp32, lane = tile row (out_proj, linear_out and down_proj
+//                    accumulate straight into it)
+//         [128,512)  three 128-column accumulators.  q|k|v of all four heads fill them in one
+//                    round; the GatedMLP runs them as a three-deep pipeline: gate|up of chunk
+//                    c + 3 is issued as soon as chunk c has been read, so the tensor pipe works
+//                    on chunks c + 1 .. c + 3 while the epilogue warps turn chunk c into the bf16
+//                    operand of its down projection.
+//
+//   SMEM  A (32 KB)  normed activations (K-major, 128-byte swizzle); q of all heads during
+//                    attention.   P (2 x 16 KB)  gelu(gate) * up, double buffered; attention
+//                    output; RG-LRU branch.   KV (64 KB)  keys and values of all heads during
+//                    attention, four more ring slots otherwise.   Ring (5 x 16 KB).
+//
+// Every mbarrier wait is bounded: a wait that runs out records a code in the status word, later
+// waits give up at once, and the kernel drains and returns.
+//
+// Reference arithmetic: models/yemong/attention.py:76-169, models/yemong/griffin.py:67-317.
+#include "launch_count.h"
+#include "tensor_common.cuh"
+#include "tensor_kernels.h"
+
+namespace bnb {
+namespace tensor {
+namespace pipe {
+
+constexpr int EPI_WARPS = 16;
+constexpr int EPI_THREADS = 32 * EPI_WARPS;
+constexpr int MMA_WARP = EPI_WARPS;
+constexpr int LOAD_WARP = EPI_WARPS + 1;
+constexpr int THREADS = EPI_THREADS + 64;
+constexpr int N_DEDICATED = 5;            // ring slots that are never anything else
+constexpr int N_SLOTS = N_DEDICATED + 4;  // + the key/value staging area while no attention runs
+
+constexpr int OFF_A = 0;
+constexpr int OFF_P = 32768;
+constexpr int OFF_KV = 65536;
+constexpr int OFF_RING = 131072;
+constexpr int OFF_META = OFF_RING + N_DEDICATED * CHUNK_BYTES;  // env_first[128], env_n[128], alive[128], items[128]
+constexpr int OFF_ROWINFO = OFF_META + 512;                     // hidden row of each tile row (int), then flags[128]
+constexpr int OFF_SS = OFF_ROWINFO + 640;                       // partial sums of squares [4][128]
+constexpr int OFF_BAR = OFF_SS + 2048;
+constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+
+// mbarrier indices
+enum : int { B_OP0 = 0, B_OP1, B_ACC0, B_ACC1, B_ACC2, B_PF0, B_PF1, B_KVREL, B_FULL0, B_FREE0 = B_FULL0 + N_SLOTS, B_COUNT = B_FREE0 + N_SLOTS };
+static_assert(B_COUNT * 8 + 8 <= 256, "barrier area");
+
+constexpr uint32_t COL_RESID = 0;
+constexpr uint32_t COL_ACC0 = 128, COL_ACC1 = 256, COL_ACC2 = 384;
+constexpr uint32_t TMEM_COLS = 512;
+
+enum : int { ST_TIMEOUT_FULL = 101, ST_TIMEOUT_FREE = 102, ST_TIMEOUT_ACC = 103, ST_TIMEOUT_OPERAND = 104 };
+
+// schedule entry: slot (4 bits) | sublayer (3) | chunk (6) | wait for the key/value area first (1)
+__device__ __forceinline__ uint16_t sched_entry(int slot, int si, int ch, bool kvwait) {
+  return (uint16_t)(slot | (si << 4) | (ch << 7) | (kvwait ? 1 << 13 : 0));
+}
+constexpr int MAX_SCHED = MAX_SUBLAYERS * N_TEMPORAL_CHUNKS;
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Chunks of a sublayer's image in the order the issuing warp consumes them.
+// GatedMLP with base b: gate|up of chunk c is b + 3c (+1), its down projection b + 3c + 2; the
+// three-deep pipeline consumes GU0 GU1 GU2 D0 GU3 D1 GU4 ... GU7 D5 D6 D7.
+__device__ __forceinline__ int ffn_order(int base, int i) {
+  if (i < 6) return base + 3 * (i >> 1) + (i & 1);
+  i -= 6;                       // then 5 groups of (D(c), GU(c+3) a, b), c = 0..4, then D5, D6, D7
+  if (i < 15) {
+    const int c = i / 3, j = i % 3;
+    return j == 0 ? base + 3 * c + 2 : base + 3 * (c + 3) + (j - 1);
+  }
+  return base + 3 * (i - 15 + 5) + 2;
+}
+__device__ __forceinline__ int build_schedule(const SubLayer* subs, int n_sub, bool has_fields, uint16_t* out) {
+  int n = 0, rr = 0;
+  for (int si = 0; si < n_sub; ++si) {
+    if (subs[si].type == SUB_SPATIAL) {
+      for (int h = 0; h < HEADS; ++h)
+        for (int kh = 0; kh < 2; ++kh) {
+          out[n++] = sched_entry(rr, si, 5 * (h >> 1) + 2 * (h & 1) + kh, false);
+          rr = rr + 1 == N_SLOTS ? 0 : rr + 1;
+        }
+      // fetched while the attention runs: dedicated slots only
+      out[n++] = sched_entry(0, si, 4, false);
+      out[n++] = sched_entry(1, si, 9, false);
+      for (int i = 0; i < 3; ++i) out[n++] = sched_entry(2 + i, si, ffn_order(10, i), false);
+      rr = N_DEDICATED;
+      for (int i = 3; i < 24; ++i) {
+        out[n++] = sched_entry(rr, si, ffn_order(10, i), i == 3);
+        rr = rr + 1 == N_SLOTS ? 0 : rr + 1;
+      }
+    } else {
+      for (int i = 0; i < 12 + 24; ++i) {
+        const int ch = i < 12 ? i : ffn_order(12, i - 12);
+        if (!has_fields && (ch == 8 || ch == 9)) continue;
+        out[n++] = sched_entry(rr, si, ch, false);
+        rr = rr + 1 == N_SLOTS ? 0 : rr + 1;
+      }
+    }
+  }
+  return n;
+}
+
+__device__ __forceinline__ uint32_t slot_offset(uint32_t slot) {
+  return slot < N_DEDICATED ? OFF_RING + slot * CHUNK_BYTES : OFF_KV + (slot - N_DEDICATED) * CHUNK_BYTES;
+}
+
+// ------------------------------------------------------------------ epilogue side
+
+struct Epi {
+  uint8_t* smem;
+  uint32_t sbase;       // shared address of smem
+  uint32_t bars;        // shared address of the barrier array
+  uint32_t lane_addr;   // tensor-memory address of this thread's lane, column 0
+  uint32_t par;         // phase bits: ACC0..2 -> bits 0..2, PF0..1 -> bits 3, 4
+  int row, part;
+  int* status;
+  volatile int* aborted;
+  float* ss_part;
+};
+
+// "My share of the operand is written and my reads of the accumulator are done."
+__device__ __forceinline__ void post(const Epi& e, int bar) {
+  fence_proxy_async();
+  tc_fence_before();
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(e.bars + 8 * bar);
+}
+__device__ __forceinline__ void wait_commit(Epi& e, int bar, int bit) {
+  mbar_wait(e.bars + 8 * bar, (e.par >> bit) & 1u, e.status, e.aborted, ST_TIMEOUT_ACC);
+  e.par ^= 1u << bit;
+  tc_fence_after();
+}
+__device__ __forceinline__ void wait_acc(Epi& e, int i) { wait_commit(e, B_ACC0 + i, i); }
+__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory"); }
+
+// residual (TMEM) -> x * rsqrt(mean x^2 + eps) -> bf16 A operand (the RMSNorm gain is in the weights)
+__device__ __forceinline__ void norm_to_A(Epi& e) {
+  uint32_t v[32];
+  tmem_ld32(e.lane_addr + COL_RESID + e.part * 32, v);
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const float a = __uint_as_float(v[i]);
+    ss = fmaf(a, a, ss);
+  }
+  e.ss_part[e.part * TILE + e.row] = ss;
+  // the four warps that share these 32 rows exchange partial sums (named barriers 3..6)
+  asm volatile("bar.sync %0, 128;" ::"r"(3 + ((threadIdx.x >> 5) & 3)) : "memory");
+  ss = (e.ss_part[e.row] + e.ss_part[TILE + e.row]) + (e.ss_part[2 * TILE + e.row] + e.ss_part[3 * TILE + e.row]);
+  const float inv = rsqrtf(ss * (1.0f / D) + kRmsEps);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int col = e.part * 32 + q * 8;
+    const uint32_t* s = &v[q * 8];
+    uint4 o;
+    o.x = pack_bf16(__uint_as_float(s[0]) * inv, __uint_as_float(s[1]) * inv);
+    o.y = pack_bf16(__uint_as_float(s[2]) * inv, __uint_as_float(s[3]) * inv);
+    o.z = pack_bf16(__uint_as_float(s[4]) * inv, __uint_as_float(s[5]) * inv);
+    o.w = pack_bf16(__uint_as_float(s[6]) * inv, __uint_as_float(s[7]) * inv);
+    *reinterpret_cast<uint4*>(e.smem + OFF_A + (col >> 6) * CHUNK_BYTES + swz(e.row, (col & 63) >> 3)) = o;
+  }
+  // the partial sums are read again by the next norm only after at least one full barrier
+}
+
+__device__ __forceinline__ uint4 pack8(const uint32_t* s) {
+  return make_uint4(pack_bf16(__uint_as_float(s[0]), __uint_as_float(s[1])), pack_bf16(__uint_as_float(s[2]), __uint_as_float(s[3])),
+                    pack_bf16(__uint_as_float(s[4]), __uint_as_float(s[5])), pack_bf16(__uint_as_float(s[6]), __uint_as_float(s[7])));
+}
+
+// GatedMLP on the A operand (already normed and posted on OP0): residual += down(gelu(gate) * up).
+// Chunk c: gate = acc[c % 3][0,64), up = acc[c % 3][64,128); this thread: hidden columns
+// [16 part, 16 part + 16) of the chunk.
+__device__ __forceinline__ void ffn(Epi& e) {
+#pragma unroll 1
+  for (int c = 0; c < 8; ++c) {
+    const int ai = c % 3, pi = c & 1;
+    wait_acc(e, ai);
+    uint32_t gv[16], uv[16];
+    const uint32_t acc = e.lane_addr + COL_ACC0 + ai * 128 + e.part * 16;
+    tmem_ld16_nowait(acc, gv);
+    tmem_ld16_nowait(acc + 64, uv);
+    tmem_wait_ld();
+    uint4 o[2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        w[j] = gelu_mul_bf16x2(__uint_as_float(gv[q * 8 + 2 * j]), __uint_as_float(gv[q * 8 + 2 * j + 1]),
+                               __uint_as_float(uv[q * 8 + 2 * j]), __uint_as_float(uv[q * 8 + 2 * j + 1]));
+      o[q] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    // the down projection of chunk c - 2 has read this buffer
+    if (c >= 2) wait_commit(e, B_PF0 + pi, 3 + pi);
+#pragma unroll
+    for (int q = 0; q < 2; ++q)
+      *reinterpret_cast<uint4*>(e.smem + OFF_P + pi * CHUNK_BYTES + swz(e.row, e.part * 2 + q)) = o[q];
+    post(e, B_OP0 + pi);
+  }
+  // residual complete: the down projections of chunks 6 and 7
+  wait_commit(e, B_PF0, 3);
+  wait_commit(e, B_PF1, 4);
+}
+
+// Attention of every head and environment of the tile from the staged q (A area), k and v (KV
+// area), all in the swizzled operand layout (128 rows x 64 bf16 atoms; head h sits in atom h / 2,
+// columns 32 (h % 2) ..).  Warp w serves head w % 4 and every fourth block of 16 query rows;
+// keys are walked in blocks of 16 with a running maximum.  Output: bf16 into the P area as the
+// A operand of out_proj.
+__device__ __forceinline__ void attention(const Epi& e, int n_items) {
+  const uint8_t* meta = e.smem + OFF_META;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int h = warp & 3;
+  const uint32_t atom = (uint32_t)(h >> 1) * CHUNK_BYTES;
+  const int c8h = (h & 1) * 4;
+  const uint32_t sQ = e.sbase + OFF_A + atom, sK = e.sbase + OFF_KV + atom, sV = sK + 2 * CHUNK_BYTES;
+  const float scale = 0.17677669529663687f;  // 1/sqrt(32)
+  for (int it = warp >> 2; it < n_items; it += EPI_WARPS / 4) {
+    const int r0 = meta[384 + it];
+    const int e0 = meta[r0], n = meta[128 + r0] + 1;   // first tile row and size of the environment
+    const int last = e0 + n - 1;
+    uint32_t qa[2][4];
+    {
+      const int row = min(r0 + (lane & 7) + ((lane >> 3) & 1) * 8, last);
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks)
+        ldsm_x4(sQ + swz(row, c8h + ks * 2 + (lane >> 4)), qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3]);
+    }
+    const int nkb = (n + 15) >> 4;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    float acc[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
+#pragma unroll 1
+    for (int kb = 0; kb < nkb; ++kb) {
+      float sc[2][4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sc[nt][i] = 0.f;
+      const int krow = min(e0 + kb * 16 + (lane >> 4) * 8 + (lane & 7), last);
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(sK + swz(krow, c8h + ks * 2 + ((lane >> 3) & 1)), b0, b1, b2, b3);
+        mma_bf16(sc[0], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+        mma_bf16(sc[1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b2, b3);
+      }
+      float bm0 = -INFINITY, bm1 = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int j = kb * 16 + nt * 8 + 2 * t + i;
+          const bool valid = j < n;
+          const bool lv = valid && meta[256 + e0 + j];
+          // a dead key scores kMaskedScore (weight exactly 0 unless every key is dead: then uniform)
+          const float a = valid ? (lv ? sc[nt][i] * scale : kMaskedScore) : -INFINITY;
+          const float b = valid ? (lv ? sc[nt][2 + i] * scale : kMaskedScore) : -INFINITY;
+          sc[nt][i] = a;
+          sc[nt][2 + i] = b;
+          bm0 = fmaxf(bm0, a);
+          bm1 = fmaxf(bm1, b);
+        }
+      bm0 = fmaxf(bm0, __shfl_xor_sync(0xffffffffu, bm0, 1));
+      bm0 = fmaxf(bm0, __shfl_xor_sync(0xffffffffu, bm0, 2));
+      bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, 1));
+      bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, 2));
+      const float n0 = fmaxf(m0, bm0), n1 = fmaxf(m1, bm1);   // finite: every block holds a valid key
+      const float c0 = __expf(m0 - n0), c1 = __expf(m1 - n1); // exp(-inf) = 0 on the first block
+      m0 = n0;
+      m1 = n1;
+      l0 *= c0;
+      l1 *= c1;
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        acc[nt][0] *= c0; acc[nt][1] *= c0;
+        acc[nt][2] *= c1; acc[nt][3] *= c1;
+      }
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const float a = __expf(sc[nt][i] - m0), b = __expf(sc[nt][2 + i] - m1);
+          sc[nt][i] = a;
+          sc[nt][2 + i] = b;
+          l0 += a;
+          l1 += b;
+        }
+      const uint32_t a0 = pack_bf16(sc[0][0], sc[0][1]), a1 = pack_bf16(sc[0][2], sc[0][3]);
+      const uint32_t a2 = pack_bf16(sc[1][0], sc[1][1]), a3 = pack_bf16(sc[1][2], sc[1][3]);
+      const int vrow = min(e0 + kb * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), last);
+#pragma unroll
+      for (int np = 0; np < 2; ++np) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(sV + swz(vrow, c8h + np * 2 + (lane >> 4)), b0, b1, b2, b3);
+        mma_bf16(acc[np * 2], a0, a1, a2, a3, b0, b1);
+        mma_bf16(acc[np * 2 + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float i0 = 1.0f / l0, i1 = 1.0f / l1;
+    const int q0 = r0 + g, q1 = r0 + g + 8;
+    uint8_t* po = e.smem + OFF_P + atom;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      if (q0 <= last) *reinterpret_cast<uint32_t*>(po + swz(q0, c8h + nt) + t * 4) = pack_bf16(acc[nt][0] * i0, acc[nt][1] * i0);
+      if (q1 <= last) *reinterpret_cast<uint32_t*>(po + swz(q1, c8h + nt) + t * 4) = pack_bf16(acc[nt][2] * i1, acc[nt][3] * i1);
+    }
+  }
+}
+
+__device__ __forceinline__ void run_spatial(Epi& e, int n_items, bool row_valid) {
+  norm_to_A(e);
+  post(e, B_OP0);
+  wait_acc(e, 0);   // q|k|v of head h in columns [128 + 96 h, +96)
+  {
+    // this thread stages head `part` of its row: q into the A area (the normed operand has been
+    // consumed), k and v into the KV area, all in the swizzled atom layout
+    const int h = e.part;
+    const uint32_t atom = (uint32_t)(h >> 1) * CHUNK_BYTES;
+    const int c8h = (h & 1) * 4;
+    const uint32_t dst[3] = {OFF_A + atom, OFF_KV + atom, OFF_KV + 2 * CHUNK_BYTES + atom};
+#pragma unroll
+    for (int p = 0; p < 3; ++p) {
+      uint32_t v[32];
+      tmem_ld32(e.lane_addr + COL_ACC0 + h * 96 + p * 32, v);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(e.smem + dst[p] + swz(e.row, c8h + q)) = pack8(&v[q * 8]);
+    }
+    if (!row_valid) {
+      // rows outside every environment contribute a zero operand row to out_proj
+#pragma unroll
+      for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(e.smem + OFF_P + atom + swz(e.row, c8h + q)) = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+  tc_fence_before();
+  epi_sync();
+  attention(e, n_items);
+  // keys and values are dead: the area may take weight chunks again
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(e.bars + 8 * B_KVREL);
+  post(e, B_OP0);   // attention output in P
+  wait_acc(e, 0);   // out_proj accumulated into the residual
+  norm_to_A(e);
+  post(e, B_OP0);
+  ffn(e);
+}
+
+struct RowState {
+  int hrow;        // row of the packed hidden state, -1 for field / invalid rows
+  int lag_ok;      // stored conv lags still inside the current episode (0..3)
+  bool zero_in;    // incoming state taken as zero (reset_env)
+};
+
+// One temporal sublayer on the tile at one timestep.  In the gate epilogue thread (row, part)
+// works on hidden columns [64 rnd + 16 part, +16), and parks b2 for exactly those.
+__device__ __forceinline__ void run_temporal(Epi& e, const SubLayer& s, const RowState& rs, bool is_field, bool boundary,
+                                             bool has_fields, const float* hid_in) {
+  const bool is_ship = rs.hrow >= 0;
+  norm_to_A(e);
+  post(e, B_OP0);
+  wait_acc(e, 0);   // acc0 = linear2 n, acc1 = linear1 n
+  // b2 = bf16(gelu(linear2 n)) for this thread's columns, parked as packed bf16 pairs
+  uint32_t b2p[2][8];
+#pragma unroll
+  for (int rnd = 0; rnd < 2; ++rnd) {
+    uint32_t v[16];
+    tmem_ld16_nowait(e.lane_addr + COL_ACC0 + rnd * 64 + e.part * 16, v);
+    tmem_wait_ld();
+#pragma unroll
+    for (int j = 0; j < 8; ++j) b2p[rnd][j] = pack_bf16(gelu_fast(__uint_as_float(v[2 * j])), gelu_fast(__uint_as_float(v[2 * j + 1])));
+  }
+  // b1 = bf16(linear1 n) into the A operand; ships: causal conv with the stored taps -> u
+  {
+    uint32_t v[32];
+    tmem_ld32(e.lane_addr + COL_ACC1 + e.part * 32, v);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int col = e.part * 32 + q * 8;
+      *reinterpret_cast<uint4*>(e.smem + OFF_A + (col >> 6) * CHUNK_BYTES + swz(e.row, (col & 63) >> 3)) = pack8(&v[q * 8]);
+    }
+  }
+  tc_fence_before();
+  epi_sync();
+  const float* hin = is_ship ? hid_in + (size_t)rs.hrow * 4 * D : nullptr;
+  float* hout = is_ship ? s.hid_out + (size_t)rs.hrow * 4 * D : nullptr;
+  // Causal conv, one warp per ship row and four columns per lane, so that the stored taps are
+  // read and written as whole 512-byte rows.  u = bias + w0 tap0 + w1 tap1 + w2 tap2 + w3 b1,
+  // summed in the reference's order; new taps = (tap1, tap2, b1); bf16(u) replaces b1 in A.
+  {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int col = lane * 4;
+    float cw[4][4], cb[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 w4 = __ldg(reinterpret_cast<const float4*>(s.conv_w + (col + i) * 4));
+      cw[i][0] = w4.x; cw[i][1] = w4.y; cw[i][2] = w4.z; cw[i][3] = w4.w;
+      cb[i] = __ldg(s.conv_b + col + i);
+    }
+    const int* row_hrow = reinterpret_cast<const int*>(e.smem + OFF_ROWINFO);
+    const uint8_t* row_flags = e.smem + OFF_ROWINFO + 512;
+    // Four rows at a time: all loads of the group are issued before any store, because the
+    // state may be updated in place and the compiler must otherwise keep loads behind stores.
+#pragma unroll 1
+    for (int r0 = warp; r0 < TILE; r0 += 4 * EPI_WARPS) {
+      float4 t0[4], t1[4], t2[4];
+      uint2 bw[4];
+      int hr[4], lag[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int r = r0 + EPI_WARPS * k;
+        hr[k] = row_hrow[r];
+        const int flags = row_flags[r];
+        lag[k] = flags & 3;
+        t0[k] = t1[k] = t2[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        bw[k] = make_uint2(0u, 0u);
+        if (hr[k] >= 0) {
+          if (!(flags & 4)) {
+            const float* hi = hid_in + (size_t)hr[k] * 4 * D + col;
+            t0[k] = *reinterpret_cast<const float4*>(hi + D);
+            t1[k] = *reinterpret_cast<const float4*>(hi + 2 * D);
+            t2[k] = *reinterpret_cast<const float4*>(hi + 3 * D);
+          }
+          bw[k] = *reinterpret_cast<const uint2*>(e.smem + OFF_A + (lane >> 4) * CHUNK_BYTES + swz(r, (lane & 15) >> 1) + (lane & 1) * 8);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (hr[k] < 0) continue;
+        const int r = r0 + EPI_WARPS * k;
+        float* ho = s.hid_out + (size_t)hr[k] * 4 * D + col;
+        const float b1[4] = {bf16_lo(bw[k].x), bf16_hi(bw[k].x), bf16_lo(bw[k].y), bf16_hi(bw[k].y)};
+        *reinterpret_cast<float4*>(ho + D) = t1[k];
+        *reinterpret_cast<float4*>(ho + 2 * D) = t2[k];
+        *reinterpret_cast<float4*>(ho + 3 * D) = make_float4(b1[0], b1[1], b1[2], b1[3]);
+        const float a0[4] = {t0[k].x, t0[k].y, t0[k].z, t0[k].w}, a1[4] = {t1[k].x, t1[k].y, t1[k].z, t1[k].w},
+                    a2[4] = {t2[k].x, t2[k].y, t2[k].z, t2[k].w};
+        float u[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float p0 = lag[k] >= 3 ? __fmul_rn(a0[i], cw[i][0]) : 0.f;
+          const float p1 = lag[k] >= 2 ? __fmul_rn(a1[i], cw[i][1]) : 0.f;
+          const float p2 = lag[k] >= 1 ? __fmul_rn(a2[i], cw[i][2]) : 0.f;
+          const float p3 = __fmul_rn(b1[i], cw[i][3]);
+          u[i] = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(p0, p1), p2), p3), cb[i]);
+        }
+        *reinterpret_cast<uint2*>(e.smem + OFF_A + (lane >> 4) * CHUNK_BYTES + swz(r, (lane & 15) >> 1) + (lane & 1) * 8) =
+            make_uint2(pack_bf16(u[0], u[1]), pack_bf16(u[2], u[3]));
+      }
+    }
+  }
+  post(e, B_OP0);   // A = u (ship rows) / b1 (field rows)
+  // previous state of this thread's columns of the first half, requested before the gates arrive
+  float4 hprev[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    hprev[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (is_ship && !rs.zero_in) hprev[q] = *reinterpret_cast<const float4*>(hin + e.part * 16 + q * 4);
+  }
+  wait_acc(e, 0);   // acc0 / acc1 = [W_a u | W_x u] of hidden columns [0,64) / [64,128); acc2 = field_sub b1
+  // gates and state update
+#pragma unroll
+  for (int rnd = 0; rnd < 2; ++rnd) {
+    uint32_t rv[16], iv[16];
+    const uint32_t acc = e.lane_addr + COL_ACC0 + rnd * 128 + e.part * 16;
+    tmem_ld16_nowait(acc, rv);        // executed by every lane of the warp
+    tmem_ld16_nowait(acc + 64, iv);
+    tmem_wait_ld();
+    float4 hnext[4];
+    if (rnd == 0) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        hnext[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (is_ship && !rs.zero_in) hnext[q] = *reinterpret_cast<const float4*>(hin + 64 + e.part * 16 + q * 4);
+      }
+    }
+    if (is_ship) {
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int col = rnd * 64 + e.part * 16 + q * 8;
+        // u (bf16) back from the A operand (K atom rnd)
+        uint8_t* ua = e.smem + OFF_A + rnd * CHUNK_BYTES + swz(e.row, e.part * 2 + q);
+        const uint4 ub = *reinterpret_cast<const uint4*>(ua);
+        const uint32_t uw[4] = {ub.x, ub.y, ub.z, ub.w};
+        uint32_t ob[4];
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const int cc = col + hf * 4;
+          const float4 hv = hprev[q * 2 + hf];
+          const float4 ab = __ldg(reinterpret_cast<const float4*>(s.a_b + cc));
+          const float4 xb = __ldg(reinterpret_cast<const float4*>(s.x_b + cc));
+          const float4 dl = __ldg(reinterpret_cast<const float4*>(s.decay_log2 + cc));
+          const float abv[4] = {ab.x, ab.y, ab.z, ab.w}, xbv[4] = {xb.x, xb.y, xb.z, xb.w}, dlv[4] = {dl.x, dl.y, dl.z, dl.w};
+          float hn[4] = {hv.x, hv.y, hv.z, hv.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int k = q * 8 + hf * 4 + i;
+            const float rg = round_bf16(sigmoid_fast(__uint_as_float(rv[k]) + abv[i]));
+            const float ig = round_bf16(sigmoid_fast(__uint_as_float(iv[k]) + xbv[i]));
+            // sigmoid(Lambda)^(8 r) = 2^(r * 8 log2 sigmoid(Lambda)); the table is part of the weight image
+            float a = ex2_fast(rg * dlv[i]);
+            const float gate = sqrt_fast(fmaxf((1.0f - a) * (1.0f + a), kGateFloor));
+            const uint32_t uword = uw[hf * 2 + (i >> 1)];
+            const float uu = (i & 1) ? bf16_hi(uword) : bf16_lo(uword);
+            const float bb = gate * (ig * uu);
+            if (boundary) a = 0.f;
+            hn[i] = fmaf(a, hn[i], bb);
+          }
+          *reinterpret_cast<float4*>(hout + cc) = make_float4(hn[0], hn[1], hn[2], hn[3]);
+          const int bi = q * 4 + hf * 2;
+          ob[hf * 2] = pack_bf16(hn[0] * bf16_lo(b2p[rnd][bi]), hn[1] * bf16_hi(b2p[rnd][bi]));
+          ob[hf * 2 + 1] = pack_bf16(hn[2] * bf16_lo(b2p[rnd][bi + 1]), hn[3] * bf16_hi(b2p[rnd][bi + 1]));
+        }
+        // branch operand of linear_out: K atom 0 lives in P0, K atom 1 in place in A
+        uint8_t* dst = rnd == 0 ? e.smem + OFF_P + swz(e.row, e.part * 2 + q) : ua;
+        *reinterpret_cast<uint4*>(dst) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+      }
+    }
+    if (rnd == 0) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) hprev[q] = hnext[q];
+    }
+  }
+  if (has_fields) {
+    // field rows: branch = bf16(bf16(field_sub b1) * b2)
+#pragma unroll
+    for (int rnd = 0; rnd < 2; ++rnd) {
+      uint32_t v[16];
+      tmem_ld16_nowait(e.lane_addr + COL_ACC2 + rnd * 64 + e.part * 16, v);        // executed by every lane of the warp
+      tmem_wait_ld();
+      if (!is_ship) {
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          uint32_t ob[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int bi = q * 4 + j;
+            const float f0 = is_field ? round_bf16(__uint_as_float(v[q * 8 + 2 * j])) * bf16_lo(b2p[rnd][bi]) : 0.f;
+            const float f1 = is_field ? round_bf16(__uint_as_float(v[q * 8 + 2 * j + 1])) * bf16_hi(b2p[rnd][bi]) : 0.f;
+            ob[j] = pack_bf16(f0, f1);
+          }
+          uint8_t* dst = rnd == 0 ? e.smem + OFF_P + swz(e.row, e.part * 2 + q)
+                                  : e.smem + OFF_A + CHUNK_BYTES + swz(e.row, e.part * 2 + q);
+          *reinterpret_cast<uint4*>(dst) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+        }
+      }
+    }
+  } else if (!is_ship) {
+    // rows outside every environment: zero operand rows
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      *reinterpret_cast<uint4*>(e.smem + OFF_P + swz(e.row, e.part * 2 + q)) = make_uint4(0u, 0u, 0u, 0u);
+      *reinterpret_cast<uint4*>(e.smem + OFF_A + CHUNK_BYTES + swz(e.row, e.part * 2 + q)) = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+  post(e, B_OP0);   // branch operand
+  wait_acc(e, 0);   // residual += linear_out(branch)
+  norm_to_A(e);
+  post(e, B_OP0);
+  ffn(e);
+}
+
+// ------------------------------------------------------------------ issuing side (one lane)
+
+struct Issuer {
+  uint32_t sbase, bars, tmem;
+  uint32_t full_par;   // per-slot phase bits of the full barriers
+  uint32_t op_par;     // phase bits of OP0, OP1
+  const uint16_t* sched;
+  int sched_len, idx;
+  int* status;
+  volatile int* aborted;
+};
+
+__device__ __forceinline__ void wait_operand(Issuer& m, int i) {
+  mbar_wait(m.bars + 8 * (B_OP0 + i), (m.op_par >> i) & 1u, m.status, m.aborted, ST_TIMEOUT_OPERAND);
+  m.op_par ^= 1u << i;
+  tc_fence_after();
+}
+// D[128 x n] (+)= A[128 x 64] * W[n x 64]^T with the next weight chunk of the schedule.
+__device__ __forceinline__ void issue_chunk(Issuer& m, uint32_t a_off, uint32_t n, uint32_t d_col, uint32_t accumulate) {
+  const uint32_t slot = m.sched[m.idx] & 15u;
+  m.idx = m.idx + 1 == m.sched_len ? 0 : m.idx + 1;
+  mbar_wait(m.bars + 8 * (B_FULL0 + slot), (m.full_par >> slot) & 1u, m.status, m.aborted, ST_TIMEOUT_FULL);
+  m.full_par ^= 1u << slot;
+  tc_fence_after();
+  const uint32_t a_addr = m.sbase + a_off, b_addr = m.sbase + slot_offset(slot);
+  const uint32_t idesc = instr_desc(n);
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+    tc_mma(m.tmem + d_col, smem_desc(a_addr + k * 32), smem_desc(b_addr + k * 32), idesc, (accumulate | (uint32_t)k) ? 1u : 0u);
+  tc_commit(m.bars + 8 * (B_FREE0 + slot));
+}
+__device__ __forceinline__ void issue_pair(Issuer& m, uint32_t a_off, uint32_t n, uint32_t d_col) {
+  issue_chunk(m, a_off, n, d_col, 0);
+  issue_chunk(m, a_off + CHUNK_BYTES, n, d_col, 1);
+}
+__device__ __forceinline__ void commit(const Issuer& m, int bar) { tc_commit(m.bars + 8 * bar); }
+
+__device__ __forceinline__ void issue_ffn(Issuer& m) {
+  wait_operand(m, 0);
+#pragma unroll 1
+  for (int c = 0; c < 3; ++c) {
+    issue_pair(m, OFF_A, 128, COL_ACC0 + 128 * c);
+    commit(m, B_ACC0 + c);
+  }
+#pragma unroll 1
+  for (int c = 0; c < 8; ++c) {
+    wait_operand(m, c & 1);   // product of chunk c written, accumulator c % 3 read
+    issue_chunk(m, OFF_P + (c & 1) * CHUNK_BYTES, 128, COL_RESID, 1);
+    commit(m, B_PF0 + (c & 1));
+    if (c + 3 < 8) {
+      issue_pair(m, OFF_A, 128, COL_ACC0 + 128 * (c % 3));
+      commit(m, B_ACC0 + c % 3);
+    }
+  }
+}
+__device__ __forceinline__ void issue_spatial(Issuer& m) {
+  wait_operand(m, 0);
+#pragma unroll 1
+  for (int h = 0; h < HEADS; ++h) issue_pair(m, OFF_A, 96, COL_ACC0 + 96 * h);
+  commit(m, B_ACC0);
+  wait_operand(m, 0);   // attention output: K atom 0 = heads 0, 1; K atom 1 = heads 2, 3
+  issue_chunk(m, OFF_P, 128, COL_RESID, 1);
+  issue_chunk(m, OFF_P + CHUNK_BYTES, 128, COL_RESID, 1);
+  commit(m, B_ACC0);
+  issue_ffn(m);
+}
+__device__ __forceinline__ void issue_temporal(Issuer& m, bool has_fields) {
+  wait_operand(m, 0);
+  issue_pair(m, OFF_A, 128, COL_ACC0);   // linear2
+  issue_pair(m, OFF_A, 128, COL_ACC1);   // linear1
+  commit(m, B_ACC0);
+  wait_operand(m, 0);
+  issue_pair(m, OFF_A, 128, COL_ACC0);   // gates of hidden columns [0,64)
+  issue_pair(m, OFF_A, 128, COL_ACC1);   // gates of hidden columns [64,128)
+  if (has_fields) issue_pair(m, OFF_A, 128, COL_ACC2);   // field_sub
+  commit(m, B_ACC0);
+  wait_operand(m, 0);
+  issue_chunk(m, OFF_P, 128, COL_RESID, 1);                 // linear_out, K atom 0
+  issue_chunk(m, OFF_A + CHUNK_BYTES, 128, COL_RESID, 1);   // K atom 1
+  commit(m, B_ACC0);
+  issue_ffn(m);
+}
+
+// ------------------------------------------------------------------ the kernel
+
+__global__ void __launch_bounds__(THREADS, 1) k_trunk_pipelined(const __grid_constant__ TrunkArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ int s_aborted;
+  __shared__ int s_items;
+  __shared__ SubLayer s_sub[MAX_SUBLAYERS];  // kernel parameters are slow to index dynamically
+  __shared__ uint16_t s_sched[MAX_SCHED];
+  __shared__ int s_sched_len;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid < args.n_sub) s_sub[tid] = args.sub[tid];
+  if (tid == 32) s_sched_len = build_schedule(args.sub, args.n_sub, args.has_fields != 0, s_sched);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_BAR + 8 * B_COUNT);
+  if (tid == 0) {
+    s_aborted = (*args.status != 0) ? 1 : 0;
+    mbar_init(smem_u32(&bars[B_OP0]), EPI_WARPS);
+    mbar_init(smem_u32(&bars[B_OP1]), EPI_WARPS);
+    mbar_init(smem_u32(&bars[B_KVREL]), EPI_WARPS);
+    for (int i = B_ACC0; i <= B_PF1; ++i) mbar_init(smem_u32(&bars[i]), 1);
+    for (int i = B_FULL0; i < B_COUNT; ++i) mbar_init(smem_u32(&bars[i]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    __syncwarp();
+    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int my_tiles = blockIdx.x < args.n_tiles ? (args.n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const int passes = my_tiles * args.t_loop;
+
+  if (warp == LOAD_WARP) {
+    // ---------------------------------------------------------------- weight stream
+    if ((tid & 31) == 0) {
+      const uint32_t sbase = smem_u32(smem), bar0 = smem_u32(bars);
+      uint32_t free_par = (1u << N_SLOTS) - 1u;   // a fresh barrier passes a wait on parity 1: every slot starts free
+      uint32_t kv_par = 0;
+      const int len = s_sched_len;
+      for (int pass = 0; pass < passes; ++pass)
+        for (int i = 0; i < len; ++i) {
+          const uint32_t en = s_sched[i];
+          const uint32_t slot = en & 15u;
+          if (en & (1u << 13)) {
+            mbar_wait(bar0 + 8 * B_KVREL, kv_par, args.status, &s_aborted, ST_TIMEOUT_FREE);
+            kv_par ^= 1u;
+          }
+          mbar_wait(bar0 + 8 * (B_FREE0 + slot), (free_par >> slot) & 1u, args.status, &s_aborted, ST_TIMEOUT_FREE);
+          free_par ^= 1u << slot;
+          const uint32_t full = bar0 + 8 * (B_FULL0 + slot);
+          mbar_expect_tx(full, CHUNK_BYTES);
+          bulk_g2s(sbase + slot_offset(slot), s_sub[(en >> 4) & 7u].packed + (size_t)((en >> 7) & 63u) * CHUNK_BYTES, CHUNK_BYTES, full);
+        }
+    }
+  } else if (warp == MMA_WARP) {
+    // ---------------------------------------------------------------- tensor-core issue
+    if ((tid & 31) == 0) {
+      Issuer m;
+      m.sbase = smem_u32(smem);
+      m.bars = smem_u32(bars);
+      m.tmem = tmem_base;
+      m.full_par = 0;
+      m.op_par = 0;
+      m.sched = s_sched;
+      m.sched_len = s_sched_len;
+      m.idx = 0;
+      m.status = args.status;
+      m.aborted = &s_aborted;
+      for (int pass = 0; pass < passes; ++pass)
+        for (int si = 0; si < args.n_sub; ++si) {
+          if (s_sub[si].type == SUB_SPATIAL) issue_spatial(m);
+          else issue_temporal(m, args.has_fields != 0);
+        }
+    }
+  } else {
+    // ---------------------------------------------------------------- tile owners
+    Epi e;
+    e.smem = smem;
+    e.sbase = smem_u32(smem);
+    e.bars = smem_u32(bars);
+    e.row = tid & (TILE - 1);
+    e.part = tid >> 7;
+    e.lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    e.par = 0;
+    e.status = args.status;
+    e.aborted = &s_aborted;
+    e.ss_part = reinterpret_cast<float*>(smem + OFF_SS);
+    uint8_t* meta = smem + OFF_META;
+    const EnvMap& map = args.map;
+    const int NM = map.tokens_per_env;
+    const int row = e.row;
+
+    for (int tile = blockIdx.x; tile < args.n_tiles; tile += gridDim.x) {
+      // ---- rows of this tile: whole environments, ships first then fields in each
+      const int grp = tile / args.env_tiles, eb = tile - grp * args.env_tiles;
+      bool valid;
+      int env, tok, env_first, env_n, env_ships;
+      size_t grow = 0;
+      int hrow_if_ship;
+      if (args.tile_env_begin) {
+        // ragged: the tile holds the environments tile_env_ids[k_lo .. k_hi), rows in that order
+        const int k_lo = args.tile_env_begin[eb], k_hi = args.tile_env_begin[eb + 1];
+        int k = k_lo, first = 0;
+        env = args.tile_env_ids[k];
+        int cnt = map.tok_off[env + 1] - map.tok_off[env];
+        while (row >= first + cnt && k + 1 < k_hi) {
+          first += cnt;
+          ++k;
+          env = args.tile_env_ids[k];
+          cnt = map.tok_off[env + 1] - map.tok_off[env];
+        }
+        valid = row < first + cnt;
+        env_first = first;
+        env_n = cnt;
+        env_ships = map.ship_off[env + 1] - map.ship_off[env];
+        tok = row - first;
+        grow = (size_t)grp * map.total_tokens + (size_t)(map.tok_off[env] + tok);
+        hrow_if_ship = map.ship_off[env] + tok;
+      } else {
+        const int env0 = eb * args.envs_per_tile;
+        const int env_cnt = min(args.envs_per_tile, map.n_envs - env0);
+        const int el = row / NM;
+        tok = row - el * NM;
+        valid = el < env_cnt;
+        env = env0 + el;
+        env_first = el * NM;
+        env_n = NM;
+        env_ships = map.ships_per_env;
+        grow = (size_t)grp * map.total_tokens + (size_t)env * NM + tok;
+        hrow_if_ship = env * map.ships_per_env + tok;
+      }
+      if (!valid) { grow = 0; env = 0; }
+      const bool is_ship = valid && tok < env_ships;
+      const bool is_field = valid && !is_ship;
+      RowState rs;
+      rs.hrow = is_ship ? hrow_if_ship : -1;
+      rs.lag_ok = BNB_CONV_KERNEL - 1;
+      rs.zero_in = is_ship && args.reset_env && args.reset_env[env];
+      epi_sync();  // previous tile's readers of the meta arrays are done
+      if (e.part == 0) {
+        meta[row] = (uint8_t)(valid ? env_first : row);
+        meta[128 + row] = (uint8_t)(valid ? env_n - 1 : 0);
+        reinterpret_cast<int*>(smem + OFF_ROWINFO)[row] = rs.hrow;
+      }
+      if (tid == 0) s_items = 0;
+      epi_sync();
+      if (e.part == 0 && valid && (tok & 15) == 0) meta[384 + atomicAdd(&s_items, 1)] = (uint8_t)row;
+
+      for (int t = 0; t < args.t_loop; ++t) {
+        const size_t trow = grow + (size_t)t * map.total_tokens;
+        if (e.part == 0) meta[256 + row] = valid ? (args.alive ? args.alive[trow] : (uint8_t)1) : (uint8_t)0;
+        // residual <- x (this thread: columns [32 part, 32 part + 32))
+        {
+          uint32_t v[32];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (valid) f = *reinterpret_cast<const float4*>(args.x + trow * D + e.part * 32 + q * 4);
+            v[q * 4 + 0] = __float_as_uint(f.x); v[q * 4 + 1] = __float_as_uint(f.y);
+            v[q * 4 + 2] = __float_as_uint(f.z); v[q * 4 + 3] = __float_as_uint(f.w);
+          }
+          tmem_st32(e.lane_addr + COL_RESID + e.part * 32, v);
+        }
+        bool boundary = false;
+        if (t >= 1) {
+          boundary = is_ship && args.done && args.done[(size_t)(t - 1) * map.n_envs + env];
+          rs.lag_ok = boundary ? 0 : min(rs.lag_ok + 1, BNB_CONV_KERNEL - 1);
+          rs.zero_in = false;
+        }
+        if (e.part == 0) smem[OFF_ROWINFO + 512 + row] = (uint8_t)(rs.lag_ok | (rs.zero_in ? 4 : 0));
+        epi_sync();
+        const int n_items = s_items;
+        for (int si = 0; si < args.n_sub; ++si) {
+          const SubLayer& s = s_sub[si];
+          // Ask L2 for the recurrent state of the temporal sublayer that follows this one: the
+          // rows are needed one sublayer from now.
+          if (is_ship && t == 0 && si + 1 < args.n_sub && s_sub[si + 1].type == SUB_TEMPORAL && s.type != SUB_TEMPORAL) {
+            const char* base = reinterpret_cast<const char*>(s_sub[si + 1].hid_in + (size_t)rs.hrow * 4 * D) + e.part * 512;
+#pragma unroll
+            for (int l = 0; l < 4; ++l) asm volatile("prefetch.global.L2 [%0];" ::"l"(base + l * 128));
+          }
+          if (s.type == SUB_SPATIAL) run_spatial(e, n_items, valid);
+          else run_temporal(e, s, rs, is_field, boundary, args.has_fields != 0, t == 0 ? s.hid_in : s.hid_out);
+        }
+        // y <- residual
+        {
+          uint32_t v[32];
+          tmem_ld32(e.lane_addr + COL_RESID + e.part * 32, v);
+          if (valid) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<float4*>(args.y + trow * D + e.part * 32 + q * 4) =
+                  make_float4(__uint_as_float(v[q * 4]), __uint_as_float(v[q * 4 + 1]), __uint_as_float(v[q * 4 + 2]), __uint_as_float(v[q * 4 + 3]));
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (s_aborted && warp == LOAD_WARP) {
+    // a wait ran out: copies may still be in flight towards this CTA's shared memory; give them
+    // time to land before the CTA gives it up
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  __syncthreads();
+  if (warp == 0) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace pipe
+
+int launch_pipelined(const TrunkArgs& a, cudaStream_t st) {
+  static bool configured[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BNB_ERR_NO_DEVICE;
+  if (!configured[dev]) {
+    if (cudaFuncSetAttribute(pipe::k_trunk_pipelined, cudaFuncAttributeMaxDynamicSharedMemorySize, pipe::SMEM_BYTES) != cudaSuccess)
+      return BNB_ERR_LAUNCH;
+    configured[dev] = true;
+  }
+  const int grid = a.n_tiles < 148 ? a.n_tiles : 148;
+  count_launch();
+  pipe::k_trunk_pipelined<<<grid, pipe::THREADS, pipe::SMEM_BYTES, st>>>(a);
+  return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
+}
+
+}  // namespace tensor
+}  // namespace bnb

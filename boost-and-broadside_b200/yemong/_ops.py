@@ -32,7 +32,7 @@ def _debug_check(fn: str, dev: torch.device, precision: int) -> None:
     """With BNB_DEBUG_SYNC=1 in the environment every call waits for its kernels and raises if
     one of the tensor-core kernels' bounded waits ran out (status word at the head of the scratch
     buffer).  Off by default: the check synchronises, so it cannot run under graph capture."""
-    if precision == _capi.BNB_BF16 and os.environ.get("BNB_DEBUG_SYNC") == "1":
+    if precision == _capi.BNB_BF16 and os.environ.get("BNB_DEBUG_SYNC") == "1" and not torch.cuda.is_current_stream_capturing():
         st = _capi.tensor_engine_status(dev)
         if 100 < st < 200:   # the ST_TIMEOUT_* codes; other values are scratch data of the exact engine
             raise RuntimeError(f"{fn}: a bounded wait of the tensor-core kernels ran out (code {st})")
