@@ -42,21 +42,31 @@ constexpr int EPI_THREADS = 32 * EPI_WARPS;
 constexpr int MMA_WARP = EPI_WARPS;
 constexpr int LOAD_WARP = EPI_WARPS + 1;
 constexpr int THREADS = EPI_THREADS + 64;
-constexpr int N_DEDICATED = 5;            // ring slots that are never anything else
-constexpr int N_SLOTS = N_DEDICATED + 4;  // + the key/value staging area while no attention runs
+// Weight ring: three pair slots (32 KB: both K atoms of one 128-row weight block, consumed by
+// eight MMAs) and three single slots (16 KB: one down-projection chunk).  Slots 0, 1 (pairs) and
+// 3 (single) are dedicated; 2, 4 and 5 live in the key/value staging area and carry weights only
+// while no attention runs.
+constexpr int N_SLOTS = 6;
+constexpr int RING_BYTES = 5 * CHUNK_BYTES;
 
 constexpr int OFF_A = 0;
 constexpr int OFF_P = 32768;
 constexpr int OFF_KV = 65536;
 constexpr int OFF_RING = 131072;
-constexpr int OFF_META = OFF_RING + N_DEDICATED * CHUNK_BYTES;  // env_first[128], env_n[128], alive[128], items[128]
+constexpr int OFF_META = OFF_RING + RING_BYTES;  // env_first[128], env_n[128], alive[128], items[128]
 constexpr int OFF_ROWINFO = OFF_META + 512;                     // hidden row of each tile row (int), then flags[128]
 constexpr int OFF_SS = OFF_ROWINFO + 640;                       // partial sums of squares [4][128]
 constexpr int OFF_BAR = OFF_SS + 2048;
 constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
 
 // mbarrier indices
-enum : int { B_OP0 = 0, B_OP1, B_ACC0, B_ACC1, B_ACC2, B_PF0, B_PF1, B_KVREL, B_FULL0, B_FREE0 = B_FULL0 + N_SLOTS, B_COUNT = B_FREE0 + N_SLOTS };
+// OP: operand ready (epilogue warps -> issuing lane).  KVREL: the key/value area may take weights
+// again (epilogue warps -> fetching lane).  FULL[s]: the weights of slot s have landed.  DONE[s]:
+// the MMAs that read slot s are complete (tcgen05.commit) -- the fetching lane takes it as "slot
+// free" and, inside the GatedMLP pipeline, the epilogue warps as "accumulator ready" / "product
+// buffer read": one commit per ring operation serves both.  ACC: every MMA of a round outside the
+// GatedMLP pipeline is complete (one more commit per round).
+enum : int { B_OP0 = 0, B_OP1, B_KVREL, B_ACC, B_FULL0, B_DONE0 = B_FULL0 + N_SLOTS, B_COUNT = B_DONE0 + N_SLOTS };
 static_assert(B_COUNT * 8 + 8 <= 256, "barrier area");
 
 constexpr uint32_t COL_RESID = 0;
@@ -65,70 +75,130 @@ constexpr uint32_t TMEM_COLS = 512;
 
 enum : int { ST_TIMEOUT_FULL = 101, ST_TIMEOUT_FREE = 102, ST_TIMEOUT_ACC = 103, ST_TIMEOUT_OPERAND = 104 };
 
-// schedule entry: slot (4 bits) | sublayer (3) | chunk (6) | wait for the key/value area first (1)
-__device__ __forceinline__ uint16_t sched_entry(int slot, int si, int ch, bool kvwait) {
-  return (uint16_t)(slot | (si << 4) | (ch << 7) | (kvwait ? 1 << 13 : 0));
+// Optional cycle accounting (compile with -DBNB_TIMING): thread 0 (an epilogue thread), the
+// issuing lane and the fetching lane of every CTA add up the cycles they spend in each phase and
+// store them behind the status word: 32 counters per CTA from byte 256 on.
+enum : int { TE_ACC_WAIT = 0, TE_FFN_ACC_WAIT, TE_FFN_PF_WAIT, TE_FFN_MATH, TE_NORM, TE_STAGE, TE_ATTN, TE_SYNC, TE_TEMPORAL,
+             TE_IO, TE_TOTAL, TM_FULL_WAIT, TM_OP_WAIT, TM_ISSUE, TM_TOTAL, TL_FREE_WAIT, TL_KV_WAIT, TL_TOTAL, T_COUNT };
+#ifdef BNB_TIMING
+#define T_BEGIN() const long long _t0 = clock64()
+#define T_END(acc, slot) (acc)[slot] += clock64() - _t0
+#define T_WAITSLOT(e, s) (e).wait_slot = (s)
+#define T_MARK(name) long long name = clock64()
+#define T_RESET(name) name = clock64()
+#define T_SINCE(acc, slot, name) do { const long long _n = clock64(); (acc)[slot] += _n - name; name = _n; } while (0)
+#define T_STORE(args, acc, lo, hi) for (int _i = lo; _i < hi; ++_i) reinterpret_cast<long long*>((args).status)[32 + blockIdx.x * 32 + _i] = (acc)[_i]
+#else
+#define T_BEGIN()
+#define T_END(acc, slot)
+#define T_WAITSLOT(e, s)
+#define T_MARK(name)
+#define T_RESET(name)
+#define T_SINCE(acc, slot, name)
+#define T_STORE(args, acc, lo, hi)
+#endif
+
+// Optional event trace (compile with -DBNB_TRACE): CTA 0 records (event id, clock) pairs of one
+// epilogue thread, the issuing lane and the fetching lane from byte 16384 of the status area on,
+// 1500 events per role.
+#ifdef BNB_TRACE
+struct Trace { unsigned long long* buf; int n; };
+__device__ __forceinline__ void trace_init(Trace& t, int* status, int role) {
+  t.buf = reinterpret_cast<unsigned long long*>(status) + 2048 + role * 1500;
+  t.n = blockIdx.x == 0 ? 0 : 1500;
 }
-constexpr int MAX_SCHED = MAX_SUBLAYERS * N_TEMPORAL_CHUNKS;
+__device__ __forceinline__ void trace(Trace& t, int id) {
+  if (t.n < 1500) t.buf[t.n++] = ((unsigned long long)id << 48) | ((unsigned long long)clock64() & 0xFFFFFFFFFFFFull);
+}
+#define TRACE(t, id) trace(t, id)
+#else
+#define TRACE(t, id)
+#endif
+
+// Schedule entry of one ring operation: slot (3 bits) | sublayer (3) | first chunk (6) | second
+// chunk (6; 63 = none: a single) | wait for the key/value area first (1).
+constexpr uint32_t NO_CHUNK = 63;
+__device__ __forceinline__ uint32_t sched_entry(int slot, int si, int ch0, int ch1, bool kvwait) {
+  return (uint32_t)slot | ((uint32_t)si << 3) | ((uint32_t)ch0 << 6) | ((uint32_t)ch1 << 12) | (kvwait ? 1u << 18 : 0u);
+}
+constexpr int MAX_SCHED = MAX_SUBLAYERS * 22;
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-// Chunks of a sublayer's image in the order the issuing warp consumes them.
-// GatedMLP with base b: gate|up of chunk c is b + 3c (+1), its down projection b + 3c + 2; the
-// three-deep pipeline consumes GU0 GU1 GU2 D0 GU3 D1 GU4 ... GU7 D5 D6 D7.
-__device__ __forceinline__ int ffn_order(int base, int i) {
-  if (i < 6) return base + 3 * (i >> 1) + (i & 1);
-  i -= 6;                       // then 5 groups of (D(c), GU(c+3) a, b), c = 0..4, then D5, D6, D7
-  if (i < 15) {
-    const int c = i / 3, j = i % 3;
-    return j == 0 ? base + 3 * c + 2 : base + 3 * (c + 3) + (j - 1);
+// Ring operations of a sublayer in the order the issuing lane consumes them.  GatedMLP with
+// image base b: gate|up of chunk c are chunks b + 3c, b + 3c + 1 (a pair), its down projection is
+// b + 3c + 2 (a single); the three-deep pipeline consumes GU0 GU1 GU2 D0 GU3 D1 GU4 D2 ... GU7 D5 D6 D7.
+struct SlotRotation {
+  int pair, single;
+  __device__ __forceinline__ int next_pair() { const int r = pair; pair = pair == 2 ? 0 : pair + 1; return r; }
+  __device__ __forceinline__ int next_single() { const int r = single; single = single == 5 ? 3 : single + 1; return r; }
+};
+__device__ __forceinline__ int ffn_ops(uint32_t* out, int n, int si, int base, SlotRotation& rot, int first_flagged) {
+  // first_flagged: index (in GU order) of the first gate|up pair that must wait for the key/value area, or -1
+  for (int c = 0; c < 3; ++c) out[n++] = sched_entry(rot.next_pair(), si, base + 3 * c, base + 3 * c + 1, c == first_flagged);
+  for (int c = 0; c < 8; ++c) {
+    out[n++] = sched_entry(rot.next_single(), si, base + 3 * c + 2, NO_CHUNK, false);
+    if (c + 3 < 8) out[n++] = sched_entry(rot.next_pair(), si, base + 3 * (c + 3), base + 3 * (c + 3) + 1, false);
   }
-  return base + 3 * (i - 15 + 5) + 2;
+  return n;
 }
-__device__ __forceinline__ int build_schedule(const SubLayer* subs, int n_sub, bool has_fields, uint16_t* out) {
-  int n = 0, rr = 0;
+__device__ __forceinline__ int build_schedule(const SubLayer* subs, int n_sub, bool has_fields, uint32_t* out) {
+  int n = 0;
+  SlotRotation rot{0, 3};
   for (int si = 0; si < n_sub; ++si) {
     if (subs[si].type == SUB_SPATIAL) {
-      for (int h = 0; h < HEADS; ++h)
-        for (int kh = 0; kh < 2; ++kh) {
-          out[n++] = sched_entry(rr, si, 5 * (h >> 1) + 2 * (h & 1) + kh, false);
-          rr = rr + 1 == N_SLOTS ? 0 : rr + 1;
-        }
-      // fetched while the attention runs: dedicated slots only
-      out[n++] = sched_entry(0, si, 4, false);
-      out[n++] = sched_entry(1, si, 9, false);
-      for (int i = 0; i < 3; ++i) out[n++] = sched_entry(2 + i, si, ffn_order(10, i), false);
-      rr = N_DEDICATED;
-      for (int i = 3; i < 24; ++i) {
-        out[n++] = sched_entry(rr, si, ffn_order(10, i), i == 3);
-        rr = rr + 1 == N_SLOTS ? 0 : rr + 1;
+      for (int h = 0; h < HEADS; ++h) {
+        const int ch = 5 * (h >> 1) + 2 * (h & 1);
+        out[n++] = sched_entry(rot.next_pair(), si, ch, ch + 1, false);
       }
+      // fetched while the attention runs: the dedicated slots only.  out_proj -> pair slot 0, the
+      // first gate|up -> pair slot 1 and the first down projection -> single slot 3; the second
+      // gate|up is the first operation that goes to the key/value area and waits for it.
+      out[n++] = sched_entry(0, si, 4, 9, false);
+      rot.pair = 1;
+      rot.single = 3;
+      n = ffn_ops(out, n, si, 10, rot, 1);
     } else {
-      for (int i = 0; i < 12 + 24; ++i) {
-        const int ch = i < 12 ? i : ffn_order(12, i - 12);
-        if (!has_fields && (ch == 8 || ch == 9)) continue;
-        out[n++] = sched_entry(rr, si, ch, false);
-        rr = rr + 1 == N_SLOTS ? 0 : rr + 1;
+      for (int i = 0; i < 6; ++i) {
+        if (!has_fields && i == 4) continue;
+        out[n++] = sched_entry(rot.next_pair(), si, 2 * i, 2 * i + 1, false);
       }
+      n = ffn_ops(out, n, si, 12, rot, -1);
     }
   }
   return n;
 }
 
 __device__ __forceinline__ uint32_t slot_offset(uint32_t slot) {
-  return slot < N_DEDICATED ? OFF_RING + slot * CHUNK_BYTES : OFF_KV + (slot - N_DEDICATED) * CHUNK_BYTES;
+  switch (slot) {
+    case 0: return OFF_RING;
+    case 1: return OFF_RING + 2 * CHUNK_BYTES;
+    case 2: return OFF_KV;
+    case 3: return OFF_RING + 4 * CHUNK_BYTES;
+    case 4: return OFF_KV + 2 * CHUNK_BYTES;
+    default: return OFF_KV + 3 * CHUNK_BYTES;
+  }
 }
 
 // ------------------------------------------------------------------ epilogue side
 
 struct Epi {
+#ifdef BNB_TRACE
+  Trace tr;
+#endif
+#ifdef BNB_TIMING
+  long long tacc[T_COUNT];
+  int wait_slot;
+#endif
   uint8_t* smem;
   uint32_t sbase;       // shared address of smem
   uint32_t bars;        // shared address of the barrier array
   uint32_t lane_addr;   // tensor-memory address of this thread's lane, column 0
-  uint32_t par;         // phase bits: ACC0..2 -> bits 0..2, PF0..1 -> bits 3, 4
+  uint32_t par;         // phase bits of the DONE barriers, one per ring slot
+  const uint32_t* sched;
+  int sched_len, cur;   // cursor into the schedule: the next ring operation this thread waits for
   int row, part;
   int* status;
   volatile int* aborted;
@@ -136,22 +206,54 @@ struct Epi {
 };
 
 // "My share of the operand is written and my reads of the accumulator are done."
-__device__ __forceinline__ void post(const Epi& e, int bar) {
+__device__ __forceinline__ void post(Epi& e, int bar) {
+  TRACE(e.tr, 200 + bar);
   fence_proxy_async();
   tc_fence_before();
   __syncwarp();
   if ((threadIdx.x & 31) == 0) mbar_arrive(e.bars + 8 * bar);
+  TRACE(e.tr, 210 + bar);
 }
-__device__ __forceinline__ void wait_commit(Epi& e, int bar, int bit) {
-  mbar_wait(e.bars + 8 * bar, (e.par >> bit) & 1u, e.status, e.aborted, ST_TIMEOUT_ACC);
-  e.par ^= 1u << bit;
+// The epilogue threads walk the schedule of ring operations with a cursor of their own and keep
+// one phase bit per DONE barrier.
+//
+// wait_round: a round outside the GatedMLP pipeline (n operations, then a commit on ACC).  The
+// threads wait on ACC and flip the phase bits of the n operations, which are complete by then.
+__device__ __forceinline__ void wait_round(Epi& e, int n) {
+  T_BEGIN();
+  mbar_wait(e.bars + 8 * B_ACC, (e.par >> 8) & 1u, e.status, e.aborted, ST_TIMEOUT_ACC);
+  e.par ^= 1u << 8;
+  for (int i = 0; i < n; ++i) {
+    const uint32_t slot = e.sched[e.cur] & 7u;
+    e.cur = e.cur + 1 == e.sched_len ? 0 : e.cur + 1;
+    e.par ^= 1u << slot;
+  }
   tc_fence_after();
+  T_END(e.tacc, e.wait_slot);
+  TRACE(e.tr, 110 + n);
 }
-__device__ __forceinline__ void wait_acc(Epi& e, int i) { wait_commit(e, B_ACC0 + i, i); }
+// wait_ops: inside the GatedMLP pipeline the threads wait for each operation on its own DONE
+// barrier, in schedule order.  A slot is not reused before the threads have seen its previous
+// operation complete: the reuse distance is three operations of a kind, and the issuing lane
+// issues gate|up of chunk c + 3 and the down projection of chunk c only after the post of chunk c.
+__device__ __forceinline__ void wait_ops(Epi& e, int n) {
+  T_BEGIN();
+  for (int i = 0; i < n; ++i) {
+    const uint32_t slot = e.sched[e.cur] & 7u;
+    e.cur = e.cur + 1 == e.sched_len ? 0 : e.cur + 1;
+    mbar_wait(e.bars + 8 * (B_DONE0 + slot), (e.par >> slot) & 1u, e.status, e.aborted, ST_TIMEOUT_ACC);
+    e.par ^= 1u << slot;
+  }
+  tc_fence_after();
+  T_END(e.tacc, e.wait_slot);
+  TRACE(e.tr, 100 + n);
+}
 __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory"); }
 
 // residual (TMEM) -> x * rsqrt(mean x^2 + eps) -> bf16 A operand (the RMSNorm gain is in the weights)
 __device__ __forceinline__ void norm_to_A(Epi& e) {
+  TRACE(e.tr, 300);
+  T_BEGIN();
   uint32_t v[32];
   tmem_ld32(e.lane_addr + COL_RESID + e.part * 32, v);
   float ss = 0.f;
@@ -177,6 +279,7 @@ __device__ __forceinline__ void norm_to_A(Epi& e) {
     *reinterpret_cast<uint4*>(e.smem + OFF_A + (col >> 6) * CHUNK_BYTES + swz(e.row, (col & 63) >> 3)) = o;
   }
   // the partial sums are read again by the next norm only after at least one full barrier
+  T_END(e.tacc, TE_NORM);
 }
 
 __device__ __forceinline__ uint4 pack8(const uint32_t* s) {
@@ -191,7 +294,9 @@ __device__ __forceinline__ void ffn(Epi& e) {
 #pragma unroll 1
   for (int c = 0; c < 8; ++c) {
     const int ai = c % 3, pi = c & 1;
-    wait_acc(e, ai);
+    T_WAITSLOT(e, TE_FFN_ACC_WAIT);
+    wait_ops(e, 1);   // gate|up of chunk c
+    T_BEGIN();
     uint32_t gv[16], uv[16];
     const uint32_t acc = e.lane_addr + COL_ACC0 + ai * 128 + e.part * 16;
     tmem_ld16_nowait(acc, gv);
@@ -207,16 +312,18 @@ __device__ __forceinline__ void ffn(Epi& e) {
                                __uint_as_float(uv[q * 8 + 2 * j]), __uint_as_float(uv[q * 8 + 2 * j + 1]));
       o[q] = make_uint4(w[0], w[1], w[2], w[3]);
     }
+    T_END(e.tacc, TE_FFN_MATH);
     // the down projection of chunk c - 2 has read this buffer
-    if (c >= 2) wait_commit(e, B_PF0 + pi, 3 + pi);
+    T_WAITSLOT(e, TE_FFN_PF_WAIT);
+    if (c >= 2) wait_ops(e, 1);
 #pragma unroll
     for (int q = 0; q < 2; ++q)
       *reinterpret_cast<uint4*>(e.smem + OFF_P + pi * CHUNK_BYTES + swz(e.row, e.part * 2 + q)) = o[q];
     post(e, B_OP0 + pi);
   }
   // residual complete: the down projections of chunks 6 and 7
-  wait_commit(e, B_PF0, 3);
-  wait_commit(e, B_PF1, 4);
+  wait_ops(e, 2);
+  T_WAITSLOT(e, TE_ACC_WAIT);
 }
 
 // Attention of every head and environment of the tile from the staged q (A area), k and v (KV
@@ -224,7 +331,8 @@ __device__ __forceinline__ void ffn(Epi& e) {
 // columns 32 (h % 2) ..).  Warp w serves head w % 4 and every fourth block of 16 query rows;
 // keys are walked in blocks of 16 with a running maximum.  Output: bf16 into the P area as the
 // A operand of out_proj.
-__device__ __forceinline__ void attention(const Epi& e, int n_items) {
+__device__ __forceinline__ void attention(Epi& e, int n_items) {
+  TRACE(e.tr, 310);
   const uint8_t* meta = e.smem + OFF_META;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -336,8 +444,9 @@ __device__ __forceinline__ void attention(const Epi& e, int n_items) {
 __device__ __forceinline__ void run_spatial(Epi& e, int n_items, bool row_valid) {
   norm_to_A(e);
   post(e, B_OP0);
-  wait_acc(e, 0);   // q|k|v of head h in columns [128 + 96 h, +96)
+  wait_round(e, HEADS);   // q|k|v of head h in columns [128 + 96 h, +96)
   {
+    T_BEGIN();
     // this thread stages head `part` of its row: q into the A area (the normed operand has been
     // consumed), k and v into the KV area, all in the swizzled atom layout
     const int h = e.part;
@@ -356,15 +465,24 @@ __device__ __forceinline__ void run_spatial(Epi& e, int n_items, bool row_valid)
 #pragma unroll
       for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(e.smem + OFF_P + atom + swz(e.row, c8h + q)) = make_uint4(0u, 0u, 0u, 0u);
     }
+    T_END(e.tacc, TE_STAGE);
   }
   tc_fence_before();
-  epi_sync();
-  attention(e, n_items);
+  {
+    T_BEGIN();
+    epi_sync();
+    T_END(e.tacc, TE_SYNC);
+  }
+  {
+    T_BEGIN();
+    attention(e, n_items);
+    T_END(e.tacc, TE_ATTN);
+  }
   // keys and values are dead: the area may take weight chunks again
   __syncwarp();
   if ((threadIdx.x & 31) == 0) mbar_arrive(e.bars + 8 * B_KVREL);
   post(e, B_OP0);   // attention output in P
-  wait_acc(e, 0);   // out_proj accumulated into the residual
+  wait_round(e, 1);   // out_proj accumulated into the residual
   norm_to_A(e);
   post(e, B_OP0);
   ffn(e);
@@ -383,7 +501,8 @@ __device__ __forceinline__ void run_temporal(Epi& e, const SubLayer& s, const Ro
   const bool is_ship = rs.hrow >= 0;
   norm_to_A(e);
   post(e, B_OP0);
-  wait_acc(e, 0);   // acc0 = linear2 n, acc1 = linear1 n
+  wait_round(e, 2);   // acc0 = linear2 n, acc1 = linear1 n
+  T_MARK(tt);
   // b2 = bf16(gelu(linear2 n)) for this thread's columns, parked as packed bf16 pairs
   uint32_t b2p[2][8];
 #pragma unroll
@@ -405,7 +524,9 @@ __device__ __forceinline__ void run_temporal(Epi& e, const SubLayer& s, const Ro
     }
   }
   tc_fence_before();
+  T_SINCE(e.tacc, TE_TEMPORAL, tt);
   epi_sync();
+  T_SINCE(e.tacc, TE_SYNC, tt);
   const float* hin = is_ship ? hid_in + (size_t)rs.hrow * 4 * D : nullptr;
   float* hout = is_ship ? s.hid_out + (size_t)rs.hrow * 4 * D : nullptr;
   // Causal conv, one warp per ship row and four columns per lane, so that the stored taps are
@@ -474,6 +595,7 @@ __device__ __forceinline__ void run_temporal(Epi& e, const SubLayer& s, const Ro
     }
   }
   post(e, B_OP0);   // A = u (ship rows) / b1 (field rows)
+  T_SINCE(e.tacc, TE_TEMPORAL, tt);
   // previous state of this thread's columns of the first half, requested before the gates arrive
   float4 hprev[4];
 #pragma unroll
@@ -481,7 +603,8 @@ __device__ __forceinline__ void run_temporal(Epi& e, const SubLayer& s, const Ro
     hprev[q] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (is_ship && !rs.zero_in) hprev[q] = *reinterpret_cast<const float4*>(hin + e.part * 16 + q * 4);
   }
-  wait_acc(e, 0);   // acc0 / acc1 = [W_a u | W_x u] of hidden columns [0,64) / [64,128); acc2 = field_sub b1
+  wait_round(e, has_fields ? 3 : 2);   // acc0 / acc1 = [W_a u | W_x u] of hidden columns [0,64) / [64,128); acc2 = field_sub b1
+  T_MARK(tu);
   // gates and state update
 #pragma unroll
   for (int rnd = 0; rnd < 2; ++rnd) {
@@ -578,7 +701,8 @@ __device__ __forceinline__ void run_temporal(Epi& e, const SubLayer& s, const Ro
     }
   }
   post(e, B_OP0);   // branch operand
-  wait_acc(e, 0);   // residual += linear_out(branch)
+  T_SINCE(e.tacc, TE_TEMPORAL, tu);
+  wait_round(e, 1);   // residual += linear_out(branch)
   norm_to_A(e);
   post(e, B_OP0);
   ffn(e);
@@ -587,83 +711,96 @@ __device__ __forceinline__ void run_temporal(Epi& e, const SubLayer& s, const Ro
 // ------------------------------------------------------------------ issuing side (one lane)
 
 struct Issuer {
+#ifdef BNB_TRACE
+  Trace tr;
+#endif
+#ifdef BNB_TIMING
+  long long tacc[T_COUNT];
+#endif
   uint32_t sbase, bars, tmem;
   uint32_t full_par;   // per-slot phase bits of the full barriers
   uint32_t op_par;     // phase bits of OP0, OP1
-  const uint16_t* sched;
+  const uint32_t* sched;
   int sched_len, idx;
+  uint32_t next_slot;  // ring slot of the next chunk of the schedule
   int* status;
   volatile int* aborted;
 };
 
 __device__ __forceinline__ void wait_operand(Issuer& m, int i) {
+  T_BEGIN();
   mbar_wait(m.bars + 8 * (B_OP0 + i), (m.op_par >> i) & 1u, m.status, m.aborted, ST_TIMEOUT_OPERAND);
   m.op_par ^= 1u << i;
   tc_fence_after();
+  T_END(m.tacc, TM_OP_WAIT);
+  TRACE(m.tr, 400 + i);
 }
-// D[128 x n] (+)= A[128 x 64] * W[n x 64]^T with the next weight chunk of the schedule.
-__device__ __forceinline__ void issue_chunk(Issuer& m, uint32_t a_off, uint32_t n, uint32_t d_col, uint32_t accumulate) {
-  const uint32_t slot = m.sched[m.idx] & 15u;
+// The next ring operation of the schedule: wait for its weights, issue its MMAs
+// (D[128 x n] (+)= A[128 x 64] * W[n x 64]^T per K atom: a pair reads K atom 0 of the operand at
+// a_off0 and K atom 1 at a_off1), and commit on the slot's DONE barrier.
+__device__ __forceinline__ void issue_op(Issuer& m, bool pair, uint32_t a_off0, uint32_t a_off1, uint32_t n, uint32_t d_col,
+                                         uint32_t accumulate) {
+  const uint32_t slot = m.next_slot;
   m.idx = m.idx + 1 == m.sched_len ? 0 : m.idx + 1;
+  m.next_slot = m.sched[m.idx] & 7u;   // not needed before the next call: the load's latency is hidden
+  T_MARK(tw);
   mbar_wait(m.bars + 8 * (B_FULL0 + slot), (m.full_par >> slot) & 1u, m.status, m.aborted, ST_TIMEOUT_FULL);
   m.full_par ^= 1u << slot;
-  tc_fence_after();
-  const uint32_t a_addr = m.sbase + a_off, b_addr = m.sbase + slot_offset(slot);
+  T_SINCE(m.tacc, TM_FULL_WAIT, tw);
+  TRACE(m.tr, 410);
+  const uint32_t b_addr = m.sbase + slot_offset(slot);
   const uint32_t idesc = instr_desc(n);
 #pragma unroll
   for (int k = 0; k < 4; ++k)
-    tc_mma(m.tmem + d_col, smem_desc(a_addr + k * 32), smem_desc(b_addr + k * 32), idesc, (accumulate | (uint32_t)k) ? 1u : 0u);
-  tc_commit(m.bars + 8 * (B_FREE0 + slot));
+    tc_mma(m.tmem + d_col, smem_desc(m.sbase + a_off0 + k * 32), smem_desc(b_addr + k * 32), idesc, (accumulate | (uint32_t)k) ? 1u : 0u);
+  if (pair) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      tc_mma(m.tmem + d_col, smem_desc(m.sbase + a_off1 + k * 32), smem_desc(b_addr + CHUNK_BYTES + k * 32), idesc, 1u);
+  }
+  tc_commit(m.bars + 8 * (B_DONE0 + slot));
+  T_SINCE(m.tacc, TM_ISSUE, tw);
+  TRACE(m.tr, 420);
 }
 __device__ __forceinline__ void issue_pair(Issuer& m, uint32_t a_off, uint32_t n, uint32_t d_col) {
-  issue_chunk(m, a_off, n, d_col, 0);
-  issue_chunk(m, a_off + CHUNK_BYTES, n, d_col, 1);
+  issue_op(m, true, a_off, a_off + CHUNK_BYTES, n, d_col, 0);
 }
-__device__ __forceinline__ void commit(const Issuer& m, int bar) { tc_commit(m.bars + 8 * bar); }
+__device__ __forceinline__ void commit_round(const Issuer& m) { tc_commit(m.bars + 8 * B_ACC); }
 
 __device__ __forceinline__ void issue_ffn(Issuer& m) {
   wait_operand(m, 0);
 #pragma unroll 1
-  for (int c = 0; c < 3; ++c) {
-    issue_pair(m, OFF_A, 128, COL_ACC0 + 128 * c);
-    commit(m, B_ACC0 + c);
-  }
+  for (int c = 0; c < 3; ++c) issue_pair(m, OFF_A, 128, COL_ACC0 + 128 * c);
 #pragma unroll 1
   for (int c = 0; c < 8; ++c) {
     wait_operand(m, c & 1);   // product of chunk c written, accumulator c % 3 read
-    issue_chunk(m, OFF_P + (c & 1) * CHUNK_BYTES, 128, COL_RESID, 1);
-    commit(m, B_PF0 + (c & 1));
-    if (c + 3 < 8) {
-      issue_pair(m, OFF_A, 128, COL_ACC0 + 128 * (c % 3));
-      commit(m, B_ACC0 + c % 3);
-    }
+    issue_op(m, false, OFF_P + (c & 1) * CHUNK_BYTES, 0, 128, COL_RESID, 1);
+    if (c + 3 < 8) issue_pair(m, OFF_A, 128, COL_ACC0 + 128 * (c % 3));
   }
 }
 __device__ __forceinline__ void issue_spatial(Issuer& m) {
   wait_operand(m, 0);
 #pragma unroll 1
   for (int h = 0; h < HEADS; ++h) issue_pair(m, OFF_A, 96, COL_ACC0 + 96 * h);
-  commit(m, B_ACC0);
+  commit_round(m);
   wait_operand(m, 0);   // attention output: K atom 0 = heads 0, 1; K atom 1 = heads 2, 3
-  issue_chunk(m, OFF_P, 128, COL_RESID, 1);
-  issue_chunk(m, OFF_P + CHUNK_BYTES, 128, COL_RESID, 1);
-  commit(m, B_ACC0);
+  issue_op(m, true, OFF_P, OFF_P + CHUNK_BYTES, 128, COL_RESID, 1);
+  commit_round(m);
   issue_ffn(m);
 }
 __device__ __forceinline__ void issue_temporal(Issuer& m, bool has_fields) {
   wait_operand(m, 0);
   issue_pair(m, OFF_A, 128, COL_ACC0);   // linear2
   issue_pair(m, OFF_A, 128, COL_ACC1);   // linear1
-  commit(m, B_ACC0);
+  commit_round(m);
   wait_operand(m, 0);
   issue_pair(m, OFF_A, 128, COL_ACC0);   // gates of hidden columns [0,64)
   issue_pair(m, OFF_A, 128, COL_ACC1);   // gates of hidden columns [64,128)
   if (has_fields) issue_pair(m, OFF_A, 128, COL_ACC2);   // field_sub
-  commit(m, B_ACC0);
+  commit_round(m);
   wait_operand(m, 0);
-  issue_chunk(m, OFF_P, 128, COL_RESID, 1);                 // linear_out, K atom 0
-  issue_chunk(m, OFF_A + CHUNK_BYTES, 128, COL_RESID, 1);   // K atom 1
-  commit(m, B_ACC0);
+  issue_op(m, true, OFF_P, OFF_A + CHUNK_BYTES, 128, COL_RESID, 1);   // linear_out: K atom 0 from P0, K atom 1 in place in A
+  commit_round(m);
   issue_ffn(m);
 }
 
@@ -675,7 +812,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_trunk_pipelined(const __grid_con
   __shared__ int s_aborted;
   __shared__ int s_items;
   __shared__ SubLayer s_sub[MAX_SUBLAYERS];  // kernel parameters are slow to index dynamically
-  __shared__ uint16_t s_sched[MAX_SCHED];
+  __shared__ uint32_t s_sched[MAX_SCHED];
   __shared__ int s_sched_len;
   const int tid = threadIdx.x, warp = tid >> 5;
   if (tid < args.n_sub) s_sub[tid] = args.sub[tid];
@@ -687,8 +824,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_trunk_pipelined(const __grid_con
     mbar_init(smem_u32(&bars[B_OP0]), EPI_WARPS);
     mbar_init(smem_u32(&bars[B_OP1]), EPI_WARPS);
     mbar_init(smem_u32(&bars[B_KVREL]), EPI_WARPS);
-    for (int i = B_ACC0; i <= B_PF1; ++i) mbar_init(smem_u32(&bars[i]), 1);
-    for (int i = B_FULL0; i < B_COUNT; ++i) mbar_init(smem_u32(&bars[i]), 1);
+    for (int i = B_ACC; i < B_COUNT; ++i) mbar_init(smem_u32(&bars[i]), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
@@ -709,20 +845,49 @@ __global__ void __launch_bounds__(THREADS, 1) k_trunk_pipelined(const __grid_con
       uint32_t free_par = (1u << N_SLOTS) - 1u;   // a fresh barrier passes a wait on parity 1: every slot starts free
       uint32_t kv_par = 0;
       const int len = s_sched_len;
+#ifdef BNB_TIMING
+      long long tacc[T_COUNT];
+      for (int i = 0; i < T_COUNT; ++i) tacc[i] = 0;
+#endif
+      T_MARK(t_start);
+#ifdef BNB_TRACE
+      Trace ltr;
+      trace_init(ltr, args.status, 2);
+#endif
       for (int pass = 0; pass < passes; ++pass)
         for (int i = 0; i < len; ++i) {
           const uint32_t en = s_sched[i];
-          const uint32_t slot = en & 15u;
-          if (en & (1u << 13)) {
+          const uint32_t slot = en & 7u;
+          T_MARK(tw);
+          if (en & (1u << 18)) {
             mbar_wait(bar0 + 8 * B_KVREL, kv_par, args.status, &s_aborted, ST_TIMEOUT_FREE);
             kv_par ^= 1u;
           }
-          mbar_wait(bar0 + 8 * (B_FREE0 + slot), (free_par >> slot) & 1u, args.status, &s_aborted, ST_TIMEOUT_FREE);
+          T_SINCE(tacc, TL_KV_WAIT, tw);
+          mbar_wait(bar0 + 8 * (B_DONE0 + slot), (free_par >> slot) & 1u, args.status, &s_aborted, ST_TIMEOUT_FREE);
           free_par ^= 1u << slot;
+          T_SINCE(tacc, TL_FREE_WAIT, tw);
+          TRACE(ltr, 500 + slot);
           const uint32_t full = bar0 + 8 * (B_FULL0 + slot);
-          mbar_expect_tx(full, CHUNK_BYTES);
-          bulk_g2s(sbase + slot_offset(slot), s_sub[(en >> 4) & 7u].packed + (size_t)((en >> 7) & 63u) * CHUNK_BYTES, CHUNK_BYTES, full);
+          const uint8_t* image = s_sub[(en >> 3) & 7u].packed;
+          const uint32_t ch0 = (en >> 6) & 63u, ch1 = (en >> 12) & 63u;
+          const uint32_t dst = sbase + slot_offset(slot);
+          if (ch1 == NO_CHUNK) {
+            mbar_expect_tx(full, CHUNK_BYTES);
+            bulk_g2s(dst, image + (size_t)ch0 * CHUNK_BYTES, CHUNK_BYTES, full);
+          } else if (ch1 == ch0 + 1) {
+            mbar_expect_tx(full, 2 * CHUNK_BYTES);
+            bulk_g2s(dst, image + (size_t)ch0 * CHUNK_BYTES, 2 * CHUNK_BYTES, full);
+          } else {
+            mbar_expect_tx(full, 2 * CHUNK_BYTES);
+            bulk_g2s(dst, image + (size_t)ch0 * CHUNK_BYTES, CHUNK_BYTES, full);
+            bulk_g2s(dst + CHUNK_BYTES, image + (size_t)ch1 * CHUNK_BYTES, CHUNK_BYTES, full);
+          }
         }
+#ifdef BNB_TIMING
+      tacc[TL_TOTAL] = clock64() - t_start;
+      T_STORE(args, tacc, TL_FREE_WAIT, T_COUNT);
+#endif
     }
   } else if (warp == MMA_WARP) {
     // ---------------------------------------------------------------- tensor-core issue
@@ -736,13 +901,25 @@ __global__ void __launch_bounds__(THREADS, 1) k_trunk_pipelined(const __grid_con
       m.sched = s_sched;
       m.sched_len = s_sched_len;
       m.idx = 0;
+      m.next_slot = s_sched[0] & 7u;
       m.status = args.status;
       m.aborted = &s_aborted;
+#ifdef BNB_TRACE
+      trace_init(m.tr, args.status, 1);
+#endif
+#ifdef BNB_TIMING
+      for (int i = 0; i < T_COUNT; ++i) m.tacc[i] = 0;
+#endif
+      T_MARK(t_start);
       for (int pass = 0; pass < passes; ++pass)
         for (int si = 0; si < args.n_sub; ++si) {
           if (s_sub[si].type == SUB_SPATIAL) issue_spatial(m);
           else issue_temporal(m, args.has_fields != 0);
         }
+#ifdef BNB_TIMING
+      m.tacc[TM_TOTAL] = clock64() - t_start;
+      T_STORE(args, m.tacc, TM_FULL_WAIT, TL_FREE_WAIT);
+#endif
     }
   } else {
     // ---------------------------------------------------------------- tile owners
@@ -754,9 +931,21 @@ __global__ void __launch_bounds__(THREADS, 1) k_trunk_pipelined(const __grid_con
     e.part = tid >> 7;
     e.lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     e.par = 0;
+    e.sched = s_sched;
+    e.sched_len = s_sched_len;
+    e.cur = 0;
     e.status = args.status;
     e.aborted = &s_aborted;
     e.ss_part = reinterpret_cast<float*>(smem + OFF_SS);
+#ifdef BNB_TRACE
+    trace_init(e.tr, args.status, 0);
+    if (tid != 0) e.tr.n = 1500;
+#endif
+#ifdef BNB_TIMING
+    for (int i = 0; i < T_COUNT; ++i) e.tacc[i] = 0;
+    e.wait_slot = TE_ACC_WAIT;
+#endif
+    T_MARK(t_start);
     uint8_t* meta = smem + OFF_META;
     const EnvMap& map = args.map;
     const int NM = map.tokens_per_env;
@@ -764,6 +953,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_trunk_pipelined(const __grid_con
 
     for (int tile = blockIdx.x; tile < args.n_tiles; tile += gridDim.x) {
       // ---- rows of this tile: whole environments, ships first then fields in each
+      T_MARK(t_io);
       const int grp = tile / args.env_tiles, eb = tile - grp * args.env_tiles;
       bool valid;
       int env, tok, env_first, env_n, env_ships;
@@ -841,6 +1031,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_trunk_pipelined(const __grid_con
         }
         if (e.part == 0) smem[OFF_ROWINFO + 512 + row] = (uint8_t)(rs.lag_ok | (rs.zero_in ? 4 : 0));
         epi_sync();
+        T_SINCE(e.tacc, TE_IO, t_io);
         const int n_items = s_items;
         for (int si = 0; si < args.n_sub; ++si) {
           const SubLayer& s = s_sub[si];
@@ -855,6 +1046,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_trunk_pipelined(const __grid_con
           else run_temporal(e, s, rs, is_field, boundary, args.has_fields != 0, t == 0 ? s.hid_in : s.hid_out);
         }
         // y <- residual
+        T_RESET(t_io);
         {
           uint32_t v[32];
           tmem_ld32(e.lane_addr + COL_RESID + e.part * 32, v);
@@ -865,8 +1057,13 @@ __global__ void __launch_bounds__(THREADS, 1) k_trunk_pipelined(const __grid_con
                   make_float4(__uint_as_float(v[q * 4]), __uint_as_float(v[q * 4 + 1]), __uint_as_float(v[q * 4 + 2]), __uint_as_float(v[q * 4 + 3]));
           }
         }
+        T_SINCE(e.tacc, TE_IO, t_io);
       }
     }
+#ifdef BNB_TIMING
+    e.tacc[TE_TOTAL] = clock64() - t_start;
+    if (tid == 0) T_STORE(args, e.tacc, 0, TM_FULL_WAIT);
+#endif
   }
   tc_fence_before();
   __syncthreads();

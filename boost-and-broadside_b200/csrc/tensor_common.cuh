@@ -108,6 +108,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait: gives up after `limit` polls, records `code` and lets the caller go on.
 __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* status, volatile int* aborted, int code) {
+  if (mbar_try_wait(bar, parity)) return;   // the common case costs one instruction
   const int limit = *aborted ? 4 : (1 << 20);
   for (int i = 0; i < limit; ++i)
     if (mbar_try_wait(bar, parity)) return;
