@@ -735,6 +735,20 @@ __device__ __forceinline__ void wait_operand(Issuer& m, int i) {
   T_END(m.tacc, TM_OP_WAIT);
   TRACE(m.tr, 400 + i);
 }
+// tcgen05.mma with both shared-memory descriptors built from 32-bit halves inside the asm block
+// (K-major, 128-byte swizzle, 8-row groups 1024 B apart: the high word is a constant), which keeps
+// the issuing lane's register count low.
+__device__ __forceinline__ uint32_t desc_lo(uint32_t addr) { return ((addr & 0x3FFFFu) >> 4) | (1u << 16); }
+__device__ __forceinline__ void tc_mma_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %5};\n\t"
+      "mov.b64 db, {%2, %5};\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(0x40004040u) : "memory");
+}
+
 // The next ring operation of the schedule: wait for its weights, issue its MMAs
 // (D[128 x n] (+)= A[128 x 64] * W[n x 64]^T per K atom: a pair reads K atom 0 of the operand at
 // a_off0 and K atom 1 at a_off1), and commit on the slot's DONE barrier.
@@ -748,15 +762,16 @@ __device__ __forceinline__ void issue_op(Issuer& m, bool pair, uint32_t a_off0, 
   m.full_par ^= 1u << slot;
   T_SINCE(m.tacc, TM_FULL_WAIT, tw);
   TRACE(m.tr, 410);
-  const uint32_t b_addr = m.sbase + slot_offset(slot);
+  const uint32_t b_lo = desc_lo(m.sbase + slot_offset(slot));
   const uint32_t idesc = instr_desc(n);
+  // a step of 16 K columns = 32 bytes = 2 in descriptor units; a K atom = 16 KB = 1024 units
+  const uint32_t a0 = desc_lo(m.sbase + a_off0);
 #pragma unroll
-  for (int k = 0; k < 4; ++k)
-    tc_mma(m.tmem + d_col, smem_desc(m.sbase + a_off0 + k * 32), smem_desc(b_addr + k * 32), idesc, (accumulate | (uint32_t)k) ? 1u : 0u);
+  for (uint32_t k = 0; k < 4; ++k) tc_mma_lo(m.tmem + d_col, a0 + 2 * k, b_lo + 2 * k, idesc, (accumulate | k) ? 1u : 0u);
   if (pair) {
+    const uint32_t a1 = desc_lo(m.sbase + a_off1);
 #pragma unroll
-    for (int k = 0; k < 4; ++k)
-      tc_mma(m.tmem + d_col, smem_desc(m.sbase + a_off1 + k * 32), smem_desc(b_addr + CHUNK_BYTES + k * 32), idesc, 1u);
+    for (uint32_t k = 0; k < 4; ++k) tc_mma_lo(m.tmem + d_col, a1 + 2 * k, b_lo + 1024 + 2 * k, idesc, 1u);
   }
   tc_commit(m.bars + 8 * (B_DONE0 + slot));
   T_SINCE(m.tacc, TM_ISSUE, tw);
