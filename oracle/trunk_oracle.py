@@ -477,3 +477,50 @@ def split_trunk_state_dict(sd: Mapping[str, torch.Tensor], prefix: str = "yemong
         i, name = rest.split(".", 1)
         out.setdefault(int(i), {})[name] = v.detach().to(torch.float32)
     return [out[i] for i in sorted(out)]
+
+
+def synthetic_trunk_state_dict(d_model: int = 128, n_blocks: int = 2, n_spatial: int = 2, n_temporal: int = 1,
+                               n_bullet_cross: int = 1, seed: int = 0) -> dict[str, torch.Tensor]:
+    """A state dict with the trunk's keys and shapes (models/yemong/griffin.py:335-368,
+    attention.py:51-74) and weights of the layers' fan-in scale, for timing the restatement where
+    neither the reference's modules nor their init are at hand.  NOT the reference's init: its
+    values match the reference in distribution only, which is all a timing needs."""
+    g = torch.Generator().manual_seed(seed)
+    D = d_model
+
+    def lin(out_f: int, in_f: int) -> torch.Tensor:
+        bound = in_f ** -0.5
+        return (torch.rand(out_f, in_f, generator=g) * 2 - 1) * bound
+
+    sd: dict[str, torch.Tensor] = {}
+    for i in range(n_blocks):
+        for j in range(n_spatial):
+            p = f"yemong_layers.{i}.spatial.{j}."
+            sd[p + "norm1.weight"] = torch.ones(D)
+            sd[p + "qkv.weight"] = lin(3 * D, D)
+            sd[p + "out_proj.weight"] = lin(D, D)
+            if j < n_bullet_cross:
+                sd[p + "norm_bullet.weight"] = torch.ones(D)
+                sd[p + "kv_bullet.weight"] = lin(2 * D, D)
+            sd[p + "norm2.weight"] = torch.ones(D)
+            sd[p + "ffn.gate_proj.weight"] = lin(4 * D, D)
+            sd[p + "ffn.up_proj.weight"] = lin(4 * D, D)
+            sd[p + "ffn.down_proj.weight"] = lin(D, 4 * D)
+        for j in range(n_temporal):
+            p = f"yemong_layers.{i}.temporal.{j}."
+            sd[p + "norm1.weight"] = torch.ones(D)
+            sd[p + "linear1.weight"] = lin(D, D)
+            sd[p + "conv.weight"] = (torch.rand(D, 1, 4, generator=g) * 2 - 1) * 0.5
+            sd[p + "conv.bias"] = (torch.rand(D, generator=g) * 2 - 1) * 0.5
+            sd[p + "rg_lru.log_lambda"] = torch.linspace(0, 4, D)
+            for n in ("linear_a", "linear_x"):
+                sd[p + f"rg_lru.{n}.weight"] = lin(D, D)
+                sd[p + f"rg_lru.{n}.bias"] = (torch.rand(D, generator=g) * 2 - 1) * D ** -0.5
+            sd[p + "linear2.weight"] = lin(D, D)
+            sd[p + "linear_out.weight"] = lin(D, D)
+            sd[p + "norm2.weight"] = torch.ones(D)
+            sd[p + "gated_mlp.gate_proj.weight"] = lin(4 * D, D)
+            sd[p + "gated_mlp.up_proj.weight"] = lin(4 * D, D)
+            sd[p + "gated_mlp.down_proj.weight"] = lin(D, 4 * D)
+            sd[f"yemong_layers.{i}.field_sub.{j}.weight"] = torch.eye(D)
+    return sd
