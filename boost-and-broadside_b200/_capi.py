@@ -94,6 +94,10 @@ EXPORTS = {
     "bnb_packed_temporal_bytes": (C.c_size_t, [C.c_int]),
     "bnb_pack_spatial": (C.c_int, [C.POINTER(SpatialWeights), C.c_int, C.c_int, _fp, _fp]),
     "bnb_pack_temporal": (C.c_int, [C.POINTER(TemporalWeights), C.c_int, _fp, _fp]),
+    "bnb_pack_trunk": (C.c_int, [C.POINTER(SpatialWeights), C.c_int, C.POINTER(TemporalWeights), C.c_int, C.c_int, C.c_int, _fp]),
+    "bnb_last_status": (C.c_int, []),
+    "bnb_clear_status": (None, []),
+    "bnb_debug_wait_test": (None, [C.c_int, C.c_int]),
 }
 
 
@@ -174,6 +178,9 @@ def stream_handle(device: torch.device) -> int:
 
 
 _scratch: dict[tuple[int, int], torch.Tensor] = {}
+# Scratch buffers that were outgrown.  They are never freed: launches still in flight on their
+# stream, and CUDA graphs captured while they were current, hold their address.
+_scratch_outgrown: list[torch.Tensor] = []
 _alloc_worker = None
 
 
@@ -204,7 +211,11 @@ def scratch_for(device: torch.device, nbytes: int) -> torch.Tensor:
     key = (device.index if device.index is not None else torch.cuda.current_device(), stream_handle(device))
     buf = _scratch.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = persistent_bytes(device, max(nbytes, 1 << 20))
+        if buf is not None:
+            _scratch_outgrown.append(buf)
+        # grow geometrically, so that a run settles on a few buffers however its batch sizes vary
+        want = max(nbytes, 1 << 20, 0 if buf is None else 2 * buf.numel() if 2 * buf.numel() < (8 << 30) else 0)
+        buf = persistent_bytes(device, want)
         _scratch[key] = buf
     return buf
 

@@ -7,6 +7,7 @@
 #include "bullet_slices.h"
 #include "exact_kernels.h"
 #include "launch_count.h"
+#include "validate.h"
 #include "tensor_kernels.h"
 
 namespace bnb {
@@ -15,44 +16,7 @@ std::atomic<unsigned long long> g_launches{0};
 
 namespace {
 
-inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
-
-int check_dims(int D, int H) {
-  if (D <= 0 || H <= 0 || D % H != 0) return BNB_ERR_BAD_ARGUMENT;
-  if (D % 32 != 0 || D > 128) return BNB_ERR_UNSUPPORTED_DIMS;
-  int dh = D / H;
-  if (dh != 8 && dh != 16 && dh != 32 && dh != 64) return BNB_ERR_UNSUPPORTED_DIMS;
-  return BNB_OK;
-}
-
-int check_batch(const BnbBatch* b) {
-  if (!b) return BNB_ERR_NULL_POINTER;
-  if (b->n_envs < 0 || b->total_tokens < 0 || b->total_ships < 0 || b->total_ships > b->total_tokens)
-    return BNB_ERR_BAD_ARGUMENT;
-  if ((b->tok_off == nullptr) != (b->ship_off == nullptr)) return BNB_ERR_BAD_ARGUMENT;
-  if (!b->tok_off) {
-    if (b->tokens_per_env < 0 || b->ships_per_env < 0 || b->ships_per_env > b->tokens_per_env)
-      return BNB_ERR_BAD_ARGUMENT;
-    if ((long long)b->n_envs * b->tokens_per_env != b->total_tokens) return BNB_ERR_BAD_ARGUMENT;
-    if ((long long)b->n_envs * b->ships_per_env != b->total_ships) return BNB_ERR_BAD_ARGUMENT;
-    if (b->max_tokens_per_env < b->tokens_per_env) return BNB_ERR_BAD_ARGUMENT;
-  } else if (b->max_tokens_per_env <= 0) {
-    return BNB_ERR_BAD_ARGUMENT;
-  }
-  return BNB_OK;
-}
-
-int check_spatial(const BnbSpatialWeights* w) {
-  if (!w) return BNB_ERR_NULL_POINTER;
-  const void* ps[] = {w->norm1_w, w->qkv_w, w->out_w, w->norm2_w, w->gate_w, w->up_w, w->down_w};
-  for (const void* p : ps) {
-    if (!p) return BNB_ERR_NULL_POINTER;
-    if (!aligned16(p)) return BNB_ERR_MISALIGNED;
-  }
-  if ((w->norm_bullet_w == nullptr) != (w->kv_bullet_w == nullptr)) return BNB_ERR_NULL_POINTER;
-  if (!aligned16(w->norm_bullet_w) || !aligned16(w->kv_bullet_w)) return BNB_ERR_MISALIGNED;
-  return BNB_OK;
-}
+using namespace bnb::validate;
 
 // bullets may be null (no cross-attention in this call); otherwise it must be complete.
 int check_bullets(const BnbBullets* b) {
@@ -150,6 +114,10 @@ const char* bnb_status_string(int status) {
     case BNB_ERR_SCRATCH_TOO_SMALL: return "scratch buffer smaller than bnb_scratch_bytes";
     case BNB_ERR_LAUNCH: return "CUDA launch failed";
     case BNB_ERR_NO_DEVICE: return "no CUDA device";
+    case BNB_STATUS_WAIT_WEIGHTS: return "a bounded wait for a weight copy ran out inside a tensor-core kernel";
+    case BNB_STATUS_WAIT_SLOT: return "a bounded wait for a free weight slot ran out inside a tensor-core kernel";
+    case BNB_STATUS_WAIT_MMA: return "a bounded wait for tensor-core results ran out inside a tensor-core kernel";
+    case BNB_STATUS_WAIT_OPERAND: return "a bounded wait for an operand ran out inside a tensor-core kernel";
     case BNB_ERR_EXCEEDS_STATIC_LIMIT: return "batch has more rows than the fixed scratch of the no-allocation entry point holds";
     default: return "unknown status";
   }
@@ -339,6 +307,30 @@ int bnb_pack_spatial(const BnbSpatialWeights* w, int d_model, int n_heads, void*
   if (!aligned16(packed)) return BNB_ERR_MISALIGNED;
   return bnb::tensor::pack_spatial(*w, d_model, n_heads, packed, static_cast<cudaStream_t>(stream));
 }
+
+int bnb_pack_trunk(const BnbSpatialWeights* spatial, int n_spatial_total, const BnbTemporalWeights* temporal,
+                   int n_temporal_total, int d_model, int n_heads, void* stream) {
+  int st = check_dims(d_model, n_heads);
+  if (st) return st;
+  if (n_spatial_total < 0 || n_temporal_total < 0) return BNB_ERR_BAD_ARGUMENT;
+  if ((n_spatial_total > 0 && !spatial) || (n_temporal_total > 0 && !temporal)) return BNB_ERR_NULL_POINTER;
+  for (int i = 0; i < n_spatial_total; ++i) {
+    if ((st = check_spatial(&spatial[i]))) return st;
+    if (!spatial[i].packed) return BNB_ERR_NULL_POINTER;
+    if (!aligned16(spatial[i].packed)) return BNB_ERR_MISALIGNED;
+  }
+  for (int i = 0; i < n_temporal_total; ++i) {
+    if ((st = check_temporal(&temporal[i], false))) return st;
+    if (!temporal[i].packed) return BNB_ERR_NULL_POINTER;
+    if (!aligned16(temporal[i].packed)) return BNB_ERR_MISALIGNED;
+  }
+  return bnb::tensor::pack_trunk(spatial, n_spatial_total, temporal, n_temporal_total, d_model, n_heads,
+                                 static_cast<cudaStream_t>(stream));
+}
+
+int bnb_last_status(void) { return bnb::tensor::last_status(); }
+void bnb_clear_status(void) { bnb::tensor::clear_status(); }
+void bnb_debug_wait_test(int skip_op, int poll_limit) { bnb::tensor::debug_wait_test(skip_op, poll_limit); }
 
 int bnb_pack_temporal(const BnbTemporalWeights* w, int d_model, void* packed, void* stream) {
   int st = check_dims(d_model, d_model / 32);

@@ -14,6 +14,7 @@
 
 #include "bnb_trunk.h"
 #include "exact_kernels.h"
+#include "validate.h"
 
 namespace {
 
@@ -30,13 +31,14 @@ constexpr int kMaxDevices = 64;
 std::mutex g_mutex;
 float* g_scratch_ptr[kMaxDevices] = {};  // device address of g_static_scratch on each GPU
 
-// Device address of the array on the current device; looked up once per device.
-int scratch_address(float** out) {
+// Device address of the array on the current device; looked up once per device (again with
+// `refresh`, after a launch failed on the cached address).
+int scratch_address(float** out, bool refresh) {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return BNB_ERR_NO_DEVICE;
   if (dev >= kMaxDevices) return BNB_ERR_BAD_ARGUMENT;
   std::lock_guard<std::mutex> lock(g_mutex);
-  if (!g_scratch_ptr[dev]) {
+  if (!g_scratch_ptr[dev] || refresh) {
     void* p = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
     if (e != cudaSuccess || !p) return BNB_ERR_LAUNCH;
@@ -46,38 +48,36 @@ int scratch_address(float** out) {
   return BNB_OK;
 }
 
-inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
-
 }  // namespace
 
 extern "C" int bnb_spatial_block_fwd_static(const BnbSpatialWeights* w, int d_model, int n_heads, const float* x,
                                             const uint8_t* alive, float* y, const BnbBatch* batch, int n_groups,
                                             int precision, void* stream) {
-  if (!w || !batch) return BNB_ERR_NULL_POINTER;
-  if (d_model <= 0 || n_heads <= 0 || d_model % n_heads != 0 || n_groups < 0) return BNB_ERR_BAD_ARGUMENT;
-  if (d_model % 32 != 0 || d_model > kMaxWidth) return BNB_ERR_UNSUPPORTED_DIMS;
-  const int dh = d_model / n_heads;
-  if (dh != 8 && dh != 16 && dh != 32 && dh != 64) return BNB_ERR_UNSUPPORTED_DIMS;
+  // the same checks, in the same order, as bnb_spatial_block_fwd
+  int st = bnb::validate::check_dims(d_model, n_heads);
+  if (st) return st;
+  if ((st = bnb::validate::check_batch(batch))) return st;
+  if ((st = bnb::validate::check_spatial(w))) return st;
+  if (n_groups < 0) return BNB_ERR_BAD_ARGUMENT;
   if (precision != BNB_FP32 && precision != BNB_BF16) return BNB_ERR_BAD_ARGUMENT;
-  if (batch->n_envs < 0 || batch->total_tokens < 0 || batch->total_ships < 0) return BNB_ERR_BAD_ARGUMENT;
-  if ((batch->tok_off == nullptr) != (batch->ship_off == nullptr)) return BNB_ERR_BAD_ARGUMENT;
-  if (!batch->tok_off && (long long)batch->n_envs * batch->tokens_per_env != batch->total_tokens)
-    return BNB_ERR_BAD_ARGUMENT;
   const long long n_rows = (long long)n_groups * batch->total_tokens;
   if (n_rows > kMaxRows) return BNB_ERR_EXCEEDS_STATIC_LIMIT;
   if (n_rows == 0) return BNB_OK;
-  const void* ps[] = {w->norm1_w, w->qkv_w, w->out_w, w->norm2_w, w->gate_w, w->up_w, w->down_w, x, y};
-  for (const void* p : ps) {
-    if (!p) return BNB_ERR_NULL_POINTER;
-    if (!aligned16(p)) return BNB_ERR_MISALIGNED;
-  }
-  float* scratch = nullptr;
-  int st = scratch_address(&scratch);
-  if (st) return st;
+  if (!x || !y) return BNB_ERR_NULL_POINTER;
+  if (!bnb::validate::aligned16(x) || !bnb::validate::aligned16(y)) return BNB_ERR_MISALIGNED;
   // Nothing in the array has to start at zero: the q/k/v rows and the attention rows this
   // call reads are all written by this call first.  What an earlier call left is ignored.
-  float* qkv = scratch;
-  float* o = scratch + (size_t)kMaxRows * 3 * kMaxWidth;
-  return bnb::exact::spatial_block(*w, d_model, n_heads, x, alive, nullptr, y, *batch, n_groups,
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    float* scratch = nullptr;
+    if ((st = scratch_address(&scratch, attempt == 1))) return st;
+    float* qkv = scratch;
+    float* o = scratch + (size_t)kMaxRows * 3 * kMaxWidth;
+    st = bnb::exact::spatial_block(*w, d_model, n_heads, x, alive, nullptr, y, *batch, n_groups,
                                    precision == BNB_BF16, qkv, o, nullptr, 0, static_cast<cudaStream_t>(stream));
+    // A launch that fails may mean the cached address belongs to a context that is gone (the
+    // caller reset the device): look the array up again, once.
+    if (st != BNB_ERR_LAUNCH) break;
+    (void)cudaGetLastError();
+  }
+  return st;
 }

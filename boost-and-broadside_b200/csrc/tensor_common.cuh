@@ -84,8 +84,16 @@ struct TrunkArgs {
   const int* row_index;
   const int* n_rows_dev;
   int* status;
+  // Test hooks of the bounded waits (0 / -1 in normal use): the poll limit of this launch, and the
+  // ring operation of CTA 0 whose weight copy the fetching lane leaves out, so that the issuing
+  // lane's wait for it runs out and the kernel has to drain and return with a status code.
+  int poll_limit;
+  int skip_op;
   SubLayer sub[MAX_SUBLAYERS];
 };
+// Process-wide values of the two hooks, set by bnb_debug_wait_test and copied into every launch.
+extern int g_debug_poll_limit;
+extern int g_debug_skip_op;
 
 // ------------------------------------------------------------------ PTX wrappers
 
@@ -106,10 +114,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after `limit` polls, records `code` and lets the caller go on.
+// Bounded wait: gives up after a number of polls, records `code` in the status word and lets the
+// caller go on.  `aborted` points at two shared ints: [0] is set once any wait of the CTA has run
+// out (later waits then give up after four polls, so the kernel drains quickly), [1] is the poll
+// limit of this launch.
+constexpr int DEFAULT_POLL_LIMIT = 1 << 20;
 __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* status, volatile int* aborted, int code) {
   if (mbar_try_wait(bar, parity)) return;   // the common case costs one instruction
-  const int limit = *aborted ? 4 : (1 << 20);
+  const int limit = aborted[0] ? 4 : aborted[1];
   for (int i = 0; i < limit; ++i)
     if (mbar_try_wait(bar, parity)) return;
   *aborted = 1;

@@ -31,6 +31,7 @@
 #include <cuda_fp16.h>
 
 #include <cstdlib>
+#include <mutex>
 #include <vector>
 
 #include "common.cuh"
@@ -40,6 +41,9 @@
 
 namespace bnb {
 namespace tensor {
+
+int g_debug_poll_limit = 0;
+int g_debug_skip_op = -1;
 
 // ------------------------------------------------------------------ weight image
 
@@ -129,6 +133,32 @@ __global__ void k_pack_temporal(BnbTemporalWeights w, uint8_t* out) {
   }
   pack_image(w, N_TEMPORAL_CHUNKS, out, [](const BnbTemporalWeights& ww, int c, int r) { return temporal_chunk_row(ww, c, r); },
              [](const BnbTemporalWeights& ww, int c) { return temporal_chunk_gain(ww, c); });
+}
+
+// Every image of a trunk in one launch: blockIdx.y selects the sublayer.
+constexpr int MAX_PACK_JOBS = 8;
+struct PackJobs {
+  int n_spatial, n_temporal;
+  BnbSpatialWeights sw[MAX_PACK_JOBS];
+  BnbTemporalWeights tw[MAX_PACK_JOBS];
+};
+__global__ void k_pack_trunk(const __grid_constant__ PackJobs jobs) {
+  const int j = blockIdx.y;
+  if (j < jobs.n_spatial) {
+    const BnbSpatialWeights& w = jobs.sw[j];
+    pack_image(w, N_SPATIAL_IMAGE, static_cast<uint8_t*>(const_cast<void*>(w.packed)),
+               [](const BnbSpatialWeights& ww, int c, int r) { return spatial_chunk_row(ww, c, r); },
+               [](const BnbSpatialWeights& ww, int c) { return spatial_chunk_gain(ww, c); });
+  } else {
+    const BnbTemporalWeights& w = jobs.tw[j - jobs.n_spatial];
+    uint8_t* out = static_cast<uint8_t*>(const_cast<void*>(w.packed));
+    if (blockIdx.x == 0 && threadIdx.x < D) {
+      float sg = 1.0f / (1.0f + expf(-w.log_lambda[threadIdx.x]));
+      reinterpret_cast<float*>(out + (size_t)N_TEMPORAL_CHUNKS * CHUNK_BYTES)[threadIdx.x] = kRglruC * log2f(sg);
+    }
+    pack_image(w, N_TEMPORAL_CHUNKS, out, [](const BnbTemporalWeights& ww, int c, int r) { return temporal_chunk_row(ww, c, r); },
+               [](const BnbTemporalWeights& ww, int c) { return temporal_chunk_gain(ww, c); });
+  }
 }
 
 // ------------------------------------------------------------------ the tile kernel
@@ -891,7 +921,7 @@ template <int NQ, int MAXKB>
 __global__ void __launch_bounds__(128 * NQ, NQ == 4 ? 1 : 2) k_trunk_tiles(const __grid_constant__ TrunkArgs args) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ int s_aborted;
+  __shared__ int s_aborted[2];
   __shared__ int s_items;
   __shared__ SubLayer s_sub[MAX_SUBLAYERS];  // kernel parameters are slow to index dynamically
   __shared__ uint16_t s_sched[MAX_SUBLAYERS * N_TEMPORAL_CHUNKS];  // (chunk << 6) | (sublayer << 2) | slot
@@ -916,7 +946,8 @@ __global__ void __launch_bounds__(128 * NQ, NQ == 4 ? 1 : 2) k_trunk_tiles(const
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_BAR + 48);
 
   if (tid == 0) {
-    s_aborted = (*args.status != 0) ? 1 : 0;
+    s_aborted[0] = (*args.status != 0) ? 1 : 0;
+    s_aborted[1] = args.poll_limit > 0 ? args.poll_limit : DEFAULT_POLL_LIMIT;
     mbar_init(smem_u32(&bars[0]), 1);
     mbar_init(smem_u32(&bars[1]), 1);
     mbar_init(smem_u32(&bars[2]), 1);
@@ -950,7 +981,7 @@ __global__ void __launch_bounds__(128 * NQ, NQ == 4 ? 1 : 2) k_trunk_tiles(const
     c.part = tid >> 7;
     c.lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     c.status = args.status;
-    c.aborted = &s_aborted;
+    c.aborted = s_aborted;
     c.acc_phase = 0;
     c.ss_part = reinterpret_cast<float*>(smem + OFF_SS);
 #ifdef BNB_TIMING
@@ -1513,6 +1544,84 @@ int pack_temporal(const BnbTemporalWeights& w, int d_model, void* packed, cudaSt
   return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
 }
 
+int pack_trunk(const BnbSpatialWeights* spatial, int n_spatial, const BnbTemporalWeights* temporal, int n_temporal,
+               int d_model, int n_heads, cudaStream_t st) {
+  if (d_model != D || n_heads != HEADS) return BNB_ERR_UNSUPPORTED_DIMS;
+  // as many launches as it takes at MAX_PACK_JOBS sublayers of each kind per launch (one for the
+  // trunks of the shipped profiles)
+  for (int s0 = 0, t0 = 0; s0 < n_spatial || t0 < n_temporal;) {
+    PackJobs jobs{};
+    for (; s0 < n_spatial && jobs.n_spatial < MAX_PACK_JOBS; ++s0) {
+      if (!spatial[s0].packed) return BNB_ERR_NULL_POINTER;
+      jobs.sw[jobs.n_spatial++] = spatial[s0];
+    }
+    for (; t0 < n_temporal && jobs.n_temporal < MAX_PACK_JOBS; ++t0) {
+      if (!temporal[t0].packed) return BNB_ERR_NULL_POINTER;
+      jobs.tw[jobs.n_temporal++] = temporal[t0];
+    }
+    count_launch();
+    k_pack_trunk<<<dim3(24, jobs.n_spatial + jobs.n_temporal), 256, 0, st>>>(jobs);
+    if (cudaGetLastError() != cudaSuccess) return BNB_ERR_LAUNCH;
+  }
+  return BNB_OK;
+}
+
+// ------------------------------------------------------------------ status word on the host
+//
+// The bounded waits record a code in the status word at the head of the scratch buffer.  Every
+// call copies that word to a pinned host word of its device when its kernels are done
+// (asynchronously, on the call's stream); whoever asks later -- the next call, or
+// bnb_last_status -- finds a non-zero code there and keeps it until it is cleared.
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_status_mutex;
+int* g_host_status[kMaxDevices] = {};
+int g_sticky_status[kMaxDevices] = {};
+
+void latch_status(int dev) {
+  if (g_host_status[dev]) {
+    const int v = *static_cast<volatile int*>(g_host_status[dev]);
+    if (v != 0 && g_sticky_status[dev] == 0) g_sticky_status[dev] = v;
+  }
+}
+}  // namespace
+
+int report_status(const int* status, cudaStream_t st) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return BNB_ERR_NO_DEVICE;
+  std::lock_guard<std::mutex> lock(g_status_mutex);
+  if (!g_host_status[dev]) {
+    // the first call on a device allocates the word; it should not come during a stream capture
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return BNB_OK;
+    void* p = nullptr;
+    if (cudaHostAlloc(&p, 64, cudaHostAllocDefault) != cudaSuccess) { (void)cudaGetLastError(); return BNB_OK; }
+    g_host_status[dev] = static_cast<int*>(p);
+    *g_host_status[dev] = 0;
+  }
+  latch_status(dev);
+  if (cudaMemcpyAsync(g_host_status[dev], status, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess) return BNB_ERR_LAUNCH;
+  return BNB_OK;
+}
+int last_status() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+  std::lock_guard<std::mutex> lock(g_status_mutex);
+  latch_status(dev);
+  return g_sticky_status[dev];
+}
+void clear_status() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return;
+  std::lock_guard<std::mutex> lock(g_status_mutex);
+  g_sticky_status[dev] = 0;
+  if (g_host_status[dev]) *g_host_status[dev] = 0;
+}
+void debug_wait_test(int skip_op, int poll_limit) {
+  g_debug_skip_op = skip_op;
+  g_debug_poll_limit = poll_limit;
+}
+
 static int launch(TrunkArgs& a, const BnbBatch& b, cudaStream_t st) {
   a.map = make_env_map(b);
   if (a.flat_rows) {
@@ -1531,6 +1640,8 @@ static int launch(TrunkArgs& a, const BnbBatch& b, cudaStream_t st) {
   }
   a.n_tiles = a.env_tiles * a.n_groups;
   a.has_fields = b.total_tokens > b.total_ships ? 1 : 0;
+  a.poll_limit = g_debug_poll_limit;
+  a.skip_op = g_debug_skip_op;
   if (a.n_tiles == 0) return BNB_OK;
   {
     bool fused = !a.flat_rows;
@@ -1805,7 +1916,8 @@ int spatial_block(const BnbSpatialWeights& w, int d_model, int n_heads, const fl
   int rc = make_plan(p, scratch, scratch_bytes, n_groups);
   if (rc) return rc;
   if ((rc = p.add_spatial(w, n_groups))) return rc;
-  return p.flush();
+  if ((rc = p.flush())) return rc;
+  return report_status(p.status, st);
 }
 
 int temporal_block(const BnbTemporalWeights& w, int d_model, const float* x, float* y, const float* hidden_in,
@@ -1816,7 +1928,8 @@ int temporal_block(const BnbTemporalWeights& w, int d_model, const float* x, flo
   int rc = make_plan(p, scratch, scratch_bytes, T);
   if (rc) return rc;
   if ((rc = p.add_temporal(w, hidden_in, hidden_out, T))) return rc;
-  return p.flush();
+  if ((rc = p.flush())) return rc;
+  return report_status(p.status, st);
 }
 
 int trunk(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal, int n_blocks, int n_spatial,
@@ -1846,7 +1959,7 @@ int trunk(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal, 
     if (cudaMemcpyAsync(y, x, (size_t)T * b.total_tokens * D * sizeof(float), cudaMemcpyDeviceToDevice, st) != cudaSuccess)
       return BNB_ERR_LAUNCH;
   }
-  return BNB_OK;
+  return report_status(p.status, st);
 }
 
 }  // namespace tensor

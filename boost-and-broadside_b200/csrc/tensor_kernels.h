@@ -25,6 +25,15 @@ size_t packed_spatial_bytes(int D);
 size_t packed_temporal_bytes(int D);
 int pack_spatial(const BnbSpatialWeights& w, int D, int H, void* packed, cudaStream_t st);
 int pack_temporal(const BnbTemporalWeights& w, int D, void* packed, cudaStream_t st);
+// Every weight image of a trunk (each struct's `packed` names its destination) in one launch.
+int pack_trunk(const BnbSpatialWeights* spatial, int n_spatial, const BnbTemporalWeights* temporal, int n_temporal,
+               int D, int H, cudaStream_t st);
+
+// Status word of the bounded waits, as last copied to the host for the current device (sticky
+// until cleared); and the test hooks that make a wait run out.
+int last_status();
+void clear_status();
+void debug_wait_test(int skip_op, int poll_limit);
 
 int spatial_block(const BnbSpatialWeights& w, int D, int H, const float* x, const uint8_t* alive,
                   const BnbBullets* bullets, float* y, const BnbBatch& b, int n_groups, void* scratch,

@@ -21,7 +21,7 @@ from torch import Tensor
 import os
 
 from .. import _capi
-from ._weights import N_SPATIAL, N_TEMPORAL, packed_image, spatial_struct_from, temporal_struct_from
+from ._weights import N_SPATIAL, N_TEMPORAL, image_buffer, packed_image, spatial_struct_from, temporal_struct_from
 
 # geom: the integers of a call, in this order
 (G_BLOCKS, G_SPATIAL, G_TEMPORAL, G_HEADS, G_BULLET_CROSS, G_FIELD_SUB, G_ENVS, G_TOKENS_PER_ENV, G_SHIPS_PER_ENV,
@@ -36,6 +36,18 @@ def _debug_check(fn: str, dev: torch.device, precision: int) -> None:
         st = _capi.tensor_engine_status(dev)
         if 100 < st < 200:   # the ST_TIMEOUT_* codes; other values are scratch data of the exact engine
             raise RuntimeError(f"{fn}: a bounded wait of the tensor-core kernels ran out (code {st})")
+
+
+def _raise_pending_status(dev: torch.device) -> None:
+    """A bounded wait of an earlier call on this device ran out (its kernels drained and its
+    outputs were garbage): say so once, at the next call, without synchronising."""
+    with torch.cuda.device(dev):
+        st = _capi.lib.bnb_last_status()
+        if st:
+            _capi.lib.bnb_clear_status()
+            raise RuntimeError(
+                f"an earlier tensor-core call on {dev} gave up a bounded wait: {_capi.lib.bnb_status_string(st).decode()} "
+                f"(status {st}); its outputs, and any state carried from them, are invalid")
 
 
 def uniform_geom(n_envs: int, tokens: int, ships: int) -> List[int]:
@@ -100,19 +112,24 @@ def trunk_forward(
                 ts = list(weights[pos : pos + n])
                 pos += n
                 sw[i * n_spatial + j] = spatial_struct_from(
-                    ts, dev, packed_image("spatial", ts, n_heads, dev, precision, engine))
+                    ts, dev, image_buffer("spatial", ts, n_heads, dev, precision, engine))
             for j in range(n_temporal):
                 n = N_TEMPORAL + (1 if field_sub else 0)
                 ts = list(weights[pos : pos + n])
                 pos += n
                 tw[i * n_temporal + j] = temporal_struct_from(
-                    ts, dev, packed_image("temporal", ts, 4, dev, precision, engine))
+                    ts, dev, image_buffer("temporal", ts, 4, dev, precision, engine))
         if pos != len(weights):
             raise RuntimeError(f"expected {pos} parameter tensors for this trunk structure, got {len(weights)}")
         bul = _capi.BulletArgs(bullets if n_cross > 0 else None, bullet_mask, T * batch.n_envs, D)
         nbytes = _capi.lib.bnb_scratch_bytes(D, batch, T, bul.per_env)
         scratch = _capi.scratch_for(dev, nbytes)
         stream = _capi.stream_handle(dev)
+        _raise_pending_status(dev)
+        ns_total, nt_total = n_blocks * n_spatial, n_blocks * n_temporal
+        if all(sw[i].packed for i in range(ns_total)) and all(tw[i].packed for i in range(nt_total)) and ns_total + nt_total > 0:
+            # the weight images of the whole trunk, rewritten from the live parameters on every call
+            _capi.check("bnb_pack_trunk", _capi.lib.bnb_pack_trunk(sw, ns_total, tw, nt_total, D, n_heads, stream))
         if geom[G_TIMESTEPS] == 0:
             fn = "bnb_trunk_step"
             st = _capi.lib.bnb_trunk_step(
@@ -161,6 +178,7 @@ def spatial_forward(
         bul = _capi.BulletArgs(bullets if len(ts) > N_SPATIAL else None, bullet_mask, B, D)
         nbytes = _capi.lib.bnb_scratch_bytes(D, batch, 1, bul.per_env)
         scratch = _capi.scratch_for(dev, nbytes)
+        _raise_pending_status(dev)
         w = spatial_struct_from(ts, dev, packed_image("spatial", ts, n_heads, dev, precision, engine))
         st = _capi.lib.bnb_spatial_block_fwd(
             w, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8), bul.arg, y.data_ptr(), batch, 1, precision, engine,

@@ -70,17 +70,32 @@ def temporal_struct(tb, sub, dev: torch.device, packed: int | None = None) -> _c
     return temporal_struct_from(temporal_tensors(tb, sub), dev, packed)
 
 
-# (kind, device, ids of the parameter tensors) -> (stamp, image buffer, weak references)
+# (kind, device, ids of the parameter tensors) -> (image buffer, weak references)
 _images: dict[tuple, tuple] = {}
+# Buffers whose parameters were garbage-collected.  They are kept (a bounded number of them): a
+# launch still in flight, or a captured CUDA graph, may hold their address.
+_retired: list[torch.Tensor] = []
+_RETIRED_MAX = 512
 
 
-def packed_image(kind: str, ts: list[torch.Tensor], n_heads: int, dev: torch.device, precision: int, engine: int):
-    """Device address of the tensor-core weight image of one sublayer, or None.
+def _retire(key: tuple) -> None:
+    hit = _images.pop(key, None)
+    if hit is not None:
+        _retired.append(hit[0])
+        if len(_retired) > _RETIRED_MAX:
+            del _retired[0]
 
-    The image is derived data: it is rebuilt whenever a parameter's storage or version
-    changes, lives in a process-wide cache that drops an entry when one of its parameters is
-    garbage-collected, and is never part of a state_dict.
-    """
+
+def image_buffer(kind: str, ts: list[torch.Tensor], n_heads: int, dev: torch.device, precision: int, engine: int):
+    """Device address of the buffer that holds the tensor-core weight image of one sublayer, or
+    None when the call does not use the tensor engine.  Nothing is packed here: the image is
+    written by ``bnb_pack_trunk`` / ``bnb_pack_*`` **on every call**, on the call's stream, so it
+    cannot go stale -- not after an optimizer step, not after ``p.data.copy_()`` (which bumps no
+    version counter; the reference's running-average policy is updated that way,
+    train/rl/opponents.py:112), and not in a replayed CUDA graph (the pack launch is part of the
+    captured work and re-reads the live float32 parameters).  The buffer itself is persistent and
+    keyed on the identity of the parameter tensors; it is derived data and never part of a
+    state_dict."""
     if precision != _capi.BNB_BF16 or engine == _capi.ENGINE_SIMT:
         return None
     D = ts[0].shape[-1]
@@ -90,20 +105,30 @@ def packed_image(kind: str, ts: list[torch.Tensor], n_heads: int, dev: torch.dev
     if nbytes == 0:
         return None
     key = (kind, dev.index, tuple(id(t) for t in ts))
-    stamp = tuple((t.data_ptr(), t._version) for t in ts)
     hit = _images.get(key)
-    if hit is not None and not all(r() is t for r, t in zip(hit[2], ts)):
-        hit = None  # an id was reused by another tensor
-    if hit is not None and hit[0] == stamp:
-        return hit[1].data_ptr()
-    buf = hit[1] if hit is not None else _capi.persistent_bytes(dev, nbytes)
+    if hit is not None and not all(r() is t for r, t in zip(hit[1], ts)):
+        _retire(key)  # an id was reused by another tensor
+        hit = None
+    if hit is None:
+        buf = _capi.persistent_bytes(dev, nbytes)
+        refs = tuple(weakref.ref(t, lambda _r, k=key: _retire(k)) for t in ts)
+        hit = (buf, refs)
+        _images[key] = hit
+    return hit[0].data_ptr()
+
+
+def packed_image(kind: str, ts: list[torch.Tensor], n_heads: int, dev: torch.device, precision: int, engine: int):
+    """``image_buffer`` plus the pack launch of this one sublayer (callers that run a single
+    sublayer; a trunk call packs all of its sublayers with one ``bnb_pack_trunk`` instead)."""
+    ptr = image_buffer(kind, ts, n_heads, dev, precision, engine)
+    if ptr is None:
+        return None
+    D = ts[0].shape[-1]
     stream = _capi.stream_handle(dev)
     if kind == "spatial":
-        st = _capi.lib.bnb_pack_spatial(spatial_struct_from(ts, dev), D, n_heads, buf.data_ptr(), stream)
+        st = _capi.lib.bnb_pack_spatial(spatial_struct_from(ts, dev), D, n_heads, ptr, stream)
         _capi.check("bnb_pack_spatial", st)
     else:
-        st = _capi.lib.bnb_pack_temporal(temporal_struct_from(ts, dev), D, buf.data_ptr(), stream)
+        st = _capi.lib.bnb_pack_temporal(temporal_struct_from(ts, dev), D, ptr, stream)
         _capi.check("bnb_pack_temporal", st)
-    refs = tuple(weakref.ref(t, lambda _r, k=key: _images.pop(k, None)) for t in ts)
-    _images[key] = (stamp, buf, refs)
-    return buf.data_ptr()
+    return ptr

@@ -113,6 +113,12 @@ class YemongTrunk(nn.Module):
         if torch.is_grad_enabled() and (x.requires_grad or hidden.requires_grad):
             raise NotImplementedError("the CUDA trunk is forward-only; call it under torch.no_grad()")
 
+    @staticmethod
+    def _check_mask(mask: torch.Tensor | None, shape: tuple, what: str) -> None:
+        """Masks are read on the device one byte per element: a short one would be read out of bounds."""
+        if mask is not None and tuple(mask.shape) != tuple(shape):
+            raise RuntimeError(f"{what} must have shape {tuple(shape)}, got {tuple(mask.shape)}")
+
     def step(
         self,
         x: torch.Tensor,  # (B, N+M, D)
@@ -127,8 +133,10 @@ class YemongTrunk(nn.Module):
         self._check(x, hidden)
         B, NM, D = x.shape
         n_rec = hidden.shape[1] // B if self.n_hidden_layers else NM
-        if self.n_hidden_layers and hidden.shape[1] != B * n_rec:
-            raise RuntimeError("hidden rows are not a multiple of the environment count")
+        if self.n_hidden_layers and (hidden.shape[1] != B * n_rec or n_rec > NM):
+            raise RuntimeError(f"hidden has {hidden.shape[1]} rows: not a multiple of the {B} environments, or more than their tokens")
+        self._check_mask(alive, (B, NM), "alive")
+        self._check_mask(reset_env, (B,), "reset_env")
         batch = _ops.uniform_geom(B, NM, n_rec)
         y, nh = run_trunk(list(self.yemong_layers), self.n_heads, x.reshape(B * NM, D),
                           None if alive is None else alive.reshape(-1), hidden, None, reset_env, batch, None, engine,
@@ -149,6 +157,10 @@ class YemongTrunk(nn.Module):
         self._check(x, initial_hidden)
         T, B, NM, D = x.shape
         n_rec = initial_hidden.shape[1] // B if self.n_hidden_layers else NM
+        if self.n_hidden_layers and (initial_hidden.shape[1] != B * n_rec or n_rec > NM):
+            raise RuntimeError(f"initial_hidden has {initial_hidden.shape[1]} rows: not a multiple of the {B} environments, or more than their tokens")
+        self._check_mask(alive_mask, (T, B, NM), "alive_mask")
+        self._check_mask(done_mask, (T, B), "done_mask")
         batch = _ops.uniform_geom(B, NM, n_rec)
         y, nh = run_trunk(list(self.yemong_layers), self.n_heads, x.reshape(T, B * NM, D),
                           None if alive_mask is None else alive_mask.reshape(T, -1), initial_hidden, done_mask, None,
@@ -168,8 +180,9 @@ class YemongTrunk(nn.Module):
         """One step over environments of different sizes (ships first, then fields, per env)."""
         self._check(x, hidden)
         batch, offsets = ragged.build(x.device)
-        if x.shape[0] != batch[4] or hidden.shape[1] != batch[5]:
+        if x.dim() != 2 or x.shape[0] != batch[4] or hidden.shape[1] != batch[5]:
             raise RuntimeError("x / hidden rows do not match the ragged batch")
+        self._check_mask(alive, (batch[4],), "alive")
         y, nh = run_trunk(list(self.yemong_layers), self.n_heads, x, alive, hidden, None, None, batch, None, engine,
                           offsets=offsets, bullets=bullets, bullet_mask=bullet_mask)
         return y, nh

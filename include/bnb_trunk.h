@@ -44,8 +44,31 @@ typedef enum {
   BNB_ERR_SCRATCH_TOO_SMALL = 6,
   BNB_ERR_LAUNCH = 7,             /* the CUDA runtime refused a launch; see cudaGetLastError */
   BNB_ERR_NO_DEVICE = 8,
-  BNB_ERR_EXCEEDS_STATIC_LIMIT = 9 /* more rows than bnb_spatial_block_fwd_static's fixed scratch holds */
+  BNB_ERR_EXCEEDS_STATIC_LIMIT = 9, /* more rows than bnb_spatial_block_fwd_static's fixed scratch holds */
+  /* Codes a tensor-core kernel leaves in the status word (below) when one of its bounded waits
+   * ran out; entry points never return them, bnb_last_status does. */
+  BNB_STATUS_WAIT_WEIGHTS = 101,  /* a weight copy did not land */
+  BNB_STATUS_WAIT_SLOT = 102,     /* a weight slot (or the key/value area) was not released */
+  BNB_STATUS_WAIT_MMA = 103,      /* tensor-core results did not arrive */
+  BNB_STATUS_WAIT_OPERAND = 104   /* an operand was not posted */
 } BnbStatus;
+
+/* The status word.  Every wait inside the tensor-core kernels is bounded.  A wait that runs out
+ * writes one of the BNB_STATUS_WAIT_* codes into the first 4 bytes of the call's scratch buffer
+ * (an int at byte offset 0; each call zeroes it first), the kernel drains and returns, and the
+ * call's outputs are then unspecified.  The entry point has returned BNB_OK long before, so every
+ * BNB_BF16 call also copies the word to a pinned host word of its device, asynchronously on its
+ * stream; bnb_last_status() reports the first non-zero code seen there since the last
+ * bnb_clear_status().  The first BNB_BF16 call on a device allocates the host word and should
+ * come before any stream capture (a call that finds itself capturing without it skips the copy). */
+int bnb_last_status(void);
+void bnb_clear_status(void);
+
+/* Test hook for the above, never needed in production: the next launches of the fused tile
+ * kernel use `poll_limit` polls per wait (0 = default) and CTA 0 leaves out the weight copy of
+ * its `skip_op`-th ring operation (-1 = none), so that exactly one wait runs out, nothing
+ * faults or spins, and the status word reads BNB_STATUS_WAIT_WEIGHTS. */
+void bnb_debug_wait_test(int skip_op, int poll_limit);
 
 typedef enum { BNB_FP32 = 0, BNB_BF16 = 1 } BnbPrecision;
 
@@ -269,6 +292,14 @@ size_t bnb_packed_temporal_bytes(int d_model);
  * No counterpart in the reference (it casts weights per call under autocast). */
 int bnb_pack_spatial(const BnbSpatialWeights* w, int d_model, int n_heads, void* packed, void* stream);
 int bnb_pack_temporal(const BnbTemporalWeights* w, int d_model, void* packed, void* stream);
+
+/* The same for every sublayer of a trunk in one launch: each struct's `packed` names the
+ * destination of its image.  Cheap enough (about 10 MB of traffic) to run before every call, which
+ * is what the Python binding does: an image then never goes stale, whatever updated the
+ * parameters (an optimizer step, an in-place copy that bumps no version counter, a replayed CUDA
+ * graph whose captured work includes this launch). */
+int bnb_pack_trunk(const BnbSpatialWeights* spatial, int n_spatial_total, const BnbTemporalWeights* temporal,
+                   int n_temporal_total, int d_model, int n_heads, void* stream);
 
 #ifdef __cplusplus
 }

@@ -129,6 +129,40 @@ def test_block_api_matches_policy_loop(mode):
     assert_close(nh, g["hidden_" + mode], mode, "block loop hidden")
 
 
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("name", SEQ_CASES)
+def test_block_sequence_api_matches_policy_loop(name, mode):
+    """YemongBlock.sequence (griffin.py:419-472) called directly and chained as
+    models/yemong/policy.py:455-478 does -- slices of the packed hidden state, done mask, the
+    recurrent-token count -- reproduces the reference's sequence output; its returned final states
+    equal the trunk's."""
+    from boost_and_broadside_b200 import CONV_KERNEL
+
+    g = golden(name)
+    trunk = build_trunk(g["dims"], g).to(DEV)
+    x, alive, hidden, done = _to(g["x"]), _to(g["alive"]), _to(g["hidden"]), _to(g["done"])
+    T, B, NM, D = x.shape
+    L, R, _ = hidden.shape
+    n_rec = R // B
+    n_t = trunk.yemong_layers[0].n_temporal
+    with torch.no_grad(), autocast_for(mode, DEV):
+        hs = hidden[:, :, :D]
+        cs = hidden[:, :, D:].reshape(L, R, CONV_KERNEL - 1, D)
+        cur = x
+        hs_out, cs_out = [], []
+        for i, layer in enumerate(trunk.yemong_layers):
+            sl = slice(i * n_t, (i + 1) * n_t)
+            cur, h, cb = layer.sequence(cur, alive, hs[sl], cs[sl], done, n_rec, None, None)
+            assert h.shape == (n_t, R, D) and cb.shape == (n_t, R, CONV_KERNEL - 1, D)
+            hs_out.append(h)
+            cs_out.append(cb)
+        nh = torch.cat([torch.cat(hs_out), torch.cat(cs_out).reshape(L, R, (CONV_KERNEL - 1) * D)], dim=-1)
+        y_trunk, nh_trunk = trunk.sequence(x, alive, hidden, done)
+    assert_close(cur, g["y_" + mode], mode, name + " block loop y")
+    assert_close(nh, g["hidden_" + mode], mode, name + " block loop hidden")
+    assert torch.equal(cur, y_trunk) and torch.equal(nh, nh_trunk)
+
+
 # ------------------------------------------------------------------ configurations vs the oracle
 
 
