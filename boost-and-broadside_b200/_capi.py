@@ -61,6 +61,7 @@ EXPORTS = {
     "bnb_abi_version": (C.c_int, []),
     "bnb_status_string": (C.c_char_p, [C.c_int]),
     "bnb_launch_count": (C.c_ulonglong, []),
+    "bnb_auto_fallback_count": (C.c_ulonglong, []),
     "bnb_supported": (C.c_int, [C.c_int] * 5),
     "bnb_plan_tiles": (C.c_int, [_fp, C.c_int, _fp, _fp, C.c_int, C.POINTER(C.c_int)]),
     "bnb_scratch_bytes": (C.c_size_t, [C.c_int, C.POINTER(Batch), C.c_int, C.c_int]),
@@ -94,6 +95,8 @@ EXPORTS = {
     "bnb_packed_temporal_bytes": (C.c_size_t, [C.c_int]),
     "bnb_pack_spatial": (C.c_int, [C.POINTER(SpatialWeights), C.c_int, C.c_int, _fp, _fp]),
     "bnb_pack_temporal": (C.c_int, [C.POINTER(TemporalWeights), C.c_int, _fp, _fp]),
+    "bnb_gated_mlp_fwd": (C.c_int, [_fp, _fp, _fp, C.c_int, _fp, _fp, C.c_int, C.c_int, _fp]),
+    "bnb_rglru_fwd": (C.c_int, [_fp] * 5 + [C.c_int, _fp, _fp, _fp, _fp, _fp, C.c_int, C.c_int, C.c_int, _fp]),
     "bnb_pack_trunk": (C.c_int, [C.POINTER(SpatialWeights), C.c_int, C.POINTER(TemporalWeights), C.c_int, C.c_int, C.c_int, _fp]),
     "bnb_last_status": (C.c_int, []),
     "bnb_clear_status": (None, []),
@@ -133,6 +136,27 @@ def check(fn: str, status: int) -> None:
         if status == 3:  # BNB_ERR_UNSUPPORTED_DIMS
             raise ValueError(f"{fn}: {lib.bnb_status_string(status).decode()}")
         raise BnbError(fn, status)
+
+
+_fallbacks_seen = 0
+_fallback_warned = False
+
+
+def note_engine_choice(what: str) -> None:
+    """Warn, once per process, when a bfloat16 call left to BNB_ENGINE_AUTO was served by the exact
+    kernels: the result is right, the speed is several times lower, and nothing else says so."""
+    global _fallbacks_seen, _fallback_warned
+    n = lib.bnb_auto_fallback_count()
+    if n != _fallbacks_seen:
+        _fallbacks_seen = n
+        if not _fallback_warned:
+            _fallback_warned = True
+            import warnings
+
+            warnings.warn(
+                f"{what}: this bfloat16 call runs on the exact (SIMT) kernels, not the fused tensor-core kernels, "
+                "because they are not built for its shape (d_model 128 with 4 heads, at most 512 tokens per "
+                "environment); bnb_auto_fallback_count() counts such calls", RuntimeWarning, stacklevel=3)
 
 
 def ptr(t: Optional[torch.Tensor]) -> Optional[int]:

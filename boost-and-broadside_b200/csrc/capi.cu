@@ -82,10 +82,16 @@ int carve(void* scratch, size_t bytes, size_t n_rows, int D, long long total_env
   return BNB_OK;
 }
 
+// BNB_BF16 calls that asked for BNB_ENGINE_AUTO and were served by the exact kernels because the
+// tensor-core kernels are not built for their shape (read by bnb_auto_fallback_count).
+std::atomic<unsigned long long> g_auto_fallbacks{0};
+
 bool use_tensor(int precision, int engine, int D, int H, const BnbBatch* b, const BnbBullets* bullets) {
   if (precision != BNB_BF16 || engine == BNB_ENGINE_SIMT) return false;
-  if (bullets && !bnb::tensor::supported_bullets(*b, bullets->per_env)) return false;
-  return bnb::tensor::supported_batch(D, H, *b);
+  bool ok = bnb::tensor::supported_batch(D, H, *b);
+  if (ok && bullets && !bnb::tensor::supported_bullets(*b, bullets->per_env)) ok = false;
+  if (!ok && engine == BNB_ENGINE_AUTO) g_auto_fallbacks.fetch_add(1, std::memory_order_relaxed);
+  return ok;
 }
 
 // The tensor engine needs the packed weight image of every sublayer it runs.
@@ -102,6 +108,7 @@ extern "C" {
 int bnb_abi_version(void) { return BNB_ABI_VERSION; }
 
 unsigned long long bnb_launch_count(void) { return bnb::g_launches.load(std::memory_order_relaxed); }
+unsigned long long bnb_auto_fallback_count(void) { return g_auto_fallbacks.load(std::memory_order_relaxed); }
 
 const char* bnb_status_string(int status) {
   switch (status) {
@@ -294,6 +301,37 @@ int bnb_reset_hidden(const float* hidden_in, float* hidden_out, const uint8_t* d
   if (!aligned16(hidden_in) || !aligned16(hidden_out)) return BNB_ERR_MISALIGNED;
   return bnb::exact::reset_hidden(hidden_in, hidden_out, done, n_slots, d_model, *batch,
                                   static_cast<cudaStream_t>(stream));
+}
+
+int bnb_gated_mlp_fwd(const float* gate_w, const float* up_w, const float* down_w, int d_model, const float* x,
+                      float* y, int n_rows, int precision, void* stream) {
+  if (d_model <= 0 || d_model % 32 != 0 || d_model > 128) return BNB_ERR_UNSUPPORTED_DIMS;
+  if (n_rows < 0) return BNB_ERR_BAD_ARGUMENT;
+  if (precision != BNB_FP32 && precision != BNB_BF16) return BNB_ERR_BAD_ARGUMENT;
+  if (n_rows == 0) return BNB_OK;
+  const void* ps[] = {gate_w, up_w, down_w, x, y};
+  for (const void* p : ps) {
+    if (!p) return BNB_ERR_NULL_POINTER;
+    if (!aligned16(p)) return BNB_ERR_MISALIGNED;
+  }
+  return bnb::exact::gated_mlp(gate_w, up_w, down_w, d_model, x, y, n_rows, precision == BNB_BF16,
+                               static_cast<cudaStream_t>(stream));
+}
+
+int bnb_rglru_fwd(const float* a_w, const float* a_b, const float* x_w, const float* x_b, const float* log_lambda,
+                  int d_model, const float* x, float* y, const float* h0, float* h_out, const uint8_t* done,
+                  int n_rows, int timesteps, int precision, void* stream) {
+  if (d_model <= 0 || d_model % 32 != 0 || d_model > 128) return BNB_ERR_UNSUPPORTED_DIMS;
+  if (n_rows < 0 || timesteps < 1) return BNB_ERR_BAD_ARGUMENT;
+  if (precision != BNB_FP32 && precision != BNB_BF16) return BNB_ERR_BAD_ARGUMENT;
+  if (n_rows == 0) return BNB_OK;
+  const void* ps[] = {a_w, a_b, x_w, x_b, log_lambda, x, y, h0, h_out};
+  for (const void* p : ps) {
+    if (!p) return BNB_ERR_NULL_POINTER;
+    if (!aligned16(p)) return BNB_ERR_MISALIGNED;
+  }
+  return bnb::exact::rglru(a_w, a_b, x_w, x_b, log_lambda, d_model, x, y, h0, h_out, done, n_rows, timesteps,
+                           precision == BNB_BF16, static_cast<cudaStream_t>(stream));
 }
 
 size_t bnb_packed_spatial_bytes(int d_model) { return bnb::tensor::packed_spatial_bytes(d_model); }

@@ -610,6 +610,119 @@ __global__ void k_reset_hidden(const float* __restrict__ in, float* __restrict__
   }
 }
 
+// ------------------------------------------------------------------ GatedMLP and RG-LRU on their own
+//
+// The two sub-modules the reference's own tests call directly (models/yemong/attention.py:21-37,
+// griffin.py:169-219).  Inside a trunk call they run fused in the kernels above; these two kernels
+// serve the module methods GatedMLP.forward, RGLRU._step and RGLRU.forward_sequence.
+
+// y = down(gelu(gate x) * up x); a Linear casts its input to bf16 under autocast, and so does EMU.
+template <bool EMU>
+__global__ void __launch_bounds__(NTHREADS)
+k_gated_mlp(const float* __restrict__ x, float* __restrict__ y, int n_rows, int D,
+            const float* __restrict__ Wg, const float* __restrict__ Wu, const float* __restrict__ Wd) {
+  extern __shared__ __align__(16) float smem[];
+  const int ld = max(D, NCHUNK) + 4;
+  float* X = smem;
+  float* P = X + ROWS * ld;
+  float* Ws = P + ROWS * ld;
+  const int row0 = blockIdx.x * ROWS;
+  const int n_valid = min(ROWS, n_rows - row0);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  for (int idx = tid; idx < ROWS * (D / 4); idx += NTHREADS) {
+    int r = idx / (D / 4), q = idx % (D / 4);
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < n_valid) v = *reinterpret_cast<const float4*>(x + (size_t)(row0 + r) * D + q * 4);
+    v.x = rnd<EMU>(v.x); v.y = rnd<EMU>(v.y); v.z = rnd<EMU>(v.z); v.w = rnd<EMU>(v.w);
+    *reinterpret_cast<float4*>(X + r * ld + q * 4) = v;
+  }
+  __syncthreads();
+  float down[4][4];
+  tile_gated_mlp<EMU>(X, P, ld, D, Wg, Wu, Wd, Ws, down);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int r = 4 * warp + i;
+    if (r < n_valid)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        int c = lane + 32 * j;
+        if (c < D) y[(size_t)(row0 + r) * D + c] = rnd<EMU>(down[i][j]);
+      }
+  }
+}
+
+// The RG-LRU over T steps of n_rows independent rows, time-major x (T, n_rows, D):
+// r = sigmoid(W_a x + b_a), i = sigmoid(W_x x + b_x), a = sigmoid(Lambda)^(8 r),
+// h = a h + sqrt(max((1 - a)(1 + a), 1e-6)) (i x); a_t := 0 where done[t - 1] (griffin.py:213-218).
+// The output of a step is its state.  Evaluated as the sequential loop the reference pins its
+// parallel scan against.
+template <bool EMU>
+__global__ void __launch_bounds__(NTHREADS)
+k_rglru(const float* __restrict__ x, float* __restrict__ y, const float* __restrict__ h0, float* __restrict__ h_out,
+        const uint8_t* __restrict__ done, int n_rows, int T, int D, const float* __restrict__ Wa,
+        const float* __restrict__ ba, const float* __restrict__ Wx, const float* __restrict__ bx,
+        const float* __restrict__ log_lambda) {
+  extern __shared__ __align__(16) float smem[];
+  const int ld = max(D, NCHUNK) + 4;
+  float* X = smem;                 // x_t, float32 (the product i * x uses the unrounded input)
+  float* P = X + ROWS * ld;        // x_t as the Linear layers see it
+  float* Ws = P + ROWS * ld;
+  const int row0 = blockIdx.x * ROWS;
+  const int n_valid = min(ROWS, n_rows - row0);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  float hst[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      int r = 4 * warp + i, c = lane + 32 * j;
+      hst[i][j] = (r < n_valid && c < D) ? h0[(size_t)(row0 + r) * D + c] : 0.f;
+    }
+  for (int t = 0; t < T; ++t) {
+    __syncthreads();
+    for (int idx = tid; idx < ROWS * (D / 4); idx += NTHREADS) {
+      int r = idx / (D / 4), q = idx % (D / 4);
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (r < n_valid) v = *reinterpret_cast<const float4*>(x + ((size_t)t * n_rows + row0 + r) * D + q * 4);
+      *reinterpret_cast<float4*>(X + r * ld + q * 4) = v;
+      v.x = rnd<EMU>(v.x); v.y = rnd<EMU>(v.y); v.z = rnd<EMU>(v.z); v.w = rnd<EMU>(v.w);
+      *reinterpret_cast<float4*>(P + r * ld + q * 4) = v;
+    }
+    __syncthreads();
+    float ga[4][4], gx[4][4];
+    zero_acc(ga);
+    tile_linear<EMU>(P, ld, Wa, D, D, D, Ws, ga);
+    zero_acc(gx);
+    tile_linear<EMU>(P, ld, Wx, D, D, D, Ws, gx);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      int r = 4 * warp + i;
+      bool reset = done && t >= 1 && r < n_valid && done[(size_t)(t - 1) * n_rows + row0 + r] != 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        int c = lane + 32 * j;
+        if (r < n_valid && c < D) {
+          float rg = rnd<EMU>(sigmoidf_(rnd<EMU>(ga[i][j] + rnd<EMU>(ba[c]))));
+          float ig = rnd<EMU>(sigmoidf_(rnd<EMU>(gx[i][j] + rnd<EMU>(bx[c]))));
+          float a = powf(sigmoidf_(log_lambda[c]), kRglruC * rg);
+          float gate = sqrtf(fmaxf((1.0f - a) * (1.0f + a), kGateFloor));
+          float bb = gate * (ig * X[r * ld + c]);
+          if (reset) a = 0.f;
+          hst[i][j] = a * hst[i][j] + bb;
+          y[((size_t)t * n_rows + row0 + r) * D + c] = hst[i][j];
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      int r = 4 * warp + i, c = lane + 32 * j;
+      if (r < n_valid && c < D) h_out[(size_t)(row0 + r) * D + c] = hst[i][j];
+    }
+}
+
 // ------------------------------------------------------------------ host launchers
 
 static size_t smem_rows(int D, int tiles) {
@@ -715,6 +828,39 @@ int temporal_block(const BnbTemporalWeights& w, int D, const float* x, float* y,
                    int T, bool emulate_bf16, cudaStream_t st) {
   return emulate_bf16 ? temporal_impl<true>(w, D, x, y, hidden_in, hidden_out, done, reset_env, b, T, st)
                       : temporal_impl<false>(w, D, x, y, hidden_in, hidden_out, done, reset_env, b, T, st);
+}
+
+template <bool EMU>
+static int gated_mlp_impl(const float* gate_w, const float* up_w, const float* down_w, int D, const float* x, float* y,
+                          int n_rows, cudaStream_t st) {
+  size_t sm = smem_rows(D, 2);
+  if (!opt_in(k_gated_mlp<EMU>, sm)) return BNB_ERR_LAUNCH;
+  count_launch();
+  k_gated_mlp<EMU><<<(n_rows + ROWS - 1) / ROWS, NTHREADS, sm, st>>>(x, y, n_rows, D, gate_w, up_w, down_w);
+  return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
+}
+int gated_mlp(const float* gate_w, const float* up_w, const float* down_w, int D, const float* x, float* y,
+              int n_rows, bool emulate_bf16, cudaStream_t st) {
+  return emulate_bf16 ? gated_mlp_impl<true>(gate_w, up_w, down_w, D, x, y, n_rows, st)
+                      : gated_mlp_impl<false>(gate_w, up_w, down_w, D, x, y, n_rows, st);
+}
+
+template <bool EMU>
+static int rglru_impl(const float* a_w, const float* a_b, const float* x_w, const float* x_b, const float* log_lambda,
+                      int D, const float* x, float* y, const float* h0, float* h_out, const uint8_t* done, int n_rows,
+                      int T, cudaStream_t st) {
+  size_t sm = smem_rows(D, 2);
+  if (!opt_in(k_rglru<EMU>, sm)) return BNB_ERR_LAUNCH;
+  count_launch();
+  k_rglru<EMU><<<(n_rows + ROWS - 1) / ROWS, NTHREADS, sm, st>>>(x, y, h0, h_out, done, n_rows, T, D, a_w, a_b, x_w, x_b,
+                                                                 log_lambda);
+  return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
+}
+int rglru(const float* a_w, const float* a_b, const float* x_w, const float* x_b, const float* log_lambda, int D,
+          const float* x, float* y, const float* h0, float* h_out, const uint8_t* done, int n_rows, int T,
+          bool emulate_bf16, cudaStream_t st) {
+  return emulate_bf16 ? rglru_impl<true>(a_w, a_b, x_w, x_b, log_lambda, D, x, y, h0, h_out, done, n_rows, T, st)
+                      : rglru_impl<false>(a_w, a_b, x_w, x_b, log_lambda, D, x, y, h0, h_out, done, n_rows, T, st);
 }
 
 int reset_hidden(const float* in, float* out, const uint8_t* done, int n_slots, int D,

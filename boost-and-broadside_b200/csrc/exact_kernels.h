@@ -22,5 +22,15 @@ int temporal_block(const BnbTemporalWeights& w, int D, const float* x, float* y,
 int reset_hidden(const float* in, float* out, const uint8_t* done, int n_slots, int D,
                  const BnbBatch& b, cudaStream_t st);
 
+// GatedMLP on its own: y (n_rows, D) = down(gelu(gate x) * up x).
+int gated_mlp(const float* gate_w, const float* up_w, const float* down_w, int D, const float* x, float* y,
+              int n_rows, bool emulate_bf16, cudaStream_t st);
+
+// RG-LRU on its own over T steps: x, y (T, n_rows, D) time-major, h0 / h_out (n_rows, D),
+// done (T, n_rows) bytes or null.
+int rglru(const float* a_w, const float* a_b, const float* x_w, const float* x_b, const float* log_lambda, int D,
+          const float* x, float* y, const float* h0, float* h_out, const uint8_t* done, int n_rows, int T,
+          bool emulate_bf16, cudaStream_t st);
+
 }  // namespace exact
 }  // namespace bnb

@@ -145,6 +145,7 @@ def trunk_forward(
                 scratch.data_ptr(), scratch.numel(), stream,
             )
     _capi.check(fn, st)
+    _capi.note_engine_choice(fn)
     _debug_check(fn, dev, precision)
     return y, hout
 
@@ -185,6 +186,7 @@ def spatial_forward(
             scratch.data_ptr(), scratch.numel(), _capi.stream_handle(dev),
         )
     _capi.check("bnb_spatial_block_fwd", st)
+    _capi.note_engine_choice("bnb_spatial_block_fwd")
     _debug_check("bnb_spatial_block_fwd", dev, precision)
     return y
 

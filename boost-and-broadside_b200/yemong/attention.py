@@ -18,20 +18,45 @@ from ._weights import spatial_tensors
 
 
 class GatedMLP(nn.Module):
-    """Parameter holder for down_proj(gelu(gate_proj(x)) * up_proj(x)) (attention.py:21-37).
+    """down_proj(gelu(gate_proj(x)) * up_proj(x)), no biases (attention.py:21-37).
 
-    The product is computed inside the fused sublayer kernels, not here.
+    Inside a sublayer the product runs fused in the sublayer kernels; ``forward`` serves callers
+    that use the module on its own (the reference's tests do) through ``bnb_gated_mlp_fwd``.
     """
 
     def __init__(self, d_model: int, expand: int = 4) -> None:
         super().__init__()
+        if expand != 4:
+            raise ValueError("the CUDA GatedMLP is built for expand = 4 (the reference's only value)")
         hidden = expand * d_model
+        self.d_model = d_model
         self.gate_proj = nn.Linear(d_model, hidden, bias=False)
         self.up_proj = nn.Linear(d_model, hidden, bias=False)
         self.down_proj = nn.Linear(hidden, d_model, bias=False)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:  # pragma: no cover - not a product path
-        raise RuntimeError("GatedMLP runs only fused inside TransformerBlock / GriffinTemporalBlock kernels")
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """(..., D) -> (..., D); bfloat16 inside ``torch.autocast`` (as the reference's last Linear
+        returns it), else float32."""
+        D = self.d_model
+        if x.shape[-1] != D:
+            raise RuntimeError(f"expected x of shape (..., {D}), got {tuple(x.shape)}")
+        _capi.require_cuda(x, "x")
+        if torch.is_grad_enabled() and x.requires_grad:
+            raise NotImplementedError("the CUDA trunk is forward-only; call it under torch.no_grad()")
+        dev = x.device
+        precision = _capi.current_precision(dev)
+        with torch.cuda.device(dev):
+            flat = _capi.f32c(x).reshape(-1, D)
+            y = torch.empty_like(flat)
+            ws = [self.gate_proj.weight, self.up_proj.weight, self.down_proj.weight]
+            for w in ws:
+                if w.device != dev or w.dtype != torch.float32 or not w.is_contiguous():
+                    raise RuntimeError("GatedMLP parameters must be contiguous float32 on the input's device")
+            st = _capi.lib.bnb_gated_mlp_fwd(ws[0].data_ptr(), ws[1].data_ptr(), ws[2].data_ptr(), D, flat.data_ptr(),
+                                             y.data_ptr(), flat.shape[0], precision, _capi.stream_handle(dev))
+        _capi.check("bnb_gated_mlp_fwd", st)
+        y = y.reshape(x.shape)
+        return y.to(torch.bfloat16) if precision == _capi.BNB_BF16 else y
 
 
 class TransformerBlock(nn.Module):

@@ -25,10 +25,12 @@ def _no_grad_inputs(*tensors) -> None:
 
 
 class RGLRU(nn.Module):
-    """Parameters of the Real-Gated Linear Recurrent Unit (griffin.py:160-167).
+    """Real-Gated Linear Recurrent Unit (griffin.py:143-219).
 
     r = sigmoid(W_a x + b_a), i = sigmoid(W_x x + b_x), a = sigmoid(Lambda)^(c r),
-    h = a h + sqrt(1 - a^2) (i x).  The update runs fused inside the temporal kernels.
+    h = a h + sqrt(1 - a^2) (i x).  Inside a temporal sublayer the update runs fused in the
+    temporal kernels; ``_step`` and ``forward_sequence`` serve callers that use the unit on its own
+    (the reference's tests do) through ``bnb_rglru_fwd``.
     """
 
     def __init__(self, d_model: int, c: float = 8.0) -> None:
@@ -36,14 +38,54 @@ class RGLRU(nn.Module):
         if c != 8.0:
             raise ValueError("the CUDA RG-LRU is built for c = 8 (the reference's only value)")
         self.c = c
+        self.d_model = d_model
         self.log_lambda = nn.Parameter(torch.linspace(0.0, 4.0, d_model))
         self.linear_a = nn.Linear(d_model, d_model, bias=True)
         self.linear_x = nn.Linear(d_model, d_model, bias=True)
 
-    def forward_sequence(self, x_seq, h0, done_mask=None):  # pragma: no cover - not a product path
-        raise RuntimeError("RGLRU runs only fused inside GriffinTemporalBlock.forward_sequence")
+    def _run(self, x_t: torch.Tensor, h0: torch.Tensor, done_t: torch.Tensor | None):
+        """x_t (T, R, D) time-major float32 contiguous -> (states (T, R, D), final state (R, D))."""
+        T, R, D = x_t.shape
+        dev = x_t.device
+        precision = _capi.current_precision(dev)
+        ps = [self.linear_a.weight, self.linear_a.bias, self.linear_x.weight, self.linear_x.bias, self.log_lambda]
+        for p in ps:
+            if p.device != dev or p.dtype != torch.float32 or not p.is_contiguous():
+                raise RuntimeError("RGLRU parameters must be contiguous float32 on the input's device")
+        with torch.cuda.device(dev):
+            h = _capi.f32c(h0)
+            y = torch.empty_like(x_t)
+            h_out = torch.empty_like(h)
+            st = _capi.lib.bnb_rglru_fwd(*(p.data_ptr() for p in ps), D, x_t.data_ptr(), y.data_ptr(), h.data_ptr(),
+                                         h_out.data_ptr(), _capi.ptr(done_t), R, T, precision, _capi.stream_handle(dev))
+        _capi.check("bnb_rglru_fwd", st)
+        return y, h_out
 
-    _step = forward_sequence
+    def _check(self, x: torch.Tensor, h: torch.Tensor, dims: int) -> None:
+        if x.dim() != dims or x.shape[-1] != self.d_model:
+            raise RuntimeError(f"expected an input of {dims} dims ending in {self.d_model}, got {tuple(x.shape)}")
+        if tuple(h.shape) != (x.shape[0], self.d_model):
+            raise RuntimeError(f"expected a state of shape {(x.shape[0], self.d_model)}, got {tuple(h.shape)}")
+        _capi.require_cuda(x, "x")
+        _no_grad_inputs(x, h)
+
+    def _step(self, x: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
+        """One step (griffin.py:169-186): x, h (B_seq, D) -> new h, which is also the output."""
+        self._check(x, h, 2)
+        _, h_out = self._run(_capi.f32c(x).unsqueeze(0), h, None)
+        return h_out
+
+    def forward_sequence(self, x_seq: torch.Tensor, h0: torch.Tensor, done_mask: torch.Tensor | None = None):
+        """A full sequence (griffin.py:188-219): x_seq (B_seq, T, D), h0 (B_seq, D), done_mask
+        (B_seq, T) bool (True at t cuts the state before step t + 1) -> (states (B_seq, T, D),
+        final state (B_seq, D))."""
+        self._check(x_seq, h0, 3)
+        if done_mask is not None and tuple(done_mask.shape) != tuple(x_seq.shape[:2]):
+            raise RuntimeError(f"done_mask must have shape {tuple(x_seq.shape[:2])}, got {tuple(done_mask.shape)}")
+        x_t = _capi.f32c(x_seq.transpose(0, 1))
+        done_t = None if done_mask is None else _capi.u8(done_mask.transpose(0, 1))
+        y, h_out = self._run(x_t, h0, done_t)
+        return y.transpose(0, 1).contiguous(), h_out
 
 
 class GriffinTemporalBlock(nn.Module):

@@ -166,6 +166,13 @@ const char* bnb_status_string(int status);
  * benchmark's launch accounting; no counterpart in the reference). */
 unsigned long long bnb_launch_count(void);
 
+/* BNB_BF16 calls so far that asked for BNB_ENGINE_AUTO and ran on the exact kernels (several times
+ * slower) because the tensor-core kernels are not built for their shape: d_model other than 128,
+ * other than 4 heads, more than 512 tokens in an environment, a ragged batch without a tile plan,
+ * more bullets per environment than the attention kernel stages.  The choice is made per call and
+ * is otherwise silent; the Python binding warns once when this counter moves. */
+unsigned long long bnb_auto_fallback_count(void);
+
 /* Host-only query: 1 if (d_model, n_heads, max tokens per environment) can run with the
  * given precision and engine, else 0.  No device is touched. */
 int bnb_supported(int d_model, int n_heads, int max_tokens_per_env, int precision, int engine);
@@ -279,6 +286,25 @@ int bnb_trunk_sequence(const BnbSpatialWeights* spatial, const BnbTemporalWeight
  *   hidden_in/out (n_slots, total_ships, 4D); may alias;  done (n_envs) bytes */
 int bnb_reset_hidden(const float* hidden_in, float* hidden_out, const uint8_t* done,
                      int n_slots, int d_model, const BnbBatch* batch, void* stream);
+
+/* GatedMLP on its own: y = down(gelu_erf(gate x) * up x), no biases.
+ * Replaces: GatedMLP.forward, models/yemong/attention.py:36-37 (inside a sublayer it runs fused).
+ *   x, y (n_rows, D) float32; gate_w, up_w (4D, D); down_w (D, 4D).  BNB_BF16 applies the autocast
+ *   roundings (input, every Linear output, the gelu and the product) and leaves bf16 values in y. */
+int bnb_gated_mlp_fwd(const float* gate_w, const float* up_w, const float* down_w, int d_model,
+                      const float* x, float* y, int n_rows, int precision, void* stream);
+
+/* The RG-LRU on its own over `timesteps` steps of n_rows independent rows.
+ * Replaces: RGLRU._step (timesteps = 1, done = NULL) and RGLRU.forward_sequence,
+ * models/yemong/griffin.py:169-219 (inside a temporal sublayer it runs fused).
+ *   x, y (timesteps, n_rows, D) time-major float32: y[t] is the state after step t;
+ *   h0, h_out (n_rows, D); done (timesteps, n_rows) bytes or NULL: done[t] cuts the state
+ *   before step t + 1.  The recurrence is evaluated step by step, which is what the reference
+ *   pins its parallel scan against. */
+int bnb_rglru_fwd(const float* a_w, const float* a_b, const float* x_w, const float* x_b,
+                  const float* log_lambda, int d_model, const float* x, float* y, const float* h0,
+                  float* h_out, const uint8_t* done, int n_rows, int timesteps, int precision,
+                  void* stream);
 
 /* Bytes of the tensor-core weight image of one sublayer (bf16, pre-tiled). */
 size_t bnb_packed_spatial_bytes(int d_model);

@@ -173,3 +173,25 @@ def test_mismatched_state_and_mask_shapes_are_refused_on_the_host():
         rb = RaggedBatch(torch.full((6,), 12), torch.full((6,), 8))
         with pytest.raises(RuntimeError, match="alive must have shape"):
             trunk.step_ragged(x.reshape(-1, 128), alive.reshape(-1)[:-1], hidden, rb)
+
+
+def test_a_bf16_call_that_falls_to_the_exact_engine_is_counted_and_warned_about():
+    """BNB_ENGINE_AUTO picks the exact kernels for shapes the tensor-core kernels are not built for
+    (here d_model 64); the call is counted by the library and the binding warns once."""
+    import warnings
+
+    from boost_and_broadside_b200 import _capi
+
+    trunk = build_trunk([64, 4, 1, 1, 1, 0]).to(DEV)
+    x = torch.randn(4, 6, 64, device=DEV)
+    alive = torch.ones(4, 6, dtype=torch.bool, device=DEV)
+    hidden = trunk.initial_hidden(4, 6, torch.device(DEV))
+    before = _capi.lib.bnb_auto_fallback_count()
+    _capi._fallback_warned = False
+    with warnings.catch_warnings(record=True) as seen:
+        warnings.simplefilter("always")
+        with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
+            trunk.step(x, alive, hidden)
+            trunk.step(x, alive, hidden)
+    assert _capi.lib.bnb_auto_fallback_count() >= before + 2
+    assert sum("exact (SIMT) kernels" in str(w.message) for w in seen) == 1
