@@ -38,10 +38,11 @@ METRIC = "policy-step entity tokens/sec per B200 (attn+RG-LRU), % of HBM rooflin
 UNIT = "entity_tokens/s"
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
-# DRAM bytes per entity token of the fused C2 step, from one ncu capture of k_trunk_tiles on the
-# half-size case (dram__bytes_read.sum + dram__bytes_write.sum = 344 109 824 B for 49 152 tokens);
-# traffic grows in proportion to the tokens, so a full launch is this times its tokens.
-NCU_C2_DRAM_BYTES_PER_TOKEN = (200308992 + 150321408) / 49152
+# DRAM bytes per entity token of the fused C2 step, from one ncu capture of k_trunk_pipelined on the
+# half-size case (dram__bytes_read.sum + dram__bytes_write.sum = 310 730 496 B for 49 152 tokens,
+# profiles/k_trunk_pipelined_c2_half.md); traffic grows in proportion to the tokens, so a full
+# launch is this times its tokens.
+NCU_C2_DRAM_BYTES_PER_TOKEN = (173093120 + 137637376) / 49152
 
 
 def measured_peaks() -> tuple[float, float, float, str]:
@@ -588,9 +589,10 @@ def run_ours(args) -> None:
                     "copy_only_note": "the same three-stream loop with the trunk call removed: the host-copy floor of this leg (max over ranks)"},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
-                         "traffic": (NCU_C2_DRAM_BYTES_PER_TOKEN * tokens if args.workload == "C2" and launches == args.steps else None),
+                         "traffic": (NCU_C2_DRAM_BYTES_PER_TOKEN * tokens if args.workload == "C2" and launches == 2 * args.steps else None),
                          "of": src, "algorithmic_bytes_per_step": alg_bytes,
-                         "kernel": "k_trunk_pipelined (one launch = one trunk step)" if launches == args.steps else "whole trunk step (all launches of one step)", "kernel_ms": kernel_ms},
+                         "kernel": ("k_trunk_pipelined (one launch = one trunk step; the 8 us k_pack_trunk launch that rewrites the weight images before it is inside the timed step)"
+                                    if launches == 2 * args.steps else "whole trunk step (all launches of one step)"), "kernel_ms": kernel_ms},
             "tensor": {"achieved": alg_flops / (kernel_ms * 1e-3) / 1e12, "peak": tflops_burst, "unit": "TFLOP/s",
                        "frac": alg_flops / (kernel_ms * 1e-3) / 1e12 / tflops_burst, "of": src + " (burst: the timed region lasts milliseconds)",
                        "frac_of_sustained": alg_flops / (kernel_ms * 1e-3) / 1e12 / tflops, "peak_sustained": tflops,
