@@ -15,7 +15,7 @@ import torch
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libbnb_trunk.so")
 
-BNB_FP32, BNB_BF16 = 0, 1
+BNB_FP32, BNB_BF16, BNB_BF16_IO = 0, 1, 2
 ENGINE_AUTO, ENGINE_SIMT, ENGINE_TENSOR = 0, 1, 2
 ABI_VERSION = 2
 

@@ -216,6 +216,8 @@ static int trunk_common(const BnbSpatialWeights* spatial, const BnbTemporalWeigh
   if (st) return st;
   if ((st = check_batch(batch))) return st;
   if (n_blocks < 0 || n_spatial < 0 || n_temporal < 0 || T < 1) return BNB_ERR_BAD_ARGUMENT;
+  const bool io_bf16 = precision == BNB_BF16_IO;
+  if (io_bf16) precision = BNB_BF16;
   if (precision != BNB_FP32 && precision != BNB_BF16) return BNB_ERR_BAD_ARGUMENT;
   if (n_blocks * n_spatial > 0 && !spatial) return BNB_ERR_NULL_POINTER;
   if (n_blocks * n_temporal > 0 && !temporal) return BNB_ERR_NULL_POINTER;
@@ -237,8 +239,8 @@ static int trunk_common(const BnbSpatialWeights* spatial, const BnbTemporalWeigh
   if (use_tensor(precision, engine, D, H, batch, bullets) &&
       (engine == BNB_ENGINE_TENSOR || all_packed(spatial, n_blocks * n_spatial, temporal, n_blocks * n_temporal)))
     return bnb::tensor::trunk(spatial, temporal, n_blocks, n_spatial, n_temporal, D, H, x, alive, bullets, y, hidden_in,
-                              hidden_out, done, reset_env, *batch, T, scratch, scratch_bytes, cs);
-  if (engine == BNB_ENGINE_TENSOR) return BNB_ERR_UNSUPPORTED_DIMS;
+                              hidden_out, done, reset_env, *batch, T, scratch, scratch_bytes, cs, io_bf16);
+  if (engine == BNB_ENGINE_TENSOR || io_bf16) return BNB_ERR_UNSUPPORTED_DIMS;
 
   Scratch s{nullptr, nullptr, nullptr, 0};
   if (n_blocks * n_spatial > 0 &&

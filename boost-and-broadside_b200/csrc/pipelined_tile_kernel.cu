@@ -1043,12 +1043,27 @@ __global__ void __launch_bounds__(THREADS, 1) k_trunk_pipelined(const __grid_con
         // residual <- x (this thread: columns [32 part, 32 part + 32))
         {
           uint32_t v[32];
+          if (args.io_bf16) {
+            const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(args.x) + trow * D + e.part * 32);
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (valid) f = *reinterpret_cast<const float4*>(args.x + trow * D + e.part * 32 + q * 4);
-            v[q * 4 + 0] = __float_as_uint(f.x); v[q * 4 + 1] = __float_as_uint(f.y);
-            v[q * 4 + 2] = __float_as_uint(f.z); v[q * 4 + 3] = __float_as_uint(f.w);
+            for (int q = 0; q < 4; ++q) {
+              uint4 w = make_uint4(0u, 0u, 0u, 0u);
+              if (valid) w = src[q];
+              const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                v[q * 8 + 2 * j] = ws[j] << 16;              // a bfloat16 is the upper half of its float
+                v[q * 8 + 2 * j + 1] = ws[j] & 0xFFFF0000u;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (valid) f = *reinterpret_cast<const float4*>(args.x + trow * D + e.part * 32 + q * 4);
+              v[q * 4 + 0] = __float_as_uint(f.x); v[q * 4 + 1] = __float_as_uint(f.y);
+              v[q * 4 + 2] = __float_as_uint(f.z); v[q * 4 + 3] = __float_as_uint(f.w);
+            }
           }
           tmem_st32(e.lane_addr + COL_RESID + e.part * 32, v);
         }
@@ -1079,7 +1094,11 @@ __global__ void __launch_bounds__(THREADS, 1) k_trunk_pipelined(const __grid_con
         {
           uint32_t v[32];
           tmem_ld32(e.lane_addr + COL_RESID + e.part * 32, v);
-          if (valid) {
+          if (valid && args.io_bf16) {
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(args.y) + trow * D + e.part * 32);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) dst[q] = pack8(&v[q * 8]);
+          } else if (valid) {
 #pragma unroll
             for (int q = 0; q < 8; ++q)
               *reinterpret_cast<float4*>(args.y + trow * D + e.part * 32 + q * 4) =

@@ -89,6 +89,7 @@ struct TrunkArgs {
   // lane's wait for it runs out and the kernel has to drain and return with a status code.
   int poll_limit;
   int skip_op;
+  int io_bf16;   // x and y hold bfloat16 (BNB_BF16_IO) instead of float32
   SubLayer sub[MAX_SUBLAYERS];
 };
 // Process-wide values of the two hooks, set by bnb_debug_wait_test and copied into every launch.

@@ -1791,6 +1791,7 @@ struct Plan {
   int* env_off;          // compaction of the slice's active bullets (see launch_compact)
   int* idx;
   int compacted_e0;      // first environment of the slice env_off / idx currently describe, -1 = none
+  bool io_bf16 = false;  // x and y (and so the stream between launches) hold bfloat16
   int n_groups, t_loop;  // geometry of the pending program
   TrunkArgs a;
   int n;
@@ -1811,6 +1812,7 @@ struct Plan {
     a.t_loop = t_loop;
     a.n_sub = n;
     a.flat_rows = split ? 1 : 0;
+    a.io_bf16 = io_bf16 ? 1 : 0;
     a.x = cur;
     a.y = y;
     int rc = launch(a, b, st);
@@ -1935,13 +1937,16 @@ int temporal_block(const BnbTemporalWeights& w, int d_model, const float* x, flo
 int trunk(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal, int n_blocks, int n_spatial,
           int n_temporal, int d_model, int n_heads, const float* x, const uint8_t* alive, const BnbBullets* bullets,
           float* y, const float* hidden_in, float* hidden_out, const uint8_t* done, const uint8_t* reset_env,
-          const BnbBatch& b, int T, void* scratch, size_t scratch_bytes, cudaStream_t st) {
+          const BnbBatch& b, int T, void* scratch, size_t scratch_bytes, cudaStream_t st, bool io_bf16) {
   if (!supported_batch(d_model, n_heads, b)) return BNB_ERR_UNSUPPORTED_DIMS;
+  // bfloat16 x / y: only the fused tile kernel reads and writes them
+  if (io_bf16 && (!fits_tile(b) || bullets)) return BNB_ERR_UNSUPPORTED_DIMS;
   for (int i = 0; i < n_blocks * n_spatial; ++i) if (!spatial[i].packed) return BNB_ERR_UNSUPPORTED_DIMS;
   for (int i = 0; i < n_blocks * n_temporal; ++i) if (!temporal[i].packed) return BNB_ERR_UNSUPPORTED_DIMS;
   // a time walk carries its state through hidden_out between timesteps
   if (T > 1 && n_blocks * n_temporal > 0 && b.total_ships > 0 && !hidden_out) return BNB_ERR_NULL_POINTER;
   Plan p{b, st, nullptr, false, alive, done, reset_env, x, y, bullets};
+  p.io_bf16 = io_bf16;
   int rc = make_plan(p, scratch, scratch_bytes, T);
   if (rc) return rc;
   const size_t slot_stride = (size_t)b.total_ships * 4 * D;
@@ -1956,7 +1961,7 @@ int trunk(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal, 
   }
   if ((rc = p.flush())) return rc;
   if (p.cur == x && y != x) {
-    if (cudaMemcpyAsync(y, x, (size_t)T * b.total_tokens * D * sizeof(float), cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+    if (cudaMemcpyAsync(y, x, (size_t)T * b.total_tokens * D * (io_bf16 ? 2 : sizeof(float)), cudaMemcpyDeviceToDevice, st) != cudaSuccess)
       return BNB_ERR_LAUNCH;
   }
   return report_status(p.status, st);

@@ -46,7 +46,7 @@ int temporal_block(const BnbTemporalWeights& w, int D, const float* x, float* y,
 int trunk(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal, int n_blocks, int n_spatial,
           int n_temporal, int D, int H, const float* x, const uint8_t* alive, const BnbBullets* bullets, float* y,
           const float* hidden_in, float* hidden_out, const uint8_t* done, const uint8_t* reset_env, const BnbBatch& b, int T,
-          void* scratch, size_t scratch_bytes, cudaStream_t st);
+          void* scratch, size_t scratch_bytes, cudaStream_t st, bool io_bf16 = false);
 
 }  // namespace tensor
 }  // namespace bnb

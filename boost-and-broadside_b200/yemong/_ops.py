@@ -82,11 +82,12 @@ def trunk_forward(
     """Blocks of (spatial sublayers, temporal sublayers) over x: ``bnb_trunk_step`` when
     geom[G_TIMESTEPS] is 0, else ``bnb_trunk_sequence`` over that many timesteps.
 
-    x (total_tokens, D) or (T, total_tokens, D); hidden (L, total_ships, 4D) packed;
+    x (total_tokens, D) or (T, total_tokens, D), float32 or bfloat16; hidden (L, total_ships, 4D) packed;
     ``weights`` the parameters of every sublayer, block-major, spatial before temporal inside a
     block, each sublayer in the order of ``_weights.spatial_tensors`` / ``temporal_tensors``;
     ``offsets`` empty for environments of one size, else [tok_off, ship_off(, tile_env_begin,
-    tile_env_ids)].  Returns (y like x, new hidden like hidden), both float32.
+    tile_env_ids)].  Returns (y like x: bfloat16 for bfloat16 tokens, else float32; new hidden like
+    hidden, float32).
     """
     dev = x.device
     D = x.shape[-1]
@@ -96,7 +97,14 @@ def trunk_forward(
     T = max(1, geom[G_TIMESTEPS])
     with torch.cuda.device(dev):
         batch = _batch(geom, offsets)
-        xin = _capi.f32c(x)
+        # bfloat16 tokens (what the reference's encoder hands its trunk under CUDA autocast) stay
+        # bfloat16 on the way in and out where the fused kernel serves the call; the residual stream
+        # inside the call is float32 either way.  Anything else is converted to float32 here.
+        io16 = (x.dtype == torch.bfloat16 and precision == _capi.BNB_BF16 and engine != _capi.ENGINE_SIMT
+                and (bullets is None or n_cross == 0) and 0 < geom[G_MAX_TOKENS] <= 128
+                and bool(_capi.lib.bnb_supported(D, n_heads, geom[G_MAX_TOKENS], _capi.BNB_BF16, _capi.ENGINE_TENSOR))
+                and (not offsets or len(offsets) > 2))
+        xin = (x if x.is_contiguous() else x.contiguous()) if io16 else _capi.f32c(x)
         hin = _capi.f32c(hidden)
         alive_u8 = _capi.u8(alive)
         done_u8 = _capi.u8(done)
@@ -134,25 +142,28 @@ def trunk_forward(
             fn = "bnb_trunk_step"
             st = _capi.lib.bnb_trunk_step(
                 sw, tw, n_blocks, n_spatial, n_temporal, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8), bul.arg,
-                y.data_ptr(), _capi.ptr(hin), _capi.ptr(hout), _capi.ptr(reset_u8), batch, precision, engine,
-                scratch.data_ptr(), scratch.numel(), stream,
+                y.data_ptr(), _capi.ptr(hin), _capi.ptr(hout), _capi.ptr(reset_u8), batch,
+                _capi.BNB_BF16_IO if io16 else precision, engine, scratch.data_ptr(), scratch.numel(), stream,
             )
         else:
             fn = "bnb_trunk_sequence"
             st = _capi.lib.bnb_trunk_sequence(
                 sw, tw, n_blocks, n_spatial, n_temporal, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8), bul.arg,
-                y.data_ptr(), _capi.ptr(hin), _capi.ptr(hout), _capi.ptr(done_u8), batch, T, precision, engine,
-                scratch.data_ptr(), scratch.numel(), stream,
+                y.data_ptr(), _capi.ptr(hin), _capi.ptr(hout), _capi.ptr(done_u8), batch, T,
+                _capi.BNB_BF16_IO if io16 else precision, engine, scratch.data_ptr(), scratch.numel(), stream,
             )
     _capi.check(fn, st)
     _capi.note_engine_choice(fn)
     _debug_check(fn, dev, precision)
+    if x.dtype == torch.bfloat16 and y.dtype != torch.bfloat16:
+        y = y.to(torch.bfloat16)   # the same contract on the paths that compute from a float32 copy
     return y, hout
 
 
 @trunk_forward.register_fake
 def _trunk_forward_fake(x, alive, hidden, done, reset_env, bullets, bullet_mask, weights, offsets, geom):
-    return (x.new_empty(x.shape, dtype=torch.float32), hidden.new_empty(hidden.shape, dtype=torch.float32))
+    out_dtype = torch.bfloat16 if x.dtype == torch.bfloat16 else torch.float32
+    return (x.new_empty(x.shape, dtype=out_dtype), hidden.new_empty(hidden.shape, dtype=torch.float32))
 
 
 @torch.library.custom_op("bnb_b200::spatial_forward", mutates_args=(), device_types="cuda")

@@ -70,7 +70,20 @@ void bnb_clear_status(void);
  * faults or spins, and the status word reads BNB_STATUS_WAIT_WEIGHTS. */
 void bnb_debug_wait_test(int skip_op, int poll_limit);
 
-typedef enum { BNB_FP32 = 0, BNB_BF16 = 1 } BnbPrecision;
+typedef enum {
+  BNB_FP32 = 0,
+  BNB_BF16 = 1,
+  /* BNB_BF16 with the token tensors themselves in bfloat16: `x` and `y` of bnb_trunk_step /
+   * bnb_trunk_sequence then point to bfloat16 elements (the declared float type notwithstanding);
+   * hidden state and parameters stay float32.  This is what the reference's trunk sees on the GPU:
+   * under torch.autocast("cuda", bfloat16) its encoder ends in an RMSNorm of a bf16 Linear output,
+   * which is bf16, and its heads cast what the trunk returns to bf16.  The residual stream is still
+   * carried in float32 inside the call and rounded once, on the way out (the reference adds in
+   * bf16 after every sublayer).  Halves the bytes of the token tensors.  Served by the fused
+   * tensor-core kernel only (d_model 128, 4 heads, environments of at most 128 tokens, no
+   * bullets); any other call returns BNB_ERR_UNSUPPORTED_DIMS and the caller converts. */
+  BNB_BF16_IO = 2
+} BnbPrecision;
 
 /* Which engine runs a BNB_BF16 call.
  *   BNB_ENGINE_AUTO   the fused tcgen05 kernels where the shapes are built for them, else SIMT

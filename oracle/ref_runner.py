@@ -113,15 +113,18 @@ class ReferenceTrunk(torch.nn.Module):
         return y, new_hidden
 
 
-def workload_runner(trunk: ReferenceTrunk, w, device: str = "cpu"):
+def workload_runner(trunk: ReferenceTrunk, w, device: str = "cpu", token_dtype: torch.dtype | None = None):
     """A zero-argument callable that runs workload ``w`` (boost-and-broadside_b200/workloads.py)
-    through the reference trunk on ``device`` under the workload's precision."""
+    through the reference trunk on ``device`` under the workload's precision; ``token_dtype``
+    converts the tokens first (bfloat16: what the reference's encoder produces under CUDA autocast)."""
     dev = torch.device(device)
 
     def to(t):
         return None if t is None else t.to(dev)
 
     x, alive, hidden = to(w.x), to(w.alive), to(w.hidden)
+    if token_dtype is not None:
+        x = x.to(token_dtype)
     ctx = (lambda: torch.autocast(dev.type, dtype=torch.bfloat16)) if w.mode == "bf16" else (lambda: torch.autocast(dev.type, enabled=False))
     if w.kind == "step":
         B = w.meta["n_envs"]

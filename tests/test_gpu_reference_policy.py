@@ -177,3 +177,29 @@ def test_reference_policy_sequence_through_swapped_blocks(mode):
     flips, near = argmax_report(got[0], ref[0], 1e-4 if mode == "fp32" else 2e-2 * float(ref[0].abs().max()))
     print(f"policy sequence T=7 {mode}: logits {e_logits:.2e} x {e_x:.2e}; argmax flips {flips}, near-tie rows {near}")
     assert flips == 0
+
+
+@pytest.mark.parametrize("B,n_ships,n_fields", [(96, 8, 4), (40, 2, 0)])
+def test_bfloat16_tokens_in_and_out_as_the_reference_under_cuda_autocast(B, n_ships, n_fields):
+    """With the bfloat16 tokens its own encoder produces under torch.autocast("cuda", bfloat16), the
+    reference's trunk returns bfloat16 (its residual adds stay in bf16).  This package takes the
+    same tensor without a float32 copy, carries the residual in float32 inside the kernel and rounds
+    once on the way out: bfloat16 out, the bits of the float32-token call rounded, and within the
+    bf16 tolerance of the reference."""
+    stock, swapped = build_policies(n_ships)
+    x, alive, hidden, team, _, _, _ = inputs(B, n_ships, n_fields, 0, seed=3 * B)
+    x16 = x.to(torch.bfloat16)
+    with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
+        ref = step_from_tokens(stock, x16, alive, hidden, team, None, None)
+        got = step_from_tokens(swapped, x16, alive, hidden, team, None, None)
+        # the dtype contract itself, on the blocks
+        rx, _, _ = stock.yemong_layers[0].step(x16, alive, hidden[:1, :, :128], hidden[:1, :, 128:].reshape(1, -1, 3, 128), n_ships)
+        gx, gh, _ = swapped.yemong_layers[0].step(x16, alive, hidden[:1, :, :128], hidden[:1, :, 128:].reshape(1, -1, 3, 128), n_ships)
+        fx, fh, _ = swapped.yemong_layers[0].step(x16.float(), alive, hidden[:1, :, :128], hidden[:1, :, 128:].reshape(1, -1, 3, 128), n_ships)
+    assert rx.dtype == torch.bfloat16 and gx.dtype == torch.bfloat16 and fx.dtype == torch.float32
+    assert torch.equal(gx, fx.to(torch.bfloat16)) and torch.equal(gh, fh)
+    errs = {n: compare(n, g, r, "bf16") for n, g, r in zip(("logits", "value", "pred_next", "hidden", "x"), got, ref)}
+    flips, near = argmax_report(got[0], ref[0], 2e-2 * float(ref[0].abs().max()))
+    print(f"bf16 tokens B={B} N={n_ships}+{n_fields}: " + " ".join(f"{k} {v:.2e}" for k, v in errs.items()) +
+          f"; argmax flips {flips}, near-tie rows {near}")
+    assert flips == 0
