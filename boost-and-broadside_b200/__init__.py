@@ -2,7 +2,7 @@
 with the per-ship Griffin RG-LRU recurrence, as hand-written sm_100a CUDA kernels behind the
 reference's own ``nn.Module`` signatures.
 
-    from boost_and_broadside_b200 import ModelConfig, TransformerBlock, YemongBlock, YemongTrunk
+    from boost_and_broadside_b200 import ModelConfig, ShipEncoder, TransformerBlock, YemongBlock, YemongTrunk
 
 The modules mirror ``boost_and_broadside.models.yemong.{attention,griffin}`` of the
 reference (same constructor arguments, parameter names and forward signatures) and call
@@ -11,16 +11,19 @@ the C-ABI library ``libbnb_trunk.so`` (include/bnb_trunk.h).  There is no CPU pa
 
 from .config import ModelConfig
 from .yemong.attention import GatedMLP, TransformerBlock
+from .yemong.encoder import BulletEncoder, ShipEncoder
 from .yemong.griffin import CONV_KERNEL, RGLRU, GriffinTemporalBlock, YemongBlock
 from .yemong.trunk import YemongTrunk, RaggedBatch
 
 __all__ = [
+    "BulletEncoder",
     "CONV_KERNEL",
     "GatedMLP",
     "GriffinTemporalBlock",
     "ModelConfig",
     "RGLRU",
     "RaggedBatch",
+    "ShipEncoder",
     "TransformerBlock",
     "YemongBlock",
     "YemongTrunk",

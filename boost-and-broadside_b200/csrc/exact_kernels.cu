@@ -723,6 +723,80 @@ k_rglru(const float* __restrict__ x, float* __restrict__ y, const float* __restr
     }
 }
 
+// ------------------------------------------------------------------ encoder MLP
+//
+// Linear(in, hidden) + b -> RMSNorm(hidden) -> GELU -> Linear(hidden, out) + b -> RMSNorm(out): the chain
+// of the reference's ShipEncoder (feature_extractor, or ship_proj / field_proj + shared_proj) and
+// BulletEncoder (net), models/yemong/encoder.py:45-51, 84-102.  in <= 128 (any width; w1 comes
+// padded with zero columns to in_pad, a multiple of 32), hidden <= 256 and out <= 128 multiples of
+// 32.  EMU: every stage hands on bfloat16 as under autocast (an RMSNorm of a bf16 input is
+// computed in float32 and rounded once), and y holds bfloat16 elements.
+template <bool EMU>
+__global__ void __launch_bounds__(NTHREADS)
+k_encoder_mlp(const float* __restrict__ x, void* __restrict__ y, int n_rows, int in_dim, int in_pad, int hidden, int out_dim,
+              const float* __restrict__ w1, const float* __restrict__ b1, const float* __restrict__ g1,
+              const float* __restrict__ w2, const float* __restrict__ b2, const float* __restrict__ g2) {
+  extern __shared__ __align__(16) float smem[];
+  const int ldx = in_pad + 4, ldh = max(hidden, NCHUNK) + 4;
+  float* X = smem;
+  float* Hs = X + ROWS * ldx;
+  float* Ws = Hs + ROWS * ldh;
+  const int row0 = blockIdx.x * ROWS;
+  const int n_valid = min(ROWS, n_rows - row0);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  for (int idx = tid; idx < ROWS * in_pad; idx += NTHREADS) {
+    const int r = idx / in_pad, c = idx - r * in_pad;
+    float v = 0.f;
+    if (r < n_valid && c < in_dim) v = x[(size_t)(row0 + r) * in_dim + c];
+    X[r * ldx + c] = rnd<EMU>(v);
+  }
+  __syncthreads();
+  for (int c0 = 0; c0 < hidden; c0 += NCHUNK) {
+    const int cn = min(NCHUNK, hidden - c0);
+    float acc[4][4];
+    zero_acc(acc);
+    tile_linear<EMU>(X, ldx, w1 + (size_t)c0 * in_pad, in_pad, cn, in_pad, Ws, acc);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c = lane + 32 * j;
+        if (c < cn) Hs[(4 * warp + i) * ldh + c0 + c] = rnd<EMU>(acc[i][j] + rnd<EMU>(b1[c0 + c]));
+      }
+  }
+  __syncthreads();
+  tile_rmsnorm<EMU>(Hs, Hs, ldh, hidden, g1, ROWS);
+  for (int i = 0; i < 4; ++i)
+    for (int c = lane; c < hidden; c += 32) {
+      float* p = Hs + (4 * warp + i) * ldh + c;
+      *p = rnd<EMU>(gelu_erf(*p));
+    }
+  __syncthreads();
+  float acc[4][4];
+  zero_acc(acc);
+  tile_linear<EMU>(Hs, ldh, w2, hidden, out_dim, hidden, Ws, acc);
+  __syncthreads();  // every warp has read its rows of Hs
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = lane + 32 * j;
+      if (c < out_dim) Hs[(4 * warp + i) * ldh + c] = rnd<EMU>(acc[i][j] + rnd<EMU>(b2[c]));
+    }
+  __syncthreads();
+  tile_rmsnorm<EMU>(Hs, Hs, ldh, out_dim, g2, ROWS);
+  __syncwarp();
+  for (int i = 0; i < 4; ++i) {
+    const int r = 4 * warp + i;
+    if (r >= n_valid) continue;
+    for (int c = lane; c < out_dim; c += 32) {
+      const float v = Hs[r * ldh + c];
+      if constexpr (EMU) static_cast<__nv_bfloat16*>(y)[(size_t)(row0 + r) * out_dim + c] = __float2bfloat16_rn(v);
+      else static_cast<float*>(y)[(size_t)(row0 + r) * out_dim + c] = v;
+    }
+  }
+}
+
 // ------------------------------------------------------------------ host launchers
 
 static size_t smem_rows(int D, int tiles) {
@@ -861,6 +935,25 @@ int rglru(const float* a_w, const float* a_b, const float* x_w, const float* x_b
           bool emulate_bf16, cudaStream_t st) {
   return emulate_bf16 ? rglru_impl<true>(a_w, a_b, x_w, x_b, log_lambda, D, x, y, h0, h_out, done, n_rows, T, st)
                       : rglru_impl<false>(a_w, a_b, x_w, x_b, log_lambda, D, x, y, h0, h_out, done, n_rows, T, st);
+}
+
+template <bool EMU>
+static int encoder_mlp_impl(const float* w1, const float* b1, const float* g1, const float* w2, const float* b2,
+                            const float* g2, int in_dim, int in_pad, int hidden, int out_dim, const float* x, void* y,
+                            int n_rows, cudaStream_t st) {
+  const int ldh = (hidden > NCHUNK ? hidden : NCHUNK) + 4;
+  const size_t sm = (size_t)(ROWS * (in_pad + 4) + ROWS * ldh + NCHUNK * WS_STRIDE) * sizeof(float);
+  if (!opt_in(k_encoder_mlp<EMU>, sm)) return BNB_ERR_LAUNCH;
+  count_launch();
+  k_encoder_mlp<EMU><<<(n_rows + ROWS - 1) / ROWS, NTHREADS, sm, st>>>(x, y, n_rows, in_dim, in_pad, hidden, out_dim, w1, b1,
+                                                                       g1, w2, b2, g2);
+  return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
+}
+int encoder_mlp(const float* w1, const float* b1, const float* g1, const float* w2, const float* b2, const float* g2,
+                int in_dim, int in_pad, int hidden, int out_dim, const float* x, void* y, int n_rows, bool emulate_bf16,
+                cudaStream_t st) {
+  return emulate_bf16 ? encoder_mlp_impl<true>(w1, b1, g1, w2, b2, g2, in_dim, in_pad, hidden, out_dim, x, y, n_rows, st)
+                      : encoder_mlp_impl<false>(w1, b1, g1, w2, b2, g2, in_dim, in_pad, hidden, out_dim, x, y, n_rows, st);
 }
 
 int reset_hidden(const float* in, float* out, const uint8_t* done, int n_slots, int D,

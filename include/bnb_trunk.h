@@ -319,6 +319,23 @@ int bnb_rglru_fwd(const float* a_w, const float* a_b, const float* x_w, const fl
                   float* h_out, const uint8_t* done, int n_rows, int timesteps, int precision,
                   void* stream);
 
+/* The encoder chain Linear + b -> RMSNorm -> GELU(erf) -> Linear + b -> RMSNorm on rows of raw
+ * feature vectors: the token encoders in front of the trunk.
+ * Replaces: ShipEncoder.feature_extractor (or ship_proj / field_proj followed by shared_proj) and
+ * BulletEncoder.net, models/yemong/encoder.py:45-51, 84-102.  The FeatureCoordinator that builds
+ * the raw vectors from an observation stays the caller's.
+ *   x (n_rows, in_dim) float32, 1 <= in_dim <= 128, rows need no alignment;
+ *   w1 (hidden, in_pad) float32 = the first Linear's weight with zero columns appended up to
+ *   in_pad, a multiple of 32; b1, g1 (hidden), hidden a multiple of 32 up to 256;
+ *   w2 (out_dim, hidden), b2, g2 (out_dim), out_dim a multiple of 32 up to 128;
+ *   y (n_rows, out_dim): float32 for BNB_FP32; **bfloat16 elements** for BNB_BF16, where every
+ *   stage hands on bfloat16 as under torch.autocast (the RMSNorm of a bf16 input is computed in
+ *   float32 with the float32 eps and rounded once) -- the tensor bnb_trunk_step takes with
+ *   BNB_BF16_IO. */
+int bnb_encoder_mlp_fwd(const float* w1, const float* b1, const float* g1, const float* w2,
+                        const float* b2, const float* g2, int in_dim, int in_pad, int hidden,
+                        int out_dim, const float* x, void* y, int n_rows, int precision, void* stream);
+
 /* Bytes of the tensor-core weight image of one sublayer (bf16, pre-tiled). */
 size_t bnb_packed_spatial_bytes(int d_model);
 size_t bnb_packed_temporal_bytes(int d_model);

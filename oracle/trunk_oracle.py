@@ -524,3 +524,19 @@ def synthetic_trunk_state_dict(d_model: int = 128, n_blocks: int = 2, n_spatial:
             sd[p + "gated_mlp.down_proj.weight"] = lin(D, 4 * D)
             sd[f"yemong_layers.{i}.field_sub.{j}.weight"] = torch.eye(D)
     return sd
+
+
+# --------------------------------------------------------------------------- encoders
+
+
+def encoder_mlp(raw: torch.Tensor, w1, b1, g1, w2, b2, g2, mode: str) -> torch.Tensor:
+    """Linear -> RMSNorm -> GELU -> Linear -> RMSNorm with biases, the chain of ShipEncoder's
+    ``feature_extractor`` / ``ship_proj + shared_proj`` and BulletEncoder's ``net``
+    (models/yemong/encoder.py:45-51, 84-90, 98-102).  Under autocast every stage hands on
+    bfloat16: the Linear outputs, the RMSNorm of a bf16 input (computed in float32 with the
+    float32 eps, rounded once) and the GELU."""
+    h = linear(raw, w1, b1, mode)
+    n = _r(rms_norm(h, g1), mode)
+    a = _r(gelu_erf(n), mode)
+    o = linear(a, w2, b2, mode)
+    return _r(rms_norm(o, g2), mode)

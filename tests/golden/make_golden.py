@@ -347,6 +347,45 @@ def main() -> None:
     save("bullets_trunk_seq_d128_t4_4s2f", x=x, alive=alive, hidden=hidden, done=done, bullets=bullets,
          bullet_mask=mask, dims=dims.copy(), wsum=checksum(sd), **out)
 
+    # ------------------------------------------------------------------ encoders (rows f-2, f-4)
+    # The MLP chains of ShipEncoder (shared and split layouts) and BulletEncoder
+    # (models/yemong/encoder.py:25-130) on raw feature vectors of the coordinators' widths.
+    from boost_and_broadside.config import ShipConfig
+    from boost_and_broadside.models.yemong.encoder import BulletEncoder, ShipEncoder
+    from boost_and_broadside.train.rl.features import FeatureScope, build_bullet_coordinator, build_standard_coordinator
+
+    ships = ShipConfig()
+    sc, bc = build_standard_coordinator(ships), build_bullet_coordinator(ships)
+    gen = torch.Generator().manual_seed(21)
+    torch.manual_seed(0)
+    enc = ShipEncoder(cfg(128, 4), sc, num_ships=8).eval()
+    raw = torch.randn(7, 12, sc.total_input_dimension, generator=gen) * 1.5
+    out = {}
+    for mode in ("fp32", "bf16"):
+        with torch.no_grad(), autocast(mode):
+            out["y_" + mode] = enc.feature_extractor(raw).float()
+    save("encoder_ship_shared", raw=raw, **out, **weights_as_arrays(enc.state_dict()))
+
+    torch.manual_seed(0)
+    enc = ShipEncoder(ModelConfig(d_model=128, n_heads=4, n_yemong_blocks=2, encoder_split=True), sc, num_ships=8).eval()
+    ship_raw = torch.randn(7, 8, sc.scoped_input_dimension(FeatureScope.SHIP), generator=gen) * 1.5
+    field_raw = torch.randn(7, 4, sc.scoped_input_dimension(FeatureScope.FIELD), generator=gen) * 1.5
+    out = {}
+    for mode in ("fp32", "bf16"):
+        with torch.no_grad(), autocast(mode):
+            hidden = torch.cat([enc.ship_proj(ship_raw), enc.field_proj(field_raw)], dim=-2)
+            out["y_" + mode] = enc.shared_proj(hidden).float()
+    save("encoder_ship_split", ship_raw=ship_raw, field_raw=field_raw, **out, **weights_as_arrays(enc.state_dict()))
+
+    torch.manual_seed(0)
+    benc = BulletEncoder(cfg(128, 4, nbul=1), bc).eval()
+    raw = torch.randn(5, 80, bc.total_input_dimension, generator=gen) * 1.5
+    out = {}
+    for mode in ("fp32", "bf16"):
+        with torch.no_grad(), autocast(mode):
+            out["y_" + mode] = benc.net(raw).float()
+    save("encoder_bullet", raw=raw, **out, **weights_as_arrays(benc.state_dict()))
+
 
 if __name__ == "__main__":
     main()

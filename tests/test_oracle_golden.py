@@ -181,3 +181,27 @@ def test_trunk_sequence_with_bullets(mode):
                              g["bullets"], g["bullet_mask"])
     assert_close(y, g["y_" + mode], mode, "bullets sequence y")
     assert_close(nh, g["hidden_" + mode], mode, "bullets sequence hidden")
+
+
+@pytest.mark.parametrize("mode", ["fp32", "bf16"])
+def test_encoder_chains_match_the_reference(mode):
+    """ShipEncoder (shared and split layouts) and BulletEncoder MLP chains against the fixtures the
+    reference's modules produced (models/yemong/encoder.py)."""
+    from oracle.trunk_oracle import encoder_mlp
+
+    g = golden("encoder_ship_shared")
+    w = stored_weights(g)
+    y = encoder_mlp(g["raw"], w["feature_extractor.0.weight"], w["feature_extractor.0.bias"], w["feature_extractor.1.weight"],
+                    w["feature_extractor.3.weight"], w["feature_extractor.3.bias"], w["feature_extractor.4.weight"], mode)
+    assert_close(y, g["y_" + mode], mode, "ship encoder (shared)")
+    g = golden("encoder_ship_split")
+    w = stored_weights(g)
+    shared = (w["shared_proj.0.weight"], w["shared_proj.0.bias"], w["shared_proj.1.weight"])
+    ys = encoder_mlp(g["ship_raw"], w["ship_proj.0.weight"], w["ship_proj.0.bias"], w["ship_proj.1.weight"], *shared, mode)
+    yf = encoder_mlp(g["field_raw"], w["field_proj.0.weight"], w["field_proj.0.bias"], w["field_proj.1.weight"], *shared, mode)
+    assert_close(torch.cat([ys, yf], dim=-2), g["y_" + mode], mode, "ship encoder (split)")
+    g = golden("encoder_bullet")
+    w = stored_weights(g)
+    y = encoder_mlp(g["raw"], w["net.0.weight"], w["net.0.bias"], w["net.1.weight"], w["net.3.weight"], w["net.3.bias"],
+                    w["net.4.weight"], mode)
+    assert_close(y, g["y_" + mode], mode, "bullet encoder")
