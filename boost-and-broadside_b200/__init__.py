@@ -12,6 +12,7 @@ the C-ABI library ``libbnb_trunk.so`` (include/bnb_trunk.h).  There is no CPU pa
 from .config import ModelConfig
 from .yemong.attention import GatedMLP, TransformerBlock
 from .yemong.encoder import BulletEncoder, ShipEncoder
+from .yemong.heads import HeadMLP, NextStateHead
 from .yemong.griffin import CONV_KERNEL, RGLRU, GriffinTemporalBlock, YemongBlock
 from .yemong.trunk import YemongTrunk, RaggedBatch
 
@@ -20,7 +21,9 @@ __all__ = [
     "CONV_KERNEL",
     "GatedMLP",
     "GriffinTemporalBlock",
+    "HeadMLP",
     "ModelConfig",
+    "NextStateHead",
     "RGLRU",
     "RaggedBatch",
     "ShipEncoder",

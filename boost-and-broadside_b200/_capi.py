@@ -98,6 +98,7 @@ EXPORTS = {
     "bnb_gated_mlp_fwd": (C.c_int, [_fp, _fp, _fp, C.c_int, _fp, _fp, C.c_int, C.c_int, _fp]),
     "bnb_rglru_fwd": (C.c_int, [_fp] * 5 + [C.c_int, _fp, _fp, _fp, _fp, _fp, C.c_int, C.c_int, C.c_int, _fp]),
     "bnb_encoder_mlp_fwd": (C.c_int, [_fp] * 6 + [C.c_int] * 4 + [_fp, _fp, C.c_int, C.c_int, _fp]),
+    "bnb_head_mlp_fwd": (C.c_int, [_fp] * 5 + [C.c_int] * 4 + [_fp, _fp, C.c_int, C.c_int, _fp]),
     "bnb_pack_trunk": (C.c_int, [C.POINTER(SpatialWeights), C.c_int, C.POINTER(TemporalWeights), C.c_int, C.c_int, C.c_int, _fp]),
     "bnb_last_status": (C.c_int, []),
     "bnb_clear_status": (None, []),

@@ -348,7 +348,23 @@ int bnb_encoder_mlp_fwd(const float* w1, const float* b1, const float* g1, const
   const void* ps[] = {w1, b1, g1, w2, b2, g2, x, y};
   for (const void* p : ps) if (!p) return BNB_ERR_NULL_POINTER;
   if (!aligned16(w1) || !aligned16(w2)) return BNB_ERR_MISALIGNED;
-  return bnb::exact::encoder_mlp(w1, b1, g1, w2, b2, g2, in_dim, in_pad, hidden, out_dim, x, y, n_rows,
+  return bnb::exact::encoder_mlp(w1, b1, g1, w2, b2, g2, in_dim, in_pad, hidden, out_dim, out_dim, x, y, n_rows,
+                                 precision == BNB_BF16, static_cast<cudaStream_t>(stream));
+}
+
+int bnb_head_mlp_fwd(const float* w1, const float* b1, const float* g1, const float* w2, const float* b2, int in_dim,
+                     int hidden, int out_dim, int out_pad, const float* x, void* y, int n_rows, int precision,
+                     void* stream) {
+  if (in_dim <= 0 || in_dim % 32 != 0 || in_dim > 128) return BNB_ERR_UNSUPPORTED_DIMS;
+  if (hidden <= 0 || hidden % 32 != 0 || hidden > 256) return BNB_ERR_UNSUPPORTED_DIMS;
+  if (out_dim <= 0 || out_pad < out_dim || out_pad % 32 != 0 || out_pad > 128) return BNB_ERR_UNSUPPORTED_DIMS;
+  if (n_rows < 0) return BNB_ERR_BAD_ARGUMENT;
+  if (precision != BNB_FP32 && precision != BNB_BF16) return BNB_ERR_BAD_ARGUMENT;
+  if (n_rows == 0) return BNB_OK;
+  const void* ps[] = {w1, b1, g1, w2, b2, x, y};
+  for (const void* p : ps) if (!p) return BNB_ERR_NULL_POINTER;
+  if (!aligned16(w1) || !aligned16(w2)) return BNB_ERR_MISALIGNED;
+  return bnb::exact::encoder_mlp(w1, b1, g1, w2, b2, nullptr, in_dim, in_dim, hidden, out_pad, out_dim, x, y, n_rows,
                                  precision == BNB_BF16, static_cast<cudaStream_t>(stream));
 }
 

@@ -725,15 +725,18 @@ k_rglru(const float* __restrict__ x, float* __restrict__ y, const float* __restr
 
 // ------------------------------------------------------------------ encoder MLP
 //
-// Linear(in, hidden) + b -> RMSNorm(hidden) -> GELU -> Linear(hidden, out) + b -> RMSNorm(out): the chain
+// Linear(in, hidden) + b -> RMSNorm(hidden) -> GELU -> Linear(hidden, out) + b [-> RMSNorm(out)]: the chain
 // of the reference's ShipEncoder (feature_extractor, or ship_proj / field_proj + shared_proj) and
-// BulletEncoder (net), models/yemong/encoder.py:45-51, 84-102.  in <= 128 (any width; w1 comes
+// BulletEncoder (net), models/yemong/encoder.py:45-51, 84-102, and, without the last norm (g2
+// null) and with only the first out_store output columns stored, of the policy's heads
+// (models/yemong/policy.py:185-214).  in <= 128 (any width; w1 comes
 // padded with zero columns to in_pad, a multiple of 32), hidden <= 256 and out <= 128 multiples of
 // 32.  EMU: every stage hands on bfloat16 as under autocast (an RMSNorm of a bf16 input is
 // computed in float32 and rounded once), and y holds bfloat16 elements.
 template <bool EMU>
 __global__ void __launch_bounds__(NTHREADS)
 k_encoder_mlp(const float* __restrict__ x, void* __restrict__ y, int n_rows, int in_dim, int in_pad, int hidden, int out_dim,
+              int out_store,
               const float* __restrict__ w1, const float* __restrict__ b1, const float* __restrict__ g1,
               const float* __restrict__ w2, const float* __restrict__ b2, const float* __restrict__ g2) {
   extern __shared__ __align__(16) float smem[];
@@ -784,15 +787,15 @@ k_encoder_mlp(const float* __restrict__ x, void* __restrict__ y, int n_rows, int
       if (c < out_dim) Hs[(4 * warp + i) * ldh + c] = rnd<EMU>(acc[i][j] + rnd<EMU>(b2[c]));
     }
   __syncthreads();
-  tile_rmsnorm<EMU>(Hs, Hs, ldh, out_dim, g2, ROWS);
+  if (g2) tile_rmsnorm<EMU>(Hs, Hs, ldh, out_dim, g2, ROWS);   // the encoders end in a norm, the heads do not
   __syncwarp();
   for (int i = 0; i < 4; ++i) {
     const int r = 4 * warp + i;
     if (r >= n_valid) continue;
-    for (int c = lane; c < out_dim; c += 32) {
+    for (int c = lane; c < out_store; c += 32) {
       const float v = Hs[r * ldh + c];
-      if constexpr (EMU) static_cast<__nv_bfloat16*>(y)[(size_t)(row0 + r) * out_dim + c] = __float2bfloat16_rn(v);
-      else static_cast<float*>(y)[(size_t)(row0 + r) * out_dim + c] = v;
+      if constexpr (EMU) static_cast<__nv_bfloat16*>(y)[(size_t)(row0 + r) * out_store + c] = __float2bfloat16_rn(v);
+      else static_cast<float*>(y)[(size_t)(row0 + r) * out_store + c] = v;
     }
   }
 }
@@ -939,21 +942,22 @@ int rglru(const float* a_w, const float* a_b, const float* x_w, const float* x_b
 
 template <bool EMU>
 static int encoder_mlp_impl(const float* w1, const float* b1, const float* g1, const float* w2, const float* b2,
-                            const float* g2, int in_dim, int in_pad, int hidden, int out_dim, const float* x, void* y,
-                            int n_rows, cudaStream_t st) {
+                            const float* g2, int in_dim, int in_pad, int hidden, int out_dim, int out_store, const float* x,
+                            void* y, int n_rows, cudaStream_t st) {
   const int ldh = (hidden > NCHUNK ? hidden : NCHUNK) + 4;
   const size_t sm = (size_t)(ROWS * (in_pad + 4) + ROWS * ldh + NCHUNK * WS_STRIDE) * sizeof(float);
   if (!opt_in(k_encoder_mlp<EMU>, sm)) return BNB_ERR_LAUNCH;
   count_launch();
-  k_encoder_mlp<EMU><<<(n_rows + ROWS - 1) / ROWS, NTHREADS, sm, st>>>(x, y, n_rows, in_dim, in_pad, hidden, out_dim, w1, b1,
-                                                                       g1, w2, b2, g2);
+  k_encoder_mlp<EMU><<<(n_rows + ROWS - 1) / ROWS, NTHREADS, sm, st>>>(x, y, n_rows, in_dim, in_pad, hidden, out_dim, out_store,
+                                                                       w1, b1, g1, w2, b2, g2);
   return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
 }
 int encoder_mlp(const float* w1, const float* b1, const float* g1, const float* w2, const float* b2, const float* g2,
-                int in_dim, int in_pad, int hidden, int out_dim, const float* x, void* y, int n_rows, bool emulate_bf16,
-                cudaStream_t st) {
-  return emulate_bf16 ? encoder_mlp_impl<true>(w1, b1, g1, w2, b2, g2, in_dim, in_pad, hidden, out_dim, x, y, n_rows, st)
-                      : encoder_mlp_impl<false>(w1, b1, g1, w2, b2, g2, in_dim, in_pad, hidden, out_dim, x, y, n_rows, st);
+                int in_dim, int in_pad, int hidden, int out_dim, int out_store, const float* x, void* y, int n_rows,
+                bool emulate_bf16, cudaStream_t st) {
+  return emulate_bf16
+             ? encoder_mlp_impl<true>(w1, b1, g1, w2, b2, g2, in_dim, in_pad, hidden, out_dim, out_store, x, y, n_rows, st)
+             : encoder_mlp_impl<false>(w1, b1, g1, w2, b2, g2, in_dim, in_pad, hidden, out_dim, out_store, x, y, n_rows, st);
 }
 
 int reset_hidden(const float* in, float* out, const uint8_t* done, int n_slots, int D,

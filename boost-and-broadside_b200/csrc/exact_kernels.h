@@ -33,11 +33,11 @@ int rglru(const float* a_w, const float* a_b, const float* x_w, const float* x_b
           bool emulate_bf16, cudaStream_t st);
 
 // Encoder chain Linear + b -> RMSNorm -> GELU -> Linear + b -> RMSNorm on rows of raw features.
-// w1 is (hidden, in_pad) with zero columns beyond in_dim; y holds float32, or bfloat16 when
-// emulate_bf16.
+// w1 is (hidden, in_pad) with zero columns beyond in_dim; g2 null leaves the last norm out (the
+// policy's heads); y is (n_rows, out_store), float32, or bfloat16 when emulate_bf16.
 int encoder_mlp(const float* w1, const float* b1, const float* g1, const float* w2, const float* b2, const float* g2,
-                int in_dim, int in_pad, int hidden, int out_dim, const float* x, void* y, int n_rows, bool emulate_bf16,
-                cudaStream_t st);
+                int in_dim, int in_pad, int hidden, int out_dim, int out_store, const float* x, void* y, int n_rows,
+                bool emulate_bf16, cudaStream_t st);
 
 }  // namespace exact
 }  // namespace bnb

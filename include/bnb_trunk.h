@@ -336,6 +336,17 @@ int bnb_encoder_mlp_fwd(const float* w1, const float* b1, const float* g1, const
                         const float* b2, const float* g2, int in_dim, int in_pad, int hidden,
                         int out_dim, const float* x, void* y, int n_rows, int precision, void* stream);
 
+/* One head of the policy: Linear + b -> RMSNorm -> GELU(erf) -> Linear + b on the trunk's output.
+ * Replaces: YemongPolicy.action_head, .value_head_local, .value_head_win and NextStateHead.net,
+ * models/yemong/policy.py:56-72, 185-214 (all four have this shape).
+ *   x (n_rows, in_dim) float32, in_dim a multiple of 32 up to 128; w1 (hidden, in_dim), b1, g1
+ *   (hidden); w2 (out_pad, hidden) and b2 (out_pad): the second Linear with zero rows / entries
+ *   appended up to out_pad, a multiple of 32; y (n_rows, out_dim), float32 for BNB_FP32,
+ *   **bfloat16 elements** for BNB_BF16 (what the last Linear returns under autocast). */
+int bnb_head_mlp_fwd(const float* w1, const float* b1, const float* g1, const float* w2, const float* b2,
+                     int in_dim, int hidden, int out_dim, int out_pad, const float* x, void* y, int n_rows,
+                     int precision, void* stream);
+
 /* Bytes of the tensor-core weight image of one sublayer (bf16, pre-tiled). */
 size_t bnb_packed_spatial_bytes(int d_model);
 size_t bnb_packed_temporal_bytes(int d_model);

@@ -540,3 +540,13 @@ def encoder_mlp(raw: torch.Tensor, w1, b1, g1, w2, b2, g2, mode: str) -> torch.T
     a = _r(gelu_erf(n), mode)
     o = linear(a, w2, b2, mode)
     return _r(rms_norm(o, g2), mode)
+
+
+def head_mlp(x: torch.Tensor, w1, b1, g1, w2, b2, mode: str) -> torch.Tensor:
+    """Linear -> RMSNorm -> GELU -> Linear with biases: ``action_head``, ``value_head_local``,
+    ``value_head_win`` and ``NextStateHead.net`` (models/yemong/policy.py:56-72, 185-206).  The
+    encoder chain without its last norm."""
+    h = linear(x, w1, b1, mode)
+    n = _r(rms_norm(h, g1), mode)
+    a = _r(gelu_erf(n), mode)
+    return linear(a, w2, b2, mode)

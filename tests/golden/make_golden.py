@@ -386,6 +386,25 @@ def main() -> None:
             out["y_" + mode] = benc.net(raw).float()
     save("encoder_bullet", raw=raw, **out, **weights_as_arrays(benc.state_dict()))
 
+    # ------------------------------------------------------------------ heads (row f-4)
+    # action_head, value_head_local, value_head_win and next_state_head.net of a stock YemongPolicy
+    # (models/yemong/policy.py:56-72, 185-214) on trunk-like tokens.
+    from boost_and_broadside.models.yemong.policy import YemongPolicy
+
+    torch.manual_seed(0)
+    policy = YemongPolicy(cfg(128, 4, nbul=1), sc, num_value_components=11, num_ships=8, team_pma_k=(0, 1),
+                          bullet_coordinator=bc).eval()
+    x = torch.randn(9, 8, 128, generator=gen) * 1.5
+    arrays = {"x": x}
+    heads = {"action_head": policy.action_head, "value_head_local": policy.value_head_local,
+             "value_head_win": policy.value_head_win, "next_state_head": policy.next_state_head.net}
+    for name, head in heads.items():
+        for mode in ("fp32", "bf16"):
+            with torch.no_grad(), autocast(mode):
+                arrays[f"{name}_{mode}"] = head(x).float()
+        arrays.update(weights_as_arrays(head.state_dict(), prefix=f"w::{name}."))
+    save("policy_heads", **arrays)
+
 
 if __name__ == "__main__":
     main()

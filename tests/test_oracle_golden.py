@@ -205,3 +205,18 @@ def test_encoder_chains_match_the_reference(mode):
     y = encoder_mlp(g["raw"], w["net.0.weight"], w["net.0.bias"], w["net.1.weight"], w["net.3.weight"], w["net.3.bias"],
                     w["net.4.weight"], mode)
     assert_close(y, g["y_" + mode], mode, "bullet encoder")
+
+
+@pytest.mark.parametrize("mode", ["fp32", "bf16"])
+def test_policy_heads_match_the_reference(mode):
+    """action_head, value_head_local, value_head_win and next_state_head.net against the fixture a
+    stock reference YemongPolicy produced (models/yemong/policy.py:185-214)."""
+    from oracle.trunk_oracle import head_mlp
+
+    g = golden("policy_heads")
+    w = stored_weights(g)
+    for name in ("action_head", "value_head_local", "value_head_win", "next_state_head"):
+        y = head_mlp(g["x"], w[name + ".0.weight"], w[name + ".0.bias"], w[name + ".1.weight"], w[name + ".3.weight"],
+                     w[name + ".3.bias"], mode)
+        assert y.shape == g[f"{name}_{mode}"].shape
+        assert_close(y, g[f"{name}_{mode}"], mode, name)
