@@ -97,6 +97,42 @@ def gated_mlp(x: torch.Tensor, p: Params, prefix: str, mode: str) -> torch.Tenso
 # --------------------------------------------------------------------------- spatial
 
 
+class _AttentionLse(torch.autograd.Function):
+    """softmax(s) v with the backward of a fused attention kernel, which is what the reference's
+    F.scaled_dot_product_attention runs (attention.py:131, 157): the probabilities are recomputed
+    as exp(s - lse) from the saved log-sum-exp, and the row term is <d out, out>.  For any row with
+    a live key this is the plain softmax gradient.  Where every key is dead, lse = max + log(n)
+    rounds to max in float32 (max is the huge negative bias), the recomputed probabilities are 1
+    instead of 1/n, and the gradient is n times the textbook one -- the reference's own gradients
+    (tests/golden/grad_trunk_seq_d128_t1_8s0f.npz) show exactly that."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, bias, scale):
+        s = (q @ k.transpose(-1, -2)) * scale
+        if bias is not None:
+            s = s + bias
+        m = s.amax(dim=-1, keepdim=True)
+        e = torch.exp(s - m)
+        l = e.sum(dim=-1, keepdim=True)
+        out = (e / l) @ v
+        ctx.save_for_backward(q, k, v, bias if bias is not None else torch.zeros(()), m + torch.log(l), out)
+        ctx.scale, ctx.has_bias = scale, bias is not None
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, bias, lse, out = ctx.saved_tensors
+        s = (q @ k.transpose(-1, -2)) * ctx.scale
+        if ctx.has_bias:
+            s = s + bias
+        p = torch.exp(s - lse)
+        dv = p.transpose(-1, -2) @ dout
+        dp = dout @ v.transpose(-1, -2)
+        delta = (dout * out).sum(dim=-1, keepdim=True)
+        ds = p * (dp - delta) * ctx.scale
+        return ds @ k, ds.transpose(-1, -2) @ q, dv, None, None
+
+
 def masked_attention(
     q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, alive: torch.Tensor | None, mode: str
 ) -> torch.Tensor:
@@ -106,18 +142,13 @@ def masked_attention(
     ``(1 - alive) * finfo(dtype).min / 2`` to the scores (attention.py:101-112):
     a dead key then has weight exactly 0 while any key of its environment is alive,
     and when none is alive all scores saturate to the same value, which makes the
-    result the plain mean of v over every key of the environment.
+    result the plain mean of v over every key of the environment.  The float32 sum absorbs
+    the score of a dead key (|s| is far below the spacing of floats near the bias), so any
+    huge negative bias gives the same bits; -1e30 is used here.
     """
     dh = q.shape[-1]
-    s = (q @ k.transpose(-1, -2)) * (1.0 / math.sqrt(dh))
-    if alive is not None:
-        key_alive = alive[:, None, None, :]
-        any_alive = alive.any(dim=-1)[:, None, None, None]
-        neg = torch.full_like(s, -1.0e30)
-        s = torch.where(key_alive, s, neg)
-        s = torch.where(any_alive, s, torch.zeros_like(s))
-    p = torch.softmax(s, dim=-1)
-    return _r(p @ v, mode)
+    bias = None if alive is None else (~alive[:, None, None, :]).to(q.dtype) * -1.0e30
+    return _r(_AttentionLse.apply(q, k, v, bias, 1.0 / math.sqrt(dh)), mode)
 
 
 def spatial_block(
@@ -550,3 +581,25 @@ def head_mlp(x: torch.Tensor, w1, b1, g1, w2, b2, mode: str) -> torch.Tensor:
     n = _r(rms_norm(h, g1), mode)
     a = _r(gelu_erf(n), mode)
     return linear(a, w2, b2, mode)
+
+
+# --------------------------------------------------------------------------- gradients
+
+
+def trunk_sequence_grad(x, alive, hidden0, done, blocks, n_heads, dy, dhidden, bullets=None, bullet_mask=None,
+                        mode: str = "fp32"):
+    """Gradients of <trunk_sequence output, dy> + <final hidden, dhidden> by torch autograd over the
+    restatement above: what ``loss.backward()`` computes through ``evaluate_actions``'s trunk loop
+    (policy.py:422-478, train/rl/ppo.py:1974).  Returns (dx, dhidden0, dbullets | None, [per-block
+    dict of parameter gradients])."""
+    xg = x.detach().clone().requires_grad_(True)
+    hg = hidden0.detach().clone().requires_grad_(True)
+    bg = None if bullets is None else bullets.detach().clone().requires_grad_(True)
+    leaves = [{k: v.detach().clone().requires_grad_(True) for k, v in p.items()} for p in blocks]
+    y, nh = trunk_sequence(xg, alive, hg, done, leaves, n_heads, mode, bg, bullet_mask)
+    loss = (y * dy).sum()
+    if dhidden is not None:
+        loss = loss + (nh * dhidden).sum()
+    loss.backward()
+    grads = [{k: (v.grad if v.grad is not None else torch.zeros_like(v)) for k, v in p.items()} for p in leaves]
+    return xg.grad, hg.grad, None if bg is None else bg.grad, grads

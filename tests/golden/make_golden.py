@@ -347,6 +347,64 @@ def main() -> None:
     save("bullets_trunk_seq_d128_t4_4s2f", x=x, alive=alive, hidden=hidden, done=done, bullets=bullets,
          bullet_mask=mask, dims=dims.copy(), wsum=checksum(sd), **out)
 
+    # ------------------------------------------------------------------ gradients (row f-3)
+    # The sequence forward of policy.py:422-478 differentiated by the reference's own autograd:
+    # loss = <y, dy> + <new hidden, dhidden> with seeded random cotangents.  Stored: inputs,
+    # cotangents, d x, d hidden0, d bullets in full; each parameter gradient in full when it has at
+    # most 4096 elements, else every 13th element of the flattened gradient plus its sum and
+    # absolute sum (the full matrices would be megabytes per case).
+    GRAD_STRIDE = 13
+
+    def grad_case(tag, c, T, B, N, M, NB, seed, with_done=True):
+        layers = build_trunk(c)
+        D = c.d_model
+        gen = torch.Generator().manual_seed(seed)
+        x = torch.randn(T, B, N + M, D, generator=gen)
+        alive = team_alive(gen, T * B, N, M).reshape(T, B, N + M)
+        alive[0, 0, :N] = False          # one environment-step with every ship dead
+        hidden = torch.randn(c.n_hidden_layers, B * N, CONV_KERNEL * D, generator=gen) * 0.5
+        done = (torch.rand(T, B, generator=gen) < 0.3) if with_done else None
+        bullets = mask = None
+        if NB:
+            bullets, mask = bullet_inputs(gen, T * B, NB, D)
+        dy = torch.randn(T, B, N + M, D, generator=gen)
+        dhid = torch.randn(c.n_hidden_layers, B * N, CONV_KERNEL * D, generator=gen)
+        arrays = dict(x=x, alive=alive, hidden=hidden, dy=dy, dhidden=dhid)
+        if done is not None:
+            arrays["done"] = done
+        if NB:
+            arrays.update(bullets=bullets, bullet_mask=mask)
+        for mode in ("fp32", "bf16"):
+            xg = x.clone().requires_grad_(True)
+            hg = hidden.clone().requires_grad_(True)
+            bg = bullets.clone().requires_grad_(True) if NB else None
+            for p_ in layers.parameters():
+                p_.grad = None
+            with autocast(mode):
+                y, nh = ref_seq(layers, c, xg, alive, hg, done, bg, mask)
+            ((y.float() * dy).sum() + (nh.float() * dhid).sum()).backward()
+            arrays["dx_" + mode] = xg.grad
+            arrays["dhidden0_" + mode] = hg.grad
+            if NB:
+                arrays["dbullets_" + mode] = bg.grad
+            for name, p_ in layers.named_parameters():
+                key = f"yemong_layers.{name}"
+                g = p_.grad if p_.grad is not None else torch.zeros_like(p_)
+                if g.numel() <= 4096:
+                    arrays[f"g_{mode}::{key}"] = g.clone()
+                else:
+                    arrays[f"gsub_{mode}::{key}"] = g.flatten()[::GRAD_STRIDE].clone()
+                    arrays[f"gsum_{mode}::{key}"] = torch.stack([g.double().sum(), g.double().abs().sum()])
+        sd = {f"yemong_layers.{k}": v for k, v in layers.state_dict().items()}
+        save(f"grad_trunk_seq_{tag}", dims=np.array([D, c.n_heads, c.n_yemong_blocks, c.n_spatial_per_block,
+                                                     c.n_temporal_per_block, c.n_bullet_cross_per_block, N, M]),
+             stride=np.array([GRAD_STRIDE]), wsum=checksum(sd), **arrays)
+
+    grad_case("d128_t5_4s2f", cfg(128, 4, 2, 2, 1, 1), 5, 3, 4, 2, 0, seed=31)
+    grad_case("d128_t4_4s2f_nb12", cfg(128, 4, 2, 2, 1, 1), 4, 3, 4, 2, 12, seed=32)
+    grad_case("d64_t7_3s2f", cfg(64, 4, 2, 2, 1, 0), 7, 2, 3, 2, 0, seed=33)
+    grad_case("d128_t1_8s0f", cfg(128, 4, 1, 1, 1, 0), 1, 4, 8, 0, 0, seed=34, with_done=False)
+
     # ------------------------------------------------------------------ encoders (rows f-2, f-4)
     # The MLP chains of ShipEncoder (shared and split layouts) and BulletEncoder
     # (models/yemong/encoder.py:25-130) on raw feature vectors of the coordinators' widths.

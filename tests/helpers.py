@@ -89,3 +89,41 @@ def autocast_for(mode: str, device: str):
     if mode == "bf16":
         return torch.autocast(device, dtype=torch.bfloat16)
     return contextlib.nullcontext()
+
+
+def grad_fixture_compare(g: dict, mode: str, dx, dhidden0, dbullets, named_grads: dict, tol: float):
+    """Compare gradients with a grad_trunk_seq_* fixture (see make_golden.py: parameter gradients
+    are stored in full up to 4096 elements, else as every ``stride``-th element plus sum and
+    absolute sum).  Every tensor must be within ``tol`` normalised; returns the worst (name, error)."""
+    stride = int(g["stride"][0])
+    worst = ("", 0.0)
+
+    def check(name, got, ref):
+        nonlocal worst
+        got = got.detach().cpu().float()
+        assert got.shape == ref.shape, f"{name}: shape {tuple(got.shape)} vs {tuple(ref.shape)}"
+        assert torch.isfinite(got).all(), f"{name}: non-finite gradient"
+        e = norm_err(got, ref)
+        assert e <= tol, f"{name}: normalised gradient error {e:.3e} > {tol:.1e}"
+        if e > worst[1]:
+            worst = (name, e)
+
+    check("dx", dx, g["dx_" + mode])
+    check("dhidden0", dhidden0, g["dhidden0_" + mode])
+    if "dbullets_" + mode in g:
+        check("dbullets", dbullets, g["dbullets_" + mode])
+    seen = 0
+    for key, ref in g.items():
+        if key.startswith(f"g_{mode}::"):
+            check(key[len(mode) + 4:], named_grads[key[len(mode) + 4:]], ref)
+            seen += 1
+        elif key.startswith(f"gsub_{mode}::"):
+            name = key[len(mode) + 7:]
+            got = named_grads[name].detach().cpu().float()
+            check(name, got.flatten()[::stride], ref)
+            sums = g[f"gsum_{mode}::{name}"]
+            # the sums see every element; float32 summation order differs, so a loose gate
+            assert abs(float(got.double().abs().sum()) - float(sums[1])) <= 1e-3 * float(sums[1]) + 1e-6, name
+            seen += 1
+    assert seen == len(named_grads), f"fixture holds {seen} parameter gradients, got {len(named_grads)}"
+    return worst
