@@ -27,6 +27,21 @@ class SpatialWeights(C.Structure):
                                    "norm_bullet_w", "kv_bullet_w", "packed")]
 
 
+class SpatialGrads(C.Structure):
+    _fields_ = [(n, _fp) for n in ("norm1_w", "qkv_w", "out_w", "norm2_w", "gate_w", "up_w", "down_w",
+                                   "norm_bullet_w", "kv_bullet_w")]
+
+
+class TemporalGrads(C.Structure):
+    _fields_ = [
+        (n, _fp)
+        for n in (
+            "norm1_w", "linear1_w", "conv_w", "conv_b", "log_lambda", "a_w", "a_b", "x_w", "x_b",
+            "linear2_w", "out_w", "norm2_w", "gate_w", "up_w", "down_w", "field_sub_w",
+        )
+    ]
+
+
 class Bullets(C.Structure):
     _fields_ = [("tokens", _fp), ("active", _fp), ("per_env", C.c_int32)]
 
@@ -90,6 +105,10 @@ EXPORTS = {
          _fp, _fp, C.POINTER(Bullets), _fp, _fp, _fp, _fp, C.POINTER(Batch), C.c_int, C.c_int, C.c_int, _fp, C.c_size_t,
          _fp],
     ),
+    "bnb_trunk_bwd_scratch_bytes": (C.c_size_t, [C.c_int] * 4 + [C.POINTER(Batch), C.c_int, C.c_int]),
+    "bnb_trunk_sequence_bwd": (C.c_int, [C.POINTER(SpatialWeights), C.POINTER(TemporalWeights), C.POINTER(SpatialGrads),
+                                         C.POINTER(TemporalGrads)] + [C.c_int] * 5 + [_fp, _fp, C.POINTER(Bullets), _fp, _fp,
+                                         C.POINTER(Batch), C.c_int, _fp, _fp, _fp, _fp, _fp, _fp, C.c_size_t, _fp]),
     "bnb_reset_hidden": (C.c_int, [_fp, _fp, _fp, C.c_int, C.c_int, C.POINTER(Batch), _fp]),
     "bnb_packed_spatial_bytes": (C.c_size_t, [C.c_int]),
     "bnb_packed_temporal_bytes": (C.c_size_t, [C.c_int]),

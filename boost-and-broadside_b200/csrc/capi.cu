@@ -6,6 +6,7 @@
 #include "bnb_trunk.h"
 #include "bullet_slices.h"
 #include "exact_kernels.h"
+#include "grad_kernels.h"
 #include "launch_count.h"
 #include "validate.h"
 #include "tensor_kernels.h"
@@ -291,6 +292,67 @@ int bnb_trunk_sequence(const BnbSpatialWeights* spatial, const BnbTemporalWeight
   return trunk_common(spatial, temporal, n_blocks, n_spatial, n_temporal, d_model, n_heads, x, alive, bullets, y,
                       hidden_in, hidden_out, done, nullptr, batch, timesteps, precision, engine, scratch, scratch_bytes, stream,
                       true);
+}
+
+size_t bnb_trunk_bwd_scratch_bytes(int n_blocks, int n_spatial, int n_temporal, int d_model, const BnbBatch* batch,
+                                   int timesteps, int bullets_per_env) {
+  if (!batch || n_blocks < 0 || n_spatial < 0 || n_temporal < 0 || d_model <= 0 || timesteps < 1) return 0;
+  return bnb::grad::scratch_bytes(n_blocks, n_spatial, n_temporal, d_model, *batch, timesteps, bullets_per_env);
+}
+
+int bnb_trunk_sequence_bwd(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal,
+                           const BnbSpatialGrads* d_spatial, const BnbTemporalGrads* d_temporal, int n_blocks,
+                           int n_spatial, int n_temporal, int d_model, int n_heads, const float* x, const uint8_t* alive,
+                           const BnbBullets* bullets, const float* hidden_in, const uint8_t* done, const BnbBatch* batch,
+                           int timesteps, const float* dy, const float* d_hidden_out, float* dx, float* d_hidden_in,
+                           float* d_bullets, void* scratch, size_t scratch_bytes, void* stream) {
+  int st = check_dims(d_model, n_heads);
+  if (st) return st;
+  if ((st = check_batch(batch))) return st;
+  if (batch->tok_off) return BNB_ERR_UNSUPPORTED_DIMS;
+  if (n_blocks < 0 || n_spatial < 0 || n_temporal < 0 || timesteps < 1) return BNB_ERR_BAD_ARGUMENT;
+  if ((size_t)timesteps * batch->total_tokens == 0) return BNB_OK;
+  const int ns = n_blocks * n_spatial, nt = n_blocks * n_temporal;
+  if ((ns && (!spatial || !d_spatial)) || (nt && (!temporal || !d_temporal))) return BNB_ERR_NULL_POINTER;
+  if (!x || !dy || !dx || !scratch) return BNB_ERR_NULL_POINTER;
+  if (nt && batch->total_ships > 0 && !hidden_in) return BNB_ERR_NULL_POINTER;
+  if (!aligned16(x) || !aligned16(dy) || !aligned16(dx) || !aligned16(hidden_in) || !aligned16(d_hidden_out) ||
+      !aligned16(d_hidden_in) || !aligned16(d_bullets))
+    return BNB_ERR_MISALIGNED;
+  for (int i = 0; i < ns; ++i) {
+    if ((st = check_spatial(&spatial[i]))) return st;
+    const BnbSpatialGrads& g = d_spatial[i];
+    const void* ps[] = {g.norm1_w, g.qkv_w, g.out_w, g.norm2_w, g.gate_w, g.up_w, g.down_w};
+    for (const void* p : ps) {
+      if (!p) return BNB_ERR_NULL_POINTER;
+      if (!aligned16(p)) return BNB_ERR_MISALIGNED;
+    }
+    if (bullets && spatial[i].kv_bullet_w && (!g.norm_bullet_w || !g.kv_bullet_w)) return BNB_ERR_NULL_POINTER;
+    if (!aligned16(g.kv_bullet_w)) return BNB_ERR_MISALIGNED;
+  }
+  const bool fields = batch->total_tokens > batch->total_ships;
+  for (int i = 0; i < nt; ++i) {
+    const BnbTemporalWeights& w = temporal[i];
+    const BnbTemporalGrads& g = d_temporal[i];
+    const void* ws[] = {w.norm1_w, w.linear1_w, w.conv_w, w.conv_b, w.log_lambda, w.a_w, w.a_b, w.x_w, w.x_b,
+                        w.linear2_w, w.out_w, w.norm2_w, w.gate_w, w.up_w, w.down_w,
+                        g.norm1_w, g.linear1_w, g.conv_w, g.conv_b, g.log_lambda, g.a_w, g.a_b, g.x_w, g.x_b,
+                        g.linear2_w, g.out_w, g.norm2_w, g.gate_w, g.up_w, g.down_w};
+    for (const void* p : ws) {
+      if (!p) return BNB_ERR_NULL_POINTER;
+      if (!aligned16(p)) return BNB_ERR_MISALIGNED;
+    }
+    if (fields && (!w.field_sub_w || !g.field_sub_w)) return BNB_ERR_NULL_POINTER;
+    if (!aligned16(w.field_sub_w) || !aligned16(g.field_sub_w)) return BNB_ERR_MISALIGNED;
+  }
+  if (bullets) {
+    if (bullets->per_env < 1 || !bullets->tokens) return BNB_ERR_BAD_ARGUMENT;
+    if (!aligned16(bullets->tokens)) return BNB_ERR_MISALIGNED;
+  }
+  bnb::grad::TrunkBwdArgs a{spatial, temporal, d_spatial, d_temporal, n_blocks, n_spatial, n_temporal, d_model, n_heads,
+                            x, alive, bullets, hidden_in, done, batch, timesteps, dy, d_hidden_out, dx, d_hidden_in,
+                            d_bullets, scratch, scratch_bytes, static_cast<cudaStream_t>(stream)};
+  return bnb::grad::trunk_sequence_bwd(a);
 }
 
 int bnb_reset_hidden(const float* hidden_in, float* hidden_out, const uint8_t* done, int n_slots, int d_model,

@@ -1,0 +1,1109 @@
+// Backward pass of the Yemong trunk's sequence forward, float32.
+//
+// What loss.backward() computes through the trunk loop of evaluate_actions
+// (models/yemong/policy.py:422-478, reached from train/rl/ppo.py:1974): gradients with respect to
+// the tokens, the initial recurrent state, the bullet tokens and every parameter of
+//   TransformerBlock.forward        models/yemong/attention.py:76-169
+//   GatedMLP.forward                models/yemong/attention.py:21-37
+//   GriffinTemporalBlock.*          models/yemong/griffin.py:249-317
+//   RGLRU gates / update            models/yemong/griffin.py:169-219
+//   causal conv + tap validity      models/yemong/griffin.py:67-140
+//
+// Scheme: recompute, as the reference does with grad_checkpoint (policy.py:451-467).  A first pass
+// runs the forward sublayer by sublayer (the exact-arithmetic kernels) and keeps only the input of
+// every sublayer.  The sublayers are then walked in reverse; each recomputes its own intermediates
+// into scratch (norms, projections, attention output, gates, recurrent states) and differentiates
+// them.  Linear products -- y = x W^T, dx = dy W, dW += dy^T x -- all run on one tensor-core GEMM
+// kernel (3 x tf32 m16n8k8 MMAs per product, float32 accumulation: float32-level accuracy); the
+// weight gradients reduce over all rows with a split over the row dimension and float32 atomics,
+// so the caller hands in zeroed (or to-be-accumulated-into) gradient buffers.
+//
+// Attention gradient: the probabilities are recomputed as exp(s - lse) with lse = max + log(sum)
+// in float32 and the row term is <d out, out>, as the fused attention kernels behind
+// F.scaled_dot_product_attention do.  For a row with a live key that is the softmax gradient; for
+// an environment whose keys are all dead it is the reference's value too (lse rounds to the bias).
+#include "grad_kernels.h"
+
+#include "common.cuh"
+#include "exact_kernels.h"
+#include "launch_count.h"
+
+namespace bnb {
+namespace grad {
+
+namespace {
+
+// ------------------------------------------------------------------------------ GEMM
+
+constexpr int BM = 128, BN = 128, BK = 32, GT = 256;
+constexpr int LDK = BK + 4;    // row stride of a [row][k] tile: fragment reads hit 32 banks
+constexpr int LDR = 128 + 8;   // row stride of a [k][row] tile: likewise
+
+struct GemmArgs {
+  const float* A; int lda;
+  const float* B; int ldb;
+  float* C; int ldc;
+  int M, N, K;
+  const float* bias;        // (N) or null
+  const float* R; int ldr;  // residual (M, N) or null; may alias C
+  int beta;                 // 1: C += product
+  int k_per_split;          // K range of one blockIdx.z
+  int atomic;               // 1: atomicAdd into C (split over K)
+};
+
+__device__ __forceinline__ uint32_t to_tf32(float v) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+  return r;
+}
+__device__ __forceinline__ void split_tf32(float v, uint32_t& hi, uint32_t& lo) {
+  hi = to_tf32(v);
+  lo = to_tf32(v - __uint_as_float(hi));
+}
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// C(m, n) = sum_k A(m, k) B(n, k) [+ bias(n)] [+ R(m, n)] [+ C(m, n)].
+// A_KC: A(m, k) = A[m * lda + k], else A[k * lda + m].  B_KC: B(n, k) = B[n * ldb + k], else B[k * ldb + n].
+// The contiguous dimension of each operand is a multiple of 4 floats and its base 16-byte aligned.
+// 128 x 128 tile per CTA, 8 warps of 64 x 32, float32 operands split into two tf32 numbers each.
+template <bool A_KC, bool B_KC>
+__global__ void __launch_bounds__(GT) k_gemm(GemmArgs g) {
+  __shared__ __align__(16) float As[BM * LDK];
+  __shared__ __align__(16) float Bs[BN * LDK];
+  static_assert(BM * LDK >= BK * LDR, "either orientation fits the tile buffer");
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, t = lane & 3;
+  const int wm = (warp & 1) * 64, wn = (warp >> 1) * 32;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int kbeg = blockIdx.z * g.k_per_split;
+  const int kend = min(g.K, kbeg + g.k_per_split);
+  float c[4][4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) c[i][j][e] = 0.f;
+
+  for (int k0 = kbeg; k0 < kend; k0 += BK) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = tid + i * GT;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if constexpr (A_KC) {
+        const int row = idx >> 3, c4 = (idx & 7) * 4;
+        const int gm = m0 + row, gk = k0 + c4;
+        if (gm < g.M && gk < kend) v = *reinterpret_cast<const float4*>(g.A + (size_t)gm * g.lda + gk);
+        *reinterpret_cast<float4*>(As + row * LDK + c4) = v;
+      } else {
+        const int kk = idx >> 5, c4 = (idx & 31) * 4;
+        const int gk = k0 + kk, gm = m0 + c4;
+        if (gk < kend && gm < g.M) v = *reinterpret_cast<const float4*>(g.A + (size_t)gk * g.lda + gm);
+        *reinterpret_cast<float4*>(As + kk * LDR + c4) = v;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = tid + i * GT;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if constexpr (B_KC) {
+        const int row = idx >> 3, c4 = (idx & 7) * 4;
+        const int gn = n0 + row, gk = k0 + c4;
+        if (gn < g.N && gk < kend) v = *reinterpret_cast<const float4*>(g.B + (size_t)gn * g.ldb + gk);
+        *reinterpret_cast<float4*>(Bs + row * LDK + c4) = v;
+      } else {
+        const int kk = idx >> 5, c4 = (idx & 31) * 4;
+        const int gk = k0 + kk, gn = n0 + c4;
+        if (gk < kend && gn < g.N) v = *reinterpret_cast<const float4*>(g.B + (size_t)gk * g.ldb + gn);
+        *reinterpret_cast<float4*>(Bs + kk * LDR + c4) = v;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; kk += 8) {
+      uint32_t ah[4][4], al[4][4];
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt) {
+        const int r0 = wm + mt * 16 + gq;
+        float af[4];
+        if constexpr (A_KC) {
+          af[0] = As[r0 * LDK + kk + t];
+          af[1] = As[(r0 + 8) * LDK + kk + t];
+          af[2] = As[r0 * LDK + kk + t + 4];
+          af[3] = As[(r0 + 8) * LDK + kk + t + 4];
+        } else {
+          af[0] = As[(kk + t) * LDR + r0];
+          af[1] = As[(kk + t) * LDR + r0 + 8];
+          af[2] = As[(kk + t + 4) * LDR + r0];
+          af[3] = As[(kk + t + 4) * LDR + r0 + 8];
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) split_tf32(af[e], ah[mt][e], al[mt][e]);
+      }
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        const int nn = wn + nt * 8 + gq;
+        float b0, b1;
+        if constexpr (B_KC) {
+          b0 = Bs[nn * LDK + kk + t];
+          b1 = Bs[nn * LDK + kk + t + 4];
+        } else {
+          b0 = Bs[(kk + t) * LDR + nn];
+          b1 = Bs[(kk + t + 4) * LDR + nn];
+        }
+        uint32_t bh0, bl0, bh1, bl1;
+        split_tf32(b0, bh0, bl0);
+        split_tf32(b1, bh1, bl1);
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) {
+          mma_tf32(c[mt][nt], al[mt], bh0, bh1);
+          mma_tf32(c[mt][nt], ah[mt], bl0, bl1);
+          mma_tf32(c[mt][nt], ah[mt], bh0, bh1);
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int row = m0 + wm + mt * 16 + gq + (e >> 1) * 8;
+        const int col = n0 + wn + nt * 8 + 2 * t + (e & 1);
+        if (row < g.M && col < g.N) {
+          float v = c[mt][nt][e];
+          float* cp = g.C + (size_t)row * g.ldc + col;
+          if (g.atomic) {
+            atomicAdd(cp, v);
+          } else {
+            if (g.bias) v += g.bias[col];
+            if (g.R) v += g.R[(size_t)row * g.ldr + col];
+            if (g.beta) v += *cp;
+            *cp = v;
+          }
+        }
+      }
+}
+
+enum GemmMode { NT, NN, TN };
+
+// NT: C (M, N)  = A (M, K) . B (N, K)^T      y = x W^T
+// NN: C (M, N)  = A (M, K) . B (K, N)        dx = dy W
+// TN: C (M, N) += A (K, M)^T . B (K, N)      dW += dy^T x   (split over K, atomics)
+void gemm(GemmMode mode, const float* A, int lda, const float* B, int ldb, float* C, int ldc, int M, int N, int K,
+          const float* bias, const float* R, int ldr, int beta, cudaStream_t st) {
+  if (M <= 0 || N <= 0 || K <= 0) return;
+  GemmArgs g{A, lda, B, ldb, C, ldc, M, N, K, bias, R, ldr, beta, K, 0};
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, 1);
+  count_launch();
+  if (mode == TN) {
+    const int tiles = grid.x * grid.y;
+    int splits = (K + 511) / 512;
+    const int cap = tiles >= 592 ? 1 : 592 / tiles;   // about four CTAs per SM in flight
+    if (splits > cap) splits = cap;
+    if (splits < 1) splits = 1;
+    int per = (K + splits - 1) / splits;
+    per = (per + BK - 1) / BK * BK;
+    grid.z = (K + per - 1) / per;
+    g.k_per_split = per;
+    g.atomic = 1;
+    k_gemm<false, false><<<grid, GT, 0, st>>>(g);
+  } else if (mode == NT) {
+    k_gemm<true, true><<<grid, GT, 0, st>>>(g);
+  } else {
+    k_gemm<true, false><<<grid, GT, 0, st>>>(g);
+  }
+}
+
+// ------------------------------------------------------------------------------ row-wise pieces
+
+constexpr int MAXW = 128;   // widest normed vector (d_model)
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// n = x * rsqrt(mean(x^2) + eps) * g; the reciprocal root is kept for the backward.
+__global__ void __launch_bounds__(256) k_rmsnorm_fwd(const float* __restrict__ x, const float* __restrict__ g,
+                                                     float* __restrict__ n, float* __restrict__ inv_out, int rows, int W) {
+  const int lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+  for (int r = warp; r < rows; r += nwarps) {
+    float v[MAXW / 32], ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXW / 32; ++i) {
+      const int cidx = lane + 32 * i;
+      v[i] = cidx < W ? x[(size_t)r * W + cidx] : 0.f;
+      ss = fmaf(v[i], v[i], ss);
+    }
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)W + kRmsEps);
+    if (lane == 0) inv_out[r] = inv;
+#pragma unroll
+    for (int i = 0; i < MAXW / 32; ++i) {
+      const int cidx = lane + 32 * i;
+      if (cidx < W) n[(size_t)r * W + cidx] = v[i] * inv * g[cidx];
+    }
+  }
+}
+
+// dx = [dres +] inv * g * dn - x * inv^3 * mean(x * g * dn);  dg += sum_rows dn * x * inv.
+// dx may alias dres.
+__global__ void __launch_bounds__(256) k_rmsnorm_bwd(const float* __restrict__ x, const float* __restrict__ g,
+                                                     const float* __restrict__ inv, const float* __restrict__ dn,
+                                                     const float* dres, float* dx, float* __restrict__ dg, int rows, int W) {
+  __shared__ float sdg[8][MAXW];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+  float acc[MAXW / 32];
+#pragma unroll
+  for (int i = 0; i < MAXW / 32; ++i) acc[i] = 0.f;
+  for (int r = warp; r < rows; r += nwarps) {
+    float xv[MAXW / 32], dv[MAXW / 32], gv[MAXW / 32], dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXW / 32; ++i) {
+      const int cidx = lane + 32 * i;
+      const bool ok = cidx < W;
+      xv[i] = ok ? x[(size_t)r * W + cidx] : 0.f;
+      dv[i] = ok ? dn[(size_t)r * W + cidx] : 0.f;
+      gv[i] = ok ? g[cidx] : 0.f;
+      dot = fmaf(xv[i] * gv[i], dv[i], dot);
+    }
+    dot = warp_sum(dot);
+    const float iv = inv[r];
+    const float coef = dot * iv * iv * iv / (float)W;
+#pragma unroll
+    for (int i = 0; i < MAXW / 32; ++i) {
+      const int cidx = lane + 32 * i;
+      if (cidx < W) {
+        float v = iv * gv[i] * dv[i] - xv[i] * coef;
+        if (dres) v += dres[(size_t)r * W + cidx];
+        dx[(size_t)r * W + cidx] = v;
+        acc[i] = fmaf(dv[i] * xv[i], iv, acc[i]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < MAXW / 32; ++i) sdg[wib][lane + 32 * i] = acc[i];
+  __syncthreads();
+  if (dg && (int)threadIdx.x < W) {
+    float s = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) s += sdg[w][threadIdx.x];
+    atomicAdd(dg + threadIdx.x, s);
+  }
+}
+
+__device__ __forceinline__ float gelu_grad(float v) {
+  const float cdf = 0.5f * (1.0f + erff(v * 0.70710678118654752440f));
+  return cdf + v * 0.39894228040143267794f * expf(-0.5f * v * v);
+}
+
+// h = gelu(g) * u
+__global__ void k_gelu_mul_fwd(const float* __restrict__ g, const float* __restrict__ u, float* __restrict__ h, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    h[i] = gelu_erf(g[i]) * u[i];
+}
+
+// dg = dh * u * gelu'(g), du = dh * gelu(g).  dg may alias g, du may alias dh (or u).
+__global__ void k_gelu_mul_bwd(const float* g, const float* u, const float* dh, float* dg, float* du, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const float gv = g[i], uv = u[i], d = dh[i];
+    dg[i] = d * uv * gelu_grad(gv);
+    du[i] = d * gelu_erf(gv);
+  }
+}
+
+// out(n) += sum_rows a(row, n): bias gradients.
+__global__ void __launch_bounds__(256) k_colsum(const float* __restrict__ a, float* __restrict__ out, int rows, int N) {
+  __shared__ float s[8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + cx;
+  float acc = 0.f;
+  if (col < N)
+    for (int r = blockIdx.y * 8 + ry; r < rows; r += gridDim.y * 8) acc += a[(size_t)r * N + col];
+  s[ry][cx] = acc;
+  __syncthreads();
+  if (ry == 0 && col < N) {
+    float v = 0.f;
+    for (int i = 0; i < 8; ++i) v += s[i][cx];
+    atomicAdd(out + col, v);
+  }
+}
+
+// Rows of one kind (ships: n0 = 0, per_grp = ships per environment; fields: the rest) between the
+// token tensor (groups of NM rows) and a compact buffer.  D4 = D / 4.
+__global__ void k_gather_rows(const float4* __restrict__ full, float4* __restrict__ compact, size_t n_rows, int D4,
+                              int per_grp, int NM, int n0) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_rows * D4; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t q = i / D4;
+    const int c = (int)(i - q * D4);
+    const size_t grp = q / per_grp;
+    const int n = (int)(q - grp * per_grp);
+    compact[i] = full[(grp * NM + n0 + n) * D4 + c];
+  }
+}
+__global__ void k_scatter_rows(const float4* __restrict__ compact, float4* __restrict__ full, size_t n_rows, int D4,
+                               int per_grp, int NM, int n0) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_rows * D4; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t q = i / D4;
+    const int c = (int)(i - q * D4);
+    const size_t grp = q / per_grp;
+    const int n = (int)(q - grp * per_grp);
+    full[(grp * NM + n0 + n) * D4 + c] = compact[i];
+  }
+}
+
+// ------------------------------------------------------------------------------ attention
+
+// Forward: one thread per (query token, head), keys read in sequence with a running maximum;
+// o = self-attention [+ gate * bullet attention] (attention.py:131-166).
+template <int DH>
+__device__ __forceinline__ void attend(const float (&q)[DH], const float* __restrict__ kbase, size_t stride, int voff,
+                                       int n, const uint8_t* __restrict__ mask, float scale, float (&acc)[DH]) {
+#pragma unroll
+  for (int d = 0; d < DH; ++d) acc[d] = 0.f;
+  float m = -INFINITY, l = 0.f;
+  for (int j = 0; j < n; ++j) {
+    const float* kp = kbase + (size_t)j * stride;
+    float s = 0.f;
+#pragma unroll
+    for (int d = 0; d < DH; ++d) s = fmaf(q[d], kp[d], s);
+    s *= scale;
+    if (mask && !mask[j]) s = kMaskedScore;
+    const float mn = fmaxf(m, s);
+    const float corr = expf(m - mn), pj = expf(s - mn);
+    l = l * corr + pj;
+    const float* vp = kp + voff;
+#pragma unroll
+    for (int d = 0; d < DH; ++d) acc[d] = fmaf(pj, vp[d], acc[d] * corr);
+    m = mn;
+  }
+  const float inv = 1.0f / l;
+#pragma unroll
+  for (int d = 0; d < DH; ++d) acc[d] *= inv;
+}
+
+template <int DH>
+__global__ void __launch_bounds__(128) k_attn_fwd(const float* __restrict__ qkv, const uint8_t* __restrict__ alive,
+                                                  float* __restrict__ o, int NM, int D, int H,
+                                                  const float* __restrict__ kvb, const uint8_t* __restrict__ bactive, int nb) {
+  const size_t grp = blockIdx.x;
+  const size_t tok0 = grp * NM;
+  const float scale = rsqrtf((float)DH);
+  float gate = 1.f;
+  const uint8_t* bmask = nullptr;
+  if (kvb && bactive) {
+    bmask = bactive + grp * nb;
+    int any = 0;
+    for (int j = 0; j < nb; ++j) any |= bmask[j];
+    gate = any ? 1.f : 0.f;
+  }
+  for (int p = threadIdx.x; p < NM * H; p += blockDim.x) {
+    const int qi = p / H, h = p - qi * H;
+    const float* qp = qkv + (tok0 + qi) * 3 * D + h * DH;
+    float q[DH], acc[DH], accb[DH];
+#pragma unroll
+    for (int d = 0; d < DH; ++d) q[d] = qp[d];
+    attend<DH>(q, qkv + tok0 * 3 * D + D + h * DH, (size_t)3 * D, D, NM, alive ? alive + tok0 : nullptr, scale, acc);
+    if (kvb) {
+      attend<DH>(q, kvb + grp * nb * 2 * D + h * DH, (size_t)2 * D, D, nb, bmask, scale, accb);
+#pragma unroll
+      for (int d = 0; d < DH; ++d) acc[d] += accb[d] * gate;
+    }
+    float* op = o + (tok0 + qi) * D + h * DH;
+#pragma unroll
+    for (int d = 0; d < DH; ++d) op[d] = acc[d];
+  }
+}
+
+struct AttnBwdArgs {
+  const float* q; int ldq;                 // query i of group g: q + (g * nq + i) * ldq + h * dh
+  const float* kv; int ldkv; int voff;     // key j of group g: kv + (g * nk + j) * ldkv + h * dh, value voff further
+  const uint8_t* mask;                     // (groups, nk) or null
+  const float* d_o; int ldo;               // gradient of the attention output, rows like q
+  float* dq; int lddq; int dq_accumulate;
+  float* dkv; int lddkv; int dvoff;        // rows like kv
+  int nq, nk, dh;
+  float scale;
+  int gate_by_mask;                        // the branch is multiplied by any(mask) (bullets)
+};
+
+// One CTA per (group, head): keys, values and their gradient accumulators in shared memory, one
+// warp per query row.  p = exp(s - lse), ds = p (dp - <do, o>) scale.
+__global__ void __launch_bounds__(128) k_attn_bwd(AttnBwdArgs a) {
+  extern __shared__ __align__(16) float sm[];
+  const int nk = a.nk, dh = a.dh, lds = dh + 1;
+  const int nkp = (nk + 31) & ~31;
+  float* Ks = sm;
+  float* Vs = Ks + nk * lds;
+  float* dKs = Vs + nk * lds;
+  float* dVs = dKs + nk * dh;
+  float* per_warp = dVs + nk * dh;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  float* qs = per_warp + warp * (64 + 2 * nkp);
+  float* dos = qs + 32;
+  float* ps = dos + 32;
+  float* dss = ps + nkp;
+  const size_t grp = blockIdx.x;
+  const int h = blockIdx.y;
+  const uint8_t* mask = a.mask ? a.mask + grp * nk : nullptr;
+
+  for (int idx = tid; idx < nk * dh; idx += blockDim.x) {
+    const int j = idx / dh, d = idx - j * dh;
+    const float* kp = a.kv + (grp * nk + j) * a.ldkv + h * dh + d;
+    Ks[j * lds + d] = kp[0];
+    Vs[j * lds + d] = kp[a.voff];
+    dKs[idx] = 0.f;
+    dVs[idx] = 0.f;
+  }
+  bool open = true;
+  if (a.gate_by_mask && mask) {
+    int any = 0;
+    for (int j = 0; j < nk; ++j) any |= mask[j];
+    open = any != 0;
+  }
+  __syncthreads();
+
+  if (open) {
+    for (int i = warp; i < a.nq; i += (int)(blockDim.x >> 5)) {
+      const size_t qrow = grp * a.nq + i;
+      float qd = 0.f, dod = 0.f;
+      if (lane < dh) {
+        qd = a.q[qrow * a.ldq + h * dh + lane];
+        dod = a.d_o[qrow * a.ldo + h * dh + lane];
+      }
+      qs[lane] = qd;
+      dos[lane] = dod;
+      __syncwarp();
+      float mx = -INFINITY;
+      for (int j = lane; j < nk; j += 32) {
+        float s = 0.f, dp = 0.f;
+        for (int d = 0; d < dh; ++d) {
+          s = fmaf(qs[d], Ks[j * lds + d], s);
+          dp = fmaf(dos[d], Vs[j * lds + d], dp);
+        }
+        s *= a.scale;
+        if (mask && !mask[j]) s = kMaskedScore;
+        ps[j] = s;
+        dss[j] = dp;
+        mx = fmaxf(mx, s);
+      }
+      mx = warp_max(mx);
+      float l = 0.f;
+      for (int j = lane; j < nk; j += 32) l += expf(ps[j] - mx);
+      l = warp_sum(l);
+      const float lse = mx + logf(l);
+      const float inv_l = 1.0f / l;
+      __syncwarp();
+      float od = 0.f;
+      if (lane < dh) {
+        for (int j = 0; j < nk; ++j) od = fmaf(expf(ps[j] - mx), Vs[j * lds + lane], od);
+        od *= inv_l;
+      }
+      const float delta = warp_sum(dod * od);
+      __syncwarp();
+      for (int j = lane; j < nk; j += 32) {
+        const float p = expf(ps[j] - lse);
+        ps[j] = p;
+        dss[j] = p * (dss[j] - delta) * a.scale;
+      }
+      __syncwarp();
+      if (lane < dh) {
+        float dq = 0.f;
+        for (int j = 0; j < nk; ++j) {
+          const float dsj = dss[j], pj = ps[j];
+          dq = fmaf(dsj, Ks[j * lds + lane], dq);
+          atomicAdd(&dKs[j * dh + lane], dsj * qd);
+          atomicAdd(&dVs[j * dh + lane], pj * dod);
+        }
+        float* dqp = a.dq + qrow * a.lddq + h * dh + lane;
+        *dqp = a.dq_accumulate ? *dqp + dq : dq;
+      }
+      __syncwarp();
+    }
+  } else if (!a.dq_accumulate) {
+    for (int idx = tid; idx < a.nq * dh; idx += blockDim.x) {
+      const int i = idx / dh, d = idx - i * dh;
+      a.dq[(grp * a.nq + i) * a.lddq + h * dh + d] = 0.f;
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < nk * dh; idx += blockDim.x) {
+    const int j = idx / dh, d = idx - j * dh;
+    float* kp = a.dkv + (grp * nk + j) * a.lddkv + h * dh + d;
+    kp[0] = dKs[idx];
+    kp[a.dvoff] = dVs[idx];
+  }
+}
+
+size_t attn_bwd_smem(int nk, int dh) {
+  const int nkp = (nk + 31) & ~31;
+  return (size_t)(2 * nk * (dh + 1) + 2 * nk * dh + 4 * (64 + 2 * nkp)) * sizeof(float);
+}
+
+// ------------------------------------------------------------------------------ recurrent branch
+
+// Geometry of the ship rows of one temporal sublayer: row s = b * n_rec + n of step t sits at
+// (t * Rr + s) * D in the time-major buffers; its state at hid + s * 4 D (h | three taps, oldest first).
+struct ShipGeom {
+  int T, Rr, D, n_rec, B;
+  const uint8_t* done;   // (T, B) or null
+};
+
+// u_t = conv bias + sum over lags of tap * padded value, a lag being valid while no episode boundary
+// lies between (griffin.py:67-140).
+__global__ void __launch_bounds__(256) k_conv_fwd(const float* __restrict__ b1, const float* __restrict__ hid,
+                                                  const float* __restrict__ cw, const float* __restrict__ cb,
+                                                  float* __restrict__ u, ShipGeom gm) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)gm.Rr * gm.D) return;
+  const int s = (int)(idx / gm.D), d = (int)(idx - (size_t)s * gm.D);
+  const int b = s / gm.n_rec;
+  const float* hp = hid + (size_t)s * 4 * gm.D + d;
+  float p3 = hp[gm.D], p2 = hp[2 * gm.D], p1 = hp[3 * gm.D];
+  const float w0 = cw[d * 4], w1 = cw[d * 4 + 1], w2 = cw[d * 4 + 2], w3 = cw[d * 4 + 3], bias = cb[d];
+  int cur = BNB_CONV_KERNEL - 1;
+  for (int t = 0; t < gm.T; ++t) {
+    if (t >= 1) {
+      const bool boundary = gm.done && gm.done[(size_t)(t - 1) * gm.B + b];
+      cur = boundary ? 0 : min(cur + 1, BNB_CONV_KERNEL - 1);
+    }
+    const size_t at = ((size_t)t * gm.Rr + s) * gm.D + d;
+    const float xt = b1[at];
+    const float t0 = cur >= 3 ? __fmul_rn(p3, w0) : 0.f;
+    const float t1 = cur >= 2 ? __fmul_rn(p2, w1) : 0.f;
+    const float t2 = cur >= 1 ? __fmul_rn(p1, w2) : 0.f;
+    const float t3 = __fmul_rn(xt, w3);
+    u[at] = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(t0, t1), t2), t3), bias);
+    p3 = p2; p2 = p1; p1 = xt;
+  }
+}
+
+// h_t = a_t h_{t-1} + sqrt(1 - a_t^2) (i_t u_t), a_t = sigmoid(lambda)^(8 r_t), zeroed after a boundary
+// (griffin.py:169-219); every h_t is kept.
+__global__ void __launch_bounds__(256) k_scan_fwd(const float* __restrict__ za, const float* __restrict__ zx,
+                                                  const float* __restrict__ u, const float* __restrict__ hid,
+                                                  const float* __restrict__ log_lambda, float* __restrict__ hs, ShipGeom gm) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)gm.Rr * gm.D) return;
+  const int s = (int)(idx / gm.D), d = (int)(idx - (size_t)s * gm.D);
+  const int b = s / gm.n_rec;
+  float h = hid[(size_t)s * 4 * gm.D + d];
+  const float base = sigmoidf_(log_lambda[d]);
+  for (int t = 0; t < gm.T; ++t) {
+    const size_t at = ((size_t)t * gm.Rr + s) * gm.D + d;
+    const float rg = sigmoidf_(za[at]), ig = sigmoidf_(zx[at]);
+    float a = powf(base, kRglruC * rg);
+    const float gate = sqrtf(fmaxf((1.0f - a) * (1.0f + a), kGateFloor));
+    const float bb = gate * (ig * u[at]);
+    if (t >= 1 && gm.done && gm.done[(size_t)(t - 1) * gm.B + b]) a = 0.f;
+    h = a * h + bb;
+    hs[at] = h;
+  }
+}
+
+// Reverse-time adjoint of k_scan_fwd.  In: za, zx (with bias), u, hs, dhs (gradient reaching every
+// h_t from the output path) and the gradient of the final state.  Out: d za, d zx in place of za,
+// zx; the direct part of d u in place of dhs; d h0; d log_lambda (reduced over rows, atomics).
+__global__ void __launch_bounds__(256) k_scan_bwd(float* za, float* zx, const float* __restrict__ u,
+                                                  const float* __restrict__ hs, float* dhs, const float* __restrict__ hid,
+                                                  const float* __restrict__ d_hid_out, float* __restrict__ d_hid_in,
+                                                  const float* __restrict__ log_lambda, float* __restrict__ d_log_lambda,
+                                                  ShipGeom gm) {
+  __shared__ float s_dl[MAXW];
+  if ((int)threadIdx.x < gm.D) s_dl[threadIdx.x] = 0.f;
+  __syncthreads();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool live = idx < (size_t)gm.Rr * gm.D;
+  const int s = live ? (int)(idx / gm.D) : 0, d = live ? (int)(idx - (size_t)s * gm.D) : 0;
+  if (live) {
+    const int b = s / gm.n_rec;
+    const float lam = log_lambda[d];
+    const float base = sigmoidf_(lam);
+    const float logb = logf(base);
+    float carry = d_hid_out ? d_hid_out[(size_t)s * 4 * gm.D + d] : 0.f;
+    float dl = 0.f;
+    for (int t = gm.T - 1; t >= 0; --t) {
+      const size_t at = ((size_t)t * gm.Rr + s) * gm.D + d;
+      const float dh = dhs[at] + carry;
+      const float rg = sigmoidf_(za[at]), ig = sigmoidf_(zx[at]), uv = u[at];
+      const float a = powf(base, kRglruC * rg);
+      const float cc = (1.0f - a) * (1.0f + a);
+      const float gate = sqrtf(fmaxf(cc, kGateFloor));
+      const bool reset = t >= 1 && gm.done && gm.done[(size_t)(t - 1) * gm.B + b];
+      const float hprev = t > 0 ? hs[at - (size_t)gm.Rr * gm.D] : hid[(size_t)s * 4 * gm.D + d];
+      float da = reset ? 0.f : dh * hprev;
+      carry = reset ? 0.f : dh * a;
+      const float dgate = dh * ig * uv;
+      const float di = dh * gate * uv;
+      if (cc > kGateFloor) da -= dgate * a / gate;
+      const float dr = da * a * kRglruC * logb;
+      dl = fmaf(da * a * kRglruC * rg, 1.0f - base, dl);
+      za[at] = dr * rg * (1.0f - rg);
+      zx[at] = di * ig * (1.0f - ig);
+      dhs[at] = dh * gate * ig;
+    }
+    if (d_hid_in) d_hid_in[(size_t)s * 4 * gm.D + d] = carry;
+    atomicAdd(&s_dl[d], dl);
+  }
+  __syncthreads();
+  if ((int)threadIdx.x < gm.D) atomicAdd(d_log_lambda + threadIdx.x, s_dl[threadIdx.x]);
+}
+
+// Adjoint of k_conv_fwd: d u -> d linear1 output, d stored taps, d conv weight and bias.  The
+// new tap buffer is the last three padded values, so its gradient joins there.
+__global__ void __launch_bounds__(256) k_conv_bwd(const float* __restrict__ du, const float* __restrict__ b1,
+                                                  const float* __restrict__ hid, const float* __restrict__ d_hid_out,
+                                                  float* __restrict__ d_hid_in, const float* __restrict__ cw,
+                                                  float* __restrict__ db1, float* __restrict__ d_cw, float* __restrict__ d_cb,
+                                                  ShipGeom gm) {
+  __shared__ float s_w[MAXW * 4], s_b[MAXW];
+  for (int i = threadIdx.x; i < gm.D * 4; i += blockDim.x) s_w[i] = 0.f;
+  if ((int)threadIdx.x < gm.D) s_b[threadIdx.x] = 0.f;
+  __syncthreads();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool live = idx < (size_t)gm.Rr * gm.D;
+  const int s = live ? (int)(idx / gm.D) : 0, d = live ? (int)(idx - (size_t)s * gm.D) : 0;
+  if (live) {
+    const int b = s / gm.n_rec, T = gm.T, D = gm.D;
+    const float* hp = hid + (size_t)s * 4 * D + d;
+    // padded index p: 0..2 the stored taps, 3 + t the linear1 output of step t
+    auto emit = [&](int p, float v) {
+      if (p >= T && d_hid_out) v += d_hid_out[(size_t)s * 4 * D + D + (size_t)(p - T) * D + d];
+      if (p < 3) {
+        if (d_hid_in) d_hid_in[(size_t)s * 4 * D + D + (size_t)p * D + d] = v;
+      } else {
+        db1[((size_t)(p - 3) * gm.Rr + s) * D + d] = v;
+      }
+    };
+    const float w[4] = {cw[d * 4], cw[d * 4 + 1], cw[d * 4 + 2], cw[d * 4 + 3]};
+    float pad[4] = {hp[D], hp[2 * D], hp[3 * D], 0.f};   // padded[t .. t+3] at step t
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};                 // d padded[t .. t+3]
+    float dw[4] = {0.f, 0.f, 0.f, 0.f}, dbias = 0.f;
+    int cur = BNB_CONV_KERNEL - 1;
+    for (int t = 0; t < T; ++t) {
+      if (t >= 1) {
+        const bool boundary = gm.done && gm.done[(size_t)(t - 1) * gm.B + b];
+        cur = boundary ? 0 : min(cur + 1, BNB_CONV_KERNEL - 1);
+      }
+      const size_t at = ((size_t)t * gm.Rr + s) * D + d;
+      pad[3] = b1[at];
+      const float g = du[at];
+      dbias += g;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const bool valid = (3 - k) <= cur;   // tap k reads lag 3 - k
+        if (valid) {
+          acc[k] = fmaf(g, w[k], acc[k]);
+          dw[k] = fmaf(g, pad[k], dw[k]);
+        }
+      }
+      emit(t, acc[0]);
+      acc[0] = acc[1]; acc[1] = acc[2]; acc[2] = acc[3]; acc[3] = 0.f;
+      pad[0] = pad[1]; pad[1] = pad[2]; pad[2] = pad[3];
+    }
+    emit(T, acc[0]);
+    emit(T + 1, acc[1]);
+    emit(T + 2, acc[2]);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) atomicAdd(&s_w[d * 4 + k], dw[k]);
+    atomicAdd(&s_b[d], dbias);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < gm.D * 4; i += blockDim.x) atomicAdd(d_cw + i, s_w[i]);
+  if ((int)threadIdx.x < gm.D) atomicAdd(d_cb + threadIdx.x, s_b[threadIdx.x]);
+}
+
+// ------------------------------------------------------------------------------ host side
+
+struct Arena {
+  char* base;
+  size_t off = 0;
+  float* take(size_t n_floats) {
+    float* p = base ? reinterpret_cast<float*>(base + off) : nullptr;
+    off += (n_floats * sizeof(float) + 255) & ~(size_t)255;
+    return p;
+  }
+};
+
+constexpr int N_DBUF = 17;
+
+struct Bufs {
+  float* bound;        // inputs of sublayers 1 .. S-1
+  float* ping[2];      // gradient with respect to a sublayer's input, alternating
+  float* d[N_DBUF];    // rows x D each
+  float* w3[2];        // rows x 3D
+  float* w4[3];        // rows x 4D
+  float* inv[2];       // rows
+  float *bul_n, *bul_inv, *kvb, *dkvb, *bul_dn;
+};
+
+void plan(Arena& ar, Bufs& b, int S, size_t R, int D, size_t RB) {
+  b.bound = ar.take((size_t)(S > 1 ? S - 1 : 0) * R * D);
+  for (auto& p : b.ping) p = ar.take(R * D);
+  for (auto& p : b.d) p = ar.take(R * D);
+  for (auto& p : b.w3) p = ar.take(R * 3 * D);
+  for (auto& p : b.w4) p = ar.take(R * 4 * D);
+  for (auto& p : b.inv) p = ar.take(R);
+  b.bul_n = ar.take(RB * D);
+  b.bul_inv = ar.take(RB);
+  b.kvb = ar.take(RB * 2 * D);
+  b.dkvb = ar.take(RB * 2 * D);
+  b.bul_dn = ar.take(RB * D);
+}
+
+inline int blocks_for(size_t n, int per_block, int cap = 148 * 8) {
+  size_t g = (n + per_block - 1) / per_block;
+  if (g > (size_t)cap) g = cap;
+  return g < 1 ? 1 : (int)g;
+}
+
+struct Ctx {
+  int D, H;
+  cudaStream_t st;
+  Bufs b;
+};
+
+void rmsnorm_fwd(const Ctx& c, const float* x, const float* g, float* n, float* inv, size_t rows) {
+  if (!rows) return;
+  count_launch();
+  k_rmsnorm_fwd<<<blocks_for(rows, 8), 256, 0, c.st>>>(x, g, n, inv, (int)rows, c.D);
+}
+void rmsnorm_bwd(const Ctx& c, const float* x, const float* g, const float* inv, const float* dn, const float* dres,
+                 float* dx, float* dg, size_t rows) {
+  if (!rows) return;
+  count_launch();
+  k_rmsnorm_bwd<<<blocks_for(rows, 64, 148 * 2), 256, 0, c.st>>>(x, g, inv, dn, dres, dx, dg, (int)rows, c.D);
+}
+void gelu_mul_fwd(const Ctx& c, const float* g, const float* u, float* h, size_t n) {
+  if (!n) return;
+  count_launch();
+  k_gelu_mul_fwd<<<blocks_for(n, 1024), 256, 0, c.st>>>(g, u, h, n);
+}
+void gelu_mul_bwd(const Ctx& c, const float* g, const float* u, const float* dh, float* dg, float* du, size_t n) {
+  if (!n) return;
+  count_launch();
+  k_gelu_mul_bwd<<<blocks_for(n, 1024), 256, 0, c.st>>>(g, u, dh, dg, du, n);
+}
+void colsum(const Ctx& c, const float* a, float* out, size_t rows, int N) {
+  if (!rows) return;
+  count_launch();
+  dim3 grid((N + 31) / 32, blocks_for(rows, 256, 64));
+  k_colsum<<<grid, 256, 0, c.st>>>(a, out, (int)rows, N);
+}
+
+// Gated MLP at the end of every sublayer: given x1 and d y (y = x1 + down(gelu(gate n) * up n),
+// n = rmsnorm(x1)), accumulates the weight gradients and writes d x1 to dx1.
+// Uses w4[0..2], inv[1], d[15], d[16].
+void mlp_bwd(const Ctx& c, const float* x1, const float* dy, float* dx1, size_t rows, const float* g2, const float* Wg,
+             const float* Wu, const float* Wd, float* dg2, float* dWg, float* dWu, float* dWd) {
+  const int D = c.D, F = 4 * c.D, M = (int)rows;
+  float* n2 = c.b.d[15];
+  float* dn2 = c.b.d[16];
+  float* gb = c.b.w4[0];
+  float* ub = c.b.w4[1];
+  float* hb = c.b.w4[2];
+  rmsnorm_fwd(c, x1, g2, n2, c.b.inv[1], rows);
+  gemm(NT, n2, D, Wg, D, gb, F, M, F, D, nullptr, nullptr, 0, 0, c.st);
+  gemm(NT, n2, D, Wu, D, ub, F, M, F, D, nullptr, nullptr, 0, 0, c.st);
+  gelu_mul_fwd(c, gb, ub, hb, rows * F);
+  gemm(TN, dy, D, hb, F, dWd, F, D, F, M, nullptr, nullptr, 0, 0, c.st);        // dWd (D, 4D) += dy^T h
+  gemm(NN, dy, D, Wd, F, hb, F, M, F, D, nullptr, nullptr, 0, 0, c.st);         // dh = dy Wd
+  gelu_mul_bwd(c, gb, ub, hb, gb, ub, rows * F);                                // gb <- d gate, ub <- d up
+  gemm(TN, gb, F, n2, D, dWg, D, F, D, M, nullptr, nullptr, 0, 0, c.st);
+  gemm(TN, ub, F, n2, D, dWu, D, F, D, M, nullptr, nullptr, 0, 0, c.st);
+  gemm(NN, gb, F, Wg, D, dn2, D, M, D, F, nullptr, nullptr, 0, 0, c.st);
+  gemm(NN, ub, F, Wu, D, dn2, D, M, D, F, nullptr, nullptr, 0, 1, c.st);
+  rmsnorm_bwd(c, x1, g2, c.b.inv[1], dn2, dy, dx1, dg2, rows);
+}
+
+template <int DH>
+void attn_fwd_t(const Ctx& c, const float* qkv, const uint8_t* alive, float* o, int G, int NM, const float* kvb,
+                const uint8_t* bactive, int nb) {
+  count_launch();
+  k_attn_fwd<DH><<<G, 128, 0, c.st>>>(qkv, alive, o, NM, c.D, c.H, kvb, bactive, nb);
+}
+void attn_fwd(const Ctx& c, const float* qkv, const uint8_t* alive, float* o, int G, int NM, const float* kvb,
+              const uint8_t* bactive, int nb) {
+  if (!G) return;
+  switch (c.D / c.H) {
+    case 8: attn_fwd_t<8>(c, qkv, alive, o, G, NM, kvb, bactive, nb); break;
+    case 16: attn_fwd_t<16>(c, qkv, alive, o, G, NM, kvb, bactive, nb); break;
+    default: attn_fwd_t<32>(c, qkv, alive, o, G, NM, kvb, bactive, nb); break;
+  }
+}
+int attn_bwd(const Ctx& c, const AttnBwdArgs& a, int G) {
+  if (!G) return BNB_OK;
+  const size_t sm = attn_bwd_smem(a.nk, a.dh);
+  if (sm > 200 * 1024) return BNB_ERR_TOO_MANY_TOKENS;
+  if (cudaFuncSetAttribute(k_attn_bwd, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm) != cudaSuccess)
+    return BNB_ERR_LAUNCH;
+  count_launch();
+  k_attn_bwd<<<dim3(G, c.H), 128, sm, c.st>>>(a);
+  return BNB_OK;
+}
+
+int spatial_bwd(const Ctx& c, const BnbSpatialWeights& w, const BnbSpatialGrads& dw, const float* x, const uint8_t* alive,
+                const BnbBullets* bul, float* d_bullets, const float* dy, float* dx, int G, int NM) {
+  const int D = c.D;
+  const size_t R = (size_t)G * NM;
+  const int M = (int)R;
+  const Bufs& b = c.b;
+  float *n1 = b.d[0], *o = b.d[1], *x1 = b.d[2], *dx1 = b.d[3], *d_o = b.d[4], *dn1 = b.d[5];
+  float *qkv = b.w3[0], *dqkv = b.w3[1];
+  const bool reads = bul && w.kv_bullet_w;
+  const int nb = reads ? bul->per_env : 0;
+  const size_t RB = (size_t)G * nb;
+  if (reads && (!dw.kv_bullet_w || !dw.norm_bullet_w)) return BNB_ERR_NULL_POINTER;
+
+  rmsnorm_fwd(c, x, w.norm1_w, n1, b.inv[0], R);
+  gemm(NT, n1, D, w.qkv_w, D, qkv, 3 * D, M, 3 * D, D, nullptr, nullptr, 0, 0, c.st);
+  if (reads) {
+    rmsnorm_fwd(c, bul->tokens, w.norm_bullet_w, b.bul_n, b.bul_inv, RB);
+    gemm(NT, b.bul_n, D, w.kv_bullet_w, D, b.kvb, 2 * D, (int)RB, 2 * D, D, nullptr, nullptr, 0, 0, c.st);
+  }
+  attn_fwd(c, qkv, alive, o, G, NM, reads ? b.kvb : nullptr, reads ? bul->active : nullptr, nb);
+  gemm(NT, o, D, w.out_w, D, x1, D, M, D, D, nullptr, x, D, 0, c.st);            // x1 = x + o Wout^T
+
+  mlp_bwd(c, x1, dy, dx1, R, w.norm2_w, w.gate_w, w.up_w, w.down_w, dw.norm2_w, dw.gate_w, dw.up_w, dw.down_w);
+
+  gemm(TN, dx1, D, o, D, dw.out_w, D, D, D, M, nullptr, nullptr, 0, 0, c.st);
+  gemm(NN, dx1, D, w.out_w, D, d_o, D, M, D, D, nullptr, nullptr, 0, 0, c.st);
+  const int dh = D / c.H;
+  const float scale = 1.0f / sqrtf((float)dh);
+  AttnBwdArgs self{qkv, 3 * D, qkv + D, 3 * D, D, alive, d_o, D, dqkv, 3 * D, 0, dqkv + D, 3 * D, D, NM, NM, dh, scale, 0};
+  int rc = attn_bwd(c, self, G);
+  if (rc) return rc;
+  if (reads) {
+    AttnBwdArgs cross{qkv, 3 * D, b.kvb, 2 * D, D, bul->active, d_o, D, dqkv, 3 * D, 1, b.dkvb, 2 * D, D, NM, nb, dh, scale,
+                      bul->active ? 1 : 0};
+    rc = attn_bwd(c, cross, G);
+    if (rc) return rc;
+    gemm(TN, b.dkvb, 2 * D, b.bul_n, D, dw.kv_bullet_w, D, 2 * D, D, (int)RB, nullptr, nullptr, 0, 0, c.st);
+    gemm(NN, b.dkvb, 2 * D, w.kv_bullet_w, D, b.bul_dn, D, (int)RB, D, 2 * D, nullptr, nullptr, 0, 0, c.st);
+    // the bullet tokens feed every sublayer that reads them: their gradient accumulates
+    float* sink = d_bullets ? d_bullets : b.bul_n;   // bul_n is free once the weight gradient above is queued
+    rmsnorm_bwd(c, bul->tokens, w.norm_bullet_w, b.bul_inv, b.bul_dn, d_bullets, sink, dw.norm_bullet_w, RB);
+  }
+  gemm(TN, dqkv, 3 * D, n1, D, dw.qkv_w, D, 3 * D, D, M, nullptr, nullptr, 0, 0, c.st);
+  gemm(NN, dqkv, 3 * D, w.qkv_w, D, dn1, D, M, D, 3 * D, nullptr, nullptr, 0, 0, c.st);
+  rmsnorm_bwd(c, x, w.norm1_w, b.inv[0], dn1, dx1, dx, dw.norm1_w, R);
+  return BNB_OK;
+}
+
+void gather(const Ctx& c, const float* full, float* compact, size_t rows, int per_grp, int NM, int n0) {
+  if (!rows) return;
+  count_launch();
+  k_gather_rows<<<blocks_for(rows * (c.D / 4), 256), 256, 0, c.st>>>(reinterpret_cast<const float4*>(full),
+                                                                    reinterpret_cast<float4*>(compact), rows, c.D / 4,
+                                                                    per_grp, NM, n0);
+}
+void scatter(const Ctx& c, const float* compact, float* full, size_t rows, int per_grp, int NM, int n0) {
+  if (!rows) return;
+  count_launch();
+  k_scatter_rows<<<blocks_for(rows * (c.D / 4), 256), 256, 0, c.st>>>(reinterpret_cast<const float4*>(compact),
+                                                                     reinterpret_cast<float4*>(full), rows, c.D / 4,
+                                                                     per_grp, NM, n0);
+}
+
+// One temporal sublayer: the recurrent path over the ship rows, the non-recurrent one over the
+// field rows (griffin.py:249-317), both sharing every parameter but field_sub.
+int temporal_bwd(const Ctx& c, const BnbTemporalWeights& w, const BnbTemporalGrads& dw, const float* x, const float* hid,
+                 const float* d_hid_out, float* d_hid_in, const uint8_t* done, const float* dy, float* dx, int T, int B,
+                 int NM, int n_rec) {
+  const int D = c.D;
+  const Bufs& b = c.b;
+  const int G = T * B;
+  const size_t Rs = (size_t)G * n_rec, Rf = (size_t)G * (NM - n_rec);
+  if (Rs) {
+    const int M = (int)Rs, Rr = B * n_rec;
+    ShipGeom gm{T, Rr, D, n_rec, B, done};
+    float *xs = b.d[0], *n = b.d[1], *b1 = b.d[2], *u = b.d[3], *za = b.d[4], *zx = b.d[5], *hs = b.d[6], *b2p = b.d[7],
+          *m = b.d[8], *x1 = b.d[9], *dys = b.d[10], *dx1 = b.d[11], *dm = b.d[12], *dn = b.d[13], *dxs = b.d[14];
+    const int sblocks = (int)(((size_t)Rr * D + 255) / 256);
+    gather(c, x, xs, Rs, n_rec, NM, 0);
+    gather(c, dy, dys, Rs, n_rec, NM, 0);
+    rmsnorm_fwd(c, xs, w.norm1_w, n, b.inv[0], Rs);
+    gemm(NT, n, D, w.linear1_w, D, b1, D, M, D, D, nullptr, nullptr, 0, 0, c.st);
+    count_launch();
+    k_conv_fwd<<<sblocks, 256, 0, c.st>>>(b1, hid, w.conv_w, w.conv_b, u, gm);
+    gemm(NT, u, D, w.a_w, D, za, D, M, D, D, w.a_b, nullptr, 0, 0, c.st);
+    gemm(NT, u, D, w.x_w, D, zx, D, M, D, D, w.x_b, nullptr, 0, 0, c.st);
+    count_launch();
+    k_scan_fwd<<<sblocks, 256, 0, c.st>>>(za, zx, u, hid, w.log_lambda, hs, gm);
+    gemm(NT, n, D, w.linear2_w, D, b2p, D, M, D, D, nullptr, nullptr, 0, 0, c.st);
+    gelu_mul_fwd(c, b2p, hs, m, Rs * D);                                          // m = h * gelu(linear2 n)
+    gemm(NT, m, D, w.out_w, D, x1, D, M, D, D, nullptr, xs, D, 0, c.st);
+
+    mlp_bwd(c, x1, dys, dx1, Rs, w.norm2_w, w.gate_w, w.up_w, w.down_w, dw.norm2_w, dw.gate_w, dw.up_w, dw.down_w);
+
+    gemm(TN, dx1, D, m, D, dw.out_w, D, D, D, M, nullptr, nullptr, 0, 0, c.st);
+    gemm(NN, dx1, D, w.out_w, D, dm, D, M, D, D, nullptr, nullptr, 0, 0, c.st);
+    gelu_mul_bwd(c, b2p, hs, dm, b2p, dm, Rs * D);                                // b2p <- d linear2 out, dm <- d h
+    gemm(TN, b2p, D, n, D, dw.linear2_w, D, D, D, M, nullptr, nullptr, 0, 0, c.st);
+    gemm(NN, b2p, D, w.linear2_w, D, dn, D, M, D, D, nullptr, nullptr, 0, 0, c.st);
+    count_launch();
+    k_scan_bwd<<<sblocks, 256, 0, c.st>>>(za, zx, u, hs, dm, hid, d_hid_out, d_hid_in, w.log_lambda, dw.log_lambda, gm);
+    // za, zx hold d za, d zx; dm the direct part of d u
+    gemm(TN, za, D, u, D, dw.a_w, D, D, D, M, nullptr, nullptr, 0, 0, c.st);
+    gemm(TN, zx, D, u, D, dw.x_w, D, D, D, M, nullptr, nullptr, 0, 0, c.st);
+    colsum(c, za, dw.a_b, Rs, D);
+    colsum(c, zx, dw.x_b, Rs, D);
+    gemm(NN, za, D, w.a_w, D, dm, D, M, D, D, nullptr, nullptr, 0, 1, c.st);
+    gemm(NN, zx, D, w.x_w, D, dm, D, M, D, D, nullptr, nullptr, 0, 1, c.st);
+    float* db1 = za;   // free now
+    count_launch();
+    k_conv_bwd<<<sblocks, 256, 0, c.st>>>(dm, b1, hid, d_hid_out, d_hid_in, w.conv_w, db1, dw.conv_w, dw.conv_b, gm);
+    gemm(TN, db1, D, n, D, dw.linear1_w, D, D, D, M, nullptr, nullptr, 0, 0, c.st);
+    gemm(NN, db1, D, w.linear1_w, D, dn, D, M, D, D, nullptr, nullptr, 0, 1, c.st);
+    rmsnorm_bwd(c, xs, w.norm1_w, b.inv[0], dn, dx1, dxs, dw.norm1_w, Rs);
+    scatter(c, dxs, dx, Rs, n_rec, NM, 0);
+  }
+  if (Rf) {
+    if (!w.field_sub_w || !dw.field_sub_w) return BNB_ERR_NULL_POINTER;
+    const int M = (int)Rf, nf = NM - n_rec;
+    float *xf = b.d[0], *n = b.d[1], *c1 = b.d[2], *b1 = b.d[3], *b2p = b.d[4], *m = b.d[5], *x1 = b.d[6], *dyf = b.d[7],
+          *dx1 = b.d[8], *dm = b.d[9], *dc1 = b.d[10], *dn = b.d[11], *dxf = b.d[12];
+    gather(c, x, xf, Rf, nf, NM, n_rec);
+    gather(c, dy, dyf, Rf, nf, NM, n_rec);
+    rmsnorm_fwd(c, xf, w.norm1_w, n, b.inv[0], Rf);
+    gemm(NT, n, D, w.linear1_w, D, c1, D, M, D, D, nullptr, nullptr, 0, 0, c.st);
+    gemm(NT, c1, D, w.field_sub_w, D, b1, D, M, D, D, nullptr, nullptr, 0, 0, c.st);
+    gemm(NT, n, D, w.linear2_w, D, b2p, D, M, D, D, nullptr, nullptr, 0, 0, c.st);
+    gelu_mul_fwd(c, b2p, b1, m, Rf * D);
+    gemm(NT, m, D, w.out_w, D, x1, D, M, D, D, nullptr, xf, D, 0, c.st);
+
+    mlp_bwd(c, x1, dyf, dx1, Rf, w.norm2_w, w.gate_w, w.up_w, w.down_w, dw.norm2_w, dw.gate_w, dw.up_w, dw.down_w);
+
+    gemm(TN, dx1, D, m, D, dw.out_w, D, D, D, M, nullptr, nullptr, 0, 0, c.st);
+    gemm(NN, dx1, D, w.out_w, D, dm, D, M, D, D, nullptr, nullptr, 0, 0, c.st);
+    gelu_mul_bwd(c, b2p, b1, dm, b2p, dm, Rf * D);                                // b2p <- d linear2 out, dm <- d b1
+    gemm(TN, dm, D, c1, D, dw.field_sub_w, D, D, D, M, nullptr, nullptr, 0, 0, c.st);
+    gemm(NN, dm, D, w.field_sub_w, D, dc1, D, M, D, D, nullptr, nullptr, 0, 0, c.st);
+    gemm(TN, dc1, D, n, D, dw.linear1_w, D, D, D, M, nullptr, nullptr, 0, 0, c.st);
+    gemm(NN, dc1, D, w.linear1_w, D, dn, D, M, D, D, nullptr, nullptr, 0, 0, c.st);
+    gemm(TN, b2p, D, n, D, dw.linear2_w, D, D, D, M, nullptr, nullptr, 0, 0, c.st);
+    gemm(NN, b2p, D, w.linear2_w, D, dn, D, M, D, D, nullptr, nullptr, 0, 1, c.st);
+    rmsnorm_bwd(c, xf, w.norm1_w, b.inv[0], dn, dx1, dxf, dw.norm1_w, Rf);
+    scatter(c, dxf, dx, Rf, nf, NM, n_rec);
+  }
+  return BNB_OK;
+}
+
+bool dims_ok(int D, int H) {
+  if (D <= 0 || D > MAXW || D % 32 != 0 || H <= 0 || D % H != 0) return false;
+  const int dh = D / H;
+  return dh == 8 || dh == 16 || dh == 32;
+}
+
+}  // namespace
+
+size_t scratch_bytes(int n_blocks, int n_spatial, int n_temporal, int D, const BnbBatch& bt, int T, int bullets_per_env) {
+  Arena ar{nullptr};
+  Bufs b;
+  const int S = n_blocks * (n_spatial + n_temporal);
+  const size_t G = (size_t)T * bt.n_envs;
+  plan(ar, b, S, G * bt.tokens_per_env, D, G * (bullets_per_env > 0 ? bullets_per_env : 0));
+  return ar.off + 256;
+}
+
+int trunk_sequence_bwd(const TrunkBwdArgs& a) {
+  const BnbBatch& bt = *a.batch;
+  if (bt.tok_off || bt.ship_off) return BNB_ERR_UNSUPPORTED_DIMS;   // environments of one size only
+  if (!dims_ok(a.D, a.H)) return BNB_ERR_UNSUPPORTED_DIMS;
+  const int D = a.D, T = a.T, B = bt.n_envs, NM = bt.tokens_per_env, n_rec = bt.ships_per_env;
+  if (T < 1 || B < 0 || NM < 1 || n_rec < 0 || n_rec > NM) return BNB_ERR_BAD_ARGUMENT;
+  const int G = T * B;
+  const size_t R = (size_t)G * NM;
+  if (R > (size_t)INT32_MAX / 2) return BNB_ERR_TOO_MANY_TOKENS;
+  const int S = a.n_blocks * (a.n_spatial + a.n_temporal);
+  const int nb = a.bullets ? a.bullets->per_env : 0;
+  const size_t RB = (size_t)G * nb;
+  const size_t Rr = (size_t)B * n_rec;
+  cudaStream_t st = a.stream;
+  if (R == 0) return BNB_OK;
+
+  Ctx c;
+  c.D = D;
+  c.H = a.H;
+  c.st = st;
+  uintptr_t base = (reinterpret_cast<uintptr_t>(a.scratch) + 255) & ~(uintptr_t)255;
+  Arena ar{reinterpret_cast<char*>(base)};
+  plan(ar, c.b, S, R, D, RB);
+  if (ar.off + (base - reinterpret_cast<uintptr_t>(a.scratch)) > a.scratch_bytes) return BNB_ERR_SCRATCH_TOO_SMALL;
+
+  if (S == 0) {
+    cudaMemcpyAsync(a.dx, a.dy, R * D * sizeof(float), cudaMemcpyDeviceToDevice, st);
+    return BNB_OK;
+  }
+
+  // first pass: the input of every sublayer
+  const float* cur = a.x;
+  const float* inputs[256];
+  if (S > 256) return BNB_ERR_BAD_ARGUMENT;
+  int s = 0;
+  for (int blk = 0; blk < a.n_blocks; ++blk) {
+    for (int j = 0; j < a.n_spatial; ++j, ++s) {
+      inputs[s] = cur;
+      if (s + 1 == S) break;
+      float* out = c.b.bound + (size_t)s * R * D;
+      int rc = exact::spatial_block(a.spatial[blk * a.n_spatial + j], D, a.H, cur, a.alive, a.bullets, out, bt, T, false,
+                                    c.b.w3[0], c.b.d[1], c.b.kvb, G > 0 ? G : 1, st);
+      if (rc) return rc;
+      cur = out;
+    }
+    for (int j = 0; j < a.n_temporal; ++j, ++s) {
+      inputs[s] = cur;
+      if (s + 1 == S) break;
+      float* out = c.b.bound + (size_t)s * R * D;
+      const int slot = blk * a.n_temporal + j;
+      int rc = exact::temporal_block(a.temporal[slot], D, cur, out, a.hidden_in + (size_t)slot * Rr * 4 * D, nullptr, a.done,
+                                     nullptr, bt, T, false, st);
+      if (rc) return rc;
+      cur = out;
+    }
+  }
+
+  if (a.d_bullets && RB) cudaMemsetAsync(a.d_bullets, 0, RB * D * sizeof(float), st);
+
+  // second pass: sublayers in reverse
+  const float* dcur = a.dy;
+  for (int blk = a.n_blocks - 1; blk >= 0; --blk) {
+    for (int j = a.n_temporal - 1; j >= 0; --j) {
+      s = blk * (a.n_spatial + a.n_temporal) + a.n_spatial + j;
+      float* dout = s == 0 ? a.dx : c.b.ping[s & 1];
+      const int slot = blk * a.n_temporal + j;
+      const size_t hoff = (size_t)slot * Rr * 4 * D;
+      int rc = temporal_bwd(c, a.temporal[slot], a.d_temporal[slot], inputs[s], a.hidden_in + hoff,
+                            a.d_hidden_out ? a.d_hidden_out + hoff : nullptr, a.d_hidden_in ? a.d_hidden_in + hoff : nullptr,
+                            a.done, dcur, dout, T, B, NM, n_rec);
+      if (rc) return rc;
+      dcur = dout;
+    }
+    for (int j = a.n_spatial - 1; j >= 0; --j) {
+      s = blk * (a.n_spatial + a.n_temporal) + j;
+      float* dout = s == 0 ? a.dx : c.b.ping[s & 1];
+      const int k = blk * a.n_spatial + j;
+      int rc = spatial_bwd(c, a.spatial[k], a.d_spatial[k], inputs[s], a.alive, a.bullets, a.d_bullets, dcur, dout, G, NM);
+      if (rc) return rc;
+      dcur = dout;
+    }
+  }
+  return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
+}
+
+}  // namespace grad
+}  // namespace bnb

@@ -1,0 +1,39 @@
+// Backward pass of the Yemong trunk's sequence forward (grad_kernels.cu).
+#pragma once
+#include <cuda_runtime.h>
+
+#include "bnb_trunk.h"
+
+namespace bnb {
+namespace grad {
+
+struct TrunkBwdArgs {
+  const BnbSpatialWeights* spatial;
+  const BnbTemporalWeights* temporal;
+  const BnbSpatialGrads* d_spatial;
+  const BnbTemporalGrads* d_temporal;
+  int n_blocks, n_spatial, n_temporal, D, H;
+  const float* x;
+  const uint8_t* alive;
+  const BnbBullets* bullets;
+  const float* hidden_in;
+  const uint8_t* done;
+  const BnbBatch* batch;
+  int T;
+  const float* dy;
+  const float* d_hidden_out;
+  float* dx;
+  float* d_hidden_in;
+  float* d_bullets;
+  void* scratch;
+  size_t scratch_bytes;
+  cudaStream_t stream;
+};
+
+// Bytes of scratch trunk_sequence_bwd needs for this structure and batch.
+size_t scratch_bytes(int n_blocks, int n_spatial, int n_temporal, int D, const BnbBatch& b, int T, int bullets_per_env);
+
+int trunk_sequence_bwd(const TrunkBwdArgs& a);
+
+}  // namespace grad
+}  // namespace bnb

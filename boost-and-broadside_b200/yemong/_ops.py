@@ -7,8 +7,10 @@ shape-only fake implementation; the real implementation below builds the ctypes 
 structs, looks up (or rebuilds) the tensor-core weight images, takes scratch from torch's
 allocator and launches on the current stream.  Nothing here synchronises.
 
-The operators are forward-only: no autograd formula is registered, and the module methods
-refuse inputs that require grad.
+``trunk_forward`` carries an autograd formula (``trunk_backward`` -> ``bnb_trunk_sequence_bwd``, float32,
+environments of one size): a step or sequence through ``YemongBlock`` / ``YemongTrunk`` can be
+differentiated with respect to tokens, recurrent state, bullet tokens and parameters.  The
+single-sublayer operators are forward-only and their module methods refuse inputs that require grad.
 """
 
 from __future__ import annotations
@@ -164,6 +166,109 @@ def trunk_forward(
 def _trunk_forward_fake(x, alive, hidden, done, reset_env, bullets, bullet_mask, weights, offsets, geom):
     out_dtype = torch.bfloat16 if x.dtype == torch.bfloat16 else torch.float32
     return (x.new_empty(x.shape, dtype=out_dtype), hidden.new_empty(hidden.shape, dtype=torch.float32))
+
+
+def _sublayer_lists(weights: List[Tensor], n_blocks: int, n_spatial: int, n_temporal: int, n_cross: int, field_sub: int):
+    """``weights`` cut into the per-sublayer lists, block-major, spatial before temporal."""
+    spatial, temporal, pos = [], [], 0
+    for _ in range(n_blocks):
+        for j in range(n_spatial):
+            n = N_SPATIAL + (2 if j < n_cross else 0)
+            spatial.append(list(weights[pos : pos + n]))
+            pos += n
+        for _j in range(n_temporal):
+            n = N_TEMPORAL + (1 if field_sub else 0)
+            temporal.append(list(weights[pos : pos + n]))
+            pos += n
+    if pos != len(weights):
+        raise RuntimeError(f"expected {pos} parameter tensors for this trunk structure, got {len(weights)}")
+    return spatial, temporal
+
+
+@torch.library.custom_op("bnb_b200::trunk_backward", mutates_args=(), device_types="cuda")
+def trunk_backward(
+    dy: Tensor,
+    dhidden_out: Optional[Tensor],
+    x: Tensor,
+    alive: Optional[Tensor],
+    hidden: Tensor,
+    done: Optional[Tensor],
+    bullets: Optional[Tensor],
+    bullet_mask: Optional[Tensor],
+    weights: List[Tensor],
+    geom: List[int],
+) -> List[Tensor]:
+    """Gradients of ``trunk_forward`` (environments of one size, no ``reset_env``) through
+    ``bnb_trunk_sequence_bwd``: float32 arithmetic whatever the forward's precision was.  Returns
+    [d x, d hidden, d bullets (empty without bullets), then one gradient per tensor of ``weights``]."""
+    dev = x.device
+    D = x.shape[-1]
+    n_blocks, n_spatial, n_temporal = geom[G_BLOCKS], geom[G_SPATIAL], geom[G_TEMPORAL]
+    n_heads, n_cross, field_sub = geom[G_HEADS], geom[G_BULLET_CROSS], geom[G_FIELD_SUB]
+    T = max(1, geom[G_TIMESTEPS])
+    with torch.cuda.device(dev):
+        batch = _batch(geom, [])
+        xin, hin, dyin = _capi.f32c(x), _capi.f32c(hidden), _capi.f32c(dy)
+        dho = None if dhidden_out is None else _capi.f32c(dhidden_out)
+        alive_u8, done_u8 = _capi.u8(alive), _capi.u8(done)
+        spatial, temporal = _sublayer_lists(weights, n_blocks, n_spatial, n_temporal, n_cross, field_sub)
+        grads = [torch.zeros_like(w, dtype=torch.float32) for w in weights]
+        g_spatial, g_temporal = _sublayer_lists(grads, n_blocks, n_spatial, n_temporal, n_cross, field_sub)
+        sw = (_capi.SpatialWeights * max(1, len(spatial)))()
+        tw = (_capi.TemporalWeights * max(1, len(temporal)))()
+        sg = (_capi.SpatialGrads * max(1, len(spatial)))()
+        tg = (_capi.TemporalGrads * max(1, len(temporal)))()
+        for i, (ts, gs) in enumerate(zip(spatial, g_spatial)):
+            sw[i] = spatial_struct_from(ts, dev)
+            sg[i] = _capi.SpatialGrads(*[g.data_ptr() for g in gs], *([None] * (N_SPATIAL + 2 - len(gs))))
+        for i, (ts, gs) in enumerate(zip(temporal, g_temporal)):
+            tw[i] = temporal_struct_from(ts, dev)
+            tg[i] = _capi.TemporalGrads(*[g.data_ptr() for g in gs], *([None] * (N_TEMPORAL + 1 - len(gs))))
+        bul = _capi.BulletArgs(bullets if n_cross > 0 else None, bullet_mask, T * batch.n_envs, D)
+        dx = torch.empty_like(xin)
+        dh = torch.zeros_like(hin)
+        dbul = torch.empty_like(bul.tokens) if bul.struct is not None else xin.new_empty(0)
+        nbytes = _capi.lib.bnb_trunk_bwd_scratch_bytes(n_blocks, n_spatial, n_temporal, D, batch, T, bul.per_env)
+        scratch = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=dev)   # released after the call's stream work
+        st = _capi.lib.bnb_trunk_sequence_bwd(
+            sw, tw, sg, tg, n_blocks, n_spatial, n_temporal, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8), bul.arg,
+            _capi.ptr(hin), _capi.ptr(done_u8), batch, T, dyin.data_ptr(), _capi.ptr(dho), dx.data_ptr(),
+            _capi.ptr(dh), _capi.ptr(dbul) if bul.struct is not None else None, scratch.data_ptr(), scratch.numel(),
+            _capi.stream_handle(dev),
+        )
+    _capi.check("bnb_trunk_sequence_bwd", st)
+    return [dx, dh, dbul, *grads]
+
+
+@trunk_backward.register_fake
+def _trunk_backward_fake(dy, dhidden_out, x, alive, hidden, done, bullets, bullet_mask, weights, geom):
+    dbul = x.new_empty(bullets.shape, dtype=torch.float32) if bullets is not None and geom[G_BULLET_CROSS] > 0 else x.new_empty(0, dtype=torch.float32)
+    return [x.new_empty(x.shape, dtype=torch.float32), hidden.new_empty(hidden.shape, dtype=torch.float32), dbul,
+            *[w.new_empty(w.shape, dtype=torch.float32) for w in weights]]
+
+
+def _trunk_setup_context(ctx, inputs, output):
+    x, alive, hidden, done, reset_env, bullets, bullet_mask, weights, offsets, geom = inputs
+    ctx.geom = list(geom)
+    ctx.unsupported = ("a ragged batch" if offsets else "reset_env" if reset_env is not None else "")
+    ctx.n_offsets = len(offsets)
+    ctx.save_for_backward(x, alive, hidden, done, bullets, bullet_mask, *weights)
+
+
+def _trunk_backward_formula(ctx, dy, dhidden_out):
+    if ctx.unsupported:
+        raise NotImplementedError(f"the CUDA trunk's backward does not cover {ctx.unsupported}; run that call under torch.no_grad()")
+    x, alive, hidden, done, bullets, bullet_mask, *weights = ctx.saved_tensors
+    out = trunk_backward(dy, dhidden_out, x, alive, hidden, done, bullets, bullet_mask, list(weights), ctx.geom)
+    dx, dh, dbul, dws = out[0], out[1], out[2], out[3:]
+    dx = dx.reshape(x.shape).to(x.dtype)
+    dh = dh.reshape(hidden.shape).to(hidden.dtype)
+    dbul = dbul.reshape(bullets.shape).to(bullets.dtype) if bullets is not None and dbul.numel() else None
+    # one entry per input; a list input takes a list of the same length
+    return dx, None, dh, None, None, dbul, None, [g.to(w.dtype) for g, w in zip(dws, weights)], [None] * ctx.n_offsets, None
+
+
+trunk_forward.register_autograd(_trunk_backward_formula, setup_context=_trunk_setup_context)
 
 
 @torch.library.custom_op("bnb_b200::spatial_forward", mutates_args=(), device_types="cuda")

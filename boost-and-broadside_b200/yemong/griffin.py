@@ -21,7 +21,8 @@ CONV_KERNEL: int = 4  # causal depthwise conv kernel size (griffin.py:22)
 
 def _no_grad_inputs(*tensors) -> None:
     if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors):
-        raise NotImplementedError("the CUDA trunk is forward-only; call it under torch.no_grad()")
+        raise NotImplementedError("this method is forward-only (gradients flow through YemongBlock / YemongTrunk "
+                                  "step and sequence); call it under torch.no_grad()")
 
 
 class RGLRU(nn.Module):
@@ -259,7 +260,6 @@ class YemongBlock(nn.Module):
     ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         """Single-step forward (griffin.py:376-417): returns (x, new_h, new_conv_buf)."""
         _capi.require_cuda(x, "x")
-        _no_grad_inputs(x, h, conv_buf)
         B, NM, D = x.shape
         n_rec = NM if num_recurrent is None else num_recurrent
         batch = _ops.uniform_geom(B, NM, n_rec)
@@ -284,7 +284,6 @@ class YemongBlock(nn.Module):
     ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         """Full-sequence forward (griffin.py:419-472): returns (x, final h, final conv_buf)."""
         _capi.require_cuda(x, "x")
-        _no_grad_inputs(x, h0, conv_buf0)
         T, B, NM, D = x.shape
         n_rec = NM if num_recurrent is None else num_recurrent
         batch = _ops.uniform_geom(B, NM, n_rec)

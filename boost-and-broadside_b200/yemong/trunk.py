@@ -110,8 +110,6 @@ class YemongTrunk(nn.Module):
             raise RuntimeError(
                 f"hidden must be ({self.n_hidden_layers}, B*N, {CONV_KERNEL * self.d_model}), got {tuple(hidden.shape)}"
             )
-        if torch.is_grad_enabled() and (x.requires_grad or hidden.requires_grad):
-            raise NotImplementedError("the CUDA trunk is forward-only; call it under torch.no_grad()")
 
     @staticmethod
     def _check_mask(mask: torch.Tensor | None, shape: tuple, what: str) -> None:

@@ -336,6 +336,50 @@ int bnb_encoder_mlp_fwd(const float* w1, const float* b1, const float* g1, const
                         const float* b2, const float* g2, int in_dim, int in_pad, int hidden,
                         int out_dim, const float* x, void* y, int n_rows, int precision, void* stream);
 
+/* Gradient buffers of one sublayer: the fields of BnbSpatialWeights / BnbTemporalWeights, same
+ * shapes, float32, written by accumulation (+=), so the caller zeroes them or hands in running
+ * sums.  The bullet fields may be NULL for a sublayer that does not read bullets, field_sub_w when
+ * the batch has no field tokens. */
+typedef struct {
+  float* norm1_w; float* qkv_w; float* out_w; float* norm2_w; float* gate_w; float* up_w; float* down_w;
+  float* norm_bullet_w; float* kv_bullet_w;
+} BnbSpatialGrads;
+
+typedef struct {
+  float* norm1_w; float* linear1_w; float* conv_w; float* conv_b; float* log_lambda; float* a_w; float* a_b;
+  float* x_w; float* x_b; float* linear2_w; float* out_w; float* norm2_w; float* gate_w; float* up_w;
+  float* down_w; float* field_sub_w;
+} BnbTemporalGrads;
+
+/* Scratch bytes of bnb_trunk_sequence_bwd for this structure and batch. */
+size_t bnb_trunk_bwd_scratch_bytes(int n_blocks, int n_spatial, int n_temporal, int d_model,
+                                   const BnbBatch* batch, int timesteps, int bullets_per_env);
+
+/* Backward of bnb_trunk_sequence (and, with timesteps = 1 and no done, of bnb_trunk_step without
+ * reset_env), float32.
+ * Replaces: what loss.backward() runs through the trunk loop of YemongPolicy.evaluate_actions,
+ * models/yemong/policy.py:422-478 (reached from train/rl/ppo.py:1974), with or without
+ * grad_checkpoint (policy.py:451-467; this entry always recomputes).
+ *   x, alive, bullets, hidden_in, done, batch, timesteps: the forward call's arguments (environments
+ *   of one size only: batch->tok_off must be NULL).
+ *   dy (T, total_tokens, D): gradient of the loss with respect to the forward's y.
+ *   d_hidden_out (L, total_ships, 4D) or NULL (= zero): gradient with respect to the final state.
+ *   dx (T, total_tokens, D): written.  d_hidden_in (L, total_ships, 4D) or NULL: written.
+ *   d_bullets (T * n_envs, NB, D) or NULL: written (zeroed here, then accumulated over the sublayers
+ *   that read bullets).
+ *   d_spatial / d_temporal: one entry per sublayer, indexed like spatial / temporal; accumulated into.
+ * The attention gradient follows the fused attention kernels behind F.scaled_dot_product_attention
+ * (probabilities recomputed from the float32 log-sum-exp); d_model a multiple of 32 up to 128,
+ * head width 8, 16 or 32.  Weight gradients reduce with float32 atomics: run-to-run bits may differ
+ * in the last places. */
+int bnb_trunk_sequence_bwd(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal,
+                           const BnbSpatialGrads* d_spatial, const BnbTemporalGrads* d_temporal,
+                           int n_blocks, int n_spatial, int n_temporal, int d_model, int n_heads,
+                           const float* x, const uint8_t* alive, const BnbBullets* bullets,
+                           const float* hidden_in, const uint8_t* done, const BnbBatch* batch, int timesteps,
+                           const float* dy, const float* d_hidden_out, float* dx, float* d_hidden_in,
+                           float* d_bullets, void* scratch, size_t scratch_bytes, void* stream);
+
 /* One head of the policy: Linear + b -> RMSNorm -> GELU(erf) -> Linear + b on the trunk's output.
  * Replaces: YemongPolicy.action_head, .value_head_local, .value_head_win and NextStateHead.net,
  * models/yemong/policy.py:56-72, 185-214 (all four have this shape).

@@ -526,23 +526,14 @@ def test_bullets_at_unseen_fleet_sizes(mode, ships, fields, nb):
     assert_close(nh, ref_h, mode, "hidden")
 
 
-def test_backward_through_the_operators_is_refused_loudly():
-    """Forward-only: with grad mode on and parameters that require grad, the operators carry no
-    autograd formula, so a backward through their outputs raises instead of silently skipping
-    the trunk's parameters; inputs that require grad are refused at the call."""
-    from boost_and_broadside_b200 import ModelConfig, YemongTrunk
+def test_single_sublayer_methods_refuse_inputs_that_require_grad():
+    """Gradients flow through YemongBlock / YemongTrunk step and sequence (tests/test_gpu_gradients.py);
+    the single-sublayer methods are forward-only and say so instead of dropping the gradient."""
+    from boost_and_broadside_b200 import ModelConfig, TransformerBlock
 
-    trunk = YemongTrunk(ModelConfig(128, 4, 1, 1, 1)).to(DEV)
-    x = torch.randn(2, 3, 128, device=DEV)
-    hidden = torch.zeros(1, 6, 512, device=DEV)
+    block = TransformerBlock(ModelConfig(128, 4, 1, 1, 1)).to(DEV)
     with pytest.raises(NotImplementedError):
-        trunk.step(x.clone().requires_grad_(True), None, hidden)
-    y, _ = trunk.step(x, None, hidden)          # grad mode on, parameters require grad
-    if y.requires_grad:
-        with pytest.raises(RuntimeError):
-            y.sum().backward()
-    else:
-        assert all(p.grad is None for p in trunk.parameters())
+        block(torch.randn(2, 3, 128, device=DEV, requires_grad=True))
 
 
 @pytest.mark.parametrize("mode", MODES)
