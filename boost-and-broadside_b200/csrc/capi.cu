@@ -304,12 +304,13 @@ int bnb_trunk_sequence_bwd(const BnbSpatialWeights* spatial, const BnbTemporalWe
                            const BnbSpatialGrads* d_spatial, const BnbTemporalGrads* d_temporal, int n_blocks,
                            int n_spatial, int n_temporal, int d_model, int n_heads, const float* x, const uint8_t* alive,
                            const BnbBullets* bullets, const float* hidden_in, const uint8_t* done, const BnbBatch* batch,
-                           int timesteps, const float* dy, const float* d_hidden_out, float* dx, float* d_hidden_in,
-                           float* d_bullets, void* scratch, size_t scratch_bytes, void* stream) {
+                           int timesteps, int precision, const float* dy, const float* d_hidden_out, float* dx,
+                           float* d_hidden_in, float* d_bullets, void* scratch, size_t scratch_bytes, void* stream) {
   int st = check_dims(d_model, n_heads);
   if (st) return st;
   if ((st = check_batch(batch))) return st;
   if (batch->tok_off) return BNB_ERR_UNSUPPORTED_DIMS;
+  if (precision != BNB_FP32 && precision != BNB_BF16) return BNB_ERR_BAD_ARGUMENT;
   if (n_blocks < 0 || n_spatial < 0 || n_temporal < 0 || timesteps < 1) return BNB_ERR_BAD_ARGUMENT;
   if ((size_t)timesteps * batch->total_tokens == 0) return BNB_OK;
   const int ns = n_blocks * n_spatial, nt = n_blocks * n_temporal;
@@ -350,7 +351,7 @@ int bnb_trunk_sequence_bwd(const BnbSpatialWeights* spatial, const BnbTemporalWe
     if (!aligned16(bullets->tokens)) return BNB_ERR_MISALIGNED;
   }
   bnb::grad::TrunkBwdArgs a{spatial, temporal, d_spatial, d_temporal, n_blocks, n_spatial, n_temporal, d_model, n_heads,
-                            x, alive, bullets, hidden_in, done, batch, timesteps, dy, d_hidden_out, dx, d_hidden_in,
+                            x, alive, bullets, hidden_in, done, batch, timesteps, precision == BNB_BF16, dy, d_hidden_out, dx, d_hidden_in,
                             d_bullets, scratch, scratch_bytes, static_cast<cudaStream_t>(stream)};
   return bnb::grad::trunk_sequence_bwd(a);
 }

@@ -10,11 +10,12 @@
 //   causal conv + tap validity      models/yemong/griffin.py:67-140
 //
 // Scheme: recompute, as the reference does with grad_checkpoint (policy.py:451-467).  A first pass
-// runs the forward sublayer by sublayer (the exact-arithmetic kernels) and keeps only the input of
-// every sublayer.  The sublayers are then walked in reverse; each recomputes its own intermediates
+// runs the forward sublayer by sublayer and keeps only the input of every sublayer.  The sublayers are then walked in reverse; each recomputes its own intermediates
 // into scratch (norms, projections, attention output, gates, recurrent states) and differentiates
 // them.  Linear products -- y = x W^T, dx = dy W, dW += dy^T x -- all run on one tensor-core GEMM
-// kernel (3 x tf32 m16n8k8 MMAs per product, float32 accumulation: float32-level accuracy); the
+// kernel (3 x tf32 m16n8k8 MMAs per product, float32 accumulation: float32-level accuracy; or, for
+// a forward that ran under bf16 autocast, one bf16 m16n8k16 MMA with operands rounded on the way
+// in, as autocast does to the reference's backward products); the
 // weight gradients reduce over all rows with a split over the row dimension and float32 atomics,
 // so the caller hands in zeroed (or to-be-accumulated-into) gradient buffers.
 //
@@ -25,7 +26,6 @@
 #include "grad_kernels.h"
 
 #include "common.cuh"
-#include "exact_kernels.h"
 #include "launch_count.h"
 
 namespace bnb {
@@ -36,8 +36,11 @@ namespace {
 // ------------------------------------------------------------------------------ GEMM
 
 constexpr int BM = 128, BN = 128, BK = 32, GT = 256;
-constexpr int LDK = BK + 4;    // row stride of a [row][k] tile: fragment reads hit 32 banks
-constexpr int LDR = 128 + 8;   // row stride of a [k][row] tile: likewise
+// Row strides of the shared tiles, chosen so that the fragment reads of a warp hit 32 different
+// banks: [row][k] tiles 36 floats (tf32: 32-bit reads) or 40 (bf16: 64-bit reads of two adjacent
+// k), [k][row] tiles 136 or 132.
+template <bool BF16> struct Strides { static constexpr int LDK = BF16 ? BK + 8 : BK + 4, LDR = BF16 ? 128 + 4 : 128 + 8; };
+constexpr int TILE_FLOATS = BM * (BK + 8);
 
 struct GemmArgs {
   const float* A; int lda;
@@ -65,16 +68,30 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], 
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// two floats -> one register of two bf16, the first in the low half
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
 
 // C(m, n) = sum_k A(m, k) B(n, k) [+ bias(n)] [+ R(m, n)] [+ C(m, n)].
 // A_KC: A(m, k) = A[m * lda + k], else A[k * lda + m].  B_KC: B(n, k) = B[n * ldb + k], else B[k * ldb + n].
 // The contiguous dimension of each operand is a multiple of 4 floats and its base 16-byte aligned.
-// 128 x 128 tile per CTA, 8 warps of 64 x 32, float32 operands split into two tf32 numbers each.
-template <bool A_KC, bool B_KC>
+// 128 x 128 tile per CTA, 8 warps of 64 x 32.  BF16 unset: every float32 operand is split into two
+// tf32 numbers and three m16n8k8 MMAs give the float32 product.  BF16 set: operands are rounded to
+// bfloat16 on the way into the m16n8k16 MMA (what autocast does to the reference's backward
+// products), accumulation in float32 either way.
+template <bool A_KC, bool B_KC, bool BF16>
 __global__ void __launch_bounds__(GT) k_gemm(GemmArgs g) {
-  __shared__ __align__(16) float As[BM * LDK];
-  __shared__ __align__(16) float Bs[BN * LDK];
-  static_assert(BM * LDK >= BK * LDR, "either orientation fits the tile buffer");
+  constexpr int LDK = Strides<BF16>::LDK, LDR = Strides<BF16>::LDR;
+  __shared__ __align__(16) float As[TILE_FLOATS];
+  __shared__ __align__(16) float Bs[TILE_FLOATS];
+  static_assert(TILE_FLOATS >= BM * LDK && TILE_FLOATS >= BK * LDR, "either orientation fits the tile buffer");
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, t = lane & 3;
   const int wm = (warp & 1) * 64, wn = (warp >> 1) * 32;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -122,46 +139,88 @@ __global__ void __launch_bounds__(GT) k_gemm(GemmArgs g) {
       }
     }
     __syncthreads();
+    if constexpr (BF16) {
 #pragma unroll
-    for (int kk = 0; kk < BK; kk += 8) {
-      uint32_t ah[4][4], al[4][4];
-#pragma unroll
-      for (int mt = 0; mt < 4; ++mt) {
-        const int r0 = wm + mt * 16 + gq;
-        float af[4];
-        if constexpr (A_KC) {
-          af[0] = As[r0 * LDK + kk + t];
-          af[1] = As[(r0 + 8) * LDK + kk + t];
-          af[2] = As[r0 * LDK + kk + t + 4];
-          af[3] = As[(r0 + 8) * LDK + kk + t + 4];
-        } else {
-          af[0] = As[(kk + t) * LDR + r0];
-          af[1] = As[(kk + t) * LDR + r0 + 8];
-          af[2] = As[(kk + t + 4) * LDR + r0];
-          af[3] = As[(kk + t + 4) * LDR + r0 + 8];
-        }
-#pragma unroll
-        for (int e = 0; e < 4; ++e) split_tf32(af[e], ah[mt][e], al[mt][e]);
-      }
-#pragma unroll
-      for (int nt = 0; nt < 4; ++nt) {
-        const int nn = wn + nt * 8 + gq;
-        float b0, b1;
-        if constexpr (B_KC) {
-          b0 = Bs[nn * LDK + kk + t];
-          b1 = Bs[nn * LDK + kk + t + 4];
-        } else {
-          b0 = Bs[(kk + t) * LDR + nn];
-          b1 = Bs[(kk + t + 4) * LDR + nn];
-        }
-        uint32_t bh0, bl0, bh1, bl1;
-        split_tf32(b0, bh0, bl0);
-        split_tf32(b1, bh1, bl1);
+      for (int kk = 0; kk < BK; kk += 16) {
+        uint32_t a[4][4];
 #pragma unroll
         for (int mt = 0; mt < 4; ++mt) {
-          mma_tf32(c[mt][nt], al[mt], bh0, bh1);
-          mma_tf32(c[mt][nt], ah[mt], bl0, bl1);
-          mma_tf32(c[mt][nt], ah[mt], bh0, bh1);
+          const int r0 = wm + mt * 16 + gq, kq = kk + 2 * t;
+          if constexpr (A_KC) {
+            const float2 v0 = *reinterpret_cast<const float2*>(As + r0 * LDK + kq);
+            const float2 v1 = *reinterpret_cast<const float2*>(As + (r0 + 8) * LDK + kq);
+            const float2 v2 = *reinterpret_cast<const float2*>(As + r0 * LDK + kq + 8);
+            const float2 v3 = *reinterpret_cast<const float2*>(As + (r0 + 8) * LDK + kq + 8);
+            a[mt][0] = pack_bf16(v0.x, v0.y);
+            a[mt][1] = pack_bf16(v1.x, v1.y);
+            a[mt][2] = pack_bf16(v2.x, v2.y);
+            a[mt][3] = pack_bf16(v3.x, v3.y);
+          } else {
+            a[mt][0] = pack_bf16(As[kq * LDR + r0], As[(kq + 1) * LDR + r0]);
+            a[mt][1] = pack_bf16(As[kq * LDR + r0 + 8], As[(kq + 1) * LDR + r0 + 8]);
+            a[mt][2] = pack_bf16(As[(kq + 8) * LDR + r0], As[(kq + 9) * LDR + r0]);
+            a[mt][3] = pack_bf16(As[(kq + 8) * LDR + r0 + 8], As[(kq + 9) * LDR + r0 + 8]);
+          }
+        }
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+          const int nn = wn + nt * 8 + gq, kq = kk + 2 * t;
+          uint32_t b0, b1;
+          if constexpr (B_KC) {
+            const float2 v0 = *reinterpret_cast<const float2*>(Bs + nn * LDK + kq);
+            const float2 v1 = *reinterpret_cast<const float2*>(Bs + nn * LDK + kq + 8);
+            b0 = pack_bf16(v0.x, v0.y);
+            b1 = pack_bf16(v1.x, v1.y);
+          } else {
+            b0 = pack_bf16(Bs[kq * LDR + nn], Bs[(kq + 1) * LDR + nn]);
+            b1 = pack_bf16(Bs[(kq + 8) * LDR + nn], Bs[(kq + 9) * LDR + nn]);
+          }
+#pragma unroll
+          for (int mt = 0; mt < 4; ++mt) mma_bf16(c[mt][nt], a[mt], b0, b1);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int kk = 0; kk < BK; kk += 8) {
+        uint32_t ah[4][4], al[4][4];
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) {
+          const int r0 = wm + mt * 16 + gq;
+          float af[4];
+          if constexpr (A_KC) {
+            af[0] = As[r0 * LDK + kk + t];
+            af[1] = As[(r0 + 8) * LDK + kk + t];
+            af[2] = As[r0 * LDK + kk + t + 4];
+            af[3] = As[(r0 + 8) * LDK + kk + t + 4];
+          } else {
+            af[0] = As[(kk + t) * LDR + r0];
+            af[1] = As[(kk + t) * LDR + r0 + 8];
+            af[2] = As[(kk + t + 4) * LDR + r0];
+            af[3] = As[(kk + t + 4) * LDR + r0 + 8];
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) split_tf32(af[e], ah[mt][e], al[mt][e]);
+        }
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+          const int nn = wn + nt * 8 + gq;
+          float b0, b1;
+          if constexpr (B_KC) {
+            b0 = Bs[nn * LDK + kk + t];
+            b1 = Bs[nn * LDK + kk + t + 4];
+          } else {
+            b0 = Bs[(kk + t) * LDR + nn];
+            b1 = Bs[(kk + t + 4) * LDR + nn];
+          }
+          uint32_t bh0, bl0, bh1, bl1;
+          split_tf32(b0, bh0, bl0);
+          split_tf32(b1, bh1, bl1);
+#pragma unroll
+          for (int mt = 0; mt < 4; ++mt) {
+            mma_tf32(c[mt][nt], al[mt], bh0, bh1);
+            mma_tf32(c[mt][nt], ah[mt], bl0, bl1);
+            mma_tf32(c[mt][nt], ah[mt], bh0, bh1);
+          }
         }
       }
     }
@@ -196,8 +255,15 @@ enum GemmMode { NT, NN, TN };
 // NT: C (M, N)  = A (M, K) . B (N, K)^T      y = x W^T
 // NN: C (M, N)  = A (M, K) . B (K, N)        dx = dy W
 // TN: C (M, N) += A (K, M)^T . B (K, N)      dW += dy^T x   (split over K, atomics)
+template <bool BF16>
+void launch_gemm(GemmMode mode, const GemmArgs& g, dim3 grid, cudaStream_t st) {
+  if (mode == TN) k_gemm<false, false, BF16><<<grid, GT, 0, st>>>(g);
+  else if (mode == NT) k_gemm<true, true, BF16><<<grid, GT, 0, st>>>(g);
+  else k_gemm<true, false, BF16><<<grid, GT, 0, st>>>(g);
+}
+
 void gemm(GemmMode mode, const float* A, int lda, const float* B, int ldb, float* C, int ldc, int M, int N, int K,
-          const float* bias, const float* R, int ldr, int beta, cudaStream_t st) {
+          const float* bias, const float* R, int ldr, int beta, cudaStream_t st, bool bf16) {
   if (M <= 0 || N <= 0 || K <= 0) return;
   GemmArgs g{A, lda, B, ldb, C, ldc, M, N, K, bias, R, ldr, beta, K, 0};
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, 1);
@@ -213,12 +279,9 @@ void gemm(GemmMode mode, const float* A, int lda, const float* B, int ldb, float
     grid.z = (K + per - 1) / per;
     g.k_per_split = per;
     g.atomic = 1;
-    k_gemm<false, false><<<grid, GT, 0, st>>>(g);
-  } else if (mode == NT) {
-    k_gemm<true, true><<<grid, GT, 0, st>>>(g);
-  } else {
-    k_gemm<true, false><<<grid, GT, 0, st>>>(g);
   }
+  if (bf16) launch_gemm<true>(mode, g, grid, st);
+  else launch_gemm<false>(mode, g, grid, st);
 }
 
 // ------------------------------------------------------------------------------ row-wise pieces
@@ -311,18 +374,21 @@ __device__ __forceinline__ float gelu_grad(float v) {
   return cdf + v * 0.39894228040143267794f * expf(-0.5f * v * v);
 }
 
-// h = gelu(g) * u
-__global__ void k_gelu_mul_fwd(const float* __restrict__ g, const float* __restrict__ u, float* __restrict__ h, size_t n) {
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
-    h[i] = gelu_erf(g[i]) * u[i];
+// h = gelu(g) * u, four elements per thread
+__global__ void k_gelu_mul_fwd(const float4* __restrict__ g, const float4* __restrict__ u, float4* __restrict__ h, size_t n4) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+    const float4 a = g[i], b = u[i];
+    h[i] = make_float4(gelu_erf(a.x) * b.x, gelu_erf(a.y) * b.y, gelu_erf(a.z) * b.z, gelu_erf(a.w) * b.w);
+  }
 }
 
 // dg = dh * u * gelu'(g), du = dh * gelu(g).  dg may alias g, du may alias dh (or u).
-__global__ void k_gelu_mul_bwd(const float* g, const float* u, const float* dh, float* dg, float* du, size_t n) {
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-    const float gv = g[i], uv = u[i], d = dh[i];
-    dg[i] = d * uv * gelu_grad(gv);
-    du[i] = d * gelu_erf(gv);
+__global__ void k_gelu_mul_bwd(const float4* g, const float4* u, const float4* dh, float4* dg, float4* du, size_t n4) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+    const float4 a = g[i], b = u[i], d = dh[i];
+    dg[i] = make_float4(d.x * b.x * gelu_grad(a.x), d.y * b.y * gelu_grad(a.y), d.z * b.z * gelu_grad(a.z),
+                        d.w * b.w * gelu_grad(a.w));
+    du[i] = make_float4(d.x * gelu_erf(a.x), d.y * gelu_erf(a.y), d.z * gelu_erf(a.z), d.w * gelu_erf(a.w));
   }
 }
 
@@ -773,9 +839,15 @@ inline int blocks_for(size_t n, int per_block, int cap = 148 * 8) {
 
 struct Ctx {
   int D, H;
+  bool bf16;   // products round their operands to bfloat16 (the forward ran under autocast)
   cudaStream_t st;
   Bufs b;
 };
+
+void mm(const Ctx& c, GemmMode mode, const float* A, int lda, const float* B, int ldb, float* C, int ldc, int M, int N, int K,
+        const float* bias = nullptr, const float* R = nullptr, int ldr = 0, int beta = 0) {
+  gemm(mode, A, lda, B, ldb, C, ldc, M, N, K, bias, R, ldr, beta, c.st, c.bf16);
+}
 
 void rmsnorm_fwd(const Ctx& c, const float* x, const float* g, float* n, float* inv, size_t rows) {
   if (!rows) return;
@@ -791,12 +863,15 @@ void rmsnorm_bwd(const Ctx& c, const float* x, const float* g, const float* inv,
 void gelu_mul_fwd(const Ctx& c, const float* g, const float* u, float* h, size_t n) {
   if (!n) return;
   count_launch();
-  k_gelu_mul_fwd<<<blocks_for(n, 1024), 256, 0, c.st>>>(g, u, h, n);
+  k_gelu_mul_fwd<<<blocks_for(n / 4, 256), 256, 0, c.st>>>(reinterpret_cast<const float4*>(g), reinterpret_cast<const float4*>(u),
+                                                           reinterpret_cast<float4*>(h), n / 4);
 }
 void gelu_mul_bwd(const Ctx& c, const float* g, const float* u, const float* dh, float* dg, float* du, size_t n) {
   if (!n) return;
   count_launch();
-  k_gelu_mul_bwd<<<blocks_for(n, 1024), 256, 0, c.st>>>(g, u, dh, dg, du, n);
+  k_gelu_mul_bwd<<<blocks_for(n / 4, 256), 256, 0, c.st>>>(reinterpret_cast<const float4*>(g), reinterpret_cast<const float4*>(u),
+                                                           reinterpret_cast<const float4*>(dh), reinterpret_cast<float4*>(dg),
+                                                           reinterpret_cast<float4*>(du), n / 4);
 }
 void colsum(const Ctx& c, const float* a, float* out, size_t rows, int N) {
   if (!rows) return;
@@ -805,28 +880,32 @@ void colsum(const Ctx& c, const float* a, float* out, size_t rows, int N) {
   k_colsum<<<grid, 256, 0, c.st>>>(a, out, (int)rows, N);
 }
 
-// Gated MLP at the end of every sublayer: given x1 and d y (y = x1 + down(gelu(gate n) * up n),
-// n = rmsnorm(x1)), accumulates the weight gradients and writes d x1 to dx1.
-// Uses w4[0..2], inv[1], d[15], d[16].
+// Gated MLP at the end of every sublayer, y = x1 + down(gelu(gate n) * up n), n = rmsnorm(x1).
+// Leaves n in d[15], the reciprocal roots in inv[1], gate / up / their gated product in w4[0..2];
+// writes y when y is given.
+void mlp_fwd(const Ctx& c, const float* x1, float* y, size_t rows, const float* g2, const float* Wg, const float* Wu,
+             const float* Wd) {
+  const int D = c.D, F = 4 * c.D, M = (int)rows;
+  float *n2 = c.b.d[15], *gb = c.b.w4[0], *ub = c.b.w4[1], *hb = c.b.w4[2];
+  rmsnorm_fwd(c, x1, g2, n2, c.b.inv[1], rows);
+  mm(c, NT, n2, D, Wg, D, gb, F, M, F, D);
+  mm(c, NT, n2, D, Wu, D, ub, F, M, F, D);
+  gelu_mul_fwd(c, gb, ub, hb, rows * F);
+  if (y) mm(c, NT, hb, F, Wd, F, y, D, M, D, F, nullptr, x1, D);
+}
+
+// After mlp_fwd: given d y, accumulates the weight gradients and writes d x1.  Uses d[16].
 void mlp_bwd(const Ctx& c, const float* x1, const float* dy, float* dx1, size_t rows, const float* g2, const float* Wg,
              const float* Wu, const float* Wd, float* dg2, float* dWg, float* dWu, float* dWd) {
   const int D = c.D, F = 4 * c.D, M = (int)rows;
-  float* n2 = c.b.d[15];
-  float* dn2 = c.b.d[16];
-  float* gb = c.b.w4[0];
-  float* ub = c.b.w4[1];
-  float* hb = c.b.w4[2];
-  rmsnorm_fwd(c, x1, g2, n2, c.b.inv[1], rows);
-  gemm(NT, n2, D, Wg, D, gb, F, M, F, D, nullptr, nullptr, 0, 0, c.st);
-  gemm(NT, n2, D, Wu, D, ub, F, M, F, D, nullptr, nullptr, 0, 0, c.st);
-  gelu_mul_fwd(c, gb, ub, hb, rows * F);
-  gemm(TN, dy, D, hb, F, dWd, F, D, F, M, nullptr, nullptr, 0, 0, c.st);        // dWd (D, 4D) += dy^T h
-  gemm(NN, dy, D, Wd, F, hb, F, M, F, D, nullptr, nullptr, 0, 0, c.st);         // dh = dy Wd
-  gelu_mul_bwd(c, gb, ub, hb, gb, ub, rows * F);                                // gb <- d gate, ub <- d up
-  gemm(TN, gb, F, n2, D, dWg, D, F, D, M, nullptr, nullptr, 0, 0, c.st);
-  gemm(TN, ub, F, n2, D, dWu, D, F, D, M, nullptr, nullptr, 0, 0, c.st);
-  gemm(NN, gb, F, Wg, D, dn2, D, M, D, F, nullptr, nullptr, 0, 0, c.st);
-  gemm(NN, ub, F, Wu, D, dn2, D, M, D, F, nullptr, nullptr, 0, 1, c.st);
+  float *n2 = c.b.d[15], *dn2 = c.b.d[16], *gb = c.b.w4[0], *ub = c.b.w4[1], *hb = c.b.w4[2];
+  mm(c, TN, dy, D, hb, F, dWd, F, D, F, M);                 // dWd (D, 4D) += dy^T h
+  mm(c, NN, dy, D, Wd, F, hb, F, M, F, D);                  // dh = dy Wd
+  gelu_mul_bwd(c, gb, ub, hb, gb, ub, rows * F);            // gb <- d gate, ub <- d up
+  mm(c, TN, gb, F, n2, D, dWg, D, F, D, M);
+  mm(c, TN, ub, F, n2, D, dWu, D, F, D, M);
+  mm(c, NN, gb, F, Wg, D, dn2, D, M, D, F);
+  mm(c, NN, ub, F, Wu, D, dn2, D, M, D, F, nullptr, nullptr, 0, 1);
   rmsnorm_bwd(c, x1, g2, c.b.inv[1], dn2, dy, dx1, dg2, rows);
 }
 
@@ -856,6 +935,30 @@ int attn_bwd(const Ctx& c, const AttnBwdArgs& a, int G) {
   return BNB_OK;
 }
 
+// Spatial sublayer, forward part.  Leaves n1 in d[0] (roots in inv[0]), q|k|v in w3[0], the attention
+// output in d[1], x1 in d[2], the bullet norm / keys and values in bul_n / bul_inv / kvb, and what
+// mlp_fwd leaves; writes y when y is given.
+void spatial_fwd(const Ctx& c, const BnbSpatialWeights& w, const float* x, const uint8_t* alive, const BnbBullets* bul,
+                 float* y, int G, int NM) {
+  const int D = c.D;
+  const size_t R = (size_t)G * NM;
+  const int M = (int)R;
+  const Bufs& b = c.b;
+  float *n1 = b.d[0], *o = b.d[1], *x1 = b.d[2], *qkv = b.w3[0];
+  const bool reads = bul && w.kv_bullet_w;
+  const int nb = reads ? bul->per_env : 0;
+  const size_t RB = (size_t)G * nb;
+  rmsnorm_fwd(c, x, w.norm1_w, n1, b.inv[0], R);
+  mm(c, NT, n1, D, w.qkv_w, D, qkv, 3 * D, M, 3 * D, D);
+  if (reads) {
+    rmsnorm_fwd(c, bul->tokens, w.norm_bullet_w, b.bul_n, b.bul_inv, RB);
+    mm(c, NT, b.bul_n, D, w.kv_bullet_w, D, b.kvb, 2 * D, (int)RB, 2 * D, D);
+  }
+  attn_fwd(c, qkv, alive, o, G, NM, reads ? b.kvb : nullptr, reads ? bul->active : nullptr, nb);
+  mm(c, NT, o, D, w.out_w, D, x1, D, M, D, D, nullptr, x, D);            // x1 = x + o Wout^T
+  mlp_fwd(c, x1, y, R, w.norm2_w, w.gate_w, w.up_w, w.down_w);
+}
+
 int spatial_bwd(const Ctx& c, const BnbSpatialWeights& w, const BnbSpatialGrads& dw, const float* x, const uint8_t* alive,
                 const BnbBullets* bul, float* d_bullets, const float* dy, float* dx, int G, int NM) {
   const int D = c.D;
@@ -869,19 +972,11 @@ int spatial_bwd(const Ctx& c, const BnbSpatialWeights& w, const BnbSpatialGrads&
   const size_t RB = (size_t)G * nb;
   if (reads && (!dw.kv_bullet_w || !dw.norm_bullet_w)) return BNB_ERR_NULL_POINTER;
 
-  rmsnorm_fwd(c, x, w.norm1_w, n1, b.inv[0], R);
-  gemm(NT, n1, D, w.qkv_w, D, qkv, 3 * D, M, 3 * D, D, nullptr, nullptr, 0, 0, c.st);
-  if (reads) {
-    rmsnorm_fwd(c, bul->tokens, w.norm_bullet_w, b.bul_n, b.bul_inv, RB);
-    gemm(NT, b.bul_n, D, w.kv_bullet_w, D, b.kvb, 2 * D, (int)RB, 2 * D, D, nullptr, nullptr, 0, 0, c.st);
-  }
-  attn_fwd(c, qkv, alive, o, G, NM, reads ? b.kvb : nullptr, reads ? bul->active : nullptr, nb);
-  gemm(NT, o, D, w.out_w, D, x1, D, M, D, D, nullptr, x, D, 0, c.st);            // x1 = x + o Wout^T
-
+  spatial_fwd(c, w, x, alive, bul, nullptr, G, NM);
   mlp_bwd(c, x1, dy, dx1, R, w.norm2_w, w.gate_w, w.up_w, w.down_w, dw.norm2_w, dw.gate_w, dw.up_w, dw.down_w);
 
-  gemm(TN, dx1, D, o, D, dw.out_w, D, D, D, M, nullptr, nullptr, 0, 0, c.st);
-  gemm(NN, dx1, D, w.out_w, D, d_o, D, M, D, D, nullptr, nullptr, 0, 0, c.st);
+  mm(c, TN, dx1, D, o, D, dw.out_w, D, D, D, M);
+  mm(c, NN, dx1, D, w.out_w, D, d_o, D, M, D, D);
   const int dh = D / c.H;
   const float scale = 1.0f / sqrtf((float)dh);
   AttnBwdArgs self{qkv, 3 * D, qkv + D, 3 * D, D, alive, d_o, D, dqkv, 3 * D, 0, dqkv + D, 3 * D, D, NM, NM, dh, scale, 0};
@@ -892,14 +987,14 @@ int spatial_bwd(const Ctx& c, const BnbSpatialWeights& w, const BnbSpatialGrads&
                       bul->active ? 1 : 0};
     rc = attn_bwd(c, cross, G);
     if (rc) return rc;
-    gemm(TN, b.dkvb, 2 * D, b.bul_n, D, dw.kv_bullet_w, D, 2 * D, D, (int)RB, nullptr, nullptr, 0, 0, c.st);
-    gemm(NN, b.dkvb, 2 * D, w.kv_bullet_w, D, b.bul_dn, D, (int)RB, D, 2 * D, nullptr, nullptr, 0, 0, c.st);
+    mm(c, TN, b.dkvb, 2 * D, b.bul_n, D, dw.kv_bullet_w, D, 2 * D, D, (int)RB);
+    mm(c, NN, b.dkvb, 2 * D, w.kv_bullet_w, D, b.bul_dn, D, (int)RB, D, 2 * D);
     // the bullet tokens feed every sublayer that reads them: their gradient accumulates
     float* sink = d_bullets ? d_bullets : b.bul_n;   // bul_n is free once the weight gradient above is queued
     rmsnorm_bwd(c, bul->tokens, w.norm_bullet_w, b.bul_inv, b.bul_dn, d_bullets, sink, dw.norm_bullet_w, RB);
   }
-  gemm(TN, dqkv, 3 * D, n1, D, dw.qkv_w, D, 3 * D, D, M, nullptr, nullptr, 0, 0, c.st);
-  gemm(NN, dqkv, 3 * D, w.qkv_w, D, dn1, D, M, D, 3 * D, nullptr, nullptr, 0, 0, c.st);
+  mm(c, TN, dqkv, 3 * D, n1, D, dw.qkv_w, D, 3 * D, D, M);
+  mm(c, NN, dqkv, 3 * D, w.qkv_w, D, dn1, D, M, D, 3 * D);
   rmsnorm_bwd(c, x, w.norm1_w, b.inv[0], dn1, dx1, dx, dw.norm1_w, R);
   return BNB_OK;
 }
@@ -919,86 +1014,130 @@ void scatter(const Ctx& c, const float* compact, float* full, size_t rows, int p
                                                                      per_grp, NM, n0);
 }
 
-// One temporal sublayer: the recurrent path over the ship rows, the non-recurrent one over the
-// field rows (griffin.py:249-317), both sharing every parameter but field_sub.
-int temporal_bwd(const Ctx& c, const BnbTemporalWeights& w, const BnbTemporalGrads& dw, const float* x, const float* hid,
-                 const float* d_hid_out, float* d_hid_in, const uint8_t* done, const float* dy, float* dx, int T, int B,
-                 int NM, int n_rec) {
+struct TemporalGeom {
+  int T, B, NM, n_rec;
+  size_t Rs() const { return (size_t)T * B * n_rec; }
+  size_t Rf() const { return (size_t)T * B * (NM - n_rec); }
+};
+
+// Recurrent path over the ship rows, forward part (griffin.py:249-286).  Buffers: xs d[0], n d[1],
+// linear1 out d[2], conv out d[3], gate pre-activations d[4] d[5], states d[6], linear2 out d[7],
+// gated branch d[8], x1 d[9]; with y, the sublayer's output goes to d[14] and from there to y's ship rows.
+void ships_fwd(const Ctx& c, const BnbTemporalWeights& w, const float* x, const float* hid, const uint8_t* done, float* y,
+               const TemporalGeom& tg) {
   const int D = c.D;
   const Bufs& b = c.b;
-  const int G = T * B;
-  const size_t Rs = (size_t)G * n_rec, Rf = (size_t)G * (NM - n_rec);
+  const size_t Rs = tg.Rs();
+  const int M = (int)Rs, Rr = tg.B * tg.n_rec;
+  ShipGeom gm{tg.T, Rr, D, tg.n_rec, tg.B, done};
+  float *xs = b.d[0], *n = b.d[1], *b1 = b.d[2], *u = b.d[3], *za = b.d[4], *zx = b.d[5], *hs = b.d[6], *b2p = b.d[7],
+        *m = b.d[8], *x1 = b.d[9];
+  const int sblocks = (int)(((size_t)Rr * D + 255) / 256);
+  gather(c, x, xs, Rs, tg.n_rec, tg.NM, 0);
+  rmsnorm_fwd(c, xs, w.norm1_w, n, b.inv[0], Rs);
+  mm(c, NT, n, D, w.linear1_w, D, b1, D, M, D, D);
+  count_launch();
+  k_conv_fwd<<<sblocks, 256, 0, c.st>>>(b1, hid, w.conv_w, w.conv_b, u, gm);
+  mm(c, NT, u, D, w.a_w, D, za, D, M, D, D, w.a_b);
+  mm(c, NT, u, D, w.x_w, D, zx, D, M, D, D, w.x_b);
+  count_launch();
+  k_scan_fwd<<<sblocks, 256, 0, c.st>>>(za, zx, u, hid, w.log_lambda, hs, gm);
+  mm(c, NT, n, D, w.linear2_w, D, b2p, D, M, D, D);
+  gelu_mul_fwd(c, b2p, hs, m, Rs * D);                                  // m = h * gelu(linear2 n)
+  mm(c, NT, m, D, w.out_w, D, x1, D, M, D, D, nullptr, xs, D);
+  mlp_fwd(c, x1, y ? b.d[14] : nullptr, Rs, w.norm2_w, w.gate_w, w.up_w, w.down_w);
+  if (y) scatter(c, b.d[14], y, Rs, tg.n_rec, tg.NM, 0);
+}
+
+// Non-recurrent path over the field rows (griffin.py:288-317).  Buffers: xf d[0], n d[1], linear1 out
+// d[2], field_sub out d[3], linear2 out d[4], gated branch d[5], x1 d[6]; y as in ships_fwd.
+void fields_fwd(const Ctx& c, const BnbTemporalWeights& w, const float* x, float* y, const TemporalGeom& tg) {
+  const int D = c.D;
+  const Bufs& b = c.b;
+  const size_t Rf = tg.Rf();
+  const int M = (int)Rf, nf = tg.NM - tg.n_rec;
+  float *xf = b.d[0], *n = b.d[1], *c1 = b.d[2], *b1 = b.d[3], *b2p = b.d[4], *m = b.d[5], *x1 = b.d[6];
+  gather(c, x, xf, Rf, nf, tg.NM, tg.n_rec);
+  rmsnorm_fwd(c, xf, w.norm1_w, n, b.inv[0], Rf);
+  mm(c, NT, n, D, w.linear1_w, D, c1, D, M, D, D);
+  mm(c, NT, c1, D, w.field_sub_w, D, b1, D, M, D, D);
+  mm(c, NT, n, D, w.linear2_w, D, b2p, D, M, D, D);
+  gelu_mul_fwd(c, b2p, b1, m, Rf * D);
+  mm(c, NT, m, D, w.out_w, D, x1, D, M, D, D, nullptr, xf, D);
+  mlp_fwd(c, x1, y ? b.d[14] : nullptr, Rf, w.norm2_w, w.gate_w, w.up_w, w.down_w);
+  if (y) scatter(c, b.d[14], y, Rf, nf, tg.NM, tg.n_rec);
+}
+
+int temporal_fwd(const Ctx& c, const BnbTemporalWeights& w, const float* x, const float* hid, const uint8_t* done, float* y,
+                 const TemporalGeom& tg) {
+  if (tg.Rs()) ships_fwd(c, w, x, hid, done, y, tg);
+  if (tg.Rf()) {
+    if (!w.field_sub_w) return BNB_ERR_NULL_POINTER;
+    fields_fwd(c, w, x, y, tg);
+  }
+  return BNB_OK;
+}
+
+// One temporal sublayer: the recurrent path over the ship rows, the non-recurrent one over the
+// field rows, both sharing every parameter but field_sub.
+int temporal_bwd(const Ctx& c, const BnbTemporalWeights& w, const BnbTemporalGrads& dw, const float* x, const float* hid,
+                 const float* d_hid_out, float* d_hid_in, const uint8_t* done, const float* dy, float* dx,
+                 const TemporalGeom& tg) {
+  const int D = c.D;
+  const Bufs& b = c.b;
+  const size_t Rs = tg.Rs(), Rf = tg.Rf();
   if (Rs) {
-    const int M = (int)Rs, Rr = B * n_rec;
-    ShipGeom gm{T, Rr, D, n_rec, B, done};
+    const int M = (int)Rs, Rr = tg.B * tg.n_rec;
+    ShipGeom gm{tg.T, Rr, D, tg.n_rec, tg.B, done};
     float *xs = b.d[0], *n = b.d[1], *b1 = b.d[2], *u = b.d[3], *za = b.d[4], *zx = b.d[5], *hs = b.d[6], *b2p = b.d[7],
           *m = b.d[8], *x1 = b.d[9], *dys = b.d[10], *dx1 = b.d[11], *dm = b.d[12], *dn = b.d[13], *dxs = b.d[14];
     const int sblocks = (int)(((size_t)Rr * D + 255) / 256);
-    gather(c, x, xs, Rs, n_rec, NM, 0);
-    gather(c, dy, dys, Rs, n_rec, NM, 0);
-    rmsnorm_fwd(c, xs, w.norm1_w, n, b.inv[0], Rs);
-    gemm(NT, n, D, w.linear1_w, D, b1, D, M, D, D, nullptr, nullptr, 0, 0, c.st);
-    count_launch();
-    k_conv_fwd<<<sblocks, 256, 0, c.st>>>(b1, hid, w.conv_w, w.conv_b, u, gm);
-    gemm(NT, u, D, w.a_w, D, za, D, M, D, D, w.a_b, nullptr, 0, 0, c.st);
-    gemm(NT, u, D, w.x_w, D, zx, D, M, D, D, w.x_b, nullptr, 0, 0, c.st);
-    count_launch();
-    k_scan_fwd<<<sblocks, 256, 0, c.st>>>(za, zx, u, hid, w.log_lambda, hs, gm);
-    gemm(NT, n, D, w.linear2_w, D, b2p, D, M, D, D, nullptr, nullptr, 0, 0, c.st);
-    gelu_mul_fwd(c, b2p, hs, m, Rs * D);                                          // m = h * gelu(linear2 n)
-    gemm(NT, m, D, w.out_w, D, x1, D, M, D, D, nullptr, xs, D, 0, c.st);
-
+    ships_fwd(c, w, x, hid, done, nullptr, tg);
+    gather(c, dy, dys, Rs, tg.n_rec, tg.NM, 0);
     mlp_bwd(c, x1, dys, dx1, Rs, w.norm2_w, w.gate_w, w.up_w, w.down_w, dw.norm2_w, dw.gate_w, dw.up_w, dw.down_w);
 
-    gemm(TN, dx1, D, m, D, dw.out_w, D, D, D, M, nullptr, nullptr, 0, 0, c.st);
-    gemm(NN, dx1, D, w.out_w, D, dm, D, M, D, D, nullptr, nullptr, 0, 0, c.st);
-    gelu_mul_bwd(c, b2p, hs, dm, b2p, dm, Rs * D);                                // b2p <- d linear2 out, dm <- d h
-    gemm(TN, b2p, D, n, D, dw.linear2_w, D, D, D, M, nullptr, nullptr, 0, 0, c.st);
-    gemm(NN, b2p, D, w.linear2_w, D, dn, D, M, D, D, nullptr, nullptr, 0, 0, c.st);
+    mm(c, TN, dx1, D, m, D, dw.out_w, D, D, D, M);
+    mm(c, NN, dx1, D, w.out_w, D, dm, D, M, D, D);
+    gelu_mul_bwd(c, b2p, hs, dm, b2p, dm, Rs * D);                      // b2p <- d linear2 out, dm <- d h
+    mm(c, TN, b2p, D, n, D, dw.linear2_w, D, D, D, M);
+    mm(c, NN, b2p, D, w.linear2_w, D, dn, D, M, D, D);
     count_launch();
     k_scan_bwd<<<sblocks, 256, 0, c.st>>>(za, zx, u, hs, dm, hid, d_hid_out, d_hid_in, w.log_lambda, dw.log_lambda, gm);
     // za, zx hold d za, d zx; dm the direct part of d u
-    gemm(TN, za, D, u, D, dw.a_w, D, D, D, M, nullptr, nullptr, 0, 0, c.st);
-    gemm(TN, zx, D, u, D, dw.x_w, D, D, D, M, nullptr, nullptr, 0, 0, c.st);
+    mm(c, TN, za, D, u, D, dw.a_w, D, D, D, M);
+    mm(c, TN, zx, D, u, D, dw.x_w, D, D, D, M);
     colsum(c, za, dw.a_b, Rs, D);
     colsum(c, zx, dw.x_b, Rs, D);
-    gemm(NN, za, D, w.a_w, D, dm, D, M, D, D, nullptr, nullptr, 0, 1, c.st);
-    gemm(NN, zx, D, w.x_w, D, dm, D, M, D, D, nullptr, nullptr, 0, 1, c.st);
+    mm(c, NN, za, D, w.a_w, D, dm, D, M, D, D, nullptr, nullptr, 0, 1);
+    mm(c, NN, zx, D, w.x_w, D, dm, D, M, D, D, nullptr, nullptr, 0, 1);
     float* db1 = za;   // free now
     count_launch();
     k_conv_bwd<<<sblocks, 256, 0, c.st>>>(dm, b1, hid, d_hid_out, d_hid_in, w.conv_w, db1, dw.conv_w, dw.conv_b, gm);
-    gemm(TN, db1, D, n, D, dw.linear1_w, D, D, D, M, nullptr, nullptr, 0, 0, c.st);
-    gemm(NN, db1, D, w.linear1_w, D, dn, D, M, D, D, nullptr, nullptr, 0, 1, c.st);
+    mm(c, TN, db1, D, n, D, dw.linear1_w, D, D, D, M);
+    mm(c, NN, db1, D, w.linear1_w, D, dn, D, M, D, D, nullptr, nullptr, 0, 1);
     rmsnorm_bwd(c, xs, w.norm1_w, b.inv[0], dn, dx1, dxs, dw.norm1_w, Rs);
-    scatter(c, dxs, dx, Rs, n_rec, NM, 0);
+    scatter(c, dxs, dx, Rs, tg.n_rec, tg.NM, 0);
   }
   if (Rf) {
     if (!w.field_sub_w || !dw.field_sub_w) return BNB_ERR_NULL_POINTER;
-    const int M = (int)Rf, nf = NM - n_rec;
+    const int M = (int)Rf, nf = tg.NM - tg.n_rec;
     float *xf = b.d[0], *n = b.d[1], *c1 = b.d[2], *b1 = b.d[3], *b2p = b.d[4], *m = b.d[5], *x1 = b.d[6], *dyf = b.d[7],
           *dx1 = b.d[8], *dm = b.d[9], *dc1 = b.d[10], *dn = b.d[11], *dxf = b.d[12];
-    gather(c, x, xf, Rf, nf, NM, n_rec);
-    gather(c, dy, dyf, Rf, nf, NM, n_rec);
-    rmsnorm_fwd(c, xf, w.norm1_w, n, b.inv[0], Rf);
-    gemm(NT, n, D, w.linear1_w, D, c1, D, M, D, D, nullptr, nullptr, 0, 0, c.st);
-    gemm(NT, c1, D, w.field_sub_w, D, b1, D, M, D, D, nullptr, nullptr, 0, 0, c.st);
-    gemm(NT, n, D, w.linear2_w, D, b2p, D, M, D, D, nullptr, nullptr, 0, 0, c.st);
-    gelu_mul_fwd(c, b2p, b1, m, Rf * D);
-    gemm(NT, m, D, w.out_w, D, x1, D, M, D, D, nullptr, xf, D, 0, c.st);
-
+    fields_fwd(c, w, x, nullptr, tg);
+    gather(c, dy, dyf, Rf, nf, tg.NM, tg.n_rec);
     mlp_bwd(c, x1, dyf, dx1, Rf, w.norm2_w, w.gate_w, w.up_w, w.down_w, dw.norm2_w, dw.gate_w, dw.up_w, dw.down_w);
 
-    gemm(TN, dx1, D, m, D, dw.out_w, D, D, D, M, nullptr, nullptr, 0, 0, c.st);
-    gemm(NN, dx1, D, w.out_w, D, dm, D, M, D, D, nullptr, nullptr, 0, 0, c.st);
-    gelu_mul_bwd(c, b2p, b1, dm, b2p, dm, Rf * D);                                // b2p <- d linear2 out, dm <- d b1
-    gemm(TN, dm, D, c1, D, dw.field_sub_w, D, D, D, M, nullptr, nullptr, 0, 0, c.st);
-    gemm(NN, dm, D, w.field_sub_w, D, dc1, D, M, D, D, nullptr, nullptr, 0, 0, c.st);
-    gemm(TN, dc1, D, n, D, dw.linear1_w, D, D, D, M, nullptr, nullptr, 0, 0, c.st);
-    gemm(NN, dc1, D, w.linear1_w, D, dn, D, M, D, D, nullptr, nullptr, 0, 0, c.st);
-    gemm(TN, b2p, D, n, D, dw.linear2_w, D, D, D, M, nullptr, nullptr, 0, 0, c.st);
-    gemm(NN, b2p, D, w.linear2_w, D, dn, D, M, D, D, nullptr, nullptr, 0, 1, c.st);
+    mm(c, TN, dx1, D, m, D, dw.out_w, D, D, D, M);
+    mm(c, NN, dx1, D, w.out_w, D, dm, D, M, D, D);
+    gelu_mul_bwd(c, b2p, b1, dm, b2p, dm, Rf * D);                      // b2p <- d linear2 out, dm <- d b1
+    mm(c, TN, dm, D, c1, D, dw.field_sub_w, D, D, D, M);
+    mm(c, NN, dm, D, w.field_sub_w, D, dc1, D, M, D, D);
+    mm(c, TN, dc1, D, n, D, dw.linear1_w, D, D, D, M);
+    mm(c, NN, dc1, D, w.linear1_w, D, dn, D, M, D, D);
+    mm(c, TN, b2p, D, n, D, dw.linear2_w, D, D, D, M);
+    mm(c, NN, b2p, D, w.linear2_w, D, dn, D, M, D, D, nullptr, nullptr, 0, 1);
     rmsnorm_bwd(c, xf, w.norm1_w, b.inv[0], dn, dx1, dxf, dw.norm1_w, Rf);
-    scatter(c, dxf, dx, Rf, nf, NM, n_rec);
+    scatter(c, dxf, dx, Rf, nf, tg.NM, tg.n_rec);
   }
   return BNB_OK;
 }
@@ -1039,6 +1178,7 @@ int trunk_sequence_bwd(const TrunkBwdArgs& a) {
   Ctx c;
   c.D = D;
   c.H = a.H;
+  c.bf16 = a.bf16_products;
   c.st = st;
   uintptr_t base = (reinterpret_cast<uintptr_t>(a.scratch) + 255) & ~(uintptr_t)255;
   Arena ar{reinterpret_cast<char*>(base)};
@@ -1051,6 +1191,7 @@ int trunk_sequence_bwd(const TrunkBwdArgs& a) {
   }
 
   // first pass: the input of every sublayer
+  const TemporalGeom tgm{T, B, NM, n_rec};
   const float* cur = a.x;
   const float* inputs[256];
   if (S > 256) return BNB_ERR_BAD_ARGUMENT;
@@ -1060,9 +1201,7 @@ int trunk_sequence_bwd(const TrunkBwdArgs& a) {
       inputs[s] = cur;
       if (s + 1 == S) break;
       float* out = c.b.bound + (size_t)s * R * D;
-      int rc = exact::spatial_block(a.spatial[blk * a.n_spatial + j], D, a.H, cur, a.alive, a.bullets, out, bt, T, false,
-                                    c.b.w3[0], c.b.d[1], c.b.kvb, G > 0 ? G : 1, st);
-      if (rc) return rc;
+      spatial_fwd(c, a.spatial[blk * a.n_spatial + j], cur, a.alive, a.bullets, out, G, NM);
       cur = out;
     }
     for (int j = 0; j < a.n_temporal; ++j, ++s) {
@@ -1070,8 +1209,7 @@ int trunk_sequence_bwd(const TrunkBwdArgs& a) {
       if (s + 1 == S) break;
       float* out = c.b.bound + (size_t)s * R * D;
       const int slot = blk * a.n_temporal + j;
-      int rc = exact::temporal_block(a.temporal[slot], D, cur, out, a.hidden_in + (size_t)slot * Rr * 4 * D, nullptr, a.done,
-                                     nullptr, bt, T, false, st);
+      int rc = temporal_fwd(c, a.temporal[slot], cur, a.hidden_in + (size_t)slot * Rr * 4 * D, a.done, out, tgm);
       if (rc) return rc;
       cur = out;
     }
@@ -1089,7 +1227,7 @@ int trunk_sequence_bwd(const TrunkBwdArgs& a) {
       const size_t hoff = (size_t)slot * Rr * 4 * D;
       int rc = temporal_bwd(c, a.temporal[slot], a.d_temporal[slot], inputs[s], a.hidden_in + hoff,
                             a.d_hidden_out ? a.d_hidden_out + hoff : nullptr, a.d_hidden_in ? a.d_hidden_in + hoff : nullptr,
-                            a.done, dcur, dout, T, B, NM, n_rec);
+                            a.done, dcur, dout, tgm);
       if (rc) return rc;
       dcur = dout;
     }

@@ -20,6 +20,7 @@ struct TrunkBwdArgs {
   const uint8_t* done;
   const BnbBatch* batch;
   int T;
+  bool bf16_products;   // products round their operands to bfloat16 (forward ran under autocast)
   const float* dy;
   const float* d_hidden_out;
   float* dx;

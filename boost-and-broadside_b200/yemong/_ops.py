@@ -199,7 +199,8 @@ def trunk_backward(
     geom: List[int],
 ) -> List[Tensor]:
     """Gradients of ``trunk_forward`` (environments of one size, no ``reset_env``) through
-    ``bnb_trunk_sequence_bwd``: float32 arithmetic whatever the forward's precision was.  Returns
+    ``bnb_trunk_sequence_bwd``: float32 tensors throughout; after a forward under bf16 autocast the
+    Linear products round their operands to bfloat16, as the reference's backward does there.  Returns
     [d x, d hidden, d bullets (empty without bullets), then one gradient per tensor of ``weights``]."""
     dev = x.device
     D = x.shape[-1]
@@ -232,7 +233,8 @@ def trunk_backward(
         scratch = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=dev)   # released after the call's stream work
         st = _capi.lib.bnb_trunk_sequence_bwd(
             sw, tw, sg, tg, n_blocks, n_spatial, n_temporal, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8), bul.arg,
-            _capi.ptr(hin), _capi.ptr(done_u8), batch, T, dyin.data_ptr(), _capi.ptr(dho), dx.data_ptr(),
+            _capi.ptr(hin), _capi.ptr(done_u8), batch, T, _capi.BNB_BF16 if geom[G_PRECISION] == _capi.BNB_BF16 else _capi.BNB_FP32,
+            dyin.data_ptr(), _capi.ptr(dho), dx.data_ptr(),
             _capi.ptr(dh), _capi.ptr(dbul) if bul.struct is not None else None, scratch.data_ptr(), scratch.numel(),
             _capi.stream_handle(dev),
         )

@@ -356,7 +356,10 @@ size_t bnb_trunk_bwd_scratch_bytes(int n_blocks, int n_spatial, int n_temporal, 
                                    const BnbBatch* batch, int timesteps, int bullets_per_env);
 
 /* Backward of bnb_trunk_sequence (and, with timesteps = 1 and no done, of bnb_trunk_step without
- * reset_env), float32.
+ * reset_env).  Every tensor is float32.  precision BNB_FP32: float32-accurate products (3 x tf32).
+ * BNB_BF16: the Linear products of the recomputed forward and of the gradients round their operands
+ * to bfloat16 and accumulate in float32, as autocast makes the reference's backward do; everything
+ * else (norms, softmax, gates, recurrence, residual stream) stays float32.
  * Replaces: what loss.backward() runs through the trunk loop of YemongPolicy.evaluate_actions,
  * models/yemong/policy.py:422-478 (reached from train/rl/ppo.py:1974), with or without
  * grad_checkpoint (policy.py:451-467; this entry always recomputes).
@@ -377,7 +380,7 @@ int bnb_trunk_sequence_bwd(const BnbSpatialWeights* spatial, const BnbTemporalWe
                            int n_blocks, int n_spatial, int n_temporal, int d_model, int n_heads,
                            const float* x, const uint8_t* alive, const BnbBullets* bullets,
                            const float* hidden_in, const uint8_t* done, const BnbBatch* batch, int timesteps,
-                           const float* dy, const float* d_hidden_out, float* dx, float* d_hidden_in,
+                           int precision, const float* dy, const float* d_hidden_out, float* dx, float* d_hidden_in,
                            float* d_bullets, void* scratch, size_t scratch_bytes, void* stream);
 
 /* One head of the policy: Linear + b -> RMSNorm -> GELU(erf) -> Linear + b on the trunk's output.
