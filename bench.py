@@ -359,6 +359,78 @@ def time_gpu_reference(name: str, dev: torch.device, steps: int) -> dict:
 # ----------------------------------------------------------------------------- GPU arm
 
 
+def time_train_step(trunk, dev: torch.device, n_envs: int = 1024, timesteps: int = 32, iters: int = 3) -> dict:
+    """Forward + backward of the sequence path at the PPO-update shape (C4's environments of 8 ships,
+    T steps, bf16 autocast): loss = <y, dy>, gradients of tokens and every parameter.  This package
+    (fused forward, bnb_trunk_sequence_bwd behind autograd) beside the reference's own modules from
+    oracle/_ref through torch autograd, eager and torch.compile, same box, same shapes, CUDA events.
+    The batch is a quarter of C4 because the reference's attention (cuDNN SDPA) refuses the full
+    131072-environment-step batch when gradients are on."""
+    from oracle import ref_runner
+
+    W = workloads_module()
+    w = W.c4(n_envs=n_envs, timesteps=timesteps)
+    x, alive, hidden, done = (t.to(dev) for t in (w.x, w.alive, w.hidden, w.done))
+    dy = torch.randn(x.shape, device=dev, generator=torch.Generator(device=dev).manual_seed(0))
+    tokens = w.entity_tokens
+    out: dict = {"workload": f"C4 shape, {n_envs} environments x 8 ships x T={timesteps}, bf16 autocast, forward + backward",
+                 "tokens_per_step": tokens, "iters": iters}
+
+    def timed(fn):
+        fn()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.reset_peak_memory_stats(dev)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        ms = e0.elapsed_time(e1) / iters
+        return {"ms_per_step": ms, "value": tokens / (ms * 1e-3), "unit": UNIT,
+                "peak_gib": torch.cuda.max_memory_allocated(dev) / 2**30}
+
+    was_training = trunk.training
+    trunk.train()
+
+    def ours():
+        trunk.zero_grad(set_to_none=True)
+        xg = x.clone().requires_grad_(True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            y, _ = trunk.sequence(xg, alive, hidden, done)
+        (y.float() * dy).sum().backward()
+
+    try:
+        out["ours"] = timed(ours)
+    finally:
+        trunk.zero_grad(set_to_none=True)
+        trunk.train(was_training)
+    if not ref_runner.available():
+        out["reference"] = {"unavailable": "oracle/_ref is absent"}
+        return out
+    ref = ref_runner.ReferenceTrunk().train().to(dev)
+    xb, ab, dyb = x.reshape(timesteps, n_envs, 8, -1), alive.reshape(timesteps, n_envs, 8), dy.reshape(timesteps, n_envs, 8, -1)
+
+    def make(seq):
+        def run():
+            ref.zero_grad(set_to_none=True)
+            xg = xb.clone().requires_grad_(True)
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                y = seq(xg, ab, hidden, done)
+            (y.float() * dyb).sum().backward()
+        return run
+
+    for key, seq in (("reference_eager", ref.sequence), ("reference_compiled", None)):
+        try:
+            if seq is None:
+                seq = torch.compile(ref.sequence)
+            out[key] = timed(make(seq))
+            out[key]["ours_over_this"] = out["ours"]["value"] / out[key]["value"]
+        except Exception as e:  # noqa: BLE001 - a comparator that fails is reported, not fatal
+            out[key] = {"error": repr(e)[:200]}
+    return out
+
+
 def run_ours(args) -> None:
     import boost_and_broadside_b200 as bnb
     from boost_and_broadside_b200 import _capi
@@ -640,6 +712,8 @@ def run_ours(args) -> None:
                 if isinstance(ref.get(k), dict) and "value" in ref[k]:
                     ref[k]["ours_over_this"] = line["value"] / ref[k]["value"]
             line["gpu_reference"] = ref
+        if world == 1 and not args.no_train and args.workload == "C2":
+            line["train_step"] = time_train_step(trunk, dev)
         if world == 1 and not args.no_cpu:
             base = time_cpu(args.workload, 3, 1)
             line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
@@ -660,6 +734,7 @@ def main() -> None:
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-gpu-ref", action="store_true", help="skip the same-box GPU comparator (reference modules, eager and compiled)")
     ap.add_argument("--no-c5", action="store_true", help="skip the sharded ragged C5 record")
+    ap.add_argument("--no-train", action="store_true", help="skip the forward + backward record (train_step)")
     ap.add_argument("--shard", action="store_true",
                     help="one global batch, environments sharded contiguously over the ranks (strong scaling) "
                          "instead of one full batch per rank")

@@ -300,12 +300,49 @@ size_t bnb_trunk_bwd_scratch_bytes(int n_blocks, int n_spatial, int n_temporal, 
   return bnb::grad::scratch_bytes(n_blocks, n_spatial, n_temporal, d_model, *batch, timesteps, bullets_per_env);
 }
 
+size_t bnb_trunk_kept_bytes(int n_blocks, int n_spatial, int n_temporal, int d_model, int n_heads, const BnbBatch* batch,
+                            int timesteps, int bullets_per_env) {
+  if (!batch || n_blocks < 0 || n_spatial < 0 || n_temporal < 0 || d_model <= 0 || timesteps < 1) return 0;
+  if (check_dims(d_model, n_heads) || check_batch(batch)) return 0;
+  return bnb::grad::kept_bytes(n_blocks, n_spatial, n_temporal, d_model, n_heads, *batch, timesteps, bullets_per_env);
+}
+
+int bnb_trunk_sequence_fwd_train(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal, int n_blocks,
+                                 int n_spatial, int n_temporal, int d_model, int n_heads, const float* x,
+                                 const uint8_t* alive, const BnbBullets* bullets, float* y, const float* hidden_in,
+                                 float* hidden_out, const uint8_t* done, const BnbBatch* batch, int timesteps, int precision,
+                                 void* kept, size_t kept_bytes, void* scratch, size_t scratch_bytes, void* stream) {
+  int st = check_dims(d_model, n_heads);
+  if (st) return st;
+  if ((st = check_batch(batch))) return st;
+  if (batch->tok_off) return BNB_ERR_UNSUPPORTED_DIMS;
+  if (precision != BNB_FP32 && precision != BNB_BF16) return BNB_ERR_BAD_ARGUMENT;
+  if (n_blocks < 0 || n_spatial < 0 || n_temporal < 0 || timesteps < 1) return BNB_ERR_BAD_ARGUMENT;
+  if ((size_t)timesteps * batch->total_tokens == 0) return BNB_OK;
+  const int ns = n_blocks * n_spatial, nt = n_blocks * n_temporal;
+  if ((ns && !spatial) || (nt && !temporal)) return BNB_ERR_NULL_POINTER;
+  if (!x || !y || !scratch || !kept) return BNB_ERR_NULL_POINTER;
+  if (nt && batch->total_ships > 0 && !hidden_in) return BNB_ERR_NULL_POINTER;
+  if (!aligned16(x) || !aligned16(y) || !aligned16(hidden_in) || !aligned16(hidden_out)) return BNB_ERR_MISALIGNED;
+  for (int i = 0; i < ns; ++i)
+    if ((st = check_spatial(&spatial[i]))) return st;
+  for (int i = 0; i < nt; ++i)
+    if ((st = check_temporal(&temporal[i], batch->total_tokens > batch->total_ships))) return st;
+  if ((st = check_bullets(bullets))) return st;
+  if (!any_reads_bullets(spatial, ns, bullets)) bullets = nullptr;
+  bnb::grad::TrunkFwdTrainArgs a{spatial, temporal, n_blocks, n_spatial, n_temporal, d_model, n_heads, x, alive, bullets,
+                                 hidden_in, done, batch, timesteps, precision == BNB_BF16, y, hidden_out, scratch,
+                                 scratch_bytes, kept, kept_bytes, static_cast<cudaStream_t>(stream)};
+  return bnb::grad::trunk_sequence_fwd_train(a);
+}
+
 int bnb_trunk_sequence_bwd(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal,
                            const BnbSpatialGrads* d_spatial, const BnbTemporalGrads* d_temporal, int n_blocks,
                            int n_spatial, int n_temporal, int d_model, int n_heads, const float* x, const uint8_t* alive,
                            const BnbBullets* bullets, const float* hidden_in, const uint8_t* done, const BnbBatch* batch,
                            int timesteps, int precision, const float* dy, const float* d_hidden_out, float* dx,
-                           float* d_hidden_in, float* d_bullets, void* scratch, size_t scratch_bytes, void* stream) {
+                           float* d_hidden_in, float* d_bullets, void* kept, size_t kept_bytes, void* scratch,
+                           size_t scratch_bytes, void* stream) {
   int st = check_dims(d_model, n_heads);
   if (st) return st;
   if ((st = check_batch(batch))) return st;
@@ -352,7 +389,8 @@ int bnb_trunk_sequence_bwd(const BnbSpatialWeights* spatial, const BnbTemporalWe
   }
   bnb::grad::TrunkBwdArgs a{spatial, temporal, d_spatial, d_temporal, n_blocks, n_spatial, n_temporal, d_model, n_heads,
                             x, alive, bullets, hidden_in, done, batch, timesteps, precision == BNB_BF16, dy, d_hidden_out, dx, d_hidden_in,
-                            d_bullets, scratch, scratch_bytes, static_cast<cudaStream_t>(stream)};
+                            d_bullets, scratch, scratch_bytes, kept, kept_bytes, static_cast<cudaStream_t>(stream)};
+  if (bullets && !any_reads_bullets(spatial, ns, bullets)) a.bullets = nullptr;
   return bnb::grad::trunk_sequence_bwd(a);
 }
 

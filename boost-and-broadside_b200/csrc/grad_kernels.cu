@@ -681,6 +681,22 @@ __global__ void __launch_bounds__(256) k_scan_fwd(const float* __restrict__ za, 
   }
 }
 
+// State after the last step: h_T and the last three padded conv inputs (griffin.py:271-275).
+__global__ void __launch_bounds__(256) k_final_state(const float* __restrict__ hs, const float* __restrict__ b1,
+                                                     const float* __restrict__ hid, float* __restrict__ hid_out, ShipGeom gm) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)gm.Rr * gm.D) return;
+  const int s = (int)(idx / gm.D), d = (int)(idx - (size_t)s * gm.D);
+  const size_t step = (size_t)gm.Rr * gm.D, at0 = (size_t)s * gm.D + d;
+  float* op = hid_out + (size_t)s * 4 * gm.D + d;
+  op[0] = hs[(size_t)(gm.T - 1) * step + at0];
+#pragma unroll
+  for (int k = 0; k < 3; ++k) {
+    const int p = gm.T + k;   // padded index: 0..2 the stored taps, 3 + t the linear1 output of step t
+    op[(size_t)(k + 1) * gm.D] = p < 3 ? hid[(size_t)s * 4 * gm.D + (size_t)(p + 1) * gm.D + d] : b1[(size_t)(p - 3) * step + at0];
+  }
+}
+
 // Reverse-time adjoint of k_scan_fwd.  In: za, zx (with bias), u, hs, dhs (gradient reaching every
 // h_t from the output path) and the gradient of the final state.  Out: d za, d zx in place of za,
 // zx; the direct part of d u in place of dhs; d h0; d log_lambda (reduced over rows, atomics).
@@ -831,6 +847,25 @@ void plan(Arena& ar, Bufs& b, int S, size_t R, int D, size_t RB) {
   b.bul_dn = ar.take(RB * D);
 }
 
+// The buffers the forward part of one path writes and its backward part reads, taken from an arena
+// of their own when the activations are kept between the two (see trunk_sequence_fwd_train).
+enum PathKind { P_SPATIAL, P_SHIPS, P_FIELDS };
+
+void bind_forward(Arena& ar, Bufs& b, PathKind kind, size_t rows, int D, size_t RB) {
+  const int nd = kind == P_SPATIAL ? 3 : kind == P_SHIPS ? 10 : 7;
+  for (int i = 0; i < nd; ++i) b.d[i] = ar.take(rows * D);
+  b.d[15] = ar.take(rows * D);
+  b.inv[0] = ar.take(rows);
+  b.inv[1] = ar.take(rows);
+  if (kind == P_SPATIAL) {
+    b.w3[0] = ar.take(rows * 3 * D);
+    b.bul_n = ar.take(RB * D);
+    b.bul_inv = ar.take(RB);
+    b.kvb = ar.take(RB * 2 * D);
+  }
+  for (auto& p : b.w4) p = ar.take(rows * 4 * D);
+}
+
 inline int blocks_for(size_t n, int per_block, int cap = 148 * 8) {
   size_t g = (n + per_block - 1) / per_block;
   if (g > (size_t)cap) g = cap;
@@ -960,7 +995,7 @@ void spatial_fwd(const Ctx& c, const BnbSpatialWeights& w, const float* x, const
 }
 
 int spatial_bwd(const Ctx& c, const BnbSpatialWeights& w, const BnbSpatialGrads& dw, const float* x, const uint8_t* alive,
-                const BnbBullets* bul, float* d_bullets, const float* dy, float* dx, int G, int NM) {
+                const BnbBullets* bul, float* d_bullets, const float* dy, float* dx, int G, int NM, bool have_fwd) {
   const int D = c.D;
   const size_t R = (size_t)G * NM;
   const int M = (int)R;
@@ -972,7 +1007,7 @@ int spatial_bwd(const Ctx& c, const BnbSpatialWeights& w, const BnbSpatialGrads&
   const size_t RB = (size_t)G * nb;
   if (reads && (!dw.kv_bullet_w || !dw.norm_bullet_w)) return BNB_ERR_NULL_POINTER;
 
-  spatial_fwd(c, w, x, alive, bul, nullptr, G, NM);
+  if (!have_fwd) spatial_fwd(c, w, x, alive, bul, nullptr, G, NM);
   mlp_bwd(c, x1, dy, dx1, R, w.norm2_w, w.gate_w, w.up_w, w.down_w, dw.norm2_w, dw.gate_w, dw.up_w, dw.down_w);
 
   mm(c, TN, dx1, D, o, D, dw.out_w, D, D, D, M);
@@ -1024,7 +1059,7 @@ struct TemporalGeom {
 // linear1 out d[2], conv out d[3], gate pre-activations d[4] d[5], states d[6], linear2 out d[7],
 // gated branch d[8], x1 d[9]; with y, the sublayer's output goes to d[14] and from there to y's ship rows.
 void ships_fwd(const Ctx& c, const BnbTemporalWeights& w, const float* x, const float* hid, const uint8_t* done, float* y,
-               const TemporalGeom& tg) {
+               float* hid_out, const TemporalGeom& tg) {
   const int D = c.D;
   const Bufs& b = c.b;
   const size_t Rs = tg.Rs();
@@ -1042,6 +1077,10 @@ void ships_fwd(const Ctx& c, const BnbTemporalWeights& w, const float* x, const 
   mm(c, NT, u, D, w.x_w, D, zx, D, M, D, D, w.x_b);
   count_launch();
   k_scan_fwd<<<sblocks, 256, 0, c.st>>>(za, zx, u, hid, w.log_lambda, hs, gm);
+  if (hid_out) {
+    count_launch();
+    k_final_state<<<sblocks, 256, 0, c.st>>>(hs, b1, hid, hid_out, gm);
+  }
   mm(c, NT, n, D, w.linear2_w, D, b2p, D, M, D, D);
   gelu_mul_fwd(c, b2p, hs, m, Rs * D);                                  // m = h * gelu(linear2 n)
   mm(c, NT, m, D, w.out_w, D, x1, D, M, D, D, nullptr, xs, D);
@@ -1068,31 +1107,32 @@ void fields_fwd(const Ctx& c, const BnbTemporalWeights& w, const float* x, float
   if (y) scatter(c, b.d[14], y, Rf, nf, tg.NM, tg.n_rec);
 }
 
-int temporal_fwd(const Ctx& c, const BnbTemporalWeights& w, const float* x, const float* hid, const uint8_t* done, float* y,
-                 const TemporalGeom& tg) {
-  if (tg.Rs()) ships_fwd(c, w, x, hid, done, y, tg);
+int temporal_fwd(const Ctx& cs, const Ctx& cf, const BnbTemporalWeights& w, const float* x, const float* hid,
+                 const uint8_t* done, float* y, float* hid_out, const TemporalGeom& tg) {
+  if (tg.Rs()) ships_fwd(cs, w, x, hid, done, y, hid_out, tg);
   if (tg.Rf()) {
     if (!w.field_sub_w) return BNB_ERR_NULL_POINTER;
-    fields_fwd(c, w, x, y, tg);
+    fields_fwd(cf, w, x, y, tg);
   }
   return BNB_OK;
 }
 
 // One temporal sublayer: the recurrent path over the ship rows, the non-recurrent one over the
 // field rows, both sharing every parameter but field_sub.
-int temporal_bwd(const Ctx& c, const BnbTemporalWeights& w, const BnbTemporalGrads& dw, const float* x, const float* hid,
-                 const float* d_hid_out, float* d_hid_in, const uint8_t* done, const float* dy, float* dx,
-                 const TemporalGeom& tg) {
-  const int D = c.D;
-  const Bufs& b = c.b;
+int temporal_bwd(const Ctx& cs, const Ctx& cf, const BnbTemporalWeights& w, const BnbTemporalGrads& dw, const float* x,
+                 const float* hid, const float* d_hid_out, float* d_hid_in, const uint8_t* done, const float* dy, float* dx,
+                 const TemporalGeom& tg, bool have_fwd) {
+  const int D = cs.D;
   const size_t Rs = tg.Rs(), Rf = tg.Rf();
   if (Rs) {
+    const Ctx& c = cs;
+    const Bufs& b = c.b;
     const int M = (int)Rs, Rr = tg.B * tg.n_rec;
     ShipGeom gm{tg.T, Rr, D, tg.n_rec, tg.B, done};
     float *xs = b.d[0], *n = b.d[1], *b1 = b.d[2], *u = b.d[3], *za = b.d[4], *zx = b.d[5], *hs = b.d[6], *b2p = b.d[7],
           *m = b.d[8], *x1 = b.d[9], *dys = b.d[10], *dx1 = b.d[11], *dm = b.d[12], *dn = b.d[13], *dxs = b.d[14];
     const int sblocks = (int)(((size_t)Rr * D + 255) / 256);
-    ships_fwd(c, w, x, hid, done, nullptr, tg);
+    if (!have_fwd) ships_fwd(c, w, x, hid, done, nullptr, nullptr, tg);
     gather(c, dy, dys, Rs, tg.n_rec, tg.NM, 0);
     mlp_bwd(c, x1, dys, dx1, Rs, w.norm2_w, w.gate_w, w.up_w, w.down_w, dw.norm2_w, dw.gate_w, dw.up_w, dw.down_w);
 
@@ -1119,11 +1159,13 @@ int temporal_bwd(const Ctx& c, const BnbTemporalWeights& w, const BnbTemporalGra
     scatter(c, dxs, dx, Rs, tg.n_rec, tg.NM, 0);
   }
   if (Rf) {
+    const Ctx& c = cf;
+    const Bufs& b = c.b;
     if (!w.field_sub_w || !dw.field_sub_w) return BNB_ERR_NULL_POINTER;
     const int M = (int)Rf, nf = tg.NM - tg.n_rec;
     float *xf = b.d[0], *n = b.d[1], *c1 = b.d[2], *b1 = b.d[3], *b2p = b.d[4], *m = b.d[5], *x1 = b.d[6], *dyf = b.d[7],
           *dx1 = b.d[8], *dm = b.d[9], *dc1 = b.d[10], *dn = b.d[11], *dxf = b.d[12];
-    fields_fwd(c, w, x, nullptr, tg);
+    if (!have_fwd) fields_fwd(c, w, x, nullptr, tg);
     gather(c, dy, dyf, Rf, nf, tg.NM, tg.n_rec);
     mlp_bwd(c, x1, dyf, dx1, Rf, w.norm2_w, w.gate_w, w.up_w, w.down_w, dw.norm2_w, dw.gate_w, dw.up_w, dw.down_w);
 
@@ -1148,6 +1190,57 @@ bool dims_ok(int D, int H) {
   return dh == 8 || dh == 16 || dh == 32;
 }
 
+// Everything both entry points derive from the call's geometry, and the walk over the sublayers
+// that hands each path its buffers: from the shared scratch, or (kept activations) from the arena
+// the training forward filled.
+struct Walk {
+  int D, T, B, NM, n_rec, G, S, nb;
+  size_t R, RB, Rr;
+  TemporalGeom tgm;
+};
+
+int make_walk(Walk& wk, int n_blocks, int n_spatial, int n_temporal, int D, int H, const BnbBatch& bt, int T,
+              const BnbBullets* bullets) {
+  if (bt.tok_off || bt.ship_off) return BNB_ERR_UNSUPPORTED_DIMS;   // environments of one size only
+  if (!dims_ok(D, H)) return BNB_ERR_UNSUPPORTED_DIMS;
+  wk.D = D; wk.T = T; wk.B = bt.n_envs; wk.NM = bt.tokens_per_env; wk.n_rec = bt.ships_per_env;
+  if (T < 1 || wk.B < 0 || wk.NM < 1 || wk.n_rec < 0 || wk.n_rec > wk.NM) return BNB_ERR_BAD_ARGUMENT;
+  wk.G = T * wk.B;
+  wk.R = (size_t)wk.G * wk.NM;
+  if (wk.R > (size_t)INT32_MAX / 2) return BNB_ERR_TOO_MANY_TOKENS;
+  wk.S = n_blocks * (n_spatial + n_temporal);
+  if (wk.S > 256) return BNB_ERR_BAD_ARGUMENT;
+  wk.nb = bullets ? bullets->per_env : 0;
+  wk.RB = (size_t)wk.G * wk.nb;
+  wk.Rr = (size_t)wk.B * wk.n_rec;
+  wk.tgm = TemporalGeom{T, wk.B, wk.NM, wk.n_rec};
+  return BNB_OK;
+}
+
+// Layout of the kept activations: the outputs of sublayers 0 .. S-2, then per sublayer the buffers
+// of bind_forward (a temporal sublayer: ships, then fields).
+struct Kept {
+  float* bound = nullptr;
+  Bufs first[256], second[256];   // spatial or ships | fields
+};
+
+void layout_kept(Arena& ar, Kept& k, const Walk& wk, int n_blocks, int n_spatial, int n_temporal, const Bufs& shared) {
+  k.bound = ar.take((size_t)(wk.S > 1 ? wk.S - 1 : 0) * wk.R * wk.D);
+  int s = 0;
+  for (int blk = 0; blk < n_blocks; ++blk) {
+    for (int j = 0; j < n_spatial; ++j, ++s) {
+      k.first[s] = shared;
+      bind_forward(ar, k.first[s], P_SPATIAL, wk.R, wk.D, wk.RB);
+    }
+    for (int j = 0; j < n_temporal; ++j, ++s) {
+      k.first[s] = shared;
+      k.second[s] = shared;
+      bind_forward(ar, k.first[s], P_SHIPS, wk.tgm.Rs(), wk.D, 0);
+      bind_forward(ar, k.second[s], P_FIELDS, wk.tgm.Rf(), wk.D, 0);
+    }
+  }
+}
+
 }  // namespace
 
 size_t scratch_bytes(int n_blocks, int n_spatial, int n_temporal, int D, const BnbBatch& bt, int T, int bullets_per_env) {
@@ -1159,83 +1252,156 @@ size_t scratch_bytes(int n_blocks, int n_spatial, int n_temporal, int D, const B
   return ar.off + 256;
 }
 
-int trunk_sequence_bwd(const TrunkBwdArgs& a) {
-  const BnbBatch& bt = *a.batch;
-  if (bt.tok_off || bt.ship_off) return BNB_ERR_UNSUPPORTED_DIMS;   // environments of one size only
-  if (!dims_ok(a.D, a.H)) return BNB_ERR_UNSUPPORTED_DIMS;
-  const int D = a.D, T = a.T, B = bt.n_envs, NM = bt.tokens_per_env, n_rec = bt.ships_per_env;
-  if (T < 1 || B < 0 || NM < 1 || n_rec < 0 || n_rec > NM) return BNB_ERR_BAD_ARGUMENT;
-  const int G = T * B;
-  const size_t R = (size_t)G * NM;
-  if (R > (size_t)INT32_MAX / 2) return BNB_ERR_TOO_MANY_TOKENS;
-  const int S = a.n_blocks * (a.n_spatial + a.n_temporal);
-  const int nb = a.bullets ? a.bullets->per_env : 0;
-  const size_t RB = (size_t)G * nb;
-  const size_t Rr = (size_t)B * n_rec;
-  cudaStream_t st = a.stream;
-  if (R == 0) return BNB_OK;
+size_t kept_bytes(int n_blocks, int n_spatial, int n_temporal, int D, int H, const BnbBatch& bt, int T, int bullets_per_env) {
+  Walk wk;
+  BnbBullets bul{nullptr, nullptr, bullets_per_env};
+  if (make_walk(wk, n_blocks, n_spatial, n_temporal, D, H, bt, T, bullets_per_env > 0 ? &bul : nullptr)) return 0;
+  Arena ar{nullptr};
+  static thread_local Kept k;
+  layout_kept(ar, k, wk, n_blocks, n_spatial, n_temporal, Bufs{});
+  return ar.off + 256;
+}
 
-  Ctx c;
-  c.D = D;
-  c.H = a.H;
-  c.bf16 = a.bf16_products;
-  c.st = st;
-  uintptr_t base = (reinterpret_cast<uintptr_t>(a.scratch) + 255) & ~(uintptr_t)255;
+namespace {
+
+// Shared scratch and, when given, the kept-activation arena of a call.
+int open_buffers(Ctx& c, Kept* kept, const Walk& wk, int n_blocks, int n_spatial, int n_temporal, void* scratch,
+                 size_t scratch_bytes, void* kept_ptr, size_t kept_size) {
+  uintptr_t base = (reinterpret_cast<uintptr_t>(scratch) + 255) & ~(uintptr_t)255;
   Arena ar{reinterpret_cast<char*>(base)};
-  plan(ar, c.b, S, R, D, RB);
-  if (ar.off + (base - reinterpret_cast<uintptr_t>(a.scratch)) > a.scratch_bytes) return BNB_ERR_SCRATCH_TOO_SMALL;
+  plan(ar, c.b, kept_ptr ? 0 : wk.S, wk.R, wk.D, wk.RB);
+  if (ar.off + (base - reinterpret_cast<uintptr_t>(scratch)) > scratch_bytes) return BNB_ERR_SCRATCH_TOO_SMALL;
+  if (kept_ptr) {
+    uintptr_t kb = (reinterpret_cast<uintptr_t>(kept_ptr) + 255) & ~(uintptr_t)255;
+    Arena ka{reinterpret_cast<char*>(kb)};
+    layout_kept(ka, *kept, wk, n_blocks, n_spatial, n_temporal, c.b);
+    if (ka.off + (kb - reinterpret_cast<uintptr_t>(kept_ptr)) > kept_size) return BNB_ERR_SCRATCH_TOO_SMALL;
+  }
+  return BNB_OK;
+}
+
+}  // namespace
+
+// The forward of a call that will be differentiated: the same sublayer forward parts the backward
+// recomputes from, run once with every path's intermediates written to `kept`, plus the trunk's
+// output and final state.
+int trunk_sequence_fwd_train(const TrunkFwdTrainArgs& a) {
+  Walk wk;
+  int rc = make_walk(wk, a.n_blocks, a.n_spatial, a.n_temporal, a.D, a.H, *a.batch, a.T, a.bullets);
+  if (rc) return rc;
+  if (wk.R == 0) return BNB_OK;
+  const int D = wk.D;
+  Ctx c;
+  c.D = D; c.H = a.H; c.bf16 = a.bf16_products; c.st = a.stream;
+  static thread_local Kept kept;
+  if ((rc = open_buffers(c, &kept, wk, a.n_blocks, a.n_spatial, a.n_temporal, a.scratch, a.scratch_bytes, a.kept, a.kept_bytes)))
+    return rc;
+  if (wk.S == 0) {
+    cudaMemcpyAsync(a.y, a.x, wk.R * D * sizeof(float), cudaMemcpyDeviceToDevice, a.stream);
+    return BNB_OK;
+  }
+  const float* cur = a.x;
+  int s = 0;
+  for (int blk = 0; blk < a.n_blocks; ++blk) {
+    for (int j = 0; j < a.n_spatial; ++j, ++s) {
+      float* out = s + 1 == wk.S ? a.y : kept.bound + (size_t)s * wk.R * D;
+      Ctx cs = c;
+      cs.b = kept.first[s];
+      spatial_fwd(cs, a.spatial[blk * a.n_spatial + j], cur, a.alive, a.bullets, out, wk.G, wk.NM);
+      cur = out;
+    }
+    for (int j = 0; j < a.n_temporal; ++j, ++s) {
+      float* out = s + 1 == wk.S ? a.y : kept.bound + (size_t)s * wk.R * D;
+      const int slot = blk * a.n_temporal + j;
+      const size_t hoff = (size_t)slot * wk.Rr * 4 * D;
+      Ctx cs = c, cf = c;
+      cs.b = kept.first[s];
+      cf.b = kept.second[s];
+      rc = temporal_fwd(cs, cf, a.temporal[slot], cur, a.hidden_in + hoff, a.done, out,
+                        a.hidden_out ? a.hidden_out + hoff : nullptr, wk.tgm);
+      if (rc) return rc;
+      cur = out;
+    }
+  }
+  return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
+}
+
+int trunk_sequence_bwd(const TrunkBwdArgs& a) {
+  Walk wk;
+  int rc = make_walk(wk, a.n_blocks, a.n_spatial, a.n_temporal, a.D, a.H, *a.batch, a.T, a.bullets);
+  if (rc) return rc;
+  if (wk.R == 0) return BNB_OK;
+  const int D = wk.D, S = wk.S, G = wk.G, NM = wk.NM;
+  const size_t R = wk.R, Rr = wk.Rr;
+  cudaStream_t st = a.stream;
+  Ctx c;
+  c.D = D; c.H = a.H; c.bf16 = a.bf16_products; c.st = st;
+  static thread_local Kept kept;
+  const bool have_fwd = a.kept != nullptr;
+  if ((rc = open_buffers(c, &kept, wk, a.n_blocks, a.n_spatial, a.n_temporal, a.scratch, a.scratch_bytes, a.kept, a.kept_bytes)))
+    return rc;
 
   if (S == 0) {
     cudaMemcpyAsync(a.dx, a.dy, R * D * sizeof(float), cudaMemcpyDeviceToDevice, st);
     return BNB_OK;
   }
 
-  // first pass: the input of every sublayer
-  const TemporalGeom tgm{T, B, NM, n_rec};
-  const float* cur = a.x;
+  // the input of every sublayer: kept by the training forward, or from a first pass here
   const float* inputs[256];
-  if (S > 256) return BNB_ERR_BAD_ARGUMENT;
-  int s = 0;
-  for (int blk = 0; blk < a.n_blocks; ++blk) {
-    for (int j = 0; j < a.n_spatial; ++j, ++s) {
-      inputs[s] = cur;
-      if (s + 1 == S) break;
-      float* out = c.b.bound + (size_t)s * R * D;
-      spatial_fwd(c, a.spatial[blk * a.n_spatial + j], cur, a.alive, a.bullets, out, G, NM);
-      cur = out;
-    }
-    for (int j = 0; j < a.n_temporal; ++j, ++s) {
-      inputs[s] = cur;
-      if (s + 1 == S) break;
-      float* out = c.b.bound + (size_t)s * R * D;
-      const int slot = blk * a.n_temporal + j;
-      int rc = temporal_fwd(c, a.temporal[slot], cur, a.hidden_in + (size_t)slot * Rr * 4 * D, a.done, out, tgm);
-      if (rc) return rc;
-      cur = out;
+  if (have_fwd) {
+    for (int s = 0; s < S; ++s) inputs[s] = s == 0 ? a.x : kept.bound + (size_t)(s - 1) * R * D;
+  } else {
+    const float* cur = a.x;
+    int s = 0;
+    for (int blk = 0; blk < a.n_blocks; ++blk) {
+      for (int j = 0; j < a.n_spatial; ++j, ++s) {
+        inputs[s] = cur;
+        if (s + 1 == S) break;
+        float* out = c.b.bound + (size_t)s * R * D;
+        spatial_fwd(c, a.spatial[blk * a.n_spatial + j], cur, a.alive, a.bullets, out, G, NM);
+        cur = out;
+      }
+      for (int j = 0; j < a.n_temporal; ++j, ++s) {
+        inputs[s] = cur;
+        if (s + 1 == S) break;
+        float* out = c.b.bound + (size_t)s * R * D;
+        const int slot = blk * a.n_temporal + j;
+        rc = temporal_fwd(c, c, a.temporal[slot], cur, a.hidden_in + (size_t)slot * Rr * 4 * D, a.done, out, nullptr, wk.tgm);
+        if (rc) return rc;
+        cur = out;
+      }
     }
   }
 
-  if (a.d_bullets && RB) cudaMemsetAsync(a.d_bullets, 0, RB * D * sizeof(float), st);
+  if (a.d_bullets && wk.RB) cudaMemsetAsync(a.d_bullets, 0, wk.RB * D * sizeof(float), st);
 
-  // second pass: sublayers in reverse
+  // sublayers in reverse
   const float* dcur = a.dy;
   for (int blk = a.n_blocks - 1; blk >= 0; --blk) {
     for (int j = a.n_temporal - 1; j >= 0; --j) {
-      s = blk * (a.n_spatial + a.n_temporal) + a.n_spatial + j;
+      const int s = blk * (a.n_spatial + a.n_temporal) + a.n_spatial + j;
       float* dout = s == 0 ? a.dx : c.b.ping[s & 1];
       const int slot = blk * a.n_temporal + j;
       const size_t hoff = (size_t)slot * Rr * 4 * D;
-      int rc = temporal_bwd(c, a.temporal[slot], a.d_temporal[slot], inputs[s], a.hidden_in + hoff,
-                            a.d_hidden_out ? a.d_hidden_out + hoff : nullptr, a.d_hidden_in ? a.d_hidden_in + hoff : nullptr,
-                            a.done, dcur, dout, tgm);
+      Ctx cs = c, cf = c;
+      if (have_fwd) {
+        cs.b = kept.first[s];
+        cf.b = kept.second[s];
+      }
+      rc = temporal_bwd(cs, cf, a.temporal[slot], a.d_temporal[slot], inputs[s], a.hidden_in + hoff,
+                        a.d_hidden_out ? a.d_hidden_out + hoff : nullptr, a.d_hidden_in ? a.d_hidden_in + hoff : nullptr,
+                        a.done, dcur, dout, wk.tgm, have_fwd);
       if (rc) return rc;
       dcur = dout;
     }
     for (int j = a.n_spatial - 1; j >= 0; --j) {
-      s = blk * (a.n_spatial + a.n_temporal) + j;
+      const int s = blk * (a.n_spatial + a.n_temporal) + j;
       float* dout = s == 0 ? a.dx : c.b.ping[s & 1];
       const int k = blk * a.n_spatial + j;
-      int rc = spatial_bwd(c, a.spatial[k], a.d_spatial[k], inputs[s], a.alive, a.bullets, a.d_bullets, dcur, dout, G, NM);
+      Ctx cs = c;
+      if (have_fwd) cs.b = kept.first[s];
+      rc = spatial_bwd(cs, a.spatial[k], a.d_spatial[k], inputs[s], a.alive, a.bullets, a.d_bullets, dcur, dout, G, NM,
+                       have_fwd);
       if (rc) return rc;
       dcur = dout;
     }

@@ -28,12 +28,39 @@ struct TrunkBwdArgs {
   float* d_bullets;
   void* scratch;
   size_t scratch_bytes;
+  void* kept;           // activations kept by trunk_sequence_fwd_train, or null: recompute
+  size_t kept_bytes;
+  cudaStream_t stream;
+};
+
+struct TrunkFwdTrainArgs {
+  const BnbSpatialWeights* spatial;
+  const BnbTemporalWeights* temporal;
+  int n_blocks, n_spatial, n_temporal, D, H;
+  const float* x;
+  const uint8_t* alive;
+  const BnbBullets* bullets;
+  const float* hidden_in;
+  const uint8_t* done;
+  const BnbBatch* batch;
+  int T;
+  bool bf16_products;
+  float* y;
+  float* hidden_out;
+  void* scratch;
+  size_t scratch_bytes;
+  void* kept;
+  size_t kept_bytes;
   cudaStream_t stream;
 };
 
 // Bytes of scratch trunk_sequence_bwd needs for this structure and batch.
 size_t scratch_bytes(int n_blocks, int n_spatial, int n_temporal, int D, const BnbBatch& b, int T, int bullets_per_env);
 
+// Bytes of the activations trunk_sequence_fwd_train keeps for the backward (0: unsupported geometry).
+size_t kept_bytes(int n_blocks, int n_spatial, int n_temporal, int D, int H, const BnbBatch& b, int T, int bullets_per_env);
+
+int trunk_sequence_fwd_train(const TrunkFwdTrainArgs& a);
 int trunk_sequence_bwd(const TrunkBwdArgs& a);
 
 }  // namespace grad

@@ -7,9 +7,11 @@ shape-only fake implementation; the real implementation below builds the ctypes 
 structs, looks up (or rebuilds) the tensor-core weight images, takes scratch from torch's
 allocator and launches on the current stream.  Nothing here synchronises.
 
-``trunk_forward`` carries an autograd formula (``trunk_backward`` -> ``bnb_trunk_sequence_bwd``, float32,
-environments of one size): a step or sequence through ``YemongBlock`` / ``YemongTrunk`` can be
-differentiated with respect to tokens, recurrent state, bullet tokens and parameters.  The
+``trunk_forward`` carries an autograd formula (``trunk_backward`` -> ``bnb_trunk_sequence_bwd``,
+environments of one size, recomputing activations); a call known to need gradients goes through
+``trunk_forward_train`` instead, which keeps its activations for the backward.  Either way a step or
+sequence through ``YemongBlock`` / ``YemongTrunk`` can be differentiated with respect to tokens,
+recurrent state, bullet tokens and parameters.  The
 single-sublayer operators are forward-only and their module methods refuse inputs that require grad.
 """
 
@@ -189,6 +191,7 @@ def _sublayer_lists(weights: List[Tensor], n_blocks: int, n_spatial: int, n_temp
 def trunk_backward(
     dy: Tensor,
     dhidden_out: Optional[Tensor],
+    kept: Optional[Tensor],
     x: Tensor,
     alive: Optional[Tensor],
     hidden: Tensor,
@@ -201,7 +204,9 @@ def trunk_backward(
     """Gradients of ``trunk_forward`` (environments of one size, no ``reset_env``) through
     ``bnb_trunk_sequence_bwd``: float32 tensors throughout; after a forward under bf16 autocast the
     Linear products round their operands to bfloat16, as the reference's backward does there.  Returns
-    [d x, d hidden, d bullets (empty without bullets), then one gradient per tensor of ``weights``]."""
+    [d x, d hidden, d bullets (empty without bullets), then one gradient per tensor of ``weights``].
+    ``kept``: the activations ``trunk_forward_train`` kept for this call (the backward consumes
+    them), or None: every sublayer's intermediates are recomputed."""
     dev = x.device
     D = x.shape[-1]
     n_blocks, n_spatial, n_temporal = geom[G_BLOCKS], geom[G_SPATIAL], geom[G_TEMPORAL]
@@ -228,25 +233,33 @@ def trunk_backward(
         bul = _capi.BulletArgs(bullets if n_cross > 0 else None, bullet_mask, T * batch.n_envs, D)
         dx = torch.empty_like(xin)
         dh = torch.zeros_like(hin)
-        dbul = torch.empty_like(bul.tokens) if bul.struct is not None else xin.new_empty(0)
+        dbul = torch.zeros_like(bul.tokens) if bul.struct is not None else xin.new_empty(0)
         nbytes = _capi.lib.bnb_trunk_bwd_scratch_bytes(n_blocks, n_spatial, n_temporal, D, batch, T, bul.per_env)
         scratch = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=dev)   # released after the call's stream work
         st = _capi.lib.bnb_trunk_sequence_bwd(
             sw, tw, sg, tg, n_blocks, n_spatial, n_temporal, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8), bul.arg,
             _capi.ptr(hin), _capi.ptr(done_u8), batch, T, _capi.BNB_BF16 if geom[G_PRECISION] == _capi.BNB_BF16 else _capi.BNB_FP32,
             dyin.data_ptr(), _capi.ptr(dho), dx.data_ptr(),
-            _capi.ptr(dh), _capi.ptr(dbul) if bul.struct is not None else None, scratch.data_ptr(), scratch.numel(),
-            _capi.stream_handle(dev),
+            _capi.ptr(dh), _capi.ptr(dbul) if bul.struct is not None else None, _capi.ptr(kept),
+            0 if kept is None else kept.numel(), scratch.data_ptr(), scratch.numel(), _capi.stream_handle(dev),
         )
     _capi.check("bnb_trunk_sequence_bwd", st)
     return [dx, dh, dbul, *grads]
 
 
 @trunk_backward.register_fake
-def _trunk_backward_fake(dy, dhidden_out, x, alive, hidden, done, bullets, bullet_mask, weights, geom):
+def _trunk_backward_fake(dy, dhidden_out, kept, x, alive, hidden, done, bullets, bullet_mask, weights, geom):
     dbul = x.new_empty(bullets.shape, dtype=torch.float32) if bullets is not None and geom[G_BULLET_CROSS] > 0 else x.new_empty(0, dtype=torch.float32)
     return [x.new_empty(x.shape, dtype=torch.float32), hidden.new_empty(hidden.shape, dtype=torch.float32), dbul,
             *[w.new_empty(w.shape, dtype=torch.float32) for w in weights]]
+
+
+def _shape_grads(out, x, hidden, bullets, weights):
+    dx, dh, dbul, dws = out[0], out[1], out[2], out[3:]
+    dx = dx.reshape(x.shape).to(x.dtype)
+    dh = dh.reshape(hidden.shape).to(hidden.dtype)
+    dbul = dbul.reshape(bullets.shape).to(bullets.dtype) if bullets is not None and dbul.numel() else None
+    return dx, dh, dbul, [g.to(w.dtype) for g, w in zip(dws, weights)]
 
 
 def _trunk_setup_context(ctx, inputs, output):
@@ -261,16 +274,119 @@ def _trunk_backward_formula(ctx, dy, dhidden_out):
     if ctx.unsupported:
         raise NotImplementedError(f"the CUDA trunk's backward does not cover {ctx.unsupported}; run that call under torch.no_grad()")
     x, alive, hidden, done, bullets, bullet_mask, *weights = ctx.saved_tensors
-    out = trunk_backward(dy, dhidden_out, x, alive, hidden, done, bullets, bullet_mask, list(weights), ctx.geom)
-    dx, dh, dbul, dws = out[0], out[1], out[2], out[3:]
-    dx = dx.reshape(x.shape).to(x.dtype)
-    dh = dh.reshape(hidden.shape).to(hidden.dtype)
-    dbul = dbul.reshape(bullets.shape).to(bullets.dtype) if bullets is not None and dbul.numel() else None
+    out = trunk_backward(dy, dhidden_out, None, x, alive, hidden, done, bullets, bullet_mask, list(weights), ctx.geom)
+    dx, dh, dbul, dws = _shape_grads(out, x, hidden, bullets, weights)
     # one entry per input; a list input takes a list of the same length
-    return dx, None, dh, None, None, dbul, None, [g.to(w.dtype) for g, w in zip(dws, weights)], [None] * ctx.n_offsets, None
+    return dx, None, dh, None, None, dbul, None, dws, [None] * ctx.n_offsets, None
 
 
 trunk_forward.register_autograd(_trunk_backward_formula, setup_context=_trunk_setup_context)
+
+
+@torch.library.custom_op("bnb_b200::trunk_forward_train", mutates_args=(), device_types="cuda")
+def trunk_forward_train(
+    x: Tensor,
+    alive: Optional[Tensor],
+    hidden: Tensor,
+    done: Optional[Tensor],
+    bullets: Optional[Tensor],
+    bullet_mask: Optional[Tensor],
+    weights: List[Tensor],
+    geom: List[int],
+) -> Tuple[Tensor, Tensor, Tensor]:
+    """``trunk_forward`` for a call that will be differentiated (environments of one size, no
+    ``reset_env``): ``bnb_trunk_sequence_fwd_train`` runs the trunk sublayer by sublayer and keeps
+    every sublayer's intermediates, as autograd does for the reference without grad_checkpoint;
+    the backward then skips its recomputation.  Returns (y, new hidden, kept activations); y is
+    float32, or bfloat16 for bfloat16 tokens."""
+    dev = x.device
+    D = x.shape[-1]
+    n_blocks, n_spatial, n_temporal = geom[G_BLOCKS], geom[G_SPATIAL], geom[G_TEMPORAL]
+    n_heads, n_cross, field_sub = geom[G_HEADS], geom[G_BULLET_CROSS], geom[G_FIELD_SUB]
+    T = max(1, geom[G_TIMESTEPS])
+    with torch.cuda.device(dev):
+        batch = _batch(geom, [])
+        xin, hin = _capi.f32c(x), _capi.f32c(hidden)
+        alive_u8, done_u8 = _capi.u8(alive), _capi.u8(done)
+        spatial, temporal = _sublayer_lists(weights, n_blocks, n_spatial, n_temporal, n_cross, field_sub)
+        sw = (_capi.SpatialWeights * max(1, len(spatial)))()
+        tw = (_capi.TemporalWeights * max(1, len(temporal)))()
+        for i, ts in enumerate(spatial):
+            sw[i] = spatial_struct_from(ts, dev)
+        for i, ts in enumerate(temporal):
+            tw[i] = temporal_struct_from(ts, dev)
+        bul = _capi.BulletArgs(bullets if n_cross > 0 else None, bullet_mask, T * batch.n_envs, D)
+        y = torch.empty_like(xin)
+        hout = torch.empty_like(hin)
+        kept = torch.empty(max(256, int(_capi.lib.bnb_trunk_kept_bytes(n_blocks, n_spatial, n_temporal, D, n_heads, batch, T,
+                                                                        bul.per_env))), dtype=torch.uint8, device=dev)
+        nbytes = _capi.lib.bnb_trunk_bwd_scratch_bytes(n_blocks, n_spatial, n_temporal, D, batch, T, bul.per_env)
+        scratch = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=dev)
+        st = _capi.lib.bnb_trunk_sequence_fwd_train(
+            sw, tw, n_blocks, n_spatial, n_temporal, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8), bul.arg, y.data_ptr(),
+            _capi.ptr(hin), _capi.ptr(hout), _capi.ptr(done_u8), batch, T,
+            _capi.BNB_BF16 if geom[G_PRECISION] == _capi.BNB_BF16 else _capi.BNB_FP32, kept.data_ptr(), kept.numel(),
+            scratch.data_ptr(), scratch.numel(), _capi.stream_handle(dev),
+        )
+    _capi.check("bnb_trunk_sequence_fwd_train", st)
+    if x.dtype == torch.bfloat16:
+        y = y.to(torch.bfloat16)
+    return y, hout, kept
+
+
+@trunk_forward_train.register_fake
+def _trunk_forward_train_fake(x, alive, hidden, done, bullets, bullet_mask, weights, geom):
+    out_dtype = torch.bfloat16 if x.dtype == torch.bfloat16 else torch.float32
+    return (x.new_empty(x.shape, dtype=out_dtype), hidden.new_empty(hidden.shape, dtype=torch.float32),
+            x.new_empty(256, dtype=torch.uint8))
+
+
+def _train_setup_context(ctx, inputs, output):
+    x, alive, hidden, done, bullets, bullet_mask, weights, geom = inputs
+    ctx.geom = list(geom)
+    ctx.consumed = False
+    ctx.mark_non_differentiable(output[2])
+    # autograd would otherwise materialise a zero "gradient" the size of the kept activations
+    ctx.set_materialize_grads(False)
+    ctx.save_for_backward(x, alive, hidden, done, bullets, bullet_mask, output[2], *weights)
+
+
+def _train_backward_formula(ctx, dy, dhidden_out, _dkept):
+    if ctx.consumed:
+        raise RuntimeError("the kept activations of this trunk call were consumed by an earlier backward; for a second "
+                           "backward through the same graph set BNB_GRAD_MODE=recompute")
+    ctx.consumed = True
+    x, alive, hidden, done, bullets, bullet_mask, kept, *weights = ctx.saved_tensors
+    if dy is None:
+        dy = torch.zeros_like(x, dtype=torch.float32)
+    out = trunk_backward(dy, dhidden_out, kept, x, alive, hidden, done, bullets, bullet_mask, list(weights), ctx.geom)
+    dx, dh, dbul, dws = _shape_grads(out, x, hidden, bullets, weights)
+    return dx, None, dh, None, dbul, None, dws, None
+
+
+trunk_forward_train.register_autograd(_train_backward_formula, setup_context=_train_setup_context)
+
+
+def keep_activations(dev: torch.device, geom: List[int], d_model: int, n_bullets: int) -> bool:
+    """Whether a differentiated call keeps its activations (faster) or lets the backward recompute
+    them (about a sixth of the memory): BNB_GRAD_MODE=keep | recompute decides; otherwise keep when
+    the kept buffer plus the backward's scratch fit in 70 % of the memory that is free or cached."""
+    mode = os.environ.get("BNB_GRAD_MODE", "")
+    if mode == "recompute":
+        return False
+    with torch.cuda.device(dev):
+        batch = _batch(geom, [])
+        T = max(1, geom[G_TIMESTEPS])
+        need = _capi.lib.bnb_trunk_kept_bytes(geom[G_BLOCKS], geom[G_SPATIAL], geom[G_TEMPORAL], d_model, geom[G_HEADS], batch, T,
+                                              n_bullets)
+        if need == 0:
+            return False
+        if mode == "keep":
+            return True
+        need += _capi.lib.bnb_trunk_bwd_scratch_bytes(geom[G_BLOCKS], geom[G_SPATIAL], geom[G_TEMPORAL], d_model, batch, T, n_bullets)
+        free, _ = torch.cuda.mem_get_info(dev)
+        cached = torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)
+    return need <= 0.7 * (free + cached)
 
 
 @torch.library.custom_op("bnb_b200::spatial_forward", mutates_args=(), device_types="cuda")

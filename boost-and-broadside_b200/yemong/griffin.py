@@ -209,6 +209,14 @@ def run_trunk(
             weights += temporal_tensors(tp, blk.field_sub[j] if has_fields else None)
     geom = [n_blocks, n_spatial, n_temporal, n_heads, n_cross, 1 if has_fields else 0, *batch_geom,
             0 if timesteps is None else timesteps, engine, _capi.current_precision(x.device)]
+    if (torch.is_grad_enabled() and not offsets and reset_env is None
+            and (x.requires_grad or hidden.requires_grad or (bullets is not None and bullets.requires_grad)
+                 or any(w.requires_grad for w in weights))
+            and _ops.keep_activations(x.device, geom, x.shape[-1], bullets.shape[1] if n_cross and bullets is not None else 0)):
+        # a call that will be differentiated: the forward that keeps its activations for the backward
+        y, nh, _ = _ops.trunk_forward_train(x, alive, hidden, done, bullets if n_cross else None,
+                                            bullet_mask if n_cross else None, weights, geom)
+        return y, nh
     return _ops.trunk_forward(x, alive, hidden, done, reset_env, bullets if n_cross else None,
                               bullet_mask if n_cross else None, weights, offsets or [], geom)
 

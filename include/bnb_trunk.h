@@ -371,6 +371,8 @@ size_t bnb_trunk_bwd_scratch_bytes(int n_blocks, int n_spatial, int n_temporal, 
  *   d_bullets (T * n_envs, NB, D) or NULL: written (zeroed here, then accumulated over the sublayers
  *   that read bullets).
  *   d_spatial / d_temporal: one entry per sublayer, indexed like spatial / temporal; accumulated into.
+ *   kept / kept_bytes: the buffer bnb_trunk_sequence_fwd_train filled for this call, or NULL / 0:
+ *   the backward then recomputes every sublayer's intermediates itself.
  * The attention gradient follows the fused attention kernels behind F.scaled_dot_product_attention
  * (probabilities recomputed from the float32 log-sum-exp); d_model a multiple of 32 up to 128,
  * head width 8, 16 or 32.  Weight gradients reduce with float32 atomics: run-to-run bits may differ
@@ -381,7 +383,29 @@ int bnb_trunk_sequence_bwd(const BnbSpatialWeights* spatial, const BnbTemporalWe
                            const float* x, const uint8_t* alive, const BnbBullets* bullets,
                            const float* hidden_in, const uint8_t* done, const BnbBatch* batch, int timesteps,
                            int precision, const float* dy, const float* d_hidden_out, float* dx, float* d_hidden_in,
-                           float* d_bullets, void* scratch, size_t scratch_bytes, void* stream);
+                           float* d_bullets, void* kept, size_t kept_bytes, void* scratch, size_t scratch_bytes,
+                           void* stream);
+
+/* Bytes of activations bnb_trunk_sequence_fwd_train keeps for the backward (about 60 KB per token row
+ * for two blocks of two spatial and one temporal sublayer at d_model 128); 0 for a geometry the
+ * backward does not cover. */
+size_t bnb_trunk_kept_bytes(int n_blocks, int n_spatial, int n_temporal, int d_model, int n_heads,
+                            const BnbBatch* batch, int timesteps, int bullets_per_env);
+
+/* The sequence forward for a call that will be differentiated: y and hidden_out as
+ * bnb_trunk_sequence computes them (same arithmetic contract per precision: float32, or bfloat16
+ * operands in every Linear product), run sublayer by sublayer with each sublayer's intermediates
+ * written to `kept`, so that bnb_trunk_sequence_bwd given the same `kept` skips its recomputation.
+ * Replaces: the forward half of evaluate_actions' trunk loop without grad_checkpoint
+ * (models/yemong/policy.py:422-478), where autograd stores the activations.
+ * `kept` is consumed by the backward (it overwrites parts of it): one backward per forward.
+ * scratch: bnb_trunk_bwd_scratch_bytes. */
+int bnb_trunk_sequence_fwd_train(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal,
+                                 int n_blocks, int n_spatial, int n_temporal, int d_model, int n_heads,
+                                 const float* x, const uint8_t* alive, const BnbBullets* bullets, float* y,
+                                 const float* hidden_in, float* hidden_out, const uint8_t* done,
+                                 const BnbBatch* batch, int timesteps, int precision, void* kept,
+                                 size_t kept_bytes, void* scratch, size_t scratch_bytes, void* stream);
 
 /* One head of the policy: Linear + b -> RMSNorm -> GELU(erf) -> Linear + b on the trunk's output.
  * Replaces: YemongPolicy.action_head, .value_head_local, .value_head_win and NextStateHead.net,

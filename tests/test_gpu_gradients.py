@@ -44,8 +44,16 @@ def run_backward(trunk, g, mode):
     return x.grad, hidden.grad, None if bullets is None else bullets.grad, named
 
 
+@pytest.fixture(params=["keep", "recompute"])
+def grad_mode(request, monkeypatch):
+    """Both ways a differentiated call can run: the training forward that keeps its activations
+    (bnb_trunk_sequence_fwd_train), and the plain forward whose backward recomputes them."""
+    monkeypatch.setenv("BNB_GRAD_MODE", request.param)
+    return request.param
+
+
 @pytest.mark.parametrize("tag", CASES)
-def test_gradients_match_the_reference_autograd_fp32(tag):
+def test_gradients_match_the_reference_autograd_fp32(tag, grad_mode):
     g = golden("grad_trunk_seq_" + tag)
     trunk = build_trunk(g["dims"]).to(DEV).train()
     dx, dh0, db, named = run_backward(trunk, g, "fp32")
@@ -60,11 +68,11 @@ def test_gradients_match_the_reference_autograd_fp32(tag):
                 D = int(g["dims"][0])
                 named.setdefault(name, torch.zeros((2 * D, D) if "kv_bullet" in name else (D,)))
     worst = grad_fixture_compare(g, "fp32", dx, dh0, db, named, tol=1e-4)
-    print(f"gradients {tag} fp32: worst normalised error {worst[1]:.2e} ({worst[0]})")
+    print(f"gradients {tag} fp32 ({grad_mode}): worst normalised error {worst[1]:.2e} ({worst[0]})")
 
 
 @pytest.mark.parametrize("tag", CASES[:3])
-def test_gradients_under_bf16_autocast_stay_near_the_reference_bf16_autograd(tag):
+def test_gradients_under_bf16_autocast_stay_near_the_reference_bf16_autograd(tag, grad_mode):
     g = golden("grad_trunk_seq_" + tag)
     trunk = build_trunk(g["dims"]).to(DEV).train()
     dx, dh0, db, named = run_backward(trunk, g, "bf16")
@@ -76,7 +84,7 @@ def test_gradients_under_bf16_autocast_stay_near_the_reference_bf16_autograd(tag
                 named[name] = torch.zeros((2 * D, D) if "kv_bullet" in name else (D, D) if "field_sub" in name else (D,))
     assert dx.dtype == torch.float32
     worst = grad_fixture_compare(g, "bf16", dx, dh0, db, named, tol=3e-2)
-    print(f"gradients {tag} bf16 forward: worst normalised error vs the reference's bf16 autograd {worst[1]:.2e} ({worst[0]})")
+    print(f"gradients {tag} bf16 forward ({grad_mode}): worst normalised error vs the reference's bf16 autograd {worst[1]:.2e} ({worst[0]})")
 
 
 ORACLE_CASES = [
@@ -92,7 +100,7 @@ ORACLE_CASES = [
 
 
 @pytest.mark.parametrize("dims,T,B,NB", ORACLE_CASES)
-def test_gradients_match_the_oracle_on_seeded_cases(dims, T, B, NB):
+def test_gradients_match_the_oracle_on_seeded_cases(dims, T, B, NB, grad_mode):
     D, H, _, _, nt, _, N, M = dims
     gen = torch.Generator().manual_seed(T * 100 + B)
     trunk = build_trunk(dims).to(DEV).train()
@@ -193,7 +201,7 @@ def test_backward_of_unsupported_calls_raises_instead_of_dropping_gradients():
 
 @pytest.mark.skipif(not ref_runner.available(), reason="oracle/_ref has not been built")
 @pytest.mark.parametrize("mode", ["fp32", "bf16"])
-def test_reference_policy_backward_through_swapped_blocks(mode):
+def test_reference_policy_backward_through_swapped_blocks(mode, grad_mode):
     """evaluate_actions' trunk loop and heads (policy.py:422-490) on the reference's own policy,
     stock and with this package's blocks, same loss, gradients of every parameter compared."""
     from tests.test_gpu_reference_policy import build_policies, inputs, sequence_from_tokens
@@ -255,3 +263,35 @@ def test_recompute_backward_matches_stored_activation_autograd():
     odx, _, _, og = O.trunk_sequence_grad(x, alive, hidden, None, P, 4, torch.ones(T, B, 8, 128), None)
     assert norm_err(g0, og[0]["temporal.0.linear1.weight"]) <= 1e-4
     assert norm_err(dx, odx) <= 1e-4
+
+
+@pytest.mark.parametrize("mode", ["fp32", "bf16"])
+@pytest.mark.parametrize("name", ["trunk_seq_d128_t6_8s0f", "trunk_seq_d128_t5_4s2f", "trunk_seq_d64_t7_3s2f",
+                                  "bullets_trunk_seq_d128_t4_4s2f"])
+def test_training_forward_matches_the_forward_fixtures(name, mode, monkeypatch):
+    """The forward a differentiated call runs (bnb_trunk_sequence_fwd_train) against the same
+    reference outputs the inference forward is held to: y and the final state."""
+    from tests.helpers import assert_close
+
+    monkeypatch.setenv("BNB_GRAD_MODE", "keep")
+    g = golden(name)
+    trunk = build_trunk(g["dims"], g).to(DEV).train()
+    ctx = torch.autocast(DEV, dtype=torch.bfloat16) if mode == "bf16" else torch.autocast(DEV, enabled=False)
+    bullets = g["bullets"].to(DEV) if "bullets" in g else None
+    mask = g["bullet_mask"].to(DEV) if "bullet_mask" in g else None
+    with ctx:
+        y, nh = trunk.sequence(g["x"].to(DEV), g["alive"].to(DEV), g["hidden"].to(DEV), g["done"].to(DEV),
+                               bullets=bullets, bullet_mask=mask)
+    assert y.requires_grad
+    assert_close(y, g["y_" + mode], mode, name + " y")
+    assert_close(nh, g["hidden_" + mode], mode, name + " hidden")
+
+
+def test_a_second_backward_through_kept_activations_is_refused(monkeypatch):
+    monkeypatch.setenv("BNB_GRAD_MODE", "keep")
+    trunk = build_trunk([128, 4, 1, 1, 1, 0, 2, 0]).to(DEV).train()
+    x = torch.randn(2, 3, 2, 128, device=DEV, requires_grad=True)
+    y, _ = trunk.sequence(x, None, torch.zeros(1, 6, 512, device=DEV))
+    y.sum().backward(retain_graph=True)
+    with pytest.raises(RuntimeError, match="consumed"):
+        y.sum().backward()
