@@ -86,11 +86,22 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // tf32 numbers and three m16n8k8 MMAs give the float32 product.  BF16 set: operands are rounded to
 // bfloat16 on the way into the m16n8k16 MMA (what autocast does to the reference's backward
 // products), accumulation in float32 either way.
+// 16-byte asynchronous copy into shared memory; bytes = 0 fills the destination with zeros.
+__device__ __forceinline__ void cp_async16(float* dst, const float* src, int bytes) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+constexpr int GEMM_STAGES = 2;
+constexpr size_t GEMM_SMEM = (size_t)GEMM_STAGES * 2 * TILE_FLOATS * sizeof(float);   // 80 KB: two CTAs per SM
+
 template <bool A_KC, bool B_KC, bool BF16>
-__global__ void __launch_bounds__(GT) k_gemm(GemmArgs g) {
+__global__ void __launch_bounds__(GT, BF16 ? 2 : 1) k_gemm(GemmArgs g) {
   constexpr int LDK = Strides<BF16>::LDK, LDR = Strides<BF16>::LDR;
-  __shared__ __align__(16) float As[TILE_FLOATS];
-  __shared__ __align__(16) float Bs[TILE_FLOATS];
+  extern __shared__ __align__(16) float gemm_smem[];
   static_assert(TILE_FLOATS >= BM * LDK && TILE_FLOATS >= BK * LDR, "either orientation fits the tile buffer");
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, t = lane & 3;
   const int wm = (warp & 1) * 64, wn = (warp >> 1) * 32;
@@ -105,40 +116,55 @@ __global__ void __launch_bounds__(GT) k_gemm(GemmArgs g) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) c[i][j][e] = 0.f;
 
-  for (int k0 = kbeg; k0 < kend; k0 += BK) {
+  // one K slice of both operands into a stage; out-of-range pieces are zero-filled
+  auto load_stage = [&](int stage, int k0) {
+    float* As = gemm_smem + (size_t)stage * 2 * TILE_FLOATS;
+    float* Bs = As + TILE_FLOATS;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int idx = tid + i * GT;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
       if constexpr (A_KC) {
         const int row = idx >> 3, c4 = (idx & 7) * 4;
         const int gm = m0 + row, gk = k0 + c4;
-        if (gm < g.M && gk < kend) v = *reinterpret_cast<const float4*>(g.A + (size_t)gm * g.lda + gk);
-        *reinterpret_cast<float4*>(As + row * LDK + c4) = v;
+        const bool ok = gm < g.M && gk < kend;
+        cp_async16(As + row * LDK + c4, ok ? g.A + (size_t)gm * g.lda + gk : g.A, ok ? 16 : 0);
       } else {
         const int kk = idx >> 5, c4 = (idx & 31) * 4;
         const int gk = k0 + kk, gm = m0 + c4;
-        if (gk < kend && gm < g.M) v = *reinterpret_cast<const float4*>(g.A + (size_t)gk * g.lda + gm);
-        *reinterpret_cast<float4*>(As + kk * LDR + c4) = v;
+        const bool ok = gk < kend && gm < g.M;
+        cp_async16(As + kk * LDR + c4, ok ? g.A + (size_t)gk * g.lda + gm : g.A, ok ? 16 : 0);
       }
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int idx = tid + i * GT;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
       if constexpr (B_KC) {
         const int row = idx >> 3, c4 = (idx & 7) * 4;
         const int gn = n0 + row, gk = k0 + c4;
-        if (gn < g.N && gk < kend) v = *reinterpret_cast<const float4*>(g.B + (size_t)gn * g.ldb + gk);
-        *reinterpret_cast<float4*>(Bs + row * LDK + c4) = v;
+        const bool ok = gn < g.N && gk < kend;
+        cp_async16(Bs + row * LDK + c4, ok ? g.B + (size_t)gn * g.ldb + gk : g.B, ok ? 16 : 0);
       } else {
         const int kk = idx >> 5, c4 = (idx & 31) * 4;
         const int gk = k0 + kk, gn = n0 + c4;
-        if (gk < kend && gn < g.N) v = *reinterpret_cast<const float4*>(g.B + (size_t)gk * g.ldb + gn);
-        *reinterpret_cast<float4*>(Bs + kk * LDR + c4) = v;
+        const bool ok = gk < kend && gn < g.N;
+        cp_async16(Bs + kk * LDR + c4, ok ? g.B + (size_t)gk * g.ldb + gn : g.B, ok ? 16 : 0);
       }
     }
+    cp_async_commit();
+  };
+
+  const int n_it = (kend - kbeg + BK - 1) / BK;
+  if (n_it > 0) load_stage(0, kbeg);
+  for (int it = 0; it < n_it; ++it) {
+    if (it + 1 < n_it) {
+      load_stage((it + 1) & 1, kbeg + (it + 1) * BK);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
     __syncthreads();
+    const float* As = gemm_smem + (size_t)(it & 1) * 2 * TILE_FLOATS;
+    const float* Bs = As + TILE_FLOATS;
     if constexpr (BF16) {
 #pragma unroll
       for (int kk = 0; kk < BK; kk += 16) {
@@ -232,19 +258,26 @@ __global__ void __launch_bounds__(GT) k_gemm(GemmArgs g) {
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int row = m0 + wm + mt * 16 + gq + (e >> 1) * 8;
-        const int col = n0 + wn + nt * 8 + 2 * t + (e & 1);
+      for (int half = 0; half < 2; ++half) {
+        const int row = m0 + wm + mt * 16 + gq + half * 8;
+        const int col = n0 + wn + nt * 8 + 2 * t;   // even; N is even, so col + 1 < N whenever col < N
         if (row < g.M && col < g.N) {
-          float v = c[mt][nt][e];
+          float v0 = c[mt][nt][2 * half], v1 = c[mt][nt][2 * half + 1];
           float* cp = g.C + (size_t)row * g.ldc + col;
           if (g.atomic) {
-            atomicAdd(cp, v);
+            atomicAdd(cp, v0);
+            atomicAdd(cp + 1, v1);
           } else {
-            if (g.bias) v += g.bias[col];
-            if (g.R) v += g.R[(size_t)row * g.ldr + col];
-            if (g.beta) v += *cp;
-            *cp = v;
+            if (g.bias) { v0 += g.bias[col]; v1 += g.bias[col + 1]; }
+            if (g.R) {
+              const float2 r = *reinterpret_cast<const float2*>(g.R + (size_t)row * g.ldr + col);
+              v0 += r.x; v1 += r.y;
+            }
+            if (g.beta) {
+              const float2 o = *reinterpret_cast<const float2*>(cp);
+              v0 += o.x; v1 += o.y;
+            }
+            *reinterpret_cast<float2*>(cp) = make_float2(v0, v1);
           }
         }
       }
@@ -255,11 +288,19 @@ enum GemmMode { NT, NN, TN };
 // NT: C (M, N)  = A (M, K) . B (N, K)^T      y = x W^T
 // NN: C (M, N)  = A (M, K) . B (K, N)        dx = dy W
 // TN: C (M, N) += A (K, M)^T . B (K, N)      dW += dy^T x   (split over K, atomics)
+template <bool A_KC, bool B_KC, bool BF16>
+void launch_gemm_t(const GemmArgs& g, dim3 grid, cudaStream_t st) {
+  static const bool opted =
+      cudaFuncSetAttribute(k_gemm<A_KC, B_KC, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM) == cudaSuccess;
+  (void)opted;
+  k_gemm<A_KC, B_KC, BF16><<<grid, GT, GEMM_SMEM, st>>>(g);
+}
+
 template <bool BF16>
 void launch_gemm(GemmMode mode, const GemmArgs& g, dim3 grid, cudaStream_t st) {
-  if (mode == TN) k_gemm<false, false, BF16><<<grid, GT, 0, st>>>(g);
-  else if (mode == NT) k_gemm<true, true, BF16><<<grid, GT, 0, st>>>(g);
-  else k_gemm<true, false, BF16><<<grid, GT, 0, st>>>(g);
+  if (mode == TN) launch_gemm_t<false, false, BF16>(g, grid, st);
+  else if (mode == NT) launch_gemm_t<true, true, BF16>(g, grid, st);
+  else launch_gemm_t<true, false, BF16>(g, grid, st);
 }
 
 void gemm(GemmMode mode, const float* A, int lda, const float* B, int ldb, float* C, int ldc, int M, int N, int K,
