@@ -506,19 +506,23 @@ __device__ __forceinline__ void attend(const float (&q)[DH], const float* __rest
 template <int DH>
 __global__ void __launch_bounds__(128) k_attn_fwd(const float* __restrict__ qkv, const uint8_t* __restrict__ alive,
                                                   float* __restrict__ o, int NM, int D, int H,
-                                                  const float* __restrict__ kvb, const uint8_t* __restrict__ bactive, int nb) {
-  const size_t grp = blockIdx.x;
-  const size_t tok0 = grp * NM;
+                                                  const float* __restrict__ kvb, const uint8_t* __restrict__ bactive, int nb,
+                                                  int G, int groups_per_block) {
   const float scale = rsqrtf((float)DH);
-  float gate = 1.f;
-  const uint8_t* bmask = nullptr;
-  if (kvb && bactive) {
-    bmask = bactive + grp * nb;
-    int any = 0;
-    for (int j = 0; j < nb; ++j) any |= bmask[j];
-    gate = any ? 1.f : 0.f;
-  }
-  for (int p = threadIdx.x; p < NM * H; p += blockDim.x) {
+  const int per_group = NM * H;
+  for (int pp = threadIdx.x; pp < groups_per_block * per_group; pp += blockDim.x) {
+    const int gl = pp / per_group, p = pp - gl * per_group;
+    const size_t grp = (size_t)blockIdx.x * groups_per_block + gl;
+    if (grp >= (size_t)G) break;
+    const size_t tok0 = grp * NM;
+    float gate = 1.f;
+    const uint8_t* bmask = nullptr;
+    if (kvb && bactive) {
+      bmask = bactive + grp * nb;
+      int any = 0;
+      for (int j = 0; j < nb; ++j) any |= bmask[j];
+      gate = any ? 1.f : 0.f;
+    }
     const int qi = p / H, h = p - qi * H;
     const float* qp = qkv + (tok0 + qi) * 3 * D + h * DH;
     float q[DH], acc[DH], accb[DH];
@@ -653,6 +657,96 @@ __global__ void __launch_bounds__(128) k_attn_bwd(AttnBwdArgs a) {
     float* kp = a.dkv + (grp * nk + j) * a.lddkv + h * dh + d;
     kp[0] = dKs[idx];
     kp[a.dvoff] = dVs[idx];
+  }
+}
+
+// The same gradient for small environments (at most 32 queries and 32 keys, head width 32): one
+// warp per (group, head), lane j owns key j -- its d k and d v accumulate in registers, the keys
+// and values of the group sit in the warp's slice of shared memory.
+constexpr int SMALL_WARPS = 4;
+__global__ void __launch_bounds__(32 * SMALL_WARPS) k_attn_bwd_small(AttnBwdArgs a, int n_pairs, int H) {
+  constexpr int DH = 32, LDS = DH + 1;
+  __shared__ float sK[SMALL_WARPS][32 * LDS], sV[SMALL_WARPS][32 * LDS], sDs[SMALL_WARPS][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pair = blockIdx.x * SMALL_WARPS + warp;
+  if (pair >= n_pairs) return;
+  const size_t grp = pair / H;
+  const int h = pair - (int)grp * H;
+  const int nk = a.nk, nq = a.nq;
+  float* Ks = sK[warp];
+  float* Vs = sV[warp];
+  float* ds_s = sDs[warp];
+  const uint8_t* mask = a.mask ? a.mask + grp * nk : nullptr;
+  for (int j = 0; j < nk; ++j) {   // lane = channel: coalesced rows
+    const float* kp = a.kv + (grp * nk + j) * a.ldkv + h * DH + lane;
+    Ks[j * LDS + lane] = kp[0];
+    Vs[j * LDS + lane] = kp[a.voff];
+  }
+  bool open = true;
+  bool live = lane < nk;
+  bool dead_key = false;
+  if (mask) {
+    const int mine = live ? mask[lane] : 0;
+    dead_key = live && !mine;
+    if (a.gate_by_mask) open = __any_sync(0xffffffffu, mine != 0);
+  }
+  __syncwarp();
+  float dk[DH], dv[DH];
+#pragma unroll
+  for (int d = 0; d < DH; ++d) dk[d] = dv[d] = 0.f;
+  if (open) {
+    for (int i = 0; i < nq; ++i) {
+      const size_t qrow = grp * nq + i;
+      const float4* qp = reinterpret_cast<const float4*>(a.q + qrow * a.ldq + h * DH);
+      const float4* gp = reinterpret_cast<const float4*>(a.d_o + qrow * a.ldo + h * DH);
+      float q[DH], go[DH];
+#pragma unroll
+      for (int d4 = 0; d4 < DH / 4; ++d4) {   // every lane reads the same row: one transaction each
+        const float4 v = qp[d4], w = gp[d4];
+        q[4 * d4] = v.x; q[4 * d4 + 1] = v.y; q[4 * d4 + 2] = v.z; q[4 * d4 + 3] = v.w;
+        go[4 * d4] = w.x; go[4 * d4 + 1] = w.y; go[4 * d4 + 2] = w.z; go[4 * d4 + 3] = w.w;
+      }
+      float sc = 0.f, dp = 0.f;
+      if (live) {
+#pragma unroll
+        for (int d = 0; d < DH; ++d) {
+          sc = fmaf(q[d], Ks[lane * LDS + d], sc);
+          dp = fmaf(go[d], Vs[lane * LDS + d], dp);
+        }
+        sc *= a.scale;
+        if (dead_key) sc = kMaskedScore;
+      }
+      const float mx = warp_max(live ? sc : -INFINITY);
+      const float e = live ? expf(sc - mx) : 0.f;
+      const float l = warp_sum(e);
+      const float lse = mx + logf(l);
+      const float delta = warp_sum(e / l * dp);          // <d out, out>
+      const float p = live ? expf(sc - lse) : 0.f;
+      const float ds = p * (dp - delta) * a.scale;
+      ds_s[lane] = ds;
+#pragma unroll
+      for (int d = 0; d < DH; ++d) {
+        dk[d] = fmaf(ds, q[d], dk[d]);
+        dv[d] = fmaf(p, go[d], dv[d]);
+      }
+      __syncwarp();
+      float dq = 0.f;                                    // lane = channel
+      for (int j = 0; j < nk; ++j) dq = fmaf(ds_s[j], Ks[j * LDS + lane], dq);
+      float* dqp = a.dq + qrow * a.lddq + h * DH + lane;
+      *dqp = a.dq_accumulate ? *dqp + dq : dq;
+      __syncwarp();
+    }
+  } else if (!a.dq_accumulate) {
+    for (int i = 0; i < nq; ++i) a.dq[(grp * nq + i) * a.lddq + h * DH + lane] = 0.f;
+  }
+  if (live) {
+    float4* kp = reinterpret_cast<float4*>(a.dkv + (grp * nk + lane) * a.lddkv + h * DH);
+    float4* vp = reinterpret_cast<float4*>(a.dkv + (grp * nk + lane) * a.lddkv + h * DH + a.dvoff);
+#pragma unroll
+    for (int d4 = 0; d4 < DH / 4; ++d4) {
+      kp[d4] = make_float4(dk[4 * d4], dk[4 * d4 + 1], dk[4 * d4 + 2], dk[4 * d4 + 3]);
+      vp[d4] = make_float4(dv[4 * d4], dv[4 * d4 + 1], dv[4 * d4 + 2], dv[4 * d4 + 3]);
+    }
   }
 }
 
@@ -934,7 +1028,7 @@ void rmsnorm_bwd(const Ctx& c, const float* x, const float* g, const float* inv,
                  float* dx, float* dg, size_t rows) {
   if (!rows) return;
   count_launch();
-  k_rmsnorm_bwd<<<blocks_for(rows, 64, 148 * 2), 256, 0, c.st>>>(x, g, inv, dn, dres, dx, dg, (int)rows, c.D);
+  k_rmsnorm_bwd<<<blocks_for(rows, 64, 148 * 8), 256, 0, c.st>>>(x, g, inv, dn, dres, dx, dg, (int)rows, c.D);
 }
 void gelu_mul_fwd(const Ctx& c, const float* g, const float* u, float* h, size_t n) {
   if (!n) return;
@@ -989,7 +1083,9 @@ template <int DH>
 void attn_fwd_t(const Ctx& c, const float* qkv, const uint8_t* alive, float* o, int G, int NM, const float* kvb,
                 const uint8_t* bactive, int nb) {
   count_launch();
-  k_attn_fwd<DH><<<G, 128, 0, c.st>>>(qkv, alive, o, NM, c.D, c.H, kvb, bactive, nb);
+  const int per_group = NM * c.H;
+  const int gpb = per_group >= 128 ? 1 : 128 / per_group;   // small environments share a block
+  k_attn_fwd<DH><<<(G + gpb - 1) / gpb, 128, 0, c.st>>>(qkv, alive, o, NM, c.D, c.H, kvb, bactive, nb, G, gpb);
 }
 void attn_fwd(const Ctx& c, const float* qkv, const uint8_t* alive, float* o, int G, int NM, const float* kvb,
               const uint8_t* bactive, int nb) {
@@ -1002,6 +1098,12 @@ void attn_fwd(const Ctx& c, const float* qkv, const uint8_t* alive, float* o, in
 }
 int attn_bwd(const Ctx& c, const AttnBwdArgs& a, int G) {
   if (!G) return BNB_OK;
+  if (a.dh == 32 && a.nk <= 32 && a.nq <= 32) {
+    const int n_pairs = G * c.H;
+    count_launch();
+    k_attn_bwd_small<<<(n_pairs + SMALL_WARPS - 1) / SMALL_WARPS, 32 * SMALL_WARPS, 0, c.st>>>(a, n_pairs, c.H);
+    return BNB_OK;
+  }
   const size_t sm = attn_bwd_smem(a.nk, a.dh);
   if (sm > 200 * 1024) return BNB_ERR_TOO_MANY_TOKENS;
   if (cudaFuncSetAttribute(k_attn_bwd, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm) != cudaSuccess)
