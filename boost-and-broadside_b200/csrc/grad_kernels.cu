@@ -283,6 +283,148 @@ __global__ void __launch_bounds__(GT, BF16 ? 2 : 1) k_gemm(GemmArgs g) {
       }
 }
 
+// The bf16-operand products: the same tiling, but the operands are converted to bfloat16 once, on
+// their way from global memory (through registers) into shared memory, and the fragments come out
+// of shared memory with ldmatrix (transposing for the [k][row] orientations), so the inner loop is
+// six ldmatrix and sixteen MMAs per 16-wide k step.  Global loads of the next K slice are in flight
+// while the current one is multiplied.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const __nv_bfloat16* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const __nv_bfloat16* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+
+constexpr int LDKH = BK + 8;     // bf16 per row of a [row][k] tile: 80 bytes, ldmatrix rows fall in distinct bank groups
+constexpr int LDRH = 128 + 8;    // bf16 per row of a [k][row] tile: 272 bytes, likewise
+constexpr int TILE_H = BM * LDKH;
+
+template <bool A_KC, bool B_KC>
+__global__ void __launch_bounds__(GT, 2) k_gemm_bf16(GemmArgs g) {
+  static_assert(TILE_H >= BK * LDRH, "either orientation fits the tile buffer");
+  __shared__ __align__(16) __nv_bfloat16 sA[2][TILE_H];
+  __shared__ __align__(16) __nv_bfloat16 sB[2][TILE_H];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, t = lane & 3;
+  const int wm = (warp & 1) * 64, wn = (warp >> 1) * 32;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int kbeg = blockIdx.z * g.k_per_split;
+  const int kend = min(g.K, kbeg + g.k_per_split);
+  float c[4][4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) c[i][j][e] = 0.f;
+
+  float4 pa[4], pb[4];
+  auto gload = [&](int k0) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = tid + i * GT;
+      pa[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      pb[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if constexpr (A_KC) {
+        const int gm = m0 + (idx >> 3), gk = k0 + (idx & 7) * 4;
+        if (gm < g.M && gk < kend) pa[i] = *reinterpret_cast<const float4*>(g.A + (size_t)gm * g.lda + gk);
+      } else {
+        const int gk = k0 + (idx >> 5), gm = m0 + (idx & 31) * 4;
+        if (gk < kend && gm < g.M) pa[i] = *reinterpret_cast<const float4*>(g.A + (size_t)gk * g.lda + gm);
+      }
+      if constexpr (B_KC) {
+        const int gn = n0 + (idx >> 3), gk = k0 + (idx & 7) * 4;
+        if (gn < g.N && gk < kend) pb[i] = *reinterpret_cast<const float4*>(g.B + (size_t)gn * g.ldb + gk);
+      } else {
+        const int gk = k0 + (idx >> 5), gn = n0 + (idx & 31) * 4;
+        if (gk < kend && gn < g.N) pb[i] = *reinterpret_cast<const float4*>(g.B + (size_t)gk * g.ldb + gn);
+      }
+    }
+  };
+  auto sstore = [&](int stage) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = tid + i * GT;
+      const uint2 va = make_uint2(pack_bf16(pa[i].x, pa[i].y), pack_bf16(pa[i].z, pa[i].w));
+      const uint2 vb = make_uint2(pack_bf16(pb[i].x, pb[i].y), pack_bf16(pb[i].z, pb[i].w));
+      if constexpr (A_KC) *reinterpret_cast<uint2*>(&sA[stage][(idx >> 3) * LDKH + (idx & 7) * 4]) = va;
+      else *reinterpret_cast<uint2*>(&sA[stage][(idx >> 5) * LDRH + (idx & 31) * 4]) = va;
+      if constexpr (B_KC) *reinterpret_cast<uint2*>(&sB[stage][(idx >> 3) * LDKH + (idx & 7) * 4]) = vb;
+      else *reinterpret_cast<uint2*>(&sB[stage][(idx >> 5) * LDRH + (idx & 31) * 4]) = vb;
+    }
+  };
+
+  const int n_it = (kend - kbeg + BK - 1) / BK;
+  const int mat = lane >> 3, r8 = lane & 7;
+  if (n_it > 0) {
+    gload(kbeg);
+    sstore(0);
+  }
+  __syncthreads();
+  for (int it = 0; it < n_it; ++it) {
+    const bool more = it + 1 < n_it;
+    if (more) gload(kbeg + (it + 1) * BK);
+    const __nv_bfloat16* As = sA[it & 1];
+    const __nv_bfloat16* Bs = sB[it & 1];
+#pragma unroll
+    for (int kk = 0; kk < BK; kk += 16) {
+      uint32_t a[4][4];
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt) {
+        const int r0 = wm + mt * 16;
+        if constexpr (A_KC) ldmatrix_x4(a[mt], As + (r0 + (mat & 1) * 8 + r8) * LDKH + kk + (mat >> 1) * 8);
+        else ldmatrix_x4_trans(a[mt], As + (kk + (mat >> 1) * 8 + r8) * LDRH + r0 + (mat & 1) * 8);
+      }
+#pragma unroll
+      for (int np = 0; np < 2; ++np) {
+        const int nb = wn + np * 16;
+        uint32_t b[4];   // b0, b1 of n-tile 2 np, then of n-tile 2 np + 1
+        if constexpr (B_KC) ldmatrix_x4(b, Bs + (nb + (mat >> 1) * 8 + r8) * LDKH + kk + (mat & 1) * 8);
+        else ldmatrix_x4_trans(b, Bs + (kk + (mat & 1) * 8 + r8) * LDRH + nb + (mat >> 1) * 8);
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) {
+          mma_bf16(c[mt][2 * np], a[mt], b[0], b[1]);
+          mma_bf16(c[mt][2 * np + 1], a[mt], b[2], b[3]);
+        }
+      }
+    }
+    if (more) sstore((it + 1) & 1);
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int row = m0 + wm + mt * 16 + gq + half * 8;
+        const int col = n0 + wn + nt * 8 + 2 * t;   // even; N is even, so col + 1 < N whenever col < N
+        if (row < g.M && col < g.N) {
+          float v0 = c[mt][nt][2 * half], v1 = c[mt][nt][2 * half + 1];
+          float* cp = g.C + (size_t)row * g.ldc + col;
+          if (g.atomic) {
+            atomicAdd(cp, v0);
+            atomicAdd(cp + 1, v1);
+          } else {
+            if (g.bias) { v0 += g.bias[col]; v1 += g.bias[col + 1]; }
+            if (g.R) {
+              const float2 r = *reinterpret_cast<const float2*>(g.R + (size_t)row * g.ldr + col);
+              v0 += r.x; v1 += r.y;
+            }
+            if (g.beta) {
+              const float2 o = *reinterpret_cast<const float2*>(cp);
+              v0 += o.x; v1 += o.y;
+            }
+            *reinterpret_cast<float2*>(cp) = make_float2(v0, v1);
+          }
+        }
+      }
+}
+
 enum GemmMode { NT, NN, TN };
 
 // NT: C (M, N)  = A (M, K) . B (N, K)^T      y = x W^T
@@ -298,9 +440,15 @@ void launch_gemm_t(const GemmArgs& g, dim3 grid, cudaStream_t st) {
 
 template <bool BF16>
 void launch_gemm(GemmMode mode, const GemmArgs& g, dim3 grid, cudaStream_t st) {
-  if (mode == TN) launch_gemm_t<false, false, BF16>(g, grid, st);
-  else if (mode == NT) launch_gemm_t<true, true, BF16>(g, grid, st);
-  else launch_gemm_t<true, false, BF16>(g, grid, st);
+  if constexpr (BF16) {
+    if (mode == TN) k_gemm_bf16<false, false><<<grid, GT, 0, st>>>(g);
+    else if (mode == NT) k_gemm_bf16<true, true><<<grid, GT, 0, st>>>(g);
+    else k_gemm_bf16<true, false><<<grid, GT, 0, st>>>(g);
+  } else {
+    if (mode == TN) launch_gemm_t<false, false, false>(g, grid, st);
+    else if (mode == NT) launch_gemm_t<true, true, false>(g, grid, st);
+    else launch_gemm_t<true, false, false>(g, grid, st);
+  }
 }
 
 void gemm(GemmMode mode, const float* A, int lda, const float* B, int ldb, float* C, int ldc, int M, int N, int K,
@@ -311,7 +459,7 @@ void gemm(GemmMode mode, const float* A, int lda, const float* B, int ldb, float
   count_launch();
   if (mode == TN) {
     const int tiles = grid.x * grid.y;
-    int splits = (K + 511) / 512;
+    int splits = (K + 255) / 256;
     const int cap = tiles >= 592 ? 1 : 592 / tiles;   // about four CTAs per SM in flight
     if (splits > cap) splits = cap;
     if (splits < 1) splits = 1;
