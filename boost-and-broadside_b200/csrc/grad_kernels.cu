@@ -587,8 +587,16 @@ __global__ void __launch_bounds__(256) k_colsum(const float* __restrict__ a, flo
   const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
   const int col = blockIdx.x * 32 + cx;
   float acc = 0.f;
-  if (col < N)
-    for (int r = blockIdx.y * 8 + ry; r < rows; r += gridDim.y * 8) acc += a[(size_t)r * N + col];
+  if (col < N) {
+    const int step = gridDim.y * 8;
+    int r = blockIdx.y * 8 + ry;
+    for (; r + 3 * step < rows; r += 4 * step) {   // four loads in flight
+      const float v0 = a[(size_t)r * N + col], v1 = a[(size_t)(r + step) * N + col];
+      const float v2 = a[(size_t)(r + 2 * step) * N + col], v3 = a[(size_t)(r + 3 * step) * N + col];
+      acc += (v0 + v1) + (v2 + v3);
+    }
+    for (; r < rows; r += step) acc += a[(size_t)r * N + col];
+  }
   s[ry][cx] = acc;
   __syncthreads();
   if (ry == 0 && col < N) {
@@ -808,93 +816,192 @@ __global__ void __launch_bounds__(128) k_attn_bwd(AttnBwdArgs a) {
   }
 }
 
-// The same gradient for small environments (at most 32 queries and 32 keys, head width 32): one
-// warp per (group, head), lane j owns key j -- its d k and d v accumulate in registers, the keys
-// and values of the group sit in the warp's slice of shared memory.
+// Segmented reductions: lanes are grouped in aligned runs of W (a power of two up to 32).
+template <int W>
+__device__ __forceinline__ float seg_sum(float v) {
+#pragma unroll
+  for (int o = W / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+template <int W>
+__device__ __forceinline__ float seg_max(float v) {
+#pragma unroll
+  for (int o = W / 2; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Attention for small environments (at most 32 queries and keys, head width 32).  A (group, head)
+// pair is served by LPP lanes of a warp (8, 16 or 32: the smallest that holds the keys), so a warp
+// serves 32 / LPP pairs at once; lane `sub` of a pair owns key `sub` -- its d k and d v accumulate
+// in registers -- and, in the per-channel steps, the channels sub * CPL .. + CPL - 1.  The keys and
+// values of the pair sit in the warp's slice of shared memory.
 constexpr int SMALL_WARPS = 4;
+
+template <int LPP>
 __global__ void __launch_bounds__(32 * SMALL_WARPS) k_attn_bwd_small(AttnBwdArgs a, int n_pairs, int H) {
-  constexpr int DH = 32, LDS = DH + 1;
+  constexpr int DH = 32, LDS = DH + 1, PPW = 32 / LPP, CPL = DH / LPP;
   __shared__ float sK[SMALL_WARPS][32 * LDS], sV[SMALL_WARPS][32 * LDS], sDs[SMALL_WARPS][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int pair = blockIdx.x * SMALL_WARPS + warp;
-  if (pair >= n_pairs) return;
-  const size_t grp = pair / H;
-  const int h = pair - (int)grp * H;
+  const int pw = lane / LPP, sub = lane % LPP;
+  const int pair = (blockIdx.x * SMALL_WARPS + warp) * PPW + pw;
+  const bool pair_ok = pair < n_pairs;
+  const size_t grp = pair_ok ? pair / H : 0;
+  const int h = pair_ok ? pair - (int)grp * H : 0;
   const int nk = a.nk, nq = a.nq;
-  float* Ks = sK[warp];
-  float* Vs = sV[warp];
-  float* ds_s = sDs[warp];
+  float* Ks = sK[warp] + pw * LPP * LDS;
+  float* Vs = sV[warp] + pw * LPP * LDS;
+  float* ds_s = sDs[warp] + pw * LPP;
   const uint8_t* mask = a.mask ? a.mask + grp * nk : nullptr;
-  for (int j = 0; j < nk; ++j) {   // lane = channel: coalesced rows
-    const float* kp = a.kv + (grp * nk + j) * a.ldkv + h * DH + lane;
-    Ks[j * LDS + lane] = kp[0];
-    Vs[j * LDS + lane] = kp[a.voff];
-  }
-  bool open = true;
-  bool live = lane < nk;
-  bool dead_key = false;
+  if (pair_ok)
+    for (int j = 0; j < nk; ++j)
+#pragma unroll
+      for (int cc = 0; cc < CPL; ++cc) {
+        const int d = sub + cc * LPP;   // consecutive lanes, consecutive channels
+        const float* kp = a.kv + (grp * nk + j) * a.ldkv + h * DH + d;
+        Ks[j * LDS + d] = kp[0];
+        Vs[j * LDS + d] = kp[a.voff];
+      }
+  const bool live = pair_ok && sub < nk;
+  bool dead_key = false, open = true;
   if (mask) {
-    const int mine = live ? mask[lane] : 0;
+    const int mine = live ? mask[sub] : 0;
     dead_key = live && !mine;
-    if (a.gate_by_mask) open = __any_sync(0xffffffffu, mine != 0);
+    if (a.gate_by_mask) open = seg_max<LPP>(mine ? 1.f : 0.f) > 0.f;
   }
   __syncwarp();
   float dk[DH], dv[DH];
 #pragma unroll
   for (int d = 0; d < DH; ++d) dk[d] = dv[d] = 0.f;
-  if (open) {
-    for (int i = 0; i < nq; ++i) {
-      const size_t qrow = grp * nq + i;
+  for (int i = 0; i < nq; ++i) {   // every lane of the warp walks the loop: the shuffles need them all
+    const size_t qrow = grp * nq + i;
+    float q[DH], go[DH];
+    if (pair_ok && open) {
       const float4* qp = reinterpret_cast<const float4*>(a.q + qrow * a.ldq + h * DH);
       const float4* gp = reinterpret_cast<const float4*>(a.d_o + qrow * a.ldo + h * DH);
-      float q[DH], go[DH];
 #pragma unroll
-      for (int d4 = 0; d4 < DH / 4; ++d4) {   // every lane reads the same row: one transaction each
+      for (int d4 = 0; d4 < DH / 4; ++d4) {   // the lanes of a pair read the same row
         const float4 v = qp[d4], w = gp[d4];
         q[4 * d4] = v.x; q[4 * d4 + 1] = v.y; q[4 * d4 + 2] = v.z; q[4 * d4 + 3] = v.w;
         go[4 * d4] = w.x; go[4 * d4 + 1] = w.y; go[4 * d4 + 2] = w.z; go[4 * d4 + 3] = w.w;
       }
-      float sc = 0.f, dp = 0.f;
-      if (live) {
+    } else {
 #pragma unroll
-        for (int d = 0; d < DH; ++d) {
-          sc = fmaf(q[d], Ks[lane * LDS + d], sc);
-          dp = fmaf(go[d], Vs[lane * LDS + d], dp);
-        }
-        sc *= a.scale;
-        if (dead_key) sc = kMaskedScore;
-      }
-      const float mx = warp_max(live ? sc : -INFINITY);
-      const float e = live ? expf(sc - mx) : 0.f;
-      const float l = warp_sum(e);
-      const float lse = mx + logf(l);
-      const float delta = warp_sum(e / l * dp);          // <d out, out>
-      const float p = live ? expf(sc - lse) : 0.f;
-      const float ds = p * (dp - delta) * a.scale;
-      ds_s[lane] = ds;
+      for (int d = 0; d < DH; ++d) q[d] = go[d] = 0.f;
+    }
+    float sc = 0.f, dp = 0.f;
+    if (live) {
 #pragma unroll
       for (int d = 0; d < DH; ++d) {
-        dk[d] = fmaf(ds, q[d], dk[d]);
-        dv[d] = fmaf(p, go[d], dv[d]);
+        sc = fmaf(q[d], Ks[sub * LDS + d], sc);
+        dp = fmaf(go[d], Vs[sub * LDS + d], dp);
       }
-      __syncwarp();
-      float dq = 0.f;                                    // lane = channel
-      for (int j = 0; j < nk; ++j) dq = fmaf(ds_s[j], Ks[j * LDS + lane], dq);
-      float* dqp = a.dq + qrow * a.lddq + h * DH + lane;
-      *dqp = a.dq_accumulate ? *dqp + dq : dq;
-      __syncwarp();
+      sc *= a.scale;
+      if (dead_key) sc = kMaskedScore;
     }
-  } else if (!a.dq_accumulate) {
-    for (int i = 0; i < nq; ++i) a.dq[(grp * nq + i) * a.lddq + h * DH + lane] = 0.f;
+    const float mx = seg_max<LPP>(live ? sc : -INFINITY);
+    const float e = live ? expf(sc - mx) : 0.f;
+    const float l = seg_sum<LPP>(e);
+    const float lse = mx + logf(l);
+    const float delta = seg_sum<LPP>(live ? e / l * dp : 0.f);   // <d out, out>
+    const float p = live ? expf(sc - lse) : 0.f;
+    const float ds = p * (dp - delta) * a.scale;
+    ds_s[sub] = ds;
+#pragma unroll
+    for (int d = 0; d < DH; ++d) {
+      dk[d] = fmaf(ds, q[d], dk[d]);
+      dv[d] = fmaf(p, go[d], dv[d]);
+    }
+    __syncwarp();
+    if (pair_ok) {
+      float dq[CPL];
+#pragma unroll
+      for (int cc = 0; cc < CPL; ++cc) dq[cc] = 0.f;
+      if (open)
+        for (int j = 0; j < nk; ++j) {
+          const float dsj = ds_s[j];
+#pragma unroll
+          for (int cc = 0; cc < CPL; ++cc) dq[cc] = fmaf(dsj, Ks[j * LDS + sub * CPL + cc], dq[cc]);
+        }
+      float* dqp = a.dq + qrow * a.lddq + h * DH + sub * CPL;
+      if (open || !a.dq_accumulate)
+#pragma unroll
+        for (int cc = 0; cc < CPL; ++cc) dqp[cc] = a.dq_accumulate ? dqp[cc] + dq[cc] : dq[cc];
+    }
+    __syncwarp();
   }
   if (live) {
-    float4* kp = reinterpret_cast<float4*>(a.dkv + (grp * nk + lane) * a.lddkv + h * DH);
-    float4* vp = reinterpret_cast<float4*>(a.dkv + (grp * nk + lane) * a.lddkv + h * DH + a.dvoff);
+    float4* kp = reinterpret_cast<float4*>(a.dkv + (grp * nk + sub) * a.lddkv + h * DH);
+    float4* vp = reinterpret_cast<float4*>(a.dkv + (grp * nk + sub) * a.lddkv + h * DH + a.dvoff);
 #pragma unroll
     for (int d4 = 0; d4 < DH / 4; ++d4) {
       kp[d4] = make_float4(dk[4 * d4], dk[4 * d4 + 1], dk[4 * d4 + 2], dk[4 * d4 + 3]);
       vp[d4] = make_float4(dv[4 * d4], dv[4 * d4 + 1], dv[4 * d4 + 2], dv[4 * d4 + 3]);
     }
+  }
+}
+
+// Forward for the same small environments: o = softmax(q k^T) v [+ gate * the bullet branch], the
+// pair's lanes sharing each query: lane `sub` scores key `sub`, then owns CPL output channels.
+template <int LPP>
+__global__ void __launch_bounds__(32 * SMALL_WARPS) k_attn_fwd_small(const float* __restrict__ qkv, const uint8_t* __restrict__ alive,
+                                                                   float* __restrict__ o, int NM, int D, int H, int n_pairs) {
+  constexpr int DH = 32, LDS = DH + 1, PPW = 32 / LPP, CPL = DH / LPP;
+  __shared__ float sK[SMALL_WARPS][32 * LDS], sV[SMALL_WARPS][32 * LDS], sP[SMALL_WARPS][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pw = lane / LPP, sub = lane % LPP;
+  const int pair = (blockIdx.x * SMALL_WARPS + warp) * PPW + pw;
+  const bool pair_ok = pair < n_pairs;
+  const size_t grp = pair_ok ? pair / H : 0;
+  const int h = pair_ok ? pair - (int)grp * H : 0;
+  const size_t tok0 = grp * NM;
+  float* Ks = sK[warp] + pw * LPP * LDS;
+  float* Vs = sV[warp] + pw * LPP * LDS;
+  float* p_s = sP[warp] + pw * LPP;
+  if (pair_ok)
+    for (int j = 0; j < NM; ++j)
+#pragma unroll
+      for (int cc = 0; cc < CPL; ++cc) {
+        const int d = sub + cc * LPP;
+        const float* kp = qkv + (tok0 + j) * 3 * D + D + h * DH + d;
+        Ks[j * LDS + d] = kp[0];
+        Vs[j * LDS + d] = kp[D];
+      }
+  const bool live = pair_ok && sub < NM;
+  const bool dead_key = live && alive && !alive[tok0 + sub];
+  const float scale = rsqrtf((float)DH);
+  __syncwarp();
+  for (int i = 0; i < NM; ++i) {
+    float sc = 0.f;
+    if (live) {
+      const float4* qp = reinterpret_cast<const float4*>(qkv + (tok0 + i) * 3 * D + h * DH);
+#pragma unroll
+      for (int d4 = 0; d4 < DH / 4; ++d4) {
+        const float4 v = qp[d4];
+        const float* kr = Ks + sub * LDS + 4 * d4;
+        sc = fmaf(v.x, kr[0], sc); sc = fmaf(v.y, kr[1], sc); sc = fmaf(v.z, kr[2], sc); sc = fmaf(v.w, kr[3], sc);
+      }
+      sc *= scale;
+      if (dead_key) sc = kMaskedScore;
+    }
+    const float mx = seg_max<LPP>(live ? sc : -INFINITY);
+    const float e = live ? expf(sc - mx) : 0.f;
+    const float l = seg_sum<LPP>(e);
+    p_s[sub] = e / l;
+    __syncwarp();
+    if (pair_ok) {
+      float acc[CPL];
+#pragma unroll
+      for (int cc = 0; cc < CPL; ++cc) acc[cc] = 0.f;
+      for (int j = 0; j < NM; ++j) {
+        const float pj = p_s[j];
+#pragma unroll
+        for (int cc = 0; cc < CPL; ++cc) acc[cc] = fmaf(pj, Vs[j * LDS + sub * CPL + cc], acc[cc]);
+      }
+      float* op = o + (tok0 + i) * D + h * DH + sub * CPL;
+#pragma unroll
+      for (int cc = 0; cc < CPL; ++cc) op[cc] = acc[cc];
+    }
+    __syncwarp();
   }
 }
 
@@ -1194,7 +1301,7 @@ void gelu_mul_bwd(const Ctx& c, const float* g, const float* u, const float* dh,
 void colsum(const Ctx& c, const float* a, float* out, size_t rows, int N) {
   if (!rows) return;
   count_launch();
-  dim3 grid((N + 31) / 32, blocks_for(rows, 256, 64));
+  dim3 grid((N + 31) / 32, blocks_for(rows, 256, 296));
   k_colsum<<<grid, 256, 0, c.st>>>(a, out, (int)rows, N);
 }
 
@@ -1238,6 +1345,17 @@ void attn_fwd_t(const Ctx& c, const float* qkv, const uint8_t* alive, float* o, 
 void attn_fwd(const Ctx& c, const float* qkv, const uint8_t* alive, float* o, int G, int NM, const float* kvb,
               const uint8_t* bactive, int nb) {
   if (!G) return;
+  if (c.D / c.H == 32 && NM <= 32 && !kvb) {
+    const int n_pairs = G * c.H;
+    const int lpp = NM <= 8 ? 8 : NM <= 16 ? 16 : 32;
+    const int per_block = SMALL_WARPS * (32 / lpp);
+    const int grid = (n_pairs + per_block - 1) / per_block;
+    count_launch();
+    if (lpp == 8) k_attn_fwd_small<8><<<grid, 32 * SMALL_WARPS, 0, c.st>>>(qkv, alive, o, NM, c.D, c.H, n_pairs);
+    else if (lpp == 16) k_attn_fwd_small<16><<<grid, 32 * SMALL_WARPS, 0, c.st>>>(qkv, alive, o, NM, c.D, c.H, n_pairs);
+    else k_attn_fwd_small<32><<<grid, 32 * SMALL_WARPS, 0, c.st>>>(qkv, alive, o, NM, c.D, c.H, n_pairs);
+    return;
+  }
   switch (c.D / c.H) {
     case 8: attn_fwd_t<8>(c, qkv, alive, o, G, NM, kvb, bactive, nb); break;
     case 16: attn_fwd_t<16>(c, qkv, alive, o, G, NM, kvb, bactive, nb); break;
@@ -1248,8 +1366,13 @@ int attn_bwd(const Ctx& c, const AttnBwdArgs& a, int G) {
   if (!G) return BNB_OK;
   if (a.dh == 32 && a.nk <= 32 && a.nq <= 32) {
     const int n_pairs = G * c.H;
+    const int lpp = a.nk <= 8 ? 8 : a.nk <= 16 ? 16 : 32;
+    const int per_block = SMALL_WARPS * (32 / lpp);
+    const int grid = (n_pairs + per_block - 1) / per_block;
     count_launch();
-    k_attn_bwd_small<<<(n_pairs + SMALL_WARPS - 1) / SMALL_WARPS, 32 * SMALL_WARPS, 0, c.st>>>(a, n_pairs, c.H);
+    if (lpp == 8) k_attn_bwd_small<8><<<grid, 32 * SMALL_WARPS, 0, c.st>>>(a, n_pairs, c.H);
+    else if (lpp == 16) k_attn_bwd_small<16><<<grid, 32 * SMALL_WARPS, 0, c.st>>>(a, n_pairs, c.H);
+    else k_attn_bwd_small<32><<<grid, 32 * SMALL_WARPS, 0, c.st>>>(a, n_pairs, c.H);
     return BNB_OK;
   }
   const size_t sm = attn_bwd_smem(a.nk, a.dh);
