@@ -303,7 +303,10 @@ constexpr int LDKH = BK + 8;     // bf16 per row of a [row][k] tile: 80 bytes, l
 constexpr int LDRH = 128 + 8;    // bf16 per row of a [k][row] tile: 272 bytes, likewise
 constexpr int TILE_H = BM * LDKH;
 
-template <bool A_KC, bool B_KC>
+// A_H / B_H / C_H: that operand lives in global memory as bfloat16 (the 4D-wide buffers of the gated
+// MLP in bf16 mode) instead of float32: it is then copied into shared memory as it is, or rounded
+// once on the way out.
+template <bool A_KC, bool B_KC, bool A_H, bool B_H, bool C_H>
 __global__ void __launch_bounds__(GT, 2) k_gemm_bf16(GemmArgs g) {
   static_assert(TILE_H >= BK * LDRH, "either orientation fits the tile buffer");
   __shared__ __align__(16) __nv_bfloat16 sA[2][TILE_H];
@@ -321,6 +324,19 @@ __global__ void __launch_bounds__(GT, 2) k_gemm_bf16(GemmArgs g) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) c[i][j][e] = 0.f;
 
+  // four consecutive elements of an operand: float32 (16 bytes) or bfloat16 (8 bytes, in .x .y)
+  auto fetch4 = [](const float* base, size_t elem, bool half) {
+    float4 v;
+    if (half) {
+      const uint2 h = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(base) + elem);
+      v.x = __uint_as_float(h.x);
+      v.y = __uint_as_float(h.y);
+      v.z = v.w = 0.f;
+    } else {
+      v = *reinterpret_cast<const float4*>(base + elem);
+    }
+    return v;
+  };
   float4 pa[4], pb[4];
   auto gload = [&](int k0) {
 #pragma unroll
@@ -330,17 +346,17 @@ __global__ void __launch_bounds__(GT, 2) k_gemm_bf16(GemmArgs g) {
       pb[i] = make_float4(0.f, 0.f, 0.f, 0.f);
       if constexpr (A_KC) {
         const int gm = m0 + (idx >> 3), gk = k0 + (idx & 7) * 4;
-        if (gm < g.M && gk < kend) pa[i] = *reinterpret_cast<const float4*>(g.A + (size_t)gm * g.lda + gk);
+        if (gm < g.M && gk < kend) pa[i] = fetch4(g.A, (size_t)gm * g.lda + gk, A_H);
       } else {
         const int gk = k0 + (idx >> 5), gm = m0 + (idx & 31) * 4;
-        if (gk < kend && gm < g.M) pa[i] = *reinterpret_cast<const float4*>(g.A + (size_t)gk * g.lda + gm);
+        if (gk < kend && gm < g.M) pa[i] = fetch4(g.A, (size_t)gk * g.lda + gm, A_H);
       }
       if constexpr (B_KC) {
         const int gn = n0 + (idx >> 3), gk = k0 + (idx & 7) * 4;
-        if (gn < g.N && gk < kend) pb[i] = *reinterpret_cast<const float4*>(g.B + (size_t)gn * g.ldb + gk);
+        if (gn < g.N && gk < kend) pb[i] = fetch4(g.B, (size_t)gn * g.ldb + gk, B_H);
       } else {
         const int gk = k0 + (idx >> 5), gn = n0 + (idx & 31) * 4;
-        if (gk < kend && gn < g.N) pb[i] = *reinterpret_cast<const float4*>(g.B + (size_t)gk * g.ldb + gn);
+        if (gk < kend && gn < g.N) pb[i] = fetch4(g.B, (size_t)gk * g.ldb + gn, B_H);
       }
     }
   };
@@ -348,8 +364,10 @@ __global__ void __launch_bounds__(GT, 2) k_gemm_bf16(GemmArgs g) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int idx = tid + i * GT;
-      const uint2 va = make_uint2(pack_bf16(pa[i].x, pa[i].y), pack_bf16(pa[i].z, pa[i].w));
-      const uint2 vb = make_uint2(pack_bf16(pb[i].x, pb[i].y), pack_bf16(pb[i].z, pb[i].w));
+      const uint2 va = A_H ? make_uint2(__float_as_uint(pa[i].x), __float_as_uint(pa[i].y))
+                           : make_uint2(pack_bf16(pa[i].x, pa[i].y), pack_bf16(pa[i].z, pa[i].w));
+      const uint2 vb = B_H ? make_uint2(__float_as_uint(pb[i].x), __float_as_uint(pb[i].y))
+                           : make_uint2(pack_bf16(pb[i].x, pb[i].y), pack_bf16(pb[i].z, pb[i].w));
       if constexpr (A_KC) *reinterpret_cast<uint2*>(&sA[stage][(idx >> 3) * LDKH + (idx & 7) * 4]) = va;
       else *reinterpret_cast<uint2*>(&sA[stage][(idx >> 5) * LDRH + (idx & 31) * 4]) = va;
       if constexpr (B_KC) *reinterpret_cast<uint2*>(&sB[stage][(idx >> 3) * LDKH + (idx & 7) * 4]) = vb;
@@ -406,7 +424,10 @@ __global__ void __launch_bounds__(GT, 2) k_gemm_bf16(GemmArgs g) {
         if (row < g.M && col < g.N) {
           float v0 = c[mt][nt][2 * half], v1 = c[mt][nt][2 * half + 1];
           float* cp = g.C + (size_t)row * g.ldc + col;
-          if (g.atomic) {
+          if constexpr (C_H) {   // plain product, rounded once
+            *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(g.C) + (size_t)row * g.ldc + col) =
+                __floats2bfloat162_rn(v0, v1);
+          } else if (g.atomic) {
             atomicAdd(cp, v0);
             atomicAdd(cp + 1, v1);
           } else {
@@ -441,14 +462,48 @@ void launch_gemm_t(const GemmArgs& g, dim3 grid, cudaStream_t st) {
 template <bool BF16>
 void launch_gemm(GemmMode mode, const GemmArgs& g, dim3 grid, cudaStream_t st) {
   if constexpr (BF16) {
-    if (mode == TN) k_gemm_bf16<false, false><<<grid, GT, 0, st>>>(g);
-    else if (mode == NT) k_gemm_bf16<true, true><<<grid, GT, 0, st>>>(g);
-    else k_gemm_bf16<true, false><<<grid, GT, 0, st>>>(g);
+    if (mode == TN) k_gemm_bf16<false, false, false, false, false><<<grid, GT, 0, st>>>(g);
+    else if (mode == NT) k_gemm_bf16<true, true, false, false, false><<<grid, GT, 0, st>>>(g);
+    else k_gemm_bf16<true, false, false, false, false><<<grid, GT, 0, st>>>(g);
   } else {
     if (mode == TN) launch_gemm_t<false, false, false>(g, grid, st);
     else if (mode == NT) launch_gemm_t<true, true, false>(g, grid, st);
     else launch_gemm_t<true, false, false>(g, grid, st);
   }
+}
+
+// Which operands of a bf16-mode product are stored as bfloat16.
+enum HalfOperand { H_NONE, H_A, H_B, H_C };
+
+void split_rows(GemmArgs& g, dim3& grid, int K) {
+  const int tiles = grid.x * grid.y;
+  int splits = (K + 255) / 256;
+  const int cap = tiles >= 592 ? 1 : 592 / tiles;   // about four CTAs per SM in flight
+  if (splits > cap) splits = cap;
+  if (splits < 1) splits = 1;
+  int per = (K + splits - 1) / splits;
+  per = (per + BK - 1) / BK * BK;
+  grid.z = (K + per - 1) / per;
+  g.k_per_split = per;
+  g.atomic = 1;
+}
+
+// The bf16-mode products that touch a bfloat16 buffer (gate / up / gated product of the MLP and
+// their gradients): A, B, C point to float32 or, for the operand `half` names, bfloat16 elements.
+void gemm_half(GemmMode mode, HalfOperand half, const void* A, int lda, const void* B, int ldb, void* C, int ldc, int M, int N,
+               int K, const float* R, int ldr, int beta, cudaStream_t st) {
+  if (M <= 0 || N <= 0 || K <= 0) return;
+  GemmArgs g{static_cast<const float*>(A), lda, static_cast<const float*>(B), ldb, static_cast<float*>(C), ldc, M, N, K,
+             nullptr, R, ldr, beta, K, 0};
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, 1);
+  count_launch();
+  if (mode == TN) split_rows(g, grid, K);
+  if (mode == NT && half == H_C) k_gemm_bf16<true, true, false, false, true><<<grid, GT, 0, st>>>(g);
+  else if (mode == NT && half == H_A) k_gemm_bf16<true, true, true, false, false><<<grid, GT, 0, st>>>(g);
+  else if (mode == NN && half == H_C) k_gemm_bf16<true, false, false, false, true><<<grid, GT, 0, st>>>(g);
+  else if (mode == NN && half == H_A) k_gemm_bf16<true, false, true, false, false><<<grid, GT, 0, st>>>(g);
+  else if (mode == TN && half == H_A) k_gemm_bf16<false, false, true, false, false><<<grid, GT, 0, st>>>(g);
+  else if (mode == TN && half == H_B) k_gemm_bf16<false, false, false, true, false><<<grid, GT, 0, st>>>(g);
 }
 
 void gemm(GemmMode mode, const float* A, int lda, const float* B, int ldb, float* C, int ldc, int M, int N, int K,
@@ -457,18 +512,7 @@ void gemm(GemmMode mode, const float* A, int lda, const float* B, int ldb, float
   GemmArgs g{A, lda, B, ldb, C, ldc, M, N, K, bias, R, ldr, beta, K, 0};
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, 1);
   count_launch();
-  if (mode == TN) {
-    const int tiles = grid.x * grid.y;
-    int splits = (K + 255) / 256;
-    const int cap = tiles >= 592 ? 1 : 592 / tiles;   // about four CTAs per SM in flight
-    if (splits > cap) splits = cap;
-    if (splits < 1) splits = 1;
-    int per = (K + splits - 1) / splits;
-    per = (per + BK - 1) / BK * BK;
-    grid.z = (K + per - 1) / per;
-    g.k_per_split = per;
-    g.atomic = 1;
-  }
+  if (mode == TN) split_rows(g, grid, K);
   if (bf16) launch_gemm<true>(mode, g, grid, st);
   else launch_gemm<false>(mode, g, grid, st);
 }
@@ -578,6 +622,45 @@ __global__ void k_gelu_mul_bwd(const float4* g, const float4* u, const float4* d
     dg[i] = make_float4(d.x * b.x * gelu_grad(a.x), d.y * b.y * gelu_grad(a.y), d.z * b.z * gelu_grad(a.z),
                         d.w * b.w * gelu_grad(a.w));
     du[i] = make_float4(d.x * gelu_erf(a.x), d.y * gelu_erf(a.y), d.z * gelu_erf(a.z), d.w * gelu_erf(a.w));
+  }
+}
+
+// The same two on bfloat16 buffers, eight elements per thread; gelu and the product each round to
+// bfloat16, as autocast's bf16 tensors do (attention.py:37 under autocast).
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  return make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+}
+__global__ void k_gelu_mul_fwd_h(const uint4* __restrict__ g, const uint4* __restrict__ u, uint4* __restrict__ h, size_t n8) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+    float a[8], b[8], o[8];
+    unpack8(g[i], a);
+    unpack8(u[i], b);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) o[k] = round_bf16(gelu_erf(a[k])) * b[k];
+    h[i] = pack8(o);
+  }
+}
+__global__ void k_gelu_mul_bwd_h(const uint4* g, const uint4* u, const uint4* dh, uint4* dg, uint4* du, size_t n8) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+    float a[8], b[8], d[8], og[8], ou[8];
+    unpack8(g[i], a);
+    unpack8(u[i], b);
+    unpack8(dh[i], d);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      og[k] = d[k] * b[k] * gelu_grad(a[k]);
+      ou[k] = d[k] * gelu_erf(a[k]);
+    }
+    dg[i] = pack8(og);
+    du[i] = pack8(ou);
   }
 }
 
@@ -1313,6 +1396,17 @@ void mlp_fwd(const Ctx& c, const float* x1, float* y, size_t rows, const float* 
   const int D = c.D, F = 4 * c.D, M = (int)rows;
   float *n2 = c.b.d[15], *gb = c.b.w4[0], *ub = c.b.w4[1], *hb = c.b.w4[2];
   rmsnorm_fwd(c, x1, g2, n2, c.b.inv[1], rows);
+  if (c.bf16) {   // gate, up and their gated product are bfloat16 tensors, as under autocast
+    gemm_half(NT, H_C, n2, D, Wg, D, gb, F, M, F, D, nullptr, 0, 0, c.st);
+    gemm_half(NT, H_C, n2, D, Wu, D, ub, F, M, F, D, nullptr, 0, 0, c.st);
+    if (rows) {
+      count_launch();
+      k_gelu_mul_fwd_h<<<blocks_for(rows * F / 8, 256), 256, 0, c.st>>>(reinterpret_cast<const uint4*>(gb), reinterpret_cast<const uint4*>(ub),
+                                                                     reinterpret_cast<uint4*>(hb), rows * F / 8);
+    }
+    if (y) gemm_half(NT, H_A, hb, F, Wd, F, y, D, M, D, F, x1, D, 0, c.st);
+    return;
+  }
   mm(c, NT, n2, D, Wg, D, gb, F, M, F, D);
   mm(c, NT, n2, D, Wu, D, ub, F, M, F, D);
   gelu_mul_fwd(c, gb, ub, hb, rows * F);
@@ -1324,6 +1418,22 @@ void mlp_bwd(const Ctx& c, const float* x1, const float* dy, float* dx1, size_t 
              const float* Wu, const float* Wd, float* dg2, float* dWg, float* dWu, float* dWd) {
   const int D = c.D, F = 4 * c.D, M = (int)rows;
   float *n2 = c.b.d[15], *dn2 = c.b.d[16], *gb = c.b.w4[0], *ub = c.b.w4[1], *hb = c.b.w4[2];
+  if (c.bf16) {
+    gemm_half(TN, H_B, dy, D, hb, F, dWd, F, D, F, M, nullptr, 0, 0, c.st);
+    gemm_half(NN, H_C, dy, D, Wd, F, hb, F, M, F, D, nullptr, 0, 0, c.st);
+    if (rows) {
+      count_launch();
+      k_gelu_mul_bwd_h<<<blocks_for(rows * F / 8, 256), 256, 0, c.st>>>(
+          reinterpret_cast<const uint4*>(gb), reinterpret_cast<const uint4*>(ub), reinterpret_cast<const uint4*>(hb),
+          reinterpret_cast<uint4*>(gb), reinterpret_cast<uint4*>(ub), rows * F / 8);
+    }
+    gemm_half(TN, H_A, gb, F, n2, D, dWg, D, F, D, M, nullptr, 0, 0, c.st);
+    gemm_half(TN, H_A, ub, F, n2, D, dWu, D, F, D, M, nullptr, 0, 0, c.st);
+    gemm_half(NN, H_A, gb, F, Wg, D, dn2, D, M, D, F, nullptr, 0, 0, c.st);
+    gemm_half(NN, H_A, ub, F, Wu, D, dn2, D, M, D, F, nullptr, 0, 1, c.st);
+    rmsnorm_bwd(c, x1, g2, c.b.inv[1], dn2, dy, dx1, dg2, rows);
+    return;
+  }
   mm(c, TN, dy, D, hb, F, dWd, F, D, F, M);                 // dWd (D, 4D) += dy^T h
   mm(c, NN, dy, D, Wd, F, hb, F, M, F, D);                  // dh = dy Wd
   gelu_mul_bwd(c, gb, ub, hb, gb, ub, rows * F);            // gb <- d gate, ub <- d up
