@@ -359,7 +359,8 @@ def time_gpu_reference(name: str, dev: torch.device, steps: int) -> dict:
 # ----------------------------------------------------------------------------- GPU arm
 
 
-def time_train_step(trunk, dev: torch.device, n_envs: int = 1024, timesteps: int = 32, iters: int = 3) -> dict:
+def time_train_step(trunk, dev: torch.device, n_envs: int = 1024, timesteps: int = 32, iters: int = 3,
+                    with_reference: bool = True) -> dict:
     """Forward + backward of the sequence path at the PPO-update shape (C4's environments of 8 ships,
     T steps, bf16 autocast): loss = <y, dy>, gradients of tokens and every parameter.  This package
     (fused forward, bnb_trunk_sequence_bwd behind autograd) beside the reference's own modules from
@@ -405,6 +406,8 @@ def time_train_step(trunk, dev: torch.device, n_envs: int = 1024, timesteps: int
     finally:
         trunk.zero_grad(set_to_none=True)
         trunk.train(was_training)
+    if not with_reference:
+        return out
     if not ref_runner.available():
         out["reference"] = {"unavailable": "oracle/_ref is absent"}
         return out
@@ -429,6 +432,20 @@ def time_train_step(trunk, dev: torch.device, n_envs: int = 1024, timesteps: int
         except Exception as e:  # noqa: BLE001 - a comparator that fails is reported, not fatal
             out[key] = {"error": repr(e)[:200]}
     return out
+
+
+def run_train_only(args) -> None:
+    """Only this package's forward + backward record, on one GPU (the command the launch-list
+    profile of the training step is taken with)."""
+    import boost_and_broadside_b200 as bnb
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    torch.manual_seed(0)
+    trunk = bnb.YemongTrunk(bnb.ModelConfig(d_model=128, n_heads=4, n_yemong_blocks=2, n_spatial_per_block=2,
+                                            n_temporal_per_block=1, n_bullet_cross_per_block=1)).to(dev)
+    print(json.dumps({"train_step": time_train_step(trunk, dev, n_envs=args.train_envs, iters=args.steps if args.steps < 20 else 3,
+                                                    with_reference=False)}), flush=True)
 
 
 def run_ours(args) -> None:
@@ -735,6 +752,8 @@ def main() -> None:
     ap.add_argument("--no-gpu-ref", action="store_true", help="skip the same-box GPU comparator (reference modules, eager and compiled)")
     ap.add_argument("--no-c5", action="store_true", help="skip the sharded ragged C5 record")
     ap.add_argument("--no-train", action="store_true", help="skip the forward + backward record (train_step)")
+    ap.add_argument("--train-only", action="store_true", help="only this package's forward + backward record (for profiling)")
+    ap.add_argument("--train-envs", type=int, default=1024, help="environments of the forward + backward record")
     ap.add_argument("--shard", action="store_true",
                     help="one global batch, environments sharded contiguously over the ranks (strong scaling) "
                          "instead of one full batch per rank")
@@ -742,7 +761,9 @@ def main() -> None:
                     help="fraction of the workload's environments (small cases for profiler captures only)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    if args.impl == "reference":
+    if args.train_only:
+        run_train_only(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -105,11 +105,11 @@ EXPORTS = {
          _fp, _fp, C.POINTER(Bullets), _fp, _fp, _fp, _fp, C.POINTER(Batch), C.c_int, C.c_int, C.c_int, _fp, C.c_size_t,
          _fp],
     ),
-    "bnb_trunk_bwd_scratch_bytes": (C.c_size_t, [C.c_int] * 4 + [C.POINTER(Batch), C.c_int, C.c_int]),
+    "bnb_trunk_bwd_scratch_bytes": (C.c_size_t, [C.c_int] * 4 + [C.POINTER(Batch), C.c_int, C.c_int, C.c_int]),
     "bnb_trunk_sequence_bwd": (C.c_int, [C.POINTER(SpatialWeights), C.POINTER(TemporalWeights), C.POINTER(SpatialGrads),
                                          C.POINTER(TemporalGrads)] + [C.c_int] * 5 + [_fp, _fp, C.POINTER(Bullets), _fp, _fp,
                                          C.POINTER(Batch), C.c_int, C.c_int, _fp, _fp, _fp, _fp, _fp, _fp, C.c_size_t, _fp, C.c_size_t, _fp]),
-    "bnb_trunk_kept_bytes": (C.c_size_t, [C.c_int] * 5 + [C.POINTER(Batch), C.c_int, C.c_int]),
+    "bnb_trunk_kept_bytes": (C.c_size_t, [C.c_int] * 5 + [C.POINTER(Batch), C.c_int, C.c_int, C.c_int]),
     "bnb_trunk_sequence_fwd_train": (
         C.c_int,
         [C.POINTER(SpatialWeights), C.POINTER(TemporalWeights), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,

@@ -295,16 +295,18 @@ int bnb_trunk_sequence(const BnbSpatialWeights* spatial, const BnbTemporalWeight
 }
 
 size_t bnb_trunk_bwd_scratch_bytes(int n_blocks, int n_spatial, int n_temporal, int d_model, const BnbBatch* batch,
-                                   int timesteps, int bullets_per_env) {
+                                   int timesteps, int bullets_per_env, int precision) {
   if (!batch || n_blocks < 0 || n_spatial < 0 || n_temporal < 0 || d_model <= 0 || timesteps < 1) return 0;
-  return bnb::grad::scratch_bytes(n_blocks, n_spatial, n_temporal, d_model, *batch, timesteps, bullets_per_env);
+  return bnb::grad::scratch_bytes(n_blocks, n_spatial, n_temporal, d_model, *batch, timesteps, bullets_per_env,
+                                  precision == BNB_BF16);
 }
 
 size_t bnb_trunk_kept_bytes(int n_blocks, int n_spatial, int n_temporal, int d_model, int n_heads, const BnbBatch* batch,
-                            int timesteps, int bullets_per_env) {
+                            int timesteps, int bullets_per_env, int precision) {
   if (!batch || n_blocks < 0 || n_spatial < 0 || n_temporal < 0 || d_model <= 0 || timesteps < 1) return 0;
   if (check_dims(d_model, n_heads) || check_batch(batch)) return 0;
-  return bnb::grad::kept_bytes(n_blocks, n_spatial, n_temporal, d_model, n_heads, *batch, timesteps, bullets_per_env);
+  return bnb::grad::kept_bytes(n_blocks, n_spatial, n_temporal, d_model, n_heads, *batch, timesteps, bullets_per_env,
+                               precision == BNB_BF16);
 }
 
 int bnb_trunk_sequence_fwd_train(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal, int n_blocks,

@@ -1306,12 +1306,13 @@ struct Bufs {
   float *bul_n, *bul_inv, *kvb, *dkvb, *bul_dn;
 };
 
-void plan(Arena& ar, Bufs& b, int S, size_t R, int D, size_t RB) {
+// half_mlp: the three 4D-wide buffers hold bfloat16 (bf16 mode), so they take half the bytes.
+void plan(Arena& ar, Bufs& b, int S, size_t R, int D, size_t RB, bool half_mlp) {
   b.bound = ar.take((size_t)(S > 1 ? S - 1 : 0) * R * D);
   for (auto& p : b.ping) p = ar.take(R * D);
   for (auto& p : b.d) p = ar.take(R * D);
   for (auto& p : b.w3) p = ar.take(R * 3 * D);
-  for (auto& p : b.w4) p = ar.take(R * 4 * D);
+  for (auto& p : b.w4) p = ar.take(R * 4 * D / (half_mlp ? 2 : 1));
   for (auto& p : b.inv) p = ar.take(R);
   b.bul_n = ar.take(RB * D);
   b.bul_inv = ar.take(RB);
@@ -1324,7 +1325,7 @@ void plan(Arena& ar, Bufs& b, int S, size_t R, int D, size_t RB) {
 // of their own when the activations are kept between the two (see trunk_sequence_fwd_train).
 enum PathKind { P_SPATIAL, P_SHIPS, P_FIELDS };
 
-void bind_forward(Arena& ar, Bufs& b, PathKind kind, size_t rows, int D, size_t RB) {
+void bind_forward(Arena& ar, Bufs& b, PathKind kind, size_t rows, int D, size_t RB, bool half_mlp) {
   const int nd = kind == P_SPATIAL ? 3 : kind == P_SHIPS ? 10 : 7;
   for (int i = 0; i < nd; ++i) b.d[i] = ar.take(rows * D);
   b.d[15] = ar.take(rows * D);
@@ -1336,7 +1337,7 @@ void bind_forward(Arena& ar, Bufs& b, PathKind kind, size_t rows, int D, size_t 
     b.bul_inv = ar.take(RB);
     b.kvb = ar.take(RB * 2 * D);
   }
-  for (auto& p : b.w4) p = ar.take(rows * 4 * D);
+  for (auto& p : b.w4) p = ar.take(rows * 4 * D / (half_mlp ? 2 : 1));
 }
 
 inline int blocks_for(size_t n, int per_block, int cap = 148 * 8) {
@@ -1748,41 +1749,44 @@ struct Kept {
   Bufs first[256], second[256];   // spatial or ships | fields
 };
 
-void layout_kept(Arena& ar, Kept& k, const Walk& wk, int n_blocks, int n_spatial, int n_temporal, const Bufs& shared) {
+void layout_kept(Arena& ar, Kept& k, const Walk& wk, int n_blocks, int n_spatial, int n_temporal, const Bufs& shared,
+                 bool half_mlp) {
   k.bound = ar.take((size_t)(wk.S > 1 ? wk.S - 1 : 0) * wk.R * wk.D);
   int s = 0;
   for (int blk = 0; blk < n_blocks; ++blk) {
     for (int j = 0; j < n_spatial; ++j, ++s) {
       k.first[s] = shared;
-      bind_forward(ar, k.first[s], P_SPATIAL, wk.R, wk.D, wk.RB);
+      bind_forward(ar, k.first[s], P_SPATIAL, wk.R, wk.D, wk.RB, half_mlp);
     }
     for (int j = 0; j < n_temporal; ++j, ++s) {
       k.first[s] = shared;
       k.second[s] = shared;
-      bind_forward(ar, k.first[s], P_SHIPS, wk.tgm.Rs(), wk.D, 0);
-      bind_forward(ar, k.second[s], P_FIELDS, wk.tgm.Rf(), wk.D, 0);
+      bind_forward(ar, k.first[s], P_SHIPS, wk.tgm.Rs(), wk.D, 0, half_mlp);
+      bind_forward(ar, k.second[s], P_FIELDS, wk.tgm.Rf(), wk.D, 0, half_mlp);
     }
   }
 }
 
 }  // namespace
 
-size_t scratch_bytes(int n_blocks, int n_spatial, int n_temporal, int D, const BnbBatch& bt, int T, int bullets_per_env) {
+size_t scratch_bytes(int n_blocks, int n_spatial, int n_temporal, int D, const BnbBatch& bt, int T, int bullets_per_env,
+                     bool bf16) {
   Arena ar{nullptr};
   Bufs b;
   const int S = n_blocks * (n_spatial + n_temporal);
   const size_t G = (size_t)T * bt.n_envs;
-  plan(ar, b, S, G * bt.tokens_per_env, D, G * (bullets_per_env > 0 ? bullets_per_env : 0));
+  plan(ar, b, S, G * bt.tokens_per_env, D, G * (bullets_per_env > 0 ? bullets_per_env : 0), bf16);
   return ar.off + 256;
 }
 
-size_t kept_bytes(int n_blocks, int n_spatial, int n_temporal, int D, int H, const BnbBatch& bt, int T, int bullets_per_env) {
+size_t kept_bytes(int n_blocks, int n_spatial, int n_temporal, int D, int H, const BnbBatch& bt, int T, int bullets_per_env,
+                  bool bf16) {
   Walk wk;
   BnbBullets bul{nullptr, nullptr, bullets_per_env};
   if (make_walk(wk, n_blocks, n_spatial, n_temporal, D, H, bt, T, bullets_per_env > 0 ? &bul : nullptr)) return 0;
   Arena ar{nullptr};
   static thread_local Kept k;
-  layout_kept(ar, k, wk, n_blocks, n_spatial, n_temporal, Bufs{});
+  layout_kept(ar, k, wk, n_blocks, n_spatial, n_temporal, Bufs{}, bf16);
   return ar.off + 256;
 }
 
@@ -1793,12 +1797,12 @@ int open_buffers(Ctx& c, Kept* kept, const Walk& wk, int n_blocks, int n_spatial
                  size_t scratch_bytes, void* kept_ptr, size_t kept_size) {
   uintptr_t base = (reinterpret_cast<uintptr_t>(scratch) + 255) & ~(uintptr_t)255;
   Arena ar{reinterpret_cast<char*>(base)};
-  plan(ar, c.b, kept_ptr ? 0 : wk.S, wk.R, wk.D, wk.RB);
+  plan(ar, c.b, kept_ptr ? 0 : wk.S, wk.R, wk.D, wk.RB, c.bf16);
   if (ar.off + (base - reinterpret_cast<uintptr_t>(scratch)) > scratch_bytes) return BNB_ERR_SCRATCH_TOO_SMALL;
   if (kept_ptr) {
     uintptr_t kb = (reinterpret_cast<uintptr_t>(kept_ptr) + 255) & ~(uintptr_t)255;
     Arena ka{reinterpret_cast<char*>(kb)};
-    layout_kept(ka, *kept, wk, n_blocks, n_spatial, n_temporal, c.b);
+    layout_kept(ka, *kept, wk, n_blocks, n_spatial, n_temporal, c.b, c.bf16);
     if (ka.off + (kb - reinterpret_cast<uintptr_t>(kept_ptr)) > kept_size) return BNB_ERR_SCRATCH_TOO_SMALL;
   }
   return BNB_OK;

@@ -55,10 +55,12 @@ struct TrunkFwdTrainArgs {
 };
 
 // Bytes of scratch trunk_sequence_bwd needs for this structure and batch.
-size_t scratch_bytes(int n_blocks, int n_spatial, int n_temporal, int D, const BnbBatch& b, int T, int bullets_per_env);
+size_t scratch_bytes(int n_blocks, int n_spatial, int n_temporal, int D, const BnbBatch& b, int T, int bullets_per_env,
+                     bool bf16);
 
 // Bytes of the activations trunk_sequence_fwd_train keeps for the backward (0: unsupported geometry).
-size_t kept_bytes(int n_blocks, int n_spatial, int n_temporal, int D, int H, const BnbBatch& b, int T, int bullets_per_env);
+size_t kept_bytes(int n_blocks, int n_spatial, int n_temporal, int D, int H, const BnbBatch& b, int T, int bullets_per_env,
+                  bool bf16);
 
 int trunk_sequence_fwd_train(const TrunkFwdTrainArgs& a);
 int trunk_sequence_bwd(const TrunkBwdArgs& a);

@@ -170,6 +170,11 @@ def _trunk_forward_fake(x, alive, hidden, done, reset_env, bullets, bullet_mask,
     return (x.new_empty(x.shape, dtype=out_dtype), hidden.new_empty(hidden.shape, dtype=torch.float32))
 
 
+def _grad_precision(geom: List[int]) -> int:
+    """Precision of the training forward and the backward: bf16 operands after an autocast forward."""
+    return _capi.BNB_BF16 if geom[G_PRECISION] == _capi.BNB_BF16 else _capi.BNB_FP32
+
+
 def _sublayer_lists(weights: List[Tensor], n_blocks: int, n_spatial: int, n_temporal: int, n_cross: int, field_sub: int):
     """``weights`` cut into the per-sublayer lists, block-major, spatial before temporal."""
     spatial, temporal, pos = [], [], 0
@@ -234,11 +239,12 @@ def trunk_backward(
         dx = torch.empty_like(xin)
         dh = torch.zeros_like(hin)
         dbul = torch.zeros_like(bul.tokens) if bul.struct is not None else xin.new_empty(0)
-        nbytes = _capi.lib.bnb_trunk_bwd_scratch_bytes(n_blocks, n_spatial, n_temporal, D, batch, T, bul.per_env)
+        nbytes = _capi.lib.bnb_trunk_bwd_scratch_bytes(n_blocks, n_spatial, n_temporal, D, batch, T, bul.per_env,
+                                                       _grad_precision(geom))
         scratch = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=dev)   # released after the call's stream work
         st = _capi.lib.bnb_trunk_sequence_bwd(
             sw, tw, sg, tg, n_blocks, n_spatial, n_temporal, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8), bul.arg,
-            _capi.ptr(hin), _capi.ptr(done_u8), batch, T, _capi.BNB_BF16 if geom[G_PRECISION] == _capi.BNB_BF16 else _capi.BNB_FP32,
+            _capi.ptr(hin), _capi.ptr(done_u8), batch, T, _grad_precision(geom),
             dyin.data_ptr(), _capi.ptr(dho), dx.data_ptr(),
             _capi.ptr(dh), _capi.ptr(dbul) if bul.struct is not None else None, _capi.ptr(kept),
             0 if kept is None else kept.numel(), scratch.data_ptr(), scratch.numel(), _capi.stream_handle(dev),
@@ -319,13 +325,15 @@ def trunk_forward_train(
         y = torch.empty_like(xin)
         hout = torch.empty_like(hin)
         kept = torch.empty(max(256, int(_capi.lib.bnb_trunk_kept_bytes(n_blocks, n_spatial, n_temporal, D, n_heads, batch, T,
-                                                                        bul.per_env))), dtype=torch.uint8, device=dev)
-        nbytes = _capi.lib.bnb_trunk_bwd_scratch_bytes(n_blocks, n_spatial, n_temporal, D, batch, T, bul.per_env)
+                                                                        bul.per_env, _grad_precision(geom)))),
+                           dtype=torch.uint8, device=dev)
+        nbytes = _capi.lib.bnb_trunk_bwd_scratch_bytes(n_blocks, n_spatial, n_temporal, D, batch, T, bul.per_env,
+                                                       _grad_precision(geom))
         scratch = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=dev)
         st = _capi.lib.bnb_trunk_sequence_fwd_train(
             sw, tw, n_blocks, n_spatial, n_temporal, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8), bul.arg, y.data_ptr(),
             _capi.ptr(hin), _capi.ptr(hout), _capi.ptr(done_u8), batch, T,
-            _capi.BNB_BF16 if geom[G_PRECISION] == _capi.BNB_BF16 else _capi.BNB_FP32, kept.data_ptr(), kept.numel(),
+            _grad_precision(geom), kept.data_ptr(), kept.numel(),
             scratch.data_ptr(), scratch.numel(), _capi.stream_handle(dev),
         )
     _capi.check("bnb_trunk_sequence_fwd_train", st)
@@ -378,12 +386,13 @@ def keep_activations(dev: torch.device, geom: List[int], d_model: int, n_bullets
         batch = _batch(geom, [])
         T = max(1, geom[G_TIMESTEPS])
         need = _capi.lib.bnb_trunk_kept_bytes(geom[G_BLOCKS], geom[G_SPATIAL], geom[G_TEMPORAL], d_model, geom[G_HEADS], batch, T,
-                                              n_bullets)
+                                              n_bullets, _grad_precision(geom))
         if need == 0:
             return False
         if mode == "keep":
             return True
-        need += _capi.lib.bnb_trunk_bwd_scratch_bytes(geom[G_BLOCKS], geom[G_SPATIAL], geom[G_TEMPORAL], d_model, batch, T, n_bullets)
+        need += _capi.lib.bnb_trunk_bwd_scratch_bytes(geom[G_BLOCKS], geom[G_SPATIAL], geom[G_TEMPORAL], d_model, batch, T, n_bullets,
+                                                      _grad_precision(geom))
         free, _ = torch.cuda.mem_get_info(dev)
         cached = torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)
     return need <= 0.7 * (free + cached)

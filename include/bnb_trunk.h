@@ -353,7 +353,7 @@ typedef struct {
 
 /* Scratch bytes of bnb_trunk_sequence_bwd for this structure and batch. */
 size_t bnb_trunk_bwd_scratch_bytes(int n_blocks, int n_spatial, int n_temporal, int d_model,
-                                   const BnbBatch* batch, int timesteps, int bullets_per_env);
+                                   const BnbBatch* batch, int timesteps, int bullets_per_env, int precision);
 
 /* Backward of bnb_trunk_sequence (and, with timesteps = 1 and no done, of bnb_trunk_step without
  * reset_env).  Every tensor is float32.  precision BNB_FP32: float32-accurate products (3 x tf32).
@@ -386,11 +386,12 @@ int bnb_trunk_sequence_bwd(const BnbSpatialWeights* spatial, const BnbTemporalWe
                            float* d_bullets, void* kept, size_t kept_bytes, void* scratch, size_t scratch_bytes,
                            void* stream);
 
-/* Bytes of activations bnb_trunk_sequence_fwd_train keeps for the backward (about 60 KB per token row
- * for two blocks of two spatial and one temporal sublayer at d_model 128); 0 for a geometry the
- * backward does not cover. */
+/* Bytes of activations bnb_trunk_sequence_fwd_train keeps for the backward (for two blocks of two
+ * spatial and one temporal sublayer at d_model 128: about 65 KB per token row with BNB_FP32, 47 KB
+ * with BNB_BF16, where the 4 d_model-wide buffers of the gated MLPs hold bfloat16); 0 for a geometry
+ * the backward does not cover.  Sizes depend on the precision: query with the call's. */
 size_t bnb_trunk_kept_bytes(int n_blocks, int n_spatial, int n_temporal, int d_model, int n_heads,
-                            const BnbBatch* batch, int timesteps, int bullets_per_env);
+                            const BnbBatch* batch, int timesteps, int bullets_per_env, int precision);
 
 /* The sequence forward for a call that will be differentiated: y and hidden_out as
  * bnb_trunk_sequence computes them (same arithmetic contract per precision: float32, or bfloat16
