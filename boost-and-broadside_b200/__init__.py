@@ -12,7 +12,7 @@ the C-ABI library ``libbnb_trunk.so`` (include/bnb_trunk.h).  There is no CPU pa
 from .config import ModelConfig
 from .yemong.attention import GatedMLP, TransformerBlock
 from .yemong.encoder import BulletEncoder, ShipEncoder
-from .yemong.heads import HeadMLP, NextStateHead
+from .yemong.heads import HeadMLP, NextStateHead, TeamPMA, evaluate_action, sample_action
 from .yemong.griffin import CONV_KERNEL, RGLRU, GriffinTemporalBlock, YemongBlock
 from .yemong.trunk import YemongTrunk, RaggedBatch
 
@@ -27,7 +27,10 @@ __all__ = [
     "RGLRU",
     "RaggedBatch",
     "ShipEncoder",
+    "TeamPMA",
     "TransformerBlock",
     "YemongBlock",
     "YemongTrunk",
+    "evaluate_action",
+    "sample_action",
 ]

@@ -124,6 +124,9 @@ EXPORTS = {
     "bnb_rglru_fwd": (C.c_int, [_fp] * 5 + [C.c_int, _fp, _fp, _fp, _fp, _fp, C.c_int, C.c_int, C.c_int, _fp]),
     "bnb_encoder_mlp_fwd": (C.c_int, [_fp] * 6 + [C.c_int] * 4 + [_fp, _fp, C.c_int, C.c_int, _fp]),
     "bnb_head_mlp_fwd": (C.c_int, [_fp] * 5 + [C.c_int] * 4 + [_fp, _fp, C.c_int, C.c_int, _fp]),
+    "bnb_action_dist_fwd": (C.c_int, [_fp] * 6 + [C.c_int, C.c_int, _fp]),
+    "bnb_team_pma_scratch_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
+    "bnb_team_pma_fwd": (C.c_int, [_fp] * 4 + [C.c_int, C.c_int, _fp, _fp, _fp, _fp] + [C.c_int] * 4 + [_fp, C.c_size_t, _fp]),
     "bnb_pack_trunk": (C.c_int, [C.POINTER(SpatialWeights), C.c_int, C.POINTER(TemporalWeights), C.c_int, C.c_int, C.c_int, _fp]),
     "bnb_last_status": (C.c_int, []),
     "bnb_clear_status": (None, []),

@@ -471,6 +471,42 @@ int bnb_head_mlp_fwd(const float* w1, const float* b1, const float* g1, const fl
                                  precision == BNB_BF16, static_cast<cudaStream_t>(stream));
 }
 
+size_t bnb_team_pma_scratch_bytes(int d_model, int n_envs, int n_ships) {
+  if (d_model <= 0 || n_envs < 0 || n_ships < 0) return 0;
+  return ((size_t)n_envs * n_ships * 2 * d_model + 2 * (size_t)d_model) * sizeof(float) + 256;
+}
+
+int bnb_team_pma_fwd(const float* seeds, const float* in_proj_w, const float* out_w, const float* norm_w, int d_model,
+                     int n_heads, const float* x, const int32_t* team_id, const uint8_t* alive, void* y, int y_is_bf16,
+                     int n_envs, int n_ships, int precision, void* scratch, size_t scratch_bytes, void* stream) {
+  int st = check_dims(d_model, n_heads);
+  if (st) return st;
+  if (n_envs < 0 || n_ships < 0) return BNB_ERR_BAD_ARGUMENT;
+  if (precision != BNB_FP32 && precision != BNB_BF16) return BNB_ERR_BAD_ARGUMENT;
+  if ((size_t)n_envs * n_ships == 0) return BNB_OK;
+  const void* ps[] = {seeds, in_proj_w, out_w, norm_w, x, team_id, alive, y, scratch};
+  for (const void* p : ps)
+    if (!p) return BNB_ERR_NULL_POINTER;
+  if (!aligned16(in_proj_w) || !aligned16(out_w) || !aligned16(x) || !aligned16(y)) return BNB_ERR_MISALIGNED;
+  if (scratch_bytes < bnb_team_pma_scratch_bytes(d_model, n_envs, n_ships)) return BNB_ERR_SCRATCH_TOO_SMALL;
+  uintptr_t base = (reinterpret_cast<uintptr_t>(scratch) + 255) & ~(uintptr_t)255;
+  float* kv = reinterpret_cast<float*>(base);
+  float* q = kv + (size_t)n_envs * n_ships * 2 * d_model;
+  return bnb::exact::team_pma(seeds, in_proj_w, out_w, norm_w, d_model, n_heads, x, team_id, alive, y, y_is_bf16 != 0, n_envs,
+                              n_ships, kv, q, precision == BNB_BF16, static_cast<cudaStream_t>(stream));
+}
+
+int bnb_action_dist_fwd(const float* logits, const float* uniforms, const int64_t* given_action, int64_t* action,
+                        float* logprob, float* entropy, int n_rows, int precision, void* stream) {
+  if (n_rows < 0) return BNB_ERR_BAD_ARGUMENT;
+  if (precision != BNB_FP32 && precision != BNB_BF16) return BNB_ERR_BAD_ARGUMENT;
+  if (n_rows == 0) return BNB_OK;
+  if (!logits || !logprob) return BNB_ERR_NULL_POINTER;
+  if (!given_action && (!uniforms || !action)) return BNB_ERR_NULL_POINTER;
+  return bnb::exact::sample_action(logits, uniforms, given_action, action, logprob, entropy, n_rows, precision == BNB_BF16,
+                                   static_cast<cudaStream_t>(stream));
+}
+
 size_t bnb_packed_spatial_bytes(int d_model) { return bnb::tensor::packed_spatial_bytes(d_model); }
 size_t bnb_packed_temporal_bytes(int d_model) { return bnb::tensor::packed_temporal_bytes(d_model); }
 

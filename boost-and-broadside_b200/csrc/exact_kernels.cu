@@ -209,7 +209,15 @@ k_spatial_qkv(const float* __restrict__ x, float* __restrict__ qkv, int n_rows, 
     *reinterpret_cast<float4*>(X + r * ld + q * 4) = v;
   }
   __syncthreads();
-  tile_rmsnorm<EMU>(X, Nrm, ld, D, g1, n_valid);
+  if (g1) {
+    tile_rmsnorm<EMU>(X, Nrm, ld, D, g1, n_valid);
+  } else {   // a plain projection of the rows (TeamPMA's keys and values)
+    for (int idx = tid; idx < ROWS * D; idx += NTHREADS) {
+      const int r = idx / D, cc = idx - r * D;
+      Nrm[r * ld + cc] = rnd<EMU>(X[r * ld + cc]);
+    }
+    __syncthreads();
+  }
   for (int c0 = 0; c0 < n_out; c0 += NCHUNK) {
     int cn = min(NCHUNK, n_out - c0);
     float acc[4][4];
@@ -800,6 +808,176 @@ k_encoder_mlp(const float* __restrict__ x, void* __restrict__ y, int n_rows, int
   }
 }
 
+// ------------------------------------------------------------------ TeamPMA (policy.py:78-121)
+// q[t] = W_q seeds[t] for the two team seeds (one block).
+template <bool EMU>
+__global__ void k_team_query(const float* __restrict__ seeds, const float* __restrict__ Wq, float* __restrict__ q, int D) {
+  for (int o = threadIdx.x; o < 2 * D; o += blockDim.x) {
+    const int t = o / D, c = o - t * D;
+    float acc = 0.f;
+    for (int k = 0; k < D; ++k) acc = fmaf(rnd<EMU>(seeds[t * D + k]), rnd<EMU>(Wq[(size_t)c * D + k]), acc);
+    q[o] = rnd<EMU>(acc);
+  }
+}
+
+// Pooling by attention over the alive ships of each team, 16 environments (32 team rows) per CTA:
+// per (environment, team) a softmax per head over that team's alive ships with the team's seed as
+// the query, the pooled values through out_proj (a 32-row tile product), zero where the team has no
+// ship alive, RMSNorm, and every ship gets its team's row (team_id clamped to 0..1).
+template <bool EMU>
+__global__ void __launch_bounds__(NTHREADS)
+k_team_pool(const float* __restrict__ kv, const float* __restrict__ q, const int32_t* __restrict__ team_id,
+            const uint8_t* __restrict__ alive, void* __restrict__ y, int y_bf16, int n_envs, int N, int D, int H,
+            const float* __restrict__ Wo, const float* __restrict__ gn) {
+  extern __shared__ __align__(16) float smem[];
+  const int ld = max(D, NCHUNK) + 4;
+  float* P = smem;                   // pooled rows, then the normed team rows
+  float* Ws = P + ROWS * ld;
+  float* sc = Ws + NCHUNK * WS_STRIDE;   // per warp: N x H softmax weights
+  __shared__ float s_has[ROWS];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int env0 = blockIdx.x * (ROWS / 2);
+  const int dh = D / H;
+  const float scale = rsqrtf((float)dh);
+  float* my = sc + (size_t)warp * N * H;
+  for (int i = 0; i < 4; ++i) {
+    const int r = 4 * warp + i;
+    const int e = env0 + (r >> 1), t = r & 1;
+    bool any = false;
+    if (e < n_envs) {
+      const size_t base = (size_t)e * N;
+      // scores of this team's alive ships, per head
+      for (int n = lane; n < N; n += 32) {
+        const bool ok = team_id[base + n] == t && alive[base + n];
+        const float* kp = kv + (base + n) * 2 * D;
+        for (int h = 0; h < H; ++h) {
+          float acc = -INFINITY;
+          if (ok) {
+            acc = 0.f;
+            for (int d = 0; d < dh; ++d) acc = fmaf(q[t * D + h * dh + d], kp[h * dh + d], acc);
+            acc *= scale;
+          }
+          my[n * H + h] = acc;
+        }
+        any |= ok;
+      }
+      any = __any_sync(0xffffffffu, any);
+      __syncwarp();
+      if (any) {
+        for (int h = 0; h < H; ++h) {
+          float m = -INFINITY;
+          for (int n = lane; n < N; n += 32) m = fmaxf(m, my[n * H + h]);
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+          float l = 0.f;
+          for (int n = lane; n < N; n += 32) {
+            const float ex = expf(my[n * H + h] - m);   // exp(-inf) = 0 for the masked ships
+            my[n * H + h] = ex;
+            l += ex;
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+          const float inv = 1.0f / l;
+          for (int n = lane; n < N; n += 32) my[n * H + h] *= inv;
+        }
+        __syncwarp();
+      }
+    }
+    for (int c = lane; c < D; c += 32) {
+      float acc = 0.f;
+      if (e < n_envs && any) {
+        const int h = c / dh;
+        for (int n = 0; n < N; ++n) acc = fmaf(my[n * H + h], kv[((size_t)e * N + n) * 2 * D + D + c], acc);
+      }
+      P[r * ld + c] = rnd<EMU>(acc);
+    }
+    if (lane == 0) s_has[r] = (e < n_envs && any) ? 1.f : 0.f;
+    __syncwarp();
+  }
+  __syncthreads();
+  float acc[4][4];
+  zero_acc(acc);
+  tile_linear<EMU>(P, ld, Wo, D, D, D, Ws, acc);
+  __syncthreads();   // every warp has read its rows of P
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = lane + 32 * j;
+      if (c < D) P[(4 * warp + i) * ld + c] = rnd<EMU>(acc[i][j]) * s_has[4 * warp + i];
+    }
+  __syncthreads();
+  tile_rmsnorm<EMU>(P, P, ld, D, gn, ROWS);
+  __syncthreads();
+  const int envs_here = min(ROWS / 2, n_envs - env0);
+  for (int idx = tid; idx < envs_here * N * (D / 4); idx += NTHREADS) {
+    const int c4 = idx % (D / 4), sn = idx / (D / 4);
+    const int el = sn / N;
+    const size_t row = (size_t)(env0 + el) * N + (sn - el * N);
+    const int t = min(max(team_id[row], 0), 1);
+    const float4 v = *reinterpret_cast<const float4*>(P + (2 * el + t) * ld + c4 * 4);
+    if (y_bf16) {
+      __nv_bfloat162* yp = reinterpret_cast<__nv_bfloat162*>(static_cast<__nv_bfloat16*>(y) + row * D + c4 * 4);
+      yp[0] = __floats2bfloat162_rn(v.x, v.y);
+      yp[1] = __floats2bfloat162_rn(v.z, v.w);
+    } else {
+      *reinterpret_cast<float4*>(static_cast<float*>(y) + row * D + c4 * 4) = v;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ action sampling (policy.py:551-575)
+// One thread per ship: three independent categorical draws over the logit slices [0, 3), [3, 10),
+// [10, 12) (constants.py:43-48) by inverse CDF from the caller's uniforms, and the sum of the three
+// log-probabilities.  EMU: the logits are bfloat16 values and the normalised log-probabilities round
+// to bfloat16 like torch.distributions.Categorical's do under autocast.
+template <bool EMU>
+__global__ void k_sample_action(const float* __restrict__ logits, const float* __restrict__ uniforms,
+                                const int64_t* __restrict__ given, int64_t* __restrict__ action, float* __restrict__ logprob,
+                                float* __restrict__ entropy, int n_rows) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= n_rows) return;
+  const int lo[3] = {0, 3, 10}, hi[3] = {3, 10, 12};
+  float lp_sum = 0.f, ent_sum = 0.f;
+  for (int s = 0; s < 3; ++s) {
+    float v[7], m = -INFINITY;
+    const int n = hi[s] - lo[s];
+    for (int k = 0; k < n; ++k) {
+      v[k] = rnd<EMU>(logits[(size_t)r * 12 + lo[s] + k]);
+      m = fmaxf(m, v[k]);
+    }
+    float l = 0.f;
+    for (int k = 0; k < n; ++k) l += expf(v[k] - m);
+    const float lse = rnd<EMU>(m + logf(l));
+    int pick;
+    if (given) {
+      pick = (int)given[(size_t)r * 3 + s];
+      pick = min(max(pick, 0), n - 1);
+    } else {
+      // inverse CDF: the first k with u * l < sum_{j <= k} exp(v_j - m)
+      const float target = uniforms[(size_t)r * 3 + s] * l;
+      float c = 0.f;
+      pick = n - 1;
+      for (int k = 0; k < n; ++k) {
+        c += expf(v[k] - m);
+        if (target < c) { pick = k; break; }
+      }
+      action[(size_t)r * 3 + s] = pick;
+    }
+    lp_sum = rnd<EMU>(lp_sum + rnd<EMU>(v[pick] - lse));
+    if (entropy) {
+      float e = 0.f;
+      for (int k = 0; k < n; ++k) {
+        const float lg = rnd<EMU>(v[k] - lse);
+        e += rnd<EMU>(lg * rnd<EMU>(expf(lg)));
+      }
+      ent_sum = rnd<EMU>(ent_sum + rnd<EMU>(-rnd<EMU>(e)));
+    }
+  }
+  logprob[r] = lp_sum;
+  if (entropy) entropy[r] = ent_sum;
+}
+
 // ------------------------------------------------------------------ host launchers
 
 static size_t smem_rows(int D, int tiles) {
@@ -958,6 +1136,43 @@ int encoder_mlp(const float* w1, const float* b1, const float* g1, const float* 
   return emulate_bf16
              ? encoder_mlp_impl<true>(w1, b1, g1, w2, b2, g2, in_dim, in_pad, hidden, out_dim, out_store, x, y, n_rows, st)
              : encoder_mlp_impl<false>(w1, b1, g1, w2, b2, g2, in_dim, in_pad, hidden, out_dim, out_store, x, y, n_rows, st);
+}
+
+template <bool EMU>
+static int team_pma_impl(const float* seeds, const float* in_proj_w, const float* out_w, const float* norm_w, int D, int H,
+                         const float* x, const int32_t* team_id, const uint8_t* alive, void* y, bool y_bf16, int n_envs, int N,
+                         float* kv, float* q, cudaStream_t st) {
+  const int n_rows = n_envs * N;
+  const size_t sm_qkv = (size_t)(2 * ROWS * (D + 4) + NCHUNK * WS_STRIDE) * sizeof(float);
+  if (!opt_in(k_spatial_qkv<EMU>, sm_qkv)) return BNB_ERR_LAUNCH;
+  count_launch();
+  k_spatial_qkv<EMU><<<(n_rows + ROWS - 1) / ROWS, NTHREADS, sm_qkv, st>>>(x, kv, n_rows, D, 2 * D, nullptr,
+                                                                          in_proj_w + (size_t)D * D);
+  count_launch();
+  k_team_query<EMU><<<1, 256, 0, st>>>(seeds, in_proj_w, q, D);
+  const int ld = (D > NCHUNK ? D : NCHUNK) + 4;
+  const size_t sm = (size_t)(ROWS * ld + NCHUNK * WS_STRIDE + (NTHREADS / 32) * N * H) * sizeof(float);
+  if (sm > 200 * 1024) return BNB_ERR_TOO_MANY_TOKENS;
+  if (!opt_in(k_team_pool<EMU>, sm)) return BNB_ERR_LAUNCH;
+  count_launch();
+  k_team_pool<EMU><<<(n_envs + ROWS / 2 - 1) / (ROWS / 2), NTHREADS, sm, st>>>(kv, q, team_id, alive, y, y_bf16 ? 1 : 0, n_envs, N,
+                                                                             D, H, out_w, norm_w);
+  return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
+}
+int team_pma(const float* seeds, const float* in_proj_w, const float* out_w, const float* norm_w, int D, int H, const float* x,
+             const int32_t* team_id, const uint8_t* alive, void* y, bool y_bf16, int n_envs, int N, float* kv, float* q,
+             bool emulate_bf16, cudaStream_t st) {
+  return emulate_bf16 ? team_pma_impl<true>(seeds, in_proj_w, out_w, norm_w, D, H, x, team_id, alive, y, y_bf16, n_envs, N, kv, q, st)
+                      : team_pma_impl<false>(seeds, in_proj_w, out_w, norm_w, D, H, x, team_id, alive, y, y_bf16, n_envs, N, kv, q, st);
+}
+
+int sample_action(const float* logits, const float* uniforms, const int64_t* given, int64_t* action, float* logprob,
+                  float* entropy, int n_rows, bool emulate_bf16, cudaStream_t st) {
+  if (n_rows == 0) return BNB_OK;
+  count_launch();
+  if (emulate_bf16) k_sample_action<true><<<(n_rows + 127) / 128, 128, 0, st>>>(logits, uniforms, given, action, logprob, entropy, n_rows);
+  else k_sample_action<false><<<(n_rows + 127) / 128, 128, 0, st>>>(logits, uniforms, given, action, logprob, entropy, n_rows);
+  return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
 }
 
 int reset_hidden(const float* in, float* out, const uint8_t* done, int n_slots, int D,

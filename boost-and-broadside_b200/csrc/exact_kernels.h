@@ -39,5 +39,16 @@ int encoder_mlp(const float* w1, const float* b1, const float* g1, const float* 
                 int in_dim, int in_pad, int hidden, int out_dim, int out_store, const float* x, void* y, int n_rows,
                 bool emulate_bf16, cudaStream_t st);
 
+// TeamPMA: pooling by attention over each team's alive ships, broadcast back to the ships.
+// kv holds n_envs * N * 2D floats of scratch, q 2D floats; y is (n_envs, N, D) float32 or bfloat16.
+int team_pma(const float* seeds, const float* in_proj_w, const float* out_w, const float* norm_w, int D, int H, const float* x,
+             const int32_t* team_id, const uint8_t* alive, void* y, bool y_bf16, int n_envs, int N, float* kv, float* q,
+             bool emulate_bf16, cudaStream_t st);
+
+// Factored categorical over the 12 action logits: draws from `uniforms` (n_rows, 3) into `action`,
+// or scores the `given` actions; logprob (n_rows) and, when asked, entropy (n_rows).
+int sample_action(const float* logits, const float* uniforms, const int64_t* given, int64_t* action, float* logprob,
+                  float* entropy, int n_rows, bool emulate_bf16, cudaStream_t st);
+
 }  // namespace exact
 }  // namespace bnb

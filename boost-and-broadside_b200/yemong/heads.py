@@ -1,6 +1,7 @@
 """Output heads behind the trunk, mirroring the reference's ``models/yemong/policy.py``.
 
-The policy's four heads -- ``action_head``, ``value_head_local``, ``value_head_win``
+``TeamPMA`` (policy.py:78-121) pools each team's alive ships with a learned seed
+(``bnb_team_pma_fwd``).  The policy's four heads -- ``action_head``, ``value_head_local``, ``value_head_win``
 (policy.py:185-206) and ``NextStateHead.net`` (policy.py:56-72) -- are one shape:
 ``Sequential(Linear(D, 2D), RMSNorm(2D), GELU(), Linear(2D, out))``.  ``HeadMLP`` is that
 ``nn.Sequential`` with the same child indices (0, 1, 3 carry parameters), so the reference's
@@ -69,3 +70,95 @@ class NextStateHead(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.net(x)
+
+
+class TeamPMA(nn.Module):
+    """Pooling by multi-head attention over per-team ship embeddings (policy.py:78-121): for each
+    team a learned seed attends over that team's alive ships; every ship receives its team's pooled,
+    normed embedding.  Same sub-modules and parameter names as the reference (``seeds``,
+    ``attn.in_proj_weight``, ``attn.out_proj.weight``, ``norm.weight``); ``attn`` only holds the
+    parameters here, the arithmetic runs in ``bnb_team_pma_fwd``."""
+
+    def __init__(self, d_model: int, n_heads: int) -> None:
+        super().__init__()
+        self.d_model = d_model
+        self.n_heads = n_heads
+        self.seeds = nn.Parameter(torch.zeros(2, d_model))
+        self.attn = nn.MultiheadAttention(d_model, n_heads, batch_first=True, bias=False)
+        self.norm = nn.RMSNorm(d_model)
+
+    def forward(self, x: torch.Tensor, team_id: torch.Tensor, alive: torch.Tensor) -> torch.Tensor:
+        """x (B, N, D), team_id (B, N) int, alive (B, N) bool -> (B, N, D) in x's dtype."""
+        if torch.is_grad_enabled() and x.requires_grad:
+            raise NotImplementedError("the CUDA TeamPMA is forward-only; call it under torch.no_grad()")
+        _capi.require_cuda(x, "x")
+        if x.dim() != 3 or x.shape[-1] != self.d_model:
+            raise RuntimeError(f"expected x of shape (B, N, {self.d_model}), got {tuple(x.shape)}")
+        B, N, D = x.shape
+        if tuple(team_id.shape) != (B, N) or tuple(alive.shape) != (B, N):
+            raise RuntimeError(f"team_id and alive must have shape {(B, N)}")
+        dev = x.device
+        precision = _capi.current_precision(dev)
+        ps = [self.seeds, self.attn.in_proj_weight, self.attn.out_proj.weight, self.norm.weight]
+        for p in ps:
+            if p.device != dev or p.dtype != torch.float32 or not p.is_contiguous():
+                raise RuntimeError("TeamPMA parameters must be contiguous float32 on the input's device")
+        with torch.cuda.device(dev):
+            xin = _capi.f32c(x)
+            tid = team_id.to(torch.int32).contiguous()
+            al = _capi.u8(alive)
+            y = torch.empty(B, N, D, device=dev, dtype=torch.bfloat16 if x.dtype == torch.bfloat16 else torch.float32)
+            nbytes = _capi.lib.bnb_team_pma_scratch_bytes(D, B, N)
+            scratch = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=dev)
+            st = _capi.lib.bnb_team_pma_fwd(*(p.data_ptr() for p in ps), D, self.n_heads, xin.data_ptr(), tid.data_ptr(),
+                                            al.data_ptr(), y.data_ptr(), 1 if y.dtype == torch.bfloat16 else 0, B, N,
+                                            precision, scratch.data_ptr(), scratch.numel(), _capi.stream_handle(dev))
+        _capi.check("bnb_team_pma_fwd", st)
+        return y
+
+
+def _action_dist(logits: torch.Tensor, given: torch.Tensor | None, want_entropy: bool, generator=None):
+    if torch.is_grad_enabled() and logits.requires_grad:
+        raise NotImplementedError("the CUDA action distribution is forward-only; call it under torch.no_grad()")
+    _capi.require_cuda(logits, "logits")
+    if logits.shape[-1] != 12:
+        raise RuntimeError(f"expected 12 action logits in the last dim, got {tuple(logits.shape)}")
+    dev = logits.device
+    lead = logits.shape[:-1]
+    precision = _capi.BNB_BF16 if logits.dtype == torch.bfloat16 else _capi.BNB_FP32
+    with torch.cuda.device(dev):
+        flat = _capi.f32c(logits).reshape(-1, 12)
+        R = flat.shape[0]
+        logprob = torch.empty(R, device=dev, dtype=torch.float32)
+        entropy = torch.empty(R, device=dev, dtype=torch.float32) if want_entropy else None
+        if given is None:
+            uniforms = torch.rand(R, 3, device=dev, generator=generator)
+            action = torch.empty(R, 3, device=dev, dtype=torch.int64)
+            g = None
+        else:
+            if tuple(given.shape) != (*lead, 3):
+                raise RuntimeError(f"actions must have shape {(*lead, 3)}, got {tuple(given.shape)}")
+            uniforms = action = None
+            g = given.to(torch.int64).reshape(-1, 3).contiguous()
+        st = _capi.lib.bnb_action_dist_fwd(flat.data_ptr(), _capi.ptr(uniforms), _capi.ptr(g), _capi.ptr(action),
+                                           logprob.data_ptr(), _capi.ptr(entropy), R, precision, _capi.stream_handle(dev))
+    _capi.check("bnb_action_dist_fwd", st)
+    out_dtype = logits.dtype if logits.dtype == torch.bfloat16 else torch.float32
+    logprob = logprob.reshape(lead).to(out_dtype)
+    if entropy is not None:
+        entropy = entropy.reshape(lead).to(out_dtype)
+    return (None if action is None else action.reshape(*lead, 3)), logprob, entropy
+
+
+def sample_action(logits: torch.Tensor, generator: torch.Generator | None = None):
+    """``_sample_action`` (policy.py:551-575): logits (..., 12) -> (action (..., 3) int64, logprob (...)).
+    The draws are inverse-CDF samples of uniforms from ``torch.rand`` on the device (the caller's
+    generator): the same distribution as the reference's, not the same random stream."""
+    action, logprob, _ = _action_dist(logits, None, False, generator)
+    return action, logprob
+
+
+def evaluate_action(logits: torch.Tensor, actions: torch.Tensor):
+    """``_evaluate_action`` (policy.py:578-602), forward only: (logprob (...), entropy (...))."""
+    _, logprob, entropy = _action_dist(logits, actions, True)
+    return logprob, entropy

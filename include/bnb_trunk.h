@@ -419,6 +419,33 @@ int bnb_head_mlp_fwd(const float* w1, const float* b1, const float* g1, const fl
                      int in_dim, int hidden, int out_dim, int out_pad, const float* x, void* y, int n_rows,
                      int precision, void* stream);
 
+/* TeamPMA: for each team t in {0, 1} a learned seed attends over the trunk outputs of that team's
+ * alive ships (an nn.MultiheadAttention without biases), the result goes through out_proj, is zeroed
+ * where the team has no ship alive, RMS-normed, and every ship receives its team's row.
+ * Replaces: TeamPMA.forward, models/yemong/policy.py:78-121.
+ *   seeds (2, D); in_proj_w (3D, D) = attn.in_proj_weight; out_w (D, D) = attn.out_proj.weight;
+ *   norm_w (D); x (n_envs, n_ships, D) float32; team_id (n_envs, n_ships) int32; alive bytes;
+ *   y (n_envs, n_ships, D): float32, or bfloat16 elements when y_is_bf16 (the reference writes into a
+ *   tensor of x's dtype).  scratch: bnb_team_pma_scratch_bytes. */
+size_t bnb_team_pma_scratch_bytes(int d_model, int n_envs, int n_ships);
+int bnb_team_pma_fwd(const float* seeds, const float* in_proj_w, const float* out_w, const float* norm_w,
+                     int d_model, int n_heads, const float* x, const int32_t* team_id, const uint8_t* alive,
+                     void* y, int y_is_bf16, int n_envs, int n_ships, int precision, void* scratch,
+                     size_t scratch_bytes, void* stream);
+
+/* The factored categorical over the 12 action logits [power 0:3 | turn 3:10 | shoot 10:12]
+ * (constants.py:43-48).
+ * Replaces: _sample_action and _evaluate_action, models/yemong/policy.py:551-602 (forward only).
+ *   logits (n_rows, 12) float32 (bfloat16 values under BNB_BF16).
+ *   given_action NULL: one inverse-CDF draw per slice from uniforms (n_rows, 3) in [0, 1) into
+ *   action (n_rows, 3) int64; the caller supplies the uniforms (torch.rand on the device), so the
+ *   draws follow the caller's generator, not torch.multinomial's stream.
+ *   given_action (n_rows, 3) int64: those actions are scored instead.
+ *   logprob (n_rows): sum of the three log-probabilities; entropy (n_rows) or NULL. */
+int bnb_action_dist_fwd(const float* logits, const float* uniforms, const int64_t* given_action,
+                        int64_t* action, float* logprob, float* entropy, int n_rows, int precision,
+                        void* stream);
+
 /* Bytes of the tensor-core weight image of one sublayer (bf16, pre-tiled). */
 size_t bnb_packed_spatial_bytes(int d_model);
 size_t bnb_packed_temporal_bytes(int d_model);

@@ -93,3 +93,87 @@ def test_head_on_an_empty_batch_and_a_wrong_width():
             head(torch.zeros(4, 64, device=DEV))
         with pytest.raises(RuntimeError):
             head(torch.zeros(4, 128))   # a CPU tensor: there is no CPU path
+
+
+@needs_ref
+@pytest.mark.parametrize("mode", ["fp32", "bf16"])
+@pytest.mark.parametrize("B,N", [(64, 8), (5, 2), (3, 40), (2, 152)])
+def test_team_pma_matches_the_reference(B, N, mode):
+    """TeamPMA (policy.py:78-121) of a stock reference policy against this package's, same
+    parameters: random teams (ids outside 0..1 included: they are clamped for the gather), dead
+    ships, an environment with a whole team dead and one with everybody dead."""
+    import boost_and_broadside_b200 as bnb
+
+    stock, _ = build_policies(8)
+    ref = stock.team_pma
+    with torch.no_grad():   # away from the near-zero seeds of the default init
+        ref.seeds.normal_(0.0, 0.5)
+        ref.norm.weight.uniform_(0.5, 1.5)
+    mine = bnb.TeamPMA(128, 4).to(DEV)
+    mine.load_state_dict(ref.state_dict(), strict=True)
+    g = torch.Generator().manual_seed(B * 31 + N)
+    x = (torch.randn(B, N, 128, generator=g) * 1.5).to(DEV)
+    team = torch.randint(0, 2, (B, N), generator=g)
+    alive = torch.rand(B, N, generator=g) < 0.7
+    alive[0] = team[0] == 0            # team 1 entirely dead in environment 0
+    if B > 1:
+        alive[1] = False               # nobody alive in environment 1
+    team, alive = team.to(DEV), alive.to(DEV)
+    ctx = torch.autocast(DEV, dtype=torch.bfloat16) if mode == "bf16" else torch.autocast(DEV, enabled=False)
+    with torch.no_grad(), ctx:
+        r, m = ref(x, team, alive), mine(x, team, alive)
+        if mode == "bf16":
+            r16, m16 = ref(x.to(torch.bfloat16), team, alive), mine(x.to(torch.bfloat16), team, alive)
+    assert m.shape == r.shape and m.dtype == r.dtype
+    assert torch.isfinite(m).all()
+    if mode == "fp32":
+        err = float((m - r).abs().max())
+        assert err <= 1e-4, f"max-abs {err:.3e}"
+    else:
+        err = float((m.float() - r.float()).abs().max() / r.float().abs().max())
+        assert err <= 2e-2, f"normalised {err:.3e}"
+        assert m16.dtype == r16.dtype == torch.bfloat16
+        e16 = float((m16.float() - r16.float()).abs().max() / r16.float().abs().max())
+        assert e16 <= 2e-2, f"bf16 input, normalised {e16:.3e}"
+    # rows of a team without a living ship are exactly zero, as in the reference
+    rows = m[0][team[0] == 1]          # team 1 of environment 0 has no ship alive
+    if rows.numel():
+        assert float(rows.abs().max()) == 0.0
+    print(f"team_pma B={B} N={N} {mode}: {err:.2e}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_action_distribution_matches_torch_categorical(dtype):
+    """sample_action / evaluate_action against torch.distributions.Categorical over the three
+    logit slices, which is what the reference's _sample_action / _evaluate_action build
+    (policy.py:551-602): log-probability and entropy of given actions, and the empirical
+    distribution of 200 000 draws per slice (total variation below 1e-2)."""
+    import boost_and_broadside_b200 as bnb
+    from torch.distributions import Categorical
+
+    g = torch.Generator().manual_seed(3)
+    logits = (torch.randn(4, 7, 12, generator=g) * 2.0).to(DEV).to(dtype)
+    slices = ((0, 3), (3, 10), (10, 12))
+    actions = torch.stack([torch.randint(0, hi - lo, (4, 7), generator=g) for lo, hi in slices], -1).to(DEV)
+    dists = [Categorical(logits=logits[..., lo:hi]) for lo, hi in slices]
+    ref_lp = sum(d.log_prob(actions[..., i]) for i, d in enumerate(dists))
+    ref_ent = sum(d.entropy() for d in dists)
+    with torch.no_grad():
+        lp, ent = bnb.evaluate_action(logits, actions)
+    assert lp.dtype == ref_lp.dtype and lp.shape == ref_lp.shape
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    scale = 1.0 if dtype == torch.float32 else float(ref_lp.float().abs().max())
+    assert float((lp.float() - ref_lp.float()).abs().max()) <= tol * scale
+    assert float((ent.float() - ref_ent.float()).abs().max()) <= tol * max(1.0, float(ref_ent.float().abs().max()))
+
+    one = logits[0, 0].float().expand(200_000, 12).contiguous().to(dtype)
+    with torch.no_grad():
+        a, lp_s = bnb.sample_action(one, generator=torch.Generator(device=DEV).manual_seed(1))
+    assert a.dtype == torch.int64 and tuple(a.shape) == (200_000, 3)
+    for i, (lo, hi) in enumerate(slices):
+        want = torch.softmax(one[0, lo:hi].float(), -1)
+        got = torch.bincount(a[:, i], minlength=hi - lo).float() / a.shape[0]
+        assert float((got - want).abs().sum()) / 2 <= 1e-2, (i, got.tolist(), want.tolist())
+    # the log-probability returned with the draws is that of the drawn actions
+    lp_again, _ = bnb.evaluate_action(one, a)
+    assert torch.equal(lp_s, lp_again)

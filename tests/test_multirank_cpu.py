@@ -1,6 +1,6 @@
 """The N > 1 path on CPU: two gloo ranks shard the environments contiguously, run their
 shard with no data-path collective, and the pieces put together equal the single-rank result
-bit for bit (environments are independent).  The arithmetic here is the CPU oracle; the
+to float32 rounding (environments are independent).  The arithmetic here is the CPU oracle; the
 point of the test is the sharding and reduction logic that bench.py uses on GPUs."""
 
 import os
@@ -64,6 +64,12 @@ def test_env_shard_ranges():
         env_shard(4, 2, 2)
 
 
+# The shards run the same float32 arithmetic on smaller batches: the CPU matmul blocks its sums
+# differently for a different batch size, so the comparison is to float32 rounding of O(1)
+# activations, not to the bit.
+SHARD_ATOL = 5e-5
+
+
 def test_two_ranks_reproduce_the_single_rank_result(tmp_path):
     import boost_and_broadside_b200 as bnb
     from boost_and_broadside_b200 import workloads as W
@@ -81,20 +87,20 @@ def test_two_ranks_reproduce_the_single_rank_result(tmp_path):
 
     w = W.c2(n_envs=37, seed=11)
     y, h = O.trunk_step(w.x, w.alive, w.hidden, P, 4, "fp32")
-    assert torch.allclose(torch.cat([p["c2"][0] for p in parts]), y, atol=1e-5)
-    assert torch.allclose(torch.cat([p["c2"][1] for p in parts], dim=1), h, atol=1e-5)
+    assert torch.allclose(torch.cat([p["c2"][0] for p in parts]), y, atol=SHARD_ATOL)
+    assert torch.allclose(torch.cat([p["c2"][1] for p in parts], dim=1), h, atol=SHARD_ATOL)
 
     w = W.c2b(n_envs=11, seed=14, bullets_per_env=9)
     y, h = O.trunk_step(w.x, w.alive, w.hidden, P, 4, "fp32", w.bullets, w.bullet_mask)
-    assert torch.allclose(torch.cat([p["c2b"][0] for p in parts]), y, atol=1e-5)
-    assert torch.allclose(torch.cat([p["c2b"][1] for p in parts], dim=1), h, atol=1e-5)
+    assert torch.allclose(torch.cat([p["c2b"][0] for p in parts]), y, atol=SHARD_ATOL)
+    assert torch.allclose(torch.cat([p["c2b"][1] for p in parts], dim=1), h, atol=SHARD_ATOL)
 
     w = W.c4(n_envs=5, timesteps=4, seed=12)
     y, h = O.trunk_sequence(w.x, w.alive, w.hidden, w.done, P, 4, "fp32")
-    assert torch.allclose(torch.cat([p["c4"][0] for p in parts], dim=1), y, atol=1e-5)
-    assert torch.allclose(torch.cat([p["c4"][1] for p in parts], dim=1), h, atol=1e-5)
+    assert torch.allclose(torch.cat([p["c4"][0] for p in parts], dim=1), y, atol=SHARD_ATOL)
+    assert torch.allclose(torch.cat([p["c4"][1] for p in parts], dim=1), h, atol=SHARD_ATOL)
 
     w = W.c5(n_envs=21, seed=13, max_tokens=20)
     y, h = O.trunk_step_ragged(w.x, w.alive, w.hidden, w.n_tokens.tolist(), w.n_ships.tolist(), P, 4, "fp32")
-    assert torch.allclose(torch.cat([p["c5"][0] for p in parts]), y, atol=1e-5)
-    assert torch.allclose(torch.cat([p["c5"][1] for p in parts], dim=1), h, atol=1e-5)
+    assert torch.allclose(torch.cat([p["c5"][0] for p in parts]), y, atol=SHARD_ATOL)
+    assert torch.allclose(torch.cat([p["c5"][1] for p in parts], dim=1), h, atol=SHARD_ATOL)
