@@ -14,6 +14,7 @@ from .yemong.attention import GatedMLP, TransformerBlock
 from .yemong.encoder import BulletEncoder, ShipEncoder
 from .yemong.heads import HeadMLP, NextStateHead, TeamPMA, evaluate_action, sample_action
 from .yemong.griffin import CONV_KERNEL, RGLRU, GriffinTemporalBlock, YemongBlock
+from .yemong.policy import YemongPolicy
 from .yemong.trunk import YemongTrunk, RaggedBatch
 
 __all__ = [
@@ -30,6 +31,7 @@ __all__ = [
     "TeamPMA",
     "TransformerBlock",
     "YemongBlock",
+    "YemongPolicy",
     "YemongTrunk",
     "evaluate_action",
     "sample_action",

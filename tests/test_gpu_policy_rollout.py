@@ -1,0 +1,66 @@
+"""The whole rollout step on this package's kernels: ``YemongPolicy.get_action_and_value``
+(models/yemong/policy.py:291-373) with the reference's state_dict loaded, on the reference's own
+observation container and FeatureCoordinators, against the stock reference policy (oracle/_ref) run
+module by module on the same observation: value, next-state prediction, new hidden state, and the
+log-probability of the actions this package drew, scored under the reference's logits.
+
+Tolerances: float32 max-abs <= 1e-4; bf16 autocast normalised max error <= 2e-2.
+"""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from oracle import ref_runner
+from tests.test_gpu_encoders import _observation
+from tests.test_gpu_reference_policy import build_policies, step_from_tokens
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not ref_runner.available(), reason="oracle/_ref has not been built")]
+DEV = "cuda"
+
+
+@pytest.mark.parametrize("mode", ["fp32", "bf16"])
+@pytest.mark.parametrize("B,N,M,NB", [(24, 8, 4, 80), (7, 2, 0, 6)])
+def test_rollout_step_matches_the_reference_policy(B, N, M, NB, mode):
+    import boost_and_broadside_b200 as bnb
+    from torch.distributions import Categorical
+
+    stock, _ = build_policies(N)
+    with torch.no_grad():   # the default init leaves the win head and the seeds near zero
+        stock.team_pma.seeds.normal_(0.0, 0.5)
+        for p in stock.value_head_win.parameters():
+            p.add_(0.05 * torch.randn_like(p))
+    cfg = stock.yemong_layers[0]
+    ref_cfg = bnb.ModelConfig(d_model=128, n_heads=4, n_yemong_blocks=2, n_spatial_per_block=2, n_temporal_per_block=1,
+                              n_bullet_cross_per_block=1)
+    mine = bnb.YemongPolicy(ref_cfg, stock.coordinator, num_value_components=11, num_ships=N, team_pma_k=(0, 1),
+                            bullet_coordinator=stock.bullet_encoder.coordinator).to(DEV).eval()
+    assert list(mine.state_dict()) == list(stock.state_dict())
+    mine.load_state_dict(stock.state_dict(), strict=True)
+    del cfg
+
+    obs = _observation(B, N, M, NB, seed=B)
+    obs["alive"][:, 1] = False
+    hidden = torch.randn(mine.n_hidden_layers, B * N, 512, device=DEV) * 0.5
+    ctx = torch.autocast(DEV, dtype=torch.bfloat16) if mode == "bf16" else torch.autocast(DEV, enabled=False)
+    with torch.no_grad(), ctx:
+        x = stock.encoder(obs)
+        bullets, mask = stock._encode_bullets(obs)
+        logits, value, pred, new_hidden, _ = step_from_tokens(stock, x, obs["alive"], hidden, obs["team_id"], bullets, mask)
+        action, logprob, v, pn, nh = mine.get_action_and_value(obs, hidden, generator=torch.Generator(device=DEV).manual_seed(0))
+    assert tuple(action.shape) == (B, N, 3) and action.dtype == torch.int64
+    assert tuple(logprob.shape) == (B, N) and tuple(v.shape) == (B, N, 11)
+
+    def err(got, ref):
+        got, ref = got.float(), ref.float()
+        return float((got - ref).abs().max()) if mode == "fp32" else float((got - ref).abs().max() / ref.abs().max())
+
+    tol = 1e-4 if mode == "fp32" else 2e-2
+    errs = {"value": err(v, value), "pred_next": err(pn, pred), "hidden": err(nh, new_hidden)}
+    ref_lp = sum(Categorical(logits=logits[..., lo:hi]).log_prob(action[..., i]) for i, (lo, hi) in enumerate(((0, 3), (3, 10), (10, 12))))
+    errs["logprob"] = err(logprob, ref_lp)
+    print(f"rollout step B={B} N={N}+{M} NB={NB} {mode}: " + " ".join(f"{k} {e:.2e}" for k, e in errs.items()))
+    for k, e in errs.items():
+        assert e <= (tol if k != "logprob" or mode == "fp32" else 4e-2), f"{k}: {e:.3e}"
+    assert 0 <= int(action[..., 0].max()) < 3 and 0 <= int(action[..., 1].max()) < 7 and 0 <= int(action[..., 2].max()) < 2
