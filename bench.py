@@ -434,6 +434,52 @@ def time_train_step(trunk, dev: torch.device, n_envs: int = 1024, timesteps: int
     return out
 
 
+def time_other_workloads(trunk, dev: torch.device, n_params_all: int, cfg, steps: int = 5) -> dict:
+    """The other BASELINE configurations, device-timed like the headline (CUDA events, 3 warm-up
+    steps, inputs resident, bf16 autocast, float32 tokens): C3 (152-token fleets), C4 (the T = 32
+    sequence forward), C2B (C2 with 80 bullet slots per environment).  C5 is in c5_sharded."""
+    W = workloads_module()
+    hbm, tflops_burst, _, src = measured_peaks()
+    out: dict = {}
+    for name in ("C3", "C4", "C2B"):
+        try:
+            w = make_workload(name, 0, 1.0)
+            x, alive, hidden = w.x.to(dev), w.alive.to(dev), w.hidden.to(dev)
+            done = None if w.done is None else w.done.to(dev)
+            bul = None if w.bullets is None else w.bullets.to(dev)
+            bmask = None if w.bullet_mask is None else w.bullet_mask.to(dev)
+
+            def run(h):
+                if w.kind == "sequence":
+                    return trunk.sequence(x, alive, h, done)
+                return trunk.step(x, alive, h, bullets=bul, bullet_mask=bmask)
+
+            with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+                h = hidden
+                for _ in range(3):
+                    _, h2 = run(h)
+                    h = h if w.kind == "sequence" else h2
+                torch.cuda.synchronize(dev)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(steps):
+                    _, h2 = run(h)
+                    h = h if w.kind == "sequence" else h2
+                e1.record()
+                torch.cuda.synchronize(dev)
+            ms = e0.elapsed_time(e1) / steps
+            n_params = n_params_all if w.bullets is not None else sum(
+                p.numel() for n, p in trunk.named_parameters() if "bullet" not in n)
+            alg_bytes, alg_flops = W.algorithmic_bytes(w, n_params), W.algorithmic_flops(w, cfg)
+            out[name] = {"workload": WORKLOAD_TEXT[name], "ms_per_step": ms, "value": w.entity_tokens / (ms * 1e-3), "unit": UNIT,
+                         "steps": steps, "hbm_frac": alg_bytes / (ms * 1e-3) / 1e9 / hbm,
+                         "tensor_frac_of_burst": alg_flops / (ms * 1e-3) / 1e12 / tflops_burst, "of": src}
+            del x, alive, hidden, h, h2, w
+        except Exception as e:  # noqa: BLE001 - a side record that fails is reported, not fatal
+            out[name] = {"error": repr(e)[:200]}
+    return out
+
+
 def run_train_only(args) -> None:
     """Only this package's forward + backward record, on one GPU (the command the launch-list
     profile of the training step is taken with)."""
@@ -729,6 +775,9 @@ def run_ours(args) -> None:
                 if isinstance(ref.get(k), dict) and "value" in ref[k]:
                     ref[k]["ours_over_this"] = line["value"] / ref[k]["value"]
             line["gpu_reference"] = ref
+        if world == 1 and not args.no_others and args.workload == "C2":
+            line["other_workloads"] = time_other_workloads(
+                trunk, dev, sum(p.numel() for p in trunk.parameters()), cfg)
         if world == 1 and not args.no_train and args.workload == "C2":
             line["train_step"] = time_train_step(trunk, dev)
         if world == 1 and not args.no_cpu:
@@ -752,6 +801,7 @@ def main() -> None:
     ap.add_argument("--no-gpu-ref", action="store_true", help="skip the same-box GPU comparator (reference modules, eager and compiled)")
     ap.add_argument("--no-c5", action="store_true", help="skip the sharded ragged C5 record")
     ap.add_argument("--no-train", action="store_true", help="skip the forward + backward record (train_step)")
+    ap.add_argument("--no-others", action="store_true", help="skip the C3 / C4 / C2B records (other_workloads)")
     ap.add_argument("--train-only", action="store_true", help="only this package's forward + backward record (for profiling)")
     ap.add_argument("--train-envs", type=int, default=1024, help="environments of the forward + backward record")
     ap.add_argument("--shard", action="store_true",
