@@ -175,6 +175,13 @@ def _grad_precision(geom: List[int]) -> int:
     return _capi.BNB_BF16 if geom[G_PRECISION] == _capi.BNB_BF16 else _capi.BNB_FP32
 
 
+def _kept_size(geom: List[int], d_model: int, bullets_per_env: int) -> int:
+    """Bytes of the kept-activation buffer of a training forward (host arithmetic only)."""
+    need = _capi.lib.bnb_trunk_kept_bytes(geom[G_BLOCKS], geom[G_SPATIAL], geom[G_TEMPORAL], d_model, geom[G_HEADS],
+                                          _batch(geom, []), max(1, geom[G_TIMESTEPS]), bullets_per_env, _grad_precision(geom))
+    return max(256, int(need))
+
+
 def _sublayer_lists(weights: List[Tensor], n_blocks: int, n_spatial: int, n_temporal: int, n_cross: int, field_sub: int):
     """``weights`` cut into the per-sublayer lists, block-major, spatial before temporal."""
     spatial, temporal, pos = [], [], 0
@@ -324,9 +331,7 @@ def trunk_forward_train(
         bul = _capi.BulletArgs(bullets if n_cross > 0 else None, bullet_mask, T * batch.n_envs, D)
         y = torch.empty_like(xin)
         hout = torch.empty_like(hin)
-        kept = torch.empty(max(256, int(_capi.lib.bnb_trunk_kept_bytes(n_blocks, n_spatial, n_temporal, D, n_heads, batch, T,
-                                                                        bul.per_env, _grad_precision(geom)))),
-                           dtype=torch.uint8, device=dev)
+        kept = torch.empty(_kept_size(geom, D, bul.per_env), dtype=torch.uint8, device=dev)
         nbytes = _capi.lib.bnb_trunk_bwd_scratch_bytes(n_blocks, n_spatial, n_temporal, D, batch, T, bul.per_env,
                                                        _grad_precision(geom))
         scratch = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=dev)
@@ -345,8 +350,9 @@ def trunk_forward_train(
 @trunk_forward_train.register_fake
 def _trunk_forward_train_fake(x, alive, hidden, done, bullets, bullet_mask, weights, geom):
     out_dtype = torch.bfloat16 if x.dtype == torch.bfloat16 else torch.float32
+    per_env = bullets.shape[1] if bullets is not None and geom[G_BULLET_CROSS] > 0 else 0
     return (x.new_empty(x.shape, dtype=out_dtype), hidden.new_empty(hidden.shape, dtype=torch.float32),
-            x.new_empty(256, dtype=torch.uint8))
+            x.new_empty(_kept_size(geom, x.shape[-1], per_env), dtype=torch.uint8))
 
 
 def _train_setup_context(ctx, inputs, output):

@@ -8,6 +8,8 @@ sublayer, ``bnb_trunk_step`` / ``bnb_trunk_sequence`` (with one block) for a Yem
 
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.nn as nn
 
@@ -170,6 +172,15 @@ class GriffinTemporalBlock(nn.Module):
         return y.reshape(x.shape)
 
 
+def _keep(x: torch.Tensor, geom: list[int], n_bullets: int) -> bool:
+    """Keep activations for the backward, or recompute them?  While a compiler traces the call the
+    answer comes from BNB_GRAD_MODE alone (the memory query is a library call a tracer cannot see
+    through); otherwise ``_ops.keep_activations`` also looks at the free memory."""
+    if torch.compiler.is_compiling():
+        return os.environ.get("BNB_GRAD_MODE", "") != "recompute" and 0 < geom[_ops.G_MAX_TOKENS]
+    return _ops.keep_activations(x.device, geom, x.shape[-1], n_bullets)
+
+
 def run_trunk(
     blocks,
     n_heads: int,
@@ -212,7 +223,7 @@ def run_trunk(
     if (torch.is_grad_enabled() and not offsets and reset_env is None
             and (x.requires_grad or hidden.requires_grad or (bullets is not None and bullets.requires_grad)
                  or any(w.requires_grad for w in weights))
-            and _ops.keep_activations(x.device, geom, x.shape[-1], bullets.shape[1] if n_cross and bullets is not None else 0)):
+            and _keep(x, geom, bullets.shape[1] if n_cross and bullets is not None else 0)):
         # a call that will be differentiated: the forward that keeps its activations for the backward
         y, nh, _ = _ops.trunk_forward_train(x, alive, hidden, done, bullets if n_cross else None,
                                             bullet_mask if n_cross else None, weights, geom)
