@@ -332,3 +332,58 @@ def test_training_step_under_torch_compile(grad_mode):
     for k in gp0:
         assert norm_err(gp1[k], gp0[k]) <= 1e-4, k   # atomics: the last bits vary from run to run
     torch._dynamo.reset()
+
+
+@pytest.mark.skipif(not ref_runner.available(), reason="oracle/_ref has not been built")
+@pytest.mark.parametrize("mode", ["fp32", "bf16"])
+def test_reference_evaluate_actions_with_swapped_blocks(mode, grad_mode):
+    """``YemongPolicy.evaluate_actions`` itself (policy.py:379-516), the call ppo.py:1974 differentiates:
+    the reference's own policy, stock and with this package's blocks, on a (T, B, N+M) observation in
+    the reference's container with bullets and done flags; the reference's own loss of its
+    grad-checkpoint test (log-probability + value + next-state prediction, summed); outputs and the
+    gradient of every parameter of the policy -- encoders and heads included, which stay the
+    reference's modules and receive their gradient through this package's trunk backward."""
+    from tests.test_gpu_encoders import _observation
+    from tests.test_gpu_reference_policy import build_policies
+
+    T, B, N, M, NB = 4, 5, 8, 4, 12
+    stock, swapped = build_policies(N)
+    stock.train()
+    swapped.train()
+    flat = _observation(T * B, N, M, NB, seed=21)
+    obs = type(flat)(data={k: v.reshape(T, B, *v.shape[1:]) for k, v in flat.data.items()},
+                     bullets={k: v.reshape(T, B, *v.shape[1:]) for k, v in flat.bullets.items()})
+    gen = torch.Generator().manual_seed(2)
+    alive = obs["alive"].clone()
+    alive[:, :, 2] = False
+    actions = torch.stack([torch.randint(0, n, (T, B, N), generator=gen) for n in (3, 7, 2)], -1).to(DEV)
+    done = (torch.rand(T, B, generator=gen) < 0.25).to(DEV)
+    hidden = (torch.randn(2, B * N, 512, generator=gen) * 0.5).to(DEV)
+    results = []
+    for policy in (stock, swapped):
+        policy.zero_grad()
+        ctx = torch.autocast(DEV, dtype=torch.bfloat16) if mode == "bf16" else torch.autocast(DEV, enabled=False)
+        with ctx:
+            lp, ent, val, logits, _, pn = policy.evaluate_actions(obs, actions, hidden, alive, done)
+        (lp.float().sum() + val.float().sum() + pn.float().sum() + 0.1 * ent.float().sum()).backward()
+        results.append(((lp.float(), ent.float(), val.float(), logits.float(), pn.float()),
+                        {k: p.grad.float().clone() for k, p in policy.named_parameters() if p.grad is not None}))
+    tol = 1e-4 if mode == "fp32" else 3e-2
+    for name, got, ref in zip(("logprob", "entropy", "value", "logits", "pred_next"), results[1][0], results[0][0]):
+        assert norm_err(got, ref) <= tol, f"{name}: {norm_err(got, ref):.3e}"
+    worst, checked = ("", 0.0), 0
+    for k, ref in results[0][1].items():
+        got = results[1][1].get(k)
+        if got is None:
+            assert float(ref.abs().max()) == 0.0, k
+            continue
+        if float(ref.abs().max()) == 0.0:
+            assert float(got.abs().max()) == 0.0, k
+            continue
+        e = norm_err(got, ref)
+        assert e <= tol, f"{k}: normalised gradient error {e:.3e} > {tol:.0e}"
+        checked += 1
+        if e > worst[1]:
+            worst = (k, e)
+    assert checked > 80
+    print(f"evaluate_actions {mode} ({grad_mode}): {checked} parameter gradients, worst {worst[1]:.2e} ({worst[0]})")
