@@ -314,12 +314,16 @@ __device__ __forceinline__ void ffn(Epi& e) {
       o[q] = make_uint4(w[0], w[1], w[2], w[3]);
     }
     T_END(e.tacc, TE_FFN_MATH);
-    // the down projection of chunk c - 2 has read this buffer
+    // the down projection of chunk c - 2 is next in the schedule: its wait keeps the cursor in step
     T_WAITSLOT(e, TE_FFN_PF_WAIT);
     if (c >= 2) wait_ops(e, 1);
-#pragma unroll
-    for (int q = 0; q < 2; ++q)
-      *reinterpret_cast<uint4*>(e.smem + OFF_P + pi * CHUNK_BYTES + swz(e.row, e.part * 2 + q)) = o[q];
+    // The gated product stays in tensor memory as the A operand of the down projection: this
+    // thread's 16 k (8 columns of packed bf16 pairs) over the first half of its own 16 gate
+    // columns, which it has just read; K step `part` of the MMA reads exactly those columns.
+    {
+      const uint32_t w8[8] = {o[0].x, o[0].y, o[0].z, o[0].w, o[1].x, o[1].y, o[1].z, o[1].w};
+      tmem_st8(e.lane_addr + COL_ACC0 + ai * 128 + e.part * 16, w8);
+    }
     post(e, B_OP0 + pi);
   }
   // residual complete: the down projections of chunks 6 and 7
@@ -778,6 +782,28 @@ __device__ __forceinline__ void issue_op(Issuer& m, bool pair, uint32_t a_off0, 
   T_SINCE(m.tacc, TM_ISSUE, tw);
   TRACE(m.tr, 420);
 }
+// The same with the A operand in tensor memory: K step k reads the 8 columns at a_col + 16 k
+// (lane = row, a 32-bit column = two consecutive k as bfloat16).
+__device__ __forceinline__ void tc_mma_tmem_a(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %5};\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(0x40004040u) : "memory");
+}
+__device__ __forceinline__ void issue_down_tmem(Issuer& m, uint32_t a_col) {
+  const uint32_t slot = m.next_slot;
+  m.idx = m.idx + 1 == m.sched_len ? 0 : m.idx + 1;
+  m.next_slot = m.sched[m.idx] & 7u;
+  mbar_wait(m.bars + 8 * (B_FULL0 + slot), (m.full_par >> slot) & 1u, m.status, m.aborted, ST_TIMEOUT_FULL);
+  m.full_par ^= 1u << slot;
+  const uint32_t b_lo = desc_lo(m.sbase + slot_offset(slot));
+  const uint32_t idesc = instr_desc(128);
+#pragma unroll
+  for (uint32_t k = 0; k < 4; ++k) tc_mma_tmem_a(m.tmem + COL_RESID, m.tmem + a_col + 16 * k, b_lo + 2 * k, idesc, 1u);
+  tc_commit(m.bars + 8 * (B_DONE0 + slot));
+}
 __device__ __forceinline__ void issue_pair(Issuer& m, uint32_t a_off, uint32_t n, uint32_t d_col) {
   issue_op(m, true, a_off, a_off + CHUNK_BYTES, n, d_col, 0);
 }
@@ -790,7 +816,7 @@ __device__ __forceinline__ void issue_ffn(Issuer& m) {
 #pragma unroll 1
   for (int c = 0; c < 8; ++c) {
     wait_operand(m, c & 1);   // product of chunk c written, accumulator c % 3 read
-    issue_op(m, false, OFF_P + (c & 1) * CHUNK_BYTES, 0, 128, COL_RESID, 1);
+    issue_down_tmem(m, COL_ACC0 + 128 * (c % 3));
     if (c + 3 < 8) issue_pair(m, OFF_A, 128, COL_ACC0 + 128 * (c % 3));
   }
 }
