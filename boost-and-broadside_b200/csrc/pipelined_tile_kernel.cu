@@ -161,6 +161,17 @@ __device__ __forceinline__ int build_schedule(const SubLayer* subs, int n_sub, b
       rot.pair = 1;
       rot.single = 3;
       n = ffn_ops(out, n, si, 10, rot, 1);
+    } else if (subs[si].type == SUB_SPATIAL_PRE) {
+      // q|k|v only: the attention runs in a kernel of its own between this launch and the next
+      for (int h = 0; h < HEADS; ++h) {
+        const int ch = 5 * (h >> 1) + 2 * (h & 1);
+        out[n++] = sched_entry(rot.next_pair(), si, ch, ch + 1, false);
+      }
+    } else if (subs[si].type == SUB_SPATIAL_POST) {
+      // out_proj on the attention output read back from global memory, then the GatedMLP; nothing
+      // of this sublayer uses the key/value area, so no operation waits for it
+      out[n++] = sched_entry(rot.next_pair(), si, 4, 9, false);
+      n = ffn_ops(out, n, si, 10, rot, -1);
     } else {
       for (int i = 0; i < 6; ++i) {
         if (!has_fields && i == 4) continue;
@@ -487,6 +498,44 @@ __device__ __forceinline__ void run_spatial(Epi& e, int n_items, bool row_valid)
   __syncwarp();
   if ((threadIdx.x & 31) == 0) mbar_arrive(e.bars + 8 * B_KVREL);
   post(e, B_OP0);   // attention output in P
+  wait_round(e, 1);   // out_proj accumulated into the residual
+  norm_to_A(e);
+  post(e, B_OP0);
+  ffn(e);
+}
+
+// A spatial sublayer around a separate attention kernel (environments larger than a tile, or a
+// sublayer that reads bullets).  First part: norm1 and q|k|v of every head, written as bf16 to
+// global scratch, (rows, 384) = q | k | v with the heads side by side inside each third.
+__device__ __forceinline__ void run_spatial_pre(Epi& e, const SubLayer& s, size_t grow, bool row_valid) {
+  norm_to_A(e);
+  post(e, B_OP0);
+  wait_round(e, HEADS);   // q|k|v of head h in columns [128 + 96 h, +96)
+  const int h = e.part;
+  __nv_bfloat16* dst = s.qkv_out + grow * (3 * D) + h * DH;
+#pragma unroll
+  for (int p = 0; p < 3; ++p) {
+    uint32_t v[32];
+    tmem_ld32(e.lane_addr + COL_ACC0 + h * 96 + p * 32, v);
+    if (row_valid) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(dst + p * D + q * 8) = pack8(&v[q * 8]);
+    }
+  }
+  tc_fence_before();
+}
+// Second part: the attention output (bf16, (rows, 128)) becomes the A operand of out_proj, which
+// accumulates into the residual; then norm2 and the GatedMLP.
+__device__ __forceinline__ void run_spatial_post(Epi& e, const SubLayer& s, size_t grow, bool row_valid) {
+  const uint4* src = reinterpret_cast<const uint4*>(s.o_in + grow * D + e.part * 32);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int col = e.part * 32 + q * 8;
+    uint4 o = make_uint4(0u, 0u, 0u, 0u);
+    if (row_valid) o = src[q];
+    *reinterpret_cast<uint4*>(e.smem + OFF_A + (col >> 6) * CHUNK_BYTES + swz(e.row, (col & 63) >> 3)) = o;
+  }
+  post(e, B_OP0);
   wait_round(e, 1);   // out_proj accumulated into the residual
   norm_to_A(e);
   post(e, B_OP0);
@@ -830,6 +879,18 @@ __device__ __forceinline__ void issue_spatial(Issuer& m) {
   commit_round(m);
   issue_ffn(m);
 }
+__device__ __forceinline__ void issue_spatial_pre(Issuer& m) {
+  wait_operand(m, 0);
+#pragma unroll 1
+  for (int h = 0; h < HEADS; ++h) issue_pair(m, OFF_A, 96, COL_ACC0 + 96 * h);
+  commit_round(m);
+}
+__device__ __forceinline__ void issue_spatial_post(Issuer& m) {
+  wait_operand(m, 0);   // attention output in A: K atom 0 = heads 0, 1; K atom 1 = heads 2, 3
+  issue_op(m, true, OFF_A, OFF_A + CHUNK_BYTES, 128, COL_RESID, 1);
+  commit_round(m);
+  issue_ffn(m);
+}
 __device__ __forceinline__ void issue_temporal(Issuer& m, bool has_fields) {
   wait_operand(m, 0);
   issue_pair(m, OFF_A, 128, COL_ACC0);   // linear2
@@ -962,7 +1023,10 @@ __global__ void __launch_bounds__(THREADS, 1) k_trunk_pipelined(const __grid_con
       T_MARK(t_start);
       for (int pass = 0; pass < passes; ++pass)
         for (int si = 0; si < args.n_sub; ++si) {
-          if (s_sub[si].type == SUB_SPATIAL) issue_spatial(m);
+          const int type = s_sub[si].type;
+          if (type == SUB_SPATIAL) issue_spatial(m);
+          else if (type == SUB_SPATIAL_PRE) issue_spatial_pre(m);
+          else if (type == SUB_SPATIAL_POST) issue_spatial_post(m);
           else issue_temporal(m, args.has_fields != 0);
         }
       // Nothing issued here may outlive the CTA: its tensor memory is freed and its barriers go
@@ -1014,7 +1078,19 @@ __global__ void __launch_bounds__(THREADS, 1) k_trunk_pipelined(const __grid_con
       int env, tok, env_first, env_n, env_ships;
       size_t grow = 0;
       int hrow_if_ship;
-      if (args.tile_env_begin) {
+      if (args.flat_rows) {
+        // plain 128-row slices of the token rows (programs without attention inside: the
+        // environments are larger than a tile); the environment of a row is looked up
+        const int r = eb * TILE + row;
+        valid = r < map.total_tokens;
+        env = valid ? map.env_of_token(r) : 0;
+        env_first = 0;
+        env_n = 1;
+        tok = valid ? r - map.env_tok_begin(env) : 0;
+        env_ships = valid ? map.env_ship_count(env) : 0;
+        grow = (size_t)grp * map.total_tokens + (size_t)r;
+        hrow_if_ship = map.env_ship_begin(env) + tok;
+      } else if (args.tile_env_begin) {
         // ragged: the tile holds the environments tile_env_ids[k_lo .. k_hi), rows in that order
         const int k_lo = args.tile_env_begin[eb], k_hi = args.tile_env_begin[eb + 1];
         int k = k_lo, first = 0;
@@ -1113,6 +1189,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_trunk_pipelined(const __grid_con
             for (int l = 0; l < 4; ++l) asm volatile("prefetch.global.L2 [%0];" ::"l"(base + l * 128));
           }
           if (s.type == SUB_SPATIAL) run_spatial(e, n_items, valid);
+          else if (s.type == SUB_SPATIAL_PRE) run_spatial_pre(e, s, trow, valid);
+          else if (s.type == SUB_SPATIAL_POST) run_spatial_post(e, s, trow, valid);
           else run_temporal(e, s, rs, is_field, boundary, args.has_fields != 0, t == 0 ? s.hid_in : s.hid_out);
         }
         // y <- residual

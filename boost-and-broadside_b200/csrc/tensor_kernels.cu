@@ -1644,8 +1644,13 @@ static int launch(TrunkArgs& a, const BnbBatch& b, cudaStream_t st) {
   a.skip_op = g_debug_skip_op;
   if (a.n_tiles == 0) return BNB_OK;
   {
-    bool fused = !a.flat_rows;
-    for (int i = 0; i < a.n_sub; ++i) fused = fused && (a.sub[i].type == SUB_SPATIAL || a.sub[i].type == SUB_TEMPORAL);
+    // the pipelined kernel runs every program of spatial (whole or split around the attention
+    // kernel) and temporal sublayers; whole spatial sublayers need tiles of whole environments
+    bool fused = !a.row_index && !a.n_rows_dev;
+    for (int i = 0; i < a.n_sub; ++i) {
+      const int t = a.sub[i].type;
+      fused = fused && ((t == SUB_SPATIAL && !a.flat_rows) || t == SUB_TEMPORAL || t == SUB_SPATIAL_PRE || t == SUB_SPATIAL_POST);
+    }
     const char* force_old = getenv("BNB_OLD_TILE_KERNEL");
     if (fused && !(force_old && force_old[0] == '1')) return launch_pipelined(a, st);
   }
