@@ -7,8 +7,11 @@ names (``encoder``, ``bullet_encoder``, ``yemong_layers``, ``action_head``, ``va
 unchanged.  ``get_action_and_value`` (policy.py:291-373) runs, from the coordinators' raw feature
 vectors on: the encoder kernels, the trunk in one call on the packed state, the head kernels,
 TeamPMA and the action draw.  The ``FeatureCoordinator`` objects are the caller's and run as they
-are.  ``evaluate_actions`` is not mirrored here: its trunk loop is ``YemongTrunk.sequence`` (with
-the backward), its encoders and heads have no backward in this package.
+are.  ``evaluate_actions`` (policy.py:379-516) is mirrored as a forward: evaluation, crossover and
+logging call it without gradients.  For the PPO update itself -- ``evaluate_actions`` differentiated
+-- keep the reference's policy and swap its blocks for this package's ``YemongBlock``: the trunk then
+runs forward and backward here, and the reference's encoders and heads, which have no backward in
+this package, stay torch modules.
 """
 
 from __future__ import annotations
@@ -18,7 +21,7 @@ import torch.nn as nn
 
 from .encoder import BulletEncoder, ShipEncoder
 from .griffin import YemongBlock
-from .heads import HeadMLP, NextStateHead, TeamPMA, sample_action
+from .heads import HeadMLP, NextStateHead, TeamPMA, evaluate_action, sample_action
 from .trunk import YemongTrunk
 
 TOTAL_ACTION_LOGITS = 12  # constants.py:43
@@ -79,3 +82,33 @@ class YemongPolicy(YemongTrunk):
                 value[:, :, k] = win_val[:, :, i]
         action, logprob = sample_action(logits, generator)
         return action, logprob, value, pred_next, new_hidden
+
+    @torch.no_grad()
+    def evaluate_actions(self, obs, actions: torch.Tensor, initial_hidden: torch.Tensor, alive_mask: torch.Tensor,
+                         done_mask: torch.Tensor | None = None, return_encoder_output: bool = False):
+        """The rollout re-evaluated over T steps (policy.py:379-516), without gradients: obs with
+        (T, B, N+M, ...) tensors, actions (T, B, N, 3).  Returns (logprob (T, B, N), entropy (T, B, N),
+        value (T, B, N, K), logits (T, B, N, 12), encoder output or None, pred_next (T, B, N, pred_dim))."""
+        T, B, N = actions.shape[:3]
+        flat = type(obs)(
+            data={k: v.reshape(T * B, *v.shape[2:]) for k, v in obs.items()},
+            bullets=None if obs.bullets is None else {k: v.reshape(T * B, *v.shape[2:]) for k, v in obs.bullets.items()},
+        )
+        x = self.encoder(flat)
+        NM, D = x.shape[1], x.shape[2]
+        x = x.reshape(T, B, NM, D)
+        bullets, bullet_mask = self._encode_bullets(flat)
+        z = x if return_encoder_output else None
+        x, _ = self.sequence(x, alive_mask, initial_hidden, done_mask, bullets=bullets, bullet_mask=bullet_mask)
+        x_ships = x[:, :, :N, :].contiguous()
+        logits = self.action_head(x_ships)
+        pred_next = self.next_state_head(x_ships)
+        value = self.value_head_local(x_ships)
+        if self._team_pma_k:
+            pooled = self.team_pma(x_ships.reshape(T * B, N, D), obs["team_id"][:, :, :N].reshape(T * B, N),
+                                   alive_mask[:, :, :N].reshape(T * B, N))
+            win_val = self.value_head_win(pooled.reshape(T, B, N, D))
+            for i, k in enumerate(self._team_pma_k):
+                value[..., k] = win_val[..., i]
+        logprob, entropy = evaluate_action(logits, actions)
+        return logprob, entropy, value, logits, z, pred_next

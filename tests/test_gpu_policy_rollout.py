@@ -64,3 +64,45 @@ def test_rollout_step_matches_the_reference_policy(B, N, M, NB, mode):
     for k, e in errs.items():
         assert e <= (tol if k != "logprob" or mode == "fp32" else 4e-2), f"{k}: {e:.3e}"
     assert 0 <= int(action[..., 0].max()) < 3 and 0 <= int(action[..., 1].max()) < 7 and 0 <= int(action[..., 2].max()) < 2
+
+
+@pytest.mark.parametrize("mode", ["fp32", "bf16"])
+def test_evaluate_actions_forward_matches_the_reference_policy(mode):
+    """``YemongPolicy.evaluate_actions`` (policy.py:379-516) without gradients, on a (T, B, N+M)
+    observation with bullets and done flags, against the stock reference policy's own call."""
+    import boost_and_broadside_b200 as bnb
+
+    T, B, N, M, NB = 4, 6, 8, 4, 24
+    stock, _ = build_policies(N)
+    with torch.no_grad():
+        stock.team_pma.seeds.normal_(0.0, 0.5)
+        for p in stock.value_head_win.parameters():
+            p.add_(0.05 * torch.randn_like(p))
+    cfg = bnb.ModelConfig(d_model=128, n_heads=4, n_yemong_blocks=2, n_spatial_per_block=2, n_temporal_per_block=1,
+                          n_bullet_cross_per_block=1)
+    mine = bnb.YemongPolicy(cfg, stock.coordinator, num_value_components=11, num_ships=N, team_pma_k=(0, 1),
+                            bullet_coordinator=stock.bullet_encoder.coordinator).to(DEV).eval()
+    mine.load_state_dict(stock.state_dict(), strict=True)
+    flat = _observation(T * B, N, M, NB, seed=77)
+    obs = type(flat)(data={k: v.reshape(T, B, *v.shape[1:]) for k, v in flat.data.items()},
+                     bullets={k: v.reshape(T, B, *v.shape[1:]) for k, v in flat.bullets.items()})
+    gen = torch.Generator().manual_seed(5)
+    alive = obs["alive"].clone()
+    alive[:, :, 3] = False
+    actions = torch.stack([torch.randint(0, n, (T, B, N), generator=gen) for n in (3, 7, 2)], -1).to(DEV)
+    done = (torch.rand(T, B, generator=gen) < 0.25).to(DEV)
+    hidden = (torch.randn(2, B * N, 512, generator=gen) * 0.5).to(DEV)
+    ctx = torch.autocast(DEV, dtype=torch.bfloat16) if mode == "bf16" else torch.autocast(DEV, enabled=False)
+    with torch.no_grad(), ctx:
+        ref = stock.evaluate_actions(obs, actions, hidden, alive, done, return_encoder_output=True)
+        got = mine.evaluate_actions(obs, actions, hidden, alive, done, return_encoder_output=True)
+    names = ("logprob", "entropy", "value", "logits", "encoder output", "pred_next")
+    tol = 1e-4 if mode == "fp32" else 3e-2
+    report = []
+    for name, g, r in zip(names, got, ref):
+        assert g.shape == r.shape, (name, g.shape, r.shape)
+        g, r = g.float(), r.float()
+        e = float((g - r).abs().max()) if mode == "fp32" else float((g - r).abs().max() / r.abs().max())
+        assert e <= tol, f"{name}: {e:.3e}"
+        report.append(f"{name} {e:.1e}")
+    print(f"evaluate_actions forward {mode}: " + " ".join(report))
