@@ -335,8 +335,9 @@ def test_training_step_under_torch_compile(grad_mode):
 
 
 @pytest.mark.skipif(not ref_runner.available(), reason="oracle/_ref has not been built")
+@pytest.mark.parametrize("checkpoint", [False, True])
 @pytest.mark.parametrize("mode", ["fp32", "bf16"])
-def test_reference_evaluate_actions_with_swapped_blocks(mode, grad_mode):
+def test_reference_evaluate_actions_with_swapped_blocks(mode, grad_mode, checkpoint):
     """``YemongPolicy.evaluate_actions`` itself (policy.py:379-516), the call ppo.py:1974 differentiates:
     the reference's own policy, stock and with this package's blocks, on a (T, B, N+M) observation in
     the reference's container with bullets and done flags; the reference's own loss of its
@@ -350,6 +351,8 @@ def test_reference_evaluate_actions_with_swapped_blocks(mode, grad_mode):
     stock, swapped = build_policies(N)
     stock.train()
     swapped.train()
+    # the reference's grad_checkpoint switch (policy.py:451-467): torch.utils.checkpoint around each block
+    stock._grad_checkpoint = swapped._grad_checkpoint = checkpoint
     flat = _observation(T * B, N, M, NB, seed=21)
     obs = type(flat)(data={k: v.reshape(T, B, *v.shape[1:]) for k, v in flat.data.items()},
                      bullets={k: v.reshape(T, B, *v.shape[1:]) for k, v in flat.bullets.items()})
@@ -386,4 +389,4 @@ def test_reference_evaluate_actions_with_swapped_blocks(mode, grad_mode):
         if e > worst[1]:
             worst = (k, e)
     assert checked > 80
-    print(f"evaluate_actions {mode} ({grad_mode}): {checked} parameter gradients, worst {worst[1]:.2e} ({worst[0]})")
+    print(f"evaluate_actions {mode} ({grad_mode}, checkpoint {checkpoint}): {checked} parameter gradients, worst {worst[1]:.2e} ({worst[0]})")
