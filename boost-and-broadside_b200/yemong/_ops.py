@@ -216,7 +216,8 @@ def trunk_backward(
     """Gradients of ``trunk_forward`` (environments of one size, no ``reset_env``) through
     ``bnb_trunk_sequence_bwd``: float32 tensors throughout; after a forward under bf16 autocast the
     Linear products round their operands to bfloat16, as the reference's backward does there.  Returns
-    [d x, d hidden, d bullets (empty without bullets), then one gradient per tensor of ``weights``].
+    [d x, d hidden, d bullets (empty without bullets), every parameter gradient in one flat buffer
+    (``_split_grads`` cuts it into one view per tensor of ``weights``)].
     ``kept``: the activations ``trunk_forward_train`` kept for this call (the backward consumes
     them), or None: every sublayer's intermediates are recomputed."""
     dev = x.device
@@ -230,7 +231,10 @@ def trunk_backward(
         dho = None if dhidden_out is None else _capi.f32c(dhidden_out)
         alive_u8, done_u8 = _capi.u8(alive), _capi.u8(done)
         spatial, temporal = _sublayer_lists(weights, n_blocks, n_spatial, n_temporal, n_cross, field_sub)
-        grads = [torch.zeros_like(w, dtype=torch.float32) for w in weights]
+        # one zeroed buffer for every parameter gradient (the kernels accumulate into it), cut into
+        # views at 16-byte boundaries
+        flat_grads = torch.zeros(sum(_grad_sizes(weights)), dtype=torch.float32, device=dev)
+        grads = _split_grads(flat_grads, weights)
         g_spatial, g_temporal = _sublayer_lists(grads, n_blocks, n_spatial, n_temporal, n_cross, field_sub)
         sw = (_capi.SpatialWeights * max(1, len(spatial)))()
         tw = (_capi.TemporalWeights * max(1, len(temporal)))()
@@ -257,18 +261,31 @@ def trunk_backward(
             0 if kept is None else kept.numel(), scratch.data_ptr(), scratch.numel(), _capi.stream_handle(dev),
         )
     _capi.check("bnb_trunk_sequence_bwd", st)
-    return [dx, dh, dbul, *grads]
+    return [dx, dh, dbul, flat_grads]
 
 
 @trunk_backward.register_fake
 def _trunk_backward_fake(dy, dhidden_out, kept, x, alive, hidden, done, bullets, bullet_mask, weights, geom):
     dbul = x.new_empty(bullets.shape, dtype=torch.float32) if bullets is not None and geom[G_BULLET_CROSS] > 0 else x.new_empty(0, dtype=torch.float32)
     return [x.new_empty(x.shape, dtype=torch.float32), hidden.new_empty(hidden.shape, dtype=torch.float32), dbul,
-            *[w.new_empty(w.shape, dtype=torch.float32) for w in weights]]
+            x.new_empty(sum(_grad_sizes(weights)), dtype=torch.float32)]
+
+
+def _grad_sizes(weights: List[Tensor]) -> List[int]:
+    """Elements each parameter gradient takes in the flat buffer (16-byte granules)."""
+    return [(w.numel() + 3) // 4 * 4 for w in weights]
+
+
+def _split_grads(flat: Tensor, weights: List[Tensor]) -> List[Tensor]:
+    views, off = [], 0
+    for w, n in zip(weights, _grad_sizes(weights)):
+        views.append(flat[off : off + w.numel()].view(w.shape))
+        off += n
+    return views
 
 
 def _shape_grads(out, x, hidden, bullets, weights):
-    dx, dh, dbul, dws = out[0], out[1], out[2], out[3:]
+    dx, dh, dbul, dws = out[0], out[1], out[2], _split_grads(out[3], weights)
     dx = dx.reshape(x.shape).to(x.dtype)
     dh = dh.reshape(hidden.shape).to(hidden.dtype)
     dbul = dbul.reshape(bullets.shape).to(bullets.dtype) if bullets is not None and dbul.numel() else None
