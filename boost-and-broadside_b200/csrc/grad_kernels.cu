@@ -309,8 +309,10 @@ constexpr int TILE_H = BM * LDKH;
 template <bool A_KC, bool B_KC, bool A_H, bool B_H, bool C_H>
 __global__ void __launch_bounds__(GT, 2) k_gemm_bf16(GemmArgs g) {
   static_assert(TILE_H >= BK * LDRH, "either orientation fits the tile buffer");
-  __shared__ __align__(16) __nv_bfloat16 sA[2][TILE_H];
-  __shared__ __align__(16) __nv_bfloat16 sB[2][TILE_H];
+  // one buffer: two stages of A, two of B; a bfloat16 output tile is staged in it after the loop
+  __shared__ __align__(16) __nv_bfloat16 smem_all[4 * TILE_H];
+  __nv_bfloat16(*sA)[TILE_H] = reinterpret_cast<__nv_bfloat16(*)[TILE_H]>(smem_all);
+  __nv_bfloat16(*sB)[TILE_H] = reinterpret_cast<__nv_bfloat16(*)[TILE_H]>(smem_all + 2 * TILE_H);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, t = lane & 3;
   const int wm = (warp & 1) * 64, wn = (warp >> 1) * 32;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -413,6 +415,31 @@ __global__ void __launch_bounds__(GT, 2) k_gemm_bf16(GemmArgs g) {
     __syncthreads();
   }
 
+  if constexpr (C_H) {
+    // plain product, rounded once: the tile goes through shared memory so that every thread
+    // writes 16 contiguous bytes of a row (the loop's last barrier has freed the buffer)
+    constexpr int LDO = BN + 8;
+    static_assert(BM * LDO <= 4 * TILE_H, "the output tile fits the operand buffer");
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int half = 0; half < 2; ++half)
+          *reinterpret_cast<__nv_bfloat162*>(smem_all + (wm + mt * 16 + gq + half * 8) * LDO + wn + nt * 8 + 2 * t) =
+              __floats2bfloat162_rn(c[mt][nt][2 * half], c[mt][nt][2 * half + 1]);
+    __syncthreads();
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(g.C);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int idx = tid + i * GT;
+      const int row = idx >> 4, c8 = (idx & 15) * 8;
+      if (m0 + row < g.M && n0 + c8 < g.N)   // N is a multiple of 8
+        *reinterpret_cast<uint4*>(out + (size_t)(m0 + row) * g.ldc + n0 + c8) =
+            *reinterpret_cast<const uint4*>(smem_all + row * LDO + c8);
+    }
+    return;
+  }
 #pragma unroll
   for (int mt = 0; mt < 4; ++mt)
 #pragma unroll
@@ -424,10 +451,7 @@ __global__ void __launch_bounds__(GT, 2) k_gemm_bf16(GemmArgs g) {
         if (row < g.M && col < g.N) {
           float v0 = c[mt][nt][2 * half], v1 = c[mt][nt][2 * half + 1];
           float* cp = g.C + (size_t)row * g.ldc + col;
-          if constexpr (C_H) {   // plain product, rounded once
-            *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(g.C) + (size_t)row * g.ldc + col) =
-                __floats2bfloat162_rn(v0, v1);
-          } else if (g.atomic) {
+          if (g.atomic) {
             atomicAdd(cp, v0);
             atomicAdd(cp + 1, v1);
           } else {
