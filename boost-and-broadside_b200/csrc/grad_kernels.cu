@@ -496,8 +496,8 @@ void launch_gemm(GemmMode mode, const GemmArgs& g, dim3 grid, cudaStream_t st) {
   }
 }
 
-// Which operands of a bf16-mode product are stored as bfloat16.
-enum HalfOperand { H_NONE, H_A, H_B, H_C };
+// Which operands of a bf16-mode product are stored as bfloat16 (a bit mask).
+enum : int { H_A = 1, H_B = 2, H_C = 4 };
 
 void split_rows(GemmArgs& g, dim3& grid, int K) {
   const int tiles = grid.x * grid.y;
@@ -512,22 +512,32 @@ void split_rows(GemmArgs& g, dim3& grid, int K) {
   g.atomic = 1;
 }
 
-// The bf16-mode products that touch a bfloat16 buffer (gate / up / gated product of the MLP and
-// their gradients): A, B, C point to float32 or, for the operand `half` names, bfloat16 elements.
-void gemm_half(GemmMode mode, HalfOperand half, const void* A, int lda, const void* B, int ldb, void* C, int ldc, int M, int N,
-               int K, const float* R, int ldr, int beta, cudaStream_t st) {
-  if (M <= 0 || N <= 0 || K <= 0) return;
+// The bf16-mode products that touch a bfloat16 buffer (normed activations; gate / up / gated
+// product of the MLP and their gradients): A, B, C point to float32 or, for the operands `halves`
+// names, bfloat16 elements.
+int gemm_half(GemmMode mode, int halves, const void* A, int lda, const void* B, int ldb, void* C, int ldc, int M, int N, int K,
+              const float* bias, const float* R, int ldr, int beta, cudaStream_t st) {
+  if (M <= 0 || N <= 0 || K <= 0) return BNB_OK;
   GemmArgs g{static_cast<const float*>(A), lda, static_cast<const float*>(B), ldb, static_cast<float*>(C), ldc, M, N, K,
-             nullptr, R, ldr, beta, K, 0};
+             bias, R, ldr, beta, K, 0};
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, 1);
   count_launch();
   if (mode == TN) split_rows(g, grid, K);
-  if (mode == NT && half == H_C) k_gemm_bf16<true, true, false, false, true><<<grid, GT, 0, st>>>(g);
-  else if (mode == NT && half == H_A) k_gemm_bf16<true, true, true, false, false><<<grid, GT, 0, st>>>(g);
-  else if (mode == NN && half == H_C) k_gemm_bf16<true, false, false, false, true><<<grid, GT, 0, st>>>(g);
-  else if (mode == NN && half == H_A) k_gemm_bf16<true, false, true, false, false><<<grid, GT, 0, st>>>(g);
-  else if (mode == TN && half == H_A) k_gemm_bf16<false, false, true, false, false><<<grid, GT, 0, st>>>(g);
-  else if (mode == TN && half == H_B) k_gemm_bf16<false, false, false, true, false><<<grid, GT, 0, st>>>(g);
+#define BNB_GEMM_CASE(MODE, HALVES, AKC, BKC, AH, BH, CH) \
+  if (mode == MODE && halves == (HALVES)) { k_gemm_bf16<AKC, BKC, AH, BH, CH><<<grid, GT, 0, st>>>(g); return BNB_OK; }
+  BNB_GEMM_CASE(NT, 0, true, true, false, false, false)
+  BNB_GEMM_CASE(NT, H_A, true, true, true, false, false)
+  BNB_GEMM_CASE(NT, H_C, true, true, false, false, true)
+  BNB_GEMM_CASE(NT, H_A | H_C, true, true, true, false, true)
+  BNB_GEMM_CASE(NN, 0, true, false, false, false, false)
+  BNB_GEMM_CASE(NN, H_A, true, false, true, false, false)
+  BNB_GEMM_CASE(NN, H_C, true, false, false, false, true)
+  BNB_GEMM_CASE(TN, 0, false, false, false, false, false)
+  BNB_GEMM_CASE(TN, H_A, false, false, true, false, false)
+  BNB_GEMM_CASE(TN, H_B, false, false, false, true, false)
+  BNB_GEMM_CASE(TN, H_A | H_B, false, false, true, true, false)
+#undef BNB_GEMM_CASE
+  return BNB_ERR_BAD_ARGUMENT;   // a combination no caller uses
 }
 
 void gemm(GemmMode mode, const float* A, int lda, const float* B, int ldb, float* C, int ldc, int M, int N, int K,
@@ -557,6 +567,7 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 
 // n = x * rsqrt(mean(x^2) + eps) * g; the reciprocal root is kept for the backward.
+template <bool HALF_OUT>
 __global__ void __launch_bounds__(256) k_rmsnorm_fwd(const float* __restrict__ x, const float* __restrict__ g,
                                                      float* __restrict__ n, float* __restrict__ inv_out, int rows, int W) {
   const int lane = threadIdx.x & 31;
@@ -575,7 +586,11 @@ __global__ void __launch_bounds__(256) k_rmsnorm_fwd(const float* __restrict__ x
 #pragma unroll
     for (int i = 0; i < MAXW / 32; ++i) {
       const int cidx = lane + 32 * i;
-      if (cidx < W) n[(size_t)r * W + cidx] = v[i] * inv * g[cidx];
+      if (cidx < W) {
+        const float o = v[i] * inv * g[cidx];
+        if constexpr (HALF_OUT) reinterpret_cast<__nv_bfloat16*>(n)[(size_t)r * W + cidx] = __float2bfloat16_rn(o);
+        else n[(size_t)r * W + cidx] = o;
+      }
     }
   }
 }
@@ -1351,8 +1366,12 @@ enum PathKind { P_SPATIAL, P_SHIPS, P_FIELDS };
 
 void bind_forward(Arena& ar, Bufs& b, PathKind kind, size_t rows, int D, size_t RB, bool half_mlp) {
   const int nd = kind == P_SPATIAL ? 3 : kind == P_SHIPS ? 10 : 7;
-  for (int i = 0; i < nd; ++i) b.d[i] = ar.take(rows * D);
-  b.d[15] = ar.take(rows * D);
+  // the normed activations (slot 0 of a spatial path, slot 1 of a temporal one, slot 15 before the
+  // MLP) are bfloat16 in bf16 mode: half the floats
+  const size_t normed = half_mlp ? (rows * D + 1) / 2 : rows * D;
+  const int n_slot = kind == P_SPATIAL ? 0 : 1;
+  for (int i = 0; i < nd; ++i) b.d[i] = ar.take(i == n_slot ? normed : rows * D);
+  b.d[15] = ar.take(normed);
   b.inv[0] = ar.take(rows);
   b.inv[1] = ar.take(rows);
   if (kind == P_SPATIAL) {
@@ -1381,11 +1400,20 @@ void mm(const Ctx& c, GemmMode mode, const float* A, int lda, const float* B, in
         const float* bias = nullptr, const float* R = nullptr, int ldr = 0, int beta = 0) {
   gemm(mode, A, lda, B, ldb, C, ldc, M, N, K, bias, R, ldr, beta, c.st, c.bf16);
 }
+// The same for products whose operands `halves` names hold bfloat16 in bf16 mode (in float32 mode
+// the same buffers hold float32 and the mask is ignored).
+void mmh(const Ctx& c, GemmMode mode, int halves, const float* A, int lda, const float* B, int ldb, float* C, int ldc, int M, int N,
+         int K, const float* bias = nullptr, const float* R = nullptr, int ldr = 0, int beta = 0) {
+  if (c.bf16) gemm_half(mode, halves, A, lda, B, ldb, C, ldc, M, N, K, bias, R, ldr, beta, c.st);
+  else gemm(mode, A, lda, B, ldb, C, ldc, M, N, K, bias, R, ldr, beta, c.st, false);
+}
 
 void rmsnorm_fwd(const Ctx& c, const float* x, const float* g, float* n, float* inv, size_t rows) {
   if (!rows) return;
   count_launch();
-  k_rmsnorm_fwd<<<blocks_for(rows, 8), 256, 0, c.st>>>(x, g, n, inv, (int)rows, c.D);
+  // the normed activations only ever feed Linear products: in bf16 mode they are stored as bfloat16
+  if (c.bf16) k_rmsnorm_fwd<true><<<blocks_for(rows, 8), 256, 0, c.st>>>(x, g, n, inv, (int)rows, c.D);
+  else k_rmsnorm_fwd<false><<<blocks_for(rows, 8), 256, 0, c.st>>>(x, g, n, inv, (int)rows, c.D);
 }
 void rmsnorm_bwd(const Ctx& c, const float* x, const float* g, const float* inv, const float* dn, const float* dres,
                  float* dx, float* dg, size_t rows) {
@@ -1422,14 +1450,14 @@ void mlp_fwd(const Ctx& c, const float* x1, float* y, size_t rows, const float* 
   float *n2 = c.b.d[15], *gb = c.b.w4[0], *ub = c.b.w4[1], *hb = c.b.w4[2];
   rmsnorm_fwd(c, x1, g2, n2, c.b.inv[1], rows);
   if (c.bf16) {   // gate, up and their gated product are bfloat16 tensors, as under autocast
-    gemm_half(NT, H_C, n2, D, Wg, D, gb, F, M, F, D, nullptr, 0, 0, c.st);
-    gemm_half(NT, H_C, n2, D, Wu, D, ub, F, M, F, D, nullptr, 0, 0, c.st);
+    gemm_half(NT, H_A | H_C, n2, D, Wg, D, gb, F, M, F, D, nullptr, nullptr, 0, 0, c.st);
+    gemm_half(NT, H_A | H_C, n2, D, Wu, D, ub, F, M, F, D, nullptr, nullptr, 0, 0, c.st);
     if (rows) {
       count_launch();
       k_gelu_mul_fwd_h<<<blocks_for(rows * F / 8, 256), 256, 0, c.st>>>(reinterpret_cast<const uint4*>(gb), reinterpret_cast<const uint4*>(ub),
                                                                      reinterpret_cast<uint4*>(hb), rows * F / 8);
     }
-    if (y) gemm_half(NT, H_A, hb, F, Wd, F, y, D, M, D, F, x1, D, 0, c.st);
+    if (y) gemm_half(NT, H_A, hb, F, Wd, F, y, D, M, D, F, nullptr, x1, D, 0, c.st);
     return;
   }
   mm(c, NT, n2, D, Wg, D, gb, F, M, F, D);
@@ -1444,18 +1472,18 @@ void mlp_bwd(const Ctx& c, const float* x1, const float* dy, float* dx1, size_t 
   const int D = c.D, F = 4 * c.D, M = (int)rows;
   float *n2 = c.b.d[15], *dn2 = c.b.d[16], *gb = c.b.w4[0], *ub = c.b.w4[1], *hb = c.b.w4[2];
   if (c.bf16) {
-    gemm_half(TN, H_B, dy, D, hb, F, dWd, F, D, F, M, nullptr, 0, 0, c.st);
-    gemm_half(NN, H_C, dy, D, Wd, F, hb, F, M, F, D, nullptr, 0, 0, c.st);
+    gemm_half(TN, H_B, dy, D, hb, F, dWd, F, D, F, M, nullptr, nullptr, 0, 0, c.st);
+    gemm_half(NN, H_C, dy, D, Wd, F, hb, F, M, F, D, nullptr, nullptr, 0, 0, c.st);
     if (rows) {
       count_launch();
       k_gelu_mul_bwd_h<<<blocks_for(rows * F / 8, 256), 256, 0, c.st>>>(
           reinterpret_cast<const uint4*>(gb), reinterpret_cast<const uint4*>(ub), reinterpret_cast<const uint4*>(hb),
           reinterpret_cast<uint4*>(gb), reinterpret_cast<uint4*>(ub), rows * F / 8);
     }
-    gemm_half(TN, H_A, gb, F, n2, D, dWg, D, F, D, M, nullptr, 0, 0, c.st);
-    gemm_half(TN, H_A, ub, F, n2, D, dWu, D, F, D, M, nullptr, 0, 0, c.st);
-    gemm_half(NN, H_A, gb, F, Wg, D, dn2, D, M, D, F, nullptr, 0, 0, c.st);
-    gemm_half(NN, H_A, ub, F, Wu, D, dn2, D, M, D, F, nullptr, 0, 1, c.st);
+    gemm_half(TN, H_A | H_B, gb, F, n2, D, dWg, D, F, D, M, nullptr, nullptr, 0, 0, c.st);
+    gemm_half(TN, H_A | H_B, ub, F, n2, D, dWu, D, F, D, M, nullptr, nullptr, 0, 0, c.st);
+    gemm_half(NN, H_A, gb, F, Wg, D, dn2, D, M, D, F, nullptr, nullptr, 0, 0, c.st);
+    gemm_half(NN, H_A, ub, F, Wu, D, dn2, D, M, D, F, nullptr, nullptr, 0, 1, c.st);
     rmsnorm_bwd(c, x1, g2, c.b.inv[1], dn2, dy, dx1, dg2, rows);
     return;
   }
@@ -1533,10 +1561,10 @@ void spatial_fwd(const Ctx& c, const BnbSpatialWeights& w, const float* x, const
   const int nb = reads ? bul->per_env : 0;
   const size_t RB = (size_t)G * nb;
   rmsnorm_fwd(c, x, w.norm1_w, n1, b.inv[0], R);
-  mm(c, NT, n1, D, w.qkv_w, D, qkv, 3 * D, M, 3 * D, D);
+  mmh(c, NT, H_A, n1, D, w.qkv_w, D, qkv, 3 * D, M, 3 * D, D);
   if (reads) {
     rmsnorm_fwd(c, bul->tokens, w.norm_bullet_w, b.bul_n, b.bul_inv, RB);
-    mm(c, NT, b.bul_n, D, w.kv_bullet_w, D, b.kvb, 2 * D, (int)RB, 2 * D, D);
+    mmh(c, NT, H_A, b.bul_n, D, w.kv_bullet_w, D, b.kvb, 2 * D, (int)RB, 2 * D, D);
   }
   attn_fwd(c, qkv, alive, o, G, NM, reads ? b.kvb : nullptr, reads ? bul->active : nullptr, nb);
   mm(c, NT, o, D, w.out_w, D, x1, D, M, D, D, nullptr, x, D);            // x1 = x + o Wout^T
@@ -1571,13 +1599,13 @@ int spatial_bwd(const Ctx& c, const BnbSpatialWeights& w, const BnbSpatialGrads&
                       bul->active ? 1 : 0};
     rc = attn_bwd(c, cross, G);
     if (rc) return rc;
-    mm(c, TN, b.dkvb, 2 * D, b.bul_n, D, dw.kv_bullet_w, D, 2 * D, D, (int)RB);
+    mmh(c, TN, H_B, b.dkvb, 2 * D, b.bul_n, D, dw.kv_bullet_w, D, 2 * D, D, (int)RB);
     mm(c, NN, b.dkvb, 2 * D, w.kv_bullet_w, D, b.bul_dn, D, (int)RB, D, 2 * D);
     // the bullet tokens feed every sublayer that reads them: their gradient accumulates
     float* sink = d_bullets ? d_bullets : b.bul_n;   // bul_n is free once the weight gradient above is queued
     rmsnorm_bwd(c, bul->tokens, w.norm_bullet_w, b.bul_inv, b.bul_dn, d_bullets, sink, dw.norm_bullet_w, RB);
   }
-  mm(c, TN, dqkv, 3 * D, n1, D, dw.qkv_w, D, 3 * D, D, M);
+  mmh(c, TN, H_B, dqkv, 3 * D, n1, D, dw.qkv_w, D, 3 * D, D, M);
   mm(c, NN, dqkv, 3 * D, w.qkv_w, D, dn1, D, M, D, 3 * D);
   rmsnorm_bwd(c, x, w.norm1_w, b.inv[0], dn1, dx1, dx, dw.norm1_w, R);
   return BNB_OK;
@@ -1619,7 +1647,7 @@ void ships_fwd(const Ctx& c, const BnbTemporalWeights& w, const float* x, const 
   const int sblocks = (int)(((size_t)Rr * D + 255) / 256);
   gather(c, x, xs, Rs, tg.n_rec, tg.NM, 0);
   rmsnorm_fwd(c, xs, w.norm1_w, n, b.inv[0], Rs);
-  mm(c, NT, n, D, w.linear1_w, D, b1, D, M, D, D);
+  mmh(c, NT, H_A, n, D, w.linear1_w, D, b1, D, M, D, D);
   count_launch();
   k_conv_fwd<<<sblocks, 256, 0, c.st>>>(b1, hid, w.conv_w, w.conv_b, u, gm);
   mm(c, NT, u, D, w.a_w, D, za, D, M, D, D, w.a_b);
@@ -1630,7 +1658,7 @@ void ships_fwd(const Ctx& c, const BnbTemporalWeights& w, const float* x, const 
     count_launch();
     k_final_state<<<sblocks, 256, 0, c.st>>>(hs, b1, hid, hid_out, gm);
   }
-  mm(c, NT, n, D, w.linear2_w, D, b2p, D, M, D, D);
+  mmh(c, NT, H_A, n, D, w.linear2_w, D, b2p, D, M, D, D);
   gelu_mul_fwd(c, b2p, hs, m, Rs * D);                                  // m = h * gelu(linear2 n)
   mm(c, NT, m, D, w.out_w, D, x1, D, M, D, D, nullptr, xs, D);
   mlp_fwd(c, x1, y ? b.d[14] : nullptr, Rs, w.norm2_w, w.gate_w, w.up_w, w.down_w);
@@ -1647,9 +1675,9 @@ void fields_fwd(const Ctx& c, const BnbTemporalWeights& w, const float* x, float
   float *xf = b.d[0], *n = b.d[1], *c1 = b.d[2], *b1 = b.d[3], *b2p = b.d[4], *m = b.d[5], *x1 = b.d[6];
   gather(c, x, xf, Rf, nf, tg.NM, tg.n_rec);
   rmsnorm_fwd(c, xf, w.norm1_w, n, b.inv[0], Rf);
-  mm(c, NT, n, D, w.linear1_w, D, c1, D, M, D, D);
+  mmh(c, NT, H_A, n, D, w.linear1_w, D, c1, D, M, D, D);
   mm(c, NT, c1, D, w.field_sub_w, D, b1, D, M, D, D);
-  mm(c, NT, n, D, w.linear2_w, D, b2p, D, M, D, D);
+  mmh(c, NT, H_A, n, D, w.linear2_w, D, b2p, D, M, D, D);
   gelu_mul_fwd(c, b2p, b1, m, Rf * D);
   mm(c, NT, m, D, w.out_w, D, x1, D, M, D, D, nullptr, xf, D);
   mlp_fwd(c, x1, y ? b.d[14] : nullptr, Rf, w.norm2_w, w.gate_w, w.up_w, w.down_w);
@@ -1688,7 +1716,7 @@ int temporal_bwd(const Ctx& cs, const Ctx& cf, const BnbTemporalWeights& w, cons
     mm(c, TN, dx1, D, m, D, dw.out_w, D, D, D, M);
     mm(c, NN, dx1, D, w.out_w, D, dm, D, M, D, D);
     gelu_mul_bwd(c, b2p, hs, dm, b2p, dm, Rs * D);                      // b2p <- d linear2 out, dm <- d h
-    mm(c, TN, b2p, D, n, D, dw.linear2_w, D, D, D, M);
+    mmh(c, TN, H_B, b2p, D, n, D, dw.linear2_w, D, D, D, M);
     mm(c, NN, b2p, D, w.linear2_w, D, dn, D, M, D, D);
     count_launch();
     k_scan_bwd<<<sblocks, 256, 0, c.st>>>(za, zx, u, hs, dm, hid, d_hid_out, d_hid_in, w.log_lambda, dw.log_lambda, gm);
@@ -1702,7 +1730,7 @@ int temporal_bwd(const Ctx& cs, const Ctx& cf, const BnbTemporalWeights& w, cons
     float* db1 = za;   // free now
     count_launch();
     k_conv_bwd<<<sblocks, 256, 0, c.st>>>(dm, b1, hid, d_hid_out, d_hid_in, w.conv_w, db1, dw.conv_w, dw.conv_b, gm);
-    mm(c, TN, db1, D, n, D, dw.linear1_w, D, D, D, M);
+    mmh(c, TN, H_B, db1, D, n, D, dw.linear1_w, D, D, D, M);
     mm(c, NN, db1, D, w.linear1_w, D, dn, D, M, D, D, nullptr, nullptr, 0, 1);
     rmsnorm_bwd(c, xs, w.norm1_w, b.inv[0], dn, dx1, dxs, dw.norm1_w, Rs);
     scatter(c, dxs, dx, Rs, tg.n_rec, tg.NM, 0);
@@ -1723,9 +1751,9 @@ int temporal_bwd(const Ctx& cs, const Ctx& cf, const BnbTemporalWeights& w, cons
     gelu_mul_bwd(c, b2p, b1, dm, b2p, dm, Rf * D);                      // b2p <- d linear2 out, dm <- d b1
     mm(c, TN, dm, D, c1, D, dw.field_sub_w, D, D, D, M);
     mm(c, NN, dm, D, w.field_sub_w, D, dc1, D, M, D, D);
-    mm(c, TN, dc1, D, n, D, dw.linear1_w, D, D, D, M);
+    mmh(c, TN, H_B, dc1, D, n, D, dw.linear1_w, D, D, D, M);
     mm(c, NN, dc1, D, w.linear1_w, D, dn, D, M, D, D);
-    mm(c, TN, b2p, D, n, D, dw.linear2_w, D, D, D, M);
+    mmh(c, TN, H_B, b2p, D, n, D, dw.linear2_w, D, D, D, M);
     mm(c, NN, b2p, D, w.linear2_w, D, dn, D, M, D, D, nullptr, nullptr, 0, 1);
     rmsnorm_bwd(c, xf, w.norm1_w, b.inv[0], dn, dx1, dxf, dw.norm1_w, Rf);
     scatter(c, dxf, dx, Rf, nf, tg.NM, tg.n_rec);
