@@ -1184,7 +1184,7 @@ __global__ void __launch_bounds__(128 * NQ, NQ == 4 ? 1 : 2) k_trunk_tiles(const
 //
 // One CTA per (environment, head): q, k, v of that head are staged from the bf16 scratch the
 // PRE phase wrote, then each warp takes blocks of 16 query rows and walks the keys in blocks of
-// 16 with a running maximum (mma.sync, fp32 softmax).  Dead keys score kMaskedScore, so their
+// 32 with a running maximum (mma.sync, fp32 softmax).  Dead keys score kMaskedScore, so their
 // weight is exactly 0 unless no key of the environment is alive, in which case every key gets
 // the same weight (models/yemong/attention.py:101-112 of the reference).  When the sublayer
 // reads bullets, the environment's bullet keys and values (written by the BULLET_KV phase) are
@@ -1194,54 +1194,56 @@ __global__ void __launch_bounds__(128 * NQ, NQ == 4 ? 1 : 2) k_trunk_tiles(const
 // a staged row holds HPC x 32 bf16 plus 16 bytes of padding, which keeps ldmatrix conflict-free.
 __host__ __device__ constexpr int flash_stride(int hpc) { return hpc * 64 + 16; }
 
-// One softmax pass of a block of 16 queries (fragments qa) over n keys staged at sK / sV with
-// liveness bytes `live`; returns the normalised output fragments in acc.
+// One softmax pass of a block of 16 queries (fragments qa) over n keys staged at sK / sV; returns
+// the normalised output fragments in acc.  Keys are walked 32 at a time.  `bias` holds one float
+// per key, padded to a multiple of 32: 0 for a live key, kMaskedScore for a dead one, -inf beyond
+// n.  Scores are carried in the log2 domain: t = (q.k) * log2(e) / sqrt(32) + bias, p = 2^(t - max).
 __device__ __forceinline__ void flash_pass(const uint32_t (&qa)[2][4], uint32_t sK, uint32_t sV, int stride,
-                                           const uint8_t* __restrict__ live, int n, int lane, float (&acc)[4][4]) {
+                                           const float* __restrict__ bias, int n, int lane, float (&acc)[4][4]) {
   const int t = lane & 3;
-  const float scale = 0.17677669529663687f;
+  const float c2 = 0.17677669529663687f * 1.4426950408889634f;
   const int last = n - 1;
-  const int nkb = (n + 15) >> 4;
+  const int nkb = (n + 31) >> 5;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 #pragma unroll
   for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
   for (int kb = 0; kb < nkb; ++kb) {
-    float sc[2][4];
+    float sc[4][4];
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
+    for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
       for (int i = 0; i < 4; ++i) sc[nt][i] = 0.f;
-    const int krow = min(kb * 16 + (lane >> 4) * 8 + (lane & 7), last);
 #pragma unroll
-    for (int ks = 0; ks < 2; ++ks) {
-      uint32_t b0, b1, b2, b3;
-      ldsm_x4(sK + krow * stride + (ks * 16 + ((lane >> 3) & 1) * 8) * 2, b0, b1, b2, b3);
-      mma_bf16(sc[0], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
-      mma_bf16(sc[1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b2, b3);
+    for (int h = 0; h < 2; ++h) {
+      const int krow = min(kb * 32 + h * 16 + (lane >> 4) * 8 + (lane & 7), last);
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(sK + krow * stride + (ks * 16 + ((lane >> 3) & 1) * 8) * 2, b0, b1, b2, b3);
+        mma_bf16(sc[2 * h], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+        mma_bf16(sc[2 * h + 1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b2, b3);
+      }
     }
     float bm0 = -INFINITY, bm1 = -INFINITY;
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int j = kb * 16 + nt * 8 + 2 * t + i;
-        const bool valid = j < n;
-        const bool lv = valid && (!live || live[j]);
-        const float a = valid ? (lv ? sc[nt][i] * scale : kMaskedScore) : -INFINITY;
-        const float b = valid ? (lv ? sc[nt][2 + i] * scale : kMaskedScore) : -INFINITY;
-        sc[nt][i] = a;
-        sc[nt][2 + i] = b;
-        bm0 = fmaxf(bm0, a);
-        bm1 = fmaxf(bm1, b);
-      }
+    for (int nt = 0; nt < 4; ++nt) {
+      // a dead key's bias swallows its score: kMaskedScore exactly (weight 0 unless every key is dead)
+      const float2 bj = *reinterpret_cast<const float2*>(bias + kb * 32 + nt * 8 + 2 * t);
+      sc[nt][0] = fmaf(sc[nt][0], c2, bj.x);
+      sc[nt][1] = fmaf(sc[nt][1], c2, bj.y);
+      sc[nt][2] = fmaf(sc[nt][2], c2, bj.x);
+      sc[nt][3] = fmaf(sc[nt][3], c2, bj.y);
+      bm0 = fmaxf(bm0, fmaxf(sc[nt][0], sc[nt][1]));
+      bm1 = fmaxf(bm1, fmaxf(sc[nt][2], sc[nt][3]));
+    }
     bm0 = fmaxf(bm0, __shfl_xor_sync(0xffffffffu, bm0, 1));
     bm0 = fmaxf(bm0, __shfl_xor_sync(0xffffffffu, bm0, 2));
     bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, 1));
     bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, 2));
-    const float n0 = fmaxf(m0, bm0), n1 = fmaxf(m1, bm1);   // finite: every block holds a valid key
-    const float c0 = __expf(m0 - n0), c1 = __expf(m1 - n1); // exp(-inf) = 0 on the first block
+    const float n0 = fmaxf(m0, bm0), n1 = fmaxf(m1, bm1);       // finite: every block holds a valid key
+    const float c0 = ex2_fast(m0 - n0), c1 = ex2_fast(m1 - n1); // 2^(-inf) = 0 on the first block
     m0 = n0;
     m1 = n1;
     l0 *= c0;
@@ -1252,24 +1254,26 @@ __device__ __forceinline__ void flash_pass(const uint32_t (&qa)[2][4], uint32_t 
       acc[nt][2] *= c1; acc[nt][3] *= c1;
     }
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
+    for (int nt = 0; nt < 4; ++nt) {
+      sc[nt][0] = ex2_fast(sc[nt][0] - m0);
+      sc[nt][1] = ex2_fast(sc[nt][1] - m0);
+      sc[nt][2] = ex2_fast(sc[nt][2] - m1);
+      sc[nt][3] = ex2_fast(sc[nt][3] - m1);
+      l0 += sc[nt][0] + sc[nt][1];
+      l1 += sc[nt][2] + sc[nt][3];
+    }
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const float a = __expf(sc[nt][i] - m0), b = __expf(sc[nt][2 + i] - m1);
-        sc[nt][i] = a;
-        sc[nt][2 + i] = b;
-        l0 += a;
-        l1 += b;
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t a0 = pack_bf16(sc[2 * h][0], sc[2 * h][1]), a1 = pack_bf16(sc[2 * h][2], sc[2 * h][3]);
+      const uint32_t a2 = pack_bf16(sc[2 * h + 1][0], sc[2 * h + 1][1]), a3 = pack_bf16(sc[2 * h + 1][2], sc[2 * h + 1][3]);
+      const int vrow = min(kb * 32 + h * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), last);
+#pragma unroll
+      for (int np = 0; np < 2; ++np) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(sV + vrow * stride + ((np * 2 + (lane >> 4)) * 8) * 2, b0, b1, b2, b3);
+        mma_bf16(acc[np * 2], a0, a1, a2, a3, b0, b1);
+        mma_bf16(acc[np * 2 + 1], a0, a1, a2, a3, b2, b3);
       }
-    const uint32_t a0 = pack_bf16(sc[0][0], sc[0][1]), a1 = pack_bf16(sc[0][2], sc[0][3]);
-    const uint32_t a2 = pack_bf16(sc[1][0], sc[1][1]), a3 = pack_bf16(sc[1][2], sc[1][3]);
-    const int vrow = min(kb * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), last);
-#pragma unroll
-    for (int np = 0; np < 2; ++np) {
-      uint32_t b0, b1, b2, b3;
-      ldsm_x4_t(sV + vrow * stride + ((np * 2 + (lane >> 4)) * 8) * 2, b0, b1, b2, b3);
-      mma_bf16(acc[np * 2], a0, a1, a2, a3, b0, b1);
-      mma_bf16(acc[np * 2 + 1], a0, a1, a2, a3, b2, b3);
     }
   }
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
@@ -1289,8 +1293,9 @@ __device__ __forceinline__ void flash_pass(const uint32_t (&qa)[2][4], uint32_t 
 // environment i of the launch owning rows [env_off[i], env_off[i+1]) (an inactive bullet has
 // weight exactly 0 and an environment without active bullets is gated off, so neither needs a
 // row); without env_off, nb rows per environment, all of them keys (no mask was given).
-// blockIdx.y selects a group of hpc heads; the warps share out (head, query block) pairs.
-__global__ void __launch_bounds__(128) k_attention_flash(const __nv_bfloat16* __restrict__ qkv, const uint8_t* __restrict__ alive,
+// blockIdx.y selects a group of hpc heads; the warps (4 to 8, chosen by the launcher so that the
+// (head, query block) pairs divide evenly) share the pairs out.
+__global__ void __launch_bounds__(256) k_attention_flash(const __nv_bfloat16* __restrict__ qkv, const uint8_t* __restrict__ alive,
                                                          __nv_bfloat16* __restrict__ o, EnvMap map, int env_base, int hpc,
                                                          const __nv_bfloat16* __restrict__ kvb,
                                                          const int* __restrict__ env_off, int nb) {
@@ -1314,7 +1319,9 @@ __global__ void __launch_bounds__(128) k_attention_flash(const __nv_bfloat16* __
   uint8_t* Vs = Ks + (size_t)n * stride;
   uint8_t* Kb = Vs + (size_t)n * stride;
   uint8_t* Vb = Kb + (size_t)nb * stride;
-  uint8_t* live = Vb + (size_t)nb * stride;
+  float* bias_s = reinterpret_cast<float*>(Vb + (size_t)nb * stride);   // strides are multiples of 16 bytes
+  const int n32 = (n + 31) & ~31, nb32 = (nb + 31) & ~31;
+  float* bias_b = bias_s + n32;
   const int gpr = hpc * 4;   // 16-byte groups per staged row
   // asynchronous 16-byte copies: all of them are in flight before the first one is waited for
   for (int i = threadIdx.x; i < n * 3 * gpr; i += blockDim.x) {
@@ -1328,14 +1335,17 @@ __global__ void __launch_bounds__(128) k_attention_flash(const __nv_bfloat16* __
                kvb + (brow0 + r) * (2 * D) + part * D + hd0 * DH + q * 8);
   }
   asm volatile("cp.async.commit_group;" ::: "memory");
-  for (int i = threadIdx.x; i < n; i += blockDim.x) live[i] = alive ? alive[tok0 + i] : (uint8_t)1;
+  for (int i = threadIdx.x; i < n32; i += blockDim.x)
+    bias_s[i] = i < n ? ((!alive || alive[tok0 + i]) ? 0.f : kMaskedScore) : -INFINITY;
+  for (int i = threadIdx.x; i < nb32; i += blockDim.x) bias_b[i] = i < nb ? 0.f : -INFINITY;
   asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int last = n - 1;
   const int nqb = (n + 15) >> 4;
-  for (int item = warp; item < hpc * nqb; item += 4) {
+  const int n_warps = blockDim.x >> 5;
+  for (int item = warp; item < hpc * nqb; item += n_warps) {
     const int hl = item % hpc, qb = item / hpc;
     const uint32_t hoff = (uint32_t)hl * 64;
     const uint32_t sQ = smem_u32(Qs) + hoff, sK = smem_u32(Ks) + hoff, sV = smem_u32(Vs) + hoff;
@@ -1347,10 +1357,10 @@ __global__ void __launch_bounds__(128) k_attention_flash(const __nv_bfloat16* __
         ldsm_x4(sQ + row * stride + (ks * 16 + (lane >> 4) * 8) * 2, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3]);
     }
     float acc[4][4];
-    flash_pass(qa, sK, sV, stride, live, n, lane, acc);
+    flash_pass(qa, sK, sV, stride, bias_s, n, lane, acc);
     if (nb > 0) {
       float accb[4][4];
-      flash_pass(qa, smem_u32(Kb) + hoff, smem_u32(Vb) + hoff, stride, nullptr, nb, lane, accb);
+      flash_pass(qa, smem_u32(Kb) + hoff, smem_u32(Vb) + hoff, stride, bias_b, nb, lane, accb);
       // both outputs are bf16 tensors in the reference; so is their sum
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt)
@@ -1503,7 +1513,8 @@ int plan_tiles(const int32_t* tok_off, int n_envs, int32_t* tile_env_begin, int3
 static size_t round256(size_t v) { return (v + 255) / 256 * 256; }
 // Shared memory of the attention kernel for environments of up to max_tokens tokens and nb bullets.
 static size_t flash_smem(int max_tokens, int nb, int hpc) {
-  return (size_t)(3 * max_tokens + 2 * nb) * flash_stride(hpc) + (size_t)max_tokens + (size_t)nb + 16;
+  // staged q, k, v (and bullet k, v) rows, then one bias float per key, each set padded to 32 keys
+  return (size_t)(3 * max_tokens + 2 * nb) * flash_stride(hpc) + 4 * (size_t)(((max_tokens + 31) & ~31) + ((nb + 31) & ~31)) + 16;
 }
 constexpr size_t FLASH_SMEM_MAX = 227 * 1024;
 // All four heads in one CTA while that leaves room for three CTAs per SM, else one head per CTA.
@@ -1729,8 +1740,15 @@ static int launch_attention(const __nv_bfloat16* qkv, const uint8_t* alive, __nv
   const size_t smem = flash_smem(b.max_tokens_per_env, kvb ? nb : 0, hpc);
   if (smem > FLASH_SMEM_MAX) return BNB_ERR_TOO_MANY_TOKENS;
   dim3 grid(n_env, HEADS / hpc);
+  // warps per CTA: the fewest idle warp-rounds over the (head, query block) pairs of a full environment
+  const int items = hpc * ((b.max_tokens_per_env + 15) / 16);
+  int n_warps = 4, best_idle = 1 << 30;
+  for (int w = 4; w <= 8; ++w) {
+    const int idle = (items + w - 1) / w * w - items;
+    if (idle < best_idle) { best_idle = idle; n_warps = w; }
+  }
   count_launch();
-  k_attention_flash<<<grid, 128, smem, st>>>(qkv, alive, o, make_env_map(b), env_base, hpc, kvb, env_off, nb);
+  k_attention_flash<<<grid, 32 * n_warps, smem, st>>>(qkv, alive, o, make_env_map(b), env_base, hpc, kvb, env_off, nb);
   return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
 }
 
