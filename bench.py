@@ -356,6 +356,71 @@ def time_gpu_reference(name: str, dev: torch.device, steps: int) -> dict:
     return out
 
 
+def time_policy_step(dev: torch.device, n_envs: int = 8192, n_ships: int = 8, n_fields: int = 4, n_bullets: int = 80,
+                     steps: int = 10) -> dict:
+    """The whole rollout step of the policy, ``get_action_and_value`` (models/yemong/policy.py:291-373):
+    FeatureCoordinator transforms, ship and bullet encoders, trunk step with bullets, the four heads,
+    TeamPMA and the action draw, on one seeded random observation of `n_envs` environments under
+    torch.autocast('cuda', bfloat16).  This package's YemongPolicy with the reference's state_dict
+    loaded, against the reference's own policy from oracle/_ref, eager and torch.compile
+    (mode="reduce-overhead", how the reference runs it: train/rl/ppo.py:396-400).  CUDA events."""
+    from oracle import ref_runner
+
+    if not ref_runner.available():
+        return {"unavailable": "oracle/_ref is absent"}
+    import boost_and_broadside_b200 as bnb
+    from boost_and_broadside_b200 import _capi
+
+    stock = ref_runner.reference_policy(n_ships).to(dev)
+    cfg = bnb.ModelConfig(**ref_runner.RL_FIELDS)
+    mine = bnb.YemongPolicy(cfg, stock.coordinator, num_value_components=11, num_ships=n_ships, team_pma_k=(0, 1),
+                            bullet_coordinator=stock.bullet_encoder.coordinator).to(dev).eval()
+    mine.load_state_dict(stock.state_dict(), strict=True)
+    obs = ref_runner.random_observation(n_envs, n_ships, n_fields, n_bullets, seed=3, device=str(dev))
+    hidden = torch.randn(mine.n_hidden_layers, n_envs * n_ships, 4 * cfg.d_model, device=dev) * 0.5
+
+    def timed(fn):
+        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize(dev)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            before = _capi.lib.bnb_launch_count()
+            e0.record()
+            for _ in range(steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize(dev)
+            return e0.elapsed_time(e1) / steps, (_capi.lib.bnb_launch_count() - before) / steps
+
+    out: dict = {"workload": f"get_action_and_value, {n_envs} envs x ({n_ships} ships + {n_fields} fields), {n_bullets} bullet slots, "
+                             "bf16 autocast", "env_steps_per_call": n_envs, "steps": steps}
+    ms, launches = timed(lambda: mine.get_action_and_value(obs, hidden))
+    out["ours"] = {"ms_per_step": ms, "env_steps_per_s": n_envs / (ms * 1e-3), "own_kernel_launches_per_step": launches}
+    try:
+        mine_c = torch.compile(mine.get_action_and_value, mode="reduce-overhead")
+        ms, launches = timed(lambda: mine_c(obs, hidden))
+        out["ours_compiled"] = {"ms_per_step": ms, "env_steps_per_s": n_envs / (ms * 1e-3), "mode": "reduce-overhead",
+                                "note": "the same torch.compile call the reference makes: the FeatureCoordinator's torch operators are "
+                                        "fused by the compiler, this package's kernels are opaque operators, and the step replays as "
+                                        "one CUDA graph (own_kernel_launches_per_step counts host-side launch calls: 0 on replay)",
+                                "own_kernel_launches_per_step": launches}
+    except Exception as e:  # noqa: BLE001 - reported, not fatal
+        out["ours_compiled"] = {"error": repr(e)[:300]}
+    try:
+        ms, _ = timed(lambda: stock.get_action_and_value(obs, hidden))
+        out["reference_eager"] = {"ms_per_step": ms, "env_steps_per_s": n_envs / (ms * 1e-3)}
+    except Exception as e:  # noqa: BLE001 - a comparator that fails is reported, not fatal
+        out["reference_eager"] = {"error": repr(e)[:200]}
+    try:
+        compiled = torch.compile(stock.get_action_and_value, mode="reduce-overhead")
+        ms, _ = timed(lambda: compiled(obs, hidden))
+        out["reference_compiled"] = {"ms_per_step": ms, "env_steps_per_s": n_envs / (ms * 1e-3), "mode": "reduce-overhead"}
+    except Exception as e:  # noqa: BLE001
+        out["reference_compiled"] = {"error": repr(e)[:200]}
+    return out
+
+
 # ----------------------------------------------------------------------------- GPU arm
 
 
@@ -780,6 +845,8 @@ def run_ours(args) -> None:
                 trunk, dev, sum(p.numel() for p in trunk.parameters()), cfg)
         if world == 1 and not args.no_train and args.workload == "C2":
             line["train_step"] = time_train_step(trunk, dev)
+        if world == 1 and not args.no_policy and args.workload == "C2":
+            line["policy_step"] = time_policy_step(dev)
         if world == 1 and not args.no_cpu:
             base = time_cpu(args.workload, 3, 1)
             line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
@@ -801,6 +868,8 @@ def main() -> None:
     ap.add_argument("--no-gpu-ref", action="store_true", help="skip the same-box GPU comparator (reference modules, eager and compiled)")
     ap.add_argument("--no-c5", action="store_true", help="skip the sharded ragged C5 record")
     ap.add_argument("--no-train", action="store_true", help="skip the forward + backward record (train_step)")
+    ap.add_argument("--no-policy", action="store_true", help="skip the whole-policy rollout step record (policy_step)")
+    ap.add_argument("--policy-only", action="store_true", help="only the whole-policy rollout step record (for profiling)")
     ap.add_argument("--no-others", action="store_true", help="skip the C3 / C4 / C2B records (other_workloads)")
     ap.add_argument("--train-only", action="store_true", help="only this package's forward + backward record (for profiling)")
     ap.add_argument("--train-envs", type=int, default=1024, help="environments of the forward + backward record")
@@ -813,6 +882,9 @@ def main() -> None:
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.train_only:
         run_train_only(args)
+    elif args.policy_only:
+        torch.cuda.set_device(0)
+        print(json.dumps({"policy_step": time_policy_step(torch.device("cuda", 0), steps=args.steps if args.steps < 20 else 10)}), flush=True)
     elif args.impl == "reference":
         run_reference(args)
     else:

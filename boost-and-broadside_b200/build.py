@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libbnb_trunk.so")
-SOURCES = ["capi.cu", "exact_kernels.cu", "tensor_kernels.cu", "pipelined_tile_kernel.cu", "static_scratch.cu", "grad_kernels.cu"]
+SOURCES = ["capi.cu", "exact_kernels.cu", "tensor_kernels.cu", "pipelined_tile_kernel.cu", "static_scratch.cu", "grad_kernels.cu", "mlp_kernels.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",

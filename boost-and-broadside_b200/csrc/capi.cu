@@ -6,6 +6,7 @@
 #include "bnb_trunk.h"
 #include "bullet_slices.h"
 #include "exact_kernels.h"
+#include "mlp_kernels.h"
 #include "grad_kernels.h"
 #include "launch_count.h"
 #include "validate.h"
@@ -451,6 +452,9 @@ int bnb_encoder_mlp_fwd(const float* w1, const float* b1, const float* g1, const
   const void* ps[] = {w1, b1, g1, w2, b2, g2, x, y};
   for (const void* p : ps) if (!p) return BNB_ERR_NULL_POINTER;
   if (!aligned16(w1) || !aligned16(w2)) return BNB_ERR_MISALIGNED;
+  if (precision == BNB_BF16 && bnb::mlp::supported(in_pad, hidden, out_dim))
+    return bnb::mlp::encoder_mlp_bf16(w1, b1, g1, w2, b2, g2, in_dim, in_pad, hidden, out_dim, out_dim, x, y, n_rows,
+                                      static_cast<cudaStream_t>(stream));
   return bnb::exact::encoder_mlp(w1, b1, g1, w2, b2, g2, in_dim, in_pad, hidden, out_dim, out_dim, x, y, n_rows,
                                  precision == BNB_BF16, static_cast<cudaStream_t>(stream));
 }
@@ -467,6 +471,9 @@ int bnb_head_mlp_fwd(const float* w1, const float* b1, const float* g1, const fl
   const void* ps[] = {w1, b1, g1, w2, b2, x, y};
   for (const void* p : ps) if (!p) return BNB_ERR_NULL_POINTER;
   if (!aligned16(w1) || !aligned16(w2)) return BNB_ERR_MISALIGNED;
+  if (precision == BNB_BF16 && bnb::mlp::supported(in_dim, hidden, out_pad))
+    return bnb::mlp::encoder_mlp_bf16(w1, b1, g1, w2, b2, nullptr, in_dim, in_dim, hidden, out_pad, out_dim, x, y, n_rows,
+                                      static_cast<cudaStream_t>(stream));
   return bnb::exact::encoder_mlp(w1, b1, g1, w2, b2, nullptr, in_dim, in_dim, hidden, out_pad, out_dim, x, y, n_rows,
                                  precision == BNB_BF16, static_cast<cudaStream_t>(stream));
 }

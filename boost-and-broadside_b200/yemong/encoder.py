@@ -17,34 +17,19 @@ import torch
 import torch.nn as nn
 
 from .. import _capi
+from . import _end_ops
 
 
 def _encoder_chain(raw: torch.Tensor, lin1: nn.Linear, norm1: nn.RMSNorm, lin2: nn.Linear, norm2: nn.RMSNorm) -> torch.Tensor:
-    """norm2(lin2(gelu(norm1(lin1(raw))))) over the last dim of ``raw`` through the C ABI."""
+    """norm2(lin2(gelu(norm1(lin1(raw))))) over the last dim of ``raw`` through the C ABI
+    (one opaque operator, ``bnb_b200::mlp_chain``)."""
     _capi.require_cuda(raw, "the raw feature vector")
-    dev = raw.device
-    in_dim, hidden, out_dim = lin1.in_features, lin1.out_features, lin2.out_features
+    in_dim, out_dim = lin1.in_features, lin2.out_features
     if raw.shape[-1] != in_dim:
         raise RuntimeError(f"expected raw features of width {in_dim}, got {tuple(raw.shape)}")
-    precision = _capi.current_precision(dev)
-    in_pad = (in_dim + 31) // 32 * 32
-    with torch.cuda.device(dev):
-        flat = _capi.f32c(raw).reshape(-1, in_dim)
-        # the first weight with zero columns up to a multiple of 32 (a few KB, rebuilt per call from
-        # the live parameter, so it cannot go stale)
-        w1 = lin1.weight.detach()
-        if in_pad != in_dim:
-            w1 = torch.nn.functional.pad(w1, (0, in_pad - in_dim))
-        w1 = w1.contiguous()
-        ps = [w1, lin1.bias, norm1.weight, lin2.weight, lin2.bias, norm2.weight]
-        for p in ps:
-            if p.device != dev or p.dtype != torch.float32 or not p.is_contiguous():
-                raise RuntimeError("encoder parameters must be contiguous float32 on the input's device")
-        y = torch.empty(flat.shape[0], out_dim, device=dev,
-                        dtype=torch.bfloat16 if precision == _capi.BNB_BF16 else torch.float32)
-        st = _capi.lib.bnb_encoder_mlp_fwd(*(p.data_ptr() for p in ps), in_dim, in_pad, hidden, out_dim, flat.data_ptr(),
-                                           y.data_ptr(), flat.shape[0], precision, _capi.stream_handle(dev))
-    _capi.check("bnb_encoder_mlp_fwd", st)
+    precision = _capi.current_precision(raw.device)
+    y = _end_ops.mlp_chain(raw.reshape(-1, in_dim), lin1.weight, lin1.bias, norm1.weight, lin2.weight, lin2.bias, norm2.weight,
+                           precision)
     return y.reshape(*raw.shape[:-1], out_dim)
 
 

@@ -16,6 +16,7 @@ import torch
 import torch.nn as nn
 
 from .. import _capi
+from . import _end_ops
 
 
 class HeadMLP(nn.Sequential):
@@ -35,28 +36,11 @@ class HeadMLP(nn.Sequential):
             raise NotImplementedError("the CUDA heads are forward-only; call them under torch.no_grad()")
         _capi.require_cuda(x, "the head's input")
         lin1, norm, lin2 = self[0], self[1], self[3]
-        dev = x.device
-        in_dim, hidden, out_dim = lin1.in_features, lin1.out_features, lin2.out_features
+        in_dim, out_dim = lin1.in_features, lin2.out_features
         if x.shape[-1] != in_dim:
             raise RuntimeError(f"expected tokens of width {in_dim}, got {tuple(x.shape)}")
-        precision = _capi.current_precision(dev)
-        out_pad = (out_dim + 31) // 32 * 32
-        with torch.cuda.device(dev):
-            flat = _capi.f32c(x).reshape(-1, in_dim)
-            # the second Linear with zero rows up to a multiple of 32 (a few KB, rebuilt per call
-            # from the live parameters, so it cannot go stale)
-            w2 = torch.nn.functional.pad(lin2.weight.detach(), (0, 0, 0, out_pad - out_dim)).contiguous()
-            b2 = torch.nn.functional.pad(lin2.bias.detach(), (0, out_pad - out_dim)).contiguous()
-            ps = [lin1.weight, lin1.bias, norm.weight, w2, b2]
-            for p in ps:
-                if p.device != dev or p.dtype != torch.float32 or not p.is_contiguous():
-                    raise RuntimeError("head parameters must be contiguous float32 on the input's device")
-            y = torch.empty(flat.shape[0], out_dim, device=dev,
-                            dtype=torch.bfloat16 if precision == _capi.BNB_BF16 else torch.float32)
-            st = _capi.lib.bnb_head_mlp_fwd(*(p.data_ptr() for p in ps), in_dim, hidden, out_dim, out_pad,
-                                            flat.data_ptr(), y.data_ptr(), flat.shape[0], precision,
-                                            _capi.stream_handle(dev))
-        _capi.check("bnb_head_mlp_fwd", st)
+        y = _end_ops.mlp_chain(x.reshape(-1, in_dim), lin1.weight, lin1.bias, norm.weight, lin2.weight, lin2.bias, None,
+                               _capi.current_precision(x.device))
         return y.reshape(*x.shape[:-1], out_dim)
 
 
@@ -97,24 +81,8 @@ class TeamPMA(nn.Module):
         B, N, D = x.shape
         if tuple(team_id.shape) != (B, N) or tuple(alive.shape) != (B, N):
             raise RuntimeError(f"team_id and alive must have shape {(B, N)}")
-        dev = x.device
-        precision = _capi.current_precision(dev)
-        ps = [self.seeds, self.attn.in_proj_weight, self.attn.out_proj.weight, self.norm.weight]
-        for p in ps:
-            if p.device != dev or p.dtype != torch.float32 or not p.is_contiguous():
-                raise RuntimeError("TeamPMA parameters must be contiguous float32 on the input's device")
-        with torch.cuda.device(dev):
-            xin = _capi.f32c(x)
-            tid = team_id.to(torch.int32).contiguous()
-            al = _capi.u8(alive)
-            y = torch.empty(B, N, D, device=dev, dtype=torch.bfloat16 if x.dtype == torch.bfloat16 else torch.float32)
-            nbytes = _capi.lib.bnb_team_pma_scratch_bytes(D, B, N)
-            scratch = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=dev)
-            st = _capi.lib.bnb_team_pma_fwd(*(p.data_ptr() for p in ps), D, self.n_heads, xin.data_ptr(), tid.data_ptr(),
-                                            al.data_ptr(), y.data_ptr(), 1 if y.dtype == torch.bfloat16 else 0, B, N,
-                                            precision, scratch.data_ptr(), scratch.numel(), _capi.stream_handle(dev))
-        _capi.check("bnb_team_pma_fwd", st)
-        return y
+        return _end_ops.team_pma(x, team_id, alive, self.seeds, self.attn.in_proj_weight, self.attn.out_proj.weight,
+                                 self.norm.weight, self.n_heads, _capi.current_precision(x.device))
 
 
 def _action_dist(logits: torch.Tensor, given: torch.Tensor | None, want_entropy: bool, generator=None):
@@ -125,29 +93,20 @@ def _action_dist(logits: torch.Tensor, given: torch.Tensor | None, want_entropy:
         raise RuntimeError(f"expected 12 action logits in the last dim, got {tuple(logits.shape)}")
     dev = logits.device
     lead = logits.shape[:-1]
-    precision = _capi.BNB_BF16 if logits.dtype == torch.bfloat16 else _capi.BNB_FP32
-    with torch.cuda.device(dev):
-        flat = _capi.f32c(logits).reshape(-1, 12)
-        R = flat.shape[0]
-        logprob = torch.empty(R, device=dev, dtype=torch.float32)
-        entropy = torch.empty(R, device=dev, dtype=torch.float32) if want_entropy else None
-        if given is None:
-            uniforms = torch.rand(R, 3, device=dev, generator=generator)
-            action = torch.empty(R, 3, device=dev, dtype=torch.int64)
-            g = None
-        else:
-            if tuple(given.shape) != (*lead, 3):
-                raise RuntimeError(f"actions must have shape {(*lead, 3)}, got {tuple(given.shape)}")
-            uniforms = action = None
-            g = given.to(torch.int64).reshape(-1, 3).contiguous()
-        st = _capi.lib.bnb_action_dist_fwd(flat.data_ptr(), _capi.ptr(uniforms), _capi.ptr(g), _capi.ptr(action),
-                                           logprob.data_ptr(), _capi.ptr(entropy), R, precision, _capi.stream_handle(dev))
-    _capi.check("bnb_action_dist_fwd", st)
+    flat = logits.reshape(-1, 12)
+    if given is None:
+        uniforms = torch.rand(flat.shape[0], 3, device=dev, generator=generator)
+        g = None
+    else:
+        if tuple(given.shape) != (*lead, 3):
+            raise RuntimeError(f"actions must have shape {(*lead, 3)}, got {tuple(given.shape)}")
+        uniforms = None
+        g = given.reshape(-1, 3)
+    action, logprob, entropy = _end_ops.action_dist(flat, uniforms, g, want_entropy)
     out_dtype = logits.dtype if logits.dtype == torch.bfloat16 else torch.float32
     logprob = logprob.reshape(lead).to(out_dtype)
-    if entropy is not None:
-        entropy = entropy.reshape(lead).to(out_dtype)
-    return (None if action is None else action.reshape(*lead, 3)), logprob, entropy
+    entropy = entropy.reshape(lead).to(out_dtype) if want_entropy else None
+    return (action.reshape(*lead, 3) if given is None else None), logprob, entropy
 
 
 def sample_action(logits: torch.Tensor, generator: torch.Generator | None = None):

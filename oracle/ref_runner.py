@@ -152,3 +152,50 @@ def workload_runner(trunk: ReferenceTrunk, w, device: str = "cpu", token_dtype: 
             with torch.no_grad(), ctx():
                 return trunk.step_ragged(x, alive, hidden, nt, ns)
     return run
+
+
+def reference_policy(num_ships: int, fields: dict | None = None, seed: int = 0):
+    """The reference's whole ``YemongPolicy`` (models/yemong/policy.py:136) with its standard ship and
+    bullet FeatureCoordinators (train/rl/features.py), default init under ``torch.manual_seed(seed)``,
+    eleven value components and the win components pooled per team, as the reference's trainer builds it."""
+    _import_ref()
+    from boost_and_broadside.config import ModelConfig, ShipConfig
+    from boost_and_broadside.models.yemong.policy import YemongPolicy
+    from boost_and_broadside.train.rl.features import build_bullet_coordinator, build_standard_coordinator
+
+    ships = ShipConfig()
+    torch.manual_seed(seed)
+    return YemongPolicy(ModelConfig(**(fields or RL_FIELDS)), build_standard_coordinator(ships), num_value_components=11,
+                        num_ships=num_ships, team_pma_k=(0, 1), bullet_coordinator=build_bullet_coordinator(ships)).eval()
+
+
+def random_observation(n_envs: int, n_ships: int, n_fields: int, n_bullets: int, seed: int, device: str = "cpu"):
+    """A seeded random observation in the reference's own container (env/observation.py): every key the
+    standard coordinators read, ``n_ships`` ships (two teams) then ``n_fields`` fields per environment,
+    ``n_bullets`` bullet slots of which about 40 % are active."""
+    _import_ref()
+    from boost_and_broadside.env.observation import BulletObsKey, ObsKey, YemongObservation
+
+    g = torch.Generator().manual_seed(seed)
+    B, T, NB = n_envs, n_ships + n_fields, n_bullets
+    r = lambda *s: torch.rand(*s, generator=g)   # noqa: E731
+    n = lambda *s: torch.randn(*s, generator=g)  # noqa: E731
+    team = torch.cat([torch.zeros(n_ships // 2), torch.ones(n_ships - n_ships // 2),
+                      torch.full((n_fields,), 2.0)]).long().expand(B, -1).contiguous()
+    data = {
+        ObsKey.POS: r(B, T, 2), ObsKey.VEL: n(B, T, 2) * 100, ObsKey.ATT: n(B, T, 2), ObsKey.ANG_VEL: n(B, T, 1),
+        ObsKey.HEALTH: r(B, T, 1), ObsKey.POWER: r(B, T, 1), ObsKey.COOLDOWN: r(B, T, 1), ObsKey.TEAM_ID: team,
+        ObsKey.ALIVE: torch.ones(B, T, dtype=torch.bool), ObsKey.PREVIOUS_ACTION: torch.randint(0, 2, (B, T, 3), generator=g),
+        ObsKey.RADIUS: r(B, T, 1), ObsKey.LOCAL_LOG_INDEX: n(B, T, 1) * 0.1, ObsKey.LOCAL_INDEX_GRADIENT: n(B, T, 2) * 0.1,
+        ObsKey.FIELD_TRANSITION_WIDTH: r(B, T, 1), ObsKey.FIELD_INSIDE_LOG_INDEX: n(B, T, 1) * 0.1,
+        ObsKey.FIELD_OUTSIDE_LOG_INDEX: n(B, T, 1) * 0.1, ObsKey.FIELD_LOG_INDEX_RATIO: n(B, T, 1) * 0.1,
+        ObsKey.FIELD_DAMAGE: r(B, T, 1),
+    }
+    bullets = {
+        BulletObsKey.POS: r(B, NB, 2) * 1024.0, BulletObsKey.VEL: n(B, NB, 2) * 400.0, BulletObsKey.DAMAGE: r(B, NB, 1),
+        BulletObsKey.LIFETIME: r(B, NB, 1), BulletObsKey.LOCAL_LOG_INDEX: n(B, NB, 1) * 0.1,
+        BulletObsKey.LOCAL_INDEX_GRADIENT: n(B, NB, 2) * 0.1, BulletObsKey.TEAM_ID: torch.randint(0, 2, (B, NB), generator=g),
+        BulletObsKey.ACTIVE: r(B, NB) < 0.4,
+    }
+    to = lambda d: {k: v.to(device) for k, v in d.items()}  # noqa: E731
+    return YemongObservation(data=to(data), bullets=to(bullets))

@@ -106,3 +106,30 @@ def test_evaluate_actions_forward_matches_the_reference_policy(mode):
         assert e <= tol, f"{name}: {e:.3e}"
         report.append(f"{name} {e:.1e}")
     print(f"evaluate_actions forward {mode}: " + " ".join(report))
+
+
+def test_rollout_step_under_torch_compile_is_one_graph_and_matches_eager():
+    """``torch.compile(policy.get_action_and_value, mode="reduce-overhead", fullgraph=True)`` -- the
+    reference's own way of running its policy (train/rl/ppo.py:396-400): every call into the C ABI is
+    an opaque operator, so there is no graph break, and value / prediction / hidden state equal the
+    eager call bit for bit (the action draw uses the device generator and is only checked for range)."""
+    import boost_and_broadside_b200 as bnb
+
+    B, N, M, NB = 16, 8, 4, 24
+    stock, _ = build_policies(N)
+    cfg = bnb.ModelConfig(d_model=128, n_heads=4, n_yemong_blocks=2, n_spatial_per_block=2, n_temporal_per_block=1,
+                          n_bullet_cross_per_block=1)
+    mine = bnb.YemongPolicy(cfg, stock.coordinator, num_value_components=11, num_ships=N, team_pma_k=(0, 1),
+                            bullet_coordinator=stock.bullet_encoder.coordinator).to(DEV).eval()
+    mine.load_state_dict(stock.state_dict(), strict=True)
+    obs = _observation(B, N, M, NB, seed=11)
+    hidden = torch.randn(mine.n_hidden_layers, B * N, 512, device=DEV) * 0.5
+    compiled = torch.compile(mine.get_action_and_value, mode="reduce-overhead", fullgraph=True)
+    with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
+        _, _, v0, p0, h0 = mine.get_action_and_value(obs, hidden)
+        for _ in range(3):   # warm-up, capture, replay
+            a, lp, v, p, h = compiled(obs, hidden)
+            v, p, h, a, lp = v.clone(), p.clone(), h.clone(), a.clone(), lp.clone()
+    assert torch.equal(v, v0) and torch.equal(p, p0) and torch.equal(h, h0)
+    assert tuple(a.shape) == (B, N, 3) and 0 <= int(a[..., 1].min()) and int(a[..., 1].max()) < 7
+    assert bool(torch.isfinite(lp.float()).all())
