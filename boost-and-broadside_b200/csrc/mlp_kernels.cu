@@ -9,9 +9,16 @@
 // is rounded once after its bias, an RMSNorm of a bfloat16 input is computed in float32 and rounded
 // once, and so is the GELU.  The float32 contract stays on the CUDA-core engine (exact_kernels.cu).
 //
-// One persistent CTA per SM slot: both weight matrices are converted to bfloat16 once per CTA and stay
-// in shared memory; the CTA then walks tiles of 128 rows.  Warp w owns rows [16 w, 16 w + 16) of the
-// tile through every stage, so only the loading of a tile needs a CTA-wide barrier.
+// One persistent CTA per SM: both weight matrices are converted to bfloat16 once per CTA and stay in
+// shared memory.  After that the warps (up to 16) are independent: each walks slices of 16 rows of
+// its own, stages the slice's input rows in its own shared-memory rows and keeps everything else in
+// registers.  The hidden activations never leave the register file: the accumulator fragment of
+// Linear 1 (row g, columns 2t, 2t+1 of two adjacent 8-column blocks) is exactly the A fragment of
+// mma.sync for a 16-wide k step of Linear 2, so each 64-column chunk of the hidden layer is normed,
+// passed through the GELU and multiplied into the output accumulators straight away.  The RMSNorm
+// needs the whole row's sum of squares first: for a hidden layer wider than one chunk Linear 1 is
+// computed twice, once for the sum alone (cheaper than a trip through shared memory: the kernel is
+// bound by instruction issue, not by the tensor pipe).  No CTA-wide barrier after the weights.
 #include "mlp_kernels.h"
 
 #include "common.cuh"
@@ -21,6 +28,7 @@
 namespace bnb {
 namespace mlp {
 
+using tensor::gelu_fast;   // the fused trunk kernel's fit of the erf GELU (max relative error 1.2e-3, below bfloat16 rounding)
 using tensor::ldsm_x4;
 using tensor::mma_bf16;
 using tensor::pack_bf16;
@@ -28,234 +36,285 @@ using tensor::smem_u32;
 
 namespace {
 
-constexpr int TILE = 128;      // rows per tile
-constexpr int THREADS = 256;   // 8 warps x 16 rows
+constexpr int SLICE = 16;      // rows per warp slice (one mma.sync row block)
+constexpr int MAX_WARPS = 16;
 constexpr int PAD = 8;         // bf16 elements of padding per staged row: ldmatrix stays conflict-free
 constexpr size_t SMEM_MAX = 227 * 1024;
 
 struct Layout {
-  int ldx, ldh;   // row strides (bf16 elements) of the in_pad-wide and the hidden-wide arrays
-  size_t w1, w2, x, h, vec, total;
+  int ldx, ldw;   // row strides (bf16 elements): in_pad-wide arrays, the second weight
+  int warps;      // warps per CTA
+  size_t w1, w2, vec, slices, per_warp, total;
 };
 __host__ __device__ inline Layout layout(int in_pad, int hidden, int out_dim) {
   Layout l;
   l.ldx = in_pad + PAD;
-  l.ldh = hidden + PAD;
+  l.ldw = hidden + PAD;
   size_t off = 0;
   l.w1 = off; off += (size_t)hidden * l.ldx * 2;
-  l.w2 = off; off += (size_t)out_dim * l.ldh * 2;
-  l.x = off; off += (size_t)TILE * l.ldx * 2;
-  l.h = off; off += (size_t)TILE * l.ldh * 2;
-  l.vec = off; off += (size_t)(2 * hidden + 2 * out_dim + TILE) * 4;   // b1, g1, b2, g2, 1/rms per row
-  l.total = off;
+  l.w2 = off; off += (size_t)out_dim * l.ldw * 2;
+  l.vec = off; off += (size_t)(2 * hidden + 2 * out_dim) * 4;   // b1, g1, b2, g2
+  l.slices = off;
+  l.per_warp = (size_t)SLICE * l.ldx * 2;                        // a warp's staged input rows
+  const size_t room = SMEM_MAX > off ? SMEM_MAX - off : 0;
+  int w = (int)(room / l.per_warp);
+  w = w > MAX_WARPS ? MAX_WARPS : w & ~1;
+  l.warps = w;
+  l.total = off + (size_t)w * l.per_warp;
   return l;
 }
 
-}  // namespace
-
-namespace {
-
-__device__ __forceinline__ float2 unpack2(uint32_t v) {
-  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v));
+// One 64-column chunk of Linear 1 for the warp's 16 rows: acc[nt] = X W1[c0 + 8 nt ..]^T.
+__device__ __forceinline__ void linear1_chunk(float (&acc)[8][4], uint32_t sX, uint32_t sW1, int ldx, int in_pad, int c0, int npairs,
+                                              int a_off, int b_row, int b_k) {
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
+  for (int k0 = 0; k0 < in_pad; k0 += 16) {
+    uint32_t a0, a1, a2, a3;
+    ldsm_x4(sX + (a_off + k0) * 2, a0, a1, a2, a3);
+#pragma unroll
+    for (int np = 0; np < 4; ++np) {
+      if (np < npairs) {
+        uint32_t q0, q1, q2, q3;
+        ldsm_x4(sW1 + ((c0 + np * 16 + b_row) * ldx + k0 + b_k) * 2, q0, q1, q2, q3);
+        mma_bf16(acc[2 * np], a0, a1, a2, a3, q0, q1);
+        mma_bf16(acc[2 * np + 1], a0, a1, a2, a3, q2, q3);
+      }
+    }
+  }
 }
 
-__global__ void __launch_bounds__(THREADS, 2)
+// NP2: pairs of 8-column output blocks held in registers (2: up to 32 output columns, the heads;
+// 8: up to 128, the encoders).
+template <int NP2>
+__global__ void __launch_bounds__(32 * MAX_WARPS, 1)
 k_mlp_bf16(const float* __restrict__ x, __nv_bfloat16* __restrict__ y, int n_rows, int in_dim, int in_pad, int hidden,
-           int out_dim, int out_store, int vec_store, const float* __restrict__ w1, const float* __restrict__ b1,
+           int out_dim, int out_store, const float* __restrict__ w1, const float* __restrict__ b1,
            const float* __restrict__ g1, const float* __restrict__ w2, const float* __restrict__ b2,
            const float* __restrict__ g2) {
   extern __shared__ __align__(16) uint8_t sm[];
   const Layout L = layout(in_pad, hidden, out_dim);
   __nv_bfloat16* W1 = reinterpret_cast<__nv_bfloat16*>(sm + L.w1);
   __nv_bfloat16* W2 = reinterpret_cast<__nv_bfloat16*>(sm + L.w2);
-  __nv_bfloat16* X = reinterpret_cast<__nv_bfloat16*>(sm + L.x);
-  __nv_bfloat16* H = reinterpret_cast<__nv_bfloat16*>(sm + L.h);
   float* b1s = reinterpret_cast<float*>(sm + L.vec);
   float* g1s = b1s + hidden;
   float* b2s = g1s + hidden;
   float* g2s = b2s + out_dim;
-  float* rinv = g2s + out_dim;
-  const int ldx = L.ldx, ldh = L.ldh;
+  const int ldx = L.ldx, ldw = L.ldw;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_threads = blockDim.x;
   const int g = lane >> 2, t = lane & 3;
 
   // the weights, once per CTA: float32 in global memory, bfloat16 operands here
-  for (int idx = tid; idx < hidden * in_pad; idx += THREADS) {
+  for (int idx = tid; idx < hidden * in_pad; idx += n_threads) {
     const int r = idx / in_pad, c = idx - r * in_pad;
     W1[r * ldx + c] = __float2bfloat16_rn(w1[idx]);
   }
-  for (int idx = tid; idx < out_dim * hidden; idx += THREADS) {
+  for (int idx = tid; idx < out_dim * hidden; idx += n_threads) {
     const int r = idx / hidden, c = idx - r * hidden;
-    W2[r * ldh + c] = __float2bfloat16_rn(w2[idx]);
+    W2[r * ldw + c] = __float2bfloat16_rn(w2[idx]);
   }
-  for (int i = tid; i < hidden; i += THREADS) {
+  for (int i = tid; i < hidden; i += n_threads) {
     b1s[i] = round_bf16(b1[i]);
     g1s[i] = g1[i];
   }
-  for (int i = tid; i < out_dim; i += THREADS) {
+  for (int i = tid; i < out_dim; i += n_threads) {
     b2s[i] = round_bf16(b2[i]);
     g2s[i] = g2 ? g2[i] : 1.0f;
   }
+  __syncthreads();   // the only CTA-wide barrier: from here on every warp works alone
 
-  const int n_tiles = (n_rows + TILE - 1) / TILE;
-  const int wr = warp * 16;
-  const uint32_t sX = smem_u32(X), sH = smem_u32(H), sW1 = smem_u32(W1), sW2 = smem_u32(W2);
+  __nv_bfloat16* X = reinterpret_cast<__nv_bfloat16*>(sm + L.slices + (size_t)warp * L.per_warp);
+  const uint32_t sX = smem_u32(X), sW1 = smem_u32(W1), sW2 = smem_u32(W2);
   // ldmatrix lane addressing: A rows by lane % 16, k half by lane / 16; B rows (output columns) by
   // lane % 8 + 8 (lane / 16), k half by (lane / 8) % 2
-  const int a_row = wr + (lane & 15), a_k = (lane >> 4) * 8;
+  const int a_off = (lane & 15) * ldx + (lane >> 4) * 8;
   const int b_row = (lane & 7) + (lane >> 4) * 8, b_k = ((lane >> 3) & 1) * 8;
+  const int n_slices = (n_rows + SLICE - 1) / SLICE;
+  const int warps = n_threads >> 5;
+  const int npairs2 = out_dim >> 4;
+  const bool two_pass = hidden > 64;
+  // input rows as 16-byte pieces when rows are whole pieces on 16-byte boundaries, else element by
+  // element; idx / d for idx < 2048 and d <= 128 as a multiplication (exact: the error stays below 1 / 512)
+  const bool vec_in = in_dim == in_pad && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  const int q_per_row = in_pad >> 2;
+  const int recip = ((1 << 20) + (vec_in ? q_per_row : in_pad) - 1) / (vec_in ? q_per_row : in_pad);
 
-  for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-    const int row0 = tile * TILE;
-    const int n_valid = min(TILE, n_rows - row0);
-    __syncthreads();   // the weights are staged; every warp is done with the previous tile's X
-    if ((in_dim & 3) == 0 && in_dim == in_pad) {
-      const int q_per_row = in_pad >> 2;
-      for (int idx = tid; idx < TILE * q_per_row; idx += THREADS) {
-        const int r = idx / q_per_row, q = idx - r * q_per_row;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (r < n_valid) v = *reinterpret_cast<const float4*>(x + (size_t)(row0 + r) * in_dim + q * 4);
-        *reinterpret_cast<uint2*>(X + r * ldx + q * 4) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
-      }
-    } else {
-      for (int idx = tid; idx < TILE * in_pad; idx += THREADS) {
-        const int r = idx / in_pad, c = idx - r * in_pad;
-        float v = 0.f;
-        if (r < n_valid && c < in_dim) v = x[(size_t)(row0 + r) * in_dim + c];
-        X[r * ldx + c] = __float2bfloat16_rn(v);
-      }
-    }
-    __syncthreads();
-
-    // ---- Linear 1 + bias, 64 output columns at a time; the rounded result goes to H, its squares are summed
-    float ss0 = 0.f, ss1 = 0.f;
-    for (int c0 = 0; c0 < hidden; c0 += 64) {
-      const int npairs = min(4, (hidden - c0) >> 4);
-      float acc[8][4];
+  for (int slice = blockIdx.x * warps + warp; slice < n_slices; slice += gridDim.x * warps) {
+    const int row0 = slice * SLICE;
+    const int n_valid = min(SLICE, n_rows - row0);
+    // ---- this slice's input rows: one contiguous span of global memory.  Eight loads (four 16-byte
+    // ones) are issued before the first is used: a warp keeps that many requests in flight.
+    if (vec_in) {
+      const int quads = n_valid * q_per_row;
+      const float4* src = reinterpret_cast<const float4*>(x + (size_t)row0 * in_dim);
+      for (int i0 = 0; i0 < (in_pad >> 3); i0 += 4) {   // SLICE * q_per_row / 32 iterations in all, a multiple of 4 or just 2
+        float4 v[4];
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt)
+        for (int j = 0; j < 4; ++j) {
+          const int idx = lane + 32 * (i0 + j);
+          v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (idx < quads) v[j] = src[idx];
+        }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
-      for (int k0 = 0; k0 < in_pad; k0 += 16) {
-        uint32_t a0, a1, a2, a3;
-        ldsm_x4(sX + (a_row * ldx + k0 + a_k) * 2, a0, a1, a2, a3);
-#pragma unroll
-        for (int np = 0; np < 4; ++np) {
-          if (np < npairs) {
-            uint32_t q0, q1, q2, q3;
-            ldsm_x4(sW1 + ((c0 + np * 16 + b_row) * ldx + k0 + b_k) * 2, q0, q1, q2, q3);
-            mma_bf16(acc[2 * np], a0, a1, a2, a3, q0, q1);
-            mma_bf16(acc[2 * np + 1], a0, a1, a2, a3, q2, q3);
+        for (int j = 0; j < 4; ++j) {
+          const int idx = lane + 32 * (i0 + j);
+          if (idx < SLICE * q_per_row) {
+            const int r = (idx * recip) >> 20, q = idx - r * q_per_row;
+            *reinterpret_cast<uint2*>(X + r * ldx + q * 4) = make_uint2(pack_bf16(v[j].x, v[j].y), pack_bf16(v[j].z, v[j].w));
           }
         }
       }
+    } else {
+      const float* src = x + (size_t)row0 * in_dim;
+      for (int i0 = 0; i0 < (in_pad >> 1); i0 += 8) {   // SLICE * in_pad / 32 iterations in all, a multiple of 8
+        float v[8];
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        if (nt < 2 * npairs) {
-          const int c = c0 + nt * 8 + 2 * t;
-          const float bb0 = b1s[c], bb1 = b1s[c + 1];
-          const float h00 = round_bf16(acc[nt][0] + bb0), h01 = round_bf16(acc[nt][1] + bb1);
-          const float h10 = round_bf16(acc[nt][2] + bb0), h11 = round_bf16(acc[nt][3] + bb1);
-          ss0 = fmaf(h00, h00, fmaf(h01, h01, ss0));
-          ss1 = fmaf(h10, h10, fmaf(h11, h11, ss1));
-          *reinterpret_cast<uint32_t*>(H + (wr + g) * ldh + c) = pack_bf16(h00, h01);
-          *reinterpret_cast<uint32_t*>(H + (wr + g + 8) * ldh + c) = pack_bf16(h10, h11);
+        for (int j = 0; j < 8; ++j) {
+          const int idx = lane + 32 * (i0 + j);
+          const int r = (idx * recip) >> 20, c = idx - r * in_pad;
+          v[j] = 0.f;
+          if (r < n_valid && c < in_dim) v[j] = src[r * in_dim + c];
         }
-      }
-    }
-    ss0 += __shfl_xor_sync(0xffffffffu, ss0, 1);
-    ss0 += __shfl_xor_sync(0xffffffffu, ss0, 2);
-    ss1 += __shfl_xor_sync(0xffffffffu, ss1, 1);
-    ss1 += __shfl_xor_sync(0xffffffffu, ss1, 2);
-    if (t == 0) {
-      rinv[wr + g] = rsqrtf(ss0 / (float)hidden + kRmsEps);
-      rinv[wr + g + 8] = rsqrtf(ss1 / (float)hidden + kRmsEps);
-    }
-    __syncwarp();
-    // ---- RMSNorm (float32, rounded once) and GELU (rounded once) over this warp's 16 rows of H
-    {
-      const int half = hidden >> 1;
-      for (int idx = lane; idx < 16 * half; idx += 32) {
-        const int r = idx / half, c = (idx - r * half) * 2;
-        uint32_t* p = reinterpret_cast<uint32_t*>(H + (wr + r) * ldh + c);
-        const float2 h = unpack2(*p);
-        const float inv = rinv[wr + r];
-        const float v0 = round_bf16(h.x * inv * g1s[c]), v1 = round_bf16(h.y * inv * g1s[c + 1]);
-        *p = pack_bf16(gelu_erf(v0), gelu_erf(v1));
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int idx = lane + 32 * (i0 + j);
+          const int r = (idx * recip) >> 20, c = idx - r * in_pad;
+          X[r * ldx + c] = __float2bfloat16_rn(v[j]);
+        }
       }
     }
     __syncwarp();
 
-    // ---- Linear 2 + bias [+ RMSNorm], all out_dim columns in registers
-    const int npairs2 = out_dim >> 4;
-    float acc[16][4];
+    float acc[8][4];
+    float ss0 = 0.f, ss1 = 0.f;
+    if (two_pass) {   // the sum of squares of the rounded Linear 1 output, every chunk
+      for (int c0 = 0; c0 < hidden; c0 += 64) {
+        const int npairs = min(4, (hidden - c0) >> 4);
+        linear1_chunk(acc, sX, sW1, ldx, in_pad, c0, npairs, a_off, b_row, b_k);
 #pragma unroll
-    for (int nt = 0; nt < 16; ++nt)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
-    for (int k0 = 0; k0 < hidden; k0 += 16) {
-      uint32_t a0, a1, a2, a3;
-      ldsm_x4(sH + (a_row * ldh + k0 + a_k) * 2, a0, a1, a2, a3);
-#pragma unroll
-      for (int np = 0; np < 8; ++np) {
-        if (np < npairs2) {
-          uint32_t q0, q1, q2, q3;
-          ldsm_x4(sW2 + ((np * 16 + b_row) * ldh + k0 + b_k) * 2, q0, q1, q2, q3);
-          mma_bf16(acc[2 * np], a0, a1, a2, a3, q0, q1);
-          mma_bf16(acc[2 * np + 1], a0, a1, a2, a3, q2, q3);
+        for (int nt = 0; nt < 8; ++nt) {
+          if (nt < 2 * npairs) {
+            const float2 bb = *reinterpret_cast<const float2*>(b1s + c0 + nt * 8 + 2 * t);
+            const float h00 = round_bf16(acc[nt][0] + bb.x), h01 = round_bf16(acc[nt][1] + bb.y);
+            const float h10 = round_bf16(acc[nt][2] + bb.x), h11 = round_bf16(acc[nt][3] + bb.y);
+            ss0 = fmaf(h00, h00, fmaf(h01, h01, ss0));
+            ss1 = fmaf(h10, h10, fmaf(h11, h11, ss1));
+          }
         }
       }
     }
-    __syncwarp();   // every lane has read its part of this warp's rows of H: they now stage the output
+    float inv0 = 0.f, inv1 = 0.f;
+    float acc2[2 * NP2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2 * NP2; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc2[nt][i] = 0.f;
+    for (int c0 = 0; c0 < hidden; c0 += 64) {
+      const int npairs = min(4, (hidden - c0) >> 4);
+      linear1_chunk(acc, sX, sW1, ldx, in_pad, c0, npairs, a_off, b_row, b_k);
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        if (nt < 2 * npairs) {
+          const float2 bb = *reinterpret_cast<const float2*>(b1s + c0 + nt * 8 + 2 * t);
+          acc[nt][0] = round_bf16(acc[nt][0] + bb.x);
+          acc[nt][1] = round_bf16(acc[nt][1] + bb.y);
+          acc[nt][2] = round_bf16(acc[nt][2] + bb.x);
+          acc[nt][3] = round_bf16(acc[nt][3] + bb.y);
+          if (!two_pass) {
+            ss0 = fmaf(acc[nt][0], acc[nt][0], fmaf(acc[nt][1], acc[nt][1], ss0));
+            ss1 = fmaf(acc[nt][2], acc[nt][2], fmaf(acc[nt][3], acc[nt][3], ss1));
+          }
+        }
+      }
+      if (c0 == 0) {   // the row sums are complete: after the first pass, or with this only chunk
+        ss0 += __shfl_xor_sync(0xffffffffu, ss0, 1);
+        ss0 += __shfl_xor_sync(0xffffffffu, ss0, 2);
+        ss1 += __shfl_xor_sync(0xffffffffu, ss1, 1);
+        ss1 += __shfl_xor_sync(0xffffffffu, ss1, 2);
+        inv0 = rsqrtf(ss0 / (float)hidden + kRmsEps);
+        inv1 = rsqrtf(ss1 / (float)hidden + kRmsEps);
+      }
+      // RMSNorm (float32, rounded once), GELU (rounded once by the pack), then straight into Linear 2
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        if (kk < npairs) {
+          uint32_t a[4];
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            const int nt = 2 * kk + hf;
+            const float2 gg = *reinterpret_cast<const float2*>(g1s + c0 + nt * 8 + 2 * t);
+            a[2 * hf] = pack_bf16(gelu_fast(round_bf16(acc[nt][0] * inv0 * gg.x)), gelu_fast(round_bf16(acc[nt][1] * inv0 * gg.y)));
+            a[2 * hf + 1] = pack_bf16(gelu_fast(round_bf16(acc[nt][2] * inv1 * gg.x)), gelu_fast(round_bf16(acc[nt][3] * inv1 * gg.y)));
+          }
+#pragma unroll
+          for (int np = 0; np < NP2; ++np) {
+            if (np < npairs2) {
+              uint32_t q0, q1, q2, q3;
+              ldsm_x4(sW2 + ((np * 16 + b_row) * ldw + c0 + kk * 16 + b_k) * 2, q0, q1, q2, q3);
+              mma_bf16(acc2[2 * np], a[0], a[1], a[2], a[3], q0, q1);
+              mma_bf16(acc2[2 * np + 1], a[0], a[1], a[2], a[3], q2, q3);
+            }
+          }
+        }
+      }
+    }
+
+    // ---- bias [+ RMSNorm] of Linear 2, then the first out_store columns of the 16 rows
     ss0 = 0.f;
     ss1 = 0.f;
 #pragma unroll
-    for (int nt = 0; nt < 16; ++nt) {
+    for (int nt = 0; nt < 2 * NP2; ++nt) {
       if (nt < 2 * npairs2) {
-        const int c = nt * 8 + 2 * t;
-        const float bb0 = b2s[c], bb1 = b2s[c + 1];
-        acc[nt][0] = round_bf16(acc[nt][0] + bb0);
-        acc[nt][1] = round_bf16(acc[nt][1] + bb1);
-        acc[nt][2] = round_bf16(acc[nt][2] + bb0);
-        acc[nt][3] = round_bf16(acc[nt][3] + bb1);
-        ss0 = fmaf(acc[nt][0], acc[nt][0], fmaf(acc[nt][1], acc[nt][1], ss0));
-        ss1 = fmaf(acc[nt][2], acc[nt][2], fmaf(acc[nt][3], acc[nt][3], ss1));
+        const float2 bb = *reinterpret_cast<const float2*>(b2s + nt * 8 + 2 * t);
+        acc2[nt][0] = round_bf16(acc2[nt][0] + bb.x);
+        acc2[nt][1] = round_bf16(acc2[nt][1] + bb.y);
+        acc2[nt][2] = round_bf16(acc2[nt][2] + bb.x);
+        acc2[nt][3] = round_bf16(acc2[nt][3] + bb.y);
+        ss0 = fmaf(acc2[nt][0], acc2[nt][0], fmaf(acc2[nt][1], acc2[nt][1], ss0));
+        ss1 = fmaf(acc2[nt][2], acc2[nt][2], fmaf(acc2[nt][3], acc2[nt][3], ss1));
       }
     }
-    float inv0 = 1.0f, inv1 = 1.0f;
+    float o0 = 1.0f, o1 = 1.0f;
     if (g2) {   // the encoders end in a norm, the heads do not
       ss0 += __shfl_xor_sync(0xffffffffu, ss0, 1);
       ss0 += __shfl_xor_sync(0xffffffffu, ss0, 2);
       ss1 += __shfl_xor_sync(0xffffffffu, ss1, 1);
       ss1 += __shfl_xor_sync(0xffffffffu, ss1, 2);
-      inv0 = rsqrtf(ss0 / (float)out_dim + kRmsEps);
-      inv1 = rsqrtf(ss1 / (float)out_dim + kRmsEps);
+      o0 = rsqrtf(ss0 / (float)out_dim + kRmsEps);
+      o1 = rsqrtf(ss1 / (float)out_dim + kRmsEps);
     }
+    __nv_bfloat16* y0 = y + (size_t)(row0 + g) * out_store;
+    __nv_bfloat16* y1 = y + (size_t)(row0 + g + 8) * out_store;
+    const bool pair_store = (out_store & 1) == 0;   // columns 2t, 2t+1 of a row share an aligned 4-byte word
 #pragma unroll
-    for (int nt = 0; nt < 16; ++nt) {
+    for (int nt = 0; nt < 2 * NP2; ++nt) {
       if (nt < 2 * npairs2) {
         const int c = nt * 8 + 2 * t;
-        const float s0 = g2s[c], s1 = g2s[c + 1];
-        *reinterpret_cast<uint32_t*>(H + (wr + g) * ldh + c) = pack_bf16(acc[nt][0] * inv0 * s0, acc[nt][1] * inv0 * s1);
-        *reinterpret_cast<uint32_t*>(H + (wr + g + 8) * ldh + c) = pack_bf16(acc[nt][2] * inv1 * s0, acc[nt][3] * inv1 * s1);
+        if (c < out_store) {
+          const float2 s = *reinterpret_cast<const float2*>(g2s + c);
+          const uint32_t v0 = pack_bf16(acc2[nt][0] * o0 * s.x, acc2[nt][1] * o0 * s.y);
+          const uint32_t v1 = pack_bf16(acc2[nt][2] * o1 * s.x, acc2[nt][3] * o1 * s.y);
+          if (pair_store) {
+            if (g < n_valid) *reinterpret_cast<uint32_t*>(y0 + c) = v0;
+            if (g + 8 < n_valid) *reinterpret_cast<uint32_t*>(y1 + c) = v1;
+          } else {
+            const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&v0), p1 = *reinterpret_cast<const __nv_bfloat162*>(&v1);
+            if (g < n_valid) {
+              y0[c] = p0.x;
+              if (c + 1 < out_store) y0[c + 1] = p0.y;
+            }
+            if (g + 8 < n_valid) {
+              y1[c] = p1.x;
+              if (c + 1 < out_store) y1[c + 1] = p1.y;
+            }
+          }
+        }
       }
     }
-    __syncwarp();
-    if (vec_store) {   // whole 16-byte pieces of a row
-      const int pieces = out_store >> 3;
-      for (int idx = lane; idx < 16 * pieces; idx += 32) {
-        const int r = idx / pieces, q = idx - r * pieces;
-        if (wr + r < n_valid)
-          *reinterpret_cast<uint4*>(y + (size_t)(row0 + wr + r) * out_store + q * 8) =
-              *reinterpret_cast<const uint4*>(H + (wr + r) * ldh + q * 8);
-      }
-    } else {
-      for (int idx = lane; idx < 16 * out_store; idx += 32) {
-        const int r = idx / out_store, c = idx - r * out_store;
-        if (wr + r < n_valid) y[(size_t)(row0 + wr + r) * out_store + c] = H[(wr + r) * ldh + c];
-      }
-    }
-    __syncwarp();   // the staged output is read before the next tile's Linear 1 writes these rows
+    __syncwarp();   // every lane is done with the staged input rows before the next slice overwrites them
   }
 }
 
@@ -263,8 +322,8 @@ k_mlp_bf16(const float* __restrict__ x, __nv_bfloat16* __restrict__ y, int n_row
 
 bool supported(int in_pad, int hidden, int out_dim) {
   if (in_pad <= 0 || in_pad % 16 != 0 || hidden <= 0 || hidden % 32 != 0 || out_dim <= 0 || out_dim % 32 != 0) return false;
-  if (in_pad > 128 || hidden > 256 || out_dim > 128 || out_dim > hidden) return false;
-  return layout(in_pad, hidden, out_dim).total <= SMEM_MAX;
+  if (in_pad > 128 || hidden > 256 || out_dim > 128) return false;
+  return layout(in_pad, hidden, out_dim).warps >= 4;
 }
 
 int encoder_mlp_bf16(const float* w1, const float* b1, const float* g1, const float* w2, const float* b2, const float* g2,
@@ -272,20 +331,19 @@ int encoder_mlp_bf16(const float* w1, const float* b1, const float* g1, const fl
                      cudaStream_t st) {
   if (!supported(in_pad, hidden, out_dim)) return BNB_ERR_UNSUPPORTED_DIMS;
   if (n_rows <= 0) return BNB_OK;
-  const size_t smem = layout(in_pad, hidden, out_dim).total;
-  if (cudaFuncSetAttribute(k_mlp_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-    return BNB_ERR_LAUNCH;
+  if (reinterpret_cast<uintptr_t>(y) & 3) return BNB_ERR_MISALIGNED;
+  const Layout L = layout(in_pad, hidden, out_dim);
+  auto kernel = out_dim <= 32 ? k_mlp_bf16<2> : k_mlp_bf16<8>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.total) != cudaSuccess) return BNB_ERR_LAUNCH;
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
     return BNB_ERR_NO_DEVICE;
-  const int per_sm = smem * 2 + 2048 <= SMEM_MAX ? 2 : 1;
-  const int n_tiles = (n_rows + TILE - 1) / TILE;
-  const int grid = n_tiles < sms * per_sm ? n_tiles : sms * per_sm;
-  // a 16-byte row store needs y and every row of it on a 16-byte boundary
-  const int vec_store = (reinterpret_cast<uintptr_t>(y) & 15) == 0 && (out_store & 7) == 0;
+  const int n_slices = (n_rows + SLICE - 1) / SLICE;
+  const int want = (n_slices + L.warps - 1) / L.warps;
+  const int grid = want < sms ? want : sms;
   count_launch();
-  k_mlp_bf16<<<grid, THREADS, smem, st>>>(x, static_cast<__nv_bfloat16*>(y), n_rows, in_dim, in_pad, hidden, out_dim, out_store, vec_store,
-                                          w1, b1, g1, w2, b2, g2);
+  kernel<<<grid, 32 * L.warps, L.total, st>>>(x, static_cast<__nv_bfloat16*>(y), n_rows, in_dim, in_pad, hidden, out_dim, out_store,
+                                              w1, b1, g1, w2, b2, g2);
   return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
 }
 
