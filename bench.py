@@ -357,7 +357,7 @@ def time_gpu_reference(name: str, dev: torch.device, steps: int) -> dict:
 
 
 def time_policy_step(dev: torch.device, n_envs: int = 8192, n_ships: int = 8, n_fields: int = 4, n_bullets: int = 80,
-                     steps: int = 10) -> dict:
+                     steps: int = 10, eager_only: bool = False) -> dict:
     """The whole rollout step of the policy, ``get_action_and_value`` (models/yemong/policy.py:291-373):
     FeatureCoordinator transforms, ship and bullet encoders, trunk step with bullets, the four heads,
     TeamPMA and the action draw, on one seeded random observation of `n_envs` environments under
@@ -397,6 +397,8 @@ def time_policy_step(dev: torch.device, n_envs: int = 8192, n_ships: int = 8, n_
                              "bf16 autocast", "env_steps_per_call": n_envs, "steps": steps}
     ms, launches = timed(lambda: mine.get_action_and_value(obs, hidden))
     out["ours"] = {"ms_per_step": ms, "env_steps_per_s": n_envs / (ms * 1e-3), "own_kernel_launches_per_step": launches}
+    if eager_only:
+        return out
     try:
         mine_c = torch.compile(mine.get_action_and_value, mode="reduce-overhead")
         ms, launches = timed(lambda: mine_c(obs, hidden))
@@ -870,6 +872,7 @@ def main() -> None:
     ap.add_argument("--no-train", action="store_true", help="skip the forward + backward record (train_step)")
     ap.add_argument("--no-policy", action="store_true", help="skip the whole-policy rollout step record (policy_step)")
     ap.add_argument("--policy-only", action="store_true", help="only the whole-policy rollout step record (for profiling)")
+    ap.add_argument("--policy-eager", action="store_true", help="with --policy-only: this package's eager leg alone (for profiler captures)")
     ap.add_argument("--no-others", action="store_true", help="skip the C3 / C4 / C2B records (other_workloads)")
     ap.add_argument("--train-only", action="store_true", help="only this package's forward + backward record (for profiling)")
     ap.add_argument("--train-envs", type=int, default=1024, help="environments of the forward + backward record")
@@ -884,7 +887,8 @@ def main() -> None:
         run_train_only(args)
     elif args.policy_only:
         torch.cuda.set_device(0)
-        print(json.dumps({"policy_step": time_policy_step(torch.device("cuda", 0), steps=args.steps if args.steps < 20 else 10)}), flush=True)
+        print(json.dumps({"policy_step": time_policy_step(torch.device("cuda", 0), steps=args.steps if args.steps < 20 else 10,
+                                                          eager_only=args.policy_eager)}), flush=True)
     elif args.impl == "reference":
         run_reference(args)
     else:

@@ -43,7 +43,7 @@ class TemporalGrads(C.Structure):
 
 
 class Bullets(C.Structure):
-    _fields_ = [("tokens", _fp), ("active", _fp), ("per_env", C.c_int32)]
+    _fields_ = [("tokens", _fp), ("active", _fp), ("per_env", C.c_int32), ("tokens_bf16", C.c_int32)]
 
 
 class TemporalWeights(C.Structure):
@@ -282,8 +282,10 @@ class BulletArgs:
     Holds the converted tensors so they outlive the asynchronous launch.
     """
 
-    def __init__(self, bullets: Optional[torch.Tensor], bullet_mask: Optional[torch.Tensor], n_envs: int, d_model: int):
+    def __init__(self, bullets: Optional[torch.Tensor], bullet_mask: Optional[torch.Tensor], n_envs: int, d_model: int,
+                 keep_bf16: bool = False):
         self.struct = None
+        self.is_bf16 = False
         self.per_env = 0
         if bullets is None:
             return
@@ -292,10 +294,13 @@ class BulletArgs:
         require_cuda(bullets, "bullets")
         if bullet_mask is not None and tuple(bullet_mask.shape) != tuple(bullets.shape[:2]):
             raise RuntimeError(f"bullet_mask must have shape {tuple(bullets.shape[:2])}, got {tuple(bullet_mask.shape)}")
-        self.tokens = f32c(bullets)
+        # bfloat16 tokens (the BulletEncoder's output under CUDA autocast) go in as they are when the
+        # caller knows the tensor-core kernels serve the call; anything else as float32
+        self.is_bf16 = keep_bf16 and bullets.dtype == torch.bfloat16
+        self.tokens = (bullets if bullets.is_contiguous() else bullets.contiguous()) if self.is_bf16 else f32c(bullets)
         self.active = u8(bullet_mask)
         self.per_env = int(bullets.shape[1])
-        self.struct = Bullets(self.tokens.data_ptr(), ptr(self.active), self.per_env)
+        self.struct = Bullets(self.tokens.data_ptr(), ptr(self.active), self.per_env, 1 if self.is_bf16 else 0)
 
     @property
     def arg(self):

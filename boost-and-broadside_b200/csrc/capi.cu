@@ -242,7 +242,7 @@ static int trunk_common(const BnbSpatialWeights* spatial, const BnbTemporalWeigh
       (engine == BNB_ENGINE_TENSOR || all_packed(spatial, n_blocks * n_spatial, temporal, n_blocks * n_temporal)))
     return bnb::tensor::trunk(spatial, temporal, n_blocks, n_spatial, n_temporal, D, H, x, alive, bullets, y, hidden_in,
                               hidden_out, done, reset_env, *batch, T, scratch, scratch_bytes, cs, io_bf16);
-  if (engine == BNB_ENGINE_TENSOR || io_bf16) return BNB_ERR_UNSUPPORTED_DIMS;
+  if (engine == BNB_ENGINE_TENSOR || io_bf16 || (bullets && bullets->tokens_bf16)) return BNB_ERR_UNSUPPORTED_DIMS;
 
   Scratch s{nullptr, nullptr, nullptr, 0};
   if (n_blocks * n_spatial > 0 &&
@@ -389,6 +389,7 @@ int bnb_trunk_sequence_bwd(const BnbSpatialWeights* spatial, const BnbTemporalWe
   if (bullets) {
     if (bullets->per_env < 1 || !bullets->tokens) return BNB_ERR_BAD_ARGUMENT;
     if (!aligned16(bullets->tokens)) return BNB_ERR_MISALIGNED;
+    if (bullets->tokens_bf16) return BNB_ERR_UNSUPPORTED_DIMS;
   }
   bnb::grad::TrunkBwdArgs a{spatial, temporal, d_spatial, d_temporal, n_blocks, n_spatial, n_temporal, d_model, n_heads,
                             x, alive, bullets, hidden_in, done, batch, timesteps, precision == BNB_BF16, dy, d_hidden_out, dx, d_hidden_in,
@@ -453,7 +454,7 @@ int bnb_encoder_mlp_fwd(const float* w1, const float* b1, const float* g1, const
   for (const void* p : ps) if (!p) return BNB_ERR_NULL_POINTER;
   if (!aligned16(w1) || !aligned16(w2)) return BNB_ERR_MISALIGNED;
   if (precision == BNB_BF16 && bnb::mlp::supported(in_pad, hidden, out_dim))
-    return bnb::mlp::encoder_mlp_bf16(w1, b1, g1, w2, b2, g2, in_dim, in_pad, hidden, out_dim, out_dim, x, y, n_rows,
+    return bnb::mlp::encoder_mlp_bf16(w1, b1, g1, w2, b2, g2, in_dim, in_pad, hidden, out_dim, out_dim, x, false, y, n_rows,
                                       static_cast<cudaStream_t>(stream));
   return bnb::exact::encoder_mlp(w1, b1, g1, w2, b2, g2, in_dim, in_pad, hidden, out_dim, out_dim, x, y, n_rows,
                                  precision == BNB_BF16, static_cast<cudaStream_t>(stream));
@@ -466,14 +467,17 @@ int bnb_head_mlp_fwd(const float* w1, const float* b1, const float* g1, const fl
   if (hidden <= 0 || hidden % 32 != 0 || hidden > 256) return BNB_ERR_UNSUPPORTED_DIMS;
   if (out_dim <= 0 || out_pad < out_dim || out_pad % 32 != 0 || out_pad > 128) return BNB_ERR_UNSUPPORTED_DIMS;
   if (n_rows < 0) return BNB_ERR_BAD_ARGUMENT;
+  const bool x_bf16 = precision == BNB_BF16_IO;   // x holds bfloat16 tokens (the trunk's output under autocast)
+  if (x_bf16) precision = BNB_BF16;
   if (precision != BNB_FP32 && precision != BNB_BF16) return BNB_ERR_BAD_ARGUMENT;
   if (n_rows == 0) return BNB_OK;
   const void* ps[] = {w1, b1, g1, w2, b2, x, y};
   for (const void* p : ps) if (!p) return BNB_ERR_NULL_POINTER;
   if (!aligned16(w1) || !aligned16(w2)) return BNB_ERR_MISALIGNED;
   if (precision == BNB_BF16 && bnb::mlp::supported(in_dim, hidden, out_pad))
-    return bnb::mlp::encoder_mlp_bf16(w1, b1, g1, w2, b2, nullptr, in_dim, in_dim, hidden, out_pad, out_dim, x, y, n_rows,
+    return bnb::mlp::encoder_mlp_bf16(w1, b1, g1, w2, b2, nullptr, in_dim, in_dim, hidden, out_pad, out_dim, x, x_bf16, y, n_rows,
                                       static_cast<cudaStream_t>(stream));
+  if (x_bf16) return BNB_ERR_UNSUPPORTED_DIMS;   // only the tiled kernel reads bfloat16 rows
   return bnb::exact::encoder_mlp(w1, b1, g1, w2, b2, nullptr, in_dim, in_dim, hidden, out_pad, out_dim, x, y, n_rows,
                                  precision == BNB_BF16, static_cast<cudaStream_t>(stream));
 }

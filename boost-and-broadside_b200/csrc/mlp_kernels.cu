@@ -90,7 +90,7 @@ __device__ __forceinline__ void linear1_chunk(float (&acc)[8][4], uint32_t sX, u
 // 8: up to 128, the encoders).
 template <int NP2>
 __global__ void __launch_bounds__(32 * MAX_WARPS, 1)
-k_mlp_bf16(const float* __restrict__ x, __nv_bfloat16* __restrict__ y, int n_rows, int in_dim, int in_pad, int hidden,
+k_mlp_bf16(const float* __restrict__ x, int x_bf16, __nv_bfloat16* __restrict__ y, int n_rows, int in_dim, int in_pad, int hidden,
            int out_dim, int out_store, const float* __restrict__ w1, const float* __restrict__ b1,
            const float* __restrict__ g1, const float* __restrict__ w2, const float* __restrict__ b2,
            const float* __restrict__ g2) {
@@ -147,7 +147,27 @@ k_mlp_bf16(const float* __restrict__ x, __nv_bfloat16* __restrict__ y, int n_row
     const int n_valid = min(SLICE, n_rows - row0);
     // ---- this slice's input rows: one contiguous span of global memory.  Eight loads (four 16-byte
     // ones) are issued before the first is used: a warp keeps that many requests in flight.
-    if (vec_in) {
+    if (x_bf16) {   // rows already hold bfloat16 (in_dim == in_pad, a multiple of 16): 16-byte pieces, copied as they are
+      const int p_per_row = in_pad >> 3, pieces = n_valid * p_per_row;
+      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(x) + (size_t)row0 * in_dim);
+      for (int i0 = 0; i0 < (in_pad >> 4); i0 += 4) {   // SLICE * p_per_row / 32 iterations in all
+        uint4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int idx = lane + 32 * (i0 + j);
+          v[j] = make_uint4(0u, 0u, 0u, 0u);
+          if (idx < pieces) v[j] = src[idx];
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int idx = lane + 32 * (i0 + j);
+          if (idx < SLICE * p_per_row) {
+            const int r = idx / p_per_row, q = idx - r * p_per_row;
+            *reinterpret_cast<uint4*>(X + r * ldx + q * 8) = v[j];
+          }
+        }
+      }
+    } else if (vec_in) {
       const int quads = n_valid * q_per_row;
       const float4* src = reinterpret_cast<const float4*>(x + (size_t)row0 * in_dim);
       for (int i0 = 0; i0 < (in_pad >> 3); i0 += 4) {   // SLICE * q_per_row / 32 iterations in all, a multiple of 4 or just 2
@@ -327,9 +347,10 @@ bool supported(int in_pad, int hidden, int out_dim) {
 }
 
 int encoder_mlp_bf16(const float* w1, const float* b1, const float* g1, const float* w2, const float* b2, const float* g2,
-                     int in_dim, int in_pad, int hidden, int out_dim, int out_store, const float* x, void* y, int n_rows,
-                     cudaStream_t st) {
+                     int in_dim, int in_pad, int hidden, int out_dim, int out_store, const void* x, bool x_bf16, void* y,
+                     int n_rows, cudaStream_t st) {
   if (!supported(in_pad, hidden, out_dim)) return BNB_ERR_UNSUPPORTED_DIMS;
+  if (x_bf16 && (in_dim != in_pad || (reinterpret_cast<uintptr_t>(x) & 15))) return BNB_ERR_UNSUPPORTED_DIMS;
   if (n_rows <= 0) return BNB_OK;
   if (reinterpret_cast<uintptr_t>(y) & 3) return BNB_ERR_MISALIGNED;
   const Layout L = layout(in_pad, hidden, out_dim);
@@ -342,7 +363,7 @@ int encoder_mlp_bf16(const float* w1, const float* b1, const float* g1, const fl
   const int want = (n_slices + L.warps - 1) / L.warps;
   const int grid = want < sms ? want : sms;
   count_launch();
-  kernel<<<grid, 32 * L.warps, L.total, st>>>(x, static_cast<__nv_bfloat16*>(y), n_rows, in_dim, in_pad, hidden, out_dim, out_store,
+  kernel<<<grid, 32 * L.warps, L.total, st>>>(static_cast<const float*>(x), x_bf16 ? 1 : 0, static_cast<__nv_bfloat16*>(y), n_rows, in_dim, in_pad, hidden, out_dim, out_store,
                                               w1, b1, g1, w2, b2, g2);
   return cudaGetLastError() == cudaSuccess ? BNB_OK : BNB_ERR_LAUNCH;
 }

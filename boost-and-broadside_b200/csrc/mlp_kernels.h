@@ -10,9 +10,10 @@ bool supported(int in_pad, int hidden, int out_dim);
 
 // Linear(in, hidden) + b1 -> RMSNorm(g1) -> GELU -> Linear(hidden, out) + b2 [-> RMSNorm(g2)], bfloat16 result,
 // the first out_store columns of each row stored.  w1 is (hidden, in_pad) with zero columns beyond in_dim.
+// x holds float32 rows, or with x_bf16 bfloat16 rows (then in_dim == in_pad and x on a 16-byte boundary).
 int encoder_mlp_bf16(const float* w1, const float* b1, const float* g1, const float* w2, const float* b2, const float* g2,
-                     int in_dim, int in_pad, int hidden, int out_dim, int out_store, const float* x, void* y, int n_rows,
-                     cudaStream_t st);
+                     int in_dim, int in_pad, int hidden, int out_dim, int out_store, const void* x, bool x_bf16, void* y,
+                     int n_rows, cudaStream_t st);
 
 }  // namespace mlp
 }  // namespace bnb

@@ -1038,7 +1038,7 @@ __global__ void __launch_bounds__(128 * NQ, NQ == 4 ? 1 : 2) k_trunk_tiles(const
           const long long rn = (long long)r + (long long)gridDim.x * TILE;
           if (rn < flat_limit) {
             const size_t src = args.row_index ? (size_t)args.row_index[rn] : (size_t)rn;
-            const char* nx = reinterpret_cast<const char*>(args.x + src * D) + c.part * (512 / NQ);
+            const char* nx = reinterpret_cast<const char*>(args.x) + src * D * (args.io_bf16 ? 2 : 4) + c.part * (512 / NQ);
 #pragma unroll
             for (int l = 0; l < 4 / NQ; ++l) asm volatile("prefetch.global.L2 [%0];" ::"l"(nx + l * 128));
           }
@@ -1110,12 +1110,28 @@ __global__ void __launch_bounds__(128 * NQ, NQ == 4 ? 1 : 2) k_trunk_tiles(const
 #pragma unroll
         for (int ch = 0; ch < CPT / 32; ++ch) {
           uint32_t v[32];
+          const size_t xoff = (xrow0 + (size_t)t * map.total_tokens) * D + c.part * CPT + ch * 32;
+          if (args.io_bf16) {   // input rows held as bfloat16 (this kernel's y, when it has one, stays float32)
+            const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(args.x) + xoff);
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (valid) f = *reinterpret_cast<const float4*>(args.x + (xrow0 + (size_t)t * map.total_tokens) * D + c.part * CPT + ch * 32 + q * 4);
-            v[q * 4 + 0] = __float_as_uint(f.x); v[q * 4 + 1] = __float_as_uint(f.y);
-            v[q * 4 + 2] = __float_as_uint(f.z); v[q * 4 + 3] = __float_as_uint(f.w);
+            for (int q = 0; q < 4; ++q) {
+              uint4 w = make_uint4(0u, 0u, 0u, 0u);
+              if (valid) w = src[q];
+              const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                v[q * 8 + 2 * j] = ws[j] << 16;              // a bfloat16 is the upper half of its float
+                v[q * 8 + 2 * j + 1] = ws[j] & 0xFFFF0000u;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (valid) f = *reinterpret_cast<const float4*>(args.x + xoff + q * 4);
+              v[q * 4 + 0] = __float_as_uint(f.x); v[q * 4 + 1] = __float_as_uint(f.y);
+              v[q * 4 + 2] = __float_as_uint(f.z); v[q * 4 + 3] = __float_as_uint(f.w);
+            }
           }
           tmem_st32(c.lane_addr + COL_RESID + c.part * CPT + ch * 32, v);
         }
@@ -1767,7 +1783,7 @@ static int launch_compact(const uint8_t* active, int n_env, int nb, int* env_off
 
 // norm_bullet + kv_bullet of bullet rows (a slice of whole environments) into kvb: all `rows`
 // rows in order, or, with idx / n_rows_dev, the first *n_rows_dev rows of idx.
-static int launch_bullet_kv(const BnbSpatialWeights& w, const float* bullet_rows, int rows, const int* idx,
+static int launch_bullet_kv(const BnbSpatialWeights& w, const float* bullet_rows, bool rows_bf16, int rows, const int* idx,
                             const int* n_rows_dev, __nv_bfloat16* kvb, int* status, cudaStream_t st) {
   if (rows <= 0) return BNB_OK;
   TrunkArgs a{};
@@ -1775,6 +1791,7 @@ static int launch_bullet_kv(const BnbSpatialWeights& w, const float* bullet_rows
   a.row_index = idx;
   a.n_rows_dev = n_rows_dev;
   a.y = nullptr;              // nothing but the keys and values leaves this program
+  a.io_bf16 = rows_bf16 ? 1 : 0;
   a.status = status;
   a.n_groups = 1;
   a.t_loop = 1;
@@ -1875,7 +1892,11 @@ struct Plan {
           if ((rc = launch_compact(bullets->active + (size_t)e0 * nb, ne, nb, env_off, idx, st))) return rc;
           compacted_e0 = e0;
         }
-        if ((rc = launch_bullet_kv(w, bullets->tokens + (size_t)e0 * nb * D, ne * nb, masked ? idx : nullptr,
+        const bool rows_bf16 = bullets->tokens_bf16 != 0;
+        const float* rows0 = rows_bf16
+            ? reinterpret_cast<const float*>(reinterpret_cast<const __nv_bfloat16*>(bullets->tokens) + (size_t)e0 * nb * D)
+            : bullets->tokens + (size_t)e0 * nb * D;
+        if ((rc = launch_bullet_kv(w, rows0, rows_bf16, ne * nb, masked ? idx : nullptr,
                                    masked ? env_off + ne : nullptr, kvb, status, st)))
           return rc;
         if ((rc = launch_attention(qkv, alive, o, b, e0, ne, kvb, masked ? env_off : nullptr, nb, st))) return rc;

@@ -133,7 +133,9 @@ def trunk_forward(
                     ts, dev, image_buffer("temporal", ts, 4, dev, precision, engine))
         if pos != len(weights):
             raise RuntimeError(f"expected {pos} parameter tensors for this trunk structure, got {len(weights)}")
-        bul = _capi.BulletArgs(bullets if n_cross > 0 else None, bullet_mask, T * batch.n_envs, D)
+        bul16 = (precision == _capi.BNB_BF16 and engine != _capi.ENGINE_SIMT and geom[G_MAX_TOKENS] > 0
+                 and bool(_capi.lib.bnb_supported(D, n_heads, geom[G_MAX_TOKENS], _capi.BNB_BF16, _capi.ENGINE_TENSOR)))
+        bul = _capi.BulletArgs(bullets if n_cross > 0 else None, bullet_mask, T * batch.n_envs, D, keep_bf16=bul16)
         nbytes = _capi.lib.bnb_scratch_bytes(D, batch, T, bul.per_env)
         scratch = _capi.scratch_for(dev, nbytes)
         stream = _capi.stream_handle(dev)
@@ -156,6 +158,15 @@ def trunk_forward(
                 y.data_ptr(), _capi.ptr(hin), _capi.ptr(hout), _capi.ptr(done_u8), batch, T,
                 _capi.BNB_BF16_IO if io16 else precision, engine, scratch.data_ptr(), scratch.numel(), stream,
             )
+        if st == 3 and bul.is_bf16:
+            # the call fell to the float32-reading kernels (a shape the tensor-core kernels do not serve,
+            # e.g. more bullet slots than their attention stages): once more with float32 bullet tokens
+            bul = _capi.BulletArgs(bullets, bullet_mask, T * batch.n_envs, D)
+            call = _capi.lib.bnb_trunk_step if geom[G_TIMESTEPS] == 0 else _capi.lib.bnb_trunk_sequence
+            tail = ((_capi.ptr(reset_u8), batch) if geom[G_TIMESTEPS] == 0 else (_capi.ptr(done_u8), batch, T))
+            st = call(sw, tw, n_blocks, n_spatial, n_temporal, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8), bul.arg,
+                      y.data_ptr(), _capi.ptr(hin), _capi.ptr(hout), *tail, _capi.BNB_BF16_IO if io16 else precision, engine,
+                      scratch.data_ptr(), scratch.numel(), stream)
     _capi.check(fn, st)
     _capi.note_engine_choice(fn)
     _debug_check(fn, dev, precision)

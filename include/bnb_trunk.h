@@ -117,6 +117,10 @@ typedef struct {
   const uint8_t* active;  /* (n_groups * n_envs, per_env) bytes, or NULL: every slot is a key and
                              the branch is never gated off (bullet_mask=None in the reference) */
   int32_t per_env;        /* NB >= 1 */
+  int32_t tokens_bf16;    /* 0: tokens are float32.  1: tokens point to bfloat16 elements (what the
+                             reference's BulletEncoder returns under CUDA autocast); only calls the
+                             tensor-core kernels serve take them (BNB_BF16 forward, supported shapes),
+                             any other call returns BNB_ERR_UNSUPPORTED_DIMS */
 } BnbBullets;
 
 /* Parameters of one temporal sublayer plus its field substitute.
@@ -414,7 +418,10 @@ int bnb_trunk_sequence_fwd_train(const BnbSpatialWeights* spatial, const BnbTemp
  *   x (n_rows, in_dim) float32, in_dim a multiple of 32 up to 128; w1 (hidden, in_dim), b1, g1
  *   (hidden); w2 (out_pad, hidden) and b2 (out_pad): the second Linear with zero rows / entries
  *   appended up to out_pad, a multiple of 32; y (n_rows, out_dim), float32 for BNB_FP32,
- *   **bfloat16 elements** for BNB_BF16 (what the last Linear returns under autocast). */
+ *   **bfloat16 elements** for BNB_BF16 (what the last Linear returns under autocast).
+ *   precision BNB_BF16_IO: the BNB_BF16 contract with x holding bfloat16 elements too (the trunk's
+ *   output under autocast), on a 16-byte boundary; served by the tiled kernel only
+ *   (BNB_ERR_UNSUPPORTED_DIMS otherwise, and the caller converts). */
 int bnb_head_mlp_fwd(const float* w1, const float* b1, const float* g1, const float* w2, const float* b2,
                      int in_dim, int hidden, int out_dim, int out_pad, const float* x, void* y, int n_rows,
                      int precision, void* stream);

@@ -268,6 +268,31 @@ def test_step_with_bullets_tensor_vs_oracle_and_simt(n_envs, ships, fields, nb):
     assert_close(yn, ref_n, "bf16", "tensor y vs oracle, no bullet mask")
 
 
+@pytest.mark.parametrize("n_envs,ships,fields,nb,masked", [(40, 8, 4, 80, True), (6, 100, 52, 33, True), (9, 8, 4, 17, False)])
+def test_bfloat16_bullet_tokens_equal_their_float32_copy(n_envs, ships, fields, nb, masked):
+    """Bullet tokens handed over as bfloat16 (what the reference's BulletEncoder returns under CUDA
+    autocast; ``BnbBullets.tokens_bf16``) are read by the key/value tile program as they are: the
+    result is bit-identical to the call with the same values widened to float32 first, for
+    environments of one tile and larger ones, with and without a mask, step and sequence."""
+    from boost_and_broadside_b200 import workloads as W
+
+    _capi, SIMT, TENSOR = _engines()
+    w = W.c2(n_envs=n_envs, seed=31, ships=ships, fields=fields)
+    bul, mask = _bullets(n_envs, nb, 9)
+    trunk = build_trunk([128, 4, 2, 2, 1, 1]).to(DEV)
+    x, alive, hidden = (t.to(DEV) for t in (w.x, w.alive, w.hidden))
+    bul16 = bul.to(DEV).to(torch.bfloat16)
+    mask_d = mask.to(DEV) if masked else None
+    with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
+        y16, h16 = trunk.step(x, alive, hidden, engine=TENSOR, bullets=bul16, bullet_mask=mask_d)
+        y32, h32 = trunk.step(x, alive, hidden, engine=TENSOR, bullets=bul16.float(), bullet_mask=mask_d)
+        # the exact engine reads float32 only: the module converts for it
+        ys, _ = trunk.step(x, alive, hidden, engine=SIMT, bullets=bul16, bullet_mask=mask_d)
+    _status_ok()
+    assert torch.equal(y16, y32) and torch.equal(h16, h32)
+    assert norm_err(y16.cpu(), ys.cpu()) < 1e-2
+
+
 def test_sequence_with_bullets_tensor_vs_oracle():
     from boost_and_broadside_b200 import workloads as W
 
