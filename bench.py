@@ -449,6 +449,7 @@ def time_train_step(trunk, dev: torch.device, n_envs: int = 1024, timesteps: int
         torch.cuda.synchronize(dev)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.reset_peak_memory_stats(dev)
+        held = torch.cuda.memory_allocated(dev)   # tensors of the bench's other legs still alive: not this step's
         e0.record()
         for _ in range(iters):
             fn()
@@ -456,7 +457,9 @@ def time_train_step(trunk, dev: torch.device, n_envs: int = 1024, timesteps: int
         torch.cuda.synchronize(dev)
         ms = e0.elapsed_time(e1) / iters
         return {"ms_per_step": ms, "value": tokens / (ms * 1e-3), "unit": UNIT,
-                "peak_gib": torch.cuda.max_memory_allocated(dev) / 2**30}
+                "peak_gib": (torch.cuda.max_memory_allocated(dev) - held) / 2**30,
+                "peak_note": "peak allocated during the timed steps above what was allocated before them "
+                             "(inputs, parameters and kept gradients included in 'before')"}
 
     was_training = trunk.training
     trunk.train()

@@ -56,7 +56,8 @@ constexpr int OFF_RING = 131072;
 constexpr int OFF_META = OFF_RING + RING_BYTES;  // env_first[128], env_n[128], alive[128], items[128]
 constexpr int OFF_ROWINFO = OFF_META + 512;                     // hidden row of each tile row (int), then flags[128]
 constexpr int OFF_SS = OFF_ROWINFO + 640;                       // partial sums of squares [4][128]
-constexpr int OFF_BAR = OFF_SS + 2048;
+constexpr int OFF_BIAS = OFF_SS + 2048;                         // attention bias of each tile row as a key (float), + 16 of slack
+constexpr int OFF_BAR = OFF_BIAS + 576;
 constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
 
 // mbarrier indices
@@ -356,7 +357,8 @@ __device__ __forceinline__ void attention(Epi& e, int n_items) {
   const uint32_t atom = (uint32_t)(h >> 1) * CHUNK_BYTES;
   const int c8h = (h & 1) * 4;
   const uint32_t sQ = e.sbase + OFF_A + atom, sK = e.sbase + OFF_KV + atom, sV = sK + 2 * CHUNK_BYTES;
-  const float scale = 0.17677669529663687f;  // 1/sqrt(32)
+  const float* key_bias = reinterpret_cast<const float*>(e.smem + OFF_BIAS);
+  const float c2 = 0.17677669529663687f * 1.4426950408889634f;  // log2(e) / sqrt(32): scores in the log2 domain
   for (int it = warp >> 2; it < n_items; it += EPI_WARPS / 4) {
     const int r0 = meta[384 + it];
     const int e0 = meta[r0], n = meta[128 + r0] + 1;   // first tile row and size of the environment
@@ -397,10 +399,11 @@ __device__ __forceinline__ void attention(Epi& e, int n_items) {
         for (int i = 0; i < 2; ++i) {
           const int j = kb * 16 + nt * 8 + 2 * t + i;
           const bool valid = j < n;
-          const bool lv = valid && meta[256 + e0 + j];
-          // a dead key scores kMaskedScore (weight exactly 0 unless every key is dead: then uniform)
-          const float a = valid ? (lv ? sc[nt][i] * scale : kMaskedScore) : -INFINITY;
-          const float b = valid ? (lv ? sc[nt][2 + i] * scale : kMaskedScore) : -INFINITY;
+          // a dead key's bias (kMaskedScore) swallows its score: weight exactly 0 unless every key is
+          // dead, then uniform; rows past the environment's last are no keys at all
+          const float bj = key_bias[e0 + j];
+          const float a = valid ? fmaf(sc[nt][i], c2, bj) : -INFINITY;
+          const float b = valid ? fmaf(sc[nt][2 + i], c2, bj) : -INFINITY;
           sc[nt][i] = a;
           sc[nt][2 + i] = b;
           bm0 = fmaxf(bm0, a);
@@ -411,7 +414,7 @@ __device__ __forceinline__ void attention(Epi& e, int n_items) {
       bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, 1));
       bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, 2));
       const float n0 = fmaxf(m0, bm0), n1 = fmaxf(m1, bm1);   // finite: every block holds a valid key
-      const float c0 = __expf(m0 - n0), c1 = __expf(m1 - n1); // exp(-inf) = 0 on the first block
+      const float c0 = ex2_fast(m0 - n0), c1 = ex2_fast(m1 - n1); // 2^(-inf) = 0 on the first block
       m0 = n0;
       m1 = n1;
       l0 *= c0;
@@ -425,7 +428,7 @@ __device__ __forceinline__ void attention(Epi& e, int n_items) {
       for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-          const float a = __expf(sc[nt][i] - m0), b = __expf(sc[nt][2 + i] - m1);
+          const float a = ex2_fast(sc[nt][i] - m0), b = ex2_fast(sc[nt][2 + i] - m1);
           sc[nt][i] = a;
           sc[nt][2 + i] = b;
           l0 += a;
@@ -1141,7 +1144,11 @@ __global__ void __launch_bounds__(THREADS, 1) k_trunk_pipelined(const __grid_con
 
       for (int t = 0; t < args.t_loop; ++t) {
         const size_t trow = grow + (size_t)t * map.total_tokens;
-        if (e.part == 0) meta[256 + row] = valid ? (args.alive ? args.alive[trow] : (uint8_t)1) : (uint8_t)0;
+        if (e.part == 0) {
+          const bool live = valid && (!args.alive || args.alive[trow]);
+          meta[256 + row] = live ? (uint8_t)1 : (uint8_t)0;
+          reinterpret_cast<float*>(smem + OFF_BIAS)[row] = live ? 0.f : kMaskedScore;
+        }
         // residual <- x (this thread: columns [32 part, 32 part + 32))
         {
           uint32_t v[32];

@@ -1,6 +1,8 @@
 """The tensor-core (tcgen05) engine against the CPU oracle and against the SIMT engine on
 the same inputs, called through the C ABI with the engine chosen explicitly."""
 
+import warnings
+
 import pytest
 import torch
 
@@ -284,13 +286,33 @@ def test_bfloat16_bullet_tokens_equal_their_float32_copy(n_envs, ships, fields, 
     bul16 = bul.to(DEV).to(torch.bfloat16)
     mask_d = mask.to(DEV) if masked else None
     with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
+        # the exact engine reads float32 only: the module converts for it (first: its scratch overlays the status word)
+        ys, _ = trunk.step(x, alive, hidden, engine=SIMT, bullets=bul16, bullet_mask=mask_d)
         y16, h16 = trunk.step(x, alive, hidden, engine=TENSOR, bullets=bul16, bullet_mask=mask_d)
         y32, h32 = trunk.step(x, alive, hidden, engine=TENSOR, bullets=bul16.float(), bullet_mask=mask_d)
-        # the exact engine reads float32 only: the module converts for it
-        ys, _ = trunk.step(x, alive, hidden, engine=SIMT, bullets=bul16, bullet_mask=mask_d)
     _status_ok()
     assert torch.equal(y16, y32) and torch.equal(h16, h32)
     assert norm_err(y16.cpu(), ys.cpu()) < 1e-2
+
+
+def test_bfloat16_bullet_tokens_on_a_shape_the_tensor_kernels_do_not_serve():
+    """3000 bullet slots per environment are more than the attention kernel stages: the call is
+    served by the float32-reading kernels, which refuse bfloat16 tokens (BNB_ERR_UNSUPPORTED_DIMS);
+    the module then hands them a float32 copy, and the result equals the float32 call."""
+    from boost_and_broadside_b200 import workloads as W
+
+    w = W.c2(n_envs=2, seed=37, ships=8, fields=4)
+    bul, mask = _bullets(2, 3000, 11, p_active=0.1)
+    trunk = build_trunk([128, 4, 2, 2, 1, 1]).to(DEV)
+    x, alive, hidden = (t.to(DEV) for t in (w.x, w.alive, w.hidden))
+    bul16 = bul.to(DEV).to(torch.bfloat16)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")   # the once-per-process note that the exact kernels served a bf16 call
+        with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
+            y16, h16 = trunk.step(x, alive, hidden, bullets=bul16, bullet_mask=mask.to(DEV))
+            y32, h32 = trunk.step(x, alive, hidden, bullets=bul16.float(), bullet_mask=mask.to(DEV))
+    assert torch.equal(y16, y32) and torch.equal(h16, h32)
+    assert bool(torch.isfinite(y16.float()).all())
 
 
 def test_sequence_with_bullets_tensor_vs_oracle():
