@@ -65,30 +65,33 @@ __host__ __device__ inline Layout layout(int in_pad, int hidden, int out_dim) {
 }
 
 // One 64-column chunk of Linear 1 for the warp's 16 rows: acc[nt] = X W1[c0 + 8 nt ..]^T.
-__device__ __forceinline__ void linear1_chunk(float (&acc)[8][4], uint32_t sX, uint32_t sW1, int ldx, int in_pad, int c0, int npairs,
+template <int IN16>
+__device__ __forceinline__ void linear1_chunk(float (&acc)[8][4], uint32_t sX, uint32_t sW1, int ldx, int c0,
                                               int a_off, int b_row, int b_k) {
 #pragma unroll
   for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
-  for (int k0 = 0; k0 < in_pad; k0 += 16) {
+#pragma unroll
+  for (int ks = 0; ks < IN16; ++ks) {
+    const int k0 = ks * 16;
     uint32_t a0, a1, a2, a3;
     ldsm_x4(sX + (a_off + k0) * 2, a0, a1, a2, a3);
 #pragma unroll
     for (int np = 0; np < 4; ++np) {
-      if (np < npairs) {
-        uint32_t q0, q1, q2, q3;
-        ldsm_x4(sW1 + ((c0 + np * 16 + b_row) * ldx + k0 + b_k) * 2, q0, q1, q2, q3);
-        mma_bf16(acc[2 * np], a0, a1, a2, a3, q0, q1);
-        mma_bf16(acc[2 * np + 1], a0, a1, a2, a3, q2, q3);
-      }
+      uint32_t q0, q1, q2, q3;
+      ldsm_x4(sW1 + ((c0 + np * 16 + b_row) * ldx + k0 + b_k) * 2, q0, q1, q2, q3);
+      mma_bf16(acc[2 * np], a0, a1, a2, a3, q0, q1);
+      mma_bf16(acc[2 * np + 1], a0, a1, a2, a3, q2, q3);
     }
   }
 }
 
-// NP2: pairs of 8-column output blocks held in registers (2: up to 32 output columns, the heads;
-// 8: up to 128, the encoders).
-template <int NP2>
+// NP2: pairs of 8-column output blocks (out_dim = 16 NP2: 32 for the heads, 128 for the encoders);
+// NCH: 64-column chunks of the hidden layer (hidden = 64 NCH).  Both are compile-time so that every
+// loop over fragments unrolls without guards; so is IN16, the 16-wide k steps of the first product
+// (in_pad = 16 IN16).
+template <int NP2, int NCH, int IN16>
 __global__ void __launch_bounds__(32 * MAX_WARPS, 1)
 k_mlp_bf16(const float* __restrict__ x, int x_bf16, __nv_bfloat16* __restrict__ y, int n_rows, int in_dim, int in_pad, int hidden,
            int out_dim, int out_store, const float* __restrict__ w1, const float* __restrict__ b1,
@@ -107,14 +110,44 @@ k_mlp_bf16(const float* __restrict__ x, int x_bf16, __nv_bfloat16* __restrict__ 
   const int n_threads = blockDim.x;
   const int g = lane >> 2, t = lane & 3;
 
-  // the weights, once per CTA: float32 in global memory, bfloat16 operands here
-  for (int idx = tid; idx < hidden * in_pad; idx += n_threads) {
-    const int r = idx / in_pad, c = idx - r * in_pad;
-    W1[r * ldx + c] = __float2bfloat16_rn(w1[idx]);
-  }
-  for (int idx = tid; idx < out_dim * hidden; idx += n_threads) {
-    const int r = idx / hidden, c = idx - r * hidden;
-    W2[r * ldw + c] = __float2bfloat16_rn(w2[idx]);
+  // the weights, once per CTA: float32 in global memory (rows of whole 16-byte pieces on 16-byte
+  // boundaries), bfloat16 operands here; four loads in flight per thread
+  {
+    constexpr int Q1 = 4 * IN16, Q2 = 16 * NCH;   // 16-byte pieces per row of w1 (in_pad wide) and w2 (hidden wide)
+    const float4* s1 = reinterpret_cast<const float4*>(w1);
+    for (int i0 = tid; i0 < hidden * Q1; i0 += 4 * n_threads) {
+      float4 v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int idx = i0 + j * n_threads;
+        if (idx < hidden * Q1) v[j] = s1[idx];
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int idx = i0 + j * n_threads;
+        if (idx < hidden * Q1) {
+          const int r = idx / Q1, q = idx - r * Q1;
+          *reinterpret_cast<uint2*>(W1 + r * ldx + q * 4) = make_uint2(pack_bf16(v[j].x, v[j].y), pack_bf16(v[j].z, v[j].w));
+        }
+      }
+    }
+    const float4* s2 = reinterpret_cast<const float4*>(w2);
+    for (int i0 = tid; i0 < out_dim * Q2; i0 += 4 * n_threads) {
+      float4 v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int idx = i0 + j * n_threads;
+        if (idx < out_dim * Q2) v[j] = s2[idx];
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int idx = i0 + j * n_threads;
+        if (idx < out_dim * Q2) {
+          const int r = idx / Q2, q = idx - r * Q2;
+          *reinterpret_cast<uint2*>(W2 + r * ldw + q * 4) = make_uint2(pack_bf16(v[j].x, v[j].y), pack_bf16(v[j].z, v[j].w));
+        }
+      }
+    }
   }
   for (int i = tid; i < hidden; i += n_threads) {
     b1s[i] = round_bf16(b1[i]);
@@ -134,8 +167,7 @@ k_mlp_bf16(const float* __restrict__ x, int x_bf16, __nv_bfloat16* __restrict__ 
   const int b_row = (lane & 7) + (lane >> 4) * 8, b_k = ((lane >> 3) & 1) * 8;
   const int n_slices = (n_rows + SLICE - 1) / SLICE;
   const int warps = n_threads >> 5;
-  const int npairs2 = out_dim >> 4;
-  const bool two_pass = hidden > 64;
+  constexpr bool two_pass = NCH > 1;
   // input rows as 16-byte pieces when rows are whole pieces on 16-byte boundaries, else element by
   // element; idx / d for idx < 2048 and d <= 128 as a multiplication (exact: the error stays below 1 / 512)
   const bool vec_in = in_dim == in_pad && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
@@ -211,18 +243,17 @@ k_mlp_bf16(const float* __restrict__ x, int x_bf16, __nv_bfloat16* __restrict__ 
     float acc[8][4];
     float ss0 = 0.f, ss1 = 0.f;
     if (two_pass) {   // the sum of squares of the rounded Linear 1 output, every chunk
-      for (int c0 = 0; c0 < hidden; c0 += 64) {
-        const int npairs = min(4, (hidden - c0) >> 4);
-        linear1_chunk(acc, sX, sW1, ldx, in_pad, c0, npairs, a_off, b_row, b_k);
+#pragma unroll 1
+      for (int ch = 0; ch < NCH; ++ch) {
+        const int c0 = ch * 64;
+        linear1_chunk<IN16>(acc, sX, sW1, ldx, c0, a_off, b_row, b_k);
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
-          if (nt < 2 * npairs) {
-            const float2 bb = *reinterpret_cast<const float2*>(b1s + c0 + nt * 8 + 2 * t);
-            const float h00 = round_bf16(acc[nt][0] + bb.x), h01 = round_bf16(acc[nt][1] + bb.y);
-            const float h10 = round_bf16(acc[nt][2] + bb.x), h11 = round_bf16(acc[nt][3] + bb.y);
-            ss0 = fmaf(h00, h00, fmaf(h01, h01, ss0));
-            ss1 = fmaf(h10, h10, fmaf(h11, h11, ss1));
-          }
+          const float2 bb = *reinterpret_cast<const float2*>(b1s + c0 + nt * 8 + 2 * t);
+          const float h00 = round_bf16(acc[nt][0] + bb.x), h01 = round_bf16(acc[nt][1] + bb.y);
+          const float h10 = round_bf16(acc[nt][2] + bb.x), h11 = round_bf16(acc[nt][3] + bb.y);
+          ss0 = fmaf(h00, h00, fmaf(h01, h01, ss0));
+          ss1 = fmaf(h10, h10, fmaf(h11, h11, ss1));
         }
       }
     }
@@ -232,21 +263,20 @@ k_mlp_bf16(const float* __restrict__ x, int x_bf16, __nv_bfloat16* __restrict__ 
     for (int nt = 0; nt < 2 * NP2; ++nt)
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc2[nt][i] = 0.f;
-    for (int c0 = 0; c0 < hidden; c0 += 64) {
-      const int npairs = min(4, (hidden - c0) >> 4);
-      linear1_chunk(acc, sX, sW1, ldx, in_pad, c0, npairs, a_off, b_row, b_k);
+#pragma unroll 1
+    for (int ch = 0; ch < NCH; ++ch) {
+      const int c0 = ch * 64;
+      linear1_chunk<IN16>(acc, sX, sW1, ldx, c0, a_off, b_row, b_k);
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
-        if (nt < 2 * npairs) {
-          const float2 bb = *reinterpret_cast<const float2*>(b1s + c0 + nt * 8 + 2 * t);
-          acc[nt][0] = round_bf16(acc[nt][0] + bb.x);
-          acc[nt][1] = round_bf16(acc[nt][1] + bb.y);
-          acc[nt][2] = round_bf16(acc[nt][2] + bb.x);
-          acc[nt][3] = round_bf16(acc[nt][3] + bb.y);
-          if (!two_pass) {
-            ss0 = fmaf(acc[nt][0], acc[nt][0], fmaf(acc[nt][1], acc[nt][1], ss0));
-            ss1 = fmaf(acc[nt][2], acc[nt][2], fmaf(acc[nt][3], acc[nt][3], ss1));
-          }
+        const float2 bb = *reinterpret_cast<const float2*>(b1s + c0 + nt * 8 + 2 * t);
+        acc[nt][0] = round_bf16(acc[nt][0] + bb.x);
+        acc[nt][1] = round_bf16(acc[nt][1] + bb.y);
+        acc[nt][2] = round_bf16(acc[nt][2] + bb.x);
+        acc[nt][3] = round_bf16(acc[nt][3] + bb.y);
+        if (!two_pass) {
+          ss0 = fmaf(acc[nt][0], acc[nt][0], fmaf(acc[nt][1], acc[nt][1], ss0));
+          ss1 = fmaf(acc[nt][2], acc[nt][2], fmaf(acc[nt][3], acc[nt][3], ss1));
         }
       }
       if (c0 == 0) {   // the row sums are complete: after the first pass, or with this only chunk
@@ -260,7 +290,7 @@ k_mlp_bf16(const float* __restrict__ x, int x_bf16, __nv_bfloat16* __restrict__ 
       // RMSNorm (float32, rounded once), GELU (rounded once by the pack), then straight into Linear 2
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {
-        if (kk < npairs) {
+        {
           uint32_t a[4];
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
@@ -271,7 +301,7 @@ k_mlp_bf16(const float* __restrict__ x, int x_bf16, __nv_bfloat16* __restrict__ 
           }
 #pragma unroll
           for (int np = 0; np < NP2; ++np) {
-            if (np < npairs2) {
+            {
               uint32_t q0, q1, q2, q3;
               ldsm_x4(sW2 + ((np * 16 + b_row) * ldw + c0 + kk * 16 + b_k) * 2, q0, q1, q2, q3);
               mma_bf16(acc2[2 * np], a[0], a[1], a[2], a[3], q0, q1);
@@ -287,7 +317,7 @@ k_mlp_bf16(const float* __restrict__ x, int x_bf16, __nv_bfloat16* __restrict__ 
     ss1 = 0.f;
 #pragma unroll
     for (int nt = 0; nt < 2 * NP2; ++nt) {
-      if (nt < 2 * npairs2) {
+      {
         const float2 bb = *reinterpret_cast<const float2*>(b2s + nt * 8 + 2 * t);
         acc2[nt][0] = round_bf16(acc2[nt][0] + bb.x);
         acc2[nt][1] = round_bf16(acc2[nt][1] + bb.y);
@@ -311,7 +341,7 @@ k_mlp_bf16(const float* __restrict__ x, int x_bf16, __nv_bfloat16* __restrict__ 
     const bool pair_store = (out_store & 1) == 0;   // columns 2t, 2t+1 of a row share an aligned 4-byte word
 #pragma unroll
     for (int nt = 0; nt < 2 * NP2; ++nt) {
-      if (nt < 2 * npairs2) {
+      {
         const int c = nt * 8 + 2 * t;
         if (c < out_store) {
           const float2 s = *reinterpret_cast<const float2*>(g2s + c);
@@ -341,8 +371,9 @@ k_mlp_bf16(const float* __restrict__ x, int x_bf16, __nv_bfloat16* __restrict__ 
 }  // namespace
 
 bool supported(int in_pad, int hidden, int out_dim) {
-  if (in_pad <= 0 || in_pad % 16 != 0 || hidden <= 0 || hidden % 32 != 0 || out_dim <= 0 || out_dim % 32 != 0) return false;
-  if (in_pad > 128 || hidden > 256 || out_dim > 128) return false;
+  if (in_pad != 32 && in_pad != 64 && in_pad != 96 && in_pad != 128) return false;   // the instantiated k-step counts
+  if (hidden != 64 && hidden != 128 && hidden != 256) return false;   // the instantiated chunk counts
+  if (out_dim != 32 && out_dim != 128) return false;                  // and output widths
   return layout(in_pad, hidden, out_dim).warps >= 4;
 }
 
@@ -354,7 +385,13 @@ int encoder_mlp_bf16(const float* w1, const float* b1, const float* g1, const fl
   if (n_rows <= 0) return BNB_OK;
   if (reinterpret_cast<uintptr_t>(y) & 3) return BNB_ERR_MISALIGNED;
   const Layout L = layout(in_pad, hidden, out_dim);
-  auto kernel = out_dim <= 32 ? k_mlp_bf16<2> : k_mlp_bf16<8>;
+  using Kernel = void (*)(const float*, int, __nv_bfloat16*, int, int, int, int, int, int, const float*, const float*, const float*,
+                          const float*, const float*, const float*);
+#define BNB_MLP_ROW(NP2, NCH) {k_mlp_bf16<NP2, NCH, 2>, k_mlp_bf16<NP2, NCH, 4>, k_mlp_bf16<NP2, NCH, 6>, k_mlp_bf16<NP2, NCH, 8>}
+  static const Kernel table[2][3][4] = {{BNB_MLP_ROW(2, 1), BNB_MLP_ROW(2, 2), BNB_MLP_ROW(2, 4)},
+                                        {BNB_MLP_ROW(8, 1), BNB_MLP_ROW(8, 2), BNB_MLP_ROW(8, 4)}};
+#undef BNB_MLP_ROW
+  const Kernel kernel = table[out_dim == 32 ? 0 : 1][hidden == 64 ? 0 : hidden == 128 ? 1 : 2][in_pad / 32 - 1];
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.total) != cudaSuccess) return BNB_ERR_LAUNCH;
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
