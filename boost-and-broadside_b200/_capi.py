@@ -16,6 +16,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libbnb_trunk.so")
 
 BNB_FP32, BNB_BF16, BNB_BF16_IO = 0, 1, 2
+ERR_UNSUPPORTED_DIMS = 3   # BNB_ERR_UNSUPPORTED_DIMS: the kernels asked for do not serve these shapes / dtypes
 ENGINE_AUTO, ENGINE_SIMT, ENGINE_TENSOR = 0, 1, 2
 ABI_VERSION = 2
 
@@ -163,7 +164,7 @@ class BnbError(RuntimeError):
 
 def check(fn: str, status: int) -> None:
     if status != 0:
-        if status == 3:  # BNB_ERR_UNSUPPORTED_DIMS
+        if status == ERR_UNSUPPORTED_DIMS:
             raise ValueError(f"{fn}: {lib.bnb_status_string(status).decode()}")
         raise BnbError(fn, status)
 

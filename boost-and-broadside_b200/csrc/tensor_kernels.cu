@@ -1983,8 +1983,9 @@ int trunk(const BnbSpatialWeights* spatial, const BnbTemporalWeights* temporal, 
           float* y, const float* hidden_in, float* hidden_out, const uint8_t* done, const uint8_t* reset_env,
           const BnbBatch& b, int T, void* scratch, size_t scratch_bytes, cudaStream_t st, bool io_bf16) {
   if (!supported_batch(d_model, n_heads, b)) return BNB_ERR_UNSUPPORTED_DIMS;
-  // bfloat16 x / y: only the fused tile kernel reads and writes them
-  if (io_bf16 && (!fits_tile(b) || bullets)) return BNB_ERR_UNSUPPORTED_DIMS;
+  // bfloat16 x / y: every tile-kernel launch of the call reads and writes bfloat16 rows, so the
+  // residual stream is rounded where one launch hands over to the next (the reference, given
+  // bfloat16 tokens, rounds it after every sublayer)
   for (int i = 0; i < n_blocks * n_spatial; ++i) if (!spatial[i].packed) return BNB_ERR_UNSUPPORTED_DIMS;
   for (int i = 0; i < n_blocks * n_temporal; ++i) if (!temporal[i].packed) return BNB_ERR_UNSUPPORTED_DIMS;
   // a time walk carries its state through hidden_out between timesteps

@@ -62,7 +62,7 @@ def mlp_chain(x: Tensor, w1: Tensor, b1: Tensor, g1: Tensor, w2: Tensor, b2: Ten
             args = (w1.data_ptr(), b1.data_ptr(), g1.data_ptr(), w2p.data_ptr(), b2p.data_ptr(), in_dim, hidden, out_dim, out_pad)
             st = _capi.lib.bnb_head_mlp_fwd(*args, flat.data_ptr(), y.data_ptr(), rows, _capi.BNB_BF16_IO if x16 else precision,
                                             _capi.stream_handle(dev))
-            if st == 3 and x16:   # widths the tiled kernel does not serve: the float32-reading kernel
+            if st == _capi.ERR_UNSUPPORTED_DIMS and x16:   # widths the tiled kernel does not serve: the float32-reading kernel
                 flat = _capi.f32c(x)
                 st = _capi.lib.bnb_head_mlp_fwd(*args, flat.data_ptr(), y.data_ptr(), rows, precision, _capi.stream_handle(dev))
             _capi.check("bnb_head_mlp_fwd", st)

@@ -105,15 +105,13 @@ def trunk_forward(
         # bfloat16 on the way in and out where the fused kernel serves the call; the residual stream
         # inside the call is float32 either way.  Anything else is converted to float32 here.
         io16 = (x.dtype == torch.bfloat16 and precision == _capi.BNB_BF16 and engine != _capi.ENGINE_SIMT
-                and (bullets is None or n_cross == 0) and 0 < geom[G_MAX_TOKENS] <= 128
+                and geom[G_MAX_TOKENS] > 0
                 and bool(_capi.lib.bnb_supported(D, n_heads, geom[G_MAX_TOKENS], _capi.BNB_BF16, _capi.ENGINE_TENSOR))
                 and (not offsets or len(offsets) > 2))
-        xin = (x if x.is_contiguous() else x.contiguous()) if io16 else _capi.f32c(x)
         hin = _capi.f32c(hidden)
         alive_u8 = _capi.u8(alive)
         done_u8 = _capi.u8(done)
         reset_u8 = _capi.u8(reset_env)
-        y = torch.empty_like(xin)
         hout = torch.empty_like(hin)
         sw = (_capi.SpatialWeights * max(1, n_blocks * n_spatial))()
         tw = (_capi.TemporalWeights * max(1, n_blocks * n_temporal))()
@@ -135,38 +133,34 @@ def trunk_forward(
             raise RuntimeError(f"expected {pos} parameter tensors for this trunk structure, got {len(weights)}")
         bul16 = (precision == _capi.BNB_BF16 and engine != _capi.ENGINE_SIMT and geom[G_MAX_TOKENS] > 0
                  and bool(_capi.lib.bnb_supported(D, n_heads, geom[G_MAX_TOKENS], _capi.BNB_BF16, _capi.ENGINE_TENSOR)))
-        bul = _capi.BulletArgs(bullets if n_cross > 0 else None, bullet_mask, T * batch.n_envs, D, keep_bf16=bul16)
-        nbytes = _capi.lib.bnb_scratch_bytes(D, batch, T, bul.per_env)
-        scratch = _capi.scratch_for(dev, nbytes)
         stream = _capi.stream_handle(dev)
         _raise_pending_status(dev)
         ns_total, nt_total = n_blocks * n_spatial, n_blocks * n_temporal
         if all(sw[i].packed for i in range(ns_total)) and all(tw[i].packed for i in range(nt_total)) and ns_total + nt_total > 0:
             # the weight images of the whole trunk, rewritten from the live parameters on every call
             _capi.check("bnb_pack_trunk", _capi.lib.bnb_pack_trunk(sw, ns_total, tw, nt_total, D, n_heads, stream))
-        if geom[G_TIMESTEPS] == 0:
-            fn = "bnb_trunk_step"
-            st = _capi.lib.bnb_trunk_step(
-                sw, tw, n_blocks, n_spatial, n_temporal, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8), bul.arg,
-                y.data_ptr(), _capi.ptr(hin), _capi.ptr(hout), _capi.ptr(reset_u8), batch,
-                _capi.BNB_BF16_IO if io16 else precision, engine, scratch.data_ptr(), scratch.numel(), stream,
-            )
-        else:
-            fn = "bnb_trunk_sequence"
-            st = _capi.lib.bnb_trunk_sequence(
-                sw, tw, n_blocks, n_spatial, n_temporal, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8), bul.arg,
-                y.data_ptr(), _capi.ptr(hin), _capi.ptr(hout), _capi.ptr(done_u8), batch, T,
-                _capi.BNB_BF16_IO if io16 else precision, engine, scratch.data_ptr(), scratch.numel(), stream,
-            )
-        if st == 3 and bul.is_bf16:
+        fn = "bnb_trunk_step" if geom[G_TIMESTEPS] == 0 else "bnb_trunk_sequence"
+
+        def run(tokens16: bool, bullets16: bool):
+            xin = (x if x.is_contiguous() else x.contiguous()) if tokens16 else _capi.f32c(x)
+            y = torch.empty_like(xin)
+            bul = _capi.BulletArgs(bullets if n_cross > 0 else None, bullet_mask, T * batch.n_envs, D, keep_bf16=bullets16)
+            scratch = _capi.scratch_for(dev, _capi.lib.bnb_scratch_bytes(D, batch, T, bul.per_env))
+            head = (sw, tw, n_blocks, n_spatial, n_temporal, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8), bul.arg,
+                    y.data_ptr(), _capi.ptr(hin), _capi.ptr(hout))
+            tail = (_capi.BNB_BF16_IO if tokens16 else precision, engine, scratch.data_ptr(), scratch.numel(), stream)
+            if geom[G_TIMESTEPS] == 0:
+                st = _capi.lib.bnb_trunk_step(*head, _capi.ptr(reset_u8), batch, *tail)
+            else:
+                st = _capi.lib.bnb_trunk_sequence(*head, _capi.ptr(done_u8), batch, T, *tail)
+            return st, y, bul.is_bf16
+
+        st, y, used_bul16 = run(io16, bul16)
+        if st == _capi.ERR_UNSUPPORTED_DIMS and (io16 or used_bul16):
             # the call fell to the float32-reading kernels (a shape the tensor-core kernels do not serve,
-            # e.g. more bullet slots than their attention stages): once more with float32 bullet tokens
-            bul = _capi.BulletArgs(bullets, bullet_mask, T * batch.n_envs, D)
-            call = _capi.lib.bnb_trunk_step if geom[G_TIMESTEPS] == 0 else _capi.lib.bnb_trunk_sequence
-            tail = ((_capi.ptr(reset_u8), batch) if geom[G_TIMESTEPS] == 0 else (_capi.ptr(done_u8), batch, T))
-            st = call(sw, tw, n_blocks, n_spatial, n_temporal, D, n_heads, xin.data_ptr(), _capi.ptr(alive_u8), bul.arg,
-                      y.data_ptr(), _capi.ptr(hin), _capi.ptr(hout), *tail, _capi.BNB_BF16_IO if io16 else precision, engine,
-                      scratch.data_ptr(), scratch.numel(), stream)
+            # e.g. more bullet slots than their attention stages; nothing was launched): once more with
+            # float32 copies of the tokens and the bullet tokens
+            st, y, _ = run(False, False)
     _capi.check(fn, st)
     _capi.note_engine_choice(fn)
     _debug_check(fn, dev, precision)

@@ -78,10 +78,12 @@ typedef enum {
    * hidden state and parameters stay float32.  This is what the reference's trunk sees on the GPU:
    * under torch.autocast("cuda", bfloat16) its encoder ends in an RMSNorm of a bf16 Linear output,
    * which is bf16, and its heads cast what the trunk returns to bf16.  The residual stream is still
-   * carried in float32 inside the call and rounded once, on the way out (the reference adds in
-   * bf16 after every sublayer).  Halves the bytes of the token tensors.  Served by the fused
-   * tensor-core kernel only (d_model 128, 4 heads, environments of at most 128 tokens, no
-   * bullets); any other call returns BNB_ERR_UNSUPPORTED_DIMS and the caller converts. */
+   * carried in float32 inside a launch and rounded on the way out (the reference adds in
+   * bf16 after every sublayer).  Halves the bytes of the token tensors.  Served by the tensor-core
+   * kernels only (d_model 128, 4 heads); any other call returns BNB_ERR_UNSUPPORTED_DIMS and the
+   * caller converts.  A call that takes several launches (environments larger than a tile, sublayers
+   * that read bullets, a time walk) rounds the residual stream where one launch hands over to the
+   * next. */
   BNB_BF16_IO = 2
 } BnbPrecision;
 

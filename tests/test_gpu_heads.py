@@ -83,6 +83,22 @@ def test_heads_match_the_reference_policy_heads(shape, mode):
     print(f"heads {shape} {mode}: " + " ".join(report))
 
 
+def test_head_reads_bfloat16_tokens_as_they_are():
+    """Under autocast a head handed bfloat16 tokens (the trunk's output dtype there) stages them
+    without a float32 copy (``BNB_BF16_IO``): bit-equal to the same values widened first; a width
+    whose hidden layer the tiled kernel is not built for (192) falls back to the float32-reading call."""
+    import boost_and_broadside_b200 as bnb
+
+    torch.manual_seed(3)
+    for d_model, out in ((128, 12), (64, 11), (96, 3)):
+        head = bnb.HeadMLP(d_model, out).to(DEV)
+        x16 = (torch.randn(1000, 7, d_model, device=DEV) * 0.7).to(torch.bfloat16)
+        with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
+            a, b = head(x16), head(x16.float())
+        assert a.dtype == torch.bfloat16 and tuple(a.shape) == (1000, 7, out)
+        assert torch.equal(a, b), d_model
+
+
 def test_head_on_an_empty_batch_and_a_wrong_width():
     import boost_and_broadside_b200 as bnb
 

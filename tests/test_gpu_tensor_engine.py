@@ -295,6 +295,33 @@ def test_bfloat16_bullet_tokens_equal_their_float32_copy(n_envs, ships, fields, 
     assert norm_err(y16.cpu(), ys.cpu()) < 1e-2
 
 
+@pytest.mark.parametrize("n_envs,ships,fields,nb", [(40, 8, 4, 80), (6, 100, 52, 33), (5, 100, 52, 0)])
+def test_bfloat16_tokens_on_the_multi_launch_paths(n_envs, ships, fields, nb):
+    """bfloat16 tokens in and out (``BNB_BF16_IO``) where the step takes several launches --
+    sublayers that read bullets, environments larger than a tile: y comes back bfloat16 without a
+    float32 copy on either side, the residual stream is rounded where one launch hands over to the
+    next, so it agrees with the float32-token call to bfloat16 rounding (<= 1e-2 normalised) and
+    the new state, which never passes through the token dtype's last rounding, to the same bound."""
+    from boost_and_broadside_b200 import workloads as W
+
+    _capi, SIMT, TENSOR = _engines()
+    w = W.c2(n_envs=n_envs, seed=41, ships=ships, fields=fields)
+    trunk = build_trunk([128, 4, 2, 2, 1, 1]).to(DEV)
+    x, alive, hidden = (t.to(DEV) for t in (w.x, w.alive, w.hidden))
+    x16 = x.to(torch.bfloat16)
+    bul16 = mask_d = None
+    if nb:
+        bul, mask = _bullets(n_envs, nb, 13)
+        bul16, mask_d = bul.to(DEV).to(torch.bfloat16), mask.to(DEV)
+    with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
+        y16, h16 = trunk.step(x16, alive, hidden, engine=TENSOR, bullets=bul16, bullet_mask=mask_d)
+        y32, h32 = trunk.step(x16.float(), alive, hidden, engine=TENSOR, bullets=bul16, bullet_mask=mask_d)
+    _status_ok()
+    assert y16.dtype == torch.bfloat16 and y32.dtype == torch.float32
+    assert norm_err(y16.float().cpu(), y32.cpu()) < 1e-2
+    assert norm_err(h16.cpu(), h32.cpu()) < 1e-2
+
+
 def test_bfloat16_bullet_tokens_on_a_shape_the_tensor_kernels_do_not_serve():
     """3000 bullet slots per environment are more than the attention kernel stages: the call is
     served by the float32-reading kernels, which refuse bfloat16 tokens (BNB_ERR_UNSUPPORTED_DIMS);
@@ -311,8 +338,12 @@ def test_bfloat16_bullet_tokens_on_a_shape_the_tensor_kernels_do_not_serve():
         with torch.no_grad(), torch.autocast(DEV, dtype=torch.bfloat16):
             y16, h16 = trunk.step(x, alive, hidden, bullets=bul16, bullet_mask=mask.to(DEV))
             y32, h32 = trunk.step(x, alive, hidden, bullets=bul16.float(), bullet_mask=mask.to(DEV))
+            # bfloat16 tokens as well: the same retry, and the module rounds the float32 result
+            yb, hb = trunk.step(x.to(torch.bfloat16), alive, hidden, bullets=bul16, bullet_mask=mask.to(DEV))
+            yf, hf = trunk.step(x.to(torch.bfloat16).float(), alive, hidden, bullets=bul16.float(), bullet_mask=mask.to(DEV))
     assert torch.equal(y16, y32) and torch.equal(h16, h32)
     assert bool(torch.isfinite(y16.float()).all())
+    assert yb.dtype == torch.bfloat16 and torch.equal(yb, yf.to(torch.bfloat16)) and torch.equal(hb, hf)
 
 
 def test_sequence_with_bullets_tensor_vs_oracle():
