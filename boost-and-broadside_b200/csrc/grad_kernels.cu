@@ -305,8 +305,10 @@ constexpr int TILE_H = BM * LDKH;
 
 // A_H / B_H / C_H: that operand lives in global memory as bfloat16 (the 4D-wide buffers of the gated
 // MLP in bf16 mode) instead of float32: it is then copied into shared memory as it is, or rounded
-// once on the way out.
-template <bool A_KC, bool B_KC, bool A_H, bool B_H, bool C_H>
+// once on the way out.  FULL: every tile of the launch lies inside the matrices and every K slice is
+// whole (M, N multiples of the tile, K and the split multiples of the slice), so no load or store
+// needs a bounds test.
+template <bool A_KC, bool B_KC, bool A_H, bool B_H, bool C_H, bool FULL>
 __global__ void __launch_bounds__(GT, 2) k_gemm_bf16(GemmArgs g) {
   static_assert(TILE_H >= BK * LDRH, "either orientation fits the tile buffer");
   // one buffer: two stages of A, two of B; a bfloat16 output tile is staged in it after the loop
@@ -348,17 +350,17 @@ __global__ void __launch_bounds__(GT, 2) k_gemm_bf16(GemmArgs g) {
       pb[i] = make_float4(0.f, 0.f, 0.f, 0.f);
       if constexpr (A_KC) {
         const int gm = m0 + (idx >> 3), gk = k0 + (idx & 7) * 4;
-        if (gm < g.M && gk < kend) pa[i] = fetch4(g.A, (size_t)gm * g.lda + gk, A_H);
+        if (FULL || (gm < g.M && gk < kend)) pa[i] = fetch4(g.A, (size_t)gm * g.lda + gk, A_H);
       } else {
         const int gk = k0 + (idx >> 5), gm = m0 + (idx & 31) * 4;
-        if (gk < kend && gm < g.M) pa[i] = fetch4(g.A, (size_t)gk * g.lda + gm, A_H);
+        if (FULL || (gk < kend && gm < g.M)) pa[i] = fetch4(g.A, (size_t)gk * g.lda + gm, A_H);
       }
       if constexpr (B_KC) {
         const int gn = n0 + (idx >> 3), gk = k0 + (idx & 7) * 4;
-        if (gn < g.N && gk < kend) pb[i] = fetch4(g.B, (size_t)gn * g.ldb + gk, B_H);
+        if (FULL || (gn < g.N && gk < kend)) pb[i] = fetch4(g.B, (size_t)gn * g.ldb + gk, B_H);
       } else {
         const int gk = k0 + (idx >> 5), gn = n0 + (idx & 31) * 4;
-        if (gk < kend && gn < g.N) pb[i] = fetch4(g.B, (size_t)gk * g.ldb + gn, B_H);
+        if (FULL || (gk < kend && gn < g.N)) pb[i] = fetch4(g.B, (size_t)gk * g.ldb + gn, B_H);
       }
     }
   };
@@ -434,7 +436,7 @@ __global__ void __launch_bounds__(GT, 2) k_gemm_bf16(GemmArgs g) {
     for (int i = 0; i < 8; ++i) {
       const int idx = tid + i * GT;
       const int row = idx >> 4, c8 = (idx & 15) * 8;
-      if (m0 + row < g.M && n0 + c8 < g.N)   // N is a multiple of 8
+      if (FULL || (m0 + row < g.M && n0 + c8 < g.N))   // N is a multiple of 8
         *reinterpret_cast<uint4*>(out + (size_t)(m0 + row) * g.ldc + n0 + c8) =
             *reinterpret_cast<const uint4*>(smem_all + row * LDO + c8);
     }
@@ -448,7 +450,7 @@ __global__ void __launch_bounds__(GT, 2) k_gemm_bf16(GemmArgs g) {
       for (int half = 0; half < 2; ++half) {
         const int row = m0 + wm + mt * 16 + gq + half * 8;
         const int col = n0 + wn + nt * 8 + 2 * t;   // even; N is even, so col + 1 < N whenever col < N
-        if (row < g.M && col < g.N) {
+        if (FULL || (row < g.M && col < g.N)) {
           float v0 = c[mt][nt][2 * half], v1 = c[mt][nt][2 * half + 1];
           float* cp = g.C + (size_t)row * g.ldc + col;
           if (g.atomic) {
@@ -472,6 +474,11 @@ __global__ void __launch_bounds__(GT, 2) k_gemm_bf16(GemmArgs g) {
 
 enum GemmMode { NT, NN, TN };
 
+// Whether no tile of the product needs a bounds test (see k_gemm_bf16's FULL).
+inline bool gemm_is_full(const GemmArgs& g) {
+  return g.M % BM == 0 && g.N % BN == 0 && g.K % BK == 0 && g.k_per_split % BK == 0;
+}
+
 // NT: C (M, N)  = A (M, K) . B (N, K)^T      y = x W^T
 // NN: C (M, N)  = A (M, K) . B (K, N)        dx = dy W
 // TN: C (M, N) += A (K, M)^T . B (K, N)      dW += dy^T x   (split over K, atomics)
@@ -486,9 +493,17 @@ void launch_gemm_t(const GemmArgs& g, dim3 grid, cudaStream_t st) {
 template <bool BF16>
 void launch_gemm(GemmMode mode, const GemmArgs& g, dim3 grid, cudaStream_t st) {
   if constexpr (BF16) {
-    if (mode == TN) k_gemm_bf16<false, false, false, false, false><<<grid, GT, 0, st>>>(g);
-    else if (mode == NT) k_gemm_bf16<true, true, false, false, false><<<grid, GT, 0, st>>>(g);
-    else k_gemm_bf16<true, false, false, false, false><<<grid, GT, 0, st>>>(g);
+    const bool full = gemm_is_full(g);
+    if (mode == TN) {
+      if (full) k_gemm_bf16<false, false, false, false, false, true><<<grid, GT, 0, st>>>(g);
+      else k_gemm_bf16<false, false, false, false, false, false><<<grid, GT, 0, st>>>(g);
+    } else if (mode == NT) {
+      if (full) k_gemm_bf16<true, true, false, false, false, true><<<grid, GT, 0, st>>>(g);
+      else k_gemm_bf16<true, true, false, false, false, false><<<grid, GT, 0, st>>>(g);
+    } else {
+      if (full) k_gemm_bf16<true, false, false, false, false, true><<<grid, GT, 0, st>>>(g);
+      else k_gemm_bf16<true, false, false, false, false, false><<<grid, GT, 0, st>>>(g);
+    }
   } else {
     if (mode == TN) launch_gemm_t<false, false, false>(g, grid, st);
     else if (mode == NT) launch_gemm_t<true, true, false>(g, grid, st);
@@ -523,8 +538,13 @@ int gemm_half(GemmMode mode, int halves, const void* A, int lda, const void* B, 
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, 1);
   count_launch();
   if (mode == TN) split_rows(g, grid, K);
-#define BNB_GEMM_CASE(MODE, HALVES, AKC, BKC, AH, BH, CH) \
-  if (mode == MODE && halves == (HALVES)) { k_gemm_bf16<AKC, BKC, AH, BH, CH><<<grid, GT, 0, st>>>(g); return BNB_OK; }
+  const bool full = gemm_is_full(g);
+#define BNB_GEMM_CASE(MODE, HALVES, AKC, BKC, AH, BH, CH)                             \
+  if (mode == MODE && halves == (HALVES)) {                                           \
+    if (full) k_gemm_bf16<AKC, BKC, AH, BH, CH, true><<<grid, GT, 0, st>>>(g);        \
+    else k_gemm_bf16<AKC, BKC, AH, BH, CH, false><<<grid, GT, 0, st>>>(g);            \
+    return BNB_OK;                                                                    \
+  }
   BNB_GEMM_CASE(NT, 0, true, true, false, false, false)
   BNB_GEMM_CASE(NT, H_A, true, true, true, false, false)
   BNB_GEMM_CASE(NT, H_C, true, true, false, false, true)

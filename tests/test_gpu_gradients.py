@@ -390,3 +390,46 @@ def test_reference_evaluate_actions_with_swapped_blocks(mode, grad_mode, checkpo
             worst = (k, e)
     assert checked > 80
     print(f"evaluate_actions {mode} ({grad_mode}, checkpoint {checkpoint}): {checked} parameter gradients, worst {worst[1]:.2e} ({worst[0]})")
+
+
+def test_aligned_shapes_take_the_unguarded_products_and_agree_with_the_guarded_ones():
+    """With every matrix a whole number of 128 x 128 tiles and 32-wide slices (here 32 environments x
+    8 ships x T = 4 = 1024 token rows, d_model 128) the bf16-mode products run without bounds tests.
+    Environments are independent, so the token and state gradients of those 32 environments must be
+    bit-identical when a 33rd environment is appended (1056 rows: the guarded kernels); and every
+    parameter gradient stays within the bf16 gate of the float32-mode gradient."""
+    dims = [128, 4, 2, 2, 1, 0, 8, 0]
+    D, N, T = 128, 8, 4
+    gen = torch.Generator().manual_seed(123)
+    trunk = build_trunk(dims).to(DEV).train()
+    with torch.no_grad():
+        for p in trunk.parameters():
+            p.add_(0.05 * torch.randn(p.shape, generator=gen).to(DEV))
+    L = trunk.n_hidden_layers
+
+    def make(B):
+        g = torch.Generator().manual_seed(7)
+        x = torch.randn(T, 33, N, D, generator=g)[:, :B].contiguous()
+        alive = (torch.rand(T, 33, N, generator=g) < 0.8)[:, :B].contiguous()
+        hidden = (torch.randn(L, 33, N, 4 * D, generator=g) * 0.5)[:, :B].reshape(L, B * N, 4 * D).contiguous()
+        done = (torch.rand(T, 33, generator=g) < 0.25)[:, :B].contiguous()
+        dy = torch.randn(T, 33, N, D, generator=g)[:, :B].contiguous()
+        return [t.to(DEV) for t in (x, alive, hidden, done, dy)]
+
+    def backward(B, bf16):
+        x, alive, hidden, done, dy = make(B)
+        trunk.zero_grad(set_to_none=True)
+        xg, hg = x.requires_grad_(True), hidden.requires_grad_(True)
+        ctx = torch.autocast(DEV, dtype=torch.bfloat16) if bf16 else torch.autocast(DEV, enabled=False)
+        with ctx:
+            y, nh = trunk.sequence(xg, alive, hg, done)
+        ((y.float() * dy).sum() + nh.sum()).backward()
+        return xg.grad, hg.grad.reshape(L, B, N, 4 * D), {k: p.grad.clone() for k, p in trunk.named_parameters() if p.grad is not None}
+
+    dx32, dh32, g32 = backward(32, True)
+    dx33, dh33, _ = backward(33, True)
+    assert torch.equal(dx32, dx33[:, :32]) and torch.equal(dh32, dh33[:, :32])
+    _, _, gref = backward(32, False)
+    worst = max((norm_err(g32[k].cpu(), gref[k].cpu()), k) for k in gref if float(gref[k].abs().max()) > 0)
+    print(f"aligned bf16 products vs float32-mode gradients: worst normalised error {worst[0]:.2e} ({worst[1]})")
+    assert worst[0] <= 3e-2
