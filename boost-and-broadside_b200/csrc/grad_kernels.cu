@@ -661,6 +661,54 @@ __global__ void __launch_bounds__(256) k_rmsnorm_bwd(const float* __restrict__ x
   }
 }
 
+// The same for rows of exactly 128 columns: a lane owns four consecutive columns (one 16-byte load per
+// array) and a warp keeps two rows in flight.
+__global__ void __launch_bounds__(256) k_rmsnorm_bwd_128(const float* __restrict__ x, const float* __restrict__ g,
+                                                         const float* __restrict__ inv, const float* __restrict__ dn,
+                                                         const float* dres, float* dx, float* __restrict__ dg, int rows) {
+  __shared__ float4 sdg[8][32];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+  const float4 gv = reinterpret_cast<const float4*>(g)[lane];
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int r0 = 2 * warp; r0 < rows; r0 += 2 * nwarps) {
+    const bool two = r0 + 1 < rows;
+    const size_t o0 = (size_t)r0 * 32 + lane, o1 = o0 + 32;
+    const float4 x0 = reinterpret_cast<const float4*>(x)[o0], d0 = reinterpret_cast<const float4*>(dn)[o0];
+    float4 x1 = make_float4(0.f, 0.f, 0.f, 0.f), d1 = x1, e0 = x1, e1 = x1;
+    if (two) {
+      x1 = reinterpret_cast<const float4*>(x)[o1];
+      d1 = reinterpret_cast<const float4*>(dn)[o1];
+    }
+    if (dres) {
+      e0 = reinterpret_cast<const float4*>(dres)[o0];
+      if (two) e1 = reinterpret_cast<const float4*>(dres)[o1];
+    }
+    float dot0 = fmaf(x0.x * gv.x, d0.x, fmaf(x0.y * gv.y, d0.y, fmaf(x0.z * gv.z, d0.z, x0.w * gv.w * d0.w)));
+    float dot1 = fmaf(x1.x * gv.x, d1.x, fmaf(x1.y * gv.y, d1.y, fmaf(x1.z * gv.z, d1.z, x1.w * gv.w * d1.w)));
+    dot0 = warp_sum(dot0);
+    dot1 = warp_sum(dot1);
+    const float iv0 = inv[r0], iv1 = two ? inv[r0 + 1] : 0.f;
+    const float c0 = dot0 * iv0 * iv0 * iv0 * (1.0f / 128.0f), c1 = dot1 * iv1 * iv1 * iv1 * (1.0f / 128.0f);
+    reinterpret_cast<float4*>(dx)[o0] = make_float4(iv0 * gv.x * d0.x - x0.x * c0 + e0.x, iv0 * gv.y * d0.y - x0.y * c0 + e0.y,
+                                                    iv0 * gv.z * d0.z - x0.z * c0 + e0.z, iv0 * gv.w * d0.w - x0.w * c0 + e0.w);
+    if (two)
+      reinterpret_cast<float4*>(dx)[o1] = make_float4(iv1 * gv.x * d1.x - x1.x * c1 + e1.x, iv1 * gv.y * d1.y - x1.y * c1 + e1.y,
+                                                      iv1 * gv.z * d1.z - x1.z * c1 + e1.z, iv1 * gv.w * d1.w - x1.w * c1 + e1.w);
+    acc.x += d0.x * x0.x * iv0 + d1.x * x1.x * iv1;
+    acc.y += d0.y * x0.y * iv0 + d1.y * x1.y * iv1;
+    acc.z += d0.z * x0.z * iv0 + d1.z * x1.z * iv1;
+    acc.w += d0.w * x0.w * iv0 + d1.w * x1.w * iv1;
+  }
+  sdg[wib][lane] = acc;
+  __syncthreads();
+  if (dg && threadIdx.x < 128) {
+    float s = 0.f;
+    for (int w = 0; w < 8; ++w) s += reinterpret_cast<const float*>(&sdg[w][0])[threadIdx.x];
+    atomicAdd(dg + threadIdx.x, s);
+  }
+}
+
 __device__ __forceinline__ float gelu_grad(float v) {
   const float cdf = 0.5f * (1.0f + erff(v * 0.70710678118654752440f));
   return cdf + v * 0.39894228040143267794f * expf(-0.5f * v * v);
@@ -1439,7 +1487,11 @@ void rmsnorm_bwd(const Ctx& c, const float* x, const float* g, const float* inv,
                  float* dx, float* dg, size_t rows) {
   if (!rows) return;
   count_launch();
-  k_rmsnorm_bwd<<<blocks_for(rows, 64, 148 * 8), 256, 0, c.st>>>(x, g, inv, dn, dres, dx, dg, (int)rows, c.D);
+  const auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (c.D == 128 && al(x) && al(g) && al(dn) && al(dx) && (!dres || al(dres)))
+    k_rmsnorm_bwd_128<<<blocks_for(rows, 64, 148 * 8), 256, 0, c.st>>>(x, g, inv, dn, dres, dx, dg, (int)rows);
+  else
+    k_rmsnorm_bwd<<<blocks_for(rows, 64, 148 * 8), 256, 0, c.st>>>(x, g, inv, dn, dres, dx, dg, (int)rows, c.D);
 }
 void gelu_mul_fwd(const Ctx& c, const float* g, const float* u, float* h, size_t n) {
   if (!n) return;
