@@ -13,6 +13,7 @@
 // of the reference.
 #include "common.cuh"
 #include "exact_kernels.h"
+#include "grad_kernels.h"
 #include "launch_count.h"
 
 namespace bnb {
@@ -847,19 +848,38 @@ k_team_pool(const float* __restrict__ kv, const float* __restrict__ q, const int
     if (e < n_envs) {
       const size_t base = (size_t)e * N;
       // scores of this team's alive ships, per head
-      for (int n = lane; n < N; n += 32) {
-        const bool ok = team_id[base + n] == t && alive[base + n];
-        const float* kp = kv + (base + n) * 2 * D;
-        for (int h = 0; h < H; ++h) {
-          float acc = -INFINITY;
+      if ((D & 31) == 0 && D <= 128 && (32 % H) == 0) {
+        // the warp reads one ship's key row at a time (contiguous): a lane owns D / 32 consecutive
+        // channels, the 32 / H lanes of a head add their partial dot products up
+        const int dpl = D >> 5, lph = 32 / H;
+        float qv[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int j = 0; j < dpl; ++j) qv[j] = q[t * D + lane * dpl + j];
+        for (int n = 0; n < N; ++n) {
+          const bool ok = team_id[base + n] == t && alive[base + n];   // the same in every lane
+          float part = 0.f;
           if (ok) {
-            acc = 0.f;
-            for (int d = 0; d < dh; ++d) acc = fmaf(q[t * D + h * dh + d], kp[h * dh + d], acc);
-            acc *= scale;
+            const float* kp = kv + (base + n) * 2 * D + lane * dpl;
+            for (int j = 0; j < dpl; ++j) part = fmaf(qv[j], rnd<EMU>(kp[j]), part);
           }
-          my[n * H + h] = acc;
+          for (int o = lph >> 1; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+          if ((lane & (lph - 1)) == 0) my[n * H + lane / lph] = ok ? part * scale : -INFINITY;
+          any |= ok;
         }
-        any |= ok;
+      } else {
+        for (int n = lane; n < N; n += 32) {
+          const bool ok = team_id[base + n] == t && alive[base + n];
+          const float* kp = kv + (base + n) * 2 * D;
+          for (int h = 0; h < H; ++h) {
+            float acc = -INFINITY;
+            if (ok) {
+              acc = 0.f;
+              for (int d = 0; d < dh; ++d) acc = fmaf(q[t * D + h * dh + d], rnd<EMU>(kp[h * dh + d]), acc);
+              acc *= scale;
+            }
+            my[n * H + h] = acc;
+          }
+          any |= ok;
+        }
       }
       any = __any_sync(0xffffffffu, any);
       __syncwarp();
@@ -887,7 +907,7 @@ k_team_pool(const float* __restrict__ kv, const float* __restrict__ q, const int
       float acc = 0.f;
       if (e < n_envs && any) {
         const int h = c / dh;
-        for (int n = 0; n < N; ++n) acc = fmaf(my[n * H + h], kv[((size_t)e * N + n) * 2 * D + D + c], acc);
+        for (int n = 0; n < N; ++n) acc = fmaf(my[n * H + h], rnd<EMU>(kv[((size_t)e * N + n) * 2 * D + D + c]), acc);
       }
       P[r * ld + c] = rnd<EMU>(acc);
     }
@@ -1143,11 +1163,17 @@ static int team_pma_impl(const float* seeds, const float* in_proj_w, const float
                          const float* x, const int32_t* team_id, const uint8_t* alive, void* y, bool y_bf16, int n_envs, int N,
                          float* kv, float* q, cudaStream_t st) {
   const int n_rows = n_envs * N;
-  const size_t sm_qkv = (size_t)(2 * ROWS * (D + 4) + NCHUNK * WS_STRIDE) * sizeof(float);
-  if (!opt_in(k_spatial_qkv<EMU>, sm_qkv)) return BNB_ERR_LAUNCH;
-  count_launch();
-  k_spatial_qkv<EMU><<<(n_rows + ROWS - 1) / ROWS, NTHREADS, sm_qkv, st>>>(x, kv, n_rows, D, 2 * D, nullptr,
-                                                                          in_proj_w + (size_t)D * D);
+  if (EMU) {
+    // keys and values under the bfloat16 contract: operands rounded to bfloat16 inside the tiled
+    // product, float32 accumulation; k_team_pool rounds the results as it reads them
+    grad::linear_nt(x, in_proj_w + (size_t)D * D, kv, n_rows, 2 * D, D, true, st);
+  } else {
+    const size_t sm_qkv = (size_t)(2 * ROWS * (D + 4) + NCHUNK * WS_STRIDE) * sizeof(float);
+    if (!opt_in(k_spatial_qkv<EMU>, sm_qkv)) return BNB_ERR_LAUNCH;
+    count_launch();
+    k_spatial_qkv<EMU><<<(n_rows + ROWS - 1) / ROWS, NTHREADS, sm_qkv, st>>>(x, kv, n_rows, D, 2 * D, nullptr,
+                                                                            in_proj_w + (size_t)D * D);
+  }
   count_launch();
   k_team_query<EMU><<<1, 256, 0, st>>>(seeds, in_proj_w, q, D);
   const int ld = (D > NCHUNK ? D : NCHUNK) + 4;

@@ -1893,6 +1893,10 @@ void layout_kept(Arena& ar, Kept& k, const Walk& wk, int n_blocks, int n_spatial
 
 }  // namespace
 
+void linear_nt(const float* x, const float* W, float* y, int M, int N, int K, bool bf16_operands, cudaStream_t st) {
+  gemm(NT, x, K, W, K, y, N, M, N, K, nullptr, nullptr, 0, 0, st, bf16_operands);
+}
+
 size_t scratch_bytes(int n_blocks, int n_spatial, int n_temporal, int D, const BnbBatch& bt, int T, int bullets_per_env,
                      bool bf16) {
   Arena ar{nullptr};

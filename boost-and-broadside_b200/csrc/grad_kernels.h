@@ -62,6 +62,10 @@ size_t scratch_bytes(int n_blocks, int n_spatial, int n_temporal, int D, const B
 size_t kept_bytes(int n_blocks, int n_spatial, int n_temporal, int D, int H, const BnbBatch& b, int T, int bullets_per_env,
                   bool bf16);
 
+// y (M, N) = x (M, K) . W (N, K)^T, row-major, on the tiled product kernels: with bf16_operands the
+// operands are rounded to bfloat16 and accumulated in float32 (y is not rounded), else 3 x tf32.
+void linear_nt(const float* x, const float* W, float* y, int M, int N, int K, bool bf16_operands, cudaStream_t st);
+
 int trunk_sequence_fwd_train(const TrunkFwdTrainArgs& a);
 int trunk_sequence_bwd(const TrunkBwdArgs& a);
 
