@@ -37,7 +37,9 @@ using tensor::smem_u32;
 namespace {
 
 constexpr int SLICE = 16;      // rows per warp slice (one mma.sync row block)
-constexpr int MAX_WARPS = 16;
+// Warps per CTA: 16 where the output accumulators take 64 registers (out_dim 128), 28 where they
+// take 16 (out_dim 32: the heads, whose 65 536 rows are then one 16-row slice per warp of the grid).
+__host__ __device__ constexpr int max_warps(int out_dim) { return out_dim <= 32 ? 28 : 16; }
 constexpr int PAD = 8;         // bf16 elements of padding per staged row: ldmatrix stays conflict-free
 constexpr size_t SMEM_MAX = 227 * 1024;
 
@@ -58,7 +60,7 @@ __host__ __device__ inline Layout layout(int in_pad, int hidden, int out_dim) {
   l.per_warp = (size_t)SLICE * l.ldx * 2;                        // a warp's staged input rows
   const size_t room = SMEM_MAX > off ? SMEM_MAX - off : 0;
   int w = (int)(room / l.per_warp);
-  w = w > MAX_WARPS ? MAX_WARPS : w & ~1;
+  w = w > max_warps(out_dim) ? max_warps(out_dim) : w & ~1;
   l.warps = w;
   l.total = off + (size_t)w * l.per_warp;
   return l;
@@ -92,7 +94,7 @@ __device__ __forceinline__ void linear1_chunk(float (&acc)[8][4], uint32_t sX, u
 // loop over fragments unrolls without guards; so is IN16, the 16-wide k steps of the first product
 // (in_pad = 16 IN16).
 template <int NP2, int NCH, int IN16>
-__global__ void __launch_bounds__(32 * MAX_WARPS, 1)
+__global__ void __launch_bounds__(32 * max_warps(16 * NP2), 1)
 k_mlp_bf16(const float* __restrict__ x, int x_bf16, __nv_bfloat16* __restrict__ y, int n_rows, int in_dim, int in_pad, int hidden,
            int out_dim, int out_store, const float* __restrict__ w1, const float* __restrict__ b1,
            const float* __restrict__ g1, const float* __restrict__ w2, const float* __restrict__ b2,
