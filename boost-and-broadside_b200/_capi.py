@@ -18,7 +18,7 @@ LIB_PATH = os.path.join(_HERE, "libbnb_trunk.so")
 BNB_FP32, BNB_BF16, BNB_BF16_IO = 0, 1, 2
 ERR_UNSUPPORTED_DIMS = 3   # BNB_ERR_UNSUPPORTED_DIMS: the kernels asked for do not serve these shapes / dtypes
 ENGINE_AUTO, ENGINE_SIMT, ENGINE_TENSOR = 0, 1, 2
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 _fp = C.c_void_p
 

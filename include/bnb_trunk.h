@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define BNB_ABI_VERSION 2
+#define BNB_ABI_VERSION 3 /* 3: BnbBullets.tokens_bf16; BNB_BF16_IO accepted by bnb_head_mlp_fwd and on multi-launch trunk calls */
 #define BNB_CONV_KERNEL 4 /* models/yemong/griffin.py:22 */
 
 typedef enum {

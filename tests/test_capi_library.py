@@ -29,7 +29,7 @@ def test_library_exports_every_declared_symbol():
     lib = C.CDLL(_capi.LIB_PATH)
     for name in declared_functions():
         assert hasattr(lib, name), f"{name} is declared in bnb_trunk.h but not exported"
-    assert _capi.lib.bnb_abi_version() == 2
+    assert _capi.lib.bnb_abi_version() == 3
     assert _capi.lib.bnb_status_string(0) == b"ok"
     assert b"null" in _capi.lib.bnb_status_string(1)
 
