@@ -10,7 +10,7 @@
 // once, and so is the GELU.  The float32 contract stays on the CUDA-core engine (exact_kernels.cu).
 //
 // One persistent CTA per SM: both weight matrices are converted to bfloat16 once per CTA and stay in
-// shared memory.  After that the warps (up to 16) are independent: each walks slices of 16 rows of
+// shared memory.  After that the warps (up to 16, 28 for the heads) are independent: each walks slices of 16 rows of
 // its own, stages the slice's input rows in its own shared-memory rows and keeps everything else in
 // registers.  The hidden activations never leave the register file: the accumulator fragment of
 // Linear 1 (row g, columns 2t, 2t+1 of two adjacent 8-column blocks) is exactly the A fragment of
