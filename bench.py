@@ -544,6 +544,21 @@ def time_other_workloads(trunk, dev: torch.device, n_params_all: int, cfg, steps
             out[name] = {"workload": WORKLOAD_TEXT[name], "ms_per_step": ms, "value": w.entity_tokens / (ms * 1e-3), "unit": UNIT,
                          "steps": steps, "hbm_frac": alg_bytes / (ms * 1e-3) / 1e9 / hbm,
                          "tensor_frac_of_burst": alg_flops / (ms * 1e-3) / 1e12 / tflops_burst, "of": src}
+            if w.kind != "sequence":
+                # the same step with bfloat16 tokens (and bullet tokens), as the reference's encoders hand
+                # them over under CUDA autocast: no float32 copies on either side of the kernels
+                x, bul = x.to(torch.bfloat16), None if bul is None else bul.to(torch.bfloat16)
+                with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+                    for _ in range(3):
+                        _, h = run(h)
+                    torch.cuda.synchronize(dev)
+                    e0.record()
+                    for _ in range(steps):
+                        _, h = run(h)
+                    e1.record()
+                    torch.cuda.synchronize(dev)
+                ms16 = e0.elapsed_time(e1) / steps
+                out[name]["bf16_tokens"] = {"ms_per_step": ms16, "value": w.entity_tokens / (ms16 * 1e-3), "unit": UNIT}
             del x, alive, hidden, h, h2, w
         except Exception as e:  # noqa: BLE001 - a side record that fails is reported, not fatal
             out[name] = {"error": repr(e)[:200]}
