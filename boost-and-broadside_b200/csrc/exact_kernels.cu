@@ -813,11 +813,16 @@ k_encoder_mlp(const float* __restrict__ x, void* __restrict__ y, int n_rows, int
 // q[t] = W_q seeds[t] for the two team seeds (one block).
 template <bool EMU>
 __global__ void k_team_query(const float* __restrict__ seeds, const float* __restrict__ Wq, float* __restrict__ q, int D) {
-  for (int o = threadIdx.x; o < 2 * D; o += blockDim.x) {
+  // one warp per output: the lanes read a row of Wq contiguously and add their partial sums up
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  for (int o = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; o < 2 * D; o += warps) {
     const int t = o / D, c = o - t * D;
     float acc = 0.f;
-    for (int k = 0; k < D; ++k) acc = fmaf(rnd<EMU>(seeds[t * D + k]), rnd<EMU>(Wq[(size_t)c * D + k]), acc);
-    q[o] = rnd<EMU>(acc);
+    for (int k = lane; k < D; k += 32) acc = fmaf(rnd<EMU>(seeds[t * D + k]), rnd<EMU>(Wq[(size_t)c * D + k]), acc);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (lane == 0) q[o] = rnd<EMU>(acc);
   }
 }
 
@@ -1175,7 +1180,7 @@ static int team_pma_impl(const float* seeds, const float* in_proj_w, const float
                                                                             in_proj_w + (size_t)D * D);
   }
   count_launch();
-  k_team_query<EMU><<<1, 256, 0, st>>>(seeds, in_proj_w, q, D);
+  k_team_query<EMU><<<(2 * D + 7) / 8, 256, 0, st>>>(seeds, in_proj_w, q, D);
   const int ld = (D > NCHUNK ? D : NCHUNK) + 4;
   const size_t sm = (size_t)(ROWS * ld + NCHUNK * WS_STRIDE + (NTHREADS / 32) * N * H) * sizeof(float);
   if (sm > 200 * 1024) return BNB_ERR_TOO_MANY_TOKENS;
